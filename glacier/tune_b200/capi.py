@@ -1,0 +1,267 @@
+"""ctypes binding of libglaciertune_b200.so - the same C ABI a C# ``[LibraryImport]`` host binds.
+
+Host arrays are numpy (C-contiguous fp32 / uint8); device arrays are anything with a ``data_ptr()`` (torch
+tensors on the engine's device).  Every failure raises :class:`GtError` carrying ``gt_last_error()``;
+nothing here falls back to a CPU implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build as _build
+
+TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
+MATH_BF16, MATH_FP16, MATH_FP32 = 0, 1, 2
+DIR_FORWARD, DIR_BACKWARD = 0, 1
+FLAG_DEVICE_PTRS, FLAG_NO_LORA = 1, 2
+
+EXPORTS = [
+    "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
+    "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
+    "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
+    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward",
+    "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_grads_scale_clip",
+    "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
+]
+
+
+class GtError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"glaciertune_b200 error {code}: {msg}")
+        self.code = code
+
+
+class GtConfig(C.Structure):
+    _fields_ = [("device", C.c_int32), ("math_mode", C.c_int32), ("stream", C.c_void_p), ("max_tokens", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+_lib = None
+
+
+def load_library(path: str | None = None) -> C.CDLL:
+    """Load the shared library (building it in-tree when the sources are newer and nvcc is present)."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or _build.LIB_PATH
+    if path is None and _build.is_stale():
+        try:
+            _build.build()
+        except Exception as exc:  # noqa: BLE001 - a stale/missing library is fatal, never a fallback
+            if not os.path.exists(p):
+                raise RuntimeError(f"libglaciertune_b200.so is missing and could not be built: {exc}") from exc
+    lib = C.CDLL(p, mode=C.RTLD_GLOBAL)
+    lib.gt_last_error.restype = C.c_char_p
+    lib.gt_version.restype = C.c_char_p
+    lib.gt_engine_create.argtypes = [C.POINTER(GtConfig), C.POINTER(C.c_void_p)]
+    lib.gt_engine_destroy.argtypes = [C.c_void_p]
+    lib.gt_engine_set_math_mode.argtypes = [C.c_void_p, C.c_int]
+    lib.gt_sync.argtypes = [C.c_void_p]
+    lib.gt_supports.argtypes = [C.c_int, C.c_int]
+    lib.gt_weight_upload.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p,
+                                     C.POINTER(C.c_void_p)]
+    lib.gt_weight_free.argtypes = [C.c_void_p]
+    lib.gt_dequant_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int32]
+    lib.gt_adapter_create.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.POINTER(C.c_void_p)]
+    lib.gt_adapter_free.argtypes = [C.c_void_p]
+    for name in ("gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_bind_grads"):
+        getattr(lib, name).argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.gt_adapter_grads_zero.argtypes = [C.c_void_p]
+    lib.gt_adapter_set_alpha.argtypes = [C.c_void_p, C.c_float]
+    lib.gt_adapter_device_ptrs.argtypes = [C.c_void_p] + [C.POINTER(C.c_void_p)] * 4
+    lib.gt_proj_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
+    lib.gt_proj_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                     C.c_int32]
+    lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
+    lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
+    lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
+    if hasattr(lib, "gt_dp_init"):
+        lib.gt_dp_unique_id.argtypes = [C.c_void_p, C.c_int32]
+        lib.gt_dp_init.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32]
+        lib.gt_dp_allreduce.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float]
+        lib.gt_dp_finalize.argtypes = [C.c_void_p]
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise GtError(rc, load_library().gt_last_error().decode(errors="replace"))
+
+
+def _ptr(a, dtype=None):
+    """(address, is_device) of a numpy array or a device tensor."""
+    if a is None:
+        return None, False
+    if hasattr(a, "data_ptr"):
+        if not a.is_contiguous():
+            raise ValueError("device tensors must be contiguous")
+        return C.c_void_p(a.data_ptr()), bool(getattr(a, "is_cuda", False))
+    if not isinstance(a, np.ndarray) or not a.flags.c_contiguous or (dtype is not None and a.dtype != dtype):
+        raise ValueError(f"host arrays must be C-contiguous numpy {dtype}")
+    return a.ctypes.data_as(C.c_void_p), False
+
+
+def supports(ggml_type: int, direction: int) -> bool:
+    return bool(load_library().gt_supports(ggml_type, direction))
+
+
+class Engine:
+    """One CUDA context user: stream, scratch, math mode (replaces GpuLoraEngine's construction)."""
+
+    def __init__(self, device: int = 0, math_mode: int = MATH_BF16, stream: int | None = None):
+        self.lib = load_library()
+        cfg = GtConfig(device=device, math_mode=math_mode, stream=C.c_void_p(stream) if stream else None, max_tokens=0)
+        h = C.c_void_p()
+        _check(self.lib.gt_engine_create(C.byref(cfg), C.byref(h)))
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.gt_engine_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+    def set_math_mode(self, mode: int):
+        _check(self.lib.gt_engine_set_math_mode(self.h, mode))
+
+    def sync(self):
+        _check(self.lib.gt_sync(self.h))
+
+    def upload_weight(self, ggml_type: int, data: np.ndarray, out_features: int, in_features: int, bias=None) -> "Weight":
+        data = np.ascontiguousarray(data)
+        bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        h = C.c_void_p()
+        _check(self.lib.gt_weight_upload(self.h, ggml_type, data.ctypes.data_as(C.c_void_p), data.nbytes, out_features,
+                                         in_features, None if bias is None else bias.ctypes.data_as(C.c_void_p),
+                                         C.byref(h)))
+        return Weight(self, h, ggml_type, out_features, in_features)
+
+    def create_adapter(self, in_features: int, out_features: int, rank: int = 16, alpha: float = 32.0) -> "Adapter":
+        h = C.c_void_p()
+        _check(self.lib.gt_adapter_create(self.h, in_features, out_features, rank, alpha, C.byref(h)))
+        return Adapter(self, h, in_features, out_features, rank)
+
+    # ---- projection calls -------------------------------------------------------------------------
+    def forward(self, w: "Weight", adapter, X, Y=None, flags: int = 0):
+        """Y[T, out] = X W^T + bias + scaling (X A) B.  Host numpy in -> numpy out; device tensors need Y."""
+        xp, dev = _ptr(X, np.float32)
+        T = X.shape[0]
+        if dev:
+            assert Y is not None
+            flags |= FLAG_DEVICE_PTRS
+        elif Y is None:
+            Y = np.empty((T, w.N), np.float32)
+        yp, _ = _ptr(Y, np.float32)
+        _check(self.lib.gt_proj_forward(self.h, w.h, adapter.h if adapter else None, xp, yp, T, flags))
+        return Y
+
+    def backward(self, w: "Weight", adapter, dY, X, dX=None, flags: int = 0):
+        """dX += dY W + adapter term; adapter grads accumulate.  dX None skips the input gradient."""
+        gp, dev = _ptr(dY, np.float32)
+        xp, _ = _ptr(X, np.float32)
+        dp, _ = _ptr(dX, np.float32)
+        if dev:
+            flags |= FLAG_DEVICE_PTRS
+        _check(self.lib.gt_proj_backward(self.h, w.h, adapter.h if adapter else None, gp, xp, dp, dY.shape[0], flags))
+        return dX
+
+    def launch_gemm_batch(self, w: "Weight", Y, X, batch: int, residual=None):
+        yp, _ = _ptr(Y)
+        xp, _ = _ptr(X)
+        rp, _ = _ptr(residual)
+        _check(self.lib.gt_launch_gemm_batch(self.h, w.h, yp, xp, batch, rp))
+
+    def launch_gemm_bwd(self, w: "Weight", dX, dY, batch: int):
+        _check(self.lib.gt_launch_gemm_bwd(self.h, w.h, _ptr(dX)[0], _ptr(dY)[0], batch))
+
+    def dequant_rows(self, w: "Weight", row0: int, nrows: int, out=None):
+        if out is None:
+            out = np.empty((nrows, w.K), np.float32)
+        op, dev = _ptr(out, np.float32)
+        _check(self.lib.gt_dequant_rows(self.h, w.h, row0, nrows, op, FLAG_DEVICE_PTRS if dev else 0))
+        return out
+
+    def grads_scale_clip(self, g_dev, pre_scale: float, max_norm: float) -> float:
+        norm = C.c_double()
+        _check(self.lib.gt_grads_scale_clip(self.h, _ptr(g_dev)[0], g_dev.numel(), pre_scale, max_norm, C.byref(norm)))
+        return norm.value
+
+    # ---- data parallel ----------------------------------------------------------------------------
+    def dp_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(128)
+        _check(self.lib.gt_dp_unique_id(buf, 128))
+        return buf.raw
+
+    def dp_init(self, world: int, rank: int, unique_id: bytes):
+        _check(self.lib.gt_dp_init(self.h, world, rank, C.c_char_p(unique_id), len(unique_id)))
+
+    def dp_allreduce(self, g_dev, scale: float = 1.0):
+        _check(self.lib.gt_dp_allreduce(self.h, _ptr(g_dev)[0], g_dev.numel(), scale))
+
+    def dp_finalize(self):
+        _check(self.lib.gt_dp_finalize(self.h))
+
+
+class Weight:
+    def __init__(self, eng: Engine, h, qtype: int, N: int, K: int):
+        self.eng, self.h, self.qtype, self.N, self.K = eng, h, qtype, N, K
+
+    def free(self):
+        if self.h:
+            self.eng.lib.gt_weight_free(self.h)
+            self.h = None
+
+
+class Adapter:
+    def __init__(self, eng: Engine, h, in_features: int, out_features: int, rank: int):
+        self.eng, self.h, self.K, self.N, self.rank = eng, h, in_features, out_features, rank
+
+    def upload(self, A=None, B=None):
+        A = None if A is None else np.ascontiguousarray(A, np.float32)
+        B = None if B is None else np.ascontiguousarray(B, np.float32)
+        assert A is None or A.shape == (self.K, self.rank)
+        assert B is None or B.shape == (self.rank, self.N)
+        _check(self.eng.lib.gt_adapter_upload(self.h, _ptr(A)[0], _ptr(B)[0]))
+
+    def download(self):
+        A = np.empty((self.K, self.rank), np.float32)
+        B = np.empty((self.rank, self.N), np.float32)
+        _check(self.eng.lib.gt_adapter_download(self.h, _ptr(A)[0], _ptr(B)[0]))
+        return A, B
+
+    def grads(self):
+        dA = np.empty((self.K, self.rank), np.float32)
+        dB = np.empty((self.rank, self.N), np.float32)
+        _check(self.eng.lib.gt_adapter_grads_download(self.h, _ptr(dA)[0], _ptr(dB)[0]))
+        return dA, dB
+
+    def zero_grads(self):
+        _check(self.eng.lib.gt_adapter_grads_zero(self.h))
+
+    def set_alpha(self, alpha: float):
+        _check(self.eng.lib.gt_adapter_set_alpha(self.h, alpha))
+
+    def bind_grads(self, dA_dev, dB_dev):
+        _check(self.eng.lib.gt_adapter_bind_grads(self.h, _ptr(dA_dev)[0], _ptr(dB_dev)[0]))
+
+    def device_ptrs(self):
+        ps = [C.c_void_p() for _ in range(4)]
+        _check(self.eng.lib.gt_adapter_device_ptrs(self.h, *[C.byref(p) for p in ps]))
+        return [p.value for p in ps]
+
+    def free(self):
+        if self.h:
+            self.eng.lib.gt_adapter_free(self.h)
+            self.h = None

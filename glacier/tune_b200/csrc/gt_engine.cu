@@ -1,0 +1,704 @@
+// C ABI of libglaciertune_b200.so (declared in include/glaciertune_b200.h): engine, weight upload,
+// adapters, projection forward / backward.  Host-side orchestration only; kernels are in
+// gt_fp32_kernels.cu (CUDA cores) and gt_umma_gemm.cu (tcgen05).
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../../include/glaciertune_b200.h"
+#include "gt_internal.h"
+#include "gt_quant.cuh"
+
+using namespace gt;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define GT_CUDA(call)                                                                                   \
+    do {                                                                                                \
+        cudaError_t _e = (call);                                                                        \
+        if (_e != cudaSuccess) return fail(GT_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(_e)); \
+    } while (0)
+
+// grow-only device buffer (the reference engine grows its scratch x2 on demand and never shrinks:
+// src/Glacier.Tune/Gpu/GpuLoraEngine.Memory.cs:7-114)
+struct Scratch {
+    void *p = nullptr;
+    size_t cap = 0;
+    cudaError_t reserve(size_t bytes) {
+        if (bytes <= cap) return cudaSuccess;
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+        size_t want = bytes + bytes / 4;
+        cudaError_t e = cudaMalloc(&p, want);
+        if (e == cudaSuccess) cap = want;
+        return e;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+    }
+};
+
+}  // namespace
+
+struct gt_engine {
+    int device = 0;
+    int math_mode = GT_MATH_BF16;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    std::mutex mu;
+    int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
+    double *clip = nullptr;      // device double[2]
+    Scratch x16, dy16, low, low16, dlow, dlow16, ytmp;
+    Scratch h_in0, h_in1, h_out;  // device staging for host-pointer calls
+    ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
+    int dp_world = 1, dp_rank = 0;
+};
+
+struct gt_weight {
+    gt_engine *eng = nullptr;
+    WeightDev dev;
+};
+
+struct gt_adapter {
+    gt_engine *eng = nullptr;
+    int in = 0, out = 0, rank = 0;
+    float alpha = 0.f, scaling = 0.f;
+    float *A = nullptr, *B = nullptr, *dA = nullptr, *dB = nullptr;
+    bool own_grads = true;
+    int *b_nonzero = nullptr;    // device flag: any(B != 0), refreshed whenever B is uploaded
+};
+
+namespace {
+
+int check_status(gt_engine *e) {
+    int h[4] = {0, 0, 0, 0};
+    GT_CUDA(cudaMemcpyAsync(h, e->status, sizeof(h), cudaMemcpyDeviceToHost, e->stream));
+    GT_CUDA(cudaStreamSynchronize(e->stream));
+    if (h[0] != 0) {
+        cudaMemsetAsync(e->status, 0, 4 * sizeof(int), e->stream);
+        return fail(GT_ERR_KERNEL, "tensor-core GEMM gave up on a bounded wait (code %d: role %d, barrier %d)", h[0],
+                    h[0] / 100, h[0] % 100);
+    }
+    return GT_OK;
+}
+
+bool tensor_path(const gt_engine *e, const gt_weight *w) {
+    return e->math_mode != GT_MATH_FP32 && w->dev.tma_ok && (w->dev.qtype == kTypeQ4K || w->dev.qtype == kTypeQ6K);
+}
+
+int round8(int n) { return (n + 7) & ~7; }
+
+// out[T, N] = act * W^T (+bias) (+ lora) on the engine stream, device pointers.
+int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora) {
+    const WeightDev &wd = w->dev;
+    const int N = wd.N, K = wd.K;
+    if (use_lora) GT_CUDA(e->low.reserve((size_t)T * ad->rank * sizeof(float)));
+    if (!tensor_path(e, w)) {
+        GT_CUDA(launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
+        if (use_lora) {
+            GT_CUDA(launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, ad->rank, e->stream));
+            GT_CUDA(launch_lora_delta_fp32((const float *)e->low.p, ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling,
+                                           ad->b_nonzero, e->stream));
+        }
+        return GT_OK;
+    }
+    const int fp16 = e->math_mode == GT_MATH_FP16;
+    GT_CUDA(e->x16.reserve((size_t)T * K * 2));
+    if (use_lora) {
+        GT_CUDA(e->low16.reserve((size_t)T * 64 * 2));
+        GT_CUDA(launch_lora_low(Xd, ad->A, (float *)e->low.p, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
+        GT_CUDA(launch_pack_low16((const float *)e->low.p, e->low16.p, ad->scaling, T, ad->rank, fp16, e->stream));
+    } else {
+        GT_CUDA(launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
+    }
+    UmmaLaunch L;
+    L.w = &wd;
+    L.backward = 0;
+    L.fp16 = fp16;
+    L.act16 = e->x16.p;
+    L.ld_act = K;
+    L.T = T;
+    L.out = Yd;
+    L.ld_out = N;
+    L.bias = wd.bias;
+    L.splits = umma_pick_splits(&wd, 0, T, e->sm_count);
+    if (L.splits > 1) {
+        GT_CUDA(launch_fill_rows(Yd, wd.bias, T, N, e->stream));
+        L.out_prefilled = 1;
+    }
+    if (use_lora) {
+        L.lora_act16 = e->low16.p;
+        L.lora_w = ad->B;
+        L.rank = ad->rank;
+        L.lora_flag = ad->b_nonzero;
+    }
+    L.status = e->status;
+    const char *msg = nullptr;
+    cudaError_t ce = launch_umma_gemm(L, e->stream, &msg);
+    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    return GT_OK;
+}
+
+// dX += dY*W (+ lora term); dA, dB accumulate.  Device pointers.
+int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
+                    bool use_lora) {
+    const WeightDev &wd = w->dev;
+    const int N = wd.N, K = wd.K;
+    const bool tensor = tensor_path(e, w) && dXd != nullptr;
+    const int fp16 = e->math_mode == GT_MATH_FP16;
+    const int ld16 = round8(N);
+    if (tensor) GT_CUDA(e->dy16.reserve((size_t)T * ld16 * 2));
+    if (use_lora) {
+        const int R = ad->rank;
+        GT_CUDA(e->low.reserve((size_t)T * R * sizeof(float)));
+        GT_CUDA(e->dlow.reserve((size_t)T * R * sizeof(float)));
+        GT_CUDA(launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, R, e->stream));
+        GT_CUDA(cudaMemsetAsync(e->dlow.p, 0, (size_t)T * R * sizeof(float), e->stream));
+        GT_CUDA(launch_lora_bwd_dy(dYd, (const float *)e->low.p, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr,
+                                   ld16, fp16, ad->scaling, T, N, R, e->stream));
+        GT_CUDA(launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
+        if (dXd && !tensor) GT_CUDA(launch_lora_dx_fp32((const float *)e->dlow.p, ad->A, dXd, ad->scaling, T, K, R, e->stream));
+        if (tensor) {
+            GT_CUDA(e->dlow16.reserve((size_t)T * 64 * 2));
+            GT_CUDA(launch_pack_low16((const float *)e->dlow.p, e->dlow16.p, ad->scaling, T, R, fp16, e->stream));
+        }
+    } else if (tensor) {
+        GT_CUDA(launch_cast16(dYd, e->dy16.p, T, N, ld16, fp16, e->stream));
+    }
+    if (!dXd) return GT_OK;
+    if (!tensor) {
+        GT_CUDA(launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
+        return GT_OK;
+    }
+    UmmaLaunch L;
+    L.w = &wd;
+    L.backward = 1;
+    L.fp16 = fp16;
+    L.act16 = e->dy16.p;
+    L.ld_act = ld16;
+    L.T = T;
+    L.out = dXd;
+    L.ld_out = K;
+    L.splits = umma_pick_splits(&wd, 1, T, e->sm_count);
+    if (use_lora) {
+        L.lora_act16 = e->dlow16.p;
+        L.lora_w = ad->A;
+        L.rank = ad->rank;
+        L.lora_flag = nullptr;
+    }
+    L.status = e->status;
+    const char *msg = nullptr;
+    cudaError_t ce = launch_umma_gemm(L, e->stream, &msg);
+    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    return GT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *gt_last_error(void) { return g_err; }
+const char *gt_version(void) { return "glaciertune_b200 0.1 (sm_100a)"; }
+
+int gt_supports(int ggml_type, int direction) {
+    if (direction != GT_DIR_FORWARD && direction != GT_DIR_BACKWARD) return 0;
+    return (ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K || ggml_type == GT_TYPE_F32) ? 1 : 0;
+}
+
+int gt_engine_create(const gt_config *cfg, gt_engine **out) {
+    if (!out) return fail(GT_ERR_INVALID, "gt_engine_create: out is null");
+    *out = nullptr;
+    const int dev = cfg ? cfg->device : 0;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        return fail(GT_ERR_NO_DEVICE, "no CUDA device is visible; this library has no CPU path");
+    }
+    if (dev < 0 || dev >= count) return fail(GT_ERR_INVALID, "device ordinal %d out of range (%d devices)", dev, count);
+    cudaDeviceProp prop;
+    GT_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10) return fail(GT_ERR_NO_DEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only", dev, prop.major, prop.minor);
+    GT_CUDA(cudaSetDevice(dev));
+    if (!umma_available()) return fail(GT_ERR_CUDA, "the CUDA driver does not export cuTensorMapEncodeTiled");
+    gt_engine *e = new (std::nothrow) gt_engine();
+    if (!e) return fail(GT_ERR_OOM, "out of host memory");
+    e->device = dev;
+    e->sm_count = prop.multiProcessorCount;
+    e->math_mode = cfg ? cfg->math_mode : GT_MATH_BF16;
+    if (e->math_mode < GT_MATH_BF16 || e->math_mode > GT_MATH_FP32) {
+        delete e;
+        return fail(GT_ERR_INVALID, "unknown math mode %d", cfg->math_mode);
+    }
+    if (cfg && cfg->stream) {
+        e->stream = (cudaStream_t)cfg->stream;
+    } else {
+        cudaError_t ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+        if (ce != cudaSuccess) {
+            delete e;
+            return fail(GT_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(ce));
+        }
+        e->own_stream = true;
+    }
+    cudaError_t ce = cudaMalloc((void **)&e->status, 4 * sizeof(int));
+    if (ce == cudaSuccess) ce = cudaMalloc((void **)&e->clip, 2 * sizeof(double));
+    if (ce == cudaSuccess) ce = cudaMemset(e->status, 0, 4 * sizeof(int));
+    if (ce != cudaSuccess) {
+        gt_engine_destroy(e);
+        return fail(GT_ERR_CUDA, "engine allocation failed: %s", cudaGetErrorString(ce));
+    }
+    *out = e;
+    return GT_OK;
+}
+
+int gt_engine_destroy(gt_engine *e) {
+    if (!e) return GT_OK;
+    cudaSetDevice(e->device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    Scratch *all[] = {&e->x16, &e->dy16, &e->low, &e->low16, &e->dlow, &e->dlow16, &e->ytmp, &e->h_in0, &e->h_in1, &e->h_out};
+    for (Scratch *s : all) s->release();
+    if (e->status) cudaFree(e->status);
+    if (e->clip) cudaFree(e->clip);
+    if (e->own_stream && e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+    return GT_OK;
+}
+
+int gt_engine_set_math_mode(gt_engine *e, int math_mode) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    if (math_mode < GT_MATH_BF16 || math_mode > GT_MATH_FP32) return fail(GT_ERR_INVALID, "unknown math mode %d", math_mode);
+    std::lock_guard<std::mutex> lk(e->mu);
+    e->math_mode = math_mode;
+    return GT_OK;
+}
+
+int gt_sync(gt_engine *e) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return check_status(e);
+}
+
+int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_t nbytes, int32_t out_features,
+                     int32_t in_features, const float *bias, gt_weight **out) {
+    if (!e || !host_bytes || !out) return fail(GT_ERR_INVALID, "gt_weight_upload: null argument");
+    *out = nullptr;
+    if (!gt_supports(ggml_type, GT_DIR_FORWARD)) return fail(GT_ERR_UNSUPPORTED, "ggml type %d is not supported", ggml_type);
+    if (out_features <= 0 || in_features <= 0) return fail(GT_ERR_INVALID, "bad shape [%d, %d]", out_features, in_features);
+    const int64_t nelem = (int64_t)out_features * in_features;
+    int64_t expect;
+    if (ggml_type == GT_TYPE_F32) {
+        expect = nelem * 4;
+    } else {
+        if (nelem % 256 != 0 || in_features % 32 != 0)
+            return fail(GT_ERR_INVALID, "K-quant tensor [%d, %d] is not a whole number of 256-weight super-blocks", out_features,
+                        in_features);
+        expect = nelem / 256 * (ggml_type == GT_TYPE_Q4_K ? kQ4KBlockBytes : kQ6KGgufBlockBytes);
+    }
+    if (nbytes != expect) return fail(GT_ERR_INVALID, "tensor byte size %lld does not match shape (expected %lld)", (long long)nbytes, (long long)expect);
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    gt_weight *w = new (std::nothrow) gt_weight();
+    if (!w) return fail(GT_ERR_OOM, "out of host memory");
+    w->eng = e;
+    WeightDev &d = w->dev;
+    d.qtype = ggml_type;
+    d.N = out_features;
+    d.K = in_features;
+    cudaError_t ce = cudaSuccess;
+    if (ggml_type == GT_TYPE_Q6_K) {
+        const int64_t nb = nelem / 256;
+        d.nbytes = nb * kQ6KDevBlockBytes;
+        void *tmp = nullptr;
+        ce = cudaMalloc((void **)&d.data, d.nbytes);
+        if (ce == cudaSuccess) ce = cudaMalloc(&tmp, nbytes);
+        if (ce == cudaSuccess) ce = cudaMemcpyAsync(tmp, host_bytes, nbytes, cudaMemcpyHostToDevice, e->stream);
+        if (ce == cudaSuccess) ce = launch_q6k_repack((const uint8_t *)tmp, d.data, nb, e->stream);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+        if (tmp) cudaFree(tmp);
+    } else {
+        d.nbytes = nbytes;
+        ce = cudaMalloc((void **)&d.data, d.nbytes);
+        if (ce == cudaSuccess) ce = cudaMemcpyAsync(d.data, host_bytes, nbytes, cudaMemcpyHostToDevice, e->stream);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+    }
+    if (ce == cudaSuccess && bias) {
+        ce = cudaMalloc((void **)&d.bias, (size_t)out_features * sizeof(float));
+        if (ce == cudaSuccess) ce = cudaMemcpy(d.bias, bias, (size_t)out_features * sizeof(float), cudaMemcpyHostToDevice);
+    }
+    if (ce != cudaSuccess) {
+        gt_weight_free(w);
+        return fail(ce == cudaErrorMemoryAllocation ? GT_ERR_OOM : GT_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(ce));
+    }
+    if (ggml_type != GT_TYPE_F32 && in_features % 256 == 0) d.row_bytes = (int64_t)(in_features / 256) * dev_block_bytes(ggml_type);
+    const char *msg = nullptr;
+    if (umma_init_weight_maps(&d, &msg) != cudaSuccess) {
+        gt_weight_free(w);
+        return fail(GT_ERR_CUDA, "%s", msg ? msg : "tensor map creation failed");
+    }
+    *out = w;
+    return GT_OK;
+}
+
+int gt_weight_free(gt_weight *w) {
+    if (!w) return GT_OK;
+    if (w->eng) cudaSetDevice(w->eng->device);
+    if (w->dev.data) cudaFree(w->dev.data);
+    if (w->dev.bias) cudaFree(w->dev.bias);
+    delete w;
+    return GT_OK;
+}
+
+int gt_dequant_rows(gt_engine *e, const gt_weight *w, int64_t row0, int64_t nrows, float *out, int32_t flags) {
+    if (!e || !w || !out) return fail(GT_ERR_INVALID, "gt_dequant_rows: null argument");
+    if (row0 < 0 || nrows < 0 || row0 + nrows > w->dev.N) return fail(GT_ERR_INVALID, "rows [%lld, %lld) outside [0, %d)", (long long)row0, (long long)(row0 + nrows), w->dev.N);
+    if (nrows == 0) return GT_OK;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    const size_t bytes = (size_t)nrows * w->dev.K * sizeof(float);
+    float *dst = out;
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) {
+        GT_CUDA(e->h_out.reserve(bytes));
+        dst = (float *)e->h_out.p;
+    }
+    GT_CUDA(launch_dequant_rows(w->dev.qtype, w->dev.data, w->dev.K, row0, nrows, dst, e->stream));
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) {
+        GT_CUDA(cudaMemcpyAsync(out, dst, bytes, cudaMemcpyDeviceToHost, e->stream));
+        GT_CUDA(cudaStreamSynchronize(e->stream));
+    }
+    return GT_OK;
+}
+
+int gt_adapter_create(gt_engine *e, int32_t in_features, int32_t out_features, int32_t rank, float alpha, gt_adapter **out) {
+    if (!e || !out) return fail(GT_ERR_INVALID, "gt_adapter_create: null argument");
+    *out = nullptr;
+    if (in_features <= 0 || out_features <= 0 || rank <= 0) return fail(GT_ERR_INVALID, "bad adapter shape in=%d out=%d rank=%d", in_features, out_features, rank);
+    if (rank > 64) return fail(GT_ERR_UNSUPPORTED, "rank %d > 64 is not supported", rank);
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    gt_adapter *a = new (std::nothrow) gt_adapter();
+    if (!a) return fail(GT_ERR_OOM, "out of host memory");
+    a->eng = e;
+    a->in = in_features;
+    a->out = out_features;
+    a->rank = rank;
+    a->alpha = alpha;
+    a->scaling = alpha / (float)rank;   // LoraAdapter.cs:99
+    const size_t na = (size_t)in_features * rank * sizeof(float), nb = (size_t)rank * out_features * sizeof(float);
+    cudaError_t ce = cudaMalloc((void **)&a->A, na);
+    if (ce == cudaSuccess) ce = cudaMalloc((void **)&a->B, nb);
+    if (ce == cudaSuccess) ce = cudaMalloc((void **)&a->dA, na);
+    if (ce == cudaSuccess) ce = cudaMalloc((void **)&a->dB, nb);
+    if (ce == cudaSuccess) ce = cudaMalloc((void **)&a->b_nonzero, sizeof(int));
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(a->A, 0, na, e->stream);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(a->B, 0, nb, e->stream);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(a->dA, 0, na, e->stream);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(a->dB, 0, nb, e->stream);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(a->b_nonzero, 0, sizeof(int), e->stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+    if (ce != cudaSuccess) {
+        gt_adapter_free(a);
+        return fail(GT_ERR_CUDA, "adapter allocation failed: %s", cudaGetErrorString(ce));
+    }
+    *out = a;
+    return GT_OK;
+}
+
+int gt_adapter_free(gt_adapter *a) {
+    if (!a) return GT_OK;
+    if (a->eng) cudaSetDevice(a->eng->device);
+    if (a->A) cudaFree(a->A);
+    if (a->B) cudaFree(a->B);
+    if (a->own_grads) {
+        if (a->dA) cudaFree(a->dA);
+        if (a->dB) cudaFree(a->dB);
+    }
+    if (a->b_nonzero) cudaFree(a->b_nonzero);
+    delete a;
+    return GT_OK;
+}
+
+int gt_adapter_upload(gt_adapter *a, const float *A, const float *B) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    gt_engine *e = a->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (A) GT_CUDA(cudaMemcpyAsync(a->A, A, (size_t)a->in * a->rank * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    if (B) {
+        GT_CUDA(cudaMemcpyAsync(a->B, B, (size_t)a->rank * a->out * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+        GT_CUDA(launch_any_nonzero(a->B, (int64_t)a->rank * a->out, a->b_nonzero, e->stream));
+    }
+    GT_CUDA(cudaStreamSynchronize(e->stream));
+    return GT_OK;
+}
+
+int gt_adapter_download(gt_adapter *a, float *A, float *B) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    gt_engine *e = a->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (A) GT_CUDA(cudaMemcpyAsync(A, a->A, (size_t)a->in * a->rank * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    if (B) GT_CUDA(cudaMemcpyAsync(B, a->B, (size_t)a->rank * a->out * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    GT_CUDA(cudaStreamSynchronize(e->stream));
+    return GT_OK;
+}
+
+int gt_adapter_grads_download(gt_adapter *a, float *dA, float *dB) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    gt_engine *e = a->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (dA) GT_CUDA(cudaMemcpyAsync(dA, a->dA, (size_t)a->in * a->rank * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    if (dB) GT_CUDA(cudaMemcpyAsync(dB, a->dB, (size_t)a->rank * a->out * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    GT_CUDA(cudaStreamSynchronize(e->stream));
+    return GT_OK;
+}
+
+int gt_adapter_grads_zero(gt_adapter *a) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    gt_engine *e = a->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    GT_CUDA(cudaMemsetAsync(a->dA, 0, (size_t)a->in * a->rank * sizeof(float), e->stream));
+    GT_CUDA(cudaMemsetAsync(a->dB, 0, (size_t)a->rank * a->out * sizeof(float), e->stream));
+    return GT_OK;
+}
+
+int gt_adapter_set_alpha(gt_adapter *a, float alpha) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    std::lock_guard<std::mutex> lk(a->eng->mu);
+    a->alpha = alpha;
+    a->scaling = a->rank > 0 ? alpha / (float)a->rank : 0.f;
+    return GT_OK;
+}
+
+int gt_adapter_device_ptrs(gt_adapter *a, float **A, float **B, float **dA, float **dB) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    if (A) *A = a->A;
+    if (B) *B = a->B;
+    if (dA) *dA = a->dA;
+    if (dB) *dB = a->dB;
+    return GT_OK;
+}
+
+int gt_adapter_bind_grads(gt_adapter *a, float *dA_dev, float *dB_dev) {
+    if (!a || !dA_dev || !dB_dev) return fail(GT_ERR_INVALID, "gt_adapter_bind_grads: null argument");
+    std::lock_guard<std::mutex> lk(a->eng->mu);
+    cudaSetDevice(a->eng->device);
+    if (a->own_grads) {
+        cudaStreamSynchronize(a->eng->stream);
+        if (a->dA) cudaFree(a->dA);
+        if (a->dB) cudaFree(a->dB);
+    }
+    a->own_grads = false;
+    a->dA = dA_dev;
+    a->dB = dB_dev;
+    return GT_OK;
+}
+
+int gt_proj_forward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *X, float *Y, int32_t T, int32_t flags) {
+    if (!e || !w || !X || !Y) return fail(GT_ERR_INVALID, "gt_proj_forward: null argument");
+    if (T <= 0) return fail(GT_ERR_INVALID, "T must be positive (got %d)", T);
+    if (ad && (ad->in != w->dev.K || ad->out != w->dev.N)) return fail(GT_ERR_INVALID, "adapter [%d -> %d] does not match weight [%d -> %d]", ad->in, ad->out, w->dev.K, w->dev.N);
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    // LoraAdapter.Forward: the delta is skipped when the adapter is disabled, scaling == 0, or B == 0
+    // (B == 0 is decided on the device from the flag written at upload).
+    const bool use_lora = ad && !(flags & GT_FLAG_NO_LORA) && ad->rank > 0 && ad->scaling != 0.f;
+    const int N = w->dev.N, K = w->dev.K;
+    if (flags & GT_FLAG_DEVICE_PTRS) return forward_device(e, w, ad, X, Y, T, use_lora);
+    const size_t bx = (size_t)T * K * sizeof(float), by = (size_t)T * N * sizeof(float);
+    GT_CUDA(e->h_in0.reserve(bx));
+    GT_CUDA(e->h_out.reserve(by));
+    GT_CUDA(cudaMemcpyAsync(e->h_in0.p, X, bx, cudaMemcpyHostToDevice, e->stream));
+    int rc = forward_device(e, w, ad, (const float *)e->h_in0.p, (float *)e->h_out.p, T, use_lora);
+    if (rc != GT_OK) return rc;
+    GT_CUDA(cudaMemcpyAsync(Y, e->h_out.p, by, cudaMemcpyDeviceToHost, e->stream));
+    return check_status(e);
+}
+
+int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dY, const float *X, float *dX, int32_t T,
+                     int32_t flags) {
+    if (!e || !w || !dY) return fail(GT_ERR_INVALID, "gt_proj_backward: null argument");
+    if (T <= 0) return fail(GT_ERR_INVALID, "T must be positive (got %d)", T);
+    if (ad && (ad->in != w->dev.K || ad->out != w->dev.N)) return fail(GT_ERR_INVALID, "adapter [%d -> %d] does not match weight [%d -> %d]", ad->in, ad->out, w->dev.K, w->dev.N);
+    const bool use_lora = ad && !(flags & GT_FLAG_NO_LORA) && ad->rank > 0;
+    if (use_lora && !X) return fail(GT_ERR_INVALID, "gt_proj_backward: X is required for the adapter gradients");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    const int N = w->dev.N, K = w->dev.K;
+    if (flags & GT_FLAG_DEVICE_PTRS) return backward_device(e, w, ad, dY, X, dX, T, use_lora);
+    const size_t bx = (size_t)T * K * sizeof(float), by = (size_t)T * N * sizeof(float);
+    GT_CUDA(e->h_in0.reserve(by));
+    GT_CUDA(cudaMemcpyAsync(e->h_in0.p, dY, by, cudaMemcpyHostToDevice, e->stream));
+    if (use_lora) {
+        GT_CUDA(e->h_in1.reserve(bx));
+        GT_CUDA(cudaMemcpyAsync(e->h_in1.p, X, bx, cudaMemcpyHostToDevice, e->stream));
+    }
+    if (dX) {
+        // the reference uploads dX too: the kernel accumulates into it (GpuLoraEngine.Backward.cs:85-89)
+        GT_CUDA(e->h_out.reserve(bx));
+        GT_CUDA(cudaMemcpyAsync(e->h_out.p, dX, bx, cudaMemcpyHostToDevice, e->stream));
+    }
+    int rc = backward_device(e, w, ad, (const float *)e->h_in0.p, use_lora ? (const float *)e->h_in1.p : nullptr,
+                             dX ? (float *)e->h_out.p : nullptr, T, use_lora);
+    if (rc != GT_OK) return rc;
+    if (dX) GT_CUDA(cudaMemcpyAsync(dX, e->h_out.p, bx, cudaMemcpyDeviceToHost, e->stream));
+    return check_status(e);
+}
+
+int gt_launch_gemm_batch(gt_engine *e, const gt_weight *w, float *dY_out, const float *dX_in, int32_t batch, float *d_residual) {
+    if (!e || !w || !dX_in) return fail(GT_ERR_INVALID, "gt_launch_gemm_batch: null argument");
+    if (batch <= 0) return fail(GT_ERR_INVALID, "batch must be positive (got %d)", batch);
+    if (!dY_out && !d_residual) return GT_OK;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    const int N = w->dev.N, K = w->dev.K;
+    if (!tensor_path(e, w)) {
+        GT_CUDA(launch_gemm_fp32_fwd(w->dev.qtype, w->dev.data, dX_in, dY_out, d_residual, w->dev.bias, batch, N, K, e->stream));
+        return GT_OK;
+    }
+    float *yd = dY_out;
+    if (!yd) {
+        GT_CUDA(e->ytmp.reserve((size_t)batch * N * sizeof(float)));
+        yd = (float *)e->ytmp.p;
+    }
+    int rc = forward_device(e, w, nullptr, dX_in, yd, batch, false);
+    if (rc != GT_OK) return rc;
+    if (d_residual) GT_CUDA(launch_add_inplace(d_residual, yd, (int64_t)batch * N, e->stream));
+    return GT_OK;
+}
+
+int gt_launch_gemm_bwd(gt_engine *e, const gt_weight *w, float *dDX, const float *dDY, int32_t batch) {
+    if (!e || !w || !dDX || !dDY) return fail(GT_ERR_INVALID, "gt_launch_gemm_bwd: null argument");
+    if (batch <= 0) return fail(GT_ERR_INVALID, "batch must be positive (got %d)", batch);
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return backward_device(e, w, nullptr, dDY, nullptr, dDX, batch, false);
+}
+
+int gt_grads_scale_clip(gt_engine *e, float *g_dev, int64_t n, float pre_scale, double max_norm, double *norm_out) {
+    if (!e || !g_dev || n < 0) return fail(GT_ERR_INVALID, "gt_grads_scale_clip: bad argument");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    GT_CUDA(launch_scale_clip(g_dev, n, pre_scale, max_norm, e->clip, e->stream));
+    double h[2] = {0, 0};
+    GT_CUDA(cudaMemcpyAsync(h, e->clip, sizeof(h), cudaMemcpyDeviceToHost, e->stream));
+    GT_CUDA(cudaStreamSynchronize(e->stream));
+    if (norm_out) *norm_out = max_norm > 0.0 ? h[1] : 0.0;   // ClipGradients returns 0 when maxNorm <= 0
+    return GT_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Data parallel: one process per GPU, every rank holds a replica of the frozen base and of the adapters;
+// the flat fp32 LoRA-gradient buffer is summed over NVLink with one NCCL all-reduce per step.
+// NCCL is bound at run time (dlopen) so the library loads on hosts without it.
+// ------------------------------------------------------------------------------------------------
+namespace {
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+NcclApi &nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        api.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!api.handle) api.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (api.handle) {
+            api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(api.handle, "ncclGetUniqueId");
+            api.CommInitRank = (decltype(api.CommInitRank))dlsym(api.handle, "ncclCommInitRank");
+            api.AllReduce = (decltype(api.AllReduce))dlsym(api.handle, "ncclAllReduce");
+            api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
+            api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
+            api.ok = api.GetUniqueId && api.CommInitRank && api.AllReduce && api.CommDestroy && api.GetErrorString;
+        }
+    }
+    return api;
+}
+}  // namespace
+
+int gt_dp_unique_id(void *out, int32_t nbytes) {
+    if (!out || nbytes < (int32_t)sizeof(ncclUniqueId)) return fail(GT_ERR_INVALID, "unique id buffer must hold %d bytes", (int)sizeof(ncclUniqueId));
+    NcclApi &n = nccl_api();
+    if (!n.ok) return fail(GT_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    ncclUniqueId id;
+    ncclResult_t r = n.GetUniqueId(&id);
+    if (r != ncclSuccess) return fail(GT_ERR_NCCL, "ncclGetUniqueId: %s", n.GetErrorString(r));
+    memcpy(out, &id, sizeof(id));
+    return GT_OK;
+}
+
+int gt_dp_init(gt_engine *e, int32_t world, int32_t rank, const void *unique_id, int32_t nbytes) {
+    if (!e || !unique_id || nbytes < (int32_t)sizeof(ncclUniqueId)) return fail(GT_ERR_INVALID, "gt_dp_init: bad argument");
+    if (world < 1 || rank < 0 || rank >= world) return fail(GT_ERR_INVALID, "bad rank %d of world %d", rank, world);
+    NcclApi &n = nccl_api();
+    if (!n.ok) return fail(GT_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (e->comm) return fail(GT_ERR_INVALID, "data-parallel group already initialised");
+    ncclUniqueId id;
+    memcpy(&id, unique_id, sizeof(id));
+    ncclResult_t r = n.CommInitRank(&e->comm, world, id, rank);
+    if (r != ncclSuccess) {
+        e->comm = nullptr;
+        return fail(GT_ERR_NCCL, "ncclCommInitRank: %s", n.GetErrorString(r));
+    }
+    e->dp_world = world;
+    e->dp_rank = rank;
+    return GT_OK;
+}
+
+int gt_dp_allreduce(gt_engine *e, float *g_dev, int64_t count, float scale) {
+    if (!e || !g_dev || count < 0) return fail(GT_ERR_INVALID, "gt_dp_allreduce: bad argument");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (e->comm) {
+        NcclApi &n = nccl_api();
+        ncclResult_t r = n.AllReduce(g_dev, g_dev, (size_t)count, ncclFloat, ncclSum, e->comm, e->stream);
+        if (r != ncclSuccess) return fail(GT_ERR_NCCL, "ncclAllReduce: %s", n.GetErrorString(r));
+    }
+    if (scale != 1.0f) GT_CUDA(launch_scale_clip(g_dev, count, scale, 0.0, e->clip, e->stream));
+    return GT_OK;
+}
+
+int gt_dp_finalize(gt_engine *e) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    std::lock_guard<std::mutex> lk(e->mu);
+    if (e->comm) {
+        cudaSetDevice(e->device);
+        cudaStreamSynchronize(e->stream);
+        nccl_api().CommDestroy(e->comm);
+        e->comm = nullptr;
+    }
+    e->dp_world = 1;
+    e->dp_rank = 0;
+    return GT_OK;
+}
+
+}  // extern "C"

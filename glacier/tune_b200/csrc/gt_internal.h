@@ -1,0 +1,83 @@
+// Internal launch interface between the translation units of libglaciertune_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gt {
+
+// Device copy of one frozen base tensor.
+struct WeightDev {
+    int qtype = 0;
+    int N = 0, K = 0;             // [out_features, in_features]
+    uint8_t *data = nullptr;      // device blocks (Q4_K: GGUF bytes; Q6_K: 224-byte device blocks; F32: floats)
+    int64_t nbytes = 0;
+    int64_t row_bytes = 0;        // K/256 * block bytes when K % 256 == 0, else 0 (flat super-block stream)
+    float *bias = nullptr;        // [N] or null
+    bool tma_ok = false;          // row-aligned and tensor maps built
+    CUtensorMap tm_hdr, tm_q0, tm_q1;   // 2-D byte maps over [N, row_bytes], boxes of 64 rows
+};
+
+// ---- CUDA-core kernels (gt_fp32_kernels.cu) -------------------------------------------------------------
+cudaError_t launch_q6k_repack(const uint8_t *gguf_blocks, uint8_t *dev_blocks, int64_t nblocks, cudaStream_t s);
+cudaError_t launch_dequant_rows(int qt, const uint8_t *w, int K, int64_t row0, int64_t nrows, float *out, cudaStream_t s);
+cudaError_t launch_gemm_fp32_fwd(int qt, const uint8_t *w, const float *X, float *Y, float *residual, const float *bias,
+                                 int T, int N, int K, cudaStream_t s);
+cudaError_t launch_gemm_fp32_bwd(int qt, const uint8_t *w, const float *dY, float *dX, int T, int N, int K, cudaStream_t s);
+
+// LoRA (all fp32 arithmetic).  A is [K, R] row-major, B is [R, N] row-major.  Kernels handle ranks
+// [r0, r0+16) of R per launch.
+// low[T,R] = X*A ; optionally x16[T, ldx16] = round16(X) (r0 == 0 pass only).
+cudaError_t launch_lora_low(const float *X, const float *A, float *low, void *x16, int ldx16, int fp16, int T, int K,
+                            int R, cudaStream_t s);
+// low16[T, 64] = round16(scale * low[T, R]) zero-padded to 64 columns.
+cudaError_t launch_pack_low16(const float *low, void *low16, float scale, int T, int R, int fp16, cudaStream_t s);
+// Y[T,N] += scaling * low * B
+cudaError_t launch_lora_delta_fp32(const float *low, const float *B, float *Y, float *residual, int T, int N, int R,
+                                   float scaling, const int *nonzero_flag, cudaStream_t s);
+// One pass over dY: dB += scaling * low^T * dY ; dLow (pre-zeroed) += dY * B^T ; dy16 = round16(dY) (optional).
+cudaError_t launch_lora_bwd_dy(const float *dY, const float *low, const float *B, float *dB, float *dLow, void *dy16,
+                               int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s);
+// dA += scaling * X^T * dLow
+cudaError_t launch_lora_bwd_x(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R,
+                              cudaStream_t s);
+// dX[T,K] += scaling * dLow * A^T
+cudaError_t launch_lora_dx_fp32(const float *dLow, const float *A, float *dX, float scaling, int T, int K, int R,
+                                cudaStream_t s);
+cudaError_t launch_cast16(const float *src, void *dst, int rows, int cols, int ld_dst, int fp16, cudaStream_t s);
+// Y[t, :] = bias (or 0)
+cudaError_t launch_fill_rows(float *Y, const float *bias, int T, int N, cudaStream_t s);
+// residual += Y
+cudaError_t launch_add_inplace(float *dst, const float *src, int64_t n, cudaStream_t s);
+// *flag = any(B != 0)
+cudaError_t launch_any_nonzero(const float *B, int64_t n, int *flag, cudaStream_t s);
+// scratch: 2 doubles on the device
+cudaError_t launch_scale_clip(float *g, int64_t n, float pre_scale, double max_norm, double *scratch, cudaStream_t s);
+
+// ---- tcgen05 kernels (gt_umma_gemm.cu) ------------------------------------------------------------------
+struct UmmaLaunch {
+    const WeightDev *w = nullptr;
+    int backward = 0;              // 0: out[T,N] = act[T,K] * W^T ; 1: out[T,K] += act[T,N] * W
+    int fp16 = 0;                  // operand format: 0 bf16, 1 fp16
+    const void *act16 = nullptr;   // 16-bit activations [T, ld_act]
+    int ld_act = 0;
+    int T = 0;
+    float *out = nullptr;          // fp32 [T, ld_out]
+    int ld_out = 0;
+    const float *bias = nullptr;   // forward only
+    int out_prefilled = 0;         // forward: out already holds bias/zero, accumulate with atomics (split-K)
+    // fused LoRA rank-update (optional)
+    const void *lora_act16 = nullptr;   // [T, 64] zero-padded 16-bit, already scaled
+    const float *lora_w = nullptr;      // forward: B [R, N]; backward: A [K, R]
+    int rank = 0;
+    const int *lora_flag = nullptr;     // device int: 0 -> skip the update
+    int splits = 1;
+    int *status = nullptr;              // device int[4]
+};
+int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count);
+// Returns cudaSuccess or an error; `err` receives a description on failure of a non-CUDA kind.
+cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err);
+cudaError_t umma_init_weight_maps(WeightDev *w, const char **err);
+bool umma_available();
+
+}  // namespace gt

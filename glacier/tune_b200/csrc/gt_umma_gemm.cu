@@ -1,0 +1,489 @@
+// Frozen-base K-quant projection GEMMs on the sm_100a tensor cores.
+//
+//   forward   out[T, N]  = act[T, K] * W[N, K]^T (+ bias) (+ lora_act[T, r] * B[r, N])
+//   backward  out[T, K] += act[T, N] * W[N, K]            (+ lora_act[T, r] * A[K, r]^T)
+//
+// Replaces the CUDA-core kernels gemm_q4_k_batch / gemm_q6_k_batch (Glacier.Inference fatbin, launched at
+// src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:83-129) and gemm_q4_k_bwd / gemm_q6_k_bwd
+// (src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:193-332), and folds in the rank-r products that the reference runs
+// on the host (src/Glacier.Tune/Kernels/LoraKernels.cs:57-86,296-339).
+//
+// One CTA owns 128 weight rows (forward) or 128 weight columns (backward) and ALL tokens of its token chunk
+// (up to 512), so each weight is dequantized once per CTA and reused by every token:
+//   D[128 x tokens] (TMEM, fp32)  +=  Wtile[128 x 64] (SMEM, dequantized 16-bit)  x  act[tokens x 64]^T (SMEM via TMA)
+//
+// Warp roles (320 threads):
+//   warp 0      TMA producer: packed half-super-blocks of W (raw bytes) and 16-bit activation tiles
+//   warp 1      tcgen05.mma issuer (one thread); owns the TMEM allocation
+//   warps 2-9   dequantize raw blocks -> 128-byte-swizzled operand tiles; afterwards the epilogue
+//               (tcgen05.ld -> bias -> global store / atomic add)
+//
+// The dequantized tile image is the same for both directions: row = weight row n, 128 bytes = 64 consecutive
+// k, chunks XOR-swizzled by (row & 7).  Forward reads it as a K-major A operand (M = n, K = k); backward
+// reads it as an MN-major A operand (M = k, K = n) - no transposed copy of W is ever formed.
+//
+// Every mbarrier wait is bounded (wall-clock limit); on a timeout the CTA records a code in status[0], all
+// roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstring>
+#include <type_traits>
+
+#include "gt_internal.h"
+#include "gt_ptx.cuh"
+#include "gt_quant.cuh"
+
+namespace gt {
+
+namespace {
+
+constexpr int kTileW = 128;        // UMMA M
+constexpr int kChunk = 64;         // contraction elements per operand stage (one 128-byte row)
+constexpr int kMaxTok = 512;       // tokens per CTA = TMEM columns
+constexpr int kAStageBytes = kTileW * kChunk * 2;   // 16 KiB
+constexpr int kXStageBytes = kMaxTok * kChunk * 2;  // 64 KiB
+constexpr int kRawStageBytes = 16384;
+constexpr int kNumA = 3, kNumX = 2, kNumRaw = 2;
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = 32 * (2 + kDequantWarps);
+
+constexpr int kOffX = 0;
+constexpr int kOffA = kOffX + kNumX * kXStageBytes;
+constexpr int kOffRaw = kOffA + kNumA * kAStageBytes;
+constexpr int kOffBar = kOffRaw + kNumRaw * kRawStageBytes;
+constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for 1024-byte alignment
+
+// barrier slots (8 bytes each) inside the kOffBar region
+constexpr int kBarRawFull = 0, kBarRawEmpty = 2, kBarXFull = 4, kBarXEmpty = 6, kBarAFull = 8, kBarAEmpty = 11,
+              kBarAcc = 14, kNumBars = 15;
+constexpr int kOffTmemSlot = kNumBars * 8;       // u32
+constexpr int kOffAbort = kOffTmemSlot + 4;      // int
+
+struct Params {
+    CUtensorMap tm_act, tm_lora, tm_hdr, tm_q0, tm_q1;
+    float *out;
+    const float *bias;
+    const float *lora_w;
+    const int *lora_flag;
+    int *status;
+    int ld_out, T, N, K, rank;
+    int t_box;       // token rows per activation TMA box
+    int splits, units;
+    int atomic_out;  // 1: red.add into out, 0: plain store (+bias)
+    int tmem_cols;
+};
+
+// status codes written on a bounded-wait timeout: 100*role + barrier kind
+enum { kCodeProducer = 100, kCodeMma = 200, kCodeDequant = 300, kCodeEpilogue = 400 };
+
+struct Ring {
+    int idx = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int n) {
+        if (++idx == n) {
+            idx = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+template <int QT, typename T16, bool BWD>
+__global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant__ Params p) {
+    using QS = QuantStage<QT>;
+    constexpr int H = QS::kHdrBytes, Q1 = QS::kQ1Bytes;
+    constexpr int kRows = BWD ? 64 : 128;      // weight rows per raw stage
+    constexpr int kSub = BWD ? 1 : 2;          // operand stages produced per raw stage
+    constexpr uint32_t kFmt = std::is_same<T16, __half>::value ? 0u : 1u;   // UMMA operand format: 0 f16, 1 bf16
+
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + kOffBar;
+    auto bar = [&](int slot) -> uint32_t { return bar0 + 8u * (uint32_t)slot; };
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + kOffBar + kOffAbort);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kOffBar + kOffTmemSlot);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int tok0 = blockIdx.z * kMaxTok;
+    const int tok_left = p.T - tok0;
+    const int tb = min(kMaxTok, (tok_left + 15) & ~15);          // token columns of this CTA (multiple of 16)
+    const int n_box = (tb + p.t_box - 1) / p.t_box;
+    const int n_mma = (tb + 255) >> 8;
+    const int u0 = (int)((int64_t)p.units * split / p.splits);
+    const int u1 = (int)((int64_t)p.units * (split + 1) / p.splits);
+    const int rank_pad = (p.rank + 15) & ~15;
+    const bool do_lora = p.rank > 0 && split == 0 && (p.lora_flag == nullptr || *p.lora_flag != 0);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(kBarRawFull + 0), 1);
+        mbar_init(bar(kBarRawFull + 1), 1);
+        mbar_init(bar(kBarRawEmpty + 0), kDequantWarps * 32);
+        mbar_init(bar(kBarRawEmpty + 1), kDequantWarps * 32);
+        mbar_init(bar(kBarXFull + 0), 1);
+        mbar_init(bar(kBarXFull + 1), 1);
+        mbar_init(bar(kBarXEmpty + 0), 1);
+        mbar_init(bar(kBarXEmpty + 1), 1);
+        for (int i = 0; i < kNumA; i++) {
+            mbar_init(bar(kBarAFull + i), kDequantWarps * 32);
+            mbar_init(bar(kBarAEmpty + i), 1);
+        }
+        mbar_init(bar(kBarAcc), 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&p.tm_act);
+        tma_prefetch_desc(&p.tm_hdr);
+        tma_prefetch_desc(&p.tm_q0);
+    }
+    if (warp == 1) {
+        tmem_alloc(sbase + kOffBar + kOffTmemSlot, (uint32_t)p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            Ring raw, xs;
+            bool ok = true;
+            for (int u = u0; u < u1 && ok; u++) {
+                ok = mbar_wait_bounded(bar(kBarRawEmpty + raw.idx), raw.phase ^ 1u, abort_flag, p.status, kCodeProducer + 1);
+                if (!ok) break;
+                const uint32_t rdst = sbase + kOffRaw + raw.idx * kRawStageBytes;
+                const uint32_t rbar = bar(kBarRawFull + raw.idx);
+                int sb, half, row0;
+                if (BWD) {
+                    sb = tile >> 1; half = tile & 1; row0 = u * 64;
+                } else {
+                    sb = u >> 1; half = u & 1; row0 = tile * kTileW;
+                }
+                const int xb = sb * QS::kBlockBytes;
+                mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
+#pragma unroll
+                for (int rr = 0; rr < kRows; rr += 64) {
+                    tma_load_2d(rdst + rr * H, &p.tm_hdr, xb + QS::hdr_x(half), row0 + rr, rbar);
+                    tma_load_2d(rdst + kRows * H + rr * 64, &p.tm_q0, xb + QS::q0_x(half), row0 + rr, rbar);
+                    if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64) + rr * Q1, &p.tm_q1, xb + QS::q1_x(half), row0 + rr, rbar);
+                }
+                raw.advance(kNumRaw);
+                for (int s = 0; s < kSub && ok; s++) {
+                    ok = mbar_wait_bounded(bar(kBarXEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
+                    if (!ok) break;
+                    const uint32_t xdst = sbase + kOffX + xs.idx * kXStageBytes;
+                    const uint32_t xbar = bar(kBarXFull + xs.idx);
+                    mbar_arrive_expect_tx(xbar, (uint32_t)(n_box * p.t_box * 128));
+                    const int c0 = BWD ? u * 64 : (u * 2 + s) * 64;
+                    for (int b = 0; b < n_box; b++) tma_load_2d(xdst + b * p.t_box * 128, &p.tm_act, c0, tok0 + b * p.t_box, xbar);
+                    xs.advance(kNumX);
+                }
+            }
+            if (ok && do_lora) {
+                ok = mbar_wait_bounded(bar(kBarXEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
+                if (ok) {
+                    const uint32_t xdst = sbase + kOffX + xs.idx * kXStageBytes;
+                    const uint32_t xbar = bar(kBarXFull + xs.idx);
+                    mbar_arrive_expect_tx(xbar, (uint32_t)(n_box * p.t_box * 128));
+                    for (int b = 0; b < n_box; b++) tma_load_2d(xdst + b * p.t_box * 128, &p.tm_lora, 0, tok0 + b * p.t_box, xbar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            Ring as, xs;
+            bool ok = true, first = true;
+            const uint32_t a_mn = BWD ? 1u : 0u;
+            auto issue_stage = [&](int ksteps) {
+                const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
+                const uint32_t x_addr = sbase + kOffX + xs.idx * kXStageBytes;
+                for (int ks = 0; ks < ksteps; ks++) {
+                    const uint64_t adesc = BWD ? umma_desc_sw128(a_addr + ks * 2048, 8192, 1024)
+                                               : umma_desc_sw128(a_addr + ks * 32, 16, 1024);
+                    for (int i = 0; i < n_mma; i++) {
+                        const int ntok = min(256, tb - 256 * i);
+                        const uint64_t bdesc = umma_desc_sw128(x_addr + i * 256 * 128 + ks * 32, 16, 1024);
+                        umma_f16_ss(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok),
+                                    (first && ks == 0) ? 0u : 1u);
+                    }
+                }
+                first = false;
+                umma_commit(bar(kBarAEmpty + as.idx));
+                umma_commit(bar(kBarXEmpty + xs.idx));
+                as.advance(kNumA);
+                xs.advance(kNumX);
+            };
+            for (int u = u0; u < u1 && ok; u++) {
+                for (int s = 0; s < kSub && ok; s++) {
+                    ok = mbar_wait_bounded(bar(kBarAFull + as.idx), as.phase, abort_flag, p.status, kCodeMma + 1) &&
+                         mbar_wait_bounded(bar(kBarXFull + xs.idx), xs.phase, abort_flag, p.status, kCodeMma + 2);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_stage(4);
+                }
+            }
+            if (ok && do_lora) {
+                ok = mbar_wait_bounded(bar(kBarAFull + as.idx), as.phase, abort_flag, p.status, kCodeMma + 3) &&
+                     mbar_wait_bounded(bar(kBarXFull + xs.idx), xs.phase, abort_flag, p.status, kCodeMma + 4);
+                if (ok) {
+                    tc_fence_after_sync();
+                    issue_stage(rank_pad >> 4);
+                }
+            }
+            if (ok) umma_commit(bar(kBarAcc));
+        }
+    } else {
+        // ------------------------------------------------------------------ dequant warps, then epilogue
+        const int dt = threadIdx.x - 64;
+        Ring raw, as;
+        bool ok = true;
+        for (int u = u0; u < u1 && ok; u++) {
+            ok = mbar_wait_bounded(bar(kBarRawFull + raw.idx), raw.phase, abort_flag, p.status, kCodeDequant + 1);
+            if (!ok) break;
+            const uint8_t *rs = smem + kOffRaw + raw.idx * kRawStageBytes;
+            for (int s = 0; s < kSub && ok; s++) {
+                ok = mbar_wait_bounded(bar(kBarAEmpty + as.idx), as.phase ^ 1u, abort_flag, p.status, kCodeDequant + 2);
+                if (!ok) break;
+                const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
+                int row, grp, half, chunk0;
+                uint32_t dst_row;
+                if (BWD) {
+                    row = dt & 63; grp = dt >> 6; half = tile & 1;
+                    dst_row = a_addr + (uint32_t)((grp >> 1) * 8192 + row * 128);
+                    chunk0 = 4 * (grp & 1);
+                } else {
+                    row = dt & 127; grp = 2 * s + (dt >> 7); half = u & 1;
+                    dst_row = a_addr + (uint32_t)(row * 128);
+                    chunk0 = 4 * (dt >> 7);
+                }
+                dequant32_to_swizzled_row<QT, T16>(rs + row * H, rs + kRows * H + row * 64,
+                                                   rs + kRows * (H + 64) + row * (Q1 > 0 ? Q1 : 1), half, grp, dst_row,
+                                                   row & 7, chunk0);
+                fence_proxy_async_smem();
+                mbar_arrive(bar(kBarAFull + as.idx));
+                as.advance(kNumA);
+            }
+            if (ok) mbar_arrive(bar(kBarRawEmpty + raw.idx));
+            raw.advance(kNumRaw);
+        }
+        if (ok && do_lora) {
+            ok = mbar_wait_bounded(bar(kBarAEmpty + as.idx), as.phase ^ 1u, abort_flag, p.status, kCodeDequant + 3);
+            if (ok) {
+                const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
+                if (!BWD) {
+                    // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
+                    const int row = dt & 127, n = tile * kTileW + row;
+                    for (int j = dt >> 7; j * 8 < rank_pad; j += 2) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const int r = 8 * j + i;
+                            v[i] = (r < p.rank && n < p.N) ? p.lora_w[(int64_t)r * p.N + n] : 0.f;
+                        }
+                        st_shared_v4(a_addr + (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4)), pack2<T16>(v[0], v[1]),
+                                     pack2<T16>(v[2], v[3]), pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
+                    }
+                } else {
+                    // image(kcol >> 6)[row = r][col = kcol & 63] = A[k, r]
+                    const int kcol = dt & 127, c = kcol & 63, k = tile * kTileW + kcol;
+                    for (int r = dt >> 7; r < rank_pad; r += 2) {
+                        const float v = (r < p.rank && k < p.K) ? p.lora_w[(int64_t)k * p.rank + r] : 0.f;
+                        const uint32_t addr =
+                            a_addr + (uint32_t)((kcol >> 6) * 8192 + r * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
+                        const uint32_t bits = pack2<T16>(v, 0.f) & 0xFFFFu;
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)bits) : "memory");
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(bar(kBarAFull + as.idx));
+            }
+        }
+        // epilogue: TMEM lane = weight row / column of this tile, TMEM column = token
+        if (ok) ok = mbar_wait_bounded(bar(kBarAcc), 0u, abort_flag, p.status, kCodeEpilogue + 1, 8000000000ull);
+        ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: take the epilogue only as a whole warp
+        if (ok) {
+            tc_fence_after_sync();
+            const int quad = warp & 3, grp2 = (warp - 2) >> 2;
+            const int orow = tile * kTileW + quad * 32 + lane;
+            const bool row_ok = orow < (BWD ? p.K : p.N);
+            const float bv = (!BWD && !p.atomic_out && p.bias && row_ok) ? p.bias[orow] : 0.f;
+            const int nch = (tb + 31) >> 5;
+            for (int c = grp2; c < nch; c += 2) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int tl = c * 32 + j;
+                        const int t = tok0 + tl;
+                        if (tl < tb && t < p.T) {
+                            float *dst = p.out + (int64_t)t * p.ld_out + orow;
+                            const float val = __uint_as_float(v[j]);
+                            if (BWD || p.atomic_out) atomicAdd(dst, val);
+                            else *dst = val + bv;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        // give loads that were already issued time to land before the CTA's shared memory is released
+        for (int i = 0; i < 64; i++) __nanosleep(2000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+bool encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, int esize, const void *base, uint64_t d0, uint64_t d1,
+               uint64_t stride1_bytes, uint32_t b0, uint32_t b1, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t gdim[2] = {d0, d1};
+    cuuint64_t gstr[1] = {stride1_bytes};
+    cuuint32_t box[2] = {b0, b1};
+    cuuint32_t estr[2] = {1, 1};
+    (void)esize;
+    return fn(tm, dt, 2, const_cast<void *>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int QT, typename T16, bool BWD>
+cudaError_t launch_one(const Params &p, dim3 grid, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_umma_gemm<QT, T16, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    k_umma_gemm<QT, T16, BWD><<<grid, kThreads, kSmemBytes, s>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool umma_available() { return get_encode_fn() != nullptr; }
+
+cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
+    w->tma_ok = false;
+    if (w->qtype != kTypeQ4K && w->qtype != kTypeQ6K) return cudaSuccess;
+    if (w->K % 256 != 0 || w->row_bytes == 0) return cudaSuccess;   // flat streams run on the CUDA-core path
+    const int H = w->qtype == kTypeQ4K ? 16 : 32;
+    bool ok = encode_2d(&w->tm_hdr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                        (uint64_t)w->row_bytes, H, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode_2d(&w->tm_q0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                         (uint64_t)w->row_bytes, 64, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (w->qtype == kTypeQ6K)
+        ok = ok && encode_2d(&w->tm_q1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                             (uint64_t)w->row_bytes, 32, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+    else
+        w->tm_q1 = w->tm_q0;
+    if (!ok) {
+        if (err) *err = "cuTensorMapEncodeTiled failed for a weight tensor";
+        return cudaErrorInvalidValue;
+    }
+    w->tma_ok = true;
+    return cudaSuccess;
+}
+
+int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count) {
+    const int tiles = backward ? w->K / kTileW : (w->N + kTileW - 1) / kTileW;
+    const int units = backward ? (w->N + 63) / 64 : w->K / 128;
+    const int chunks = (T + kMaxTok - 1) / kMaxTok;
+    int s = sm_count / (tiles * chunks > 0 ? tiles * chunks : 1);
+    const int cap = units / 2 > 1 ? units / 2 : 1;
+    if (s > cap) s = cap;
+    if (s < 1) s = 1;
+    if (s > units) s = units;
+    return s;
+}
+
+cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err) {
+    const WeightDev *w = L.w;
+    if (!w || !w->tma_ok) {
+        if (err) *err = "weight tensor has no TMA maps (K % 256 != 0 or unsupported type)";
+        return cudaErrorInvalidValue;
+    }
+    if (L.T <= 0) return cudaSuccess;
+    if (L.rank > 64) {
+        if (err) *err = "fused LoRA update supports rank <= 64";
+        return cudaErrorInvalidValue;
+    }
+    Params p;
+    memset(&p, 0, sizeof(p));
+    const int cols = L.backward ? w->N : w->K;       // contraction length of the activation operand
+    const int tmax = L.T < kMaxTok ? L.T : kMaxTok;
+    const int tb = (tmax + 15) & ~15;
+    p.t_box = tb < 128 ? tb : 128;
+    int tc = 32;
+    while (tc < tb) tc <<= 1;
+    p.tmem_cols = tc;
+    const CUtensorMapDataType dt = L.fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (!encode_2d(&p.tm_act, dt, 2, L.act16, (uint64_t)cols, (uint64_t)L.T, (uint64_t)L.ld_act * 2, 64, (uint32_t)p.t_box,
+                   CU_TENSOR_MAP_SWIZZLE_128B)) {
+        if (err) *err = "cuTensorMapEncodeTiled failed for the activation operand";
+        return cudaErrorInvalidValue;
+    }
+    p.rank = 0;
+    p.tm_lora = p.tm_act;
+    if (L.rank > 0 && L.lora_act16 && L.lora_w) {
+        if (!encode_2d(&p.tm_lora, dt, 2, L.lora_act16, 64, (uint64_t)L.T, 128, 64, (uint32_t)p.t_box, CU_TENSOR_MAP_SWIZZLE_128B)) {
+            if (err) *err = "cuTensorMapEncodeTiled failed for the low-rank operand";
+            return cudaErrorInvalidValue;
+        }
+        p.rank = L.rank;
+        p.lora_w = L.lora_w;
+        p.lora_flag = L.lora_flag;
+    }
+    p.tm_hdr = w->tm_hdr;
+    p.tm_q0 = w->tm_q0;
+    p.tm_q1 = w->tm_q1;
+    p.out = L.out;
+    p.ld_out = L.ld_out;
+    p.bias = L.bias;
+    p.status = L.status;
+    p.T = L.T;
+    p.N = w->N;
+    p.K = w->K;
+    p.units = L.backward ? (w->N + 63) / 64 : w->K / 128;
+    p.splits = L.splits < 1 ? 1 : (L.splits > p.units ? p.units : L.splits);
+    p.atomic_out = L.backward ? 1 : (p.splits > 1 || L.out_prefilled ? 1 : 0);
+    const int tiles = L.backward ? w->K / kTileW : (w->N + kTileW - 1) / kTileW;
+    dim3 grid(tiles, p.splits, (L.T + kMaxTok - 1) / kMaxTok);
+    if (w->qtype == kTypeQ4K) {
+        if (!L.fp16) return L.backward ? launch_one<kTypeQ4K, __nv_bfloat16, true>(p, grid, s) : launch_one<kTypeQ4K, __nv_bfloat16, false>(p, grid, s);
+        return L.backward ? launch_one<kTypeQ4K, __half, true>(p, grid, s) : launch_one<kTypeQ4K, __half, false>(p, grid, s);
+    }
+    if (!L.fp16) return L.backward ? launch_one<kTypeQ6K, __nv_bfloat16, true>(p, grid, s) : launch_one<kTypeQ6K, __nv_bfloat16, false>(p, grid, s);
+    return L.backward ? launch_one<kTypeQ6K, __half, true>(p, grid, s) : launch_one<kTypeQ6K, __half, false>(p, grid, s);
+}
+
+}  // namespace gt

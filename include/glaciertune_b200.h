@@ -1,0 +1,178 @@
+/*
+ * glaciertune_b200.h — C ABI of libglaciertune_b200.so
+ *
+ * A B200 (sm_100a) replacement for the CUDA backend of Glacier.Tune's frozen-base projection path:
+ *   forward   Y  = X * W^T (+ bias) + (alpha/r) * (X * A) * B
+ *   backward  dX += dY * W + (alpha/r) * (dY * B^T) * A^T ;  dA += ... ;  dB += ...
+ * with W a GGUF K-quant tensor (Q4_K, Q6_K) or F32, row-major [out, in], super-blocks along `in`.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative gt_status; gt_last_error() gives the text of
+ *     the calling thread's last failure.  Nothing throws, nothing calls back.
+ *   - plain pointers and integer sizes only.  Activation pointers are HOST pointers unless the call is
+ *     given GT_FLAG_DEVICE_PTRS, in which case they are device pointers on the engine's device and the
+ *     call only enqueues work on the engine's stream.
+ *   - host-pointer calls are complete on return (the reference engine is synchronous:
+ *     src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:29-47).
+ *   - an engine serialises its calls internally; it may be used from several host threads
+ *     (the reference takes one lock per call: src/Glacier.Tune/Gpu/GpuLoraEngine.cs:54).
+ *   - LoRA factors use the reference's storage: A is [in, rank] row-major, B is [rank, out] row-major
+ *     (src/Glacier.Tune/Model/LoraAdapter.cs:25-26).  All activations and gradients are fp32 row-major.
+ *   - there is no CPU fallback: without a usable sm_100 device gt_engine_create fails.
+ *
+ * "Replaces" comments cite the reference member each entry point stands in for
+ * (paths relative to the reference project root).
+ */
+#ifndef GLACIERTUNE_B200_H
+#define GLACIERTUNE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GT_API __attribute__((visibility("default")))
+#else
+#define GT_API
+#endif
+
+typedef struct gt_engine gt_engine;
+typedef struct gt_weight gt_weight;
+typedef struct gt_adapter gt_adapter;
+
+/* ggml tensor type ids, as in the reference's GgufType */
+enum { GT_TYPE_F32 = 0, GT_TYPE_Q4_K = 12, GT_TYPE_Q6_K = 14 };
+
+enum gt_status {
+    GT_OK = 0,
+    GT_ERR_INVALID = -1,     /* bad argument (null pointer, size mismatch, in % 256 != 0, ...) */
+    GT_ERR_UNSUPPORTED = -2, /* tensor type / shape outside what the kernels handle */
+    GT_ERR_CUDA = -3,        /* a CUDA call failed; text in gt_last_error() */
+    GT_ERR_NO_DEVICE = -4,   /* no sm_100 device */
+    GT_ERR_KERNEL = -5,      /* a kernel reported a bounded-wait timeout or a self-check failure */
+    GT_ERR_NCCL = -6,
+    GT_ERR_OOM = -7
+};
+
+/* arithmetic of the base GEMMs */
+enum gt_math_mode {
+    GT_MATH_BF16 = 0, /* tcgen05 MMA, bf16 operands, fp32 accumulation (default) */
+    GT_MATH_FP16 = 1, /* tcgen05 MMA, fp16 operands rounded once from the exact fp32 weight: validation mode */
+    GT_MATH_FP32 = 2  /* CUDA-core fp32 FMA on exactly dequantized weights: validation mode */
+};
+
+enum gt_direction { GT_DIR_FORWARD = 0, GT_DIR_BACKWARD = 1 };
+
+enum gt_flags {
+    GT_FLAG_DEVICE_PTRS = 1, /* activation pointers are device pointers; asynchronous on the engine stream */
+    GT_FLAG_NO_LORA = 2      /* skip the adapter terms even when an adapter is given */
+};
+
+typedef struct gt_config {
+    int32_t device;       /* CUDA device ordinal                                              */
+    int32_t math_mode;    /* gt_math_mode                                                     */
+    void *stream;         /* cudaStream_t to run on, or NULL: the engine creates its own      */
+    int32_t max_tokens;   /* scratch is sized for this many tokens up front (0: 512); grows   */
+    int32_t reserved;
+} gt_config;
+
+GT_API const char *gt_last_error(void);
+GT_API const char *gt_version(void);
+
+/* Replaces: new GpuLoraEngine(weights, deviceOrdinal) / Dispose()
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.cs:114-218,335-383).  Weight upload is a separate call. */
+GT_API int gt_engine_create(const gt_config *cfg, gt_engine **out);
+GT_API int gt_engine_destroy(gt_engine *eng);
+GT_API int gt_engine_set_math_mode(gt_engine *eng, int math_mode);
+/* Wait for everything queued on the engine's stream; reports bounded-wait timeouts of the kernels. */
+GT_API int gt_sync(gt_engine *eng);
+
+/* Replaces: SupportsForwardGemm / SupportsBackwardGemm
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:13-14, GpuLoraEngine.Backward.cs:12-13).  Returns 1 or 0. */
+GT_API int gt_supports(int ggml_type, int direction);
+
+/* Replaces: UploadBaseWeights (src/Glacier.Tune/Gpu/GpuLoraEngine.cs:240-321) for one tensor, and the
+ * Get{Q,K,V,AttnOut,Gate,Up,Down}/Get*Bias handles (GpuLoraEngine.cs:323-333).
+ * host_bytes is the GGUF tensor data ([out, in] row-major, nbytes = out*in/256 * block size, or out*in*4
+ * for F32).  The bytes are copied; Q6_K is re-laid out on the device in 16-byte-aligned blocks with
+ * identical dequantized values.  bias may be NULL. */
+GT_API int gt_weight_upload(gt_engine *eng, int ggml_type, const void *host_bytes, int64_t nbytes,
+                            int32_t out_features, int32_t in_features, const float *bias_or_null,
+                            gt_weight **out);
+GT_API int gt_weight_free(gt_weight *w);
+
+/* Replaces: the role of QuantKernels.ExtractEmbedding(type, W, row, dst, K) on the uploaded copy
+ * (call sites src/Glacier.Tune/Kernels/LoraKernels.BaseBackward.cs:117,125): dequantize rows
+ * [row0, row0+nrows) to fp32, bit-exact with the reference decode
+ * (src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:209-211,234-240,279-289,311-315).  `out` follows `flags`. */
+GT_API int gt_dequant_rows(gt_engine *eng, const gt_weight *w, int64_t row0, int64_t nrows, float *out,
+                           int32_t flags);
+
+/* Replaces: the LoraAdapter state that the reference keeps on the host
+ * (src/Glacier.Tune/Model/LoraAdapter.cs:88-125): A, B and their gradient accumulators, on the device. */
+GT_API int gt_adapter_create(gt_engine *eng, int32_t in_features, int32_t out_features, int32_t rank, float alpha,
+                             gt_adapter **out);
+GT_API int gt_adapter_free(gt_adapter *ad);
+GT_API int gt_adapter_upload(gt_adapter *ad, const float *A_in_by_rank, const float *B_rank_by_out);
+GT_API int gt_adapter_download(gt_adapter *ad, float *A_in_by_rank, float *B_rank_by_out);
+GT_API int gt_adapter_grads_download(gt_adapter *ad, float *dA_in_by_rank, float *dB_rank_by_out);
+GT_API int gt_adapter_grads_zero(gt_adapter *ad);
+/* Replaces: LoraAdapter.UpdateAlpha (src/Glacier.Tune/Model/LoraAdapter.cs:74-77). */
+GT_API int gt_adapter_set_alpha(gt_adapter *ad, float alpha);
+/* Device addresses of A, B, dA, dB (fp32) for a resident optimizer or a gradient all-reduce. */
+GT_API int gt_adapter_device_ptrs(gt_adapter *ad, float **A, float **B, float **dA, float **dB);
+/* Point the adapter's gradient accumulators into a caller-owned device buffer (one flat allocation per
+ * model in the reference's parameter order, src/Glacier.Tune/Model/TransformerBlock.cs:167-174). */
+GT_API int gt_adapter_bind_grads(gt_adapter *ad, float *dA_dev, float *dB_dev);
+
+/* Replaces: LoraAdapter.Forward -> GpuLoraEngine.ForwardProjection + LoraKernels.ApplyLoraDelta
+ * (src/Glacier.Tune/Model/LoraAdapter.cs:128-184, src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:16-48,
+ *  src/Glacier.Tune/Kernels/LoraKernels.cs:18-122).
+ * Y[T,out] = X[T,in] * W^T + bias + scaling*(X*A)*B.  The adapter term is skipped when adapter is NULL,
+ * GT_FLAG_NO_LORA is set, or B is entirely zero (LoraAdapter.IsZeroDelta, LoraAdapter.cs:48-72). */
+GT_API int gt_proj_forward(gt_engine *eng, const gt_weight *w, gt_adapter *adapter_or_null, const float *X, float *Y,
+                           int32_t T, int32_t flags);
+
+/* Replaces: LoraAdapter.Backward -> GpuLoraEngine.BackwardProjection + LoraKernels.Backward
+ * (src/Glacier.Tune/Model/LoraAdapter.cs:190-260, src/Glacier.Tune/Gpu/GpuLoraEngine.Backward.cs:58-92,
+ *  src/Glacier.Tune/Kernels/LoraKernels.cs:125-346).
+ * dX (may be NULL) is ACCUMULATED into: dX += dY*W + scaling*(dY*B^T)*A^T; the reference hands in a
+ * zero-filled buffer (src/Glacier.Tune/Model/AutogradScratchWorkspace.cs:138-145).  The adapter's dA and dB
+ * accumulate across calls until gt_adapter_grads_zero. */
+GT_API int gt_proj_backward(gt_engine *eng, const gt_weight *w, gt_adapter *adapter_or_null, const float *dY,
+                            const float *X, float *dX_accum_or_null, int32_t T, int32_t flags);
+
+/* Replaces: GpuLoraEngine.LaunchGemmBatch(type, dY, dX, dW, kCols, mRows, batch, dBias, dResidual)
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:83-129): device pointers, asynchronous.
+ * Y (may be NULL) = X*W^T + bias; residual (may be NULL) += X*W^T + bias, as the reference kernels do
+ * (src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:118-124). */
+GT_API int gt_launch_gemm_batch(gt_engine *eng, const gt_weight *w, float *dY_out, const float *dX_in, int32_t batch,
+                                float *d_residual_or_null);
+/* Replaces: GpuLoraEngine.LaunchGemmBwd(type, dDX, dDY, dW, kCols, mRows, batch)
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Backward.cs:15-56): dDX[batch,in] += dDY[batch,out] * W. */
+GT_API int gt_launch_gemm_bwd(gt_engine *eng, const gt_weight *w, float *dDX_accum, const float *dDY, int32_t batch);
+
+/* Replaces: LoraTrainer.ScaleAccumulatedGradients / ClipGradients
+ * (src/Glacier.Tune/Trainer/LoraTrainer.cs:352-377,395-433) on a flat device gradient buffer:
+ * g *= pre_scale; norm = sqrt(sum g^2) in fp64; non-finite -> g = 0, *norm_out = 0; norm > max_norm ->
+ * g *= max_norm/(norm+1e-6).  norm_out is a host pointer; the call is complete on return. */
+GT_API int gt_grads_scale_clip(gt_engine *eng, float *g_dev, int64_t n, float pre_scale, double max_norm,
+                               double *norm_out);
+
+/* Data parallel step driver (no counterpart in the reference, which is single-GPU: one GpuContext,
+ * src/Glacier.Tune/Gpu/GpuLoraEngine.cs:114-130).  One process per GPU; each holds a replica of the frozen
+ * base and the adapters and processes its own sequences; the flat fp32 LoRA-gradient buffer is summed with
+ * one NCCL all-reduce on the engine stream, then scaled (1/world reproduces the reference's gradient-accumulation
+ * averaging, src/Glacier.Tune/Trainer/LoraTrainer.cs:217-220).  Rank 0 creates the 128-byte id and hands it
+ * to the other ranks out of band. */
+GT_API int gt_dp_unique_id(void *out_id, int32_t nbytes);
+GT_API int gt_dp_init(gt_engine *eng, int32_t world, int32_t rank, const void *unique_id, int32_t nbytes);
+GT_API int gt_dp_allreduce(gt_engine *eng, float *g_dev, int64_t count, float scale);
+GT_API int gt_dp_finalize(gt_engine *eng);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLACIERTUNE_B200_H */

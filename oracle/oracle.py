@@ -1,0 +1,233 @@
+"""ctypes front end of the CPU oracle (``oracle/gt_oracle.c``) plus numpy mirrors of its dequantizers.
+
+TEST INFRASTRUCTURE ONLY.  Imported by ``tests/``, by ``__graft_entry__.smoke()`` (as the checker) and by
+``bench.py``'s CPU-baseline leg.  The shipped package never imports this module.
+
+The numpy functions restate the same reference lines as the C file, independently, so the two can be
+checked against each other:
+  Q4_K decode  src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:28-33,43-51,209-211,234-240
+  Q6_K decode  src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:35-40,279-289,311-315   (parity unpinned: the
+               reference has no Q6_K test or CPU source)
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libgt_oracle.so")
+
+TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
+BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q6_K: 210}
+
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the committed Makefile (gcc, OpenMP)."""
+    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < os.path.getmtime(
+            os.path.join(HERE, "gt_oracle.c")):
+        subprocess.check_call(["make", "-C", HERE, "-s"])
+    return LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            build()
+        _lib = C.CDLL(LIB_PATH)
+        _lib.gt_oracle_half_to_float.restype = C.c_float
+        _lib.gt_oracle_half_to_float.argtypes = [C.c_uint16]
+        _lib.gt_oracle_float_to_half.restype = C.c_uint16
+        _lib.gt_oracle_float_to_half.argtypes = [C.c_float]
+        _lib.gt_oracle_clip_gradients.restype = C.c_double
+        _lib.gt_oracle_clip_gradients.argtypes = [C.c_void_p, C.c_int64, C.c_double]
+        _lib.gt_oracle_block_bytes.restype = C.c_int64
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _u8(a):
+    return np.ascontiguousarray(a, dtype=np.uint8)
+
+
+def num_threads() -> int:
+    return int(lib().gt_oracle_num_threads())
+
+
+def set_threads(n: int) -> None:
+    lib().gt_oracle_set_threads(C.c_int(n))
+
+
+def get_scale_min_k4(j: int, scales12) -> tuple[int, int]:
+    q = _u8(scales12)
+    sc, m = C.c_uint8(), C.c_uint8()
+    lib().gt_oracle_get_scale_min_k4(C.c_int(j), _p(q), C.byref(sc), C.byref(m))
+    return sc.value, m.value
+
+
+def set_scale_min_k4(j: int, scales12: np.ndarray, sc: int, m: int) -> None:
+    assert scales12.dtype == np.uint8 and scales12.flags.c_contiguous
+    lib().gt_oracle_set_scale_min_k4(C.c_int(j), _p(scales12), C.c_uint8(sc), C.c_uint8(m))
+
+
+def dequant_blocks(qtype: int, blocks) -> np.ndarray:
+    b = _u8(blocks).reshape(-1)
+    n = b.size // BLOCK_BYTES[qtype]
+    out = np.empty(n * 256, np.float32)
+    rc = lib().gt_oracle_dequant_blocks(C.c_int(qtype), _p(b), C.c_int64(n), _p(out))
+    assert rc == 0
+    return out
+
+
+def dequant_rows(qtype: int, w, K: int, row0: int, nrows: int) -> np.ndarray:
+    wb = _u8(w).reshape(-1) if qtype != TYPE_F32 else _f32(w).reshape(-1)
+    out = np.empty((nrows, K), np.float32)
+    rc = lib().gt_oracle_dequant_rows(C.c_int(qtype), _p(wb), C.c_int(K), C.c_int64(row0), C.c_int64(nrows), _p(out))
+    assert rc == 0
+    return out
+
+
+def quantize_row_q4k(src) -> np.ndarray:
+    s = _f32(src).reshape(-1)
+    assert s.size % 256 == 0
+    out = np.zeros(s.size // 256 * 144, np.uint8)
+    lib().gt_oracle_quantize_row_q4k(_p(s), _p(out), C.c_int(s.size))
+    return out
+
+
+def _w(qtype, w):
+    return _f32(w).reshape(-1) if qtype == TYPE_F32 else _u8(w).reshape(-1)
+
+
+def matmul_batch(qtype, w, x, K, N, T, bias=None, f64=False) -> np.ndarray:
+    wb, x = _w(qtype, w), _f32(x)
+    bias = None if bias is None else _f32(bias)
+    y = np.empty((T, N), np.float64 if f64 else np.float32)
+    fn = lib().gt_oracle_matmul_batch_f64 if f64 else lib().gt_oracle_matmul_batch
+    rc = fn(C.c_int(qtype), _p(wb), _p(x), _p(y), C.c_int(K), C.c_int(N), C.c_int(T), _p(bias))
+    assert rc == 0
+    return y
+
+
+def proj_forward(qtype, w, bias, x, K, N, T, a=None, b=None, R=0, scaling=0.0) -> np.ndarray:
+    """LoraAdapter.Forward on the CPU path (fp32)."""
+    wb, x = _w(qtype, w), _f32(x)
+    bias = None if bias is None else _f32(bias)
+    a = None if a is None else _f32(a)
+    b = None if b is None else _f32(b)
+    y = np.empty((T, N), np.float32)
+    rc = lib().gt_oracle_proj_forward(C.c_int(qtype), _p(wb), _p(bias), _p(x), _p(y), C.c_int(K), C.c_int(N),
+                                      C.c_int(T), _p(a), _p(b), C.c_int(R), C.c_float(scaling))
+    assert rc == 0
+    return y
+
+
+def proj_backward(qtype, w, dy, x, K, N, T, a=None, b=None, R=0, scaling=0.0, dx=None, ga=None, gb=None,
+                  want_dx=True):
+    """LoraAdapter.Backward on the CPU path: accumulates into dx / ga / gb (created as zeros when absent)."""
+    wb, dy, x = _w(qtype, w), _f32(dy), _f32(x)
+    if want_dx and dx is None:
+        dx = np.zeros((T, K), np.float32)
+    if a is not None:
+        a, b = _f32(a), _f32(b)
+        if ga is None:
+            ga = np.zeros((K, R), np.float32)
+        if gb is None:
+            gb = np.zeros((R, N), np.float32)
+    rc = lib().gt_oracle_proj_backward(C.c_int(qtype), _p(wb), _p(dy), _p(x), _p(dx), C.c_int(K), C.c_int(N),
+                                       C.c_int(T), _p(a), _p(b), _p(ga), _p(gb), C.c_int(R), C.c_float(scaling))
+    assert rc == 0
+    return dx, ga, gb
+
+
+def base_backward_f64(qtype, w, dy, K, N, T) -> np.ndarray:
+    wb, dy = _w(qtype, w), _f32(dy)
+    dx = np.empty((T, K), np.float64)
+    rc = lib().gt_oracle_base_backward_f64(C.c_int(qtype), _p(wb), _p(dy), _p(dx), C.c_int(T), C.c_int(K), C.c_int(N))
+    assert rc == 0
+    return dx
+
+
+def lora_backward(x, dy, a, b, T, K, N, R, scaling, dx=None, ga=None, gb=None):
+    x, dy, a, b = _f32(x), _f32(dy), _f32(a), _f32(b)
+    if ga is None:
+        ga = np.zeros((K, R), np.float32)
+    if gb is None:
+        gb = np.zeros((R, N), np.float32)
+    rc = lib().gt_oracle_lora_backward(_p(x), _p(dy), _p(a), _p(b), _p(ga), _p(gb), _p(dx), C.c_int(T), C.c_int(K),
+                                       C.c_int(N), C.c_int(R), C.c_float(scaling))
+    assert rc == 0
+    return dx, ga, gb
+
+
+def clip_gradients(g: np.ndarray, max_norm: float) -> float:
+    assert g.dtype == np.float32 and g.flags.c_contiguous
+    return float(lib().gt_oracle_clip_gradients(_p(g), C.c_int64(g.size), C.c_double(max_norm)))
+
+
+# ------------------------------------------------------------------------------------------------
+# numpy mirrors (independent restatement, vectorised)
+# ------------------------------------------------------------------------------------------------
+def np_unpack_scales_q4k(scales: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """scales [..., 12] uint8 -> (sc [..., 8], m [..., 8]) per tune_bwd.cu:43-51."""
+    q = scales.astype(np.uint8)
+    sc = np.empty(q.shape[:-1] + (8,), np.uint8)
+    m = np.empty_like(sc)
+    for j in range(4):
+        sc[..., j] = q[..., j] & 63
+        m[..., j] = q[..., j + 4] & 63
+    for j in range(4, 8):
+        sc[..., j] = (q[..., j + 4] & 0x0F) | ((q[..., j - 4] >> 6) << 4)
+        m[..., j] = (q[..., j + 4] >> 4) | ((q[..., j] >> 6) << 4)
+    return sc, m
+
+
+def np_dequant_q4k(blocks: np.ndarray) -> np.ndarray:
+    """blocks [nb, 144] uint8 -> [nb, 256] float32, fp32 arithmetic in the reference's order."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 144)
+    d = b[:, 0:2].copy().view(np.float16).astype(np.float32)            # [nb,1]
+    dmin = b[:, 2:4].copy().view(np.float16).astype(np.float32)
+    sc, m = np_unpack_scales_q4k(b[:, 4:16])
+    qs = b[:, 16:144].reshape(-1, 4, 32)
+    nib = np.stack([qs & 0x0F, qs >> 4], axis=2).reshape(-1, 8, 32).astype(np.float32)   # sub-block ib = 2g + hi
+    d_sub = (d * sc.astype(np.float32))[:, :, None]
+    m_sub = (dmin * m.astype(np.float32))[:, :, None]
+    return (d_sub * nib - m_sub).astype(np.float32).reshape(-1, 256)
+
+
+def np_dequant_q6k(blocks: np.ndarray) -> np.ndarray:
+    """blocks [nb, 210] uint8 -> [nb, 256] float32 per tune_bwd.cu:279-289,311-315."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 210)
+    ql, qh = b[:, 0:128], b[:, 128:192]
+    scales = b[:, 192:208].copy().view(np.int8).astype(np.float32)
+    d = b[:, 208:210].copy().view(np.float16).astype(np.float32)
+    c = np.arange(256)
+    step, rem = c >> 7, c & 127
+    quad, lane = rem >> 5, rem & 31
+    ql_idx = step * 64 + (quad & 1) * 32 + lane
+    ql_shift = np.where(quad >= 2, 4, 0).astype(np.uint8)
+    qh_idx = step * 32 + lane
+    qh_shift = (quad * 2).astype(np.uint8)
+    sc_idx = step * 8 + (lane >> 4) + quad * 2
+    q = (((ql[:, ql_idx] >> ql_shift) & 0x0F) | (((qh[:, qh_idx] >> qh_shift) & 0x03) << 4)).astype(np.int32) - 32
+    return ((d * scales[:, sc_idx]).astype(np.float32) * q.astype(np.float32)).astype(np.float32)
+
+
+def rel_fro(got, want) -> float:
+    """Relative Frobenius error ||got - want|| / ||want|| in fp64."""
+    g = np.asarray(got, np.float64)
+    w = np.asarray(want, np.float64)
+    den = np.linalg.norm(w)
+    return float(np.linalg.norm(g - w) / (den if den > 0 else 1.0))
