@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the frozen-base K-quant projection path on B200.
+
+A step is one pass of the hot path over one 512-token sequence: the seven Qwen2.5-7B layer projections
+(q, k, v, o, gate, up, down; Q4_K base, LoRA r=16, alpha=32), each forward + dX + dA/dB, through
+libglaciertune_b200.so.  The metric counts the base GEMM terms only: 4*M*N*K per projection, 477.28 GFLOP per
+step.  With N > 1 GPUs every rank runs the same step on its own sequence (weak scaling) and the flat fp32
+LoRA-gradient buffer of the layer is summed with one NCCL all-reduce inside the step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+`--impl reference` times the CPU restatement of the reference's own CPU path (the oracle) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from glacier.tune_b200 import synth  # noqa: E402
+
+M_TOKENS = 512
+RANK, ALPHA = 16, 32.0
+PROJ_ORDER = ["q", "k", "v", "o", "gate", "up", "down"]
+METRIC = "q4k_gemm_fwd_dx_tflops"
+UNIT = "TFLOP/s"
+WORKLOAD = "qwen2.5-7b layer projections q,k,v,o,gate,up,down in Q4_K, M=512, fwd+dX+LoRA grads (r=16)"
+# DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/ (None until captured)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def step_flops(names=PROJ_ORDER, m=M_TOKENS) -> float:
+    return float(sum(4 * m * synth.QWEN7B_PROJ[n][0] * synth.QWEN7B_PROJ[n][1] for n in names))
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(bf16_tflops=float(d["bf16_tflops"]), bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", 0)),
+                    hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_layer_pass(O, cases) -> float:
+    """One pass of LoraAdapter.Forward + LoraAdapter.Backward per projection on the CPU path; returns seconds."""
+    t0 = time.perf_counter()
+    for c in cases:
+        O.proj_forward(c["qtype"], c["w"], None, c["x"], c["K"], c["N"], c["T"], c["a"], c["b"], RANK, c["scaling"])
+        O.proj_backward(c["qtype"], c["w"], c["dy"], c["x"], c["K"], c["N"], c["T"], c["a"], c["b"], RANK, c["scaling"])
+    return time.perf_counter() - t0
+
+
+def make_cpu_cases(names, seed_base=0):
+    return [synth.make_projection_case(synth.TYPE_Q4_K, *synth.QWEN7B_PROJ[n], M_TOKENS,
+                                       synth.seed_for(1, 0, n) + seed_base, rank=RANK, alpha=ALPHA, x_bf16=True)
+            for n in names]
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    cores = O.num_threads()
+    budget_s = 150.0
+    names = list(PROJ_ORDER)
+    cases = make_cpu_cases(["k"])
+    cpu_layer_pass(O, cases)                      # page in / warm the thread pool
+    probe = make_cpu_cases(["q"])
+    t_q = cpu_layer_pass(O, probe)
+    est_full = t_q * step_flops() / step_flops(["q"])
+    if est_full * (args.steps + args.warmup) > budget_s:
+        names = ["q", "k", "v", "o"]
+        if t_q * step_flops(names) / step_flops(["q"]) * (args.steps + args.warmup) > budget_s:
+            names = ["q"]
+    cases = make_cpu_cases(names)
+    for _ in range(args.warmup):
+        cpu_layer_pass(O, cases)
+    times = [cpu_layer_pass(O, cases) for _ in range(args.steps)]
+    total = sum(times)
+    fl = step_flops(names)
+    value = fl * args.steps / total / 1e12
+    sample = f"projections {','.join(names)} of the workload per step ({fl / 1e9:.1f} GFLOP), fp32, OpenMP"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens": M_TOKENS, "rank": RANK},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms from the warm-up to the end of the timed region
+    (samples below 250 W are idle and dropped)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.NamedTemporaryFile(prefix="gt_clocks_", suffix=".csv", delete=False).name
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                                          "50", "-i", str(self.gpu_index)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for ln in f:
+                    p = [x.strip() for x in ln.split(",")]
+                    if len(p) < 9:
+                        continue
+                    try:
+                        if float(p[3]) < 250.0:       # idle samples (before the load starts) are not "under load"
+                            continue
+                        sm.append(float(p[1]))
+                        mx.append(float(p[2]))
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from glacier.tune_b200 import capi as G
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the projection path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    # a real (non-default) stream shared by torch and the engine, so torch.cuda.Event brackets the engine's kernels
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
+    eng = G.Engine(local_rank, G.MATH_BF16, stream=stream.cuda_stream)
+
+    # ---- build the layer: weights, adapters (grads bound into one flat buffer in the reference's order)
+    n_grad = sum(RANK * (synth.QWEN7B_PROJ[n][0] + synth.QWEN7B_PROJ[n][1]) for n in PROJ_ORDER)
+    flat_grads = torch.zeros(n_grad, dtype=torch.float32, device=dev)
+    layer, off = [], 0
+    for n in PROJ_ORDER:
+        N, K = synth.QWEN7B_PROJ[n]
+        c = synth.make_projection_case(synth.TYPE_Q4_K, N, K, M_TOKENS, synth.seed_for(1, 0, n) + 100000 * rank, rank=RANK,
+                                       alpha=ALPHA, x_bf16=True)
+        w = eng.upload_weight(synth.TYPE_Q4_K, c["w"], N, K)
+        ad = eng.create_adapter(K, N, RANK, ALPHA)
+        ad.upload(c["a"], c["b"])
+        dA = flat_grads[off: off + K * RANK]; off += K * RANK
+        dB = flat_grads[off: off + RANK * N]; off += RANK * N
+        ad.bind_grads(dA, dB)
+        pin = lambda a: torch.from_numpy(a).pin_memory()   # noqa: E731
+        hx, hdy = pin(c["x"]), pin(c["dy"])
+        layer.append(dict(name=n, N=N, K=K, w=w, ad=ad, hx=hx, hdy=hdy,
+                          hy=torch.empty((M_TOKENS, N), dtype=torch.float32).pin_memory(),
+                          hdx=torch.zeros((M_TOKENS, K), dtype=torch.float32).pin_memory(),
+                          X=hx.to(dev), dY=hdy.to(dev), Y=torch.empty((M_TOKENS, N), dtype=torch.float32, device=dev),
+                          dX=torch.empty((M_TOKENS, K), dtype=torch.float32, device=dev)))
+    if world > 1:
+        ident = [eng.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ident, src=0)
+        eng.dp_init(world, rank, ident[0])
+
+    l2_flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step_resident():
+        flat_grads.zero_()
+        for p in layer:
+            eng.forward(p["w"], p["ad"], p["X"], p["Y"])
+        for p in reversed(layer):
+            p["dX"].zero_()     # the reference hands Backward a zero-filled dX (AutogradScratchWorkspace.Wrap)
+            eng.backward(p["w"], p["ad"], p["dY"], p["X"], p["dX"])
+        if world > 1:
+            eng.dp_allreduce(flat_grads, 1.0 / world)
+
+    def step_host():
+        for p in layer:
+            eng.forward(p["w"], p["ad"], p["hx"].numpy(), p["hy"].numpy())
+        for p in reversed(layer):
+            eng.backward(p["w"], p["ad"], p["hdy"].numpy(), p["hx"].numpy(), p["hdx"].numpy())
+        if world > 1:
+            eng.dp_allreduce(flat_grads, 1.0 / world)
+            eng.sync()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing.  The clock sampler starts before the warm-up, and the warm-up runs for at
+    # least half a second so that the clocks have ramped and nvidia-smi has samples taken under load.
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    warm_t0, n_warm = time.perf_counter(), 0
+    while n_warm < max(args.warmup, 3) or time.perf_counter() - warm_t0 < 0.6:
+        step_resident()
+        l2_flush.zero_()
+        n_warm += 1
+        if n_warm % 16 == 0:
+            torch.cuda.synchronize()
+    eng.sync()
+    eng.profile_read(reset=True)
+    eng.profile_enable(True)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        l2_flush.zero_()                      # > L2 (126 MB) written between timed steps
+        starts[i].record(stream)
+        step_resident()
+        ends[i].record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else {}
+    eng.sync()
+    prof = eng.profile_read(reset=True)
+    eng.profile_enable(False)
+    total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    fl = step_flops()
+    value = world * fl * args.steps / (total_ms * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers (H2D of the inputs, D2H of the results, every step)
+    e2e_steps = max(1, min(args.steps, 8))
+    step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_host()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    e2e_value = world * fl * e2e_steps / e2e_s / 1e12
+    h2d = sum(4 * M_TOKENS * (p["K"] + p["N"] + p["K"] + p["K"]) for p in layer)   # X (fwd), dY, X, dX (bwd)
+    d2h = sum(4 * M_TOKENS * (p["N"] + p["K"]) for p in layer)                      # Y, dX
+
+    if rank == 0:
+        peaks = measured_peaks()
+        gemm_tflops = prof["gemm_flops"] / (prof["gemm_ms"] * 1e-3) / 1e12 if prof["gemm_ms"] > 0 else 0.0
+        roofline = {
+            "bound": "tensor", "kernel": "k_umma_gemm (tcgen05 Q4_K forward / dX)",
+            "achieved": gemm_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": gemm_tflops / peaks["bf16_tflops"], "peak_source": f"{peaks['source']} burst bf16",
+            "frac_of_sustained": (gemm_tflops / peaks["bf16_tflops_sustained"]) if peaks["bf16_tflops_sustained"] else None,
+            "launches": prof["gemm_launches"], "avg_launch_us": 1e3 * prof["gemm_ms"] / max(1, prof["gemm_launches"]),
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+        }
+        # CPU baseline: the oracle (a port of the reference's CPU path) on this host, one pass over the same layer
+        from oracle import oracle as O
+        O.build()
+        cpu_layer_pass(O, make_cpu_cases(["k"]))
+        names = list(PROJ_ORDER)
+        t_q = cpu_layer_pass(O, make_cpu_cases(["q"]))
+        if t_q * step_flops() / step_flops(["q"]) > 45.0:
+            names = ["q", "k", "v", "o"]
+        cpu_s = cpu_layer_pass(O, make_cpu_cases(names))
+        cpu_val = step_flops(names) / cpu_s / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens_per_gpu": M_TOKENS, "rank": RANK, "parallelism": f"dp{world}",
+                       "l2": "256 MiB written between timed steps; per-step inputs (131 MB weights + activations) exceed L2",
+                       "tokens_per_s": world * M_TOKENS * args.steps / (total_ms * 1e-3)},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps},
+            "gpu_launches": prof["kernel_launches"],
+            "roofline": roofline,
+            "cpu_baseline": {"value": cpu_val, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+                             "sample": f"one pass over projections {','.join(names)} ({step_flops(names) / 1e9:.1f} GFLOP), fp32 OpenMP"},
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        eng.dp_finalize()
+        dist.destroy_process_group()
+    eng.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -24,7 +24,7 @@ EXPORTS = [
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_grads_scale_clip",
-    "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
+    "gt_profile_enable", "gt_profile_read", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
 
@@ -79,6 +79,9 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
+    lib.gt_profile_enable.argtypes = [C.c_void_p, C.c_int]
+    lib.gt_profile_read.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double),
+                                    C.POINTER(C.c_int64), C.c_int]
     if hasattr(lib, "gt_dp_init"):
         lib.gt_dp_unique_id.argtypes = [C.c_void_p, C.c_int32]
         lib.gt_dp_init.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32]
@@ -197,6 +200,14 @@ class Engine:
         norm = C.c_double()
         _check(self.lib.gt_grads_scale_clip(self.h, _ptr(g_dev)[0], g_dev.numel(), pre_scale, max_norm, C.byref(norm)))
         return norm.value
+
+    def profile_enable(self, on: bool = True):
+        _check(self.lib.gt_profile_enable(self.h, 1 if on else 0))
+
+    def profile_read(self, reset: bool = True) -> dict:
+        ms, nl, fl, kl = C.c_double(), C.c_int64(), C.c_double(), C.c_int64()
+        _check(self.lib.gt_profile_read(self.h, C.byref(ms), C.byref(nl), C.byref(fl), C.byref(kl), 1 if reset else 0))
+        return dict(gemm_ms=ms.value, gemm_launches=nl.value, gemm_flops=fl.value, kernel_launches=kl.value)
 
     # ---- data parallel ----------------------------------------------------------------------------
     def dp_unique_id(self) -> bytes:

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "../../../include/glaciertune_b200.h"
 #include "gt_internal.h"
@@ -33,6 +34,12 @@ int fail(int code, const char *fmt, ...) {
     do {                                                                                                \
         cudaError_t _e = (call);                                                                        \
         if (_e != cudaSuccess) return fail(GT_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(_e)); \
+    } while (0)
+
+#define GT_LAUNCH(eng, call) \
+    do {                       \
+        GT_CUDA(call);         \
+        (eng)->kernel_launches += 1; \
     } while (0)
 
 // grow-only device buffer (the reference engine grows its scratch x2 on demand and never shrinks:
@@ -72,6 +79,12 @@ struct gt_engine {
     Scratch h_in0, h_in1, h_out;  // device staging for host-pointer calls
     ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
     int dp_world = 1, dp_rank = 0;
+    // profiling: CUDA-event pairs around every tensor-core GEMM launch, and a count of kernel launches
+    bool profile = false;
+    std::vector<cudaEvent_t> ev_pool;
+    size_t ev_used = 0;
+    double gemm_flops = 0.0;
+    int64_t gemm_launches = 0, kernel_launches = 0;
 };
 
 struct gt_weight {
@@ -108,16 +121,41 @@ bool tensor_path(const gt_engine *e, const gt_weight *w) {
 
 int round8(int n) { return (n + 7) & ~7; }
 
+cudaEvent_t next_event(gt_engine *e) {
+    if (e->ev_used == e->ev_pool.size()) {
+        cudaEvent_t ev = nullptr;
+        if (cudaEventCreate(&ev) != cudaSuccess) return nullptr;
+        e->ev_pool.push_back(ev);
+    }
+    return e->ev_pool[e->ev_used++];
+}
+
+// launch the tensor-core GEMM, bracketed by events when profiling is on
+cudaError_t timed_umma(gt_engine *e, const UmmaLaunch &L, const char **msg) {
+    cudaEvent_t a = nullptr, b = nullptr;
+    if (e->profile) {
+        a = next_event(e);
+        b = next_event(e);
+        if (a) cudaEventRecord(a, e->stream);
+    }
+    cudaError_t ce = launch_umma_gemm(L, e->stream, msg);
+    if (e->profile && b) cudaEventRecord(b, e->stream);
+    e->gemm_launches += 1;
+    e->kernel_launches += 1;
+    e->gemm_flops += 2.0 * (double)L.T * (double)L.w->N * (double)L.w->K;
+    return ce;
+}
+
 // out[T, N] = act * W^T (+bias) (+ lora) on the engine stream, device pointers.
 int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora) {
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
     if (use_lora) GT_CUDA(e->low.reserve((size_t)T * ad->rank * sizeof(float)));
     if (!tensor_path(e, w)) {
-        GT_CUDA(launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
+        GT_LAUNCH(e, launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
         if (use_lora) {
-            GT_CUDA(launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, ad->rank, e->stream));
-            GT_CUDA(launch_lora_delta_fp32((const float *)e->low.p, ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling,
+            GT_LAUNCH(e, launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, ad->rank, e->stream));
+            GT_LAUNCH(e, launch_lora_delta_fp32((const float *)e->low.p, ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling,
                                            ad->b_nonzero, e->stream));
         }
         return GT_OK;
@@ -126,10 +164,10 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
     GT_CUDA(e->x16.reserve((size_t)T * K * 2));
     if (use_lora) {
         GT_CUDA(e->low16.reserve((size_t)T * 64 * 2));
-        GT_CUDA(launch_lora_low(Xd, ad->A, (float *)e->low.p, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
-        GT_CUDA(launch_pack_low16((const float *)e->low.p, e->low16.p, ad->scaling, T, ad->rank, fp16, e->stream));
+        GT_LAUNCH(e, launch_lora_low(Xd, ad->A, (float *)e->low.p, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
+        GT_LAUNCH(e, launch_pack_low16((const float *)e->low.p, e->low16.p, ad->scaling, T, ad->rank, fp16, e->stream));
     } else {
-        GT_CUDA(launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
+        GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
     }
     UmmaLaunch L;
     L.w = &wd;
@@ -143,7 +181,7 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
     L.bias = wd.bias;
     L.splits = umma_pick_splits(&wd, 0, T, e->sm_count);
     if (L.splits > 1) {
-        GT_CUDA(launch_fill_rows(Yd, wd.bias, T, N, e->stream));
+        GT_LAUNCH(e, launch_fill_rows(Yd, wd.bias, T, N, e->stream));
         L.out_prefilled = 1;
     }
     if (use_lora) {
@@ -154,7 +192,7 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
     }
     L.status = e->status;
     const char *msg = nullptr;
-    cudaError_t ce = launch_umma_gemm(L, e->stream, &msg);
+    cudaError_t ce = timed_umma(e, L, &msg);
     if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
     return GT_OK;
 }
@@ -172,22 +210,22 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
         const int R = ad->rank;
         GT_CUDA(e->low.reserve((size_t)T * R * sizeof(float)));
         GT_CUDA(e->dlow.reserve((size_t)T * R * sizeof(float)));
-        GT_CUDA(launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, R, e->stream));
+        GT_LAUNCH(e, launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, R, e->stream));
         GT_CUDA(cudaMemsetAsync(e->dlow.p, 0, (size_t)T * R * sizeof(float), e->stream));
-        GT_CUDA(launch_lora_bwd_dy(dYd, (const float *)e->low.p, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr,
+        GT_LAUNCH(e, launch_lora_bwd_dy(dYd, (const float *)e->low.p, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr,
                                    ld16, fp16, ad->scaling, T, N, R, e->stream));
-        GT_CUDA(launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
-        if (dXd && !tensor) GT_CUDA(launch_lora_dx_fp32((const float *)e->dlow.p, ad->A, dXd, ad->scaling, T, K, R, e->stream));
+        GT_LAUNCH(e, launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
+        if (dXd && !tensor) GT_LAUNCH(e, launch_lora_dx_fp32((const float *)e->dlow.p, ad->A, dXd, ad->scaling, T, K, R, e->stream));
         if (tensor) {
             GT_CUDA(e->dlow16.reserve((size_t)T * 64 * 2));
-            GT_CUDA(launch_pack_low16((const float *)e->dlow.p, e->dlow16.p, ad->scaling, T, R, fp16, e->stream));
+            GT_LAUNCH(e, launch_pack_low16((const float *)e->dlow.p, e->dlow16.p, ad->scaling, T, R, fp16, e->stream));
         }
     } else if (tensor) {
-        GT_CUDA(launch_cast16(dYd, e->dy16.p, T, N, ld16, fp16, e->stream));
+        GT_LAUNCH(e, launch_cast16(dYd, e->dy16.p, T, N, ld16, fp16, e->stream));
     }
     if (!dXd) return GT_OK;
     if (!tensor) {
-        GT_CUDA(launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
+        GT_LAUNCH(e, launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
         return GT_OK;
     }
     UmmaLaunch L;
@@ -208,7 +246,7 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
     }
     L.status = e->status;
     const char *msg = nullptr;
-    cudaError_t ce = launch_umma_gemm(L, e->stream, &msg);
+    cudaError_t ce = timed_umma(e, L, &msg);
     if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
     return GT_OK;
 }
@@ -278,6 +316,7 @@ int gt_engine_destroy(gt_engine *e) {
     for (Scratch *s : all) s->release();
     if (e->status) cudaFree(e->status);
     if (e->clip) cudaFree(e->clip);
+    for (cudaEvent_t ev : e->ev_pool) cudaEventDestroy(ev);
     if (e->own_stream && e->stream) cudaStreamDestroy(e->stream);
     delete e;
     return GT_OK;
@@ -296,6 +335,38 @@ int gt_sync(gt_engine *e) {
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
     return check_status(e);
+}
+
+int gt_profile_enable(gt_engine *e, int on) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    std::lock_guard<std::mutex> lk(e->mu);
+    e->profile = on != 0;
+    return GT_OK;
+}
+
+int gt_profile_read(gt_engine *e, double *gemm_ms, int64_t *gemm_launches, double *gemm_flops, int64_t *kernel_launches,
+                    int reset) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    GT_CUDA(cudaStreamSynchronize(e->stream));
+    double ms = 0.0;
+    for (size_t i = 0; i + 1 < e->ev_used; i += 2) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, e->ev_pool[i], e->ev_pool[i + 1]) == cudaSuccess) ms += t;
+    }
+    cudaGetLastError();
+    if (gemm_ms) *gemm_ms = ms;
+    if (gemm_launches) *gemm_launches = e->gemm_launches;
+    if (gemm_flops) *gemm_flops = e->gemm_flops;
+    if (kernel_launches) *kernel_launches = e->kernel_launches;
+    if (reset) {
+        e->ev_used = 0;
+        e->gemm_launches = 0;
+        e->kernel_launches = 0;
+        e->gemm_flops = 0.0;
+    }
+    return GT_OK;
 }
 
 int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_t nbytes, int32_t out_features,

@@ -1,0 +1,44 @@
+"""Host-side pieces of the data-parallel step driver (one process per GPU).
+
+The frozen quantized base and the adapters are replicated; each rank processes its own sequences; after the
+backward pass the flat fp32 LoRA-gradient buffer is summed across ranks and scaled by 1/world, which reproduces
+the reference's gradient-accumulation averaging (src/Glacier.Tune/Trainer/LoraTrainer.cs:217-220) with ranks in
+the place of micro-batches.  On GPUs the sum is the library's NCCL all-reduce (gt_dp_allreduce); the functions
+here are the parts that need no GPU: the layout of the flat buffer and the rendezvous of the NCCL id.
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+PROJ_ORDER = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def flat_grad_layout(proj_shapes: Iterable[tuple[str, int, int]], rank: int, layers: int = 1):
+    """Offsets of (dA [in, r], dB [r, out]) per layer and projection inside one flat buffer.
+
+    Order follows the reference's parameter list: layer, then q, k, v, o, gate, up, down, then A before B
+    (src/Glacier.Tune/Model/TransformerBlock.cs:167-174).  proj_shapes yields (name, out_features, in_features).
+    Returns (entries, total) with entries[(layer, name)] = (offset_dA, size_dA, offset_dB, size_dB).
+    """
+    shapes = list(proj_shapes)
+    entries, off = {}, 0
+    for layer in range(layers):
+        for name, out_f, in_f in shapes:
+            na, nb = in_f * rank, rank * out_f
+            entries[(layer, name)] = (off, na, off + na, nb)
+            off += na + nb
+    return entries, off
+
+
+def share_unique_id(make_id, dist_module, src: int = 0) -> bytes:
+    """Rank `src` creates the communicator id; every rank returns the same bytes (torch.distributed rendezvous)."""
+    box = [make_id() if dist_module.get_rank() == src else None]
+    dist_module.broadcast_object_list(box, src=src)
+    return box[0]
+
+
+def average_gradients_reference(flat, dist_module) -> None:
+    """The same reduction with torch.distributed (gloo on CPU): sum over ranks, then 1/world.  Used by the CPU tests
+    of the driver logic; the GPU path calls gt_dp_allreduce instead."""
+    dist_module.all_reduce(flat)
+    flat.mul_(1.0 / dist_module.get_world_size())

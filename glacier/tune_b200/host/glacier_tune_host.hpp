@@ -1,0 +1,133 @@
+// C++ host mirror of the reference's projection API over the C ABI of libglaciertune_b200.so.
+//
+// The reference host is C# (src/Glacier.Tune/Gpu/GpuLoraEngine*.cs, src/Glacier.Tune/Model/LoraAdapter.cs); this header
+// keeps its member names, argument order and error behaviour (a failing call throws, as CuDriver.Check does) so a
+// maintainer can read one against the other.  It contains no arithmetic: every call lands in the shared library.
+#pragma once
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../../include/glaciertune_b200.h"
+
+namespace Glacier::Tune {
+
+enum class GgufType : int { F32 = GT_TYPE_F32, Q4_K = GT_TYPE_Q4_K, Q6_K = GT_TYPE_Q6_K };
+
+// Minimal stand-in for Glacier.Tensor's Tensor<float>: caller-owned contiguous fp32 memory.
+struct Tensor {
+    float *DataPointer = nullptr;
+    int Shape[2] = {0, 0};
+    Tensor() = default;
+    Tensor(float *p, int rows, int cols) : DataPointer(p), Shape{rows, cols} {}
+    int64_t ElementCount() const { return (int64_t)Shape[0] * Shape[1]; }
+};
+
+inline void Check(int rc, const char *label) {
+    if (rc != GT_OK) throw std::runtime_error(std::string(label) + ": " + gt_last_error());
+}
+
+// Replaces GpuLoraEngine (src/Glacier.Tune/Gpu/GpuLoraEngine.cs:114-218).  The constructor throws when no sm_100
+// device is usable; the reference's caller logs and carries on on the CPU (src/Glacier.Tune/Model/GgufLoraModel.cs:76-80).
+class GpuLoraEngine {
+public:
+    explicit GpuLoraEngine(int deviceOrdinal = 0, int mathMode = GT_MATH_BF16) {
+        gt_config cfg{};
+        cfg.device = deviceOrdinal;
+        cfg.math_mode = mathMode;
+        Check(gt_engine_create(&cfg, &eng_), "gt_engine_create");
+    }
+    ~GpuLoraEngine() { Dispose(); }
+    GpuLoraEngine(const GpuLoraEngine &) = delete;
+    GpuLoraEngine &operator=(const GpuLoraEngine &) = delete;
+
+    void Dispose() {
+        for (gt_weight *w : weights_) gt_weight_free(w);
+        weights_.clear();
+        if (eng_) gt_engine_destroy(eng_);
+        eng_ = nullptr;
+    }
+    gt_engine *Handle() const { return eng_; }
+
+    bool SupportsForwardGemm(GgufType t) const { return gt_supports((int)t, GT_DIR_FORWARD) != 0; }
+    bool SupportsBackwardGemm(GgufType t) const { return gt_supports((int)t, GT_DIR_BACKWARD) != 0; }
+
+    // One tensor of UploadBaseWeights (GpuLoraEngine.cs:240-321); the handle plays the role of GetQ/GetK/... (:323-333).
+    gt_weight *UploadBaseWeight(GgufType type, const void *bytes, int64_t nbytes, int outFeatures, int inFeatures,
+                                const float *bias = nullptr) {
+        gt_weight *w = nullptr;
+        Check(gt_weight_upload(eng_, (int)type, bytes, nbytes, outFeatures, inFeatures, bias, &w), "gt_weight_upload");
+        weights_.push_back(w);
+        return w;
+    }
+
+    // GpuLoraEngine.Forward.cs:16-48: host tensors in and out, complete on return.
+    void ForwardProjection(GgufType, gt_weight *dW, const Tensor &x, Tensor &output, int /*inFeatures*/, int /*outFeatures*/,
+                           int seqLen) {
+        Check(gt_proj_forward(eng_, dW, nullptr, x.DataPointer, output.DataPointer, seqLen, 0), "ForwardProjection");
+    }
+    // GpuLoraEngine.Backward.cs:58-92: dXInput is accumulated into.
+    void BackwardProjection(GgufType, gt_weight *dW, const Tensor &dY, Tensor &dXInput, int, int, int seqLen) {
+        Check(gt_proj_backward(eng_, dW, nullptr, dY.DataPointer, nullptr, dXInput.DataPointer, seqLen, 0), "BackwardProjection");
+    }
+    // GpuLoraEngine.Forward.cs:83-129 / Backward.cs:15-56: device pointers, asynchronous.
+    void LaunchGemmBatch(gt_weight *dW, float *dY, const float *dX, int batchSize, float *dResidual = nullptr) {
+        Check(gt_launch_gemm_batch(eng_, dW, dY, dX, batchSize, dResidual), "LaunchGemmBatch");
+    }
+    void LaunchGemmBwd(gt_weight *dW, float *dDX, const float *dDY, int batchSize) {
+        Check(gt_launch_gemm_bwd(eng_, dW, dDX, dDY, batchSize), "LaunchGemmBwd");
+    }
+    void Synchronize() { Check(gt_sync(eng_), "gt_sync"); }
+
+private:
+    gt_engine *eng_ = nullptr;
+    std::vector<gt_weight *> weights_;
+};
+
+// Replaces LoraAdapter (src/Glacier.Tune/Model/LoraAdapter.cs).  A is [InFeatures, Rank], B is [Rank, OutFeatures].
+class LoraAdapter {
+public:
+    LoraAdapter(GpuLoraEngine &engine, int inFeatures, int outFeatures, int rank = 16, float alpha = 32.f)
+        : engine_(engine), in_(inFeatures), out_(outFeatures), rank_(rank), scaling_(rank > 0 ? alpha / rank : 0.f) {
+        Check(gt_adapter_create(engine.Handle(), inFeatures, outFeatures, rank, alpha, &ad_), "gt_adapter_create");
+    }
+    ~LoraAdapter() { gt_adapter_free(ad_); }
+    LoraAdapter(const LoraAdapter &) = delete;
+    LoraAdapter &operator=(const LoraAdapter &) = delete;
+
+    int InFeatures() const { return in_; }
+    int OutFeatures() const { return out_; }
+    int Rank() const { return rank_; }
+    float Scaling() const { return scaling_; }
+
+    void SetGpuBaseWeights(gt_weight *dBaseWeight) { w_ = dBaseWeight; }             // LoraAdapter.cs:79-84
+    void UpdateAlpha(float alpha) {                                                    // LoraAdapter.cs:74-77
+        scaling_ = rank_ > 0 ? alpha / rank_ : 0.f;
+        Check(gt_adapter_set_alpha(ad_, alpha), "gt_adapter_set_alpha");
+    }
+    void SetParameters(const float *A, const float *B) { Check(gt_adapter_upload(ad_, A, B), "gt_adapter_upload"); }
+    void GetParameters(float *A, float *B) { Check(gt_adapter_download(ad_, A, B), "gt_adapter_download"); }
+    void GetGradients(float *dA, float *dB) { Check(gt_adapter_grads_download(ad_, dA, dB), "gt_adapter_grads_download"); }
+    void ZeroGrad() { Check(gt_adapter_grads_zero(ad_), "gt_adapter_grads_zero"); }
+
+    // LoraAdapter.cs:128-184: output = x W^T + bias + scaling (x A) B (delta skipped while B == 0).
+    void Forward(GgufType, const Tensor &x, Tensor &output, int seqLen) {
+        Check(gt_proj_forward(engine_.Handle(), w_, ad_, x.DataPointer, output.DataPointer, seqLen, 0), "LoraAdapter.Forward");
+    }
+    // LoraAdapter.cs:190-219: dXInput (optional) += dY W + adapter term; dA, dB accumulate.
+    void Backward(GgufType, const Tensor &dY, const Tensor &x, Tensor *dXInput = nullptr) {
+        Check(gt_proj_backward(engine_.Handle(), w_, ad_, dY.DataPointer, x.DataPointer, dXInput ? dXInput->DataPointer : nullptr,
+                               x.Shape[0], 0),
+              "LoraAdapter.Backward");
+    }
+
+private:
+    GpuLoraEngine &engine_;
+    gt_weight *w_ = nullptr;
+    gt_adapter *ad_ = nullptr;
+    int in_, out_, rank_;
+    float scaling_;
+};
+
+}  // namespace Glacier::Tune

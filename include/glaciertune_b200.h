@@ -161,6 +161,15 @@ GT_API int gt_launch_gemm_bwd(gt_engine *eng, const gt_weight *w, float *dDX_acc
 GT_API int gt_grads_scale_clip(gt_engine *eng, float *g_dev, int64_t n, float pre_scale, double max_norm,
                                double *norm_out);
 
+/* Profiling (the reference only has Stopwatch breakdowns at Debug level,
+ * src/Glacier.Tune/Model/TransformerBlock.cs:311-312,582-586).  While enabled, every tensor-core GEMM launch is
+ * bracketed by CUDA events on the engine stream.  gt_profile_read synchronises and returns the summed GEMM time,
+ * the number of GEMM launches, their base-term FLOPs (2*T*out*in each) and the number of kernels launched by
+ * the projection calls since the last reset. */
+GT_API int gt_profile_enable(gt_engine *eng, int on);
+GT_API int gt_profile_read(gt_engine *eng, double *gemm_ms, int64_t *gemm_launches, double *gemm_flops,
+                           int64_t *kernel_launches, int reset);
+
 /* Data parallel step driver (no counterpart in the reference, which is single-GPU: one GpuContext,
  * src/Glacier.Tune/Gpu/GpuLoraEngine.cs:114-130).  One process per GPU; each holds a replica of the frozen
  * base and the adapters and processes its own sequences; the flat fp32 LoRA-gradient buffer is summed with

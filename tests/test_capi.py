@@ -1,0 +1,73 @@
+"""CPU tests of the drop-in boundary: the shared library loads, exports every symbol the header declares, and
+refuses to run without a GPU (there is no CPU fallback).  No compute calls here."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "glaciertune_b200.h")).read()
+    return sorted(set(re.findall(r"GT_API\s+[\w\s\*]+?\b(gt_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_surface():
+    syms = _header_symbols()
+    for name in ("gt_engine_create", "gt_weight_upload", "gt_proj_forward", "gt_proj_backward", "gt_dequant_rows",
+                 "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_dp_allreduce", "gt_last_error"):
+        assert name in syms
+    assert len(syms) >= 28
+
+
+def test_library_exports_every_declared_symbol():
+    from glacier.tune_b200 import capi
+    lib = capi.load_library()
+    for name in _header_symbols():
+        assert hasattr(lib, name), f"{name} declared in include/glaciertune_b200.h but not exported"
+    assert set(capi.EXPORTS) == set(_header_symbols())
+    assert b"sm_100a" in lib.gt_version()
+
+
+def test_supports_mirrors_reference_type_list():
+    from glacier.tune_b200 import capi
+    for t in (capi.TYPE_Q4_K, capi.TYPE_Q6_K, capi.TYPE_F32):
+        assert capi.supports(t, capi.DIR_FORWARD) and capi.supports(t, capi.DIR_BACKWARD)
+    assert not capi.supports(13, capi.DIR_FORWARD)      # Q5_K: not on this path
+    assert not capi.supports(capi.TYPE_Q4_K, 7)
+
+
+def test_engine_creation_fails_loudly_without_a_gpu():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from glacier.tune_b200 import capi
+    with pytest.raises(capi.GtError) as ei:
+        capi.Engine(0)
+    assert ei.value.code == -4 and "no CPU path" in str(ei.value)
+
+
+def test_null_arguments_are_rejected_before_any_launch():
+    from glacier.tune_b200 import capi
+    lib = capi.load_library()
+    assert lib.gt_engine_create(None, None) == -1
+    assert lib.gt_proj_forward(None, None, None, None, None, 4, 0) == -1
+    assert lib.gt_proj_backward(None, None, None, None, None, None, 4, 0) == -1
+    assert lib.gt_sync(None) == -1
+    assert b"null" in lib.gt_last_error()
+    assert lib.gt_engine_destroy(None) == 0 and lib.gt_weight_free(None) == 0 and lib.gt_adapter_free(None) == 0
+
+
+def test_package_does_not_import_the_oracle():
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r); import glacier.tune_b200; "
+            "assert not any(m == 'oracle' or m.startswith('oracle.') for m in sys.modules), 'oracle imported'") % ROOT
+    subprocess.check_call([sys.executable, "-c", code])
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "glacier")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "gt_oracle" not in src and "from oracle" not in src and "import oracle" not in src, f

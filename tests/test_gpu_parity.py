@@ -1,0 +1,303 @@
+"""GPU parity tests (run with -m gpu on a B200): the CUDA path through the C ABI against the CPU oracle.
+
+Gates (the workload definition's): dequantized weights bit-exact in fp32; Y, dX, dA, dB within relative Frobenius
+error 2e-2 in bf16-MMA mode and 1e-3 in the fp16 / fp32 validation modes.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from glacier.tune_b200 import synth as S
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+TOL = {0: 2e-2, 1: 1e-3, 2: 1e-3}        # bf16, fp16, fp32 math modes
+LORA_TOL = 1e-3                           # dA, dB are fp32 CUDA-core reductions in every mode
+
+
+@pytest.fixture(scope="module")
+def G():
+    from glacier.tune_b200 import capi
+    return capi
+
+
+@pytest.fixture(scope="module")
+def eng(G):
+    e = G.Engine(0, G.MATH_BF16)          # raises without the library or an sm_100 device
+    yield e
+    e.close()
+
+
+def _reference(oracle, c, lora=True, bias=True):
+    """fp64 reference of Y, dX, dA, dB on exactly dequantized weights (the arbiter for the tolerances)."""
+    qt, N, K, T = c["qtype"], c["N"], c["K"], c["T"]
+    y = oracle.matmul_batch(qt, c["w"], c["x"], K, N, T, c["bias"] if bias else None, f64=True)
+    dx = oracle.base_backward_f64(qt, c["w"], c["dy"], K, N, T)
+    da = db = None
+    if lora:
+        X, dY, A, B = (c[k].astype(np.float64) for k in ("x", "dy", "a", "b"))
+        s = c["scaling"]
+        dlow = dY @ B.T
+        y = y + s * (X @ A) @ B
+        dx = dx + s * dlow @ A.T
+        da, db = s * X.T @ dlow, s * (X @ A).T @ dY
+    return y, dx, da, db
+
+
+def _run(G, eng, c, mode, lora=True, bias=True):
+    eng.set_math_mode(mode)
+    w = eng.upload_weight(c["qtype"], c["w"], c["N"], c["K"], c["bias"] if bias else None)
+    ad = None
+    if lora:
+        ad = eng.create_adapter(c["K"], c["N"], c["rank"], c["alpha"])
+        ad.upload(c["a"], c["b"])
+    y = eng.forward(w, ad, c["x"])
+    dx = np.zeros((c["T"], c["K"]), np.float32)
+    eng.backward(w, ad, c["dy"], c["x"], dx)
+    da, db = ad.grads() if lora else (None, None)
+    w.free()
+    if ad:
+        ad.free()
+    return y, dx, da, db
+
+
+@pytest.mark.parametrize("qtype", [S.TYPE_Q4_K, S.TYPE_Q6_K])
+@pytest.mark.parametrize("N,K", [(256, 512), (96, 1024), (64, 896)])
+def test_dequant_bit_exact(G, eng, oracle, qtype, N, K):
+    if K % 256 and qtype == S.TYPE_Q6_K:
+        pytest.skip("flat streams are exercised with Q4_K")
+    c = S.make_projection_case(qtype, N, K, 1, seed=N + K)
+    w = eng.upload_weight(qtype, c["w"], N, K)
+    got = eng.dequant_rows(w, 0, N)
+    want = oracle.dequant_rows(qtype, c["w"], K, 0, N)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    part = eng.dequant_rows(w, 3, 5)
+    assert np.array_equal(part, want[3:8])
+    w.free()
+
+
+def test_dequant_golden_fixture(G, eng):
+    d = np.load(os.path.join(GOLDEN, "dequant_golden.npz"))
+    for qtype, key in ((S.TYPE_Q4_K, "q4k"), (S.TYPE_Q6_K, "q6k")):
+        blocks = d[f"{key}_blocks"]
+        nb = blocks.shape[0]
+        w = eng.upload_weight(qtype, blocks.reshape(-1), nb, 256)     # one super-block per row
+        got = eng.dequant_rows(w, 0, nb)
+        assert np.array_equal(got.view(np.uint32), d[f"{key}_weights"].view(np.uint32))
+        w.free()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_projection_golden_fixture(G, eng, mode):
+    p = np.load(os.path.join(GOLDEN, "projection_golden.npz"))
+    c = dict(qtype=int(p["qtype"]), N=int(p["N"]), K=int(p["K"]), T=int(p["T"]), rank=int(p["rank"]), alpha=32.0,
+             scaling=float(p["scaling"]), w=p["w"], bias=p["bias"], x=p["x"], dy=p["dy"], a=p["a"], b=p["b"])
+    from oracle import oracle as O
+    y, dx, da, db = _run(G, eng, c, mode)
+    assert O.rel_fro(y, p["y"]) < TOL[mode] and O.rel_fro(dx, p["dx"]) < TOL[mode]
+    assert O.rel_fro(da, p["da"]) < LORA_TOL and O.rel_fro(db, p["db"]) < LORA_TOL
+
+
+SHAPES = [
+    # qtype, N, K, T : ragged token counts, N not a multiple of the 128-row tile, multi-chunk T, deep K
+    (S.TYPE_Q4_K, 128, 256, 1), (S.TYPE_Q4_K, 128, 256, 3), (S.TYPE_Q4_K, 200, 768, 17), (S.TYPE_Q4_K, 384, 1024, 512),
+    (S.TYPE_Q4_K, 24, 256, 8), (S.TYPE_Q4_K, 256, 512, 600), (S.TYPE_Q4_K, 512, 3584, 128),
+    (S.TYPE_Q6_K, 128, 256, 16), (S.TYPE_Q6_K, 200, 512, 33), (S.TYPE_Q6_K, 512, 3584, 512),
+]
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("qtype,N,K,T", SHAPES)
+def test_projection_parity(G, eng, oracle, mode, qtype, N, K, T):
+    if mode == 2 and T * N * K > 2e8:
+        pytest.skip("fp32 validation kernels are checked on the smaller shapes")
+    c = S.make_projection_case(qtype, N, K, T, seed=N * 7 + K + T, with_bias=True)
+    y, dx, da, db = _run(G, eng, c, mode)
+    yr, dxr, dar, dbr = _reference(oracle, c)
+    errs = dict(Y=oracle.rel_fro(y, yr), dX=oracle.rel_fro(dx, dxr), dA=oracle.rel_fro(da, dar), dB=oracle.rel_fro(db, dbr))
+    assert errs["Y"] < TOL[mode] and errs["dX"] < TOL[mode], errs
+    assert errs["dA"] < LORA_TOL and errs["dB"] < LORA_TOL, errs
+    # and against the fp32 CPU path itself (LoraAdapter.Forward / Backward as the reference runs them)
+    y_cpu = oracle.proj_forward(qtype, c["w"], c["bias"], c["x"], K, N, T, c["a"], c["b"], 16, c["scaling"])
+    assert oracle.rel_fro(y, y_cpu) < TOL[mode]
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_base_only_and_bias_free(G, eng, oracle, mode):
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 40, seed=77)
+    y, dx, _, _ = _run(G, eng, c, mode, lora=False, bias=False)
+    yr, dxr, _, _ = _reference(oracle, c, lora=False, bias=False)
+    assert oracle.rel_fro(y, yr) < TOL[mode] and oracle.rel_fro(dx, dxr) < TOL[mode]
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_config0_flat_stream_shape(G, eng, oracle, mode):
+    """W 4864x896 as a flat Q4_K super-block stream (896 = 3.5 blocks per row), X 512x896, r=16, alpha=32."""
+    c = S.make_projection_case(S.TYPE_Q4_K, 4864, 896, 512, seed=S.seed_for(0, 0, "q"))
+    y, dx, da, db = _run(G, eng, c, mode, bias=False)
+    yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
+    assert oracle.rel_fro(y, yr) < TOL[mode] and oracle.rel_fro(dx, dxr) < TOL[mode]
+    assert oracle.rel_fro(da, dar) < LORA_TOL and oracle.rel_fro(db, dbr) < LORA_TOL
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_zero_b_skips_delta_and_gives_zero_dA(G, eng, oracle, mode):
+    """Step-0 state (B == 0): forward equals the base projection, dA == 0 exactly, dB != 0
+    (tests/Glacier.Tune.Tests/GradientAndGpuParityTests.cs:37-64)."""
+    c = S.make_projection_case(S.TYPE_Q4_K, 128, 512, 24, seed=5, zero_b=True)
+    y, _, da, db = _run(G, eng, c, mode, bias=False)
+    y_base, _, _, _ = _run(G, eng, c, mode, lora=False, bias=False)
+    assert np.array_equal(y, y_base)
+    assert np.all(da == 0.0) and np.any(db != 0.0)
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_dx_and_grads_accumulate(G, eng, oracle, mode):
+    c = S.make_projection_case(S.TYPE_Q4_K, 128, 256, 20, seed=9)
+    eng.set_math_mode(mode)
+    w = eng.upload_weight(c["qtype"], c["w"], c["N"], c["K"])
+    ad = eng.create_adapter(c["K"], c["N"], 16, 32.0)
+    ad.upload(c["a"], c["b"])
+    dx0 = np.full((20, 256), 3.0, np.float32)
+    dx = dx0.copy()
+    eng.backward(w, ad, c["dy"], c["x"], dx)
+    _, dxr, dar, dbr = _reference(oracle, c, bias=False)
+    assert oracle.rel_fro(dx - dx0, dxr) < TOL[mode]          # += into the caller's buffer
+    eng.backward(w, ad, c["dy"], c["x"], None)                # grads only
+    da, db = ad.grads()
+    assert oracle.rel_fro(da, 2 * dar) < LORA_TOL and oracle.rel_fro(db, 2 * dbr) < LORA_TOL
+    ad.zero_grads()
+    da, db = ad.grads()
+    assert np.all(da == 0) and np.all(db == 0)
+    ad.set_alpha(64.0)                                         # scaling = alpha / r can change after load
+    y4 = eng.forward(w, ad, c["x"])
+    ad.set_alpha(32.0)
+    y2 = eng.forward(w, ad, c["x"])
+    y0 = eng.forward(w, None, c["x"])
+    assert oracle.rel_fro(y4 - y0, 2 * (y2 - y0)) < 5e-2
+    w.free()
+    ad.free()
+
+
+def test_rank8_adapter(G, eng, oracle):
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 64, seed=21, rank=8, alpha=16.0)
+    for mode in (0, 2):
+        y, dx, da, db = _run(G, eng, c, mode, bias=False)
+        yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
+        assert oracle.rel_fro(y, yr) < TOL[mode] and oracle.rel_fro(dx, dxr) < TOL[mode]
+        assert oracle.rel_fro(da, dar) < LORA_TOL and oracle.rel_fro(db, dbr) < LORA_TOL
+
+
+def test_device_pointer_entry_points(G, eng, oracle):
+    """LaunchGemmBatch / LaunchGemmBwd and the projection calls on device-resident tensors."""
+    import torch
+    c = S.make_projection_case(S.TYPE_Q4_K, 384, 512, 96, seed=31, with_bias=True)
+    eng.set_math_mode(0)
+    w = eng.upload_weight(c["qtype"], c["w"], 384, 512, c["bias"])
+    X = torch.from_numpy(c["x"]).cuda()
+    dY = torch.from_numpy(c["dy"]).cuda()
+    Y = torch.empty((96, 384), device="cuda")
+    res = torch.ones((96, 384), device="cuda")
+    dX = torch.zeros((96, 512), device="cuda")
+    eng.launch_gemm_batch(w, Y, X, 96, residual=res)
+    eng.launch_gemm_bwd(w, dX, dY, 96)
+    eng.sync()
+    torch.cuda.synchronize()
+    yr, dxr, _, _ = _reference(oracle, c, lora=False)
+    assert oracle.rel_fro(Y.cpu().numpy(), yr) < 2e-2
+    assert oracle.rel_fro(res.cpu().numpy() - 1.0, yr) < 2e-2
+    assert oracle.rel_fro(dX.cpu().numpy(), dxr) < 2e-2
+    ad = eng.create_adapter(512, 384, 16, 32.0)
+    ad.upload(c["a"], c["b"])
+    Y2 = torch.empty_like(Y)
+    eng.forward(w, ad, X, Y2)
+    eng.sync()
+    yl, _, _, _ = _reference(oracle, c)
+    assert oracle.rel_fro(Y2.cpu().numpy(), yl) < 2e-2
+    w.free()
+    ad.free()
+
+
+def test_full_size_properties_7b_gate(G, eng, oracle):
+    """Qwen2.5-7B gate projection (18944 x 3584, M = 512): size-independent properties instead of a CPU product.
+    Linearity in X, a checksum identity sum_o Y[:, o] = X . colsum(W), and a row-sampled check against the oracle."""
+    N, K = S.QWEN7B_PROJ["gate"]
+    T = 512
+    c = S.make_projection_case(S.TYPE_Q4_K, N, K, T, seed=S.seed_for(1, 0, "gate"), x_bf16=True)
+    eng.set_math_mode(0)
+    w = eng.upload_weight(c["qtype"], c["w"], N, K)
+    y1 = eng.forward(w, None, c["x"])
+    x2 = S.bf16_round(np.roll(c["x"], 1, axis=0) * np.float32(0.5))
+    y2 = eng.forward(w, None, x2)
+    y12 = eng.forward(w, None, c["x"] + x2)
+    assert oracle.rel_fro(y12, y1 + y2) < 1e-2
+    rows = np.arange(0, N, 997)
+    W = np.concatenate([oracle.dequant_rows(c["qtype"], c["w"], K, int(r), 1) for r in rows]).astype(np.float64)
+    assert oracle.rel_fro(y1[:, rows], c["x"].astype(np.float64) @ W.T) < 2e-2
+    Wd = eng.dequant_rows(w, 0, N)                       # device dequant, bit-exact (checked on the sampled rows)
+    assert np.array_equal(Wd[rows], W.astype(np.float32))
+    assert oracle.rel_fro(y1.astype(np.float64).sum(axis=1), c["x"].astype(np.float64) @ Wd.astype(np.float64).sum(axis=0)) < 2e-2
+    # backward on sampled input columns: dX[:, k] = dY . W[:, k]
+    dx = np.zeros((T, K), np.float32)
+    eng.backward(w, None, c["dy"], None, dx)
+    cols = np.arange(0, K, 113)
+    assert oracle.rel_fro(dx[:, cols], c["dy"].astype(np.float64) @ Wd[:, cols].astype(np.float64)) < 2e-2
+    # and the adjoint identity <dY, X W^T> == <dY W, X>, scaled by the operand norms
+    lhs = float(np.sum(c["dy"].astype(np.float64) * y1.astype(np.float64)))
+    rhs = float(np.sum(dx.astype(np.float64) * c["x"].astype(np.float64)))
+    assert abs(lhs - rhs) < 1e-4 * np.linalg.norm(c["dy"]) * np.linalg.norm(y1)
+    w.free()
+
+
+def test_error_paths(G, eng):
+    with pytest.raises(G.GtError):
+        eng.upload_weight(S.TYPE_Q4_K, np.zeros(100, np.uint8), 4, 256)          # byte size mismatch
+    with pytest.raises(G.GtError):
+        eng.upload_weight(13, np.zeros(176, np.uint8), 1, 256)                    # unsupported type
+    c = S.make_projection_case(S.TYPE_Q4_K, 128, 256, 4, seed=1)
+    w = eng.upload_weight(c["qtype"], c["w"], 128, 256)
+    ad = eng.create_adapter(512, 128, 16, 32.0)                                   # wrong in_features
+    with pytest.raises(G.GtError):
+        eng.forward(w, ad, c["x"])
+    with pytest.raises(G.GtError):
+        eng.create_adapter(256, 128, 65, 32.0)
+    w.free()
+    ad.free()
+
+
+def test_grads_scale_clip(G, eng, oracle):
+    import torch
+    g = torch.arange(1, 1001, dtype=torch.float32, device="cuda")
+    ref = g.cpu().numpy() * np.float32(0.5)
+    norm = eng.grads_scale_clip(g, 0.5, 1.0)
+    want_norm = oracle.clip_gradients(ref, 1.0)
+    assert abs(norm - want_norm) / want_norm < 1e-6
+    assert np.allclose(g.cpu().numpy(), ref, rtol=1e-5)
+    g2 = torch.ones(100, device="cuda")
+    g2[7] = float("nan")
+    assert eng.grads_scale_clip(g2, 1.0, 1.0) == 0.0 and float(g2.abs().sum()) == 0.0
+
+
+def test_cpp_host_mirror(G, eng, oracle, tmp_path):
+    """The C++ mirror of GpuLoraEngine / LoraAdapter (host/glacier_tune_host.hpp) drives the same library."""
+    from glacier.tune_b200.host import build as host_build
+    exe = host_build.build()
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 32, seed=41)
+    case, out = tmp_path / "case.bin", tmp_path / "out.bin"
+    with open(case, "wb") as f:
+        f.write(np.array([c["qtype"], 256, 512, 32, 16], np.int32).tobytes())
+        f.write(np.array([32.0], np.float32).tobytes())
+        f.write(np.array([c["w"].nbytes], np.int64).tobytes())
+        for k in ("w", "x", "dy", "a", "b"):
+            f.write(np.ascontiguousarray(c[k]).tobytes())
+    subprocess.check_call([exe, str(case), str(out)])
+    raw = np.fromfile(out, np.float32)
+    sizes = [32 * 256, 32 * 512, 512 * 16, 16 * 256]
+    y, dx, da, db = np.split(raw, np.cumsum(sizes)[:-1])
+    yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
+    assert oracle.rel_fro(y.reshape(32, 256), yr) < 2e-2 and oracle.rel_fro(dx.reshape(32, 512), dxr) < 2e-2
+    assert oracle.rel_fro(da.reshape(512, 16), dar) < LORA_TOL and oracle.rel_fro(db.reshape(16, 256), dbr) < LORA_TOL
