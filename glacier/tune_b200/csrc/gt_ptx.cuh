@@ -1,4 +1,4 @@
-// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, no cluster multicast),
+// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA tile loads (every load has a single destination CTA),
 // tcgen05 (TMEM alloc, MMA, commit, ld) and the proxy fences between them.
 #pragma once
 #include <cuda_runtime.h>
@@ -38,19 +38,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Gives up after `limit_ns` of wall time or as soon as another role of the CTA has
-// raised `*abort_flag`; on a timeout it raises the flag itself and records `code` in status[0].
-// The caller must leave its loop when this returns false.
+// Bounded wait.  Gives up after about `limit_cycles` SM clocks (default ~2 s) or as soon as another role of the
+// CTA has raised `*abort_flag`; on a timeout it raises the flag itself and records `code` in status[0].
+// The caller must leave its loop when this returns false.  The clock is the SM-local cycle counter: reading the
+// global nanosecond timer on the wait path costs on the order of a microsecond per blocked wait.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                                  int code, uint64_t limit_ns = 2000000000ull) {
+                                                  int code, long long limit_cycles = 4000000000ll) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    long long t0 = 0;
     uint32_t it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 63u) == 0u) {
+        if ((++it & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_cycles) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;
@@ -119,6 +122,96 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------- CTA pairs (cluster of 2, tcgen05 cta_group::2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// All threads of both CTAs.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `smem_addr` (a shared::cta address of this CTA) as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_cluster(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait with cluster-scope acquire (the barrier receives arrivals from the peer CTA).
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                                          int code, long long limit_cycles = 4000000000ll) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    long long t0 = 0;
+    uint32_t it = 0;
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((++it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_cycles) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+// TMA tile load issued by either CTA of a pair; the transaction bytes are credited to the mbarrier at the same
+// offset in the pair's leader (even-ranked) CTA: the caller passes the leader-mapped barrier address.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void *tmap, int32_t c0, int32_t c1,
+                                                 uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst_smem), "l"(tmap), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// M = 256 MMA over both CTAs of the pair; issued by one thread of the leader CTA.
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier at this offset in BOTH CTAs of the pair once all prior MMAs of this thread are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(mask)
+                 : "memory");
+}
 
 // ---------------------------------------------------------------- UMMA descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 encoding:

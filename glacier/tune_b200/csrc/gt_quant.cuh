@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace gt {
 
 constexpr int kTypeF32 = 0;
@@ -136,13 +138,44 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// Decode group `grp` of half block `half` of one weight row and write its 32 values, rounded once to T16,
-// as four 16-byte chunks of a 128-byte-swizzled row: chunk (chunk0 + i) lands at
-// dst_row + (((chunk0 + i) ^ swz) << 4), swz = (row index within the 1024-byte atom) & 7.
+__device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_splat(float v) {
+    __nv_bfloat162 t = __float2bfloat162_rn(v);
+    return *reinterpret_cast<uint32_t *>(&t);
+}
+
+// Decode group `grp` of half block `half` of one weight row and write its 32 values as four 16-byte chunks of
+// a 128-byte-swizzled operand row: chunk (chunk0 + i) lands at dst_row + (((chunk0 + i) ^ swz) << 4),
+// swz = (row index within the 1024-byte atom) & 7.
+//
+// The raw q0 / q1 regions were written by TMA with 64-byte / 32-byte swizzle (conflict-free reads when the
+// lanes of a warp walk consecutive rows): 16-byte chunk c of a q0 row sits at (c ^ rsw0) << 4, of a q1 row at
+// (c ^ rsw1) << 4, with rsw0 = (row >> 1) & 3 and rsw1 = (row >> 2) & 1.
+//
+// T16 = __half : every weight is evaluated exactly in fp32 (the reference formula) and rounded once.
+// T16 = bf16   : packed bf16x2 arithmetic.  A 4-bit quant q is placed in a bf16 mantissa as v = 1 + q/16
+//                (exact), then w = (16a) * v - (16a + b) in one fused multiply-add; a 6-bit quant as
+//                v = 1 + q/64, then w = (64a) * (v - 1.5) with an exact subtraction.  The per-sub-block
+//                constants are rounded to bf16, which adds an error of the size of the bf16 rounding of w itself.
 template <int QT, typename T16>
 __device__ __forceinline__ void dequant32_to_swizzled_row(const uint8_t *hdr_row, const uint8_t *q0_row,
-                                                          const uint8_t *q1_row, int half, int grp, uint32_t dst_row,
-                                                          int swz, int chunk0) {
+                                                          const uint8_t *q1_row, int rsw0, int rsw1, int half, int grp,
+                                                          uint32_t dst_row, int swz, int chunk0) {
+    constexpr bool kFast = std::is_same<T16, __nv_bfloat16>::value;
     if constexpr (QT == kTypeQ4K) {
         const uint4 h = *reinterpret_cast<const uint4 *>(hdr_row);
         const float d = half_bits_to_f32(h.x & 0xFFFFu);
@@ -150,25 +183,44 @@ __device__ __forceinline__ void dequant32_to_swizzled_row(const uint8_t *hdr_row
         int sc, m;
         q4k_scale_min_w(4 * half + grp, h.y, h.z, h.w, sc, m);
         const float a = d * (float)sc;
-        const float nb = -(dmin * (float)m);
-        const uint4 *qp = reinterpret_cast<const uint4 *>(q0_row + (grp >> 1) * 32);
-        const uint4 qa = qp[0], qb = qp[1];
+        const float b = dmin * (float)m;
+        const int c0 = (grp >> 1) * 2;
+        const uint4 qa = *reinterpret_cast<const uint4 *>(q0_row + ((c0 ^ rsw0) << 4));
+        const uint4 qb = *reinterpret_cast<const uint4 *>(q0_row + (((c0 + 1) ^ rsw0) << 4));
         const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-        const int sh = (grp & 1) * 4;
+        if constexpr (kFast) {
+            const uint32_t a16 = bf16x2_splat(16.f * a);
+            const uint32_t c16 = bf16x2_splat(-(16.f * a + b));
+            const int rot = (grp & 1) ? 31 : 3;     // nibble -> bits 3..6 of its byte: rotl 3 (low) / rotr 1 (high)
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint32_t o[4];
+            for (int i = 0; i < 4; i++) {
+                uint32_t o[4];
 #pragma unroll
-            for (int k = 0; k < 2; k++) {
-                const uint32_t v = (w[2 * i + k] >> sh) & 0x0F0F0F0Fu;
-                const float f0 = fmaf(a, byte_to_magic(v, 0) - 8388608.f, nb);
-                const float f1 = fmaf(a, byte_to_magic(v, 1) - 8388608.f, nb);
-                const float f2 = fmaf(a, byte_to_magic(v, 2) - 8388608.f, nb);
-                const float f3 = fmaf(a, byte_to_magic(v, 3) - 8388608.f, nb);
-                o[2 * k] = pack2<T16>(f0, f1);
-                o[2 * k + 1] = pack2<T16>(f2, f3);
+                for (int k = 0; k < 2; k++) {
+                    const uint32_t t = (__funnelshift_l(w[2 * i + k], w[2 * i + k], rot) & 0x78787878u) | 0x80808080u;
+                    o[2 * k] = bf16x2_fma(__byte_perm(t, 0x3F3F3F3Fu, 0x4140u), a16, c16);
+                    o[2 * k + 1] = bf16x2_fma(__byte_perm(t, 0x3F3F3F3Fu, 0x4342u), a16, c16);
+                }
+                st_shared_v4(dst_row + (uint32_t)(((chunk0 + i) ^ swz) << 4), o[0], o[1], o[2], o[3]);
             }
-            st_shared_v4(dst_row + (uint32_t)(((chunk0 + i) ^ swz) << 4), o[0], o[1], o[2], o[3]);
+        } else {
+            const float nb = -b;
+            const int sh = (grp & 1) * 4;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const uint32_t v = (w[2 * i + k] >> sh) & 0x0F0F0F0Fu;
+                    const float f0 = fmaf(a, byte_to_magic(v, 0) - 8388608.f, nb);
+                    const float f1 = fmaf(a, byte_to_magic(v, 1) - 8388608.f, nb);
+                    const float f2 = fmaf(a, byte_to_magic(v, 2) - 8388608.f, nb);
+                    const float f3 = fmaf(a, byte_to_magic(v, 3) - 8388608.f, nb);
+                    o[2 * k] = pack2<T16>(f0, f1);
+                    o[2 * k + 1] = pack2<T16>(f2, f3);
+                }
+                st_shared_v4(dst_row + (uint32_t)(((chunk0 + i) ^ swz) << 4), o[0], o[1], o[2], o[3]);
+            }
         }
     } else {
         const uint32_t scw = *reinterpret_cast<const uint32_t *>(hdr_row + 8 * half + (grp & 2) * 2);
@@ -177,27 +229,50 @@ __device__ __forceinline__ void dequant32_to_swizzled_row(const uint8_t *hdr_row
         const int s1 = (int)(int8_t)((scw >> (16 * (grp & 1) + 8)) & 0xFF);
         const float d = half_bits_to_f32(*reinterpret_cast<const uint16_t *>(hdr_row + 16));
         const float a0 = d * (float)s0, a1 = d * (float)s1;
-        const uint4 *lp = reinterpret_cast<const uint4 *>(q0_row + (grp & 1) * 32);
-        const uint4 *hp = reinterpret_cast<const uint4 *>(q1_row);
-        const uint4 la = lp[0], lb = lp[1], ha = hp[0], hb = hp[1];
+        const int c0 = (grp & 1) * 2;
+        const uint4 la = *reinterpret_cast<const uint4 *>(q0_row + ((c0 ^ rsw0) << 4));
+        const uint4 lb = *reinterpret_cast<const uint4 *>(q0_row + (((c0 + 1) ^ rsw0) << 4));
+        const uint4 ha = *reinterpret_cast<const uint4 *>(q1_row + ((0 ^ rsw1) << 4));
+        const uint4 hb = *reinterpret_cast<const uint4 *>(q1_row + ((1 ^ rsw1) << 4));
         const uint32_t lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
         const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
-        const int lsh = (grp >> 1) * 4, hsh = grp * 2;
+        if constexpr (kFast) {
+            const uint32_t m0 = bf16x2_splat(64.f * a0), m1 = bf16x2_splat(64.f * a1);
+            const uint32_t k15 = 0x3FC03FC0u;                        // bf16x2 (1.5, 1.5)
+            const int lrot = (grp >> 1) ? 29 : 1;                    // low nibble  -> bits 1..4: rotl 1 / rotr 3
+            const int hrot = (5 - 2 * grp) & 31;                     // 2 high bits -> bits 5..6
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float a = i < 2 ? a0 : a1;
-            uint32_t o[4];
+            for (int i = 0; i < 4; i++) {
+                const uint32_t mm = i < 2 ? m0 : m1;
+                uint32_t o[4];
 #pragma unroll
-            for (int k = 0; k < 2; k++) {
-                const uint32_t v = ((lw[2 * i + k] >> lsh) & 0x0F0F0F0Fu) | (((hw[2 * i + k] >> hsh) & 0x03030303u) << 4);
-                const float f0 = a * (byte_to_magic(v, 0) - 8388640.f);
-                const float f1 = a * (byte_to_magic(v, 1) - 8388640.f);
-                const float f2 = a * (byte_to_magic(v, 2) - 8388640.f);
-                const float f3 = a * (byte_to_magic(v, 3) - 8388640.f);
-                o[2 * k] = pack2<T16>(f0, f1);
-                o[2 * k + 1] = pack2<T16>(f2, f3);
+                for (int k = 0; k < 2; k++) {
+                    const uint32_t l = lw[2 * i + k], hh = hw[2 * i + k];
+                    const uint32_t t = (__funnelshift_l(l, l, lrot) & 0x1E1E1E1Eu) | (__funnelshift_l(hh, hh, hrot) & 0x60606060u) |
+                                       0x80808080u;
+                    o[2 * k] = bf16x2_mul(bf16x2_sub(__byte_perm(t, 0x3F3F3F3Fu, 0x4140u), k15), mm);
+                    o[2 * k + 1] = bf16x2_mul(bf16x2_sub(__byte_perm(t, 0x3F3F3F3Fu, 0x4342u), k15), mm);
+                }
+                st_shared_v4(dst_row + (uint32_t)(((chunk0 + i) ^ swz) << 4), o[0], o[1], o[2], o[3]);
             }
-            st_shared_v4(dst_row + (uint32_t)(((chunk0 + i) ^ swz) << 4), o[0], o[1], o[2], o[3]);
+        } else {
+            const int lsh = (grp >> 1) * 4, hsh = grp * 2;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float a = i < 2 ? a0 : a1;
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const uint32_t v = ((lw[2 * i + k] >> lsh) & 0x0F0F0F0Fu) | (((hw[2 * i + k] >> hsh) & 0x03030303u) << 4);
+                    const float f0 = a * (byte_to_magic(v, 0) - 8388640.f);
+                    const float f1 = a * (byte_to_magic(v, 1) - 8388640.f);
+                    const float f2 = a * (byte_to_magic(v, 2) - 8388640.f);
+                    const float f3 = a * (byte_to_magic(v, 3) - 8388640.f);
+                    o[2 * k] = pack2<T16>(f0, f1);
+                    o[2 * k + 1] = pack2<T16>(f2, f3);
+                }
+                st_shared_v4(dst_row + (uint32_t)(((chunk0 + i) ^ swz) << 4), o[0], o[1], o[2], o[3]);
+            }
         }
     }
 }

@@ -12,11 +12,11 @@
 // (up to 512), so each weight is dequantized once per CTA and reused by every token:
 //   D[128 x tokens] (TMEM, fp32)  +=  Wtile[128 x 64] (SMEM, dequantized 16-bit)  x  act[tokens x 64]^T (SMEM via TMA)
 //
-// Warp roles (320 threads):
+// Warp roles (576 threads):
 //   warp 0      TMA producer: packed half-super-blocks of W (raw bytes) and 16-bit activation tiles
 //   warp 1      tcgen05.mma issuer (one thread); owns the TMEM allocation
-//   warps 2-9   dequantize raw blocks -> 128-byte-swizzled operand tiles; afterwards the epilogue
-//               (tcgen05.ld -> bias -> global store / atomic add)
+//   warps 2-17  two groups of 8 warps that dequantize alternate operand stages (raw blocks -> 128-byte-swizzled
+//               tiles); afterwards all 16 run the epilogue (tcgen05.ld -> bias -> global store / atomic add)
 //
 // The dequantized tile image is the same for both directions: row = weight row n, 128 bytes = 64 consecutive
 // k, chunks XOR-swizzled by (row & 7).  Forward reads it as a K-major A operand (M = n, K = k); backward
@@ -38,25 +38,25 @@ namespace gt {
 
 namespace {
 
-constexpr int kTileW = 128;        // UMMA M
+constexpr int kTileW = 128;        // weight rows (forward) / columns (backward) per CTA = UMMA M per CTA
 constexpr int kChunk = 64;         // contraction elements per operand stage (one 128-byte row)
 constexpr int kMaxTok = 512;       // tokens per CTA = TMEM columns
 constexpr int kAStageBytes = kTileW * kChunk * 2;   // 16 KiB
-constexpr int kXStageBytes = kMaxTok * kChunk * 2;  // 64 KiB
+constexpr int kXBytes = 131072;    // activation ring: 2 x 64 KiB (single CTA) or 4 x 32 KiB (CTA pair)
 constexpr int kRawStageBytes = 16384;
-constexpr int kNumA = 3, kNumX = 2, kNumRaw = 2;
-constexpr int kDequantWarps = 8;
+constexpr int kNumA = 4, kNumRaw = 2;
+constexpr int kDequantWarps = 16;   // two groups of 8
 constexpr int kThreads = 32 * (2 + kDequantWarps);
 
 constexpr int kOffX = 0;
-constexpr int kOffA = kOffX + kNumX * kXStageBytes;
+constexpr int kOffA = kOffX + kXBytes;
 constexpr int kOffRaw = kOffA + kNumA * kAStageBytes;
 constexpr int kOffBar = kOffRaw + kNumRaw * kRawStageBytes;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for 1024-byte alignment
 
 // barrier slots (8 bytes each) inside the kOffBar region
-constexpr int kBarRawFull = 0, kBarRawEmpty = 2, kBarXFull = 4, kBarXEmpty = 6, kBarAFull = 8, kBarAEmpty = 11,
-              kBarAcc = 14, kNumBars = 15;
+constexpr int kBarRawFull = 0, kBarRawEmpty = 2, kBarXFull = 4, kBarXEmpty = 8, kBarAFull = 12, kBarAEmpty = 16,
+              kBarAcc = 20, kNumBars = 21;
 constexpr int kOffTmemSlot = kNumBars * 8;       // u32
 constexpr int kOffAbort = kOffTmemSlot + 4;      // int
 
@@ -88,12 +88,22 @@ struct Ring {
     }
 };
 
-template <int QT, typename T16, bool BWD>
+// PAIR = false: one CTA per tile, tcgen05 cta_group::1, M = 128.
+// PAIR = true : a cluster of two CTAs (the two SMs of a TPC) works on two adjacent tiles with cta_group::2 MMAs of
+//               M = 256.  Each CTA dequantizes its own 128 weight rows and loads only HALF of the token rows of
+//               every activation tile (the MMA reads the other half from the peer's shared memory), which halves
+//               the activation bytes each SM pulls from L2 per FLOP.  The even-ranked CTA (leader) issues the MMAs;
+//               its "full" barriers collect the arrivals and TMA bytes of both CTAs, and its commits release the
+//               stages in both.
+template <int QT, typename T16, bool BWD, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant__ Params p) {
     using QS = QuantStage<QT>;
     constexpr int H = QS::kHdrBytes, Q1 = QS::kQ1Bytes;
     constexpr int kRows = BWD ? 64 : 128;      // weight rows per raw stage
     constexpr int kSub = BWD ? 1 : 2;          // operand stages produced per raw stage
+    constexpr int kNumX = PAIR ? 4 : 2;
+    constexpr int kXStageBytes = kXBytes / kNumX;
+    constexpr int kMmaSlotBytes = PAIR ? 128 * 128 : 256 * 128;   // smem bytes of one MMA's activation rows in a stage
     constexpr uint32_t kFmt = std::is_same<T16, __half>::value ? 0u : 1u;   // UMMA operand format: 0 f16, 1 bf16
 
     extern __shared__ uint8_t smem_dyn[];
@@ -106,10 +116,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;        // 0 = leader
+    const bool leader = crank == 0;
     const int tok0 = blockIdx.z * kMaxTok;
     const int tok_left = p.T - tok0;
-    const int tb = min(kMaxTok, (tok_left + 15) & ~15);          // token columns of this CTA (multiple of 16)
-    const int n_box = (tb + p.t_box - 1) / p.t_box;
+    // token columns of this CTA's accumulator: multiple of 16 (single) / 32 (pair, 16 per CTA half)
+    const int tb = PAIR ? min(kMaxTok, (tok_left + 31) & ~31) : min(kMaxTok, (tok_left + 15) & ~15);
+    const int n_box = (tb + p.t_box - 1) / p.t_box;             // single-CTA mode: TMA boxes per stage
     const int n_mma = (tb + 255) >> 8;
     const int u0 = (int)((int64_t)p.units * split / p.splits);
     const int u1 = (int)((int64_t)p.units * (split + 1) / p.splits);
@@ -117,16 +130,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     const bool do_lora = p.rank > 0 && split == 0 && (p.lora_flag == nullptr || *p.lora_flag != 0);
 
     if (threadIdx.x == 0) {
-        mbar_init(bar(kBarRawFull + 0), 1);
-        mbar_init(bar(kBarRawFull + 1), 1);
-        mbar_init(bar(kBarRawEmpty + 0), kDequantWarps * 32);
-        mbar_init(bar(kBarRawEmpty + 1), kDequantWarps * 32);
-        mbar_init(bar(kBarXFull + 0), 1);
-        mbar_init(bar(kBarXFull + 1), 1);
-        mbar_init(bar(kBarXEmpty + 0), 1);
-        mbar_init(bar(kBarXEmpty + 1), 1);
+        for (int i = 0; i < kNumRaw; i++) {
+            mbar_init(bar(kBarRawFull + i), 1);
+            mbar_init(bar(kBarRawEmpty + i), BWD ? 8 : 16);      // one arrival per warp that read the stage
+        }
+        for (int i = 0; i < kNumX; i++) {
+            mbar_init(bar(kBarXFull + i), 1);                    // the (leader's) producer arrival + TMA bytes
+            mbar_init(bar(kBarXEmpty + i), 1);
+        }
         for (int i = 0; i < kNumA; i++) {
-            mbar_init(bar(kBarAFull + i), kDequantWarps * 32);
+            mbar_init(bar(kBarAFull + i), PAIR ? 16 : 8);        // one arrival per producing warp (of both CTAs)
             mbar_init(bar(kBarAEmpty + i), 1);
         }
         mbar_init(bar(kBarAcc), 1);
@@ -137,13 +150,34 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         tma_prefetch_desc(&p.tm_q0);
     }
     if (warp == 1) {
-        tmem_alloc(sbase + kOffBar + kOffTmemSlot, (uint32_t)p.tmem_cols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(sbase + kOffBar + kOffTmemSlot, (uint32_t)p.tmem_cols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(sbase + kOffBar + kOffTmemSlot, (uint32_t)p.tmem_cols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if (PAIR) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+
+    // activation tile of one stage: coordinate c0 along the contraction, this CTA's token rows
+    auto load_act_stage = [&](const CUtensorMap *tm, int c0, uint32_t xdst, uint32_t xbar_local) {
+        if (PAIR) {
+            // leader arms the barrier for the bytes of both CTAs; each CTA loads its half of every MMA's tokens
+            if (leader) mbar_arrive_expect_tx(xbar_local, (uint32_t)(2 * n_mma * 128 * 128));
+            const uint32_t lbar = mapa_cluster(xbar_local, 0);
+            for (int i = 0; i < n_mma; i++) {
+                const int ntok = min(256, tb - 256 * i);
+                tma_load_2d_pair(xdst + i * kMmaSlotBytes, tm, c0, tok0 + 256 * i + (int)crank * (ntok >> 1), lbar);
+            }
+        } else {
+            mbar_arrive_expect_tx(xbar_local, (uint32_t)(n_box * p.t_box * 128));
+            for (int b = 0; b < n_box; b++) tma_load_2d(xdst + b * p.t_box * 128, tm, c0, tok0 + b * p.t_box, xbar_local);
+        }
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -173,30 +207,26 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 for (int s = 0; s < kSub && ok; s++) {
                     ok = mbar_wait_bounded(bar(kBarXEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
                     if (!ok) break;
-                    const uint32_t xdst = sbase + kOffX + xs.idx * kXStageBytes;
-                    const uint32_t xbar = bar(kBarXFull + xs.idx);
-                    mbar_arrive_expect_tx(xbar, (uint32_t)(n_box * p.t_box * 128));
-                    const int c0 = BWD ? u * 64 : (u * 2 + s) * 64;
-                    for (int b = 0; b < n_box; b++) tma_load_2d(xdst + b * p.t_box * 128, &p.tm_act, c0, tok0 + b * p.t_box, xbar);
+                    load_act_stage(&p.tm_act, BWD ? u * 64 : (u * 2 + s) * 64, sbase + kOffX + xs.idx * kXStageBytes,
+                                   bar(kBarXFull + xs.idx));
                     xs.advance(kNumX);
                 }
             }
             if (ok && do_lora) {
                 ok = mbar_wait_bounded(bar(kBarXEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
-                if (ok) {
-                    const uint32_t xdst = sbase + kOffX + xs.idx * kXStageBytes;
-                    const uint32_t xbar = bar(kBarXFull + xs.idx);
-                    mbar_arrive_expect_tx(xbar, (uint32_t)(n_box * p.t_box * 128));
-                    for (int b = 0; b < n_box; b++) tma_load_2d(xdst + b * p.t_box * 128, &p.tm_lora, 0, tok0 + b * p.t_box, xbar);
-                }
+                if (ok) load_act_stage(&p.tm_lora, 0, sbase + kOffX + xs.idx * kXStageBytes, bar(kBarXFull + xs.idx));
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
+        if (lane == 0 && leader) {
             Ring as, xs;
             bool ok = true, first = true;
             const uint32_t a_mn = BWD ? 1u : 0u;
+            auto wait_full = [&](int slot, uint32_t phase, int code) -> bool {
+                return PAIR ? mbar_wait_bounded_cluster(bar(slot), phase, abort_flag, p.status, code)
+                            : mbar_wait_bounded(bar(slot), phase, abort_flag, p.status, code);
+            };
             auto issue_stage = [&](int ksteps) {
                 const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
                 const uint32_t x_addr = sbase + kOffX + xs.idx * kXStageBytes;
@@ -205,83 +235,109 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                                                : umma_desc_sw128(a_addr + ks * 32, 16, 1024);
                     for (int i = 0; i < n_mma; i++) {
                         const int ntok = min(256, tb - 256 * i);
-                        const uint64_t bdesc = umma_desc_sw128(x_addr + i * 256 * 128 + ks * 32, 16, 1024);
-                        umma_f16_ss(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok),
-                                    (first && ks == 0) ? 0u : 1u);
+                        const uint64_t bdesc = umma_desc_sw128(x_addr + i * kMmaSlotBytes + ks * 32, 16, 1024);
+                        const uint32_t acc = (first && ks == 0) ? 0u : 1u;
+                        if (PAIR) umma_f16_ss_pair(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 256), acc);
+                        else umma_f16_ss(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 128), acc);
                     }
                 }
                 first = false;
-                umma_commit(bar(kBarAEmpty + as.idx));
-                umma_commit(bar(kBarXEmpty + xs.idx));
+                if (PAIR) {
+                    umma_commit_pair(bar(kBarAEmpty + as.idx));
+                    umma_commit_pair(bar(kBarXEmpty + xs.idx));
+                } else {
+                    umma_commit(bar(kBarAEmpty + as.idx));
+                    umma_commit(bar(kBarXEmpty + xs.idx));
+                }
                 as.advance(kNumA);
                 xs.advance(kNumX);
             };
             for (int u = u0; u < u1 && ok; u++) {
                 for (int s = 0; s < kSub && ok; s++) {
-                    ok = mbar_wait_bounded(bar(kBarAFull + as.idx), as.phase, abort_flag, p.status, kCodeMma + 1) &&
-                         mbar_wait_bounded(bar(kBarXFull + xs.idx), xs.phase, abort_flag, p.status, kCodeMma + 2);
+                    ok = wait_full(kBarAFull + as.idx, as.phase, kCodeMma + 1) && wait_full(kBarXFull + xs.idx, xs.phase, kCodeMma + 2);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_stage(4);
                 }
             }
             if (ok && do_lora) {
-                ok = mbar_wait_bounded(bar(kBarAFull + as.idx), as.phase, abort_flag, p.status, kCodeMma + 3) &&
-                     mbar_wait_bounded(bar(kBarXFull + xs.idx), xs.phase, abort_flag, p.status, kCodeMma + 4);
+                ok = wait_full(kBarAFull + as.idx, as.phase, kCodeMma + 3) && wait_full(kBarXFull + xs.idx, xs.phase, kCodeMma + 4);
                 if (ok) {
                     tc_fence_after_sync();
                     issue_stage(rank_pad >> 4);
                 }
             }
-            if (ok) umma_commit(bar(kBarAcc));
+            if (ok) {
+                if (PAIR) umma_commit_pair(bar(kBarAcc)); else umma_commit(bar(kBarAcc));
+            }
         }
     } else {
         // ------------------------------------------------------------------ dequant warps, then epilogue
-        const int dt = threadIdx.x - 64;
-        Ring raw, as;
+        const int dt = (threadIdx.x - 64) & 255;        // thread index inside its 8-warp group
+        const int g = (warp - 2) >> 3;                  // group 0 / 1: alternate operand stages
+        const int nu = u1 - u0;
         bool ok = true;
-        for (int u = u0; u < u1 && ok; u++) {
-            ok = mbar_wait_bounded(bar(kBarRawFull + raw.idx), raw.phase, abort_flag, p.status, kCodeDequant + 1);
-            if (!ok) break;
-            const uint8_t *rs = smem + kOffRaw + raw.idx * kRawStageBytes;
-            for (int s = 0; s < kSub && ok; s++) {
-                ok = mbar_wait_bounded(bar(kBarAEmpty + as.idx), as.phase ^ 1u, abort_flag, p.status, kCodeDequant + 2);
-                if (!ok) break;
-                const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
-                int row, grp, half, chunk0;
-                uint32_t dst_row;
-                if (BWD) {
-                    row = dt & 63; grp = dt >> 6; half = tile & 1;
-                    dst_row = a_addr + (uint32_t)((grp >> 1) * 8192 + row * 128);
-                    chunk0 = 4 * (grp & 1);
-                } else {
-                    row = dt & 127; grp = 2 * s + (dt >> 7); half = u & 1;
-                    dst_row = a_addr + (uint32_t)(row * 128);
-                    chunk0 = 4 * (dt >> 7);
-                }
-                dequant32_to_swizzled_row<QT, T16>(rs + row * H, rs + kRows * H + row * 64,
-                                                   rs + kRows * (H + 64) + row * (Q1 > 0 ? Q1 : 1), half, grp, dst_row,
-                                                   row & 7, chunk0);
-                fence_proxy_async_smem();
-                mbar_arrive(bar(kBarAFull + as.idx));
-                as.advance(kNumA);
+        // "operand stage ready": on the barrier of the CTA that issues the MMAs
+        auto signal_a_full = [&](int ai) {
+            if (lane == 0) {
+                if (PAIR && !leader) mbar_arrive_cluster(mapa_cluster(bar(kBarAFull + ai), 0));
+                else mbar_arrive(bar(kBarAFull + ai));
             }
-            if (ok) mbar_arrive(bar(kBarRawEmpty + raw.idx));
-            raw.advance(kNumRaw);
+        };
+        // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i & 1
+        auto produce = [&](int n, const uint8_t *rs, int row, int grp, int half, uint32_t dst_off, int chunk0) -> bool {
+            const int ai = n & (kNumA - 1);
+            if (!mbar_wait_bounded(bar(kBarAEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 2))
+                return false;
+            const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
+            dequant32_to_swizzled_row<QT, T16>(rs + row * H, rs + kRows * H + row * 64,
+                                               rs + kRows * (H + 64) + row * (Q1 > 0 ? Q1 : 1), (row >> 1) & 3, (row >> 2) & 1,
+                                               half, grp, a_addr + dst_off, row & 7, chunk0);
+            fence_proxy_async_smem();
+            __syncwarp();
+            signal_a_full(ai);
+            return true;
+        };
+        if (!BWD) {
+            // raw stage = 128 rows x half block; group g dequantizes its 64-column half (sub-stage g)
+            const int row = dt & 127, hn = dt >> 7;
+            for (int ui = 0; ui < nu && ok; ui++) {
+                const int ri = ui & 1;
+                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui >> 1) & 1u, abort_flag, p.status, kCodeDequant + 1);
+                if (!ok) break;
+                const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
+                ok = produce(2 * ui + g, rs, row, 2 * g + hn, (u0 + ui) & 1, (uint32_t)(row * 128), 4 * hn);
+                if (!ok) break;
+                if (lane == 0) mbar_arrive(bar(kBarRawEmpty + ri));
+            }
+        } else {
+            // raw stage = 64 rows x half block = one operand stage; the groups take alternate stages
+            const int row = dt & 63, grp = dt >> 6;
+            for (int ui = g; ui < nu && ok; ui += 2) {
+                const int ri = ui & 1;
+                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui >> 1) & 1u, abort_flag, p.status, kCodeDequant + 1);
+                if (!ok) break;
+                const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
+                ok = produce(ui, rs, row, grp, tile & 1, (uint32_t)((grp >> 1) * 8192 + row * 128), 4 * (grp & 1));
+                if (!ok) break;
+                if (lane == 0) mbar_arrive(bar(kBarRawEmpty + ri));
+            }
         }
-        if (ok && do_lora) {
-            ok = mbar_wait_bounded(bar(kBarAEmpty + as.idx), as.phase ^ 1u, abort_flag, p.status, kCodeDequant + 3);
+        if (ok && do_lora && g == 0) {
+            const int n = (BWD ? 1 : 2) * nu;
+            const int ai = n & (kNumA - 1);
+            ok = mbar_wait_bounded(bar(kBarAEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
             if (ok) {
-                const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
+                const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
                 if (!BWD) {
                     // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
-                    const int row = dt & 127, n = tile * kTileW + row;
+                    const int row = dt & 127, nn = tile * kTileW + row;
                     for (int j = dt >> 7; j * 8 < rank_pad; j += 2) {
                         float v[8];
 #pragma unroll
                         for (int i = 0; i < 8; i++) {
                             const int r = 8 * j + i;
-                            v[i] = (r < p.rank && n < p.N) ? p.lora_w[(int64_t)r * p.N + n] : 0.f;
+                            v[i] = (r < p.rank && nn < p.N) ? p.lora_w[(int64_t)r * p.N + nn] : 0.f;
                         }
                         st_shared_v4(a_addr + (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4)), pack2<T16>(v[0], v[1]),
                                      pack2<T16>(v[2], v[3]), pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
@@ -298,20 +354,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     }
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(bar(kBarAFull + as.idx));
+                __syncwarp();
+                signal_a_full(ai);
             }
         }
         // epilogue: TMEM lane = weight row / column of this tile, TMEM column = token
-        if (ok) ok = mbar_wait_bounded(bar(kBarAcc), 0u, abort_flag, p.status, kCodeEpilogue + 1, 8000000000ull);
+        if (ok) ok = mbar_wait_bounded(bar(kBarAcc), 0u, abort_flag, p.status, kCodeEpilogue + 1, 16000000000ll);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: take the epilogue only as a whole warp
         if (ok) {
             tc_fence_after_sync();
-            const int quad = warp & 3, grp2 = (warp - 2) >> 2;
+            const int quad = warp & 3, cgrp = (warp - 2) >> 2;     // TMEM lane quadrant; column group 0..3
             const int orow = tile * kTileW + quad * 32 + lane;
             const bool row_ok = orow < (BWD ? p.K : p.N);
             const float bv = (!BWD && !p.atomic_out && p.bias && row_ok) ? p.bias[orow] : 0.f;
             const int nch = (tb + 31) >> 5;
-            for (int c = grp2; c < nch; c += 2) {
+            for (int c = cgrp; c < nch; c += 4) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
@@ -337,10 +394,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         for (int i = 0; i < 64; i++) __nanosleep(2000);
     }
     tc_fence_before_sync();
-    __syncthreads();
+    // pair mode: neither CTA may leave while the peer's MMAs can still read its shared memory or signal its barriers
+    if (PAIR) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         __syncwarp();
-        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+        if (PAIR) tmem_dealloc_pair(tmem_base, (uint32_t)p.tmem_cols);
+        else tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
 }
 
@@ -376,16 +435,39 @@ bool encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, int esize, const void *b
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int QT, typename T16, bool BWD>
-cudaError_t launch_one(const Params &p, dim3 grid, cudaStream_t s) {
+template <int QT, typename T16, bool BWD, bool PAIR>
+cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
     static bool configured = false;
+    auto kern = k_umma_gemm<QT, T16, BWD, PAIR>;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_umma_gemm<QT, T16, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    k_umma_gemm<QT, T16, BWD><<<grid, kThreads, kSmemBytes, s>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    if (PAIR) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+template <int QT, typename T16, bool BWD>
+cudaError_t launch_one(const Params &p, dim3 grid, bool pair, cudaStream_t s) {
+    if (pair) {
+        grid.x = (grid.x + 1) & ~1u;      // a pair owns two adjacent tiles; a padding tile is all out of range
+        return launch_variant<QT, T16, BWD, true>(p, grid, s);
+    }
+    return launch_variant<QT, T16, BWD, false>(p, grid, s);
 }
 
 }  // namespace
@@ -400,10 +482,10 @@ cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
     bool ok = encode_2d(&w->tm_hdr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
                         (uint64_t)w->row_bytes, H, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
     ok = ok && encode_2d(&w->tm_q0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
-                         (uint64_t)w->row_bytes, 64, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+                         (uint64_t)w->row_bytes, 64, 64, CU_TENSOR_MAP_SWIZZLE_64B);
     if (w->qtype == kTypeQ6K)
         ok = ok && encode_2d(&w->tm_q1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
-                             (uint64_t)w->row_bytes, 32, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+                             (uint64_t)w->row_bytes, 32, 64, CU_TENSOR_MAP_SWIZZLE_32B);
     else
         w->tm_q1 = w->tm_q0;
     if (!ok) {
@@ -441,8 +523,11 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
     memset(&p, 0, sizeof(p));
     const int cols = L.backward ? w->N : w->K;       // contraction length of the activation operand
     const int tmax = L.T < kMaxTok ? L.T : kMaxTok;
-    const int tb = (tmax + 15) & ~15;
-    p.t_box = tb < 128 ? tb : 128;
+    // CTA pairs pay off once the activation tile is the bulk of what an SM pulls from L2; small token counts are
+    // weight-streaming bound and stay on single CTAs
+    const bool pair = tmax >= 256;
+    const int tb = pair ? (tmax + 31) & ~31 : (tmax + 15) & ~15;
+    p.t_box = pair ? 128 : (tb < 128 ? tb : 128);
     int tc = 32;
     while (tc < tb) tc <<= 1;
     p.tmem_cols = tc;
@@ -479,11 +564,11 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
     const int tiles = L.backward ? w->K / kTileW : (w->N + kTileW - 1) / kTileW;
     dim3 grid(tiles, p.splits, (L.T + kMaxTok - 1) / kMaxTok);
     if (w->qtype == kTypeQ4K) {
-        if (!L.fp16) return L.backward ? launch_one<kTypeQ4K, __nv_bfloat16, true>(p, grid, s) : launch_one<kTypeQ4K, __nv_bfloat16, false>(p, grid, s);
-        return L.backward ? launch_one<kTypeQ4K, __half, true>(p, grid, s) : launch_one<kTypeQ4K, __half, false>(p, grid, s);
+        if (!L.fp16) return L.backward ? launch_one<kTypeQ4K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __nv_bfloat16, false>(p, grid, pair, s);
+        return L.backward ? launch_one<kTypeQ4K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __half, false>(p, grid, pair, s);
     }
-    if (!L.fp16) return L.backward ? launch_one<kTypeQ6K, __nv_bfloat16, true>(p, grid, s) : launch_one<kTypeQ6K, __nv_bfloat16, false>(p, grid, s);
-    return L.backward ? launch_one<kTypeQ6K, __half, true>(p, grid, s) : launch_one<kTypeQ6K, __half, false>(p, grid, s);
+    if (!L.fp16) return L.backward ? launch_one<kTypeQ6K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ6K, __nv_bfloat16, false>(p, grid, pair, s);
+    return L.backward ? launch_one<kTypeQ6K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ6K, __half, false>(p, grid, pair, s);
 }
 
 }  // namespace gt
