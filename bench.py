@@ -218,7 +218,8 @@ def run_ours(args) -> None:
             eng.forward(p["w"], p["ad"], p["X"], p["Y"])
         for p in reversed(layer):
             p["dX"].zero_()     # the reference hands Backward a zero-filled dX (AutogradScratchWorkspace.Wrap)
-            eng.backward(p["w"], p["ad"], p["dY"], p["X"], p["dX"])
+            # X is the tensor the forward above saw: X*A kept by the adapter is reused (GT_FLAG_REUSE_LOW)
+            eng.backward(p["w"], p["ad"], p["dY"], p["X"], p["dX"], flags=G.FLAG_REUSE_LOW)
         if world > 1:
             eng.dp_allreduce(flat_grads, 1.0 / world)
 

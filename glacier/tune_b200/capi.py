@@ -16,7 +16,7 @@ from . import build as _build
 TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
 MATH_BF16, MATH_FP16, MATH_FP32 = 0, 1, 2
 DIR_FORWARD, DIR_BACKWARD = 0, 1
-FLAG_DEVICE_PTRS, FLAG_NO_LORA = 1, 2
+FLAG_DEVICE_PTRS, FLAG_NO_LORA, FLAG_REUSE_LOW = 1, 2, 4
 
 EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
@@ -24,7 +24,7 @@ EXPORTS = [
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_grads_scale_clip",
-    "gt_profile_enable", "gt_profile_read", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
+    "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
 
@@ -79,6 +79,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
+    lib.gt_debug_set_trace.argtypes = [C.c_void_p, C.c_void_p]
     lib.gt_profile_enable.argtypes = [C.c_void_p, C.c_int]
     lib.gt_profile_read.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double),
                                     C.POINTER(C.c_int64), C.c_int]
@@ -200,6 +201,9 @@ class Engine:
         norm = C.c_double()
         _check(self.lib.gt_grads_scale_clip(self.h, _ptr(g_dev)[0], g_dev.numel(), pre_scale, max_norm, C.byref(norm)))
         return norm.value
+
+    def set_trace(self, dev_buf=None):
+        _check(self.lib.gt_debug_set_trace(self.h, None if dev_buf is None else C.c_void_p(dev_buf.data_ptr())))
 
     def profile_enable(self, on: bool = True):
         _check(self.lib.gt_profile_enable(self.h, 1 if on else 0))

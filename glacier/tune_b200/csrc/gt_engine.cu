@@ -75,7 +75,7 @@ struct gt_engine {
     std::mutex mu;
     int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
     double *clip = nullptr;      // device double[2]
-    Scratch x16, dy16, low, low16, dlow, dlow16, ytmp;
+    Scratch x16, dy16, low16, dlow, dlow16, ytmp;
     Scratch h_in0, h_in1, h_out;  // device staging for host-pointer calls
     ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
     int dp_world = 1, dp_rank = 0;
@@ -85,6 +85,7 @@ struct gt_engine {
     size_t ev_used = 0;
     double gemm_flops = 0.0;
     int64_t gemm_launches = 0, kernel_launches = 0;
+    void *trace = nullptr;       // device timeline buffer handed to the next GEMM launches (gt_debug_set_trace)
 };
 
 struct gt_weight {
@@ -99,6 +100,8 @@ struct gt_adapter {
     float *A = nullptr, *B = nullptr, *dA = nullptr, *dB = nullptr;
     bool own_grads = true;
     int *b_nonzero = nullptr;    // device flag: any(B != 0), refreshed whenever B is uploaded
+    Scratch low;                 // low = X*A of the last forward / backward through this adapter, [low_T, rank] fp32
+    int low_T = 0;
 };
 
 namespace {
@@ -150,13 +153,17 @@ cudaError_t timed_umma(gt_engine *e, const UmmaLaunch &L, const char **msg) {
 int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora) {
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
-    if (use_lora) GT_CUDA(e->low.reserve((size_t)T * ad->rank * sizeof(float)));
+    float *low = nullptr;
+    if (use_lora) {
+        GT_CUDA(ad->low.reserve((size_t)T * ad->rank * sizeof(float)));
+        low = (float *)ad->low.p;
+        ad->low_T = T;
+    }
     if (!tensor_path(e, w)) {
         GT_LAUNCH(e, launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
         if (use_lora) {
-            GT_LAUNCH(e, launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, ad->rank, e->stream));
-            GT_LAUNCH(e, launch_lora_delta_fp32((const float *)e->low.p, ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling,
-                                           ad->b_nonzero, e->stream));
+            GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, nullptr, 0, 0, T, K, ad->rank, e->stream));
+            GT_LAUNCH(e, launch_lora_delta_fp32(low, ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling, ad->b_nonzero, e->stream));
         }
         return GT_OK;
     }
@@ -164,8 +171,13 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
     GT_CUDA(e->x16.reserve((size_t)T * K * 2));
     if (use_lora) {
         GT_CUDA(e->low16.reserve((size_t)T * 64 * 2));
-        GT_LAUNCH(e, launch_lora_low(Xd, ad->A, (float *)e->low.p, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
-        GT_LAUNCH(e, launch_pack_low16((const float *)e->low.p, e->low16.p, ad->scaling, T, ad->rank, fp16, e->stream));
+        if (e->math_mode == GT_MATH_BF16) {
+            GT_CUDA(cudaMemsetAsync(low, 0, (size_t)T * ad->rank * sizeof(float), e->stream));
+            GT_LAUNCH(e, launch_lora_xa_tc(Xd, ad->A, low, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
+        } else {
+            GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
+        }
+        GT_LAUNCH(e, launch_pack_low16(low, e->low16.p, ad->scaling, T, ad->rank, fp16, e->stream));
     } else {
         GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
     }
@@ -191,6 +203,7 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
         L.lora_flag = ad->b_nonzero;
     }
     L.status = e->status;
+    L.trace = e->trace;
     const char *msg = nullptr;
     cudaError_t ce = timed_umma(e, L, &msg);
     if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
@@ -199,7 +212,7 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
 
 // dX += dY*W (+ lora term); dA, dB accumulate.  Device pointers.
 int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
-                    bool use_lora) {
+                    bool use_lora, bool reuse_low) {
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
     const bool tensor = tensor_path(e, w) && dXd != nullptr;
@@ -208,13 +221,30 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
     if (tensor) GT_CUDA(e->dy16.reserve((size_t)T * ld16 * 2));
     if (use_lora) {
         const int R = ad->rank;
-        GT_CUDA(e->low.reserve((size_t)T * R * sizeof(float)));
+        const bool fast = e->math_mode == GT_MATH_BF16;      // TF32 warp-MMA reductions; exact fp32 otherwise
+        const bool reuse = reuse_low && ad->low.p && ad->low_T == T;
+        GT_CUDA(ad->low.reserve((size_t)T * R * sizeof(float)));
+        float *low = (float *)ad->low.p;
         GT_CUDA(e->dlow.reserve((size_t)T * R * sizeof(float)));
-        GT_LAUNCH(e, launch_lora_low(Xd, ad->A, (float *)e->low.p, nullptr, 0, 0, T, K, R, e->stream));
+        if (!reuse) {
+            if (fast) {
+                GT_CUDA(cudaMemsetAsync(low, 0, (size_t)T * R * sizeof(float), e->stream));
+                GT_LAUNCH(e, launch_lora_xa_tc(Xd, ad->A, low, nullptr, 0, 0, T, K, R, e->stream));
+            } else {
+                GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, nullptr, 0, 0, T, K, R, e->stream));
+            }
+            ad->low_T = T;
+        }
         GT_CUDA(cudaMemsetAsync(e->dlow.p, 0, (size_t)T * R * sizeof(float), e->stream));
-        GT_LAUNCH(e, launch_lora_bwd_dy(dYd, (const float *)e->low.p, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr,
-                                   ld16, fp16, ad->scaling, T, N, R, e->stream));
-        GT_LAUNCH(e, launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
+        if (fast) {
+            GT_LAUNCH(e, launch_lora_dy_tc(dYd, low, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr, ld16, fp16,
+                                           ad->scaling, T, N, R, e->stream));
+            GT_LAUNCH(e, launch_lora_da_tc(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
+        } else {
+            GT_LAUNCH(e, launch_lora_bwd_dy(dYd, low, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr, ld16, fp16,
+                                            ad->scaling, T, N, R, e->stream));
+            GT_LAUNCH(e, launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
+        }
         if (dXd && !tensor) GT_LAUNCH(e, launch_lora_dx_fp32((const float *)e->dlow.p, ad->A, dXd, ad->scaling, T, K, R, e->stream));
         if (tensor) {
             GT_CUDA(e->dlow16.reserve((size_t)T * 64 * 2));
@@ -245,6 +275,7 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
         L.lora_flag = nullptr;
     }
     L.status = e->status;
+    L.trace = e->trace;
     const char *msg = nullptr;
     cudaError_t ce = timed_umma(e, L, &msg);
     if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
@@ -312,7 +343,7 @@ int gt_engine_destroy(gt_engine *e) {
     if (!e) return GT_OK;
     cudaSetDevice(e->device);
     if (e->stream) cudaStreamSynchronize(e->stream);
-    Scratch *all[] = {&e->x16, &e->dy16, &e->low, &e->low16, &e->dlow, &e->dlow16, &e->ytmp, &e->h_in0, &e->h_in1, &e->h_out};
+    Scratch *all[] = {&e->x16, &e->dy16, &e->low16, &e->dlow, &e->dlow16, &e->ytmp, &e->h_in0, &e->h_in1, &e->h_out};
     for (Scratch *s : all) s->release();
     if (e->status) cudaFree(e->status);
     if (e->clip) cudaFree(e->clip);
@@ -335,6 +366,13 @@ int gt_sync(gt_engine *e) {
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
     return check_status(e);
+}
+
+int gt_debug_set_trace(gt_engine *e, void *dev_buf) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    std::lock_guard<std::mutex> lk(e->mu);
+    e->trace = dev_buf;
+    return GT_OK;
 }
 
 int gt_profile_enable(gt_engine *e, int on) {
@@ -504,6 +542,7 @@ int gt_adapter_free(gt_adapter *a) {
         if (a->dB) cudaFree(a->dB);
     }
     if (a->b_nonzero) cudaFree(a->b_nonzero);
+    a->low.release();
     delete a;
     return GT_OK;
 }
@@ -617,7 +656,7 @@ int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const flo
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
     const int N = w->dev.N, K = w->dev.K;
-    if (flags & GT_FLAG_DEVICE_PTRS) return backward_device(e, w, ad, dY, X, dX, T, use_lora);
+    if (flags & GT_FLAG_DEVICE_PTRS) return backward_device(e, w, ad, dY, X, dX, T, use_lora, (flags & GT_FLAG_REUSE_LOW) != 0);
     const size_t bx = (size_t)T * K * sizeof(float), by = (size_t)T * N * sizeof(float);
     GT_CUDA(e->h_in0.reserve(by));
     GT_CUDA(cudaMemcpyAsync(e->h_in0.p, dY, by, cudaMemcpyHostToDevice, e->stream));
@@ -631,7 +670,7 @@ int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const flo
         GT_CUDA(cudaMemcpyAsync(e->h_out.p, dX, bx, cudaMemcpyHostToDevice, e->stream));
     }
     int rc = backward_device(e, w, ad, (const float *)e->h_in0.p, use_lora ? (const float *)e->h_in1.p : nullptr,
-                             dX ? (float *)e->h_out.p : nullptr, T, use_lora);
+                             dX ? (float *)e->h_out.p : nullptr, T, use_lora, (flags & GT_FLAG_REUSE_LOW) != 0);
     if (rc != GT_OK) return rc;
     if (dX) GT_CUDA(cudaMemcpyAsync(dX, e->h_out.p, bx, cudaMemcpyDeviceToHost, e->stream));
     return check_status(e);
@@ -664,7 +703,7 @@ int gt_launch_gemm_bwd(gt_engine *e, const gt_weight *w, float *dDX, const float
     if (batch <= 0) return fail(GT_ERR_INVALID, "batch must be positive (got %d)", batch);
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    return backward_device(e, w, nullptr, dDY, nullptr, dDX, batch, false);
+    return backward_device(e, w, nullptr, dDY, nullptr, dDX, batch, false, false);
 }
 
 int gt_grads_scale_clip(gt_engine *e, float *g_dev, int64_t n, float pre_scale, double max_norm, double *norm_out) {

@@ -54,6 +54,14 @@ cudaError_t launch_any_nonzero(const float *B, int64_t n, int *flag, cudaStream_
 // scratch: 2 doubles on the device
 cudaError_t launch_scale_clip(float *g, int64_t n, float pre_scale, double max_norm, double *scratch, cudaStream_t s);
 
+// ---- LoRA products on TF32 warp MMAs for the bf16 math mode (gt_lora_tc.cu); same contracts as the fp32 versions,
+// except that `low` / `dLow` must be zero on entry (partial sums arrive by atomics)
+cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed, void *x16, int ldx16, int fp16, int T, int K,
+                              int R, cudaStream_t s);
+cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
+                              int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s);
+cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s);
+
 // ---- tcgen05 kernels (gt_umma_gemm.cu) ------------------------------------------------------------------
 struct UmmaLaunch {
     const WeightDev *w = nullptr;
@@ -73,6 +81,7 @@ struct UmmaLaunch {
     const int *lora_flag = nullptr;     // device int: 0 -> skip the update
     int splits = 1;
     int *status = nullptr;              // device int[4]
+    void *trace = nullptr;              // optional device int64[12*128] timeline buffer
 };
 int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count);
 // Returns cudaSuccess or an error; `err` receives a description on failure of a non-CUDA kind.

@@ -1,0 +1,291 @@
+// Rank-r LoRA products for the bf16 math mode, one pass over each activation tensor:
+//   k_lora_xa_tc   low[T,R]  += X[T,K] * A[K,R]                       (+ 16-bit copy of X for the base GEMM)
+//   k_lora_dy_tc   dLow[T,R] += dY[T,N] * B[R,N]^T ; dB[R,N] += s * low^T * dY   (+ 16-bit copy of dY)
+//   k_lora_da_tc   dA[K,R]   += s * X[T,K]^T * dLow[T,R]
+// They replace the host loops of src/Glacier.Tune/Kernels/LoraKernels.cs:35-54,191-291.  Operands are rounded to
+// TF32 (10-bit mantissa, round to nearest) when they are staged in shared memory, products accumulate in fp32 in
+// warp-level m16n8k8 MMAs, and partial sums leave the block through fp32 atomics; the exact-fp32 CUDA-core versions
+// in gt_fp32_kernels.cu serve the validation modes.  Each launch handles 16 ranks [r0, r0 + 16).
+//
+// These kernels are bound by the HBM read of X / dY, not by arithmetic: the tile in shared memory is read once
+// from global memory and reused by every product that needs it.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gt_internal.h"
+
+namespace gt {
+
+namespace {
+
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int fp16) {
+    if (fp16) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+constexpr int TT = 64;     // tokens per tile
+constexpr int TC = 128;    // columns (of K or N) per tile
+constexpr int GS = TC + 4; // smem row stride of the activation tile (words): rows 4 banks apart
+constexpr int RS = 24;     // smem row stride of the 16-wide rank tiles (words)
+
+// Stage a [TT x TC] fp32 tile of src[T, ld] (rows t0.., columns c0..) as TF32 in shared memory, and optionally
+// write its 16-bit rounding to dst16.  256 threads; float4 loads when the tile is interior and aligned.
+__device__ __forceinline__ void stage_tile(const float *__restrict__ src, int T, int ncols, int t0, int t_end, int c0,
+                                           uint32_t (*tile)[GS], uint16_t *__restrict__ dst16, int ld16, int fp16, int tid) {
+    const bool vec = (ncols & 3) == 0 && c0 + TC <= ncols;
+#pragma unroll
+    for (int i = 0; i < (TT * TC / 4) / 256; i++) {
+        const int idx = tid + i * 256;
+        const int r = idx / (TC / 4), c = (idx % (TC / 4)) * 4;
+        const int t = t0 + r;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < t_end) {
+            const float *p = src + (int64_t)t * ncols + c0 + c;
+            if (vec) {
+                v = *reinterpret_cast<const float4 *>(p);
+            } else {
+                if (c0 + c < ncols) v.x = p[0];
+                if (c0 + c + 1 < ncols) v.y = p[1];
+                if (c0 + c + 2 < ncols) v.z = p[2];
+                if (c0 + c + 3 < ncols) v.w = p[3];
+            }
+            if (dst16) {
+                uint16_t *q = dst16 + (int64_t)t * ld16 + c0 + c;
+                if (c0 + c + 3 < ld16 && (ld16 & 3) == 0) {
+                    uint2 o = make_uint2(pack16(v.x, v.y, fp16), pack16(v.z, v.w, fp16));
+                    *reinterpret_cast<uint2 *>(q) = o;
+                } else {
+                    const float e[4] = {v.x, v.y, v.z, v.w};
+                    for (int j = 0; j < 4; j++)
+                        if (c0 + c + j < ld16) q[j] = (uint16_t)(pack16(e[j], 0.f, fp16) & 0xFFFFu);
+                }
+            }
+        }
+        *reinterpret_cast<uint4 *>(&tile[r][c]) = make_uint4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// low[T, R] += X[T, K] * A[K, R] over the block's K slice (grid.y slices of 128), fp32 atomics into low (pre-zeroed).
+// 8 warps = 4 token m-tiles x 2 rank n-tiles; each runs the 16 k-steps of the slice.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_lora_xa_tc(const float *__restrict__ X, const float *__restrict__ A,
+                                                    float *__restrict__ low, uint16_t *__restrict__ x16, int ldx16, int fp16,
+                                                    int T, int K, int R, int r0) {
+    __shared__ __align__(16) uint32_t Xs[TT][GS];
+    __shared__ uint32_t As[TC][RS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int t0 = blockIdx.x * TT, k0 = blockIdx.y * TC;
+    const int rc = min(16, R - r0);
+    stage_tile(X, T, K, t0, T, k0, Xs, r0 == 0 ? x16 : nullptr, ldx16, fp16, tid);
+    for (int i = tid; i < TC * 16; i += 256) {
+        const int k = i >> 4, r = i & 15;
+        As[k][r] = (k0 + k < K && r < rc) ? to_tf32(A[(int64_t)(k0 + k) * R + r0 + r]) : 0u;
+    }
+    __syncthreads();
+    const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < TC / 8; ks++) {
+        const int kk = ks * 8;
+        mma_tf32(d, Xs[m0 + g][kk + t4], Xs[m0 + g + 8][kk + t4], Xs[m0 + g][kk + t4 + 4], Xs[m0 + g + 8][kk + t4 + 4],
+                 As[kk + t4][n0 + g], As[kk + t4 + 4][n0 + g]);
+    }
+    const int ta = t0 + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
+    if (ta < T) {
+        if (ra < rc) atomicAdd(&low[(int64_t)ta * R + r0 + ra], d[0]);
+        if (ra + 1 < rc) atomicAdd(&low[(int64_t)ta * R + r0 + ra + 1], d[1]);
+    }
+    if (tb < T) {
+        if (ra < rc) atomicAdd(&low[(int64_t)tb * R + r0 + ra], d[2]);
+        if (ra + 1 < rc) atomicAdd(&low[(int64_t)tb * R + r0 + ra + 1], d[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// One pass over dY: the block owns a 128-column strip and a token group, walked in 64-token tiles.
+//   dLow[t, r] += sum_c dY[t, c] * B[r, c]      4 m-tiles (tokens) x 2 n-tiles (ranks) over 8 warps, 16 k-steps
+//   dB[r, c]   += s * sum_t low[t, r] * dY[t, c] 1 m-tile (ranks) x 16 n-tiles (columns), 2 per warp, 8 k-steps
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_lora_dy_tc(const float *__restrict__ dY, const float *__restrict__ low,
+                                                    const float *__restrict__ B, float *__restrict__ dB, float *__restrict__ dLow,
+                                                    uint16_t *__restrict__ dy16, int ld16, int fp16, float scaling, int T, int N,
+                                                    int R, int r0, int tok_per_group) {
+    __shared__ __align__(16) uint32_t Gs[TT][GS];
+    __shared__ uint32_t Bs[16][GS];
+    __shared__ uint32_t Ls[TT][RS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int c0 = blockIdx.x * TC;
+    const int tg0 = blockIdx.y * tok_per_group, tg1 = min(T, tg0 + tok_per_group);
+    const int rc = min(16, R - r0);
+    for (int i = tid; i < 16 * TC; i += 256) {
+        const int r = i / TC, c = i % TC;
+        Bs[r][c] = (r < rc && c0 + c < N) ? to_tf32(B[(int64_t)(r0 + r) * N + c0 + c]) : 0u;
+    }
+    float accB[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;      // dLow tiles
+    const int cb = warp * 16;                                  // dB: this warp's two 8-column n-tiles
+    for (int ts = tg0; ts < tg1; ts += TT) {
+        __syncthreads();
+        stage_tile(dY, T, N, ts, tg1, c0, Gs, r0 == 0 ? dy16 : nullptr, ld16, fp16, tid);
+        for (int i = tid; i < TT * 16; i += 256) {
+            const int tt = i >> 4, r = i & 15;
+            Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(low[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
+        }
+        __syncthreads();
+        {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < TC / 8; ks++) {
+                const int kk = ks * 8;
+                mma_tf32(d, Gs[m0 + g][kk + t4], Gs[m0 + g + 8][kk + t4], Gs[m0 + g][kk + t4 + 4], Gs[m0 + g + 8][kk + t4 + 4],
+                         Bs[n0 + g][kk + t4], Bs[n0 + g][kk + t4 + 4]);
+            }
+            const int ta = ts + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
+            if (ta < tg1) {
+                if (ra < rc) atomicAdd(&dLow[(int64_t)ta * R + r0 + ra], d[0]);
+                if (ra + 1 < rc) atomicAdd(&dLow[(int64_t)ta * R + r0 + ra + 1], d[1]);
+            }
+            if (tb < tg1) {
+                if (ra < rc) atomicAdd(&dLow[(int64_t)tb * R + r0 + ra], d[2]);
+                if (ra + 1 < rc) atomicAdd(&dLow[(int64_t)tb * R + r0 + ra + 1], d[3]);
+            }
+        }
+#pragma unroll
+        for (int ks = 0; ks < TT / 8; ks++) {
+            const int kk = ks * 8;      // token index inside the tile
+            const uint32_t a0 = Ls[kk + t4][g], a1 = Ls[kk + t4][g + 8], a2 = Ls[kk + t4 + 4][g], a3 = Ls[kk + t4 + 4][g + 8];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+                mma_tf32(accB[j], a0, a1, a2, a3, Gs[kk + t4][cb + j * 8 + g], Gs[kk + t4 + 4][cb + j * 8 + g]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int c = c0 + cb + j * 8 + 2 * t4;
+        const int ra = g, rb = g + 8;
+        if (c < N) {
+            if (ra < rc) atomicAdd(&dB[(int64_t)(r0 + ra) * N + c], accB[j][0] * scaling);
+            if (rb < rc) atomicAdd(&dB[(int64_t)(r0 + rb) * N + c], accB[j][2] * scaling);
+        }
+        if (c + 1 < N) {
+            if (ra < rc) atomicAdd(&dB[(int64_t)(r0 + ra) * N + c + 1], accB[j][1] * scaling);
+            if (rb < rc) atomicAdd(&dB[(int64_t)(r0 + rb) * N + c + 1], accB[j][3] * scaling);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dA[k, r] += s * sum_t X[t, k] * dLow[t, r]: the block owns a 128-column strip of X and a token group.
+// 8 warps = 8 m-tiles of 16 columns; each covers both rank n-tiles over the 8 token k-steps of a tile.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_lora_da_tc(const float *__restrict__ X, const float *__restrict__ dLow,
+                                                    float *__restrict__ dA, float scaling, int T, int K, int R, int r0,
+                                                    int tok_per_group) {
+    __shared__ __align__(16) uint32_t Xs[TT][GS];
+    __shared__ uint32_t Ls[TT][RS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int k0 = blockIdx.x * TC;
+    const int tg0 = blockIdx.y * tok_per_group, tg1 = min(T, tg0 + tok_per_group);
+    const int rc = min(16, R - r0);
+    const int m0 = warp * 16;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    for (int ts = tg0; ts < tg1; ts += TT) {
+        __syncthreads();
+        stage_tile(X, T, K, ts, tg1, k0, Xs, nullptr, 0, 0, tid);
+        for (int i = tid; i < TT * 16; i += 256) {
+            const int tt = i >> 4, r = i & 15;
+            Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(dLow[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < TT / 8; ks++) {
+            const int kk = ks * 8;
+            const uint32_t a0 = Xs[kk + t4][m0 + g], a1 = Xs[kk + t4][m0 + g + 8], a2 = Xs[kk + t4 + 4][m0 + g],
+                           a3 = Xs[kk + t4 + 4][m0 + g + 8];
+#pragma unroll
+            for (int j = 0; j < 2; j++) mma_tf32(acc[j], a0, a1, a2, a3, Ls[kk + t4][j * 8 + g], Ls[kk + t4 + 4][j * 8 + g]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int ka = k0 + m0 + g, kb = ka + 8, r = j * 8 + 2 * t4;
+        if (ka < K) {
+            if (r < rc) atomicAdd(&dA[(int64_t)ka * R + r0 + r], acc[j][0] * scaling);
+            if (r + 1 < rc) atomicAdd(&dA[(int64_t)ka * R + r0 + r + 1], acc[j][1] * scaling);
+        }
+        if (kb < K) {
+            if (r < rc) atomicAdd(&dA[(int64_t)kb * R + r0 + r], acc[j][2] * scaling);
+            if (r + 1 < rc) atomicAdd(&dA[(int64_t)kb * R + r0 + r + 1], acc[j][3] * scaling);
+        }
+    }
+}
+
+// token groups so that (column strips x groups) covers the SMs about twice; groups are whole 64-token tiles
+void pick_groups(int strips, int T, int &groups, int &tpg) {
+    groups = (2 * 148 + strips - 1) / (strips > 0 ? strips : 1);
+    const int max_groups = (T + TT - 1) / TT;
+    if (groups > max_groups) groups = max_groups;
+    if (groups < 1) groups = 1;
+    tpg = (T + groups - 1) / groups;
+    tpg = (tpg + TT - 1) / TT * TT;
+    groups = (T + tpg - 1) / tpg;
+}
+
+}  // namespace
+
+cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed, void *x16, int ldx16, int fp16, int T, int K,
+                              int R, cudaStream_t s) {
+    if (T <= 0 || K <= 0 || R <= 0) return cudaSuccess;
+    dim3 grid((T + TT - 1) / TT, (K + TC - 1) / TC);
+    for (int r0 = 0; r0 < R; r0 += 16) {
+        k_lora_xa_tc<<<grid, 256, 0, s>>>(X, A, low_zeroed, (uint16_t *)x16, ldx16, fp16, T, K, R, r0);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
+                              int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s) {
+    if (T <= 0 || N <= 0 || R <= 0) return cudaSuccess;
+    const int strips = (N + TC - 1) / TC;
+    int groups, tpg;
+    pick_groups(strips, T, groups, tpg);
+    for (int r0 = 0; r0 < R; r0 += 16) {
+        k_lora_dy_tc<<<dim3(strips, groups), 256, 0, s>>>(dY, low, B, dB, dLow_zeroed, (uint16_t *)dy16, ld16, fp16, scaling, T, N,
+                                                          R, r0, tpg);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s) {
+    if (T <= 0 || K <= 0 || R <= 0) return cudaSuccess;
+    const int strips = (K + TC - 1) / TC;
+    int groups, tpg;
+    pick_groups(strips, T, groups, tpg);
+    for (int r0 = 0; r0 < R; r0 += 16) {
+        k_lora_da_tc<<<dim3(strips, groups), 256, 0, s>>>(X, dLow, dA, scaling, T, K, R, r0, tpg);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace gt

@@ -42,7 +42,7 @@ constexpr int kTileW = 128;        // weight rows (forward) / columns (backward)
 constexpr int kChunk = 64;         // contraction elements per operand stage (one 128-byte row)
 constexpr int kMaxTok = 512;       // tokens per CTA = TMEM columns
 constexpr int kAStageBytes = kTileW * kChunk * 2;   // 16 KiB
-constexpr int kXBytes = 131072;    // activation ring: 2 x 64 KiB (single CTA) or 4 x 32 KiB (CTA pair)
+constexpr int kXBytes = 131072;    // activation ring: 4 x 32 KiB (a CTA holds at most 256 token rows per stage)
 constexpr int kRawStageBytes = 16384;
 constexpr int kNumA = 4, kNumRaw = 2;
 constexpr int kDequantWarps = 16;   // two groups of 8
@@ -55,8 +55,8 @@ constexpr int kOffBar = kOffRaw + kNumRaw * kRawStageBytes;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for 1024-byte alignment
 
 // barrier slots (8 bytes each) inside the kOffBar region
-constexpr int kBarRawFull = 0, kBarRawEmpty = 2, kBarXFull = 4, kBarXEmpty = 8, kBarAFull = 12, kBarAEmpty = 16,
-              kBarAcc = 20, kNumBars = 21;
+// (an operand stage = dequantized weight tile + activation tile; both share one slot index and one full/empty pair)
+constexpr int kBarRawFull = 0, kBarRawEmpty = 2, kBarFull = 4, kBarEmpty = 8, kBarAcc = 12, kNumBars = 13;
 constexpr int kOffTmemSlot = kNumBars * 8;       // u32
 constexpr int kOffAbort = kOffTmemSlot + 4;      // int
 
@@ -72,6 +72,7 @@ struct Params {
     int splits, units;
     int atomic_out;  // 1: red.add into out, 0: plain store (+bias)
     int tmem_cols;
+    long long *trace;   // optional timeline of CTA (0,0,0): [12 rows][128] SM clock values, or null
 };
 
 // status codes written on a bounded-wait timeout: 100*role + barrier kind
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     constexpr int H = QS::kHdrBytes, Q1 = QS::kQ1Bytes;
     constexpr int kRows = BWD ? 64 : 128;      // weight rows per raw stage
     constexpr int kSub = BWD ? 1 : 2;          // operand stages produced per raw stage
-    constexpr int kNumX = PAIR ? 4 : 2;
+    constexpr int kNumX = kNumA;
     constexpr int kXStageBytes = kXBytes / kNumX;
     constexpr int kMmaSlotBytes = PAIR ? 128 * 128 : 256 * 128;   // smem bytes of one MMA's activation rows in a stage
     constexpr uint32_t kFmt = std::is_same<T16, __half>::value ? 0u : 1u;   // UMMA operand format: 0 f16, 1 bf16
@@ -134,13 +135,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             mbar_init(bar(kBarRawFull + i), 1);
             mbar_init(bar(kBarRawEmpty + i), BWD ? 8 : 16);      // one arrival per warp that read the stage
         }
-        for (int i = 0; i < kNumX; i++) {
-            mbar_init(bar(kBarXFull + i), 1);                    // the (leader's) producer arrival + TMA bytes
-            mbar_init(bar(kBarXEmpty + i), 1);
-        }
         for (int i = 0; i < kNumA; i++) {
-            mbar_init(bar(kBarAFull + i), PAIR ? 16 : 8);        // one arrival per producing warp (of both CTAs)
-            mbar_init(bar(kBarAEmpty + i), 1);
+            // full: the (leader's) producer arrival carrying the TMA bytes + one arrival per dequant warp (of both CTAs)
+            mbar_init(bar(kBarFull + i), 1 + (PAIR ? 16 : 8));
+            mbar_init(bar(kBarEmpty + i), 1);                    // tcgen05.commit of the stage's MMAs
         }
         mbar_init(bar(kBarAcc), 1);
         *abort_flag = 0;
@@ -162,6 +160,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     if (PAIR) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    auto trace = [&](int row, int idx) {
+        if (tracing && idx < 128) p.trace[row * 128 + idx] = clock64();
+    };
+    if (threadIdx.x == 0) trace(11, 0);
 
     // activation tile of one stage: coordinate c0 along the contraction, this CTA's token rows
     auto load_act_stage = [&](const CUtensorMap *tm, int c0, uint32_t xdst, uint32_t xbar_local) {
@@ -203,69 +206,60 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     tma_load_2d(rdst + kRows * H + rr * 64, &p.tm_q0, xb + QS::q0_x(half), row0 + rr, rbar);
                     if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64) + rr * Q1, &p.tm_q1, xb + QS::q1_x(half), row0 + rr, rbar);
                 }
+                trace(0, u - u0);
                 raw.advance(kNumRaw);
                 for (int s = 0; s < kSub && ok; s++) {
-                    ok = mbar_wait_bounded(bar(kBarXEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
+                    ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
                     if (!ok) break;
                     load_act_stage(&p.tm_act, BWD ? u * 64 : (u * 2 + s) * 64, sbase + kOffX + xs.idx * kXStageBytes,
-                                   bar(kBarXFull + xs.idx));
+                                   bar(kBarFull + xs.idx));
+                    trace(1, (u - u0) * kSub + s);
                     xs.advance(kNumX);
                 }
             }
             if (ok && do_lora) {
-                ok = mbar_wait_bounded(bar(kBarXEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
-                if (ok) load_act_stage(&p.tm_lora, 0, sbase + kOffX + xs.idx * kXStageBytes, bar(kBarXFull + xs.idx));
+                ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
+                if (ok) load_act_stage(&p.tm_lora, 0, sbase + kOffX + xs.idx * kXStageBytes, bar(kBarFull + xs.idx));
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
         if (lane == 0 && leader) {
-            Ring as, xs;
-            bool ok = true, first = true;
+            bool ok = true;
             const uint32_t a_mn = BWD ? 1u : 0u;
-            auto wait_full = [&](int slot, uint32_t phase, int code) -> bool {
-                return PAIR ? mbar_wait_bounded_cluster(bar(slot), phase, abort_flag, p.status, code)
-                            : mbar_wait_bounded(bar(slot), phase, abort_flag, p.status, code);
+            auto wait_full = [&](int n, int code) -> bool {
+                const int slot = kBarFull + (n & (kNumA - 1));
+                const uint32_t phase = (uint32_t)(n / kNumA) & 1u;
+                const bool r = PAIR ? mbar_wait_bounded_cluster(bar(slot), phase, abort_flag, p.status, code)
+                                    : mbar_wait_bounded(bar(slot), phase, abort_flag, p.status, code);
+                tc_fence_after_sync();
+                return r;
             };
-            auto issue_stage = [&](int ksteps) {
-                const uint32_t a_addr = sbase + kOffA + as.idx * kAStageBytes;
-                const uint32_t x_addr = sbase + kOffX + xs.idx * kXStageBytes;
+            const int n_main = (u1 - u0) * kSub;
+            const int n_total = n_main + (do_lora ? 1 : 0);
+            for (int n = 0; n < n_total && ok; n++) {
+                ok = wait_full(n, kCodeMma + 1);
+                if (!ok) break;
+                const int si = n & (kNumA - 1);
+                const uint32_t a_addr = sbase + kOffA + si * kAStageBytes;
+                const uint32_t x_addr = sbase + kOffX + si * kXStageBytes;
+                const int ksteps = n < n_main ? 4 : (rank_pad >> 4);
+                trace(8, n);
+                // k-step-major order: consecutive MMAs alternate between the accumulators (measured faster than
+                // finishing one accumulator's k-steps first)
                 for (int ks = 0; ks < ksteps; ks++) {
                     const uint64_t adesc = BWD ? umma_desc_sw128(a_addr + ks * 2048, 8192, 1024)
                                                : umma_desc_sw128(a_addr + ks * 32, 16, 1024);
                     for (int i = 0; i < n_mma; i++) {
                         const int ntok = min(256, tb - 256 * i);
                         const uint64_t bdesc = umma_desc_sw128(x_addr + i * kMmaSlotBytes + ks * 32, 16, 1024);
-                        const uint32_t acc = (first && ks == 0) ? 0u : 1u;
+                        const uint32_t acc = (n == 0 && ks == 0) ? 0u : 1u;
                         if (PAIR) umma_f16_ss_pair(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 256), acc);
                         else umma_f16_ss(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 128), acc);
                     }
                 }
-                first = false;
-                if (PAIR) {
-                    umma_commit_pair(bar(kBarAEmpty + as.idx));
-                    umma_commit_pair(bar(kBarXEmpty + xs.idx));
-                } else {
-                    umma_commit(bar(kBarAEmpty + as.idx));
-                    umma_commit(bar(kBarXEmpty + xs.idx));
-                }
-                as.advance(kNumA);
-                xs.advance(kNumX);
-            };
-            for (int u = u0; u < u1 && ok; u++) {
-                for (int s = 0; s < kSub && ok; s++) {
-                    ok = wait_full(kBarAFull + as.idx, as.phase, kCodeMma + 1) && wait_full(kBarXFull + xs.idx, xs.phase, kCodeMma + 2);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_stage(4);
-                }
-            }
-            if (ok && do_lora) {
-                ok = wait_full(kBarAFull + as.idx, as.phase, kCodeMma + 3) && wait_full(kBarXFull + xs.idx, xs.phase, kCodeMma + 4);
-                if (ok) {
-                    tc_fence_after_sync();
-                    issue_stage(rank_pad >> 4);
-                }
+                if (PAIR) umma_commit_pair(bar(kBarEmpty + si)); else umma_commit(bar(kBarEmpty + si));
+                trace(9, n);
             }
             if (ok) {
                 if (PAIR) umma_commit_pair(bar(kBarAcc)); else umma_commit(bar(kBarAcc));
@@ -280,15 +274,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         // "operand stage ready": on the barrier of the CTA that issues the MMAs
         auto signal_a_full = [&](int ai) {
             if (lane == 0) {
-                if (PAIR && !leader) mbar_arrive_cluster(mapa_cluster(bar(kBarAFull + ai), 0));
-                else mbar_arrive(bar(kBarAFull + ai));
+                if (PAIR && !leader) mbar_arrive_cluster(mapa_cluster(bar(kBarFull + ai), 0));
+                else mbar_arrive(bar(kBarFull + ai));
             }
         };
         // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i & 1
         auto produce = [&](int n, const uint8_t *rs, int row, int grp, int half, uint32_t dst_off, int chunk0) -> bool {
             const int ai = n & (kNumA - 1);
-            if (!mbar_wait_bounded(bar(kBarAEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 2))
+            if (!mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 2))
                 return false;
+            if (dt == 0) trace(3 + 3 * g, n >> (BWD ? 0 : 0));
             const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
             dequant32_to_swizzled_row<QT, T16>(rs + row * H, rs + kRows * H + row * 64,
                                                rs + kRows * (H + 64) + row * (Q1 > 0 ? Q1 : 1), (row >> 1) & 3, (row >> 2) & 1,
@@ -296,6 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             fence_proxy_async_smem();
             __syncwarp();
             signal_a_full(ai);
+            if (dt == 0) trace(4 + 3 * g, n);
             return true;
         };
         if (!BWD) {
@@ -305,6 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const int ri = ui & 1;
                 ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui >> 1) & 1u, abort_flag, p.status, kCodeDequant + 1);
                 if (!ok) break;
+                if (dt == 0) trace(2 + 3 * g, 2 * ui + g);
                 const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
                 ok = produce(2 * ui + g, rs, row, 2 * g + hn, (u0 + ui) & 1, (uint32_t)(row * 128), 4 * hn);
                 if (!ok) break;
@@ -317,6 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const int ri = ui & 1;
                 ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui >> 1) & 1u, abort_flag, p.status, kCodeDequant + 1);
                 if (!ok) break;
+                if (dt == 0) trace(2 + 3 * g, ui);
                 const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
                 ok = produce(ui, rs, row, grp, tile & 1, (uint32_t)((grp >> 1) * 8192 + row * 128), 4 * (grp & 1));
                 if (!ok) break;
@@ -326,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         if (ok && do_lora && g == 0) {
             const int n = (BWD ? 1 : 2) * nu;
             const int ai = n & (kNumA - 1);
-            ok = mbar_wait_bounded(bar(kBarAEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
+            ok = mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
             if (ok) {
                 const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
                 if (!BWD) {
@@ -363,6 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: take the epilogue only as a whole warp
         if (ok) {
             tc_fence_after_sync();
+            if (threadIdx.x == 64) trace(11, 1);
             const int quad = warp & 3, cgrp = (warp - 2) >> 2;     // TMEM lane quadrant; column group 0..3
             const int orow = tile * kTileW + quad * 32 + lane;
             const bool row_ok = orow < (BWD ? p.K : p.N);
@@ -389,6 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         }
     }
 
+    if (threadIdx.x == 64) trace(11, 2);
     if (*abort_flag) {
         // give loads that were already issued time to land before the CTA's shared memory is released
         for (int i = 0; i < 64; i++) __nanosleep(2000);
@@ -555,6 +555,7 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
     p.ld_out = L.ld_out;
     p.bias = L.bias;
     p.status = L.status;
+    p.trace = (long long *)L.trace;
     p.T = L.T;
     p.N = w->N;
     p.K = w->K;

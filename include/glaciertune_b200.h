@@ -67,7 +67,10 @@ enum gt_direction { GT_DIR_FORWARD = 0, GT_DIR_BACKWARD = 1 };
 
 enum gt_flags {
     GT_FLAG_DEVICE_PTRS = 1, /* activation pointers are device pointers; asynchronous on the engine stream */
-    GT_FLAG_NO_LORA = 2      /* skip the adapter terms even when an adapter is given */
+    GT_FLAG_NO_LORA = 2,     /* skip the adapter terms even when an adapter is given */
+    GT_FLAG_REUSE_LOW = 4    /* backward: X is the tensor the last forward through this adapter saw, so X*A kept from
+                                that call is reused instead of recomputed (the reference recomputes it,
+                                src/Glacier.Tune/Kernels/LoraKernels.cs:147-186; the value is the same) */
 };
 
 typedef struct gt_config {
@@ -169,6 +172,12 @@ GT_API int gt_grads_scale_clip(gt_engine *eng, float *g_dev, int64_t n, float pr
 GT_API int gt_profile_enable(gt_engine *eng, int on);
 GT_API int gt_profile_read(gt_engine *eng, double *gemm_ms, int64_t *gemm_launches, double *gemm_flops,
                            int64_t *kernel_launches, int reset);
+
+/* Kernel timeline for tuning: while dev_buf (device, 12*128 int64, or NULL to stop) is set, the first CTA of every
+ * tensor-core GEMM launch writes SM-clock stamps of its pipeline events into it (rows: 0 weight-block loads issued,
+ * 1 activation loads issued, 2-4 / 5-7 dequant group 0 / 1 (blocks arrived, slot free, tile published), 8 MMA
+ * operands ready, 9 MMAs issued, 11 start / accumulator ready / end).  No counterpart in the reference. */
+GT_API int gt_debug_set_trace(gt_engine *eng, void *dev_buf);
 
 /* Data parallel step driver (no counterpart in the reference, which is single-GPU: one GpuContext,
  * src/Glacier.Tune/Gpu/GpuLoraEngine.cs:114-130).  One process per GPU; each holds a replica of the frozen

@@ -16,7 +16,9 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 TOL = {0: 2e-2, 1: 1e-3, 2: 1e-3}        # bf16, fp16, fp32 math modes
-LORA_TOL = 1e-3                           # dA, dB are fp32 CUDA-core reductions in every mode
+# dA, dB: TF32 warp-MMA reductions with fp32 accumulation in bf16 mode (gate 2e-2; they land near 5e-4, held to
+# 5e-3 here), exact fp32 CUDA-core reductions in the validation modes
+LTOL = {0: 5e-3, 1: 1e-3, 2: 1e-3}
 
 
 @pytest.fixture(scope="module")
@@ -99,7 +101,7 @@ def test_projection_golden_fixture(G, eng, mode):
     from oracle import oracle as O
     y, dx, da, db = _run(G, eng, c, mode)
     assert O.rel_fro(y, p["y"]) < TOL[mode] and O.rel_fro(dx, p["dx"]) < TOL[mode]
-    assert O.rel_fro(da, p["da"]) < LORA_TOL and O.rel_fro(db, p["db"]) < LORA_TOL
+    assert O.rel_fro(da, p["da"]) < LTOL[mode] and O.rel_fro(db, p["db"]) < LTOL[mode]
 
 
 SHAPES = [
@@ -120,7 +122,7 @@ def test_projection_parity(G, eng, oracle, mode, qtype, N, K, T):
     yr, dxr, dar, dbr = _reference(oracle, c)
     errs = dict(Y=oracle.rel_fro(y, yr), dX=oracle.rel_fro(dx, dxr), dA=oracle.rel_fro(da, dar), dB=oracle.rel_fro(db, dbr))
     assert errs["Y"] < TOL[mode] and errs["dX"] < TOL[mode], errs
-    assert errs["dA"] < LORA_TOL and errs["dB"] < LORA_TOL, errs
+    assert errs["dA"] < LTOL[mode] and errs["dB"] < LTOL[mode], errs
     # and against the fp32 CPU path itself (LoraAdapter.Forward / Backward as the reference runs them)
     y_cpu = oracle.proj_forward(qtype, c["w"], c["bias"], c["x"], K, N, T, c["a"], c["b"], 16, c["scaling"])
     assert oracle.rel_fro(y, y_cpu) < TOL[mode]
@@ -141,7 +143,7 @@ def test_config0_flat_stream_shape(G, eng, oracle, mode):
     y, dx, da, db = _run(G, eng, c, mode, bias=False)
     yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
     assert oracle.rel_fro(y, yr) < TOL[mode] and oracle.rel_fro(dx, dxr) < TOL[mode]
-    assert oracle.rel_fro(da, dar) < LORA_TOL and oracle.rel_fro(db, dbr) < LORA_TOL
+    assert oracle.rel_fro(da, dar) < LTOL[mode] and oracle.rel_fro(db, dbr) < LTOL[mode]
 
 
 @pytest.mark.parametrize("mode", [0, 2])
@@ -169,7 +171,7 @@ def test_dx_and_grads_accumulate(G, eng, oracle, mode):
     assert oracle.rel_fro(dx - dx0, dxr) < TOL[mode]          # += into the caller's buffer
     eng.backward(w, ad, c["dy"], c["x"], None)                # grads only
     da, db = ad.grads()
-    assert oracle.rel_fro(da, 2 * dar) < LORA_TOL and oracle.rel_fro(db, 2 * dbr) < LORA_TOL
+    assert oracle.rel_fro(da, 2 * dar) < LTOL[mode] and oracle.rel_fro(db, 2 * dbr) < LTOL[mode]
     ad.zero_grads()
     da, db = ad.grads()
     assert np.all(da == 0) and np.all(db == 0)
@@ -183,13 +185,32 @@ def test_dx_and_grads_accumulate(G, eng, oracle, mode):
     ad.free()
 
 
+def test_backward_reusing_forward_low(G, eng, oracle):
+    """GT_FLAG_REUSE_LOW: the backward takes X*A from the forward through the same adapter instead of recomputing it."""
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 300, seed=13)
+    for mode in (0, 2):
+        eng.set_math_mode(mode)
+        w = eng.upload_weight(c["qtype"], c["w"], c["N"], c["K"])
+        ad = eng.create_adapter(c["K"], c["N"], 16, 32.0)
+        ad.upload(c["a"], c["b"])
+        eng.forward(w, ad, c["x"])
+        dx = np.zeros((300, 512), np.float32)
+        eng.backward(w, ad, c["dy"], c["x"], dx, flags=G.FLAG_REUSE_LOW)
+        da, db = ad.grads()
+        _, dxr, dar, dbr = _reference(oracle, c, bias=False)
+        assert oracle.rel_fro(dx, dxr) < TOL[mode]
+        assert oracle.rel_fro(da, dar) < LTOL[mode] and oracle.rel_fro(db, dbr) < LTOL[mode]
+        w.free()
+        ad.free()
+
+
 def test_rank8_adapter(G, eng, oracle):
     c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 64, seed=21, rank=8, alpha=16.0)
     for mode in (0, 2):
         y, dx, da, db = _run(G, eng, c, mode, bias=False)
         yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
         assert oracle.rel_fro(y, yr) < TOL[mode] and oracle.rel_fro(dx, dxr) < TOL[mode]
-        assert oracle.rel_fro(da, dar) < LORA_TOL and oracle.rel_fro(db, dbr) < LORA_TOL
+        assert oracle.rel_fro(da, dar) < LTOL[mode] and oracle.rel_fro(db, dbr) < LTOL[mode]
 
 
 def test_device_pointer_entry_points(G, eng, oracle):
@@ -300,4 +321,4 @@ def test_cpp_host_mirror(G, eng, oracle, tmp_path):
     y, dx, da, db = np.split(raw, np.cumsum(sizes)[:-1])
     yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
     assert oracle.rel_fro(y.reshape(32, 256), yr) < 2e-2 and oracle.rel_fro(dx.reshape(32, 512), dxr) < 2e-2
-    assert oracle.rel_fro(da.reshape(512, 16), dar) < LORA_TOL and oracle.rel_fro(db.reshape(16, 256), dbr) < LORA_TOL
+    assert oracle.rel_fro(da.reshape(512, 16), dar) < LTOL[0] and oracle.rel_fro(db.reshape(16, 256), dbr) < LTOL[0]
