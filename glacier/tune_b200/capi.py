@@ -23,7 +23,7 @@ EXPORTS = [
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward",
-    "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_grads_scale_clip",
+    "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
@@ -78,6 +78,7 @@ def load_library(path: str | None = None) -> C.CDLL:
                                      C.c_int32]
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
+    lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
     lib.gt_debug_set_trace.argtypes = [C.c_void_p, C.c_void_p]
     lib.gt_profile_enable.argtypes = [C.c_void_p, C.c_int]
@@ -189,6 +190,10 @@ class Engine:
 
     def launch_gemm_bwd(self, w: "Weight", dX, dY, batch: int):
         _check(self.lib.gt_launch_gemm_bwd(self.h, w.h, _ptr(dX)[0], _ptr(dY)[0], batch))
+
+    def launch_gemm_bwd_static(self, w: "Weight", dX, dY, batch: int):
+        """Allocation-free variant of launch_gemm_bwd (fixed 4 MiB scratch inside the library)."""
+        _check(self.lib.gt_launch_gemm_bwd_static(self.h, w.h, _ptr(dX)[0], _ptr(dY)[0], batch))
 
     def dequant_rows(self, w: "Weight", row0: int, nrows: int, out=None):
         if out is None:

@@ -284,6 +284,12 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
 
 }  // namespace
 
+namespace gt {
+EngineView engine_view(gt_engine *e) { return EngineView{e->device, e->math_mode, e->sm_count, e->stream, e->status, &e->mu}; }
+const WeightDev *weight_view(const gt_weight *w) { return &w->dev; }
+int set_last_error(int code, const char *text) { return fail(code, "%s", text); }
+}  // namespace gt
+
 extern "C" {
 
 const char *gt_last_error(void) { return g_err; }

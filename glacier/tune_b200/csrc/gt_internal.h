@@ -89,4 +89,21 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
 cudaError_t umma_init_weight_maps(WeightDev *w, const char **err);
 bool umma_available();
 
+
+// ---- views of the opaque C-ABI handles for translation units outside gt_engine.cu ---------------------------
+struct EngineView {
+    int device;
+    int math_mode;
+    int sm_count;
+    cudaStream_t stream;
+    int *status;       // device int[4], bounded-wait codes of the tensor-core kernels
+    void *mutex;       // std::mutex * serialising calls on the engine
+};
+}  // namespace gt
+struct gt_engine;
+struct gt_weight;
+namespace gt {
+EngineView engine_view(gt_engine *e);
+const WeightDev *weight_view(const gt_weight *w);
+int set_last_error(int code, const char *text);     // records the text for gt_last_error(), returns code
 }  // namespace gt

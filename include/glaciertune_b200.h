@@ -157,6 +157,20 @@ GT_API int gt_launch_gemm_batch(gt_engine *eng, const gt_weight *w, float *dY_ou
  * (src/Glacier.Tune/Gpu/GpuLoraEngine.Backward.cs:15-56): dDX[batch,in] += dDY[batch,out] * W. */
 GT_API int gt_launch_gemm_bwd(gt_engine *eng, const gt_weight *w, float *dDX_accum, const float *dDY, int32_t batch);
 
+/* No counterpart in the reference (its engine allocates and grows device scratch on demand,
+ * src/Glacier.Tune/Gpu/GpuLoraEngine.Memory.cs:7-114).  Same result as gt_launch_gemm_bwd - dDX[batch,in] +=
+ * dDY[batch,out] * W on device pointers, asynchronous on the engine stream - for hosts that may not allocate
+ * device memory when they call: inside a stream capture, in a loop that cannot afford cudaMalloc's device-wide
+ * synchronisation, or after all memory has been handed to a pool.  The 16-bit copy of dDY that the tensor-core
+ * kernel reads lives in a fixed 4 MiB array inside the library image (held by every GPU that loads the library)
+ * instead of the engine's grow-only buffer, and the call performs no allocation of any kind.
+ *   - batch * round_up(out, 8) must be <= 2,097,152 elements, else GT_ERR_UNSUPPORTED and nothing is launched;
+ *   - tensor-core math modes and K-quant weights with in % 256 == 0 only (GT_ERR_UNSUPPORTED otherwise);
+ *   - the first call on a device looks up the array's device address: make that call before any stream capture;
+ *   - all calls share the array (it keeps the previous call's contents; every element read is rewritten first, so
+ *     nothing needs clearing); calls whose GPU work overlaps on one device race on it - serialise them. */
+GT_API int gt_launch_gemm_bwd_static(gt_engine *eng, const gt_weight *w, float *dDX_accum, const float *dDY, int32_t batch);
+
 /* Replaces: LoraTrainer.ScaleAccumulatedGradients / ClipGradients
  * (src/Glacier.Tune/Trainer/LoraTrainer.cs:352-377,395-433) on a flat device gradient buffer:
  * g *= pre_scale; norm = sqrt(sum g^2) in fp64; non-finite -> g = 0, *norm_out = 0; norm > max_norm ->
