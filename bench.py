@@ -74,6 +74,7 @@ def run_reference(args) -> None:
         return
     from oracle import oracle as O
     O.build()
+    O.set_threads(os.cpu_count() or 1)           # torchrun pins OMP_NUM_THREADS=1; the CPU arm uses every host core
     cores = O.num_threads()
     budget_s = 150.0
     names = list(PROJ_ORDER)
@@ -162,6 +163,11 @@ class ClockSampler:
         return out
 
 
+def _log(msg: str) -> None:
+    if os.environ.get("GT_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -176,6 +182,8 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"          # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     # a real (non-default) stream shared by torch and the engine, so torch.cuda.Event brackets the engine's kernels
@@ -210,6 +218,7 @@ def run_ours(args) -> None:
         dist.broadcast_object_list(ident, src=0)
         eng.dp_init(world, rank, ident[0])
 
+    _log("layer built")
     l2_flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
     def step_resident():
@@ -243,12 +252,20 @@ def run_ours(args) -> None:
     if rank == 0:
         sampler.start()
     warm_t0, n_warm = time.perf_counter(), 0
-    while n_warm < max(args.warmup, 3) or time.perf_counter() - warm_t0 < 0.6:
-        step_resident()
-        l2_flush.zero_()
-        n_warm += 1
-        if n_warm % 16 == 0:
-            torch.cuda.synchronize()
+    while True:
+        # every rank must run the same number of steps (each holds an all-reduce): warm up in chunks and let the
+        # ranks agree on whether another chunk is needed
+        for _ in range(max(args.warmup, 3) if n_warm == 0 else 50):
+            step_resident()
+            l2_flush.zero_()
+            n_warm += 1
+        torch.cuda.synchronize()
+        more = torch.tensor([1 if time.perf_counter() - warm_t0 < 0.6 else 0], dtype=torch.int32, device=dev)
+        if world > 1:
+            dist.all_reduce(more, op=dist.ReduceOp.MAX)
+        if int(more.item()) == 0:
+            break
+    _log(f"warm-up done ({n_warm} steps)")
     eng.sync()
     # The step is launch-bound on the host side (about 55 short kernels): capture it once in a CUDA graph and time
     # replays.  The engine enqueues on the stream torch captures; nothing in the step allocates after the warm-up.
@@ -257,7 +274,7 @@ def run_ours(args) -> None:
         try:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
                 step_resident()
             torch.cuda.set_stream(stream)
             for _ in range(3):
@@ -269,6 +286,7 @@ def run_ours(args) -> None:
             torch.cuda.set_stream(stream)
             torch.cuda.synchronize()
     run_step = graph.replay if graph is not None else step_resident
+    _log(f"graph={'yes' if graph is not None else 'no'}")
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
@@ -300,6 +318,7 @@ def run_ours(args) -> None:
     fl = step_flops()
     value = world * fl * args.steps / (total_ms * 1e-3) / 1e12
 
+    _log("timed region done")
     # ---- end to end through the C ABI with host buffers (H2D of the inputs, D2H of the results, every step)
     e2e_steps = max(1, min(args.steps, 8))
     step_host()
@@ -317,6 +336,7 @@ def run_ours(args) -> None:
     h2d = sum(4 * M_TOKENS * (p["K"] + p["N"] + p["K"] + p["K"]) for p in layer)   # X (fwd), dY, X, dX (bwd)
     d2h = sum(4 * M_TOKENS * (p["N"] + p["K"]) for p in layer)                      # Y, dX
 
+    _log("e2e done")
     if rank == 0:
         peaks = measured_peaks()
         gemm_tflops = prof["gemm_flops"] / (prof["gemm_ms"] * 1e-3) / 1e12 if prof["gemm_ms"] > 0 else 0.0
@@ -332,6 +352,7 @@ def run_ours(args) -> None:
         # CPU baseline: the oracle (a port of the reference's CPU path) on this host, one pass over the same layer
         from oracle import oracle as O
         O.build()
+        O.set_threads(os.cpu_count() or 1)       # torchrun pins OMP_NUM_THREADS=1
         cpu_layer_pass(O, make_cpu_cases(["k"]))
         names = list(PROJ_ORDER)
         t_q = cpu_layer_pass(O, make_cpu_cases(["q"]))

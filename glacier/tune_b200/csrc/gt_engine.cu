@@ -75,7 +75,7 @@ struct gt_engine {
     std::mutex mu;
     int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
     double *clip = nullptr;      // device double[2]
-    Scratch x16, dy16, low16, dlow, dlow16, ytmp;
+    Scratch x16, dy16, dlow, ytmp;
     Scratch h_in0, h_in1, h_out;  // device staging for host-pointer calls
     ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
     int dp_world = 1, dp_rank = 0;
@@ -170,14 +170,12 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
     const int fp16 = e->math_mode == GT_MATH_FP16;
     GT_CUDA(e->x16.reserve((size_t)T * K * 2));
     if (use_lora) {
-        GT_CUDA(e->low16.reserve((size_t)T * 64 * 2));
         if (e->math_mode == GT_MATH_BF16) {
             GT_CUDA(cudaMemsetAsync(low, 0, (size_t)T * ad->rank * sizeof(float), e->stream));
             GT_LAUNCH(e, launch_lora_xa_tc(Xd, ad->A, low, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
         } else {
             GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
         }
-        GT_LAUNCH(e, launch_pack_low16(low, e->low16.p, ad->scaling, T, ad->rank, fp16, e->stream));
     } else {
         GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
     }
@@ -197,7 +195,8 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
         L.out_prefilled = 1;
     }
     if (use_lora) {
-        L.lora_act16 = e->low16.p;
+        L.lora_act = low;
+        L.lora_scale = ad->scaling;
         L.lora_w = ad->B;
         L.rank = ad->rank;
         L.lora_flag = ad->b_nonzero;
@@ -246,10 +245,6 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
             GT_LAUNCH(e, launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
         }
         if (dXd && !tensor) GT_LAUNCH(e, launch_lora_dx_fp32((const float *)e->dlow.p, ad->A, dXd, ad->scaling, T, K, R, e->stream));
-        if (tensor) {
-            GT_CUDA(e->dlow16.reserve((size_t)T * 64 * 2));
-            GT_LAUNCH(e, launch_pack_low16((const float *)e->dlow.p, e->dlow16.p, ad->scaling, T, R, fp16, e->stream));
-        }
     } else if (tensor) {
         GT_LAUNCH(e, launch_cast16(dYd, e->dy16.p, T, N, ld16, fp16, e->stream));
     }
@@ -269,7 +264,8 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
     L.ld_out = K;
     L.splits = umma_pick_splits(&wd, 1, T, e->sm_count);
     if (use_lora) {
-        L.lora_act16 = e->dlow16.p;
+        L.lora_act = (const float *)e->dlow.p;
+        L.lora_scale = ad->scaling;
         L.lora_w = ad->A;
         L.rank = ad->rank;
         L.lora_flag = nullptr;
@@ -349,7 +345,7 @@ int gt_engine_destroy(gt_engine *e) {
     if (!e) return GT_OK;
     cudaSetDevice(e->device);
     if (e->stream) cudaStreamSynchronize(e->stream);
-    Scratch *all[] = {&e->x16, &e->dy16, &e->low16, &e->dlow, &e->dlow16, &e->ytmp, &e->h_in0, &e->h_in1, &e->h_out};
+    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->h_in0, &e->h_in1, &e->h_out};
     for (Scratch *s : all) s->release();
     if (e->status) cudaFree(e->status);
     if (e->clip) cudaFree(e->clip);

@@ -312,18 +312,6 @@ cudaError_t launch_lora_low(const float *X, const float *A, float *low, void *x1
     return cudaSuccess;
 }
 
-__global__ void k_pack_low16(const float *__restrict__ low, uint16_t *__restrict__ out, float scale, int T, int R, int fp16) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= T * 64) return;
-    const int t = i >> 6, r = i & 63;
-    out[i] = r < R ? round16(low[(int64_t)t * R + r] * scale, fp16) : (uint16_t)0;
-}
-cudaError_t launch_pack_low16(const float *low, void *low16, float scale, int T, int R, int fp16, cudaStream_t s) {
-    if (T <= 0) return cudaSuccess;
-    k_pack_low16<<<(T * 64 + 255) / 256, 256, 0, s>>>(low, (uint16_t *)low16, scale, T, R, fp16);
-    return cudaGetLastError();
-}
-
 // Y[t, n] += sum_r (low[t, r] * scaling) * B[r, n]   (LoraKernels.cs:57-86); fp32 validation path.
 __global__ void k_lora_delta_fp32(const float *__restrict__ low, const float *__restrict__ B, float *__restrict__ Y,
                                   float *__restrict__ residual, int T, int N, int R, float scaling,

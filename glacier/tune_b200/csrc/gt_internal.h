@@ -30,8 +30,6 @@ cudaError_t launch_gemm_fp32_bwd(int qt, const uint8_t *w, const float *dY, floa
 // low[T,R] = X*A ; optionally x16[T, ldx16] = round16(X) (r0 == 0 pass only).
 cudaError_t launch_lora_low(const float *X, const float *A, float *low, void *x16, int ldx16, int fp16, int T, int K,
                             int R, cudaStream_t s);
-// low16[T, 64] = round16(scale * low[T, R]) zero-padded to 64 columns.
-cudaError_t launch_pack_low16(const float *low, void *low16, float scale, int T, int R, int fp16, cudaStream_t s);
 // Y[T,N] += scaling * low * B
 cudaError_t launch_lora_delta_fp32(const float *low, const float *B, float *Y, float *residual, int T, int N, int R,
                                    float scaling, const int *nonzero_flag, cudaStream_t s);
@@ -75,7 +73,8 @@ struct UmmaLaunch {
     const float *bias = nullptr;   // forward only
     int out_prefilled = 0;         // forward: out already holds bias/zero, accumulate with atomics (split-K)
     // fused LoRA rank-update (optional)
-    const void *lora_act16 = nullptr;   // [T, 64] zero-padded 16-bit, already scaled
+    const float *lora_act = nullptr;    // fp32 [T, R]: X*A (forward) or dY*B^T (backward)
+    float lora_scale = 1.f;             // alpha / r, applied when the tile is rounded to 16 bits
     const float *lora_w = nullptr;      // forward: B [R, N]; backward: A [K, R]
     int rank = 0;
     const int *lora_flag = nullptr;     // device int: 0 -> skip the update

@@ -61,10 +61,12 @@ constexpr int kOffTmemSlot = kNumBars * 8;       // u32
 constexpr int kOffAbort = kOffTmemSlot + 4;      // int
 
 struct Params {
-    CUtensorMap tm_act, tm_lora, tm_hdr, tm_q0, tm_q1;
+    CUtensorMap tm_act, tm_hdr, tm_q0, tm_q1;
     float *out;
     const float *bias;
     const float *lora_w;
+    const float *lora_act;   // fp32 [T, rank]: X*A (forward) or dY*B^T (backward); scaled by lora_scale in the kernel
+    float lora_scale;
     const int *lora_flag;
     int *status;
     int ld_out, T, N, K, rank;
@@ -137,7 +139,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         }
         for (int i = 0; i < kNumA; i++) {
             // full: the (leader's) producer arrival carrying the TMA bytes + one arrival per dequant warp (of both CTAs)
-            mbar_init(bar(kBarFull + i), 1 + (PAIR ? 16 : 8));
+            // (every dequant warp counts twice in a normal stage, where one group of 8 produces; once in the rank-update
+            // stage, where both groups produce)
+            mbar_init(bar(kBarFull + i), 1 + (PAIR ? 32 : 16));
             mbar_init(bar(kBarEmpty + i), 1);                    // tcgen05.commit of the stage's MMAs
         }
         mbar_init(bar(kBarAcc), 1);
@@ -218,8 +222,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 }
             }
             if (ok && do_lora) {
+                // rank-update stage: both operand tiles are built by the dequant warps; the producer only adds the
+                // arrival that stands for the TMA bytes in the other stages
                 ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
-                if (ok) load_act_stage(&p.tm_lora, 0, sbase + kOffX + xs.idx * kXStageBytes, bar(kBarFull + xs.idx));
+                if (ok && leader) mbar_arrive(bar(kBarFull + xs.idx));
             }
         }
     } else if (warp == 1) {
@@ -272,10 +278,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         const int nu = u1 - u0;
         bool ok = true;
         // "operand stage ready": on the barrier of the CTA that issues the MMAs
-        auto signal_a_full = [&](int ai) {
+        auto signal_a_full = [&](int ai, uint32_t count) {
             if (lane == 0) {
-                if (PAIR && !leader) mbar_arrive_cluster(mapa_cluster(bar(kBarFull + ai), 0));
-                else mbar_arrive(bar(kBarFull + ai));
+                if (PAIR && !leader) mbar_arrive_cluster_n(mapa_cluster(bar(kBarFull + ai), 0), count);
+                else mbar_arrive_n(bar(kBarFull + ai), count);
             }
         };
         // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i & 1
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                                                half, grp, a_addr + dst_off, row & 7, chunk0);
             fence_proxy_async_smem();
             __syncwarp();
-            signal_a_full(ai);
+            signal_a_full(ai, 2);
             if (dt == 0) trace(4 + 3 * g, n);
             return true;
         };
@@ -321,13 +327,36 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 if (lane == 0) mbar_arrive(bar(kBarRawEmpty + ri));
             }
         }
-        if (ok && do_lora && g == 0) {
+        if (ok && do_lora) {
+            // rank-update stage: group 0 builds the weight-side tile from B (forward) / A (backward), group 1 the
+            // activation-side tile from the fp32 low-rank activations, both rounded to T16 here
             const int n = (BWD ? 1 : 2) * nu;
             const int ai = n & (kNumA - 1);
             ok = mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
             if (ok) {
                 const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
-                if (!BWD) {
+                if (g == 1) {
+                    // one thread per token row of this CTA's activation tile: rank_pad/8 chunks of a 128-byte row
+                    const uint32_t x_addr = sbase + kOffX + ai * kXStageBytes;
+                    for (int i = 0; i < n_mma; i++) {
+                        const int ntok = min(256, tb - 256 * i);
+                        const int rows = PAIR ? (ntok >> 1) : ntok;
+                        if (dt < rows) {
+                            const int t = tok0 + 256 * i + (PAIR ? (int)crank * rows : 0) + dt;
+                            const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + dt * 128);
+                            for (int j = 0; j * 8 < rank_pad; j++) {
+                                float v[8];
+#pragma unroll
+                                for (int q = 0; q < 8; q++) {
+                                    const int r = 8 * j + q;
+                                    v[q] = (r < p.rank && t < p.T) ? p.lora_act[(int64_t)t * p.rank + r] * p.lora_scale : 0.f;
+                                }
+                                st_shared_v4(row_addr + (uint32_t)((j ^ (dt & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
+                                             pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
+                            }
+                        }
+                    }
+                } else if (!BWD) {
                     // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
                     const int row = dt & 127, nn = tile * kTileW + row;
                     for (int j = dt >> 7; j * 8 < rank_pad; j += 2) {
@@ -353,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                signal_a_full(ai);
+                signal_a_full(ai, 1);
             }
         }
         // epilogue: TMEM lane = weight row / column of this tile, TMEM column = token
@@ -538,14 +567,11 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
         return cudaErrorInvalidValue;
     }
     p.rank = 0;
-    p.tm_lora = p.tm_act;
-    if (L.rank > 0 && L.lora_act16 && L.lora_w) {
-        if (!encode_2d(&p.tm_lora, dt, 2, L.lora_act16, 64, (uint64_t)L.T, 128, 64, (uint32_t)p.t_box, CU_TENSOR_MAP_SWIZZLE_128B)) {
-            if (err) *err = "cuTensorMapEncodeTiled failed for the low-rank operand";
-            return cudaErrorInvalidValue;
-        }
+    if (L.rank > 0 && L.lora_act && L.lora_w) {
         p.rank = L.rank;
         p.lora_w = L.lora_w;
+        p.lora_act = L.lora_act;
+        p.lora_scale = L.lora_scale;
         p.lora_flag = L.lora_flag;
     }
     p.tm_hdr = w->tm_hdr;
