@@ -176,6 +176,15 @@ def run_ours(args) -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries exactly one JSON line: anything a library prints there meanwhile (NCCL's version banner) is sent
+    # to stderr, and the line itself is written to the saved descriptor
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(text: str) -> None:
+        os.write(real_stdout, (text + "\n").encode())
+
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the projection path has no CPU implementation")
     torch.cuda.set_device(local_rank)
@@ -376,8 +385,13 @@ def run_ours(args) -> None:
                              "sample": f"one pass over projections {','.join(names)} ({step_flops(names) / 1e9:.1f} GFLOP), fp32 OpenMP"},
             "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
+    if graph is not None:
+        graph.reset()          # a communicator cannot be torn down while a captured graph still references it
+        graph = None
+    torch.cuda.synchronize()
     if world > 1:
+        dist.barrier()
         eng.dp_finalize()
         dist.destroy_process_group()
     eng.close()

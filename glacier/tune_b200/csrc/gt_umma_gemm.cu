@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -42,21 +43,26 @@ constexpr int kTileW = 128;        // weight rows (forward) / columns (backward)
 constexpr int kChunk = 64;         // contraction elements per operand stage (one 128-byte row)
 constexpr int kMaxTok = 512;       // tokens per CTA = TMEM columns
 constexpr int kAStageBytes = kTileW * kChunk * 2;   // 16 KiB
-constexpr int kXBytes = 131072;    // activation ring: 4 x 32 KiB (a CTA holds at most 256 token rows per stage)
-constexpr int kRawStageBytes = 16384;
-constexpr int kNumA = 4, kNumRaw = 2;
+constexpr int kNumA = 4;            // operand stages (dequantized weight tile + activation tile)
+constexpr int kXStageBytes = 32768; // activation tile of a stage: a CTA holds at most 256 token rows of 128 bytes
+constexpr int kXBytes = kNumA * kXStageBytes;
+// Raw (still packed) weight blocks come from HBM, whose latency is several operand-stage times: the raw ring gets
+// all the shared memory that is left, cut into as many stages as the format's stage size allows (up to 8).
+constexpr int kRawBudget = 32768;
+constexpr int kMaxRaw = 8;
 constexpr int kDequantWarps = 16;   // two groups of 8
-constexpr int kThreads = 32 * (2 + kDequantWarps);
+constexpr int kThreads = 32 * (3 + kDequantWarps);   // + producer warp, + two MMA-issuer warps (1 and 18)
 
 constexpr int kOffX = 0;
 constexpr int kOffA = kOffX + kXBytes;
 constexpr int kOffRaw = kOffA + kNumA * kAStageBytes;
-constexpr int kOffBar = kOffRaw + kNumRaw * kRawStageBytes;
+constexpr int kOffBar = kOffRaw + kRawBudget;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for 1024-byte alignment
 
 // barrier slots (8 bytes each) inside the kOffBar region
 // (an operand stage = dequantized weight tile + activation tile; both share one slot index and one full/empty pair)
-constexpr int kBarRawFull = 0, kBarRawEmpty = 2, kBarFull = 4, kBarEmpty = 8, kBarAcc = 12, kNumBars = 13;
+constexpr int kBarRawFull = 0, kBarRawEmpty = kMaxRaw, kBarFull = 2 * kMaxRaw, kBarEmpty = kBarFull + kNumA,
+              kBarAcc = kBarEmpty + kNumA, kBarTurn = kBarAcc + 1, kNumBars = kBarTurn + 2;
 constexpr int kOffTmemSlot = kNumBars * 8;       // u32
 constexpr int kOffAbort = kOffTmemSlot + 4;      // int
 
@@ -98,15 +104,18 @@ struct Ring {
 //               the activation bytes each SM pulls from L2 per FLOP.  The even-ranked CTA (leader) issues the MMAs;
 //               its "full" barriers collect the arrivals and TMA bytes of both CTAs, and its commits release the
 //               stages in both.
-template <int QT, typename T16, bool BWD, bool PAIR>
+template <int QT, typename T16, bool BWD, bool PAIR, int MTOK>
 __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant__ Params p) {
     using QS = QuantStage<QT>;
     constexpr int H = QS::kHdrBytes, Q1 = QS::kQ1Bytes;
     constexpr int kRows = BWD ? 64 : 128;      // weight rows per raw stage
     constexpr int kSub = BWD ? 1 : 2;          // operand stages produced per raw stage
     constexpr int kNumX = kNumA;
-    constexpr int kXStageBytes = kXBytes / kNumX;
-    constexpr int kMmaSlotBytes = PAIR ? 128 * 128 : 256 * 128;   // smem bytes of one MMA's activation rows in a stage
+    constexpr int kRawStageBytes = (kRows * (H + 64 + Q1) + 1023) & ~1023;
+    constexpr int kNumRaw = kRawBudget / kRawStageBytes < kMaxRaw ? kRawBudget / kRawStageBytes : kMaxRaw;
+    // MTOK = token columns per MMA (the accumulator is cut into 512 / MTOK independent tiles that the issuer visits
+    // round-robin); kMmaSlotBytes = smem bytes of one MMA's activation rows in a stage
+    constexpr int kMmaSlotBytes = (PAIR ? MTOK / 2 : MTOK) * 128;
     constexpr uint32_t kFmt = std::is_same<T16, __half>::value ? 0u : 1u;   // UMMA operand format: 0 f16, 1 bf16
 
     extern __shared__ uint8_t smem_dyn[];
@@ -126,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     // token columns of this CTA's accumulator: multiple of 16 (single) / 32 (pair, 16 per CTA half)
     const int tb = PAIR ? min(kMaxTok, (tok_left + 31) & ~31) : min(kMaxTok, (tok_left + 15) & ~15);
     const int n_box = (tb + p.t_box - 1) / p.t_box;             // single-CTA mode: TMA boxes per stage
-    const int n_mma = (tb + 255) >> 8;
+    const int n_mma = (tb + MTOK - 1) / MTOK;
     const int u0 = (int)((int64_t)p.units * split / p.splits);
     const int u1 = (int)((int64_t)p.units * (split + 1) / p.splits);
     const int rank_pad = (p.rank + 15) & ~15;
@@ -144,7 +153,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             mbar_init(bar(kBarFull + i), 1 + (PAIR ? 32 : 16));
             mbar_init(bar(kBarEmpty + i), 1);                    // tcgen05.commit of the stage's MMAs
         }
-        mbar_init(bar(kBarAcc), 1);
+        mbar_init(bar(kBarAcc), 2);        // both MMA issuers commit to it
+        mbar_init(bar(kBarTurn + 0), 1);   // issuer 1 has queued its stage: issuer 0 may queue the next one
+        mbar_init(bar(kBarTurn + 1), 1);   // and the other way round (stage order = accumulation order, run to run)
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&p.tm_act);
@@ -174,11 +185,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     auto load_act_stage = [&](const CUtensorMap *tm, int c0, uint32_t xdst, uint32_t xbar_local) {
         if (PAIR) {
             // leader arms the barrier for the bytes of both CTAs; each CTA loads its half of every MMA's tokens
-            if (leader) mbar_arrive_expect_tx(xbar_local, (uint32_t)(2 * n_mma * 128 * 128));
+            if (leader) mbar_arrive_expect_tx(xbar_local, (uint32_t)(2 * n_mma * (MTOK / 2) * 128));
             const uint32_t lbar = mapa_cluster(xbar_local, 0);
             for (int i = 0; i < n_mma; i++) {
-                const int ntok = min(256, tb - 256 * i);
-                tma_load_2d_pair(xdst + i * kMmaSlotBytes, tm, c0, tok0 + 256 * i + (int)crank * (ntok >> 1), lbar);
+                const int ntok = min(MTOK, tb - MTOK * i);
+                tma_load_2d_pair(xdst + i * kMmaSlotBytes, tm, c0, tok0 + MTOK * i + (int)crank * (ntok >> 1), lbar);
             }
         } else {
             mbar_arrive_expect_tx(xbar_local, (uint32_t)(n_box * p.t_box * 128));
@@ -228,13 +239,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 if (ok && leader) mbar_arrive(bar(kBarFull + xs.idx));
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
+    } else if (warp == 1 || warp == kThreads / 32 - 1) {
+        // ------------------------------------------------------------------ two MMA issuers (leader CTA only in pair mode)
+        // Issuing is blocking (the queue in front of the tensor pipe is short) and every stage costs a barrier wait,
+        // a fence and a commit: two threads take alternate stages, so one waits for its next stage while the other
+        // keeps the pipe fed.  They hand a turn token back and forth, so stages are queued in order and the fp32
+        // accumulation order does not change from run to run.  tcgen05.commit tracks the MMAs of the committing thread, so each releases its own stages.
         if (lane == 0 && leader) {
+            const int who = warp == 1 ? 0 : 1;
             bool ok = true;
             const uint32_t a_mn = BWD ? 1u : 0u;
             auto wait_full = [&](int n, int code) -> bool {
-                const int slot = kBarFull + (n & (kNumA - 1));
+                const int slot = kBarFull + (n % kNumA);
                 const uint32_t phase = (uint32_t)(n / kNumA) & 1u;
                 const bool r = PAIR ? mbar_wait_bounded_cluster(bar(slot), phase, abort_flag, p.status, code)
                                     : mbar_wait_bounded(bar(slot), phase, abort_flag, p.status, code);
@@ -243,29 +259,37 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             };
             const int n_main = (u1 - u0) * kSub;
             const int n_total = n_main + (do_lora ? 1 : 0);
-            for (int n = 0; n < n_total && ok; n++) {
+            for (int n = who; n < n_total && ok; n += 2) {
                 ok = wait_full(n, kCodeMma + 1);
                 if (!ok) break;
-                const int si = n & (kNumA - 1);
+                const int si = n % kNumA;
                 const uint32_t a_addr = sbase + kOffA + si * kAStageBytes;
                 const uint32_t x_addr = sbase + kOffX + si * kXStageBytes;
                 const int ksteps = n < n_main ? 4 : (rank_pad >> 4);
-                trace(8, n);
+                if (n > 0) {
+                    // take the turn: the other issuer has queued stage n - 1 (by now this thread has already waited for
+                    // its own operands, which is the latency the second issuer hides)
+                    const uint32_t turn_phase = (uint32_t)(who == 1 ? (n >> 1) : ((n >> 1) - 1)) & 1u;
+                    ok = mbar_wait_bounded(bar(kBarTurn + who), turn_phase, abort_flag, p.status, kCodeMma + 5);
+                    if (!ok) break;
+                }
+                if (who == 0) trace(8, n);
                 // k-step-major order: consecutive MMAs alternate between the accumulators (measured faster than
                 // finishing one accumulator's k-steps first)
                 for (int ks = 0; ks < ksteps; ks++) {
                     const uint64_t adesc = BWD ? umma_desc_sw128(a_addr + ks * 2048, 8192, 1024)
                                                : umma_desc_sw128(a_addr + ks * 32, 16, 1024);
                     for (int i = 0; i < n_mma; i++) {
-                        const int ntok = min(256, tb - 256 * i);
+                        const int ntok = min(MTOK, tb - MTOK * i);
                         const uint64_t bdesc = umma_desc_sw128(x_addr + i * kMmaSlotBytes + ks * 32, 16, 1024);
                         const uint32_t acc = (n == 0 && ks == 0) ? 0u : 1u;
-                        if (PAIR) umma_f16_ss_pair(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 256), acc);
-                        else umma_f16_ss(tmem_base + i * 256, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 128), acc);
+                        if (PAIR) umma_f16_ss_pair(tmem_base + i * MTOK, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 256), acc);
+                        else umma_f16_ss(tmem_base + i * MTOK, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 128), acc);
                     }
                 }
                 if (PAIR) umma_commit_pair(bar(kBarEmpty + si)); else umma_commit(bar(kBarEmpty + si));
-                trace(9, n);
+                mbar_arrive(bar(kBarTurn + (who ^ 1)));
+                if (who == 0) trace(9, n);
             }
             if (ok) {
                 if (PAIR) umma_commit_pair(bar(kBarAcc)); else umma_commit(bar(kBarAcc));
@@ -284,9 +308,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 else mbar_arrive_n(bar(kBarFull + ai), count);
             }
         };
-        // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i & 1
+        // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i % kNumRaw
         auto produce = [&](int n, const uint8_t *rs, int row, int grp, int half, uint32_t dst_off, int chunk0) -> bool {
-            const int ai = n & (kNumA - 1);
+            const int ai = n % kNumA;
             if (!mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 2))
                 return false;
             if (dt == 0) trace(3 + 3 * g, n >> (BWD ? 0 : 0));
@@ -304,8 +328,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             // raw stage = 128 rows x half block; group g dequantizes its 64-column half (sub-stage g)
             const int row = dt & 127, hn = dt >> 7;
             for (int ui = 0; ui < nu && ok; ui++) {
-                const int ri = ui & 1;
-                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui >> 1) & 1u, abort_flag, p.status, kCodeDequant + 1);
+                const int ri = ui % kNumRaw;
+                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui / kNumRaw) & 1u, abort_flag, p.status, kCodeDequant + 1);
                 if (!ok) break;
                 if (dt == 0) trace(2 + 3 * g, 2 * ui + g);
                 const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
@@ -317,8 +341,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             // raw stage = 64 rows x half block = one operand stage; the groups take alternate stages
             const int row = dt & 63, grp = dt >> 6;
             for (int ui = g; ui < nu && ok; ui += 2) {
-                const int ri = ui & 1;
-                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui >> 1) & 1u, abort_flag, p.status, kCodeDequant + 1);
+                const int ri = ui % kNumRaw;
+                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui / kNumRaw) & 1u, abort_flag, p.status, kCodeDequant + 1);
                 if (!ok) break;
                 if (dt == 0) trace(2 + 3 * g, ui);
                 const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
@@ -331,7 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             // rank-update stage: group 0 builds the weight-side tile from B (forward) / A (backward), group 1 the
             // activation-side tile from the fp32 low-rank activations, both rounded to T16 here
             const int n = (BWD ? 1 : 2) * nu;
-            const int ai = n & (kNumA - 1);
+            const int ai = n % kNumA;
             ok = mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
             if (ok) {
                 const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
@@ -339,10 +363,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     // one thread per token row of this CTA's activation tile: rank_pad/8 chunks of a 128-byte row
                     const uint32_t x_addr = sbase + kOffX + ai * kXStageBytes;
                     for (int i = 0; i < n_mma; i++) {
-                        const int ntok = min(256, tb - 256 * i);
+                        const int ntok = min(MTOK, tb - MTOK * i);
                         const int rows = PAIR ? (ntok >> 1) : ntok;
                         if (dt < rows) {
-                            const int t = tok0 + 256 * i + (PAIR ? (int)crank * rows : 0) + dt;
+                            const int t = tok0 + MTOK * i + (PAIR ? (int)crank * rows : 0) + dt;
                             const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + dt * 128);
                             for (int j = 0; j * 8 < rank_pad; j++) {
                                 float v[8];
@@ -464,10 +488,10 @@ bool encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, int esize, const void *b
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int QT, typename T16, bool BWD, bool PAIR>
+template <int QT, typename T16, bool BWD, bool PAIR, int MTOK>
 cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
     static bool configured = false;
-    auto kern = k_umma_gemm<QT, T16, BWD, PAIR>;
+    auto kern = k_umma_gemm<QT, T16, BWD, PAIR, MTOK>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
@@ -494,9 +518,10 @@ template <int QT, typename T16, bool BWD>
 cudaError_t launch_one(const Params &p, dim3 grid, bool pair, cudaStream_t s) {
     if (pair) {
         grid.x = (grid.x + 1) & ~1u;      // a pair owns two adjacent tiles; a padding tile is all out of range
-        return launch_variant<QT, T16, BWD, true>(p, grid, s);
+        if (p.t_box == 64) return launch_variant<QT, T16, BWD, true, 128>(p, grid, s);
+        return launch_variant<QT, T16, BWD, true, 256>(p, grid, s);
     }
-    return launch_variant<QT, T16, BWD, false>(p, grid, s);
+    return launch_variant<QT, T16, BWD, false, 256>(p, grid, s);
 }
 
 }  // namespace
@@ -556,7 +581,9 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
     // weight-streaming bound and stay on single CTAs
     const bool pair = tmax >= 256;
     const int tb = pair ? (tmax + 31) & ~31 : (tmax + 15) & ~15;
-    p.t_box = pair ? 128 : (tb < 128 ? tb : 128);
+    // pair mode: TMA box rows = half of an MMA's token columns (64 with four 128-column accumulators)
+    static const int mtok = getenv("GT_MMA_TOK") ? atoi(getenv("GT_MMA_TOK")) : 256;
+    p.t_box = pair ? (mtok == 128 ? 64 : 128) : (tb < 128 ? tb : 128);
     int tc = 32;
     while (tc < tb) tc <<= 1;
     p.tmem_cols = tc;
