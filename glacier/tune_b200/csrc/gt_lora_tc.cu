@@ -42,40 +42,51 @@ constexpr int TC = 128;    // columns (of K or N) per tile
 constexpr int GS = TC + 4; // smem row stride of the activation tile (words): rows 4 banks apart
 constexpr int RS = 24;     // smem row stride of the 16-wide rank tiles (words)
 
-// Stage a [TT x TC] fp32 tile of src[T, ld] (rows t0.., columns c0..) as TF32 in shared memory, and optionally
-// write its 16-bit rounding to dst16.  256 threads; float4 loads when the tile is interior and aligned.
-__device__ __forceinline__ void stage_tile(const float *__restrict__ src, int T, int ncols, int t0, int t_end, int c0,
-                                           uint32_t (*tile)[GS], uint16_t *__restrict__ dst16, int ld16, int fp16, int tid) {
+constexpr int NI = (TT * TC / 4) / 256;     // float4 loads per thread and tile
+
+// A [TT x TC] fp32 tile of src[T, ncols] (rows t0.. below t_end, columns c0..) moves in two steps so that a block can
+// have the next tile's loads in flight while it computes on the current one:
+//   tile_load   global -> registers (float4 per thread when the tile is interior and aligned)
+//   tile_store  registers -> shared memory as TF32, and optionally the 16-bit rounding to dst16 in global memory
+__device__ __forceinline__ void tile_load(const float *__restrict__ src, int ncols, int t0, int t_end, int c0, float4 (&v)[NI], int tid) {
     const bool vec = (ncols & 3) == 0 && c0 + TC <= ncols;
 #pragma unroll
-    for (int i = 0; i < (TT * TC / 4) / 256; i++) {
+    for (int i = 0; i < NI; i++) {
         const int idx = tid + i * 256;
         const int r = idx / (TC / 4), c = (idx % (TC / 4)) * 4;
         const int t = t0 + r;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < t_end) {
             const float *p = src + (int64_t)t * ncols + c0 + c;
             if (vec) {
-                v = *reinterpret_cast<const float4 *>(p);
+                v[i] = __ldg(reinterpret_cast<const float4 *>(p));
             } else {
-                if (c0 + c < ncols) v.x = p[0];
-                if (c0 + c + 1 < ncols) v.y = p[1];
-                if (c0 + c + 2 < ncols) v.z = p[2];
-                if (c0 + c + 3 < ncols) v.w = p[3];
-            }
-            if (dst16) {
-                uint16_t *q = dst16 + (int64_t)t * ld16 + c0 + c;
-                if (c0 + c + 3 < ld16 && (ld16 & 3) == 0) {
-                    uint2 o = make_uint2(pack16(v.x, v.y, fp16), pack16(v.z, v.w, fp16));
-                    *reinterpret_cast<uint2 *>(q) = o;
-                } else {
-                    const float e[4] = {v.x, v.y, v.z, v.w};
-                    for (int j = 0; j < 4; j++)
-                        if (c0 + c + j < ld16) q[j] = (uint16_t)(pack16(e[j], 0.f, fp16) & 0xFFFFu);
-                }
+                if (c0 + c < ncols) v[i].x = p[0];
+                if (c0 + c + 1 < ncols) v[i].y = p[1];
+                if (c0 + c + 2 < ncols) v[i].z = p[2];
+                if (c0 + c + 3 < ncols) v[i].w = p[3];
             }
         }
-        *reinterpret_cast<uint4 *>(&tile[r][c]) = make_uint4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
+    }
+}
+__device__ __forceinline__ void tile_store(const float4 (&v)[NI], int t0, int t_end, int c0, uint32_t (*tile)[GS],
+                                           uint16_t *__restrict__ dst16, int ld16, int fp16, int tid) {
+#pragma unroll
+    for (int i = 0; i < NI; i++) {
+        const int idx = tid + i * 256;
+        const int r = idx / (TC / 4), c = (idx % (TC / 4)) * 4;
+        const int t = t0 + r;
+        if (dst16 && t < t_end) {
+            uint16_t *q = dst16 + (int64_t)t * ld16 + c0 + c;
+            if (c0 + c + 3 < ld16 && (ld16 & 3) == 0) {
+                *reinterpret_cast<uint2 *>(q) = make_uint2(pack16(v[i].x, v[i].y, fp16), pack16(v[i].z, v[i].w, fp16));
+            } else {
+                const float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                for (int j = 0; j < 4; j++)
+                    if (c0 + c + j < ld16) q[j] = (uint16_t)(pack16(e[j], 0.f, fp16) & 0xFFFFu);
+            }
+        }
+        *reinterpret_cast<uint4 *>(&tile[r][c]) = make_uint4(to_tf32(v[i].x), to_tf32(v[i].y), to_tf32(v[i].z), to_tf32(v[i].w));
     }
 }
 
@@ -91,7 +102,9 @@ __global__ void __launch_bounds__(256) k_lora_xa_tc(const float *__restrict__ X,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.x * TT, k0 = blockIdx.y * TC;
     const int rc = min(16, R - r0);
-    stage_tile(X, T, K, t0, T, k0, Xs, r0 == 0 ? x16 : nullptr, ldx16, fp16, tid);
+    float4 v[NI];
+    tile_load(X, K, t0, T, k0, v, tid);
+    tile_store(v, t0, T, k0, Xs, r0 == 0 ? x16 : nullptr, ldx16, fp16, tid);
     for (int i = tid; i < TC * 16; i += 256) {
         const int k = i >> 4, r = i & 15;
         As[k][r] = (k0 + k < K && r < rc) ? to_tf32(A[(int64_t)(k0 + k) * R + r0 + r]) : 0u;
@@ -139,9 +152,12 @@ __global__ void __launch_bounds__(256) k_lora_dy_tc(const float *__restrict__ dY
     float accB[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;      // dLow tiles
     const int cb = warp * 16;                                  // dB: this warp's two 8-column n-tiles
+    float4 v[NI];
+    tile_load(dY, N, tg0, tg1, c0, v, tid);
     for (int ts = tg0; ts < tg1; ts += TT) {
         __syncthreads();
-        stage_tile(dY, T, N, ts, tg1, c0, Gs, r0 == 0 ? dy16 : nullptr, ld16, fp16, tid);
+        tile_store(v, ts, tg1, c0, Gs, r0 == 0 ? dy16 : nullptr, ld16, fp16, tid);
+        if (ts + TT < tg1) tile_load(dY, N, ts + TT, tg1, c0, v, tid);     // next tile's loads fly during the MMAs below
         for (int i = tid; i < TT * 16; i += 256) {
             const int tt = i >> 4, r = i & 15;
             Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(low[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
@@ -204,9 +220,12 @@ __global__ void __launch_bounds__(256) k_lora_da_tc(const float *__restrict__ X,
     const int rc = min(16, R - r0);
     const int m0 = warp * 16;
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float4 v[NI];
+    tile_load(X, K, tg0, tg1, k0, v, tid);
     for (int ts = tg0; ts < tg1; ts += TT) {
         __syncthreads();
-        stage_tile(X, T, K, ts, tg1, k0, Xs, nullptr, 0, 0, tid);
+        tile_store(v, ts, tg1, k0, Xs, nullptr, 0, 0, tid);
+        if (ts + TT < tg1) tile_load(X, K, ts + TT, tg1, k0, v, tid);      // next tile's loads fly during the MMAs below
         for (int i = tid; i < TT * 16; i += 256) {
             const int tt = i >> 4, r = i & 15;
             Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(dLow[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
