@@ -792,8 +792,12 @@ int gt_dp_allreduce(gt_engine *e, float *g_dev, int64_t count, float scale) {
     GT_CUDA(cudaSetDevice(e->device));
     if (e->comm) {
         NcclApi &n = nccl_api();
-        ncclResult_t r = n.AllReduce(g_dev, g_dev, (size_t)count, ncclFloat, ncclSum, e->comm, e->stream);
+        // scale == 1/world is the common case (gradient averaging): let the collective average, no extra pass
+        const float inv = 1.0f / (float)e->dp_world;
+        const bool avg = scale == inv;
+        ncclResult_t r = n.AllReduce(g_dev, g_dev, (size_t)count, ncclFloat, avg ? ncclAvg : ncclSum, e->comm, e->stream);
         if (r != ncclSuccess) return fail(GT_ERR_NCCL, "ncclAllReduce: %s", n.GetErrorString(r));
+        if (avg) return GT_OK;
     }
     if (scale != 1.0f) GT_CUDA(launch_scale_clip(g_dev, count, scale, 0.0, e->clip, e->stream));
     return GT_OK;

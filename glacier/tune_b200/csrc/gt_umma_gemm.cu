@@ -136,6 +136,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     const int tb = PAIR ? min(kMaxTok, (tok_left + 31) & ~31) : min(kMaxTok, (tok_left + 15) & ~15);
     const int n_box = (tb + p.t_box - 1) / p.t_box;             // single-CTA mode: TMA boxes per stage
     const int n_mma = (tb + MTOK - 1) / MTOK;
+    // Few tokens (single-CTA mode): the four k-steps of a stage go to separate accumulators, so they do not wait on
+    // each other's accumulation (a dependent MMA costs ~250 clocks whatever its size); the epilogue adds them up.
+    const int acc_stride = (tb + 31) & ~31;
+    const int n_acc = PAIR ? 1 : (acc_stride <= 128 ? 4 : (acc_stride <= 256 ? 2 : 1));
     const int u0 = (int)((int64_t)p.units * split / p.splits);
     const int u1 = (int)((int64_t)p.units * (split + 1) / p.splits);
     const int rank_pad = (p.rank + 15) & ~15;
@@ -259,12 +263,25 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             };
             const int n_main = (u1 - u0) * kSub;
             const int n_total = n_main + (do_lora ? 1 : 0);
+            // Everything an MMA needs is precomputed: the issuing thread is one thread, and at ~5 clocks per dependent
+            // instruction a few dozen instructions per MMA would cost more than the MMA itself.
+            // descriptor = (lo, hi): lo = (addr >> 4) | (LBO >> 4) << 16, hi = (SBO >> 4) | version 1 << 14 | SWIZZLE_128B << 29
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            constexpr uint32_t kALoField = (BWD ? (8192u >> 4) : 1u) << 16;     // MN-major: LBO = stride between 64-column images
+            constexpr uint32_t kAStep = (BWD ? 2048u : 32u) >> 4;               // per k-step advance of the A operand
+            constexpr int kMaxMma = 512 / MTOK;
+            uint32_t idesc[kMaxMma];
+#pragma unroll
+            for (int i = 0; i < kMaxMma; i++) {
+                const int ntok = max(16, min(MTOK, tb - MTOK * i));
+                idesc[i] = umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, PAIR ? 256u : 128u);
+            }
             for (int n = who; n < n_total && ok; n += 2) {
                 ok = wait_full(n, kCodeMma + 1);
                 if (!ok) break;
                 const int si = n % kNumA;
-                const uint32_t a_addr = sbase + kOffA + si * kAStageBytes;
-                const uint32_t x_addr = sbase + kOffX + si * kXStageBytes;
+                const uint32_t a_lo0 = (((sbase + kOffA + si * kAStageBytes) & 0x3FFFFu) >> 4) | kALoField;
+                const uint32_t b_lo0 = (((sbase + kOffX + si * kXStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
                 const int ksteps = n < n_main ? 4 : (rank_pad >> 4);
                 if (n > 0) {
                     // take the turn: the other issuer has queued stage n - 1 (by now this thread has already waited for
@@ -274,17 +291,25 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     if (!ok) break;
                 }
                 if (who == 0) trace(8, n);
+                const uint32_t first = n == 0 ? 0u : 1u;     // the very first MMA into an accumulator overwrites it
                 // k-step-major order: consecutive MMAs alternate between the accumulators (measured faster than
                 // finishing one accumulator's k-steps first)
-                for (int ks = 0; ks < ksteps; ks++) {
-                    const uint64_t adesc = BWD ? umma_desc_sw128(a_addr + ks * 2048, 8192, 1024)
-                                               : umma_desc_sw128(a_addr + ks * 32, 16, 1024);
-                    for (int i = 0; i < n_mma; i++) {
-                        const int ntok = min(MTOK, tb - MTOK * i);
-                        const uint64_t bdesc = umma_desc_sw128(x_addr + i * kMmaSlotBytes + ks * 32, 16, 1024);
-                        const uint32_t acc = (n == 0 && ks == 0) ? 0u : 1u;
-                        if (PAIR) umma_f16_ss_pair(tmem_base + i * MTOK, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 256), acc);
-                        else umma_f16_ss(tmem_base + i * MTOK, adesc, bdesc, umma_idesc_f16(kFmt, a_mn, 0u, (uint32_t)ntok, 128), acc);
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) {
+                    if (ks < ksteps) {
+                        const uint32_t a_lo = a_lo0 + ks * kAStep;
+                        if (PAIR) {
+#pragma unroll
+                            for (int i = 0; i < kMaxMma; i++)
+                                if (i < n_mma)
+                                    umma_f16_ss_lohi<true>(tmem_base + i * MTOK, a_lo, kDescHi, b_lo0 + i * (kMmaSlotBytes >> 4) + ks * 2,
+                                                           kDescHi, idesc[i], ks == 0 ? first : 1u);
+                        } else {
+                            // few tokens: one MMA per k-step, each k-step into its own partial accumulator
+                            const int a = ks % n_acc;
+                            umma_f16_ss_lohi<false>(tmem_base + a * acc_stride, a_lo, kDescHi, b_lo0 + ks * 2, kDescHi, idesc[0],
+                                                    ks < n_acc ? first : 1u);
+                        }
                     }
                 }
                 if (PAIR) umma_commit_pair(bar(kBarEmpty + si)); else umma_commit(bar(kBarEmpty + si));
@@ -424,6 +449,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
+                for (int a = 1; a < n_acc; a++) {      // partial accumulators of the few-token mode
+                    uint32_t w2[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * acc_stride + c * 32), w2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w2[j]));
+                }
                 if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -579,13 +611,17 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
     const int tmax = L.T < kMaxTok ? L.T : kMaxTok;
     // CTA pairs pay off once the activation tile is the bulk of what an SM pulls from L2; small token counts are
     // weight-streaming bound and stay on single CTAs
-    const bool pair = tmax >= 256;
+    static const int pair_min = getenv("GT_PAIR_MIN") ? atoi(getenv("GT_PAIR_MIN")) : 256;
+    const bool pair = tmax >= pair_min;
     const int tb = pair ? (tmax + 31) & ~31 : (tmax + 15) & ~15;
     // pair mode: TMA box rows = half of an MMA's token columns (64 with four 128-column accumulators)
     static const int mtok = getenv("GT_MMA_TOK") ? atoi(getenv("GT_MMA_TOK")) : 256;
     p.t_box = pair ? (mtok == 128 ? 64 : 128) : (tb < 128 ? tb : 128);
+    // single-CTA mode keeps up to four partial accumulators side by side (see n_acc in the kernel)
+    const int stride = (tb + 31) & ~31;
+    const int need_cols = pair ? tb : (stride <= 128 ? 4 * stride : (stride <= 256 ? 2 * stride : stride));
     int tc = 32;
-    while (tc < tb) tc <<= 1;
+    while (tc < need_cols) tc <<= 1;
     p.tmem_cols = tc;
     const CUtensorMapDataType dt = L.fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     if (!encode_2d(&p.tm_act, dt, 2, L.act16, (uint64_t)cols, (uint64_t)L.T, (uint64_t)L.ld_act * 2, 64, (uint32_t)p.t_box,
