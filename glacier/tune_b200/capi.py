@@ -24,7 +24,7 @@ EXPORTS = [
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
-    "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
+    "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
 
@@ -81,6 +81,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
     lib.gt_debug_set_trace.argtypes = [C.c_void_p, C.c_void_p]
+    lib.gt_debug_wait_selftest.argtypes = [C.c_void_p, C.c_int64]
     lib.gt_profile_enable.argtypes = [C.c_void_p, C.c_int]
     lib.gt_profile_read.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double),
                                     C.POINTER(C.c_int64), C.c_int]
@@ -206,6 +207,9 @@ class Engine:
         norm = C.c_double()
         _check(self.lib.gt_grads_scale_clip(self.h, _ptr(g_dev)[0], g_dev.numel(), pre_scale, max_norm, C.byref(norm)))
         return norm.value
+
+    def wait_selftest(self, limit_cycles: int = 2_000_000):
+        _check(self.lib.gt_debug_wait_selftest(self.h, limit_cycles))
 
     def set_trace(self, dev_buf=None):
         _check(self.lib.gt_debug_set_trace(self.h, None if dev_buf is None else C.c_void_p(dev_buf.data_ptr())))

@@ -370,6 +370,15 @@ int gt_sync(gt_engine *e) {
     return check_status(e);
 }
 
+int gt_debug_wait_selftest(gt_engine *e, int64_t limit_cycles) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    if (limit_cycles <= 0 || limit_cycles > 2000000000ll) return fail(GT_ERR_INVALID, "limit must be in (0, 2e9] cycles");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    GT_CUDA(launch_bounded_wait_selftest(e->status, limit_cycles, e->stream));
+    return check_status(e);       // expected: GT_ERR_KERNEL carrying code 999
+}
+
 int gt_debug_set_trace(gt_engine *e, void *dev_buf) {
     if (!e) return fail(GT_ERR_INVALID, "engine is null");
     std::lock_guard<std::mutex> lk(e->mu);

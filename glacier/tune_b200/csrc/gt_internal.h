@@ -87,6 +87,7 @@ int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count);
 cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err);
 cudaError_t umma_init_weight_maps(WeightDev *w, const char **err);
 bool umma_available();
+cudaError_t launch_bounded_wait_selftest(int *status, long long limit_cycles, cudaStream_t s);
 
 
 // ---- views of the opaque C-ABI handles for translation units outside gt_engine.cu ---------------------------

@@ -488,6 +488,25 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     }
 }
 
+// A wait that nothing will ever satisfy, with a short limit: exercises the give-up path of mbar_wait_bounded (status
+// word written, flag raised, kernel returns normally) without hanging or faulting the device.
+__global__ void k_bounded_wait_selftest(int *status, long long limit_cycles) {
+    __shared__ __align__(8) unsigned long long bar_mem;
+    __shared__ int abort_flag;
+    const uint32_t b = smem_u32(&bar_mem);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait_bounded(b, 0u, &abort_flag, status, 999, limit_cycles);
+    __syncthreads();
+    if (threadIdx.x == 1 && abort_flag) atomicAdd(status + 1, 1);     // the other threads saw the flag
+    (void)ok;
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -559,6 +578,11 @@ cudaError_t launch_one(const Params &p, dim3 grid, bool pair, cudaStream_t s) {
 }  // namespace
 
 bool umma_available() { return get_encode_fn() != nullptr; }
+
+cudaError_t launch_bounded_wait_selftest(int *status, long long limit_cycles, cudaStream_t s) {
+    k_bounded_wait_selftest<<<1, 64, 0, s>>>(status, limit_cycles);
+    return cudaGetLastError();
+}
 
 cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
     w->tma_ok = false;

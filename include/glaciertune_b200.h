@@ -187,6 +187,11 @@ GT_API int gt_profile_enable(gt_engine *eng, int on);
 GT_API int gt_profile_read(gt_engine *eng, double *gemm_ms, int64_t *gemm_launches, double *gemm_flops,
                            int64_t *kernel_launches, int reset);
 
+/* Failure-path self-test (no counterpart in the reference): launches a one-block kernel whose only wait can never
+ * be satisfied, with a limit of `limit_cycles` SM clocks.  The wait gives up, records code 999 and the kernel
+ * returns; the call then reports GT_ERR_KERNEL the way a timed-out GEMM would.  The device is not faulted or hung. */
+GT_API int gt_debug_wait_selftest(gt_engine *eng, int64_t limit_cycles);
+
 /* Kernel timeline for tuning: while dev_buf (device, 12*128 int64, or NULL to stop) is set, the first CTA of every
  * tensor-core GEMM launch writes SM-clock stamps of its pipeline events into it (rows: 0 weight-block loads issued,
  * 1 activation loads issued, 2-4 / 5-7 dequant group 0 / 1 (blocks arrived, slot free, tile published), 8 MMA

@@ -88,3 +88,40 @@ def test_two_rank_gradient_averaging_equals_accumulation(tmp_path):
         acc[oa:oa + na], acc[ob:ob + nb] = ga.reshape(-1), gb.reshape(-1)
     acc *= 0.5
     assert np.allclose(a0, acc, rtol=1e-5, atol=1e-6)
+
+
+def _leaver(rank, world, port, out_dir):
+    """Rank 1 leaves between steps (no collective in flight); rank 0 must get an error from its next exchange
+    within the process-group timeout instead of waiting forever."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    flat = torch.ones(1024)
+    dp.average_gradients_reference(flat, dist)          # step 1: both ranks take part
+    assert torch.allclose(flat, torch.ones(1024))
+    if rank == 1:
+        os._exit(0)                                      # leaves without joining step 2
+    outcome = "hung"
+    try:
+        dp.average_gradients_reference(flat, dist)      # step 2: the peer is gone
+        outcome = "completed"
+    except Exception as exc:  # noqa: BLE001 - any error raised by the backend is the expected outcome
+        outcome = "error: " + type(exc).__name__
+    with open(os.path.join(out_dir, "outcome.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+def test_lost_rank_surfaces_as_an_error_not_a_hang(tmp_path):
+    world, port = 2, _free_port()
+    ctx = mp.spawn(_leaver, args=(world, port, str(tmp_path)), nprocs=world, join=False)
+    import time
+    deadline = time.time() + 60
+    while time.time() < deadline and not (tmp_path / "outcome.txt").exists():
+        time.sleep(0.2)                       # rank 1 has left; wait for rank 0's verdict (bounded)
+    time.sleep(0.2)
+    outcome = (tmp_path / "outcome.txt").read_text() if (tmp_path / "outcome.txt").exists() else "no outcome"
+    for p in ctx.processes:
+        if p.is_alive():
+            p.kill()
+    assert outcome.startswith("error"), outcome

@@ -290,6 +290,22 @@ def test_error_paths(G, eng):
     ad.free()
 
 
+def test_bounded_wait_reports_and_context_survives(G, eng, oracle):
+    """A device-side wait that nothing satisfies gives up after its limit (about 1 ms here), the host sees
+    GT_ERR_KERNEL with the recorded code, and the same engine keeps working afterwards."""
+    with pytest.raises(G.GtError) as ei:
+        eng.wait_selftest(2_000_000)
+    assert ei.value.code == -5 and "999" in str(ei.value)
+    eng.sync()                                     # status was cleared: no stale error
+    c = S.make_projection_case(S.TYPE_Q4_K, 128, 256, 16, seed=2)
+    eng.set_math_mode(0)
+    w = eng.upload_weight(c["qtype"], c["w"], 128, 256)
+    y = eng.forward(w, None, c["x"])
+    yr, _, _, _ = _reference(oracle, c, lora=False, bias=False)
+    assert oracle.rel_fro(y, yr) < 2e-2
+    w.free()
+
+
 def test_grads_scale_clip(G, eng, oracle):
     import torch
     g = torch.arange(1, 1001, dtype=torch.float32, device="cuda")
