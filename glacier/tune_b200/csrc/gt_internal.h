@@ -85,6 +85,10 @@ struct UmmaLaunch {
 int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count);
 // Returns cudaSuccess or an error; `err` receives a description on failure of a non-CUDA kind.
 cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err);
+// Up to three projections in one launch (see gt_umma_gemm.cu); umma_group_ok tells whether they qualify.
+bool umma_group_ok(const UmmaLaunch *m, int n);
+int umma_group_splits(const UmmaLaunch *m, int n, int sm_count);
+cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const char **err);
 cudaError_t umma_init_weight_maps(WeightDev *w, const char **err);
 bool umma_available();
 cudaError_t launch_bounded_wait_selftest(int *status, long long limit_cycles, cudaStream_t s);

@@ -66,21 +66,31 @@ constexpr int kBarRawFull = 0, kBarRawEmpty = kMaxRaw, kBarFull = 2 * kMaxRaw, k
 constexpr int kOffTmemSlot = kNumBars * 8;       // u32
 constexpr int kOffAbort = kOffTmemSlot + 4;      // int
 
-struct Params {
-    CUtensorMap tm_act, tm_hdr, tm_q0, tm_q1;
-    float *out;
+// One launch serves up to kMaxMembers projections that share their input (forward: q,k,v or gate,up read the same X,
+// each writes its own Y) or their output (backward: dX += sum over members of dY_m * W_m).
+constexpr int kMaxMembers = 3;
+struct Member {
+    CUtensorMap tm_hdr, tm_q0, tm_q1;   // packed weight bytes of this member
+    CUtensorMap tm_act;                 // backward: this member's 16-bit dY; forward: member 0 holds the shared X
+    float *out;                         // forward: this member's Y; backward: the shared dX (member 0 is read)
     const float *bias;
-    const float *lora_w;
-    const float *lora_act;   // fp32 [T, rank]: X*A (forward) or dY*B^T (backward); scaled by lora_scale in the kernel
-    float lora_scale;
+    const float *lora_w;                // forward: B [R, N]; backward: A [K, R]
+    const float *lora_act;              // fp32 [T, R]: X*A (forward) or dY*B^T (backward); scaled by lora_scale in the kernel
     const int *lora_flag;
+    float lora_scale;
+    int rank, N, ld_out;
+    int first, count;                   // forward: first tile / tiles of this member; backward: first unit / units
+};
+struct Params {
+    Member m[kMaxMembers];
+    int n_members;
     int *status;
-    int ld_out, T, N, K, rank;
+    long long *trace;   // optional timeline of CTA (0,0,0): [12 rows][128] SM clock values, or null
+    int T, K;
     int t_box;       // token rows per activation TMA box
     int splits, units;
     int atomic_out;  // 1: red.add into out, 0: plain store (+bias)
     int tmem_cols;
-    long long *trace;   // optional timeline of CTA (0,0,0): [12 rows][128] SM clock values, or null
 };
 
 // status codes written on a bounded-wait timeout: 100*role + barrier kind
@@ -142,8 +152,34 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     const int n_acc = PAIR ? 1 : (acc_stride <= 128 ? 4 : (acc_stride <= 256 ? 2 : 1));
     const int u0 = (int)((int64_t)p.units * split / p.splits);
     const int u1 = (int)((int64_t)p.units * (split + 1) / p.splits);
-    const int rank_pad = (p.rank + 15) & ~15;
-    const bool do_lora = p.rank > 0 && split == 0 && (p.lora_flag == nullptr || *p.lora_flag != 0);
+    // forward: the member that owns this tile; backward: every CTA works on all members, unit by unit
+    int mi = 0;
+    if (!BWD)
+        for (int j = 1; j < p.n_members; j++)
+            if (tile >= p.m[j].first) mi = j;
+    const Member &M = p.m[mi];
+    const int ltile = BWD ? tile : tile - M.first;
+    // rank-update stages (split 0 only): forward one for this tile's member, backward one per member with an adapter
+    int lora_m[kMaxMembers];
+    int n_lora = 0;
+    if (split == 0) {
+        if (!BWD) {
+            if (M.rank > 0 && (M.lora_flag == nullptr || *M.lora_flag != 0)) lora_m[n_lora++] = mi;
+        } else {
+            for (int j = 0; j < p.n_members; j++)
+                if (p.m[j].rank > 0) lora_m[n_lora++] = j;
+        }
+    }
+    // backward: global unit index -> (member, 64-row block inside it)
+    auto unit_member = [&](int u, int &rb) -> int {
+        int j = 0;
+        rb = u;
+        while (j + 1 < p.n_members && rb >= p.m[j].count) {
+            rb -= p.m[j].count;
+            j++;
+        }
+        return j;
+    };
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumRaw; i++) {
@@ -162,9 +198,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         mbar_init(bar(kBarTurn + 1), 1);   // and the other way round (stage order = accumulation order, run to run)
         *abort_flag = 0;
         fence_mbar_init();
-        tma_prefetch_desc(&p.tm_act);
-        tma_prefetch_desc(&p.tm_hdr);
-        tma_prefetch_desc(&p.tm_q0);
+        tma_prefetch_desc(&p.m[0].tm_act);
+        tma_prefetch_desc(&M.tm_hdr);
+        tma_prefetch_desc(&M.tm_q0);
     }
     if (warp == 1) {
         if (PAIR) {
@@ -211,36 +247,39 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 if (!ok) break;
                 const uint32_t rdst = sbase + kOffRaw + raw.idx * kRawStageBytes;
                 const uint32_t rbar = bar(kBarRawFull + raw.idx);
-                int sb, half, row0;
+                int sb, half, row0, um = mi, rb = 0;
                 if (BWD) {
-                    sb = tile >> 1; half = tile & 1; row0 = u * 64;
+                    um = unit_member(u, rb);
+                    sb = tile >> 1; half = tile & 1; row0 = rb * 64;
                 } else {
-                    sb = u >> 1; half = u & 1; row0 = tile * kTileW;
+                    sb = u >> 1; half = u & 1; row0 = ltile * kTileW;
                 }
+                const Member &W = p.m[um];
                 const int xb = sb * QS::kBlockBytes;
                 mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
 #pragma unroll
                 for (int rr = 0; rr < kRows; rr += 64) {
-                    tma_load_2d(rdst + rr * H, &p.tm_hdr, xb + QS::hdr_x(half), row0 + rr, rbar);
-                    tma_load_2d(rdst + kRows * H + rr * 64, &p.tm_q0, xb + QS::q0_x(half), row0 + rr, rbar);
-                    if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64) + rr * Q1, &p.tm_q1, xb + QS::q1_x(half), row0 + rr, rbar);
+                    tma_load_2d(rdst + rr * H, &W.tm_hdr, xb + QS::hdr_x(half), row0 + rr, rbar);
+                    tma_load_2d(rdst + kRows * H + rr * 64, &W.tm_q0, xb + QS::q0_x(half), row0 + rr, rbar);
+                    if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64) + rr * Q1, &W.tm_q1, xb + QS::q1_x(half), row0 + rr, rbar);
                 }
                 trace(0, u - u0);
                 raw.advance(kNumRaw);
                 for (int s = 0; s < kSub && ok; s++) {
                     ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
                     if (!ok) break;
-                    load_act_stage(&p.tm_act, BWD ? u * 64 : (u * 2 + s) * 64, sbase + kOffX + xs.idx * kXStageBytes,
+                    load_act_stage(BWD ? &W.tm_act : &p.m[0].tm_act, BWD ? rb * 64 : (u * 2 + s) * 64, sbase + kOffX + xs.idx * kXStageBytes,
                                    bar(kBarFull + xs.idx));
                     trace(1, (u - u0) * kSub + s);
                     xs.advance(kNumX);
                 }
             }
-            if (ok && do_lora) {
+            for (int j = 0; j < n_lora && ok; j++) {
                 // rank-update stage: both operand tiles are built by the dequant warps; the producer only adds the
                 // arrival that stands for the TMA bytes in the other stages
                 ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
                 if (ok && leader) mbar_arrive(bar(kBarFull + xs.idx));
+                xs.advance(kNumX);
             }
         }
     } else if (warp == 1 || warp == kThreads / 32 - 1) {
@@ -262,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 return r;
             };
             const int n_main = (u1 - u0) * kSub;
-            const int n_total = n_main + (do_lora ? 1 : 0);
+            const int n_total = n_main + n_lora;
             // Everything an MMA needs is precomputed: the issuing thread is one thread, and at ~5 clocks per dependent
             // instruction a few dozen instructions per MMA would cost more than the MMA itself.
             // descriptor = (lo, hi): lo = (addr >> 4) | (LBO >> 4) << 16, hi = (SBO >> 4) | version 1 << 14 | SWIZZLE_128B << 29
@@ -282,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const int si = n % kNumA;
                 const uint32_t a_lo0 = (((sbase + kOffA + si * kAStageBytes) & 0x3FFFFu) >> 4) | kALoField;
                 const uint32_t b_lo0 = (((sbase + kOffX + si * kXStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
-                const int ksteps = n < n_main ? 4 : (rank_pad >> 4);
+                const int ksteps = n < n_main ? 4 : ((p.m[lora_m[n - n_main]].rank + 15) >> 4);
                 if (n > 0) {
                     // take the turn: the other issuer has queued stage n - 1 (by now this thread has already waited for
                     // its own operands, which is the latency the second issuer hides)
@@ -376,10 +415,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 if (lane == 0) mbar_arrive(bar(kBarRawEmpty + ri));
             }
         }
-        if (ok && do_lora) {
+        for (int lj = 0; lj < n_lora && ok; lj++) {
             // rank-update stage: group 0 builds the weight-side tile from B (forward) / A (backward), group 1 the
             // activation-side tile from the fp32 low-rank activations, both rounded to T16 here
-            const int n = (BWD ? 1 : 2) * nu;
+            const Member &L = p.m[lora_m[lj]];
+            const int rank_pad = (L.rank + 15) & ~15;
+            const int n = (BWD ? 1 : 2) * nu + lj;
             const int ai = n % kNumA;
             ok = mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
             if (ok) {
@@ -398,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
 #pragma unroll
                                 for (int q = 0; q < 8; q++) {
                                     const int r = 8 * j + q;
-                                    v[q] = (r < p.rank && t < p.T) ? p.lora_act[(int64_t)t * p.rank + r] * p.lora_scale : 0.f;
+                                    v[q] = (r < L.rank && t < p.T) ? L.lora_act[(int64_t)t * L.rank + r] * L.lora_scale : 0.f;
                                 }
                                 st_shared_v4(row_addr + (uint32_t)((j ^ (dt & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
                                              pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
@@ -407,13 +448,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     }
                 } else if (!BWD) {
                     // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
-                    const int row = dt & 127, nn = tile * kTileW + row;
+                    const int row = dt & 127, nn = ltile * kTileW + row;
                     for (int j = dt >> 7; j * 8 < rank_pad; j += 2) {
                         float v[8];
 #pragma unroll
                         for (int i = 0; i < 8; i++) {
                             const int r = 8 * j + i;
-                            v[i] = (r < p.rank && nn < p.N) ? p.lora_w[(int64_t)r * p.N + nn] : 0.f;
+                            v[i] = (r < L.rank && nn < L.N) ? L.lora_w[(int64_t)r * L.N + nn] : 0.f;
                         }
                         st_shared_v4(a_addr + (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4)), pack2<T16>(v[0], v[1]),
                                      pack2<T16>(v[2], v[3]), pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
@@ -422,7 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     // image(kcol >> 6)[row = r][col = kcol & 63] = A[k, r]
                     const int kcol = dt & 127, c = kcol & 63, k = tile * kTileW + kcol;
                     for (int r = dt >> 7; r < rank_pad; r += 2) {
-                        const float v = (r < p.rank && k < p.K) ? p.lora_w[(int64_t)k * p.rank + r] : 0.f;
+                        const float v = (r < L.rank && k < p.K) ? L.lora_w[(int64_t)k * L.rank + r] : 0.f;
                         const uint32_t addr =
                             a_addr + (uint32_t)((kcol >> 6) * 8192 + r * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
                         const uint32_t bits = pack2<T16>(v, 0.f) & 0xFFFFu;
@@ -441,9 +482,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             tc_fence_after_sync();
             if (threadIdx.x == 64) trace(11, 1);
             const int quad = warp & 3, cgrp = (warp - 2) >> 2;     // TMEM lane quadrant; column group 0..3
-            const int orow = tile * kTileW + quad * 32 + lane;
-            const bool row_ok = orow < (BWD ? p.K : p.N);
-            const float bv = (!BWD && !p.atomic_out && p.bias && row_ok) ? p.bias[orow] : 0.f;
+            const int orow = ltile * kTileW + quad * 32 + lane;
+            const bool row_ok = orow < (BWD ? p.K : M.N);
+            const float bv = (!BWD && !p.atomic_out && M.bias && row_ok) ? M.bias[orow] : 0.f;
+            float *const out_base = M.out;       // backward: member 0 holds the shared dX
+            const int ld_out = M.ld_out;
             const int nch = (tb + 31) >> 5;
             for (int c = cgrp; c < nch; c += 4) {
                 uint32_t v[32];
@@ -462,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                         const int tl = c * 32 + j;
                         const int t = tok0 + tl;
                         if (tl < tb && t < p.T) {
-                            float *dst = p.out + (int64_t)t * p.ld_out + orow;
+                            float *dst = out_base + (int64_t)t * ld_out + orow;
                             const float val = __uint_as_float(v[j]);
                             if (BWD || p.atomic_out) atomicAdd(dst, val);
                             else *dst = val + bv;
@@ -568,7 +611,6 @@ cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
 template <int QT, typename T16, bool BWD>
 cudaError_t launch_one(const Params &p, dim3 grid, bool pair, cudaStream_t s) {
     if (pair) {
-        grid.x = (grid.x + 1) & ~1u;      // a pair owns two adjacent tiles; a padding tile is all out of range
         if (p.t_box == 64) return launch_variant<QT, T16, BWD, true, 128>(p, grid, s);
         return launch_variant<QT, T16, BWD, true, 256>(p, grid, s);
     }
@@ -606,9 +648,7 @@ cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
     return cudaSuccess;
 }
 
-int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count) {
-    const int tiles = backward ? w->K / kTileW : (w->N + kTileW - 1) / kTileW;
-    const int units = backward ? (w->N + 63) / 64 : w->K / 128;
+static int pick_splits(int tiles, int units, int T, int sm_count) {
     const int chunks = (T + kMaxTok - 1) / kMaxTok;
     int s = sm_count / (tiles * chunks > 0 ? tiles * chunks : 1);
     const int cap = units / 2 > 1 ? units / 2 : 1;
@@ -618,21 +658,57 @@ int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count) {
     return s;
 }
 
-cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err) {
-    const WeightDev *w = L.w;
-    if (!w || !w->tma_ok) {
-        if (err) *err = "weight tensor has no TMA maps (K % 256 != 0 or unsupported type)";
+int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count) {
+    const int tiles = backward ? w->K / kTileW : (w->N + kTileW - 1) / kTileW;
+    const int units = backward ? (w->N + 63) / 64 : w->K / 128;
+    return pick_splits(tiles, units, T, sm_count);
+}
+
+bool umma_group_ok(const UmmaLaunch *m, int n) {
+    if (n < 1 || n > kMaxMembers) return false;
+    for (int j = 0; j < n; j++) {
+        const WeightDev *w = m[j].w;
+        if (!w || !w->tma_ok || w->qtype != m[0].w->qtype || w->K != m[0].w->K) return false;
+        if (m[j].rank > 64) return false;
+        if (m[j].backward != m[0].backward || m[j].fp16 != m[0].fp16 || m[j].T != m[0].T) return false;
+        if (m[0].backward && m[j].out != m[0].out) return false;       // one shared dX
+    }
+    return true;
+}
+
+int umma_group_splits(const UmmaLaunch *m, int n, int sm_count) {
+    const bool bwd = m[0].backward != 0;
+    const int tmax = m[0].T < kMaxTok ? m[0].T : kMaxTok;
+    const bool pair = tmax >= 256;
+    int tiles = 0, units = 0;
+    for (int j = 0; j < n; j++) {
+        const WeightDev *w = m[j].w;
+        if (bwd) {
+            units += (w->N + 63) / 64;
+            tiles = w->K / kTileW;
+        } else {
+            int t = (w->N + kTileW - 1) / kTileW;
+            if (pair) t = (t + 1) & ~1;
+            tiles += t;
+            units = w->K / 128;
+        }
+    }
+    return pick_splits(tiles, units, m[0].T, sm_count);
+}
+
+// Members share T, math mode, direction, in_features and quantization type (umma_group_ok).  Forward: the activation
+// operand and `splits` / `out_prefilled` come from member 0.  Backward: every member brings its own dY; `out` is shared.
+cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const char **err) {
+    if (!umma_group_ok(m, n)) {
+        if (err) *err = "projections cannot share one launch (type, in_features, token count or TMA layout differ)";
         return cudaErrorInvalidValue;
     }
-    if (L.T <= 0) return cudaSuccess;
-    if (L.rank > 64) {
-        if (err) *err = "fused LoRA update supports rank <= 64";
-        return cudaErrorInvalidValue;
-    }
+    const UmmaLaunch &L0 = m[0];
+    if (L0.T <= 0) return cudaSuccess;
+    const bool bwd = L0.backward != 0;
     Params p;
     memset(&p, 0, sizeof(p));
-    const int cols = L.backward ? w->N : w->K;       // contraction length of the activation operand
-    const int tmax = L.T < kMaxTok ? L.T : kMaxTok;
+    const int tmax = L0.T < kMaxTok ? L0.T : kMaxTok;
     // CTA pairs pay off once the activation tile is the bulk of what an SM pulls from L2; small token counts are
     // weight-streaming bound and stay on single CTAs
     static const int pair_min = getenv("GT_PAIR_MIN") ? atoi(getenv("GT_PAIR_MIN")) : 256;
@@ -647,42 +723,76 @@ cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **e
     int tc = 32;
     while (tc < need_cols) tc <<= 1;
     p.tmem_cols = tc;
-    const CUtensorMapDataType dt = L.fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    if (!encode_2d(&p.tm_act, dt, 2, L.act16, (uint64_t)cols, (uint64_t)L.T, (uint64_t)L.ld_act * 2, 64, (uint32_t)p.t_box,
-                   CU_TENSOR_MAP_SWIZZLE_128B)) {
-        if (err) *err = "cuTensorMapEncodeTiled failed for the activation operand";
+    const CUtensorMapDataType dt = L0.fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    p.n_members = n;
+    int first = 0;
+    for (int j = 0; j < n; j++) {
+        const UmmaLaunch &L = m[j];
+        const WeightDev *w = L.w;
+        Member &M = p.m[j];
+        M.tm_hdr = w->tm_hdr;
+        M.tm_q0 = w->tm_q0;
+        M.tm_q1 = w->tm_q1;
+        if (bwd || j == 0) {
+            const int cols = bwd ? w->N : w->K;       // contraction length of the activation operand
+            if (!encode_2d(&M.tm_act, dt, 2, L.act16, (uint64_t)cols, (uint64_t)L.T, (uint64_t)L.ld_act * 2, 64, (uint32_t)p.t_box,
+                           CU_TENSOR_MAP_SWIZZLE_128B)) {
+                if (err) *err = "cuTensorMapEncodeTiled failed for the activation operand";
+                return cudaErrorInvalidValue;
+            }
+        } else {
+            M.tm_act = p.m[0].tm_act;
+        }
+        M.out = L.out;
+        M.ld_out = L.ld_out;
+        M.bias = L.bias;
+        M.N = w->N;
+        if (L.rank > 0 && L.lora_act && L.lora_w) {
+            M.rank = L.rank;
+            M.lora_w = L.lora_w;
+            M.lora_act = L.lora_act;
+            M.lora_scale = L.lora_scale;
+            M.lora_flag = L.lora_flag;
+        }
+        int count;
+        if (bwd) {
+            count = (w->N + 63) / 64;
+        } else {
+            count = (w->N + kTileW - 1) / kTileW;
+            if (pair) count = (count + 1) & ~1;      // a pair owns two adjacent tiles of ONE member; a padding tile is all out of range
+        }
+        M.first = first;
+        M.count = count;
+        first += count;
+    }
+    p.status = L0.status;
+    p.trace = (long long *)L0.trace;
+    p.T = L0.T;
+    p.K = L0.w->K;
+    p.units = bwd ? first : L0.w->K / 128;
+    p.splits = L0.splits < 1 ? 1 : (L0.splits > p.units ? p.units : L0.splits);
+    p.atomic_out = bwd ? 1 : (p.splits > 1 || L0.out_prefilled ? 1 : 0);
+    const int tiles = bwd ? L0.w->K / kTileW : first;
+    dim3 grid(tiles, p.splits, (L0.T + kMaxTok - 1) / kMaxTok);
+    const int qt = L0.w->qtype;
+    if (qt == kTypeQ4K) {
+        if (!L0.fp16) return bwd ? launch_one<kTypeQ4K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __nv_bfloat16, false>(p, grid, pair, s);
+        return bwd ? launch_one<kTypeQ4K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __half, false>(p, grid, pair, s);
+    }
+    if (!L0.fp16) return bwd ? launch_one<kTypeQ6K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ6K, __nv_bfloat16, false>(p, grid, pair, s);
+    return bwd ? launch_one<kTypeQ6K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ6K, __half, false>(p, grid, pair, s);
+}
+
+cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err) {
+    if (!L.w || !L.w->tma_ok) {
+        if (err) *err = "weight tensor has no TMA maps (K % 256 != 0 or unsupported type)";
         return cudaErrorInvalidValue;
     }
-    p.rank = 0;
-    if (L.rank > 0 && L.lora_act && L.lora_w) {
-        p.rank = L.rank;
-        p.lora_w = L.lora_w;
-        p.lora_act = L.lora_act;
-        p.lora_scale = L.lora_scale;
-        p.lora_flag = L.lora_flag;
+    if (L.rank > 64) {
+        if (err) *err = "fused LoRA update supports rank <= 64";
+        return cudaErrorInvalidValue;
     }
-    p.tm_hdr = w->tm_hdr;
-    p.tm_q0 = w->tm_q0;
-    p.tm_q1 = w->tm_q1;
-    p.out = L.out;
-    p.ld_out = L.ld_out;
-    p.bias = L.bias;
-    p.status = L.status;
-    p.trace = (long long *)L.trace;
-    p.T = L.T;
-    p.N = w->N;
-    p.K = w->K;
-    p.units = L.backward ? (w->N + 63) / 64 : w->K / 128;
-    p.splits = L.splits < 1 ? 1 : (L.splits > p.units ? p.units : L.splits);
-    p.atomic_out = L.backward ? 1 : (p.splits > 1 || L.out_prefilled ? 1 : 0);
-    const int tiles = L.backward ? w->K / kTileW : (w->N + kTileW - 1) / kTileW;
-    dim3 grid(tiles, p.splits, (L.T + kMaxTok - 1) / kMaxTok);
-    if (w->qtype == kTypeQ4K) {
-        if (!L.fp16) return L.backward ? launch_one<kTypeQ4K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __nv_bfloat16, false>(p, grid, pair, s);
-        return L.backward ? launch_one<kTypeQ4K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __half, false>(p, grid, pair, s);
-    }
-    if (!L.fp16) return L.backward ? launch_one<kTypeQ6K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ6K, __nv_bfloat16, false>(p, grid, pair, s);
-    return L.backward ? launch_one<kTypeQ6K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ6K, __half, false>(p, grid, pair, s);
+    return launch_umma_group(&L, 1, s, err);
 }
 
 }  // namespace gt
