@@ -231,14 +231,30 @@ def run_ours(args) -> None:
     _log("layer built")
     l2_flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
+    # q,k,v read the same normed hidden state and gate,up the same FFN input (TransformerBlock.Forward): each group is
+    # one call that shares the input and sums the members' input gradients into one buffer
+    by_name = {p["name"]: p for p in layer}
+    groups = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]] if not args.no_group else [[n] for n in PROJ_ORDER]
+    calls = []
+    for names in groups:
+        ps = [by_name[n] for n in names]
+        calls.append(dict(ws=[p["w"] for p in ps], ads=[p["ad"] for p in ps], X=ps[0]["X"], Ys=[p["Y"] for p in ps],
+                          dYs=[p["dY"] for p in ps], dX=ps[0]["dX"]))
+
     def step_resident():
         flat_grads.zero_()
-        for p in layer:
-            eng.forward(p["w"], p["ad"], p["X"], p["Y"])
-        for p in reversed(layer):
-            p["dX"].zero_()     # the reference hands Backward a zero-filled dX (AutogradScratchWorkspace.Wrap)
+        for c in calls:
+            if len(c["ws"]) > 1:
+                eng.forward_group(c["ws"], c["ads"], c["X"], c["Ys"])
+            else:
+                eng.forward(c["ws"][0], c["ads"][0], c["X"], c["Ys"][0])
+        for c in reversed(calls):
+            c["dX"].zero_()     # the reference hands Backward a zero-filled dX (AutogradScratchWorkspace.Wrap)
             # X is the tensor the forward above saw: X*A kept by the adapter is reused (GT_FLAG_REUSE_LOW)
-            eng.backward(p["w"], p["ad"], p["dY"], p["X"], p["dX"], flags=G.FLAG_REUSE_LOW)
+            if len(c["ws"]) > 1:
+                eng.backward_group(c["ws"], c["ads"], c["dYs"], c["X"], c["dX"], flags=G.FLAG_REUSE_LOW)
+            else:
+                eng.backward(c["ws"][0], c["ads"][0], c["dYs"][0], c["X"], c["dX"], flags=G.FLAG_REUSE_LOW)
         if world > 1:
             eng.dp_allreduce(flat_grads, 1.0 / world)
 
@@ -405,6 +421,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
+    ap.add_argument("--no-group", action="store_true", help="one call per projection instead of q,k,v and gate,up groups")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -22,7 +22,7 @@ EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
-    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward",
+    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
@@ -76,6 +76,9 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_proj_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
     lib.gt_proj_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                      C.c_int32]
+    lib.gt_proj_forward_group.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
+    lib.gt_proj_backward_group.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                           C.c_int32]
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
@@ -181,6 +184,34 @@ class Engine:
         if dev:
             flags |= FLAG_DEVICE_PTRS
         _check(self.lib.gt_proj_backward(self.h, w.h, adapter.h if adapter else None, gp, xp, dp, dY.shape[0], flags))
+        return dX
+
+    @staticmethod
+    def _ptr_array(items):
+        arr = (C.c_void_p * len(items))()
+        for i, it in enumerate(items):
+            arr[i] = None if it is None else (it.h if hasattr(it, "h") else _ptr(it)[0])
+        return arr
+
+    def forward_group(self, weights, adapters, X, Ys, flags: int = 0):
+        """Projections of the same input (q,k,v or gate,up): Ys[j] = X W_j^T + ... in one launch (device tensors)."""
+        xp, dev = _ptr(X, np.float32)
+        if dev:
+            flags |= FLAG_DEVICE_PTRS
+        n = len(weights)
+        ads = self._ptr_array(adapters if adapters is not None else [None] * n)
+        _check(self.lib.gt_proj_forward_group(self.h, n, self._ptr_array(weights), ads, xp, self._ptr_array(Ys), X.shape[0], flags))
+        return Ys
+
+    def backward_group(self, weights, adapters, dYs, X, dX, flags: int = 0):
+        """dX += sum_j dYs[j] W_j + adapter terms; adapter grads accumulate (device tensors for one launch)."""
+        _, dev = _ptr(dYs[0], np.float32)
+        if dev:
+            flags |= FLAG_DEVICE_PTRS
+        n = len(weights)
+        ads = self._ptr_array(adapters if adapters is not None else [None] * n)
+        _check(self.lib.gt_proj_backward_group(self.h, n, self._ptr_array(weights), ads, self._ptr_array(dYs), _ptr(X, np.float32)[0],
+                                               _ptr(dX, np.float32)[0], dYs[0].shape[0], flags))
         return dX
 
     def launch_gemm_batch(self, w: "Weight", Y, X, batch: int, residual=None):

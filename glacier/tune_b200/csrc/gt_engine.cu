@@ -100,8 +100,10 @@ struct gt_adapter {
     float *A = nullptr, *B = nullptr, *dA = nullptr, *dB = nullptr;
     bool own_grads = true;
     int *b_nonzero = nullptr;    // device flag: any(B != 0), refreshed whenever B is uploaded
-    Scratch low;                 // low = X*A of the last forward / backward through this adapter, [low_T, rank] fp32
+    Scratch low;                 // low = X*A of the last forward / backward through this adapter, then dLow = dY*B^T;
+                                 // [low_T, rank] fp32 each
     int low_T = 0;
+    bool dlow_clean = false;     // dLow is still all zero (cleared together with low, not yet summed into)
 };
 
 namespace {
@@ -133,148 +135,268 @@ cudaEvent_t next_event(gt_engine *e) {
     return e->ev_pool[e->ev_used++];
 }
 
-// launch the tensor-core GEMM, bracketed by events when profiling is on
-cudaError_t timed_umma(gt_engine *e, const UmmaLaunch &L, const char **msg) {
+// launch the tensor-core GEMM (one launch for all members), bracketed by events when profiling is on
+cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg) {
     cudaEvent_t a = nullptr, b = nullptr;
     if (e->profile) {
         a = next_event(e);
         b = next_event(e);
         if (a) cudaEventRecord(a, e->stream);
     }
-    cudaError_t ce = launch_umma_gemm(L, e->stream, msg);
+    cudaError_t ce = launch_umma_group(m, n, e->stream, msg);
     if (e->profile && b) cudaEventRecord(b, e->stream);
     e->gemm_launches += 1;
     e->kernel_launches += 1;
-    e->gemm_flops += 2.0 * (double)L.T * (double)L.w->N * (double)L.w->K;
+    for (int j = 0; j < n; j++) e->gemm_flops += 2.0 * (double)m[j].T * (double)m[j].w->N * (double)m[j].w->K;
     return ce;
+}
+
+constexpr int kMaxGroup = 3;
+
+// The adapter's scratch holds low = X*A and dLow = dY*B^T of the current step side by side, [T, rank] fp32 each.
+size_t low_bytes(const gt_adapter *a, int T) { return ((size_t)T * a->rank * sizeof(float) + 255) & ~(size_t)255; }
+float *low_of(const gt_adapter *a) { return (float *)a->low.p; }
+float *dlow_of(const gt_adapter *a, int T) { return (float *)((char *)a->low.p + low_bytes(a, T)); }
+
+// low_j = X * A_j for every listed adapter (they share X), and optionally the 16-bit copy of X.  One memset per
+// adapter clears low (the TF32 kernel sums into it) and dLow of the same step; one kernel pass reads X.
+int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, void *x16, int fp16, int T, int K) {
+    LoraXaJob jobs[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        gt_adapter *a = ads[j];
+        GT_CUDA(a->low.reserve(2 * low_bytes(a, T)));
+        GT_CUDA(cudaMemsetAsync(a->low.p, 0, 2 * low_bytes(a, T), e->stream));
+        a->low_T = T;
+        a->dlow_clean = true;
+        jobs[j] = LoraXaJob{a->A, low_of(a), a->rank};
+    }
+    if (e->math_mode == GT_MATH_BF16) {
+        GT_LAUNCH(e, launch_lora_xa_group(Xd, jobs, n, x16, K, fp16, T, K, e->stream));
+    } else {
+        for (int j = 0; j < n; j++)
+            GT_LAUNCH(e, launch_lora_low(Xd, jobs[j].A, jobs[j].low_zeroed, j == 0 ? x16 : nullptr, K, fp16, T, K, jobs[j].R, e->stream));
+    }
+    return GT_OK;
+}
+
+int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora);
+int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
+                    bool use_lora, bool reuse_low);
+
+bool group_tensor_ok(const gt_engine *e, int n, const gt_weight *const *w) {
+    if (n < 1 || n > kMaxGroup) return false;
+    for (int j = 0; j < n; j++)
+        if (!tensor_path(e, w[j]) || w[j]->dev.qtype != w[0]->dev.qtype || w[j]->dev.K != w[0]->dev.K) return false;
+    return true;
+}
+
+// Y_j = X * W_j^T (+ bias_j) (+ lora_j) for 1..3 projections that read the same X.  Tensor-core path: one pass over X
+// (16-bit copy + every adapter's X*A), one GEMM launch.  Anything else runs member by member.
+int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
+                         int T, int flags) {
+    bool lora[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0 && ad[j]->scaling != 0.f;
+        if (ad && ad[j] && !lora[j]) ad[j]->low_T = 0;      // nothing kept for a later backward to reuse
+    }
+    if (!group_tensor_ok(e, n, w)) {
+        if (n == 1) return fail(GT_ERR_INVALID, "internal: single projection off the tensor path reached the group call");
+        for (int j = 0; j < n; j++) {
+            int rc = forward_device(e, w[j], ad ? ad[j] : nullptr, Xd, Yd[j], T, lora[j]);
+            if (rc != GT_OK) return rc;
+        }
+        return GT_OK;
+    }
+    const int K = w[0]->dev.K;
+    const int fp16 = e->math_mode == GT_MATH_FP16;
+    GT_CUDA(e->x16.reserve((size_t)T * K * 2));
+    gt_adapter *with[kMaxGroup];
+    int n_with = 0;
+    for (int j = 0; j < n; j++)
+        if (lora[j]) with[n_with++] = ad[j];
+    if (n_with) {
+        int rc = compute_low(e, with, n_with, Xd, e->x16.p, fp16, T, K);
+        if (rc != GT_OK) return rc;
+    } else {
+        GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
+    }
+    UmmaLaunch m[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        const WeightDev &wd = w[j]->dev;
+        m[j].w = &wd;
+        m[j].backward = 0;
+        m[j].fp16 = fp16;
+        m[j].act16 = e->x16.p;
+        m[j].ld_act = K;
+        m[j].T = T;
+        m[j].out = Yd[j];
+        m[j].ld_out = wd.N;
+        m[j].bias = wd.bias;
+        if (lora[j]) {
+            m[j].lora_act = low_of(ad[j]);
+            m[j].lora_scale = ad[j]->scaling;
+            m[j].lora_w = ad[j]->B;
+            m[j].rank = ad[j]->rank;
+            m[j].lora_flag = ad[j]->b_nonzero;
+        }
+        m[j].status = e->status;
+        m[j].trace = e->trace;
+    }
+    const int splits = umma_group_splits(m, n, e->sm_count);
+    for (int j = 0; j < n; j++) {
+        m[j].splits = splits;
+        if (splits > 1) {
+            GT_LAUNCH(e, launch_fill_rows(Yd[j], w[j]->dev.bias, T, w[j]->dev.N, e->stream));
+            m[j].out_prefilled = 1;
+        }
+    }
+    const char *msg = nullptr;
+    cudaError_t ce = timed_umma_group(e, m, n, &msg);
+    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    return GT_OK;
 }
 
 // out[T, N] = act * W^T (+bias) (+ lora) on the engine stream, device pointers.
 int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora) {
+    if (tensor_path(e, w)) return forward_group_device(e, 1, &w, &ad, Xd, &Yd, T, use_lora ? 0 : GT_FLAG_NO_LORA);
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
-    float *low = nullptr;
+    GT_LAUNCH(e, launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
     if (use_lora) {
-        GT_CUDA(ad->low.reserve((size_t)T * ad->rank * sizeof(float)));
-        low = (float *)ad->low.p;
-        ad->low_T = T;
+        int rc = compute_low(e, &ad, 1, Xd, nullptr, 0, T, K);
+        if (rc != GT_OK) return rc;
+        GT_LAUNCH(e, launch_lora_delta_fp32(low_of(ad), ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling, ad->b_nonzero, e->stream));
+    } else if (ad) {
+        ad->low_T = 0;
     }
-    if (!tensor_path(e, w)) {
-        GT_LAUNCH(e, launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
-        if (use_lora) {
-            GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, nullptr, 0, 0, T, K, ad->rank, e->stream));
-            GT_LAUNCH(e, launch_lora_delta_fp32(low, ad->B, Yd, nullptr, T, N, ad->rank, ad->scaling, ad->b_nonzero, e->stream));
+    return GT_OK;
+}
+
+// The adapter half of a backward: dB += s*low^T*dY, dLow = dY*B^T, dA += s*X^T*dLow for every member with an adapter
+// (one launch per product in the bf16 mode), and the 16-bit copy of each dY where dy16[j] is given.
+int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const bool *lora,
+                        const float *const *dYd, const float *Xd, void *const *dy16, const int *ld16, int T, bool reuse_low) {
+    const int K = w[0]->dev.K;
+    const int fp16 = e->math_mode == GT_MATH_FP16;
+    const bool fast = e->math_mode == GT_MATH_BF16;      // TF32 warp-MMA reductions; exact fp32 otherwise
+    gt_adapter *fresh[kMaxGroup];
+    int n_fresh = 0;
+    for (int j = 0; j < n; j++) {
+        if (!lora[j]) continue;
+        gt_adapter *a = ad[j];
+        if (reuse_low && a->low.p && a->low_T == T) {
+            if (!a->dlow_clean) GT_CUDA(cudaMemsetAsync(dlow_of(a, T), 0, low_bytes(a, T), e->stream));
+        } else {
+            fresh[n_fresh++] = a;
+        }
+    }
+    if (n_fresh) {
+        int rc = compute_low(e, fresh, n_fresh, Xd, nullptr, 0, T, K);
+        if (rc != GT_OK) return rc;
+    }
+    LoraDyJob dy[kMaxGroup];
+    LoraDaJob da[kMaxGroup];
+    int nl = 0;
+    for (int j = 0; j < n; j++) {
+        if (!lora[j]) {
+            if (dy16[j]) GT_LAUNCH(e, launch_cast16(dYd[j], dy16[j], T, w[j]->dev.N, ld16[j], fp16, e->stream));
+            continue;
+        }
+        gt_adapter *a = ad[j];
+        a->dlow_clean = false;
+        dy[nl] = LoraDyJob{dYd[j], low_of(a), a->B, a->dB, dlow_of(a, T), dy16[j], ld16[j], a->scaling, w[j]->dev.N, a->rank};
+        da[nl] = LoraDaJob{dlow_of(a, T), a->dA, a->scaling, a->rank};
+        nl++;
+    }
+    if (!nl) return GT_OK;
+    if (fast) {
+        GT_LAUNCH(e, launch_lora_dy_group(dy, nl, fp16, T, e->stream));
+        GT_LAUNCH(e, launch_lora_da_group(Xd, da, nl, T, K, e->stream));
+    } else {
+        for (int j = 0; j < nl; j++) {
+            GT_LAUNCH(e, launch_lora_bwd_dy(dy[j].dY, dy[j].low, dy[j].B, dy[j].dB, dy[j].dLow_zeroed, dy[j].dy16, dy[j].ld16, fp16,
+                                            dy[j].scaling, T, dy[j].N, dy[j].R, e->stream));
+            GT_LAUNCH(e, launch_lora_bwd_x(Xd, da[j].dLow, da[j].dA, da[j].scaling, T, K, da[j].R, e->stream));
+        }
+    }
+    return GT_OK;
+}
+
+// dX += sum_j dY_j * W_j (+ lora terms); dA_j, dB_j accumulate.  Tensor-core path: one GEMM launch for the group.
+int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dYd,
+                          const float *Xd, float *dXd, int T, int flags) {
+    bool lora[kMaxGroup];
+    for (int j = 0; j < n; j++) lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0;
+    const bool reuse_low = (flags & GT_FLAG_REUSE_LOW) != 0;
+    if (!group_tensor_ok(e, n, w) || !dXd) {
+        if (n == 1) return fail(GT_ERR_INVALID, "internal: single projection off the tensor path reached the group call");
+        for (int j = 0; j < n; j++) {
+            int rc = backward_device(e, w[j], ad ? ad[j] : nullptr, dYd[j], Xd, dXd, T, lora[j], reuse_low);
+            if (rc != GT_OK) return rc;
         }
         return GT_OK;
     }
+    const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
-    GT_CUDA(e->x16.reserve((size_t)T * K * 2));
-    if (use_lora) {
-        if (e->math_mode == GT_MATH_BF16) {
-            GT_CUDA(cudaMemsetAsync(low, 0, (size_t)T * ad->rank * sizeof(float), e->stream));
-            GT_LAUNCH(e, launch_lora_xa_tc(Xd, ad->A, low, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
-        } else {
-            GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, e->x16.p, K, fp16, T, K, ad->rank, e->stream));
+    size_t dy_off[kMaxGroup], dy_total = 0;
+    int ld16[kMaxGroup];
+    void *dy16[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        ld16[j] = round8(w[j]->dev.N);
+        dy_off[j] = dy_total;
+        dy_total += ((size_t)T * ld16[j] * 2 + 255) & ~(size_t)255;
+    }
+    GT_CUDA(e->dy16.reserve(dy_total));
+    for (int j = 0; j < n; j++) dy16[j] = (char *)e->dy16.p + dy_off[j];
+    int rc = lora_backward_group(e, n, w, ad, lora, dYd, Xd, dy16, ld16, T, reuse_low);
+    if (rc != GT_OK) return rc;
+    UmmaLaunch m[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        const WeightDev &wd = w[j]->dev;
+        m[j].w = &wd;
+        m[j].backward = 1;
+        m[j].fp16 = fp16;
+        m[j].act16 = dy16[j];
+        m[j].ld_act = ld16[j];
+        m[j].T = T;
+        m[j].out = dXd;
+        m[j].ld_out = K;
+        if (lora[j]) {
+            m[j].lora_act = dlow_of(ad[j], T);
+            m[j].lora_scale = ad[j]->scaling;
+            m[j].lora_w = ad[j]->A;
+            m[j].rank = ad[j]->rank;
         }
-    } else {
-        GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
+        m[j].status = e->status;
+        m[j].trace = e->trace;
     }
-    UmmaLaunch L;
-    L.w = &wd;
-    L.backward = 0;
-    L.fp16 = fp16;
-    L.act16 = e->x16.p;
-    L.ld_act = K;
-    L.T = T;
-    L.out = Yd;
-    L.ld_out = N;
-    L.bias = wd.bias;
-    L.splits = umma_pick_splits(&wd, 0, T, e->sm_count);
-    if (L.splits > 1) {
-        GT_LAUNCH(e, launch_fill_rows(Yd, wd.bias, T, N, e->stream));
-        L.out_prefilled = 1;
-    }
-    if (use_lora) {
-        L.lora_act = low;
-        L.lora_scale = ad->scaling;
-        L.lora_w = ad->B;
-        L.rank = ad->rank;
-        L.lora_flag = ad->b_nonzero;
-    }
-    L.status = e->status;
-    L.trace = e->trace;
+    const int splits = umma_group_splits(m, n, e->sm_count);
+    for (int j = 0; j < n; j++) m[j].splits = splits;
     const char *msg = nullptr;
-    cudaError_t ce = timed_umma(e, L, &msg);
-    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    cudaError_t ce = timed_umma_group(e, m, n, &msg);
+    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
     return GT_OK;
 }
 
 // dX += dY*W (+ lora term); dA, dB accumulate.  Device pointers.
 int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
                     bool use_lora, bool reuse_low) {
+    if (tensor_path(e, w) && dXd) {
+        const int flags = (use_lora ? 0 : GT_FLAG_NO_LORA) | (reuse_low ? GT_FLAG_REUSE_LOW : 0);
+        return backward_group_device(e, 1, &w, &ad, &dYd, Xd, dXd, T, flags);
+    }
+    // exact fp32 kernels (validation mode, weights outside the tensor-core layout) or adapter gradients only
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
-    const bool tensor = tensor_path(e, w) && dXd != nullptr;
-    const int fp16 = e->math_mode == GT_MATH_FP16;
-    const int ld16 = round8(N);
-    if (tensor) GT_CUDA(e->dy16.reserve((size_t)T * ld16 * 2));
     if (use_lora) {
-        const int R = ad->rank;
-        const bool fast = e->math_mode == GT_MATH_BF16;      // TF32 warp-MMA reductions; exact fp32 otherwise
-        const bool reuse = reuse_low && ad->low.p && ad->low_T == T;
-        GT_CUDA(ad->low.reserve((size_t)T * R * sizeof(float)));
-        float *low = (float *)ad->low.p;
-        GT_CUDA(e->dlow.reserve((size_t)T * R * sizeof(float)));
-        if (!reuse) {
-            if (fast) {
-                GT_CUDA(cudaMemsetAsync(low, 0, (size_t)T * R * sizeof(float), e->stream));
-                GT_LAUNCH(e, launch_lora_xa_tc(Xd, ad->A, low, nullptr, 0, 0, T, K, R, e->stream));
-            } else {
-                GT_LAUNCH(e, launch_lora_low(Xd, ad->A, low, nullptr, 0, 0, T, K, R, e->stream));
-            }
-            ad->low_T = T;
-        }
-        GT_CUDA(cudaMemsetAsync(e->dlow.p, 0, (size_t)T * R * sizeof(float), e->stream));
-        if (fast) {
-            GT_LAUNCH(e, launch_lora_dy_tc(dYd, low, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr, ld16, fp16,
-                                           ad->scaling, T, N, R, e->stream));
-            GT_LAUNCH(e, launch_lora_da_tc(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
-        } else {
-            GT_LAUNCH(e, launch_lora_bwd_dy(dYd, low, ad->B, ad->dB, (float *)e->dlow.p, tensor ? e->dy16.p : nullptr, ld16, fp16,
-                                            ad->scaling, T, N, R, e->stream));
-            GT_LAUNCH(e, launch_lora_bwd_x(Xd, (const float *)e->dlow.p, ad->dA, ad->scaling, T, K, R, e->stream));
-        }
-        if (dXd && !tensor) GT_LAUNCH(e, launch_lora_dx_fp32((const float *)e->dlow.p, ad->A, dXd, ad->scaling, T, K, R, e->stream));
-    } else if (tensor) {
-        GT_LAUNCH(e, launch_cast16(dYd, e->dy16.p, T, N, ld16, fp16, e->stream));
+        const bool lora = true;
+        void *no16 = nullptr;
+        const int ld16 = round8(N);
+        int rc = lora_backward_group(e, 1, &w, &ad, &lora, &dYd, Xd, &no16, &ld16, T, reuse_low);
+        if (rc != GT_OK) return rc;
+        if (dXd) GT_LAUNCH(e, launch_lora_dx_fp32(dlow_of(ad, T), ad->A, dXd, ad->scaling, T, K, ad->rank, e->stream));
     }
-    if (!dXd) return GT_OK;
-    if (!tensor) {
-        GT_LAUNCH(e, launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
-        return GT_OK;
-    }
-    UmmaLaunch L;
-    L.w = &wd;
-    L.backward = 1;
-    L.fp16 = fp16;
-    L.act16 = e->dy16.p;
-    L.ld_act = ld16;
-    L.T = T;
-    L.out = dXd;
-    L.ld_out = K;
-    L.splits = umma_pick_splits(&wd, 1, T, e->sm_count);
-    if (use_lora) {
-        L.lora_act = (const float *)e->dlow.p;
-        L.lora_scale = ad->scaling;
-        L.lora_w = ad->A;
-        L.rank = ad->rank;
-        L.lora_flag = nullptr;
-    }
-    L.status = e->status;
-    L.trace = e->trace;
-    const char *msg = nullptr;
-    cudaError_t ce = timed_umma(e, L, &msg);
-    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    if (dXd) GT_LAUNCH(e, launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
     return GT_OK;
 }
 
@@ -685,6 +807,51 @@ int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const flo
     if (rc != GT_OK) return rc;
     if (dX) GT_CUDA(cudaMemcpyAsync(dX, e->h_out.p, bx, cudaMemcpyDeviceToHost, e->stream));
     return check_status(e);
+}
+
+int gt_proj_forward_group(gt_engine *e, int32_t n, const gt_weight *const *w, gt_adapter *const *ad, const float *X, float *const *Y,
+                          int32_t T, int32_t flags) {
+    if (!e || !w || !X || !Y) return fail(GT_ERR_INVALID, "gt_proj_forward_group: null argument");
+    if (n < 1 || n > kMaxGroup) return fail(GT_ERR_INVALID, "a group holds 1 to %d projections (got %d)", kMaxGroup, n);
+    if (T <= 0) return fail(GT_ERR_INVALID, "T must be positive (got %d)", T);
+    for (int j = 0; j < n; j++) {
+        if (!w[j] || !Y[j]) return fail(GT_ERR_INVALID, "gt_proj_forward_group: member %d is null", j);
+        if (w[j]->dev.K != w[0]->dev.K) return fail(GT_ERR_INVALID, "members of a group share their input: in_features %d vs %d", w[j]->dev.K, w[0]->dev.K);
+        if (ad && ad[j] && (ad[j]->in != w[j]->dev.K || ad[j]->out != w[j]->dev.N)) return fail(GT_ERR_INVALID, "adapter %d does not match its weight", j);
+    }
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) {
+        for (int j = 0; j < n; j++) {        // host buffers: the per-projection call stages each member
+            int rc = gt_proj_forward(e, w[j], ad ? ad[j] : nullptr, X, Y[j], T, flags);
+            if (rc != GT_OK) return rc;
+        }
+        return GT_OK;
+    }
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return forward_group_device(e, n, w, ad, X, Y, T, flags);
+}
+
+int gt_proj_backward_group(gt_engine *e, int32_t n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dY,
+                           const float *X, float *dX, int32_t T, int32_t flags) {
+    if (!e || !w || !dY) return fail(GT_ERR_INVALID, "gt_proj_backward_group: null argument");
+    if (n < 1 || n > kMaxGroup) return fail(GT_ERR_INVALID, "a group holds 1 to %d projections (got %d)", kMaxGroup, n);
+    if (T <= 0) return fail(GT_ERR_INVALID, "T must be positive (got %d)", T);
+    for (int j = 0; j < n; j++) {
+        if (!w[j] || !dY[j]) return fail(GT_ERR_INVALID, "gt_proj_backward_group: member %d is null", j);
+        if (w[j]->dev.K != w[0]->dev.K) return fail(GT_ERR_INVALID, "members of a group share their input: in_features %d vs %d", w[j]->dev.K, w[0]->dev.K);
+        if (ad && ad[j] && (ad[j]->in != w[j]->dev.K || ad[j]->out != w[j]->dev.N)) return fail(GT_ERR_INVALID, "adapter %d does not match its weight", j);
+        if (ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && !X) return fail(GT_ERR_INVALID, "gt_proj_backward_group: X is required for the adapter gradients");
+    }
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) {
+        for (int j = 0; j < n; j++) {
+            int rc = gt_proj_backward(e, w[j], ad ? ad[j] : nullptr, dY[j], X, dX, T, flags);
+            if (rc != GT_OK) return rc;
+        }
+        return GT_OK;
+    }
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return backward_group_device(e, n, w, ad, dY, X, dX, T, flags);
 }
 
 int gt_launch_gemm_batch(gt_engine *e, const gt_weight *w, float *dY_out, const float *dX_in, int32_t batch, float *d_residual) {

@@ -59,6 +59,31 @@ cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed,
 cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
                               int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s);
 cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s);
+// Grouped forms: adapters of projections that share X go through one pass over it; the dY passes of several members
+// are one launch.  x16 / dy16 (may be null) receive the 16-bit copies.
+struct LoraXaJob {
+    const float *A;
+    float *low_zeroed;
+    int R;
+};
+struct LoraDyJob {
+    const float *dY, *low, *B;
+    float *dB, *dLow_zeroed;
+    void *dy16;
+    int ld16;
+    float scaling;
+    int N, R;
+};
+struct LoraDaJob {
+    const float *dLow;
+    float *dA;
+    float scaling;
+    int R;
+};
+cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, void *x16, int ldx16, int fp16, int T, int K,
+                                 cudaStream_t s);
+cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, cudaStream_t s);
+cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s);
 
 // ---- tcgen05 kernels (gt_umma_gemm.cu) ------------------------------------------------------------------
 struct UmmaLaunch {

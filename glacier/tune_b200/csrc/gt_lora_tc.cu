@@ -5,7 +5,9 @@
 // They replace the host loops of src/Glacier.Tune/Kernels/LoraKernels.cs:35-54,191-291.  Operands are rounded to
 // TF32 (10-bit mantissa, round to nearest) when they are staged in shared memory, products accumulate in fp32 in
 // warp-level m16n8k8 MMAs, and partial sums leave the block through fp32 atomics; the exact-fp32 CUDA-core versions
-// in gt_fp32_kernels.cu serve the validation modes.  Each launch handles 16 ranks [r0, r0 + 16).
+// in gt_fp32_kernels.cu serve the validation modes.  A launch handles up to three 16-rank chunks: the adapters of
+// projections that share their input (q, k, v; gate, up) go through one pass over X, and the dY passes of a group's
+// members are one launch (blockIdx.z picks the member).
 //
 // These kernels are bound by the HBM read of X / dY, not by arithmetic: the tile in shared memory is read once
 // from global memory and reused by every product that needs it.
@@ -43,6 +45,7 @@ constexpr int GS = TC + 4; // smem row stride of the activation tile (words): ro
 constexpr int RS = 24;     // smem row stride of the 16-wide rank tiles (words)
 
 constexpr int NI = (TT * TC / 4) / 256;     // float4 loads per thread and tile
+constexpr int kMaxChunks = 3;               // 16-rank chunks (of one or several adapters) served by one launch
 
 // A [TT x TC] fp32 tile of src[T, ncols] (rows t0.. below t_end, columns c0..) moves in two steps so that a block can
 // have the next tile's loads in flight while it computes on the current one:
@@ -91,76 +94,127 @@ __device__ __forceinline__ void tile_store(const float4 (&v)[NI], int t0, int t_
 }
 
 // ------------------------------------------------------------------------------------------------
-// low[T, R] += X[T, K] * A[K, R] over the block's K slice (grid.y slices of 128), fp32 atomics into low (pre-zeroed).
-// 8 warps = 4 token m-tiles x 2 rank n-tiles; each runs the 16 k-steps of the slice.
+// low_j[T, R_j] += X[T, K] * A_j[K, R_j] over the block's K slice (grid.y slices of 128) for up to kMaxChunks
+// 16-rank chunks that share X (the adapters of q, k, v or of gate, up): X is read and rounded once, fp32 atomics
+// into each low_j (pre-zeroed).  8 warps = 4 token m-tiles x 2 rank n-tiles per chunk, 16 k-steps each.
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_lora_xa_tc(const float *__restrict__ X, const float *__restrict__ A,
-                                                    float *__restrict__ low, uint16_t *__restrict__ x16, int ldx16, int fp16,
-                                                    int T, int K, int R, int r0) {
-    __shared__ __align__(16) uint32_t Xs[TT][GS];
-    __shared__ uint32_t As[TC][RS];
+struct XaChunk {
+    const float *A;
+    float *low;
+    int R, r0;
+};
+struct XaParams {
+    const float *X;
+    uint16_t *x16;
+    int ldx16, fp16, T, K, n;
+    XaChunk c[kMaxChunks];
+};
+
+__global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
+    uint32_t (*Xs)[GS] = reinterpret_cast<uint32_t (*)[GS]>(dyn_smem);
+    uint32_t (*As)[TC][RS] = reinterpret_cast<uint32_t (*)[TC][RS]>(dyn_smem + TT * GS);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.x * TT, k0 = blockIdx.y * TC;
-    const int rc = min(16, R - r0);
+    const int T = p.T, K = p.K;
     float4 v[NI];
-    tile_load(X, K, t0, T, k0, v, tid);
-    tile_store(v, t0, T, k0, Xs, r0 == 0 ? x16 : nullptr, ldx16, fp16, tid);
-    for (int i = tid; i < TC * 16; i += 256) {
-        const int k = i >> 4, r = i & 15;
-        As[k][r] = (k0 + k < K && r < rc) ? to_tf32(A[(int64_t)(k0 + k) * R + r0 + r]) : 0u;
+    tile_load(p.X, K, t0, T, k0, v, tid);
+    float av[kMaxChunks][8];       // this thread's 8 elements of each chunk's [128 x 16] tile of A, in flight with X
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++) {
+        if (j < p.n) {
+            const XaChunk c = p.c[j];
+            const int rc = min(16, c.R - c.r0);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int idx = tid + i * 256, k = idx >> 4, r = idx & 15;
+                av[j][i] = (k0 + k < K && r < rc) ? __ldg(&c.A[(int64_t)(k0 + k) * c.R + c.r0 + r]) : 0.f;
+            }
+        }
+    }
+    tile_store(v, t0, T, k0, Xs, p.x16, p.ldx16, p.fp16, tid);
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++) {
+        if (j < p.n) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int idx = tid + i * 256;
+                As[j][idx >> 4][idx & 15] = to_tf32(av[j][i]);
+            }
+        }
     }
     __syncthreads();
     const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int ks = 0; ks < TC / 8; ks++) {
-        const int kk = ks * 8;
-        mma_tf32(d, Xs[m0 + g][kk + t4], Xs[m0 + g + 8][kk + t4], Xs[m0 + g][kk + t4 + 4], Xs[m0 + g + 8][kk + t4 + 4],
-                 As[kk + t4][n0 + g], As[kk + t4 + 4][n0 + g]);
-    }
-    const int ta = t0 + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
-    if (ta < T) {
-        if (ra < rc) atomicAdd(&low[(int64_t)ta * R + r0 + ra], d[0]);
-        if (ra + 1 < rc) atomicAdd(&low[(int64_t)ta * R + r0 + ra + 1], d[1]);
-    }
-    if (tb < T) {
-        if (ra < rc) atomicAdd(&low[(int64_t)tb * R + r0 + ra], d[2]);
-        if (ra + 1 < rc) atomicAdd(&low[(int64_t)tb * R + r0 + ra + 1], d[3]);
+    for (int j = 0; j < kMaxChunks; j++) {
+        if (j >= p.n) break;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < TC / 8; ks++) {
+            const int kk = ks * 8;
+            mma_tf32(d, Xs[m0 + g][kk + t4], Xs[m0 + g + 8][kk + t4], Xs[m0 + g][kk + t4 + 4], Xs[m0 + g + 8][kk + t4 + 4],
+                     As[j][kk + t4][n0 + g], As[j][kk + t4 + 4][n0 + g]);
+        }
+        const XaChunk c = p.c[j];
+        const int rc = min(16, c.R - c.r0);
+        const int ta = t0 + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
+        if (ta < T) {
+            if (ra < rc) atomicAdd(&c.low[(int64_t)ta * c.R + c.r0 + ra], d[0]);
+            if (ra + 1 < rc) atomicAdd(&c.low[(int64_t)ta * c.R + c.r0 + ra + 1], d[1]);
+        }
+        if (tb < T) {
+            if (ra < rc) atomicAdd(&c.low[(int64_t)tb * c.R + c.r0 + ra], d[2]);
+            if (ra + 1 < rc) atomicAdd(&c.low[(int64_t)tb * c.R + c.r0 + ra + 1], d[3]);
+        }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// One pass over dY: the block owns a 128-column strip and a token group, walked in 64-token tiles.
+// One pass over dY_m per member m = blockIdx.z: the block owns a 128-column strip and a token group, walked in
+// 64-token tiles.
 //   dLow[t, r] += sum_c dY[t, c] * B[r, c]      4 m-tiles (tokens) x 2 n-tiles (ranks) over 8 warps, 16 k-steps
 //   dB[r, c]   += s * sum_t low[t, r] * dY[t, c] 1 m-tile (ranks) x 16 n-tiles (columns), 2 per warp, 8 k-steps
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_lora_dy_tc(const float *__restrict__ dY, const float *__restrict__ low,
-                                                    const float *__restrict__ B, float *__restrict__ dB, float *__restrict__ dLow,
-                                                    uint16_t *__restrict__ dy16, int ld16, int fp16, float scaling, int T, int N,
-                                                    int R, int r0, int tok_per_group) {
+struct DyMember {
+    const float *dY, *low, *B;
+    float *dB, *dLow;
+    uint16_t *dy16;
+    int ld16, N, R, r0;
+    float scaling;
+};
+struct DyParams {
+    int T, fp16, tok_per_group, n;
+    DyMember m[kMaxChunks];
+};
+
+__global__ void __launch_bounds__(256) k_lora_dy_tc(const DyParams p) {
     __shared__ __align__(16) uint32_t Gs[TT][GS];
     __shared__ uint32_t Bs[16][GS];
     __shared__ uint32_t Ls[TT][RS];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const DyMember m = p.m[blockIdx.z];
+    const int N = m.N, R = m.R, r0 = m.r0, T = p.T;
     const int c0 = blockIdx.x * TC;
-    const int tg0 = blockIdx.y * tok_per_group, tg1 = min(T, tg0 + tok_per_group);
+    if (c0 >= N) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int tg0 = blockIdx.y * p.tok_per_group, tg1 = min(T, tg0 + p.tok_per_group);
     const int rc = min(16, R - r0);
+    float4 v[NI];
+    tile_load(m.dY, N, tg0, tg1, c0, v, tid);
     for (int i = tid; i < 16 * TC; i += 256) {
         const int r = i / TC, c = i % TC;
-        Bs[r][c] = (r < rc && c0 + c < N) ? to_tf32(B[(int64_t)(r0 + r) * N + c0 + c]) : 0u;
+        Bs[r][c] = (r < rc && c0 + c < N) ? to_tf32(__ldg(&m.B[(int64_t)(r0 + r) * N + c0 + c])) : 0u;
     }
     float accB[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;      // dLow tiles
     const int cb = warp * 16;                                  // dB: this warp's two 8-column n-tiles
-    float4 v[NI];
-    tile_load(dY, N, tg0, tg1, c0, v, tid);
+    uint16_t *dy16 = r0 == 0 ? m.dy16 : nullptr;
     for (int ts = tg0; ts < tg1; ts += TT) {
         __syncthreads();
-        tile_store(v, ts, tg1, c0, Gs, r0 == 0 ? dy16 : nullptr, ld16, fp16, tid);
-        if (ts + TT < tg1) tile_load(dY, N, ts + TT, tg1, c0, v, tid);     // next tile's loads fly during the MMAs below
+        tile_store(v, ts, tg1, c0, Gs, dy16, m.ld16, p.fp16, tid);
+        if (ts + TT < tg1) tile_load(m.dY, N, ts + TT, tg1, c0, v, tid);     // next tile's loads fly during the MMAs below
         for (int i = tid; i < TT * 16; i += 256) {
             const int tt = i >> 4, r = i & 15;
-            Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(low[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
+            Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(m.low[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
         }
         __syncthreads();
         {
@@ -173,12 +227,12 @@ __global__ void __launch_bounds__(256) k_lora_dy_tc(const float *__restrict__ dY
             }
             const int ta = ts + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
             if (ta < tg1) {
-                if (ra < rc) atomicAdd(&dLow[(int64_t)ta * R + r0 + ra], d[0]);
-                if (ra + 1 < rc) atomicAdd(&dLow[(int64_t)ta * R + r0 + ra + 1], d[1]);
+                if (ra < rc) atomicAdd(&m.dLow[(int64_t)ta * R + r0 + ra], d[0]);
+                if (ra + 1 < rc) atomicAdd(&m.dLow[(int64_t)ta * R + r0 + ra + 1], d[1]);
             }
             if (tb < tg1) {
-                if (ra < rc) atomicAdd(&dLow[(int64_t)tb * R + r0 + ra], d[2]);
-                if (ra + 1 < rc) atomicAdd(&dLow[(int64_t)tb * R + r0 + ra + 1], d[3]);
+                if (ra < rc) atomicAdd(&m.dLow[(int64_t)tb * R + r0 + ra], d[2]);
+                if (ra + 1 < rc) atomicAdd(&m.dLow[(int64_t)tb * R + r0 + ra + 1], d[3]);
             }
         }
 #pragma unroll
@@ -195,40 +249,63 @@ __global__ void __launch_bounds__(256) k_lora_dy_tc(const float *__restrict__ dY
         const int c = c0 + cb + j * 8 + 2 * t4;
         const int ra = g, rb = g + 8;
         if (c < N) {
-            if (ra < rc) atomicAdd(&dB[(int64_t)(r0 + ra) * N + c], accB[j][0] * scaling);
-            if (rb < rc) atomicAdd(&dB[(int64_t)(r0 + rb) * N + c], accB[j][2] * scaling);
+            if (ra < rc) atomicAdd(&m.dB[(int64_t)(r0 + ra) * N + c], accB[j][0] * m.scaling);
+            if (rb < rc) atomicAdd(&m.dB[(int64_t)(r0 + rb) * N + c], accB[j][2] * m.scaling);
         }
         if (c + 1 < N) {
-            if (ra < rc) atomicAdd(&dB[(int64_t)(r0 + ra) * N + c + 1], accB[j][1] * scaling);
-            if (rb < rc) atomicAdd(&dB[(int64_t)(r0 + rb) * N + c + 1], accB[j][3] * scaling);
+            if (ra < rc) atomicAdd(&m.dB[(int64_t)(r0 + ra) * N + c + 1], accB[j][1] * m.scaling);
+            if (rb < rc) atomicAdd(&m.dB[(int64_t)(r0 + rb) * N + c + 1], accB[j][3] * m.scaling);
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// dA[k, r] += s * sum_t X[t, k] * dLow[t, r]: the block owns a 128-column strip of X and a token group.
-// 8 warps = 8 m-tiles of 16 columns; each covers both rank n-tiles over the 8 token k-steps of a tile.
+// dA_j[k, r] += s_j * sum_t X[t, k] * dLow_j[t, r] for up to kMaxChunks 16-rank chunks that share X: the block owns
+// a 128-column strip of X and a token group.  8 warps = 8 m-tiles of 16 columns; each covers both rank n-tiles of
+// every chunk over the 8 token k-steps of a tile.
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_lora_da_tc(const float *__restrict__ X, const float *__restrict__ dLow,
-                                                    float *__restrict__ dA, float scaling, int T, int K, int R, int r0,
-                                                    int tok_per_group) {
-    __shared__ __align__(16) uint32_t Xs[TT][GS];
-    __shared__ uint32_t Ls[TT][RS];
+struct DaChunk {
+    const float *dLow;
+    float *dA;
+    float scaling;
+    int R, r0;
+};
+struct DaParams {
+    const float *X;
+    int T, K, n, tok_per_group;
+    DaChunk c[kMaxChunks];
+};
+
+__global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
+    uint32_t (*Xs)[GS] = reinterpret_cast<uint32_t (*)[GS]>(dyn_smem);
+    uint32_t (*Ls)[TT][RS] = reinterpret_cast<uint32_t (*)[TT][RS]>(dyn_smem + TT * GS);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int T = p.T, K = p.K;
     const int k0 = blockIdx.x * TC;
-    const int tg0 = blockIdx.y * tok_per_group, tg1 = min(T, tg0 + tok_per_group);
-    const int rc = min(16, R - r0);
+    const int tg0 = blockIdx.y * p.tok_per_group, tg1 = min(T, tg0 + p.tok_per_group);
     const int m0 = warp * 16;
-    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float acc[kMaxChunks][2][4];
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) acc[j][i][0] = acc[j][i][1] = acc[j][i][2] = acc[j][i][3] = 0.f;
     float4 v[NI];
-    tile_load(X, K, tg0, tg1, k0, v, tid);
+    tile_load(p.X, K, tg0, tg1, k0, v, tid);
     for (int ts = tg0; ts < tg1; ts += TT) {
         __syncthreads();
         tile_store(v, ts, tg1, k0, Xs, nullptr, 0, 0, tid);
-        if (ts + TT < tg1) tile_load(X, K, ts + TT, tg1, k0, v, tid);      // next tile's loads fly during the MMAs below
-        for (int i = tid; i < TT * 16; i += 256) {
-            const int tt = i >> 4, r = i & 15;
-            Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(dLow[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
+        if (ts + TT < tg1) tile_load(p.X, K, ts + TT, tg1, k0, v, tid);      // next tile's loads fly during the MMAs below
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; j++) {
+            if (j < p.n) {
+                const DaChunk c = p.c[j];
+                const int rc = min(16, c.R - c.r0);
+                for (int i = tid; i < TT * 16; i += 256) {
+                    const int tt = i >> 4, r = i & 15;
+                    Ls[j][tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(c.dLow[(int64_t)(ts + tt) * c.R + c.r0 + r]) : 0u;
+                }
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -237,19 +314,31 @@ __global__ void __launch_bounds__(256) k_lora_da_tc(const float *__restrict__ X,
             const uint32_t a0 = Xs[kk + t4][m0 + g], a1 = Xs[kk + t4][m0 + g + 8], a2 = Xs[kk + t4 + 4][m0 + g],
                            a3 = Xs[kk + t4 + 4][m0 + g + 8];
 #pragma unroll
-            for (int j = 0; j < 2; j++) mma_tf32(acc[j], a0, a1, a2, a3, Ls[kk + t4][j * 8 + g], Ls[kk + t4 + 4][j * 8 + g]);
+            for (int j = 0; j < kMaxChunks; j++) {
+                if (j < p.n) {
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+                        mma_tf32(acc[j][i], a0, a1, a2, a3, Ls[j][kk + t4][i * 8 + g], Ls[j][kk + t4 + 4][i * 8 + g]);
+                }
+            }
         }
     }
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int ka = k0 + m0 + g, kb = ka + 8, r = j * 8 + 2 * t4;
-        if (ka < K) {
-            if (r < rc) atomicAdd(&dA[(int64_t)ka * R + r0 + r], acc[j][0] * scaling);
-            if (r + 1 < rc) atomicAdd(&dA[(int64_t)ka * R + r0 + r + 1], acc[j][1] * scaling);
-        }
-        if (kb < K) {
-            if (r < rc) atomicAdd(&dA[(int64_t)kb * R + r0 + r], acc[j][2] * scaling);
-            if (r + 1 < rc) atomicAdd(&dA[(int64_t)kb * R + r0 + r + 1], acc[j][3] * scaling);
+    for (int j = 0; j < kMaxChunks; j++) {
+        if (j >= p.n) break;
+        const DaChunk c = p.c[j];
+        const int rc = min(16, c.R - c.r0);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int ka = k0 + m0 + g, kb = ka + 8, r = i * 8 + 2 * t4;
+            if (ka < K) {
+                if (r < rc) atomicAdd(&c.dA[(int64_t)ka * c.R + c.r0 + r], acc[j][i][0] * c.scaling);
+                if (r + 1 < rc) atomicAdd(&c.dA[(int64_t)ka * c.R + c.r0 + r + 1], acc[j][i][1] * c.scaling);
+            }
+            if (kb < K) {
+                if (r < rc) atomicAdd(&c.dA[(int64_t)kb * c.R + c.r0 + r], acc[j][i][2] * c.scaling);
+                if (r + 1 < rc) atomicAdd(&c.dA[(int64_t)kb * c.R + c.r0 + r + 1], acc[j][i][3] * c.scaling);
+            }
         }
     }
 }
@@ -265,46 +354,132 @@ void pick_groups(int strips, int T, int &groups, int &tpg) {
     groups = (T + tpg - 1) / tpg;
 }
 
+constexpr size_t kXsBytes = (size_t)TT * GS * 4;
+constexpr size_t kAsBytes = (size_t)TC * RS * 4;       // per chunk, k_lora_xa_tc
+constexpr size_t kLsBytes = (size_t)TT * RS * 4;       // per chunk, k_lora_da_tc
+
+cudaError_t allow_dyn_smem() {
+    static cudaError_t done = [] {
+        cudaError_t e = cudaFuncSetAttribute(k_lora_xa_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kXsBytes + kMaxChunks * kAsBytes));
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(k_lora_da_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kXsBytes + kMaxChunks * kLsBytes));
+    }();
+    return done;
+}
+
 }  // namespace
+
+cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, void *x16, int ldx16, int fp16, int T, int K,
+                                 cudaStream_t s) {
+    if (T <= 0 || K <= 0 || n <= 0) return cudaSuccess;
+    cudaError_t e = allow_dyn_smem();
+    if (e != cudaSuccess) return e;
+    dim3 grid((T + TT - 1) / TT, (K + TC - 1) / TC);
+    XaParams p{};
+    p.X = X;
+    p.x16 = (uint16_t *)x16;      // written by the first launch only
+    p.ldx16 = ldx16;
+    p.fp16 = fp16;
+    p.T = T;
+    p.K = K;
+    auto flush = [&]() -> cudaError_t {
+        if (p.n == 0) return cudaSuccess;
+        k_lora_xa_tc<<<grid, 256, kXsBytes + p.n * kAsBytes, s>>>(p);
+        p.n = 0;
+        p.x16 = nullptr;
+        return cudaGetLastError();
+    };
+    for (int j = 0; j < n; j++)
+        for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
+            p.c[p.n++] = XaChunk{jobs[j].A, jobs[j].low_zeroed, jobs[j].R, r0};
+            if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
+        }
+    return flush();
+}
+
+cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, cudaStream_t s) {
+    if (T <= 0 || n <= 0) return cudaSuccess;
+    int strips_sum = 0, strips_max = 0;
+    for (int j = 0; j < n; j++) {
+        const int st = (jobs[j].N + TC - 1) / TC;
+        strips_sum += st;
+        strips_max = st > strips_max ? st : strips_max;
+    }
+    int groups, tpg;
+    pick_groups(strips_sum, T, groups, tpg);
+    DyParams p{};
+    p.T = T;
+    p.fp16 = fp16;
+    p.tok_per_group = tpg;
+    auto flush = [&]() -> cudaError_t {
+        if (p.n == 0) return cudaSuccess;
+        k_lora_dy_tc<<<dim3(strips_max, groups, p.n), 256, 0, s>>>(p);
+        p.n = 0;
+        return cudaGetLastError();
+    };
+    cudaError_t e;
+    // rank chunk 0 of every member first (it also writes the 16-bit copy of dY), then the higher chunks
+    for (int r0 = 0;; r0 += 16) {
+        bool any = false;
+        for (int j = 0; j < n; j++) {
+            const LoraDyJob &b = jobs[j];
+            if (r0 >= b.R || b.N <= 0) continue;
+            any = true;
+            DyMember m{};
+            m.dY = b.dY; m.low = b.low; m.B = b.B; m.dB = b.dB; m.dLow = b.dLow_zeroed; m.dy16 = (uint16_t *)b.dy16;
+            m.ld16 = b.ld16; m.N = b.N; m.R = b.R; m.r0 = r0; m.scaling = b.scaling;
+            p.m[p.n++] = m;
+            if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
+        }
+        if (!any) break;
+    }
+    return flush();
+}
+
+cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s) {
+    if (T <= 0 || K <= 0 || n <= 0) return cudaSuccess;
+    cudaError_t e = allow_dyn_smem();
+    if (e != cudaSuccess) return e;
+    const int strips = (K + TC - 1) / TC;
+    int groups, tpg;
+    pick_groups(strips, T, groups, tpg);
+    DaParams p{};
+    p.X = X;
+    p.T = T;
+    p.K = K;
+    p.tok_per_group = tpg;
+    auto flush = [&]() -> cudaError_t {
+        if (p.n == 0) return cudaSuccess;
+        k_lora_da_tc<<<dim3(strips, groups), 256, kXsBytes + p.n * kLsBytes, s>>>(p);
+        p.n = 0;
+        return cudaGetLastError();
+    };
+    for (int j = 0; j < n; j++)
+        for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
+            p.c[p.n++] = DaChunk{jobs[j].dLow, jobs[j].dA, jobs[j].scaling, jobs[j].R, r0};
+            if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
+        }
+    return flush();
+}
 
 cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed, void *x16, int ldx16, int fp16, int T, int K,
                               int R, cudaStream_t s) {
-    if (T <= 0 || K <= 0 || R <= 0) return cudaSuccess;
-    dim3 grid((T + TT - 1) / TT, (K + TC - 1) / TC);
-    for (int r0 = 0; r0 < R; r0 += 16) {
-        k_lora_xa_tc<<<grid, 256, 0, s>>>(X, A, low_zeroed, (uint16_t *)x16, ldx16, fp16, T, K, R, r0);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-    }
-    return cudaSuccess;
+    if (R <= 0) return cudaSuccess;
+    const LoraXaJob job{A, low_zeroed, R};
+    return launch_lora_xa_group(X, &job, 1, x16, ldx16, fp16, T, K, s);
 }
 
 cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
                               int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s) {
-    if (T <= 0 || N <= 0 || R <= 0) return cudaSuccess;
-    const int strips = (N + TC - 1) / TC;
-    int groups, tpg;
-    pick_groups(strips, T, groups, tpg);
-    for (int r0 = 0; r0 < R; r0 += 16) {
-        k_lora_dy_tc<<<dim3(strips, groups), 256, 0, s>>>(dY, low, B, dB, dLow_zeroed, (uint16_t *)dy16, ld16, fp16, scaling, T, N,
-                                                          R, r0, tpg);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-    }
-    return cudaSuccess;
+    if (N <= 0 || R <= 0) return cudaSuccess;
+    const LoraDyJob job{dY, low, B, dB, dLow_zeroed, dy16, ld16, scaling, N, R};
+    return launch_lora_dy_group(&job, 1, fp16, T, s);
 }
 
 cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s) {
-    if (T <= 0 || K <= 0 || R <= 0) return cudaSuccess;
-    const int strips = (K + TC - 1) / TC;
-    int groups, tpg;
-    pick_groups(strips, T, groups, tpg);
-    for (int r0 = 0; r0 < R; r0 += 16) {
-        k_lora_da_tc<<<dim3(strips, groups), 256, 0, s>>>(X, dLow, dA, scaling, T, K, R, r0, tpg);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-    }
-    return cudaSuccess;
+    if (R <= 0) return cudaSuccess;
+    const LoraDaJob job{dLow, dA, scaling, R};
+    return launch_lora_da_group(X, &job, 1, T, K, s);
 }
 
 }  // namespace gt

@@ -147,6 +147,18 @@ GT_API int gt_proj_forward(gt_engine *eng, const gt_weight *w, gt_adapter *adapt
 GT_API int gt_proj_backward(gt_engine *eng, const gt_weight *w, gt_adapter *adapter_or_null, const float *dY,
                             const float *X, float *dX_accum_or_null, int32_t T, int32_t flags);
 
+/* Replaces: GpuLoraEngine.ForwardQKV and the gate/up half of ForwardFfn
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:205-245,247-364): n (1..3) projections of the SAME input X,
+ * Y[j] = X * W_j^T + bias_j + scaling_j*(X*A_j)*B_j.  With device pointers and members of one quantization type the
+ * group costs one pass over X and one GEMM launch; otherwise it runs as n gt_proj_forward calls. */
+GT_API int gt_proj_forward_group(gt_engine *eng, int32_t n, const gt_weight *const *weights, gt_adapter *const *adapters_or_null,
+                                 const float *X, float *const *Y, int32_t T, int32_t flags);
+/* Replaces: the q|k|v and gate|up LoraAdapter.Backward calls of a block plus the sum of their input gradients
+ * (src/Glacier.Tune/Model/TransformerBlock.cs:660-663,812-816): dX += sum_j (dY[j] * W_j + adapter term j) into ONE
+ * buffer (dX may be NULL: gradients of the adapters only); dA_j, dB_j accumulate. */
+GT_API int gt_proj_backward_group(gt_engine *eng, int32_t n, const gt_weight *const *weights, gt_adapter *const *adapters_or_null,
+                                  const float *const *dY, const float *X, float *dX_accum_or_null, int32_t T, int32_t flags);
+
 /* Replaces: GpuLoraEngine.LaunchGemmBatch(type, dY, dX, dW, kCols, mRows, batch, dBias, dResidual)
  * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:83-129): device pointers, asynchronous.
  * Y (may be NULL) = X*W^T + bias; residual (may be NULL) += X*W^T + bias, as the reference kernels do

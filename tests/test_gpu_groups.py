@@ -1,0 +1,200 @@
+"""GPU parity of the grouped projection calls (q,k,v and gate,up of a block): several projections of one input in
+one launch, and their input gradients summed into one buffer, against the CPU oracle member by member."""
+import numpy as np
+import pytest
+
+from glacier.tune_b200 import synth as S
+
+pytestmark = pytest.mark.gpu
+
+TOL = {0: 2e-2, 1: 1e-3, 2: 1e-3}
+LTOL = {0: 5e-3, 1: 1e-3, 2: 1e-3}
+
+
+@pytest.fixture(scope="module")
+def G():
+    from glacier.tune_b200 import capi
+    return capi
+
+
+@pytest.fixture(scope="module")
+def eng(G):
+    e = G.Engine(0, G.MATH_BF16)
+    yield e
+    e.close()
+
+
+def _members(qtype, Ns, K, T, seed, adapted, biased):
+    """Projection cases that share one input X; member j has an adapter / a bias where the masks say so."""
+    cs = []
+    for j, N in enumerate(Ns):
+        c = S.make_projection_case(qtype, N, K, T, seed=seed + 17 * j, with_bias=True)
+        c["x"] = cs[0]["x"] if cs else c["x"]
+        c["lora"], c["has_bias"] = adapted[j], biased[j]
+        cs.append(c)
+    return cs
+
+
+def _reference(oracle, cs):
+    K, T = cs[0]["K"], cs[0]["T"]
+    dx = np.zeros((T, K), np.float64)
+    ys, das, dbs = [], [], []
+    for c in cs:
+        qt, N = c["qtype"], c["N"]
+        y = oracle.matmul_batch(qt, c["w"], c["x"], K, N, T, c["bias"] if c["has_bias"] else None, f64=True)
+        dx += oracle.base_backward_f64(qt, c["w"], c["dy"], K, N, T)
+        da = db = None
+        if c["lora"]:
+            X, dY, A, B = (c[k].astype(np.float64) for k in ("x", "dy", "a", "b"))
+            s = c["scaling"]
+            dlow = dY @ B.T
+            y = y + s * (X @ A) @ B
+            dx += s * dlow @ A.T
+            da, db = s * X.T @ dlow, s * (X @ A).T @ dY
+        ys.append(y)
+        das.append(da)
+        dbs.append(db)
+    return ys, dx, das, dbs
+
+
+def _upload(eng, cs):
+    ws, ads = [], []
+    for c in cs:
+        ws.append(eng.upload_weight(c["qtype"], c["w"], c["N"], c["K"], c["bias"] if c["has_bias"] else None))
+        ad = None
+        if c["lora"]:
+            ad = eng.create_adapter(c["K"], c["N"], c["rank"], c["alpha"])
+            ad.upload(c["a"], c["b"])
+        ads.append(ad)
+    return ws, ads
+
+
+def _free(ws, ads):
+    for w in ws:
+        w.free()
+    for a in ads:
+        if a:
+            a.free()
+
+
+GROUPS = [
+    # qtype, member out_features, K, T, adapters, biases
+    (S.TYPE_Q4_K, (512, 128, 128), 512, 17, (1, 0, 1), (1, 1, 1)),        # q,k,v with grouped-query widths
+    (S.TYPE_Q4_K, (512, 128, 128), 512, 300, (1, 1, 1), (1, 1, 0)),
+    (S.TYPE_Q4_K, (384, 384), 768, 512, (1, 1), (0, 0)),                 # gate,up; odd tile count per member
+    (S.TYPE_Q4_K, (640, 200), 256, 600, (0, 0), (0, 1)),                 # no adapters, ragged rows, two token chunks
+    (S.TYPE_Q6_K, (256, 128, 128), 512, 96, (1, 0, 1), (1, 0, 1)),
+    (S.TYPE_Q4_K, (256, 256), 3584, 512, (1, 1), (0, 0)),                # deep K (split across CTAs)
+]
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("qtype,Ns,K,T,adapted,biased", GROUPS)
+def test_group_forward_backward_parity(G, eng, oracle, mode, qtype, Ns, K, T, adapted, biased):
+    import torch
+    if mode == 2 and T * sum(Ns) * K > 2e8:
+        pytest.skip("fp32 validation kernels are checked on the smaller shapes")
+    cs = _members(qtype, Ns, K, T, seed=K + T, adapted=adapted, biased=biased)
+    eng.set_math_mode(mode)
+    ws, ads = _upload(eng, cs)
+    X = torch.from_numpy(cs[0]["x"]).cuda()
+    Ys = [torch.full((T, c["N"]), 7.0, device="cuda") for c in cs]          # stale contents must be overwritten
+    dYs = [torch.from_numpy(c["dy"]).cuda() for c in cs]
+    prior = torch.full((T, K), 0.5, device="cuda")
+    dX = prior.clone()
+    eng.forward_group(ws, ads, X, Ys)
+    eng.backward_group(ws, ads, dYs, X, dX, flags=G.FLAG_REUSE_LOW)
+    eng.sync()
+    ys, dxr, das, dbs = _reference(oracle, cs)
+    for j, c in enumerate(cs):
+        assert oracle.rel_fro(Ys[j].cpu().numpy(), ys[j]) < TOL[mode], (j, "Y")
+        if c["lora"]:
+            da, db = ads[j].grads()
+            assert oracle.rel_fro(da, das[j]) < LTOL[mode] and oracle.rel_fro(db, dbs[j]) < LTOL[mode], (j, "dA dB")
+    assert oracle.rel_fro((dX - prior).cpu().numpy(), dxr) < TOL[mode]
+    _free(ws, ads)
+
+
+def test_group_equals_member_calls(G, eng, oracle):
+    """The grouped launch and the per-projection calls run the same arithmetic per output tile; they differ only by
+    the order of fp32 atomic sums (X*A partial sums, split-K partial tiles) and what a last-bit change of X*A does
+    after its rounding to bf16."""
+    import torch
+    cs = _members(S.TYPE_Q4_K, (512, 128, 128), 512, 200, seed=5, adapted=(1, 1, 1), biased=(1, 1, 1))
+    eng.set_math_mode(0)
+    ws, ads = _upload(eng, cs)
+    X = torch.from_numpy(cs[0]["x"]).cuda()
+    dYs = [torch.from_numpy(c["dy"]).cuda() for c in cs]
+    Yg = [torch.empty((200, c["N"]), device="cuda") for c in cs]
+    Ym = [torch.empty((200, c["N"]), device="cuda") for c in cs]
+    eng.forward_group(ws, ads, X, Yg)
+    dXg = torch.zeros((200, 512), device="cuda")
+    eng.backward_group(ws, ads, dYs, X, dXg)
+    eng.sync()
+    grads_g = [a.grads() for a in ads]
+    for a in ads:
+        a.zero_grads()
+    dXm = torch.zeros((200, 512), device="cuda")
+    for j in range(3):
+        eng.forward(ws[j], ads[j], X, Ym[j])
+        eng.backward(ws[j], ads[j], dYs[j], X, dXm)
+    eng.sync()
+    for j in range(3):
+        assert oracle.rel_fro(Yg[j].cpu().numpy(), Ym[j].cpu().numpy()) < 1e-3
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(grads_g[j][0], da) < 1e-4 and oracle.rel_fro(grads_g[j][1], db) < 1e-4
+    assert oracle.rel_fro(dXg.cpu().numpy(), dXm.cpu().numpy()) < 1e-3
+    _free(ws, ads)
+
+
+def test_group_host_buffers_and_mixed_types(G, eng, oracle):
+    """Host buffers and members of different quantization types are served member by member with the same results."""
+    import torch
+    a = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 40, seed=3, with_bias=True)
+    b = S.make_projection_case(S.TYPE_Q6_K, 128, 512, 40, seed=4, with_bias=True)
+    b["x"] = a["x"]
+    for c in (a, b):
+        c["lora"], c["has_bias"] = True, True
+    cs = [a, b]
+    eng.set_math_mode(0)
+    ws, ads = _upload(eng, cs)
+    ys, dxr, das, dbs = _reference(oracle, cs)
+    # host buffers
+    Ys = [np.empty((40, c["N"]), np.float32) for c in cs]
+    dX = np.zeros((40, 512), np.float32)
+    eng.forward_group(ws, ads, a["x"], Ys)
+    eng.backward_group(ws, ads, [c["dy"] for c in cs], a["x"], dX)
+    for j in range(2):
+        assert oracle.rel_fro(Ys[j], ys[j]) < 2e-2
+    assert oracle.rel_fro(dX, dxr) < 2e-2
+    # device buffers, mixed types
+    for ad in ads:
+        ad.zero_grads()
+    X = torch.from_numpy(a["x"]).cuda()
+    Yd = [torch.empty((40, c["N"]), device="cuda") for c in cs]
+    dXd = torch.zeros((40, 512), device="cuda")
+    eng.forward_group(ws, ads, X, Yd)
+    eng.backward_group(ws, ads, [torch.from_numpy(c["dy"]).cuda() for c in cs], X, dXd)
+    eng.sync()
+    for j in range(2):
+        assert oracle.rel_fro(Yd[j].cpu().numpy(), ys[j]) < 2e-2
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(da, das[j]) < 5e-3 and oracle.rel_fro(db, dbs[j]) < 5e-3
+    assert oracle.rel_fro(dXd.cpu().numpy(), dxr) < 2e-2
+    _free(ws, ads)
+
+
+def test_group_error_paths(G, eng):
+    import torch
+    a = S.make_projection_case(S.TYPE_Q4_K, 128, 512, 8, seed=1)
+    b = S.make_projection_case(S.TYPE_Q4_K, 128, 256, 8, seed=2)
+    wa = eng.upload_weight(a["qtype"], a["w"], 128, 512)
+    wb = eng.upload_weight(b["qtype"], b["w"], 128, 256)
+    X = torch.zeros((8, 512), device="cuda")
+    Ys = [torch.zeros((8, 128), device="cuda") for _ in range(2)]
+    with pytest.raises(G.GtError, match="share their input"):
+        eng.forward_group([wa, wb], None, X, Ys)
+    with pytest.raises(G.GtError, match="1 to 3"):
+        eng.forward_group([wa] * 4, None, X, Ys * 2)
+    wa.free()
+    wb.free()
