@@ -248,24 +248,40 @@ def run_ours(args) -> None:
                 eng.forward_group(c["ws"], c["ads"], c["X"], c["Ys"])
             else:
                 eng.forward(c["ws"][0], c["ads"][0], c["X"], c["Ys"][0])
+        # X is the tensor the forward above saw: X*A kept by the adapter is reused (GT_FLAG_REUSE_LOW).  The reference
+        # hands Backward a zero-filled dX (AutogradScratchWorkspace.Wrap) and accumulates; GT_FLAG_DX_ASSIGN makes
+        # the call clear dX itself ("dX ="), --zero-dx keeps the separate fill and the "+=" call
+        bflags = G.FLAG_REUSE_LOW | (0 if args.zero_dx else G.FLAG_DX_ASSIGN)
         for c in reversed(calls):
-            c["dX"].zero_()     # the reference hands Backward a zero-filled dX (AutogradScratchWorkspace.Wrap)
-            # X is the tensor the forward above saw: X*A kept by the adapter is reused (GT_FLAG_REUSE_LOW)
+            if args.zero_dx:
+                c["dX"].zero_()
             if len(c["ws"]) > 1:
-                eng.backward_group(c["ws"], c["ads"], c["dYs"], c["X"], c["dX"], flags=G.FLAG_REUSE_LOW)
+                eng.backward_group(c["ws"], c["ads"], c["dYs"], c["X"], c["dX"], flags=bflags)
             else:
-                eng.backward(c["ws"][0], c["ads"][0], c["dYs"][0], c["X"], c["dX"], flags=G.FLAG_REUSE_LOW)
+                eng.backward(c["ws"][0], c["ads"][0], c["dYs"][0], c["X"], c["dX"], flags=bflags)
         if world > 1:
             eng.dp_allreduce(flat_grads, 1.0 / world)
 
+    # end to end: the same grouped calls on page-locked HOST buffers.  Every call stages its inputs to the device and its
+    # results back; GT_FLAG_HOST_ASYNC queues them (uploads, kernels and downloads of consecutive calls overlap) and
+    # gt_sync() completes the step, after which every Y and dX is in host memory.
+    hcalls = []
+    for names in groups:
+        ps = [by_name[n] for n in names]
+        hcalls.append(dict(ws=[p["w"] for p in ps], ads=[p["ad"] for p in ps], X=ps[0]["hx"].numpy(),
+                           Ys=[p["hy"].numpy() for p in ps], dYs=[p["hdy"].numpy() for p in ps], dX=ps[0]["hdx"].numpy()))
+    hflags = 0 if args.e2e_sync else G.FLAG_HOST_ASYNC
+    e2e_h2d = sum(c["X"].nbytes * 2 + sum(d.nbytes for d in c["dYs"]) for c in hcalls)
+    e2e_d2h = sum(sum(y.nbytes for y in c["Ys"]) + c["dX"].nbytes for c in hcalls)
+
     def step_host():
-        for p in layer:
-            eng.forward(p["w"], p["ad"], p["hx"].numpy(), p["hy"].numpy())
-        for p in reversed(layer):
-            eng.backward(p["w"], p["ad"], p["hdy"].numpy(), p["hx"].numpy(), p["hdx"].numpy())
+        for c in hcalls:
+            eng.forward_group(c["ws"], c["ads"], c["X"], c["Ys"], flags=hflags)
+        for c in reversed(hcalls):
+            eng.backward_group(c["ws"], c["ads"], c["dYs"], c["X"], c["dX"], flags=hflags | G.FLAG_DX_ASSIGN)
         if world > 1:
             eng.dp_allreduce(flat_grads, 1.0 / world)
-            eng.sync()
+        eng.sync()
 
     def barrier():
         if world > 1:
@@ -359,8 +375,7 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_s = float(t.item())
     e2e_value = world * fl * e2e_steps / e2e_s / 1e12
-    h2d = sum(4 * M_TOKENS * (p["K"] + p["N"] + p["K"] + p["K"]) for p in layer)   # X (fwd), dY, X, dX (bwd)
-    d2h = sum(4 * M_TOKENS * (p["N"] + p["K"]) for p in layer)                      # Y, dX
+    h2d, d2h = e2e_h2d, e2e_d2h     # per group: X (forward), every dY and X again (backward) up; every Y and one dX down
 
     _log("e2e done")
     if rank == 0:
@@ -395,7 +410,8 @@ def run_ours(args) -> None:
                        "launch": "cuda graph replay" if graph is not None else "eager",
                        "tokens_per_s": world * M_TOKENS * args.steps / (total_ms * 1e-3)},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps},
+                    "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
+                    "calls": "grouped host-buffer calls, " + ("synchronous" if args.e2e_sync else "queued (GT_FLAG_HOST_ASYNC) + gt_sync per step")},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline,
             "cpu_baseline": {"value": cpu_val, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
@@ -421,6 +437,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
+    ap.add_argument("--e2e-sync", action="store_true", help="end-to-end leg with synchronous host-buffer calls")
+    ap.add_argument("--zero-dx", action="store_true", help="zero-fill dX before each backward and accumulate into it")
     ap.add_argument("--no-group", action="store_true", help="one call per projection instead of q,k,v and gate,up groups")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -16,7 +16,7 @@ from . import build as _build
 TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
 MATH_BF16, MATH_FP16, MATH_FP32 = 0, 1, 2
 DIR_FORWARD, DIR_BACKWARD = 0, 1
-FLAG_DEVICE_PTRS, FLAG_NO_LORA, FLAG_REUSE_LOW = 1, 2, 4
+FLAG_DEVICE_PTRS, FLAG_NO_LORA, FLAG_REUSE_LOW, FLAG_DX_ASSIGN, FLAG_HOST_ASYNC = 1, 2, 4, 8, 16
 
 EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",

@@ -2,6 +2,8 @@
 // adapters, projection forward / backward.  Host-side orchestration only; kernels are in
 // gt_fp32_kernels.cu (CUDA cores) and gt_umma_gemm.cu (tcgen05).
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -66,6 +68,14 @@ struct Scratch {
 
 }  // namespace
 
+constexpr int kHostSlots = 3;
+constexpr int kSlotIn = 4, kSlotOut = 3;      // forward: X -> Y_j; backward: dY_j, X -> dX
+struct HostSlot {
+    Scratch in[kSlotIn], out[kSlotOut];
+    cudaEvent_t h2d_done = nullptr, compute_done = nullptr, d2h_done = nullptr;
+    bool used = false;
+};
+
 struct gt_engine {
     int device = 0;
     int math_mode = GT_MATH_BF16;
@@ -76,7 +86,12 @@ struct gt_engine {
     int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
     double *clip = nullptr;      // device double[2]
     Scratch x16, dy16, dlow, ytmp;
-    Scratch h_in0, h_in1, h_out;  // device staging for host-pointer calls
+    // Host-buffer calls: a ring of staging slots and two copy streams, so that the upload of one call, the kernels
+    // of the previous one and the download of the one before run at the same time (GT_FLAG_HOST_ASYNC), and a
+    // synchronous call still overlaps its own download with nothing in its way.
+    HostSlot slots[kHostSlots];
+    int slot_next = 0;
+    cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
     ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
     int dp_world = 1, dp_rank = 0;
     // profiling: CUDA-event pairs around every tensor-core GEMM launch, and a count of kernel launches
@@ -160,7 +175,8 @@ float *dlow_of(const gt_adapter *a, int T) { return (float *)((char *)a->low.p +
 
 // low_j = X * A_j for every listed adapter (they share X), and optionally the 16-bit copy of X.  One memset per
 // adapter clears low (the TF32 kernel sums into it) and dLow of the same step; one kernel pass reads X.
-int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, void *x16, int fp16, int T, int K) {
+int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, void *x16, int fp16, int T, int K,
+                const RowFill *fills = nullptr, int n_fills = 0) {
     LoraXaJob jobs[kMaxGroup];
     for (int j = 0; j < n; j++) {
         gt_adapter *a = ads[j];
@@ -171,8 +187,9 @@ int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, vo
         jobs[j] = LoraXaJob{a->A, low_of(a), a->rank};
     }
     if (e->math_mode == GT_MATH_BF16) {
-        GT_LAUNCH(e, launch_lora_xa_group(Xd, jobs, n, x16, K, fp16, T, K, e->stream));
+        GT_LAUNCH(e, launch_lora_xa_group(Xd, jobs, n, x16, K, fp16, T, K, fills, n_fills, e->stream));      // fills ride along
     } else {
+        for (int j = 0; j < n_fills; j++) GT_LAUNCH(e, launch_fill_rows(fills[j].dst, fills[j].bias, T, fills[j].N, e->stream));
         for (int j = 0; j < n; j++)
             GT_LAUNCH(e, launch_lora_low(Xd, jobs[j].A, jobs[j].low_zeroed, j == 0 ? x16 : nullptr, K, fp16, T, K, jobs[j].R, e->stream));
     }
@@ -181,7 +198,7 @@ int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, vo
 
 int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora);
 int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
-                    bool use_lora, bool reuse_low);
+                    bool use_lora, bool reuse_low, bool assign);
 
 bool group_tensor_ok(const gt_engine *e, int n, const gt_weight *const *w) {
     if (n < 1 || n > kMaxGroup) return false;
@@ -200,7 +217,6 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         if (ad && ad[j] && !lora[j]) ad[j]->low_T = 0;      // nothing kept for a later backward to reuse
     }
     if (!group_tensor_ok(e, n, w)) {
-        if (n == 1) return fail(GT_ERR_INVALID, "internal: single projection off the tensor path reached the group call");
         for (int j = 0; j < n; j++) {
             int rc = forward_device(e, w[j], ad ? ad[j] : nullptr, Xd, Yd[j], T, lora[j]);
             if (rc != GT_OK) return rc;
@@ -210,16 +226,6 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
     GT_CUDA(e->x16.reserve((size_t)T * K * 2));
-    gt_adapter *with[kMaxGroup];
-    int n_with = 0;
-    for (int j = 0; j < n; j++)
-        if (lora[j]) with[n_with++] = ad[j];
-    if (n_with) {
-        int rc = compute_low(e, with, n_with, Xd, e->x16.p, fp16, T, K);
-        if (rc != GT_OK) return rc;
-    } else {
-        GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
-    }
     UmmaLaunch m[kMaxGroup];
     for (int j = 0; j < n; j++) {
         const WeightDev &wd = w[j]->dev;
@@ -233,7 +239,6 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         m[j].ld_out = wd.N;
         m[j].bias = wd.bias;
         if (lora[j]) {
-            m[j].lora_act = low_of(ad[j]);
             m[j].lora_scale = ad[j]->scaling;
             m[j].lora_w = ad[j]->B;
             m[j].rank = ad[j]->rank;
@@ -242,13 +247,29 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         m[j].status = e->status;
         m[j].trace = e->trace;
     }
+    // split-K sums into the outputs: they start as the bias rows, written by the pass over X below
     const int splits = umma_group_splits(m, n, e->sm_count);
+    RowFill fills[kMaxGroup];
+    int n_fills = 0;
     for (int j = 0; j < n; j++) {
         m[j].splits = splits;
         if (splits > 1) {
-            GT_LAUNCH(e, launch_fill_rows(Yd[j], w[j]->dev.bias, T, w[j]->dev.N, e->stream));
+            fills[n_fills++] = RowFill{Yd[j], w[j]->dev.bias, w[j]->dev.N};
             m[j].out_prefilled = 1;
         }
+    }
+    gt_adapter *with[kMaxGroup];
+    int n_with = 0;
+    for (int j = 0; j < n; j++)
+        if (lora[j]) with[n_with++] = ad[j];
+    if (n_with) {
+        int rc = compute_low(e, with, n_with, Xd, e->x16.p, fp16, T, K, fills, n_fills);
+        if (rc != GT_OK) return rc;
+        for (int j = 0; j < n; j++)
+            if (lora[j]) m[j].lora_act = low_of(ad[j]);       // the adapter's scratch is allocated by now
+    } else {
+        GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
+        for (int j = 0; j < n_fills; j++) GT_LAUNCH(e, launch_fill_rows(fills[j].dst, fills[j].bias, T, fills[j].N, e->stream));
     }
     const char *msg = nullptr;
     cudaError_t ce = timed_umma_group(e, m, n, &msg);
@@ -275,7 +296,8 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
 // The adapter half of a backward: dB += s*low^T*dY, dLow = dY*B^T, dA += s*X^T*dLow for every member with an adapter
 // (one launch per product in the bf16 mode), and the 16-bit copy of each dY where dy16[j] is given.
 int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const bool *lora,
-                        const float *const *dYd, const float *Xd, void *const *dy16, const int *ld16, int T, bool reuse_low) {
+                        const float *const *dYd, const float *Xd, void *const *dy16, const int *ld16, int T, bool reuse_low,
+                        float *zero_dx) {
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
     const bool fast = e->math_mode == GT_MATH_BF16;      // TF32 warp-MMA reductions; exact fp32 otherwise
@@ -308,9 +330,12 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
         da[nl] = LoraDaJob{dlow_of(a, T), a->dA, a->scaling, a->rank};
         nl++;
     }
+    // "dX =" instead of "dX +=": the buffer is cleared by the pass over dY (or by a fill of its own)
+    const RowFill zero{zero_dx, nullptr, K};
+    if (zero_dx && !(fast && nl)) GT_LAUNCH(e, launch_fill_rows(zero_dx, nullptr, T, K, e->stream));
     if (!nl) return GT_OK;
     if (fast) {
-        GT_LAUNCH(e, launch_lora_dy_group(dy, nl, fp16, T, e->stream));
+        GT_LAUNCH(e, launch_lora_dy_group(dy, nl, fp16, T, zero_dx ? &zero : nullptr, zero_dx ? 1 : 0, e->stream));
         GT_LAUNCH(e, launch_lora_da_group(Xd, da, nl, T, K, e->stream));
     } else {
         for (int j = 0; j < nl; j++) {
@@ -328,10 +353,10 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
     bool lora[kMaxGroup];
     for (int j = 0; j < n; j++) lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0;
     const bool reuse_low = (flags & GT_FLAG_REUSE_LOW) != 0;
+    const bool assign = (flags & GT_FLAG_DX_ASSIGN) != 0 && dXd;
     if (!group_tensor_ok(e, n, w) || !dXd) {
-        if (n == 1) return fail(GT_ERR_INVALID, "internal: single projection off the tensor path reached the group call");
         for (int j = 0; j < n; j++) {
-            int rc = backward_device(e, w[j], ad ? ad[j] : nullptr, dYd[j], Xd, dXd, T, lora[j], reuse_low);
+            int rc = backward_device(e, w[j], ad ? ad[j] : nullptr, dYd[j], Xd, dXd, T, lora[j], reuse_low, assign && j == 0);
             if (rc != GT_OK) return rc;
         }
         return GT_OK;
@@ -348,7 +373,7 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
     }
     GT_CUDA(e->dy16.reserve(dy_total));
     for (int j = 0; j < n; j++) dy16[j] = (char *)e->dy16.p + dy_off[j];
-    int rc = lora_backward_group(e, n, w, ad, lora, dYd, Xd, dy16, ld16, T, reuse_low);
+    int rc = lora_backward_group(e, n, w, ad, lora, dYd, Xd, dy16, ld16, T, reuse_low, assign ? dXd : nullptr);
     if (rc != GT_OK) return rc;
     UmmaLaunch m[kMaxGroup];
     for (int j = 0; j < n; j++) {
@@ -380,19 +405,20 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
 
 // dX += dY*W (+ lora term); dA, dB accumulate.  Device pointers.
 int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
-                    bool use_lora, bool reuse_low) {
+                    bool use_lora, bool reuse_low, bool assign) {
     if (tensor_path(e, w) && dXd) {
-        const int flags = (use_lora ? 0 : GT_FLAG_NO_LORA) | (reuse_low ? GT_FLAG_REUSE_LOW : 0);
+        const int flags = (use_lora ? 0 : GT_FLAG_NO_LORA) | (reuse_low ? GT_FLAG_REUSE_LOW : 0) | (assign ? GT_FLAG_DX_ASSIGN : 0);
         return backward_group_device(e, 1, &w, &ad, &dYd, Xd, dXd, T, flags);
     }
     // exact fp32 kernels (validation mode, weights outside the tensor-core layout) or adapter gradients only
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
+    if (assign && dXd) GT_LAUNCH(e, launch_fill_rows(dXd, nullptr, T, K, e->stream));
     if (use_lora) {
         const bool lora = true;
         void *no16 = nullptr;
         const int ld16 = round8(N);
-        int rc = lora_backward_group(e, 1, &w, &ad, &lora, &dYd, Xd, &no16, &ld16, T, reuse_low);
+        int rc = lora_backward_group(e, 1, &w, &ad, &lora, &dYd, Xd, &no16, &ld16, T, reuse_low, nullptr);
         if (rc != GT_OK) return rc;
         if (dXd) GT_LAUNCH(e, launch_lora_dx_fp32(dlow_of(ad, T), ad->A, dXd, ad->scaling, T, K, ad->rank, e->stream));
     }
@@ -400,9 +426,112 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
     return GT_OK;
 }
 
+
+// ---- host-buffer calls -------------------------------------------------------------------------------------------
+int host_pipeline_init(gt_engine *e) {
+    if (e->s_h2d) return GT_OK;
+    GT_CUDA(cudaStreamCreateWithFlags(&e->s_h2d, cudaStreamNonBlocking));
+    GT_CUDA(cudaStreamCreateWithFlags(&e->s_d2h, cudaStreamNonBlocking));
+    for (HostSlot &sl : e->slots) {
+        GT_CUDA(cudaEventCreateWithFlags(&sl.h2d_done, cudaEventDisableTiming));
+        GT_CUDA(cudaEventCreateWithFlags(&sl.compute_done, cudaEventDisableTiming));
+        GT_CUDA(cudaEventCreateWithFlags(&sl.d2h_done, cudaEventDisableTiming));
+    }
+    return GT_OK;
+}
+
+HostSlot &next_slot(gt_engine *e) {
+    HostSlot &sl = e->slots[e->slot_next];
+    e->slot_next = (e->slot_next + 1) % kHostSlots;
+    return sl;
+}
+
+// A synchronous call returns with its outputs in the host buffers; an asynchronous one (pinned buffers) returns
+// once everything is queued, and gt_sync() completes it.
+int finish_host_call(gt_engine *e, int flags) {
+    if (flags & GT_FLAG_HOST_ASYNC) return GT_OK;
+    int rc = check_status(e);
+    GT_CUDA(cudaStreamSynchronize(e->s_d2h));
+    return rc;
+}
+
+int forward_host(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *X, float *const *Y, int T,
+                 int flags) {
+    int rc = host_pipeline_init(e);
+    if (rc != GT_OK) return rc;
+    HostSlot &sl = next_slot(e);
+    const size_t bx = (size_t)T * w[0]->dev.K * sizeof(float);
+    GT_CUDA(sl.in[0].reserve(bx));
+    float *Yd[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        GT_CUDA(sl.out[j].reserve((size_t)T * w[j]->dev.N * sizeof(float)));
+        Yd[j] = (float *)sl.out[j].p;
+    }
+    if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->s_h2d, sl.compute_done, 0));      // the slot's last call has read its inputs
+    GT_CUDA(cudaMemcpyAsync(sl.in[0].p, X, bx, cudaMemcpyHostToDevice, e->s_h2d));
+    GT_CUDA(cudaEventRecord(sl.h2d_done, e->s_h2d));
+    GT_CUDA(cudaStreamWaitEvent(e->stream, sl.h2d_done, 0));
+    if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->stream, sl.d2h_done, 0));         // ... and its outputs have left
+    rc = forward_group_device(e, n, w, ad, (const float *)sl.in[0].p, Yd, T, flags);
+    if (rc != GT_OK) return rc;
+    GT_CUDA(cudaEventRecord(sl.compute_done, e->stream));
+    GT_CUDA(cudaStreamWaitEvent(e->s_d2h, sl.compute_done, 0));
+    for (int j = 0; j < n; j++)
+        GT_CUDA(cudaMemcpyAsync(Y[j], Yd[j], (size_t)T * w[j]->dev.N * sizeof(float), cudaMemcpyDeviceToHost, e->s_d2h));
+    GT_CUDA(cudaEventRecord(sl.d2h_done, e->s_d2h));
+    sl.used = true;
+    return finish_host_call(e, flags);
+}
+
+int backward_host(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dY, const float *X,
+                  float *dX, int T, int flags) {
+    int rc = host_pipeline_init(e);
+    if (rc != GT_OK) return rc;
+    HostSlot &sl = next_slot(e);
+    const size_t bx = (size_t)T * w[0]->dev.K * sizeof(float);
+    const bool assign = (flags & GT_FLAG_DX_ASSIGN) != 0;
+    bool need_x = false;
+    for (int j = 0; j < n; j++) need_x = need_x || (ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0);
+    const float *dYd[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        GT_CUDA(sl.in[j].reserve((size_t)T * w[j]->dev.N * sizeof(float)));
+        dYd[j] = (const float *)sl.in[j].p;
+    }
+    if (need_x) GT_CUDA(sl.in[kSlotIn - 1].reserve(bx));
+    if (dX) GT_CUDA(sl.out[0].reserve(bx));
+    if (sl.used) {
+        GT_CUDA(cudaStreamWaitEvent(e->s_h2d, sl.compute_done, 0));
+        if (dX && !assign) GT_CUDA(cudaStreamWaitEvent(e->s_h2d, sl.d2h_done, 0));
+    }
+    for (int j = 0; j < n; j++)
+        GT_CUDA(cudaMemcpyAsync(sl.in[j].p, dY[j], (size_t)T * w[j]->dev.N * sizeof(float), cudaMemcpyHostToDevice, e->s_h2d));
+    if (need_x) GT_CUDA(cudaMemcpyAsync(sl.in[kSlotIn - 1].p, X, bx, cudaMemcpyHostToDevice, e->s_h2d));
+    // "dX +=": the reference uploads dX too and the kernel accumulates into it (GpuLoraEngine.Backward.cs:85-89)
+    if (dX && !assign) GT_CUDA(cudaMemcpyAsync(sl.out[0].p, dX, bx, cudaMemcpyHostToDevice, e->s_h2d));
+    GT_CUDA(cudaEventRecord(sl.h2d_done, e->s_h2d));
+    GT_CUDA(cudaStreamWaitEvent(e->stream, sl.h2d_done, 0));
+    if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->stream, sl.d2h_done, 0));
+    rc = backward_group_device(e, n, w, ad, dYd, need_x ? (const float *)sl.in[kSlotIn - 1].p : nullptr,
+                               dX ? (float *)sl.out[0].p : nullptr, T, flags);
+    if (rc != GT_OK) return rc;
+    GT_CUDA(cudaEventRecord(sl.compute_done, e->stream));
+    GT_CUDA(cudaStreamWaitEvent(e->s_d2h, sl.compute_done, 0));
+    if (dX) GT_CUDA(cudaMemcpyAsync(dX, sl.out[0].p, bx, cudaMemcpyDeviceToHost, e->s_d2h));
+    GT_CUDA(cudaEventRecord(sl.d2h_done, e->s_d2h));
+    sl.used = true;
+    return finish_host_call(e, flags);
+}
+
 }  // namespace
 
 namespace gt {
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("GT_PDL");      // off by default: measured no gain on the layer step (the GEMM CTAs hold
+        return v && v[0] == '1';               // the whole shared memory, so a dependent CTA cannot become resident early)
+    }();
+    return on;
+}
 EngineView engine_view(gt_engine *e) { return EngineView{e->device, e->math_mode, e->sm_count, e->stream, e->status, &e->mu}; }
 const WeightDev *weight_view(const gt_weight *w) { return &w->dev; }
 int set_last_error(int code, const char *text) { return fail(code, "%s", text); }
@@ -467,8 +596,19 @@ int gt_engine_destroy(gt_engine *e) {
     if (!e) return GT_OK;
     cudaSetDevice(e->device);
     if (e->stream) cudaStreamSynchronize(e->stream);
-    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->h_in0, &e->h_in1, &e->h_out};
+    if (e->s_h2d) cudaStreamSynchronize(e->s_h2d);
+    if (e->s_d2h) cudaStreamSynchronize(e->s_d2h);
+    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp};
     for (Scratch *s : all) s->release();
+    for (HostSlot &sl : e->slots) {
+        for (Scratch &b : sl.in) b.release();
+        for (Scratch &b : sl.out) b.release();
+        if (sl.h2d_done) cudaEventDestroy(sl.h2d_done);
+        if (sl.compute_done) cudaEventDestroy(sl.compute_done);
+        if (sl.d2h_done) cudaEventDestroy(sl.d2h_done);
+    }
+    if (e->s_h2d) cudaStreamDestroy(e->s_h2d);
+    if (e->s_d2h) cudaStreamDestroy(e->s_d2h);
     if (e->status) cudaFree(e->status);
     if (e->clip) cudaFree(e->clip);
     for (cudaEvent_t ev : e->ev_pool) cudaEventDestroy(ev);
@@ -489,7 +629,9 @@ int gt_sync(gt_engine *e) {
     if (!e) return fail(GT_ERR_INVALID, "engine is null");
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    return check_status(e);
+    int rc = check_status(e);                                  // drains the engine stream
+    if (e->s_d2h) GT_CUDA(cudaStreamSynchronize(e->s_d2h));      // and the downloads of asynchronous host-buffer calls
+    return rc;
 }
 
 int gt_debug_wait_selftest(gt_engine *e, int64_t limit_cycles) {
@@ -619,8 +761,8 @@ int gt_dequant_rows(gt_engine *e, const gt_weight *w, int64_t row0, int64_t nrow
     const size_t bytes = (size_t)nrows * w->dev.K * sizeof(float);
     float *dst = out;
     if (!(flags & GT_FLAG_DEVICE_PTRS)) {
-        GT_CUDA(e->h_out.reserve(bytes));
-        dst = (float *)e->h_out.p;
+        GT_CUDA(e->ytmp.reserve(bytes));
+        dst = (float *)e->ytmp.p;
     }
     GT_CUDA(launch_dequant_rows(w->dev.qtype, w->dev.data, w->dev.K, row0, nrows, dst, e->stream));
     if (!(flags & GT_FLAG_DEVICE_PTRS)) {
@@ -766,17 +908,11 @@ int gt_proj_forward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
     GT_CUDA(cudaSetDevice(e->device));
     // LoraAdapter.Forward: the delta is skipped when the adapter is disabled, scaling == 0, or B == 0
     // (B == 0 is decided on the device from the flag written at upload).
-    const bool use_lora = ad && !(flags & GT_FLAG_NO_LORA) && ad->rank > 0 && ad->scaling != 0.f;
-    const int N = w->dev.N, K = w->dev.K;
-    if (flags & GT_FLAG_DEVICE_PTRS) return forward_device(e, w, ad, X, Y, T, use_lora);
-    const size_t bx = (size_t)T * K * sizeof(float), by = (size_t)T * N * sizeof(float);
-    GT_CUDA(e->h_in0.reserve(bx));
-    GT_CUDA(e->h_out.reserve(by));
-    GT_CUDA(cudaMemcpyAsync(e->h_in0.p, X, bx, cudaMemcpyHostToDevice, e->stream));
-    int rc = forward_device(e, w, ad, (const float *)e->h_in0.p, (float *)e->h_out.p, T, use_lora);
-    if (rc != GT_OK) return rc;
-    GT_CUDA(cudaMemcpyAsync(Y, e->h_out.p, by, cudaMemcpyDeviceToHost, e->stream));
-    return check_status(e);
+    if (flags & GT_FLAG_DEVICE_PTRS) {
+        const bool use_lora = ad && !(flags & GT_FLAG_NO_LORA) && ad->rank > 0 && ad->scaling != 0.f;
+        return forward_device(e, w, ad, X, Y, T, use_lora);
+    }
+    return forward_host(e, 1, &w, &ad, X, &Y, T, flags);
 }
 
 int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dY, const float *X, float *dX, int32_t T,
@@ -788,25 +924,9 @@ int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const flo
     if (use_lora && !X) return fail(GT_ERR_INVALID, "gt_proj_backward: X is required for the adapter gradients");
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    const int N = w->dev.N, K = w->dev.K;
-    if (flags & GT_FLAG_DEVICE_PTRS) return backward_device(e, w, ad, dY, X, dX, T, use_lora, (flags & GT_FLAG_REUSE_LOW) != 0);
-    const size_t bx = (size_t)T * K * sizeof(float), by = (size_t)T * N * sizeof(float);
-    GT_CUDA(e->h_in0.reserve(by));
-    GT_CUDA(cudaMemcpyAsync(e->h_in0.p, dY, by, cudaMemcpyHostToDevice, e->stream));
-    if (use_lora) {
-        GT_CUDA(e->h_in1.reserve(bx));
-        GT_CUDA(cudaMemcpyAsync(e->h_in1.p, X, bx, cudaMemcpyHostToDevice, e->stream));
-    }
-    if (dX) {
-        // the reference uploads dX too: the kernel accumulates into it (GpuLoraEngine.Backward.cs:85-89)
-        GT_CUDA(e->h_out.reserve(bx));
-        GT_CUDA(cudaMemcpyAsync(e->h_out.p, dX, bx, cudaMemcpyHostToDevice, e->stream));
-    }
-    int rc = backward_device(e, w, ad, (const float *)e->h_in0.p, use_lora ? (const float *)e->h_in1.p : nullptr,
-                             dX ? (float *)e->h_out.p : nullptr, T, use_lora, (flags & GT_FLAG_REUSE_LOW) != 0);
-    if (rc != GT_OK) return rc;
-    if (dX) GT_CUDA(cudaMemcpyAsync(dX, e->h_out.p, bx, cudaMemcpyDeviceToHost, e->stream));
-    return check_status(e);
+    const bool assign = (flags & GT_FLAG_DX_ASSIGN) != 0;
+    if (flags & GT_FLAG_DEVICE_PTRS) return backward_device(e, w, ad, dY, X, dX, T, use_lora, (flags & GT_FLAG_REUSE_LOW) != 0, assign);
+    return backward_host(e, 1, &w, &ad, &dY, X, dX, T, flags);
 }
 
 int gt_proj_forward_group(gt_engine *e, int32_t n, const gt_weight *const *w, gt_adapter *const *ad, const float *X, float *const *Y,
@@ -819,15 +939,9 @@ int gt_proj_forward_group(gt_engine *e, int32_t n, const gt_weight *const *w, gt
         if (w[j]->dev.K != w[0]->dev.K) return fail(GT_ERR_INVALID, "members of a group share their input: in_features %d vs %d", w[j]->dev.K, w[0]->dev.K);
         if (ad && ad[j] && (ad[j]->in != w[j]->dev.K || ad[j]->out != w[j]->dev.N)) return fail(GT_ERR_INVALID, "adapter %d does not match its weight", j);
     }
-    if (!(flags & GT_FLAG_DEVICE_PTRS)) {
-        for (int j = 0; j < n; j++) {        // host buffers: the per-projection call stages each member
-            int rc = gt_proj_forward(e, w[j], ad ? ad[j] : nullptr, X, Y[j], T, flags);
-            if (rc != GT_OK) return rc;
-        }
-        return GT_OK;
-    }
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) return forward_host(e, n, w, ad, X, Y, T, flags);
     return forward_group_device(e, n, w, ad, X, Y, T, flags);
 }
 
@@ -842,15 +956,9 @@ int gt_proj_backward_group(gt_engine *e, int32_t n, const gt_weight *const *w, g
         if (ad && ad[j] && (ad[j]->in != w[j]->dev.K || ad[j]->out != w[j]->dev.N)) return fail(GT_ERR_INVALID, "adapter %d does not match its weight", j);
         if (ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && !X) return fail(GT_ERR_INVALID, "gt_proj_backward_group: X is required for the adapter gradients");
     }
-    if (!(flags & GT_FLAG_DEVICE_PTRS)) {
-        for (int j = 0; j < n; j++) {
-            int rc = gt_proj_backward(e, w[j], ad ? ad[j] : nullptr, dY[j], X, dX, T, flags);
-            if (rc != GT_OK) return rc;
-        }
-        return GT_OK;
-    }
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) return backward_host(e, n, w, ad, dY, X, dX, T, flags);
     return backward_group_device(e, n, w, ad, dY, X, dX, T, flags);
 }
 
@@ -881,7 +989,7 @@ int gt_launch_gemm_bwd(gt_engine *e, const gt_weight *w, float *dDX, const float
     if (batch <= 0) return fail(GT_ERR_INVALID, "batch must be positive (got %d)", batch);
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    return backward_device(e, w, nullptr, dDY, nullptr, dDX, batch, false, false);
+    return backward_device(e, w, nullptr, dDY, nullptr, dDX, batch, false, false, false);
 }
 
 int gt_grads_scale_clip(gt_engine *e, float *g_dev, int64_t n, float pre_scale, double max_norm, double *norm_out) {

@@ -1,6 +1,7 @@
 // CUDA-core kernels: exact dequantization, the fp32 validation GEMMs, and the rank-r LoRA products
 // (low = X*A, dB, dLow, dA) with fp32 accumulation.  The tensor-core GEMMs live in gt_umma_gemm.cu.
 #include "gt_internal.h"
+#include "gt_ptx.cuh"
 #include "gt_quant.cuh"
 
 namespace gt {
@@ -190,6 +191,8 @@ __device__ __forceinline__ uint16_t round16(float v, int fp16) {
 }
 
 __global__ void k_cast16(const float *__restrict__ src, uint16_t *__restrict__ dst, int rows, int cols, int ld, int fp16) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t total = (int64_t)rows * ld;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int r = (int)(i / ld), c = (int)(i % ld);
@@ -200,11 +203,12 @@ cudaError_t launch_cast16(const float *src, void *dst, int rows, int cols, int l
     const int64_t total = (int64_t)rows * ld_dst;
     if (total <= 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
-    k_cast16<<<blocks, 256, 0, s>>>(src, (uint16_t *)dst, rows, cols, ld_dst, fp16);
-    return cudaGetLastError();
+    return launch_k(k_cast16, dim3(blocks), dim3(256), 0, s, src, (uint16_t *)dst, rows, cols, ld_dst, fp16);
 }
 
 __global__ void k_fill_rows(float *__restrict__ Y, const float *__restrict__ bias, int T, int N) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t total = (int64_t)T * N;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
         Y[i] = bias ? bias[i % N] : 0.f;
@@ -213,8 +217,7 @@ cudaError_t launch_fill_rows(float *Y, const float *bias, int T, int N, cudaStre
     const int64_t total = (int64_t)T * N;
     if (total <= 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
-    k_fill_rows<<<blocks, 256, 0, s>>>(Y, bias, T, N);
-    return cudaGetLastError();
+    return launch_k(k_fill_rows, dim3(blocks), dim3(256), 0, s, Y, bias, T, N);
 }
 
 __global__ void k_add_inplace(float *__restrict__ dst, const float *__restrict__ src, int64_t n) {

@@ -80,9 +80,15 @@ struct LoraDaJob {
     float scaling;
     int R;
 };
+// dst[T, N] = bias[N] (or zero): up to three such fills ride along with a pass (the output of a split-K GEMM)
+struct RowFill {
+    float *dst;
+    const float *bias;
+    int N;
+};
 cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, void *x16, int ldx16, int fp16, int T, int K,
-                                 cudaStream_t s);
-cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, cudaStream_t s);
+                                 const RowFill *fills, int n_fills, cudaStream_t s);
+cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, const RowFill *fills, int n_fills, cudaStream_t s);
 cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s);
 
 // ---- tcgen05 kernels (gt_umma_gemm.cu) ------------------------------------------------------------------
@@ -128,6 +134,24 @@ struct EngineView {
     int *status;       // device int[4], bounded-wait codes of the tensor-core kernels
     void *mutex;       // std::mutex * serialising calls on the engine
 };
+// ---- launches with programmatic dependent launch (the kernel must call pdl_wait() before touching global memory).
+// Environment GT_PDL=1 turns the attribute on; the default is plain stream order.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace gt
 struct gt_engine;
 struct gt_weight;

@@ -15,6 +15,7 @@
 #include <cuda_fp16.h>
 
 #include "gt_internal.h"
+#include "gt_ptx.cuh"
 
 namespace gt {
 
@@ -46,6 +47,33 @@ constexpr int RS = 24;     // smem row stride of the 16-wide rank tiles (words)
 
 constexpr int NI = (TT * TC / 4) / 256;     // float4 loads per thread and tile
 constexpr int kMaxChunks = 3;               // 16-rank chunks (of one or several adapters) served by one launch
+
+// Row fills that ride along with a pass (the split-K GEMM that follows sums into its output, so the output starts as
+// the bias rows or as zero): dst[T, N] = bias[N] (or 0).  The blocks of the launch share each fill evenly.
+struct FillList {
+    int n;
+    struct Job {
+        float *dst;
+        const float *bias;
+        int N;
+        int64_t total;      // T * N
+    } f[kMaxChunks];
+};
+__device__ __forceinline__ void do_fills(const FillList &fl, int lb, int nb, int tid) {
+    for (int j = 0; j < fl.n; j++) {
+        const FillList::Job f = fl.f[j];
+        if ((f.N & 3) == 0) {
+            const int n4 = f.N >> 2;
+            const int64_t total4 = f.total >> 2;
+            float4 *d4 = reinterpret_cast<float4 *>(f.dst);
+            const float4 *b4 = reinterpret_cast<const float4 *>(f.bias);
+            for (int64_t i = (int64_t)lb * 256 + tid; i < total4; i += (int64_t)nb * 256)
+                d4[i] = f.bias ? __ldg(&b4[i % n4]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (int64_t i = (int64_t)lb * 256 + tid; i < f.total; i += (int64_t)nb * 256) f.dst[i] = f.bias ? f.bias[i % f.N] : 0.f;
+        }
+    }
+}
 
 // A [TT x TC] fp32 tile of src[T, ncols] (rows t0.. below t_end, columns c0..) moves in two steps so that a block can
 // have the next tile's loads in flight while it computes on the current one:
@@ -108,6 +136,7 @@ struct XaParams {
     uint16_t *x16;
     int ldx16, fp16, T, K, n;
     XaChunk c[kMaxChunks];
+    FillList fills;
 };
 
 __global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
@@ -117,6 +146,8 @@ __global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.x * TT, k0 = blockIdx.y * TC;
     const int T = p.T, K = p.K;
+    pdl_wait();
+    pdl_trigger();
     float4 v[NI];
     tile_load(p.X, K, t0, T, k0, v, tid);
     float av[kMaxChunks][8];       // this thread's 8 elements of each chunk's [128 x 16] tile of A, in flight with X
@@ -167,6 +198,7 @@ __global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
             if (ra + 1 < rc) atomicAdd(&c.low[(int64_t)tb * c.R + c.r0 + ra + 1], d[3]);
         }
     }
+    do_fills(p.fills, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, tid);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -185,16 +217,23 @@ struct DyMember {
 struct DyParams {
     int T, fp16, tok_per_group, n;
     DyMember m[kMaxChunks];
+    FillList fills;
 };
 
 __global__ void __launch_bounds__(256) k_lora_dy_tc(const DyParams p) {
     __shared__ __align__(16) uint32_t Gs[TT][GS];
     __shared__ uint32_t Bs[16][GS];
     __shared__ uint32_t Ls[TT][RS];
+    pdl_wait();
+    pdl_trigger();
     const DyMember m = p.m[blockIdx.z];
     const int N = m.N, R = m.R, r0 = m.r0, T = p.T;
     const int c0 = blockIdx.x * TC;
-    if (c0 >= N) return;
+    const int lb = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, nb = gridDim.x * gridDim.y * gridDim.z;
+    if (c0 >= N) {      // a member with fewer column strips than the widest one
+        do_fills(p.fills, lb, nb, threadIdx.x);
+        return;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int tg0 = blockIdx.y * p.tok_per_group, tg1 = min(T, tg0 + p.tok_per_group);
     const int rc = min(16, R - r0);
@@ -257,6 +296,7 @@ __global__ void __launch_bounds__(256) k_lora_dy_tc(const DyParams p) {
             if (rb < rc) atomicAdd(&m.dB[(int64_t)(r0 + rb) * N + c + 1], accB[j][3] * m.scaling);
         }
     }
+    do_fills(p.fills, lb, nb, tid);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -285,6 +325,8 @@ __global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
     const int k0 = blockIdx.x * TC;
     const int tg0 = blockIdx.y * p.tok_per_group, tg1 = min(T, tg0 + p.tok_per_group);
     const int m0 = warp * 16;
+    pdl_wait();
+    pdl_trigger();
     float acc[kMaxChunks][2][4];
 #pragma unroll
     for (int j = 0; j < kMaxChunks; j++)
@@ -369,8 +411,14 @@ cudaError_t allow_dyn_smem() {
 
 }  // namespace
 
+static void set_fills(FillList &fl, const RowFill *fills, int n_fills, int T) {
+    fl.n = 0;
+    for (int j = 0; j < n_fills && fl.n < kMaxChunks; j++)
+        fl.f[fl.n++] = FillList::Job{fills[j].dst, fills[j].bias, fills[j].N, (int64_t)T * fills[j].N};
+}
+
 cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, void *x16, int ldx16, int fp16, int T, int K,
-                                 cudaStream_t s) {
+                                 const RowFill *fills, int n_fills, cudaStream_t s) {
     if (T <= 0 || K <= 0 || n <= 0) return cudaSuccess;
     cudaError_t e = allow_dyn_smem();
     if (e != cudaSuccess) return e;
@@ -382,12 +430,14 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     p.fp16 = fp16;
     p.T = T;
     p.K = K;
+    set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        k_lora_xa_tc<<<grid, 256, kXsBytes + p.n * kAsBytes, s>>>(p);
+        cudaError_t le = launch_k(k_lora_xa_tc, grid, dim3(256), kXsBytes + p.n * kAsBytes, s, p);
         p.n = 0;
         p.x16 = nullptr;
-        return cudaGetLastError();
+        p.fills.n = 0;
+        return le;
     };
     for (int j = 0; j < n; j++)
         for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
@@ -397,7 +447,7 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     return flush();
 }
 
-cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, cudaStream_t s) {
+cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, const RowFill *fills, int n_fills, cudaStream_t s) {
     if (T <= 0 || n <= 0) return cudaSuccess;
     int strips_sum = 0, strips_max = 0;
     for (int j = 0; j < n; j++) {
@@ -411,11 +461,13 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
     p.T = T;
     p.fp16 = fp16;
     p.tok_per_group = tpg;
+    set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        k_lora_dy_tc<<<dim3(strips_max, groups, p.n), 256, 0, s>>>(p);
+        cudaError_t le = launch_k(k_lora_dy_tc, dim3(strips_max, groups, p.n), dim3(256), 0, s, p);
         p.n = 0;
-        return cudaGetLastError();
+        p.fills.n = 0;
+        return le;
     };
     cudaError_t e;
     // rank chunk 0 of every member first (it also writes the 16-bit copy of dY), then the higher chunks
@@ -450,9 +502,9 @@ cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, i
     p.tok_per_group = tpg;
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        k_lora_da_tc<<<dim3(strips, groups), 256, kXsBytes + p.n * kLsBytes, s>>>(p);
+        cudaError_t le = launch_k(k_lora_da_tc, dim3(strips, groups), dim3(256), kXsBytes + p.n * kLsBytes, s, p);
         p.n = 0;
-        return cudaGetLastError();
+        return le;
     };
     for (int j = 0; j < n; j++)
         for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
@@ -466,14 +518,14 @@ cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed,
                               int R, cudaStream_t s) {
     if (R <= 0) return cudaSuccess;
     const LoraXaJob job{A, low_zeroed, R};
-    return launch_lora_xa_group(X, &job, 1, x16, ldx16, fp16, T, K, s);
+    return launch_lora_xa_group(X, &job, 1, x16, ldx16, fp16, T, K, nullptr, 0, s);
 }
 
 cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
                               int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s) {
     if (N <= 0 || R <= 0) return cudaSuccess;
     const LoraDyJob job{dY, low, B, dB, dLow_zeroed, dy16, ld16, scaling, N, R};
-    return launch_lora_dy_group(&job, 1, fp16, T, s);
+    return launch_lora_dy_group(&job, 1, fp16, T, nullptr, 0, s);
 }
 
 cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s) {

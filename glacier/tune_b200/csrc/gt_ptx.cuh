@@ -273,4 +273,12 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t ab_format, 
            ((m >> 4) << 24);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream still runs.  pdl_wait() blocks until that predecessor has completed and its
+// memory is visible (no-op for a normal launch); pdl_trigger() lets the next kernel in the stream be scheduled once
+// every CTA of this one has called it or exited.  Every kernel launched that way calls pdl_wait() before its first
+// global-memory access and before any early return, so completion stays transitive along the stream.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace gt

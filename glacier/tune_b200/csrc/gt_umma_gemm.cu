@@ -159,17 +159,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             if (tile >= p.m[j].first) mi = j;
     const Member &M = p.m[mi];
     const int ltile = BWD ? tile : tile - M.first;
-    // rank-update stages (split 0 only): forward one for this tile's member, backward one per member with an adapter
-    int lora_m[kMaxMembers];
-    int n_lora = 0;
-    if (split == 0) {
-        if (!BWD) {
-            if (M.rank > 0 && (M.lora_flag == nullptr || *M.lora_flag != 0)) lora_m[n_lora++] = mi;
-        } else {
-            for (int j = 0; j < p.n_members; j++)
-                if (p.m[j].rank > 0) lora_m[n_lora++] = j;
-        }
-    }
     // backward: global unit index -> (member, 64-row block inside it)
     auto unit_member = [&](int u, int &rb) -> int {
         int j = 0;
@@ -211,6 +200,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             tmem_relinquish();
         }
     }
+    // Everything above touches only this CTA's shared memory, TMEM and the kernel parameters, so under a programmatic
+    // dependent launch it overlaps the tail of the previous kernel in the stream; global memory is first read (and
+    // written) below, after that kernel has completed.  The next kernel may then be scheduled behind this one.
+    pdl_wait();
+    pdl_trigger();
+    // rank-update stages (split 0 only): forward one for this tile's member, backward one per member with an adapter
+    int lora_m[kMaxMembers];
+    int n_lora = 0;
+    if (split == 0) {
+        if (!BWD) {
+            if (M.rank > 0 && (M.lora_flag == nullptr || *M.lora_flag != 0)) lora_m[n_lora++] = mi;
+        } else {
+            for (int j = 0; j < p.n_members; j++)
+                if (p.m[j].rank > 0) lora_m[n_lora++] = j;
+        }
+    }
     tc_fence_before_sync();
     if (PAIR) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
@@ -220,6 +225,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         if (tracing && idx < 128) p.trace[row * 128 + idx] = clock64();
     };
     if (threadIdx.x == 0) trace(11, 0);
+    if (p.trace != nullptr && threadIdx.x == 0) {       // wall-clock span of the grid: latest start / end over all CTAs
+        const unsigned long long now = globaltimer_ns();
+        if (tracing) p.trace[11 * 128 + 8] = (long long)now;
+        atomicMax(reinterpret_cast<unsigned long long *>(p.trace) + 11 * 128 + 10, (1ull << 62) - now);
+    }
 
     // activation tile of one stage: coordinate c0 along the contraction, this CTA's token rows
     auto load_act_stage = [&](const CUtensorMap *tm, int c0, uint32_t xdst, uint32_t xbar_local) {
@@ -517,6 +527,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     }
 
     if (threadIdx.x == 64) trace(11, 2);
+    if (p.trace != nullptr && threadIdx.x == 64) {
+        const unsigned long long now = globaltimer_ns();
+        if (tracing) p.trace[11 * 128 + 9] = (long long)now;
+        atomicMax(reinterpret_cast<unsigned long long *>(p.trace) + 11 * 128 + 11, now);
+    }
     if (*abort_flag) {
         // give loads that were already issued time to land before the CTA's shared memory is released
         for (int i = 0; i < 64; i++) __nanosleep(2000);
@@ -596,15 +611,22 @@ cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
     if (PAIR) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 2;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        na++;
     }
+    if (pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 

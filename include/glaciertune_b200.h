@@ -68,9 +68,16 @@ enum gt_direction { GT_DIR_FORWARD = 0, GT_DIR_BACKWARD = 1 };
 enum gt_flags {
     GT_FLAG_DEVICE_PTRS = 1, /* activation pointers are device pointers; asynchronous on the engine stream */
     GT_FLAG_NO_LORA = 2,     /* skip the adapter terms even when an adapter is given */
-    GT_FLAG_REUSE_LOW = 4    /* backward: X is the tensor the last forward through this adapter saw, so X*A kept from
+    GT_FLAG_REUSE_LOW = 4,   /* backward: X is the tensor the last forward through this adapter saw, so X*A kept from
                                 that call is reused instead of recomputed (the reference recomputes it,
                                 src/Glacier.Tune/Kernels/LoraKernels.cs:147-186; the value is the same) */
+    GT_FLAG_HOST_ASYNC = 16, /* host buffers only, page-locked: the call returns once its copies and kernels are queued
+                                (uploads, kernels and downloads of consecutive calls overlap on separate streams); the
+                                outputs are valid, and the inputs may be changed, after gt_sync().  Without the flag a
+                                host-buffer call returns with its outputs written, like the reference's */
+    GT_FLAG_DX_ASSIGN = 8    /* backward: dX = ... instead of dX += ...: the call clears dX itself, which replaces the
+                                zero-filled buffer the reference hands to LoraAdapter.Backward
+                                (AutogradScratchWorkspace.Wrap) without a separate fill */
 };
 
 typedef struct gt_config {

@@ -184,6 +184,93 @@ def test_group_host_buffers_and_mixed_types(G, eng, oracle):
     _free(ws, ads)
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_dx_assign_overwrites_stale_contents(G, eng, oracle, mode):
+    """GT_FLAG_DX_ASSIGN: dX = ... whatever the buffer held (single call with and without adapter, group, host buffers)."""
+    import torch
+    cs = _members(S.TYPE_Q4_K, (256, 128), 512, 150, seed=77, adapted=(1, 0), biased=(0, 0))
+    eng.set_math_mode(mode)
+    ws, ads = _upload(eng, cs)
+    X = torch.from_numpy(cs[0]["x"]).cuda()
+    dYs = [torch.from_numpy(c["dy"]).cuda() for c in cs]
+    _, dx_group, _, _ = _reference(oracle, cs)
+    singles = [_reference(oracle, [c])[1] for c in cs]
+    dX = torch.full((150, 512), 3.0, device="cuda")
+    eng.backward_group(ws, ads, dYs, X, dX, flags=G.FLAG_DX_ASSIGN)
+    eng.sync()
+    assert oracle.rel_fro(dX.cpu().numpy(), dx_group) < TOL[mode]
+    for j in range(2):
+        dX.fill_(-5.0)
+        eng.backward(ws[j], ads[j], dYs[j], X, dX, flags=G.FLAG_DX_ASSIGN)
+        eng.sync()
+        assert oracle.rel_fro(dX.cpu().numpy(), singles[j]) < TOL[mode], j
+    hdx = np.full((150, 512), 9.0, np.float32)
+    eng.backward(ws[0], ads[0], cs[0]["dy"], cs[0]["x"], hdx, flags=G.FLAG_DX_ASSIGN)
+    assert oracle.rel_fro(hdx, singles[0]) < TOL[mode]
+    hdx.fill(9.0)
+    eng.backward_group(ws, ads, [c["dy"] for c in cs], cs[0]["x"], hdx, flags=G.FLAG_DX_ASSIGN)
+    assert oracle.rel_fro(hdx, dx_group) < TOL[mode]
+    _free(ws, ads)
+
+
+def test_repeated_backward_after_one_forward(G, eng, oracle):
+    """Two backward calls that reuse X*A of one forward: the second must not see the first one's dY*B^T sums."""
+    import torch
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 100, seed=9)
+    eng.set_math_mode(0)
+    w = eng.upload_weight(c["qtype"], c["w"], 256, 512)
+    ad = eng.create_adapter(512, 256, 16, 32.0)
+    ad.upload(c["a"], c["b"])
+    X, dY = torch.from_numpy(c["x"]).cuda(), torch.from_numpy(c["dy"]).cuda()
+    Y = torch.empty((100, 256), device="cuda")
+    eng.forward(w, ad, X, Y)
+    out = []
+    for _ in range(2):
+        ad.zero_grads()
+        dX = torch.zeros((100, 512), device="cuda")
+        eng.backward(w, ad, dY, X, dX, flags=G.FLAG_REUSE_LOW)
+        eng.sync()
+        out.append((dX.cpu().numpy(),) + tuple(ad.grads()))
+    for a, b in zip(*out):
+        assert oracle.rel_fro(a, b) < 1e-4
+    w.free()
+    ad.free()
+
+
+def test_host_async_calls_complete_at_sync(G, eng, oracle):
+    """GT_FLAG_HOST_ASYNC on page-locked buffers: more calls than staging slots queued back to back, results checked
+    after one gt_sync(); they equal the synchronous calls' results."""
+    import torch
+    cs = _members(S.TYPE_Q4_K, (256, 128), 512, 130, seed=41, adapted=(1, 1), biased=(1, 0))
+    eng.set_math_mode(0)
+    ws, ads = _upload(eng, cs)
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()      # noqa: E731
+    hx = pin(cs[0]["x"])
+    hdy = [pin(c["dy"]) for c in cs]
+    rounds = 5
+    hys = [[torch.zeros((130, c["N"])).pin_memory() for c in cs] for _ in range(rounds)]
+    hdx = [torch.full((130, 512), 4.0).pin_memory() for _ in range(rounds)]
+    fl = G.FLAG_HOST_ASYNC
+    for r in range(rounds):
+        eng.forward_group(ws, ads, hx.numpy(), [y.numpy() for y in hys[r]], flags=fl)
+        eng.backward_group(ws, ads, [d.numpy() for d in hdy], hx.numpy(), hdx[r].numpy(), flags=fl | G.FLAG_DX_ASSIGN | G.FLAG_REUSE_LOW)
+    eng.sync()
+    ys, dxr, das, dbs = _reference(oracle, cs)
+    for r in range(rounds):
+        for j in range(2):
+            assert oracle.rel_fro(hys[r][j].numpy(), ys[j]) < 2e-2, (r, j)
+        assert oracle.rel_fro(hdx[r].numpy(), dxr) < 2e-2, r
+    for j in range(2):
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(da, rounds * das[j]) < 5e-3 and oracle.rel_fro(db, rounds * dbs[j]) < 5e-3
+    # synchronous host calls give the same numbers as the queued ones
+    y_sync = [np.empty((130, c["N"]), np.float32) for c in cs]
+    eng.forward_group(ws, ads, cs[0]["x"], y_sync)
+    for j in range(2):
+        assert oracle.rel_fro(y_sync[j], hys[0][j].numpy()) < 1e-3
+    _free(ws, ads)
+
+
 def test_group_error_paths(G, eng):
     import torch
     a = S.make_projection_case(S.TYPE_Q4_K, 128, 512, 8, seed=1)
