@@ -1,18 +1,25 @@
 // Rank-r LoRA products for the bf16 math mode, one pass over each activation tensor:
-//   k_lora_xa_tc   low[T,R]  += X[T,K] * A[K,R]                       (+ 16-bit copy of X for the base GEMM)
-//   k_lora_dy_tc   dLow[T,R] += dY[T,N] * B[R,N]^T ; dB[R,N] += s * low^T * dY   (+ 16-bit copy of dY)
+//   k_lora_xa_tc   low[T,R]  += X[T,K] * A[K,R]                       (+ bf16 copy of X for the base GEMM)
+//   k_lora_dy_tc   dLow[T,R] += dY[T,N] * B[R,N]^T ; dB[R,N] += s * low^T * dY   (+ bf16 copy of dY)
 //   k_lora_da_tc   dA[K,R]   += s * X[T,K]^T * dLow[T,R]
-// They replace the host loops of src/Glacier.Tune/Kernels/LoraKernels.cs:35-54,191-291.  Operands are rounded to
-// TF32 (10-bit mantissa, round to nearest) when they are staged in shared memory, products accumulate in fp32 in
-// warp-level m16n8k8 MMAs, and partial sums leave the block through fp32 atomics; the exact-fp32 CUDA-core versions
-// in gt_fp32_kernels.cu serve the validation modes.  A launch handles up to three 16-rank chunks: the adapters of
-// projections that share their input (q, k, v; gate, up) go through one pass over X, and the dY passes of a group's
-// members are one launch (blockIdx.z picks the member).
+// They replace the host loops of src/Glacier.Tune/Kernels/LoraKernels.cs:35-54,191-291.  A [64 tokens x 128 columns]
+// tile of the fp32 activation tensor is rounded to bf16 once, on its way into shared memory - the same rounding
+// that produces the 16-bit copy the base GEMM reads, which is written from the same registers - and every product
+// that needs the tile runs on warp-level m16n8k16 bf16 MMAs with fp32 accumulation, fragments fetched with
+// ldmatrix (transposed where the contraction runs over tokens).  Partial sums leave the block through fp32
+// atomics.  The exact-fp32 CUDA-core versions in gt_fp32_kernels.cu serve the validation modes.
 //
-// These kernels are bound by the HBM read of X / dY, not by arithmetic: the tile in shared memory is read once
-// from global memory and reused by every product that needs it.
+// A launch handles up to three 16-rank chunks: the adapters of projections that share their input (q, k, v; gate, up)
+// go through one pass over X, and the dY passes of a group's members are one launch (blockIdx.z picks the member).
+//
+// These kernels should be bound by the HBM read of X / dY: the tile in shared memory is read once from global
+// memory and reused by every product that needs it; the instruction count per element is what has to stay small
+// (an earlier TF32 m16n8k8 version spent 27 thread instructions per element, mostly scalar fragment loads, and ran
+// at a quarter of the HBM rate).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <cstdlib>
 
 #include "gt_internal.h"
 #include "gt_ptx.cuh"
@@ -21,32 +28,51 @@ namespace gt {
 
 namespace {
 
-__device__ __forceinline__ uint32_t to_tf32(float v) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return r;
-}
-__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t pack16(float lo, float hi, int fp16) {
-    if (fp16) {
-        __half2 v = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t *>(&v);
-    }
+// four 8x8 b16 matrices; lanes 8i..8i+7 give the row addresses of matrix i
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-constexpr int TT = 64;     // tokens per tile
-constexpr int TC = 128;    // columns (of K or N) per tile
-constexpr int GS = TC + 4; // smem row stride of the activation tile (words): rows 4 banks apart
-constexpr int RS = 24;     // smem row stride of the 16-wide rank tiles (words)
-
+constexpr int TT = 64;        // tokens per tile
+constexpr int TC = 128;       // columns (of K or N) per tile
+constexpr int GSB = 2 * TC + 16;   // smem row stride of the bf16 activation tile in bytes: 8 consecutive rows, 16 B each,
+                                   // land in 8 different 4-bank groups (what ldmatrix reads at once)
+constexpr int RSB = 48;       // smem row stride of a 16-wide bf16 rank tile in bytes (same property)
 constexpr int NI = (TT * TC / 4) / 256;     // float4 loads per thread and tile
 constexpr int kMaxChunks = 3;               // 16-rank chunks (of one or several adapters) served by one launch
+
+// ldmatrix lane -> row address of its 8x8 matrix.  `base` = tile address, rows `stride` bytes apart.
+//   A operand, stored [m][k]  (non-transposed load): matrices (m0-7,k0-7) (m8-15,k0-7) (m0-7,k8-15) (m8-15,k8-15)
+//   A operand, stored [k][m]  (transposed load)    : matrices (k0-7,m0-7) (k0-7,m8-15) (k8-15,m0-7) (k8-15,m8-15)
+//   B operand x2 n-tiles, stored [n][k] (non-transposed): (n0-7,k0-7) (n0-7,k8-15) (n8-15,k0-7) (n8-15,k8-15)
+//   B operand x2 n-tiles, stored [k][n] (transposed)    : (k0-7,n0-7) (k8-15,n0-7) (k0-7,n8-15) (k8-15,n8-15)
+// In every case registers {0,1,2,3} of the result are {a0,a1,a2,a3} resp. {b0,b1 of n-tile 0, b0,b1 of n-tile 1}.
+__device__ __forceinline__ uint32_t lm_a_mk(uint32_t base, int stride, int m0, int k0, int lane) {
+    return base + (uint32_t)((m0 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + (k0 + (lane >> 4) * 8) * 2);
+}
+__device__ __forceinline__ uint32_t lm_a_km(uint32_t base, int stride, int m0, int k0, int lane) {
+    return base + (uint32_t)((k0 + (lane & 7) + (lane >> 4) * 8) * stride + (m0 + ((lane >> 3) & 1) * 8) * 2);
+}
+__device__ __forceinline__ uint32_t lm_b_nk(uint32_t base, int stride, int n0, int k0, int lane) {
+    return base + (uint32_t)((n0 + (lane & 7) + (lane >> 4) * 8) * stride + (k0 + ((lane >> 3) & 1) * 8) * 2);
+}
+__device__ __forceinline__ uint32_t lm_b_kn(uint32_t base, int stride, int n0, int k0, int lane) {
+    return base + (uint32_t)((k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + (n0 + (lane >> 4) * 8) * 2);
+}
 
 // Row fills that ride along with a pass (the split-K GEMM that follows sums into its output, so the output starts as
 // the bias rows or as zero): dst[T, N] = bias[N] (or 0).  The blocks of the launch share each fill evenly.
@@ -77,8 +103,8 @@ __device__ __forceinline__ void do_fills(const FillList &fl, int lb, int nb, int
 
 // A [TT x TC] fp32 tile of src[T, ncols] (rows t0.. below t_end, columns c0..) moves in two steps so that a block can
 // have the next tile's loads in flight while it computes on the current one:
-//   tile_load   global -> registers (float4 per thread when the tile is interior and aligned)
-//   tile_store  registers -> shared memory as TF32, and optionally the 16-bit rounding to dst16 in global memory
+//   tile_load   global -> registers (float4 per thread when the tile is interior and aligned); a warp reads one row
+//   tile_store  registers -> bf16 in shared memory, and optionally the same bf16 values to dst16 in global memory
 __device__ __forceinline__ void tile_load(const float *__restrict__ src, int ncols, int t0, int t_end, int c0, float4 (&v)[NI], int tid) {
     const bool vec = (ncols & 3) == 0 && c0 + TC <= ncols;
 #pragma unroll
@@ -100,31 +126,61 @@ __device__ __forceinline__ void tile_load(const float *__restrict__ src, int nco
         }
     }
 }
-__device__ __forceinline__ void tile_store(const float4 (&v)[NI], int t0, int t_end, int c0, uint32_t (*tile)[GS],
-                                           uint16_t *__restrict__ dst16, int ld16, int fp16, int tid) {
+__device__ __forceinline__ void tile_store(const float4 (&v)[NI], int t0, int t_end, int c0, uint8_t *tile,
+                                           uint16_t *__restrict__ dst16, int ld16, int tid) {
 #pragma unroll
     for (int i = 0; i < NI; i++) {
         const int idx = tid + i * 256;
         const int r = idx / (TC / 4), c = (idx % (TC / 4)) * 4;
         const int t = t0 + r;
+        const uint2 pk = make_uint2(pack_bf16(v[i].x, v[i].y), pack_bf16(v[i].z, v[i].w));
         if (dst16 && t < t_end) {
             uint16_t *q = dst16 + (int64_t)t * ld16 + c0 + c;
             if (c0 + c + 3 < ld16 && (ld16 & 3) == 0) {
-                *reinterpret_cast<uint2 *>(q) = make_uint2(pack16(v[i].x, v[i].y, fp16), pack16(v[i].z, v[i].w, fp16));
+                *reinterpret_cast<uint2 *>(q) = pk;
             } else {
-                const float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                const uint16_t e[4] = {(uint16_t)(pk.x & 0xFFFFu), (uint16_t)(pk.x >> 16), (uint16_t)(pk.y & 0xFFFFu), (uint16_t)(pk.y >> 16)};
                 for (int j = 0; j < 4; j++)
-                    if (c0 + c + j < ld16) q[j] = (uint16_t)(pack16(e[j], 0.f, fp16) & 0xFFFFu);
+                    if (c0 + c + j < ld16) q[j] = e[j];
             }
         }
-        *reinterpret_cast<uint4 *>(&tile[r][c]) = make_uint4(to_tf32(v[i].x), to_tf32(v[i].y), to_tf32(v[i].z), to_tf32(v[i].w));
+        *reinterpret_cast<uint2 *>(tile + r * GSB + c * 2) = pk;
+    }
+}
+// A [rows x 16] slab of a row-major fp32 matrix with `ld` columns (rows row0.., columns r0..r0+15; zero outside
+// row_end / rc) -> bf16 rank tile in shared memory, rows RSB bytes apart.  256 threads.
+__device__ __forceinline__ void rank_tile_store(const float *__restrict__ src, int ld, int row0, int row_end, int r0, int rc, int rows,
+                                                uint8_t *tile, int tid) {
+    for (int i = tid; i < rows * 8; i += 256) {
+        const int rr = i >> 3, c = (i & 7) * 2;
+        float a = 0.f, b = 0.f;
+        if (row0 + rr < row_end) {
+            const float *p = src + (int64_t)(row0 + rr) * ld + r0 + c;
+            if (c < rc) a = __ldg(p);
+            if (c + 1 < rc) b = __ldg(p + 1);
+        }
+        *reinterpret_cast<uint32_t *>(tile + rr * RSB + c * 2) = pack_bf16(a, b);
+    }
+}
+// fp32 accumulator fragment of a 16 x 8 tile (rows m0 + g / + 8, columns n0 + 2*t4 / + 1) added into dst[rows, ld]
+__device__ __forceinline__ void frag_atomic_add(float *dst, int64_t ld, const float (&d)[4], int row_a, int row_end, int col, int col_end,
+                                                float scale) {
+    const int row_b = row_a + 8;
+    if (row_a < row_end) {
+        if (col < col_end) atomicAdd(&dst[(int64_t)row_a * ld + col], d[0] * scale);
+        if (col + 1 < col_end) atomicAdd(&dst[(int64_t)row_a * ld + col + 1], d[1] * scale);
+    }
+    if (row_b < row_end) {
+        if (col < col_end) atomicAdd(&dst[(int64_t)row_b * ld + col], d[2] * scale);
+        if (col + 1 < col_end) atomicAdd(&dst[(int64_t)row_b * ld + col + 1], d[3] * scale);
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 // low_j[T, R_j] += X[T, K] * A_j[K, R_j] over the block's K slice (grid.y slices of 128) for up to kMaxChunks
 // 16-rank chunks that share X (the adapters of q, k, v or of gate, up): X is read and rounded once, fp32 atomics
-// into each low_j (pre-zeroed).  8 warps = 4 token m-tiles x 2 rank n-tiles per chunk, 16 k-steps each.
+// into each low_j (pre-zeroed).  8 warps = 4 token m-tiles x 2 halves of the slice's 8 k-steps; each warp covers
+// both 8-wide rank n-tiles of every chunk.
 // ------------------------------------------------------------------------------------------------
 struct XaChunk {
     const float *A;
@@ -134,15 +190,18 @@ struct XaChunk {
 struct XaParams {
     const float *X;
     uint16_t *x16;
-    int ldx16, fp16, T, K, n;
+    int ldx16, T, K, n;
     XaChunk c[kMaxChunks];
     FillList fills;
 };
+constexpr int kXsBytes = TT * GSB;            // activation tile
+constexpr int kAsBytes = TC * RSB;            // per chunk, k_lora_xa_tc: A[k0.., r0..] as [128][16]
+constexpr int kLsBytes = TT * RSB;            // per chunk, k_lora_da_tc / k_lora_dy_tc: [64 tokens][16]
 
 __global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
-    extern __shared__ __align__(16) uint32_t dyn_smem[];
-    uint32_t (*Xs)[GS] = reinterpret_cast<uint32_t (*)[GS]>(dyn_smem);
-    uint32_t (*As)[TC][RS] = reinterpret_cast<uint32_t (*)[TC][RS]>(dyn_smem + TT * GS);
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t *Xs = dyn_smem;
+    uint8_t *As = dyn_smem + kXsBytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.x * TT, k0 = blockIdx.y * TC;
     const int T = p.T, K = p.K;
@@ -150,53 +209,36 @@ __global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
     pdl_trigger();
     float4 v[NI];
     tile_load(p.X, K, t0, T, k0, v, tid);
-    float av[kMaxChunks][8];       // this thread's 8 elements of each chunk's [128 x 16] tile of A, in flight with X
 #pragma unroll
     for (int j = 0; j < kMaxChunks; j++) {
         if (j < p.n) {
             const XaChunk c = p.c[j];
-            const int rc = min(16, c.R - c.r0);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int idx = tid + i * 256, k = idx >> 4, r = idx & 15;
-                av[j][i] = (k0 + k < K && r < rc) ? __ldg(&c.A[(int64_t)(k0 + k) * c.R + c.r0 + r]) : 0.f;
-            }
+            rank_tile_store(c.A, c.R, k0, K, c.r0, min(16, c.R - c.r0), TC, As + j * kAsBytes, tid);
         }
     }
-    tile_store(v, t0, T, k0, Xs, p.x16, p.ldx16, p.fp16, tid);
-#pragma unroll
-    for (int j = 0; j < kMaxChunks; j++) {
-        if (j < p.n) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int idx = tid + i * 256;
-                As[j][idx >> 4][idx & 15] = to_tf32(av[j][i]);
-            }
-        }
-    }
+    tile_store(v, t0, T, k0, Xs, p.x16, p.ldx16, tid);
     __syncthreads();
-    const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;
+    const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;
+    const uint32_t xs = smem_u32(Xs), as = smem_u32(As);
+    uint32_t a[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++) ldsm_x4(lm_a_mk(xs, GSB, m0, kh + ks * 16, lane), a[ks]);
 #pragma unroll
     for (int j = 0; j < kMaxChunks; j++) {
         if (j >= p.n) break;
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int ks = 0; ks < TC / 8; ks++) {
-            const int kk = ks * 8;
-            mma_tf32(d, Xs[m0 + g][kk + t4], Xs[m0 + g + 8][kk + t4], Xs[m0 + g][kk + t4 + 4], Xs[m0 + g + 8][kk + t4 + 4],
-                     As[j][kk + t4][n0 + g], As[j][kk + t4 + 4][n0 + g]);
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t b[4];
+            ldsm_x4_t(lm_b_kn(as + j * kAsBytes, RSB, 0, kh + ks * 16, lane), b);
+            mma_bf16(d[0], a[ks], b[0], b[1]);
+            mma_bf16(d[1], a[ks], b[2], b[3]);
         }
         const XaChunk c = p.c[j];
         const int rc = min(16, c.R - c.r0);
-        const int ta = t0 + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
-        if (ta < T) {
-            if (ra < rc) atomicAdd(&c.low[(int64_t)ta * c.R + c.r0 + ra], d[0]);
-            if (ra + 1 < rc) atomicAdd(&c.low[(int64_t)ta * c.R + c.r0 + ra + 1], d[1]);
-        }
-        if (tb < T) {
-            if (ra < rc) atomicAdd(&c.low[(int64_t)tb * c.R + c.r0 + ra], d[2]);
-            if (ra + 1 < rc) atomicAdd(&c.low[(int64_t)tb * c.R + c.r0 + ra + 1], d[3]);
-        }
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+            frag_atomic_add(c.low + c.r0, c.R, d[i], t0 + m0 + g, T, i * 8 + 2 * t4, rc, 1.f);
     }
     do_fills(p.fills, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, tid);
 }
@@ -204,8 +246,8 @@ __global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
 // ------------------------------------------------------------------------------------------------
 // One pass over dY_m per member m = blockIdx.z: the block owns a 128-column strip and a token group, walked in
 // 64-token tiles.
-//   dLow[t, r] += sum_c dY[t, c] * B[r, c]      4 m-tiles (tokens) x 2 n-tiles (ranks) over 8 warps, 16 k-steps
-//   dB[r, c]   += s * sum_t low[t, r] * dY[t, c] 1 m-tile (ranks) x 16 n-tiles (columns), 2 per warp, 8 k-steps
+//   dLow[t, r] += sum_c dY[t, c] * B[r, c]      8 warps = 4 token m-tiles x 2 halves of the strip's 8 k-steps
+//   dB[r, c]   += s * sum_t low[t, r] * dY[t, c] 1 m-tile (ranks) x 16 n-tiles (columns), 2 per warp, 4 k-steps
 // ------------------------------------------------------------------------------------------------
 struct DyMember {
     const float *dY, *low, *B;
@@ -215,15 +257,15 @@ struct DyMember {
     float scaling;
 };
 struct DyParams {
-    int T, fp16, tok_per_group, n;
+    int T, tok_per_group, n;
     DyMember m[kMaxChunks];
     FillList fills;
 };
 
-__global__ void __launch_bounds__(256) k_lora_dy_tc(const DyParams p) {
-    __shared__ __align__(16) uint32_t Gs[TT][GS];
-    __shared__ uint32_t Bs[16][GS];
-    __shared__ uint32_t Ls[TT][RS];
+__global__ void __launch_bounds__(256, 3) k_lora_dy_tc(const DyParams p) {
+    __shared__ __align__(16) uint8_t Gs[TT * GSB];
+    __shared__ __align__(16) uint8_t Bs[16 * GSB];      // B[r0.., c0..] as [16][128]
+    __shared__ __align__(16) uint8_t Ls[TT * RSB];      // low tile [64][16]
     pdl_wait();
     pdl_trigger();
     const DyMember m = p.m[blockIdx.z];
@@ -239,70 +281,59 @@ __global__ void __launch_bounds__(256) k_lora_dy_tc(const DyParams p) {
     const int rc = min(16, R - r0);
     float4 v[NI];
     tile_load(m.dY, N, tg0, tg1, c0, v, tid);
-    for (int i = tid; i < 16 * TC; i += 256) {
-        const int r = i / TC, c = i % TC;
-        Bs[r][c] = (r < rc && c0 + c < N) ? to_tf32(__ldg(&m.B[(int64_t)(r0 + r) * N + c0 + c])) : 0u;
+    for (int i = tid; i < 16 * (TC / 2); i += 256) {
+        const int r = i / (TC / 2), c = (i % (TC / 2)) * 2;
+        float a = 0.f, b = 0.f;
+        if (r < rc) {
+            const float *q = m.B + (int64_t)(r0 + r) * N + c0 + c;
+            if (c0 + c < N) a = __ldg(q);
+            if (c0 + c + 1 < N) b = __ldg(q + 1);
+        }
+        *reinterpret_cast<uint32_t *>(Bs + r * GSB + c * 2) = pack_bf16(a, b);
     }
+    const uint32_t gs = smem_u32(Gs), bs = smem_u32(Bs), ls = smem_u32(Ls);
     float accB[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8;      // dLow tiles
-    const int cb = warp * 16;                                  // dB: this warp's two 8-column n-tiles
+    const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;    // dLow: token m-tile, half of the strip's columns
+    const int cb = warp * 16;                                 // dB: this warp's two 8-column n-tiles
     uint16_t *dy16 = r0 == 0 ? m.dy16 : nullptr;
     for (int ts = tg0; ts < tg1; ts += TT) {
         __syncthreads();
-        tile_store(v, ts, tg1, c0, Gs, dy16, m.ld16, p.fp16, tid);
+        tile_store(v, ts, tg1, c0, Gs, dy16, m.ld16, tid);
         if (ts + TT < tg1) tile_load(m.dY, N, ts + TT, tg1, c0, v, tid);     // next tile's loads fly during the MMAs below
-        for (int i = tid; i < TT * 16; i += 256) {
-            const int tt = i >> 4, r = i & 15;
-            Ls[tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(m.low[(int64_t)(ts + tt) * R + r0 + r]) : 0u;
-        }
+        rank_tile_store(m.low, R, ts, tg1, r0, rc, TT, Ls, tid);
         __syncthreads();
         {
-            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-            for (int ks = 0; ks < TC / 8; ks++) {
-                const int kk = ks * 8;
-                mma_tf32(d, Gs[m0 + g][kk + t4], Gs[m0 + g + 8][kk + t4], Gs[m0 + g][kk + t4 + 4], Gs[m0 + g + 8][kk + t4 + 4],
-                         Bs[n0 + g][kk + t4], Bs[n0 + g][kk + t4 + 4]);
+            for (int ks = 0; ks < 4; ks++) {
+                uint32_t a[4], b[4];
+                ldsm_x4(lm_a_mk(gs, GSB, m0, kh + ks * 16, lane), a);
+                ldsm_x4(lm_b_nk(bs, GSB, 0, kh + ks * 16, lane), b);
+                mma_bf16(d[0], a, b[0], b[1]);
+                mma_bf16(d[1], a, b[2], b[3]);
             }
-            const int ta = ts + m0 + g, tb = ta + 8, ra = n0 + 2 * t4;
-            if (ta < tg1) {
-                if (ra < rc) atomicAdd(&m.dLow[(int64_t)ta * R + r0 + ra], d[0]);
-                if (ra + 1 < rc) atomicAdd(&m.dLow[(int64_t)ta * R + r0 + ra + 1], d[1]);
-            }
-            if (tb < tg1) {
-                if (ra < rc) atomicAdd(&m.dLow[(int64_t)tb * R + r0 + ra], d[2]);
-                if (ra + 1 < rc) atomicAdd(&m.dLow[(int64_t)tb * R + r0 + ra + 1], d[3]);
-            }
+#pragma unroll
+            for (int i = 0; i < 2; i++) frag_atomic_add(m.dLow + r0, R, d[i], ts + m0 + g, tg1, i * 8 + 2 * t4, rc, 1.f);
         }
 #pragma unroll
-        for (int ks = 0; ks < TT / 8; ks++) {
-            const int kk = ks * 8;      // token index inside the tile
-            const uint32_t a0 = Ls[kk + t4][g], a1 = Ls[kk + t4][g + 8], a2 = Ls[kk + t4 + 4][g], a3 = Ls[kk + t4 + 4][g + 8];
-#pragma unroll
-            for (int j = 0; j < 2; j++)
-                mma_tf32(accB[j], a0, a1, a2, a3, Gs[kk + t4][cb + j * 8 + g], Gs[kk + t4 + 4][cb + j * 8 + g]);
+        for (int ks = 0; ks < TT / 16; ks++) {
+            uint32_t a[4], b[4];
+            ldsm_x4_t(lm_a_km(ls, RSB, 0, ks * 16, lane), a);        // low^T: m = rank, k = token
+            ldsm_x4_t(lm_b_kn(gs, GSB, cb, ks * 16, lane), b);       // dY: k = token, n = column
+            mma_bf16(accB[0], a, b[0], b[1]);
+            mma_bf16(accB[1], a, b[2], b[3]);
         }
     }
+    // accB rows = ranks, columns = strip columns
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int c = c0 + cb + j * 8 + 2 * t4;
-        const int ra = g, rb = g + 8;
-        if (c < N) {
-            if (ra < rc) atomicAdd(&m.dB[(int64_t)(r0 + ra) * N + c], accB[j][0] * m.scaling);
-            if (rb < rc) atomicAdd(&m.dB[(int64_t)(r0 + rb) * N + c], accB[j][2] * m.scaling);
-        }
-        if (c + 1 < N) {
-            if (ra < rc) atomicAdd(&m.dB[(int64_t)(r0 + ra) * N + c + 1], accB[j][1] * m.scaling);
-            if (rb < rc) atomicAdd(&m.dB[(int64_t)(r0 + rb) * N + c + 1], accB[j][3] * m.scaling);
-        }
-    }
+    for (int i = 0; i < 2; i++) frag_atomic_add(m.dB + (int64_t)r0 * N, N, accB[i], g, rc, c0 + cb + i * 8 + 2 * t4, N, m.scaling);
     do_fills(p.fills, lb, nb, tid);
 }
 
 // ------------------------------------------------------------------------------------------------
 // dA_j[k, r] += s_j * sum_t X[t, k] * dLow_j[t, r] for up to kMaxChunks 16-rank chunks that share X: the block owns
 // a 128-column strip of X and a token group.  8 warps = 8 m-tiles of 16 columns; each covers both rank n-tiles of
-// every chunk over the 8 token k-steps of a tile.
+// every chunk over the 4 token k-steps of a tile.
 // ------------------------------------------------------------------------------------------------
 struct DaChunk {
     const float *dLow;
@@ -317,9 +348,9 @@ struct DaParams {
 };
 
 __global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
-    extern __shared__ __align__(16) uint32_t dyn_smem[];
-    uint32_t (*Xs)[GS] = reinterpret_cast<uint32_t (*)[GS]>(dyn_smem);
-    uint32_t (*Ls)[TT][RS] = reinterpret_cast<uint32_t (*)[TT][RS]>(dyn_smem + TT * GS);
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t *Xs = dyn_smem;
+    uint8_t *Ls = dyn_smem + kXsBytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int T = p.T, K = p.K;
     const int k0 = blockIdx.x * TC;
@@ -332,35 +363,32 @@ __global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
     for (int j = 0; j < kMaxChunks; j++)
 #pragma unroll
         for (int i = 0; i < 2; i++) acc[j][i][0] = acc[j][i][1] = acc[j][i][2] = acc[j][i][3] = 0.f;
+    const uint32_t xs = smem_u32(Xs), ls = smem_u32(Ls);
     float4 v[NI];
     tile_load(p.X, K, tg0, tg1, k0, v, tid);
     for (int ts = tg0; ts < tg1; ts += TT) {
         __syncthreads();
-        tile_store(v, ts, tg1, k0, Xs, nullptr, 0, 0, tid);
+        tile_store(v, ts, tg1, k0, Xs, nullptr, 0, tid);
         if (ts + TT < tg1) tile_load(p.X, K, ts + TT, tg1, k0, v, tid);      // next tile's loads fly during the MMAs below
 #pragma unroll
         for (int j = 0; j < kMaxChunks; j++) {
             if (j < p.n) {
                 const DaChunk c = p.c[j];
-                const int rc = min(16, c.R - c.r0);
-                for (int i = tid; i < TT * 16; i += 256) {
-                    const int tt = i >> 4, r = i & 15;
-                    Ls[j][tt][r] = (ts + tt < tg1 && r < rc) ? to_tf32(c.dLow[(int64_t)(ts + tt) * c.R + c.r0 + r]) : 0u;
-                }
+                rank_tile_store(c.dLow, c.R, ts, tg1, c.r0, min(16, c.R - c.r0), TT, Ls + j * kLsBytes, tid);
             }
         }
         __syncthreads();
 #pragma unroll
-        for (int ks = 0; ks < TT / 8; ks++) {
-            const int kk = ks * 8;
-            const uint32_t a0 = Xs[kk + t4][m0 + g], a1 = Xs[kk + t4][m0 + g + 8], a2 = Xs[kk + t4 + 4][m0 + g],
-                           a3 = Xs[kk + t4 + 4][m0 + g + 8];
+        for (int ks = 0; ks < TT / 16; ks++) {
+            uint32_t a[4];
+            ldsm_x4_t(lm_a_km(xs, GSB, m0, ks * 16, lane), a);       // X^T: m = column of X, k = token
 #pragma unroll
             for (int j = 0; j < kMaxChunks; j++) {
                 if (j < p.n) {
-#pragma unroll
-                    for (int i = 0; i < 2; i++)
-                        mma_tf32(acc[j][i], a0, a1, a2, a3, Ls[j][kk + t4][i * 8 + g], Ls[j][kk + t4 + 4][i * 8 + g]);
+                    uint32_t b[4];
+                    ldsm_x4_t(lm_b_kn(ls + j * kLsBytes, RSB, 0, ks * 16, lane), b);
+                    mma_bf16(acc[j][0], a, b[0], b[1]);
+                    mma_bf16(acc[j][1], a, b[2], b[3]);
                 }
             }
         }
@@ -371,23 +399,17 @@ __global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
         const DaChunk c = p.c[j];
         const int rc = min(16, c.R - c.r0);
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int ka = k0 + m0 + g, kb = ka + 8, r = i * 8 + 2 * t4;
-            if (ka < K) {
-                if (r < rc) atomicAdd(&c.dA[(int64_t)ka * c.R + c.r0 + r], acc[j][i][0] * c.scaling);
-                if (r + 1 < rc) atomicAdd(&c.dA[(int64_t)ka * c.R + c.r0 + r + 1], acc[j][i][1] * c.scaling);
-            }
-            if (kb < K) {
-                if (r < rc) atomicAdd(&c.dA[(int64_t)kb * c.R + c.r0 + r], acc[j][i][2] * c.scaling);
-                if (r + 1 < rc) atomicAdd(&c.dA[(int64_t)kb * c.R + c.r0 + r + 1], acc[j][i][3] * c.scaling);
-            }
-        }
+        for (int i = 0; i < 2; i++) frag_atomic_add(c.dA + c.r0, c.R, acc[j][i], k0 + m0 + g, K, i * 8 + 2 * t4, rc, c.scaling);
     }
 }
 
 // token groups so that (column strips x groups) covers the SMs about twice; groups are whole 64-token tiles
 void pick_groups(int strips, int T, int &groups, int &tpg) {
-    groups = (2 * 148 + strips - 1) / (strips > 0 ? strips : 1);
+    static const int waves = [] {
+        const char *v = getenv("GT_LORA_WAVES");
+        return v ? atoi(v) : 2;
+    }();
+    groups = (waves * 148 + strips - 1) / (strips > 0 ? strips : 1);
     const int max_groups = (T + TT - 1) / TT;
     if (groups > max_groups) groups = max_groups;
     if (groups < 1) groups = 1;
@@ -395,10 +417,6 @@ void pick_groups(int strips, int T, int &groups, int &tpg) {
     tpg = (tpg + TT - 1) / TT * TT;
     groups = (T + tpg - 1) / tpg;
 }
-
-constexpr size_t kXsBytes = (size_t)TT * GS * 4;
-constexpr size_t kAsBytes = (size_t)TC * RS * 4;       // per chunk, k_lora_xa_tc
-constexpr size_t kLsBytes = (size_t)TT * RS * 4;       // per chunk, k_lora_da_tc
 
 cudaError_t allow_dyn_smem() {
     static cudaError_t done = [] {
@@ -427,7 +445,7 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     p.X = X;
     p.x16 = (uint16_t *)x16;      // written by the first launch only
     p.ldx16 = ldx16;
-    p.fp16 = fp16;
+    (void)fp16;      // bf16 math mode only: the shared-memory tile and the 16-bit copy are the same bf16 values
     p.T = T;
     p.K = K;
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
@@ -459,7 +477,7 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
     pick_groups(strips_sum, T, groups, tpg);
     DyParams p{};
     p.T = T;
-    p.fp16 = fp16;
+    (void)fp16;
     p.tok_per_group = tpg;
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
