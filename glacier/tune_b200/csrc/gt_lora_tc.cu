@@ -147,21 +147,6 @@ __device__ __forceinline__ void tile_store(const float4 (&v)[NI], int t0, int t_
         *reinterpret_cast<uint2 *>(tile + r * GSB + c * 2) = pk;
     }
 }
-// A [rows x 16] slab of a row-major fp32 matrix with `ld` columns (rows row0.., columns r0..r0+15; zero outside
-// row_end / rc) -> bf16 rank tile in shared memory, rows RSB bytes apart.  256 threads.
-__device__ __forceinline__ void rank_tile_store(const float *__restrict__ src, int ld, int row0, int row_end, int r0, int rc, int rows,
-                                                uint8_t *tile, int tid) {
-    for (int i = tid; i < rows * 8; i += 256) {
-        const int rr = i >> 3, c = (i & 7) * 2;
-        float a = 0.f, b = 0.f;
-        if (row0 + rr < row_end) {
-            const float *p = src + (int64_t)(row0 + rr) * ld + r0 + c;
-            if (c < rc) a = __ldg(p);
-            if (c + 1 < rc) b = __ldg(p + 1);
-        }
-        *reinterpret_cast<uint32_t *>(tile + rr * RSB + c * 2) = pack_bf16(a, b);
-    }
-}
 // fp32 accumulator fragment of a 16 x 8 tile (rows m0 + g / + 8, columns n0 + 2*t4 / + 1) added into dst[rows, ld]
 __device__ __forceinline__ void frag_atomic_add(float *dst, int64_t ld, const float (&d)[4], int row_a, int row_end, int col, int col_end,
                                                 float scale) {
@@ -176,21 +161,40 @@ __device__ __forceinline__ void frag_atomic_add(float *dst, int64_t ld, const fl
     }
 }
 
+// Four consecutive floats src[row, col .. col + 3] of a row-major matrix with `ld` columns; zero at and beyond
+// col_end or when the row is not valid.  `vec`: rows are 16-byte aligned and ld is a multiple of 4.
+__device__ __forceinline__ float4 ld4(const float *__restrict__ src, int64_t row, int ld, int col, int col_end, bool row_ok, bool vec) {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!row_ok || col >= col_end) return r;
+    const float *p = src + row * ld + col;
+    if (vec && col + 3 < col_end) return __ldg(reinterpret_cast<const float4 *>(p));
+    r.x = __ldg(p);
+    if (col + 1 < col_end) r.y = __ldg(p + 1);
+    if (col + 2 < col_end) r.z = __ldg(p + 2);
+    if (col + 3 < col_end) r.w = __ldg(p + 3);
+    return r;
+}
+__device__ __forceinline__ void st_bf16x4(uint8_t *dst, const float4 &v) {
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
 // ------------------------------------------------------------------------------------------------
-// low_j[T, R_j] += X[T, K] * A_j[K, R_j] over the block's K slice (grid.y slices of 128) for up to kMaxChunks
-// 16-rank chunks that share X (the adapters of q, k, v or of gate, up): X is read and rounded once, fp32 atomics
-// into each low_j (pre-zeroed).  8 warps = 4 token m-tiles x 2 halves of the slice's 8 k-steps; each warp covers
-// both 8-wide rank n-tiles of every chunk.
+// low_j[T, R_j] += X[T, K] * A_j[K, R_j] for up to kMaxChunks 16-rank chunks that share X (the adapters of q, k, v or
+// of gate, up).  A block owns one 64-token tile and a run of 128-column strips of X: it walks the strips with the
+// next strip's X tile and A tiles in flight in registers, keeps its [64 x 16] partial sums of every chunk in
+// registers across the strips, and adds them into low_j (pre-zeroed) once at the end - a low element receives one
+// atomic add per block that shares its tokens, not one per strip.  X is read and rounded once; its bf16 copy goes
+// to x16.  8 warps = 4 token m-tiles x 2 halves of a strip's 8 k-steps; each warp covers both rank n-tiles.
 // ------------------------------------------------------------------------------------------------
 struct XaChunk {
     const float *A;
     float *low;
-    int R, r0;
+    int R, r0, vec;
 };
 struct XaParams {
     const float *X;
     uint16_t *x16;
-    int ldx16, T, K, n;
+    int ldx16, T, K, n, strips_per_block;
     XaChunk c[kMaxChunks];
     FillList fills;
 };
@@ -198,66 +202,105 @@ constexpr int kXsBytes = TT * GSB;            // activation tile
 constexpr int kAsBytes = TC * RSB;            // per chunk, k_lora_xa_tc: A[k0.., r0..] as [128][16]
 constexpr int kLsBytes = TT * RSB;            // per chunk, k_lora_da_tc / k_lora_dy_tc: [64 tokens][16]
 
-__global__ void __launch_bounds__(256) k_lora_xa_tc(const XaParams p) {
+__global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     uint8_t *Xs = dyn_smem;
     uint8_t *As = dyn_smem + kXsBytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int t0 = blockIdx.x * TT, k0 = blockIdx.y * TC;
     const int T = p.T, K = p.K;
+    const int t0 = blockIdx.x * TT;
+    const int n_strips = (K + TC - 1) / TC;
+    const int s0 = blockIdx.y * p.strips_per_block, s1 = min(n_strips, s0 + p.strips_per_block);
     pdl_wait();
     pdl_trigger();
-    float4 v[NI];
-    tile_load(p.X, K, t0, T, k0, v, tid);
+    float4 v[NI], av[kMaxChunks][2];
+    // this thread's two float4 of every chunk's [128 x 16] tile of A: rows k0 + (tid + 256 i) / 4, columns 4 (tid % 4)
+    auto a_load = [&](int k0) {
 #pragma unroll
-    for (int j = 0; j < kMaxChunks; j++) {
-        if (j < p.n) {
-            const XaChunk c = p.c[j];
-            rank_tile_store(c.A, c.R, k0, K, c.r0, min(16, c.R - c.r0), TC, As + j * kAsBytes, tid);
+        for (int j = 0; j < kMaxChunks; j++) {
+            if (j < p.n) {
+                const XaChunk c = p.c[j];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int idx = tid + i * 256, row = k0 + (idx >> 2);
+                    av[j][i] = ld4(c.A + c.r0, row, c.R, (idx & 3) * 4, min(16, c.R - c.r0), row < K, c.vec != 0);
+                }
+            }
         }
-    }
-    tile_store(v, t0, T, k0, Xs, p.x16, p.ldx16, tid);
-    __syncthreads();
+    };
+    tile_load(p.X, K, t0, T, s0 * TC, v, tid);
+    a_load(s0 * TC);
+    float d[kMaxChunks][2][4];
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) d[j][i][0] = d[j][i][1] = d[j][i][2] = d[j][i][3] = 0.f;
     const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;
     const uint32_t xs = smem_u32(Xs), as = smem_u32(As);
-    uint32_t a[4][4];
+    for (int s = s0; s < s1; s++) {
+        __syncthreads();
+        tile_store(v, t0, T, s * TC, Xs, p.x16, p.ldx16, tid);
 #pragma unroll
-    for (int ks = 0; ks < 4; ks++) ldsm_x4(lm_a_mk(xs, GSB, m0, kh + ks * 16, lane), a[ks]);
+        for (int j = 0; j < kMaxChunks; j++) {
+            if (j < p.n) {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int idx = tid + i * 256;
+                    st_bf16x4(As + j * kAsBytes + (idx >> 2) * RSB + (idx & 3) * 8, av[j][i]);
+                }
+            }
+        }
+        if (s + 1 < s1) {      // the next strip's loads fly during the MMAs below
+            tile_load(p.X, K, t0, T, (s + 1) * TC, v, tid);
+            a_load((s + 1) * TC);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t a[4];
+            ldsm_x4(lm_a_mk(xs, GSB, m0, kh + ks * 16, lane), a);
+#pragma unroll
+            for (int j = 0; j < kMaxChunks; j++) {
+                if (j < p.n) {
+                    uint32_t b[4];
+                    ldsm_x4_t(lm_b_kn(as + j * kAsBytes, RSB, 0, kh + ks * 16, lane), b);
+                    mma_bf16(d[j][0], a, b[0], b[1]);
+                    mma_bf16(d[j][1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
 #pragma unroll
     for (int j = 0; j < kMaxChunks; j++) {
         if (j >= p.n) break;
-        float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            uint32_t b[4];
-            ldsm_x4_t(lm_b_kn(as + j * kAsBytes, RSB, 0, kh + ks * 16, lane), b);
-            mma_bf16(d[0], a[ks], b[0], b[1]);
-            mma_bf16(d[1], a[ks], b[2], b[3]);
-        }
         const XaChunk c = p.c[j];
         const int rc = min(16, c.R - c.r0);
 #pragma unroll
-        for (int i = 0; i < 2; i++)
-            frag_atomic_add(c.low + c.r0, c.R, d[i], t0 + m0 + g, T, i * 8 + 2 * t4, rc, 1.f);
+        for (int i = 0; i < 2; i++) frag_atomic_add(c.low + c.r0, c.R, d[j][i], t0 + m0 + g, T, i * 8 + 2 * t4, rc, 1.f);
     }
     do_fills(p.fills, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, tid);
 }
 
 // ------------------------------------------------------------------------------------------------
-// One pass over dY_m per member m = blockIdx.z: the block owns a 128-column strip and a token group, walked in
-// 64-token tiles.
-//   dLow[t, r] += sum_c dY[t, c] * B[r, c]      8 warps = 4 token m-tiles x 2 halves of the strip's 8 k-steps
-//   dB[r, c]   += s * sum_t low[t, r] * dY[t, c] 1 m-tile (ranks) x 16 n-tiles (columns), 2 per warp, 4 k-steps
+// One pass over dY_m per member m = blockIdx.z.  A block owns one 64-token tile and a run of 128-column strips of
+// dY: it walks the strips with the next strip's dY tile and B tile in flight in registers.
+//   dLow[t, r] += sum_c dY[t, c] * B[r, c]      kept in registers across the strips, one atomic add per element and
+//                                               block at the end; 8 warps = 4 token m-tiles x 2 halves of a strip's
+//                                               8 k-steps, both rank n-tiles per warp
+//   dB[r, c]   += s * sum_t low[t, r] * dY[t, c] per strip: 1 m-tile (ranks) x 16 n-tiles (columns), 2 per warp,
+//                                               4 token k-steps; added into dB after every strip (one add per
+//                                               element and token tile)
+// The low tile of the block's tokens is staged once.  The bf16 copy of dY goes to dy16.
 // ------------------------------------------------------------------------------------------------
 struct DyMember {
     const float *dY, *low, *B;
     float *dB, *dLow;
     uint16_t *dy16;
-    int ld16, N, R, r0;
+    int ld16, N, R, r0, vec_b, vec_low;
     float scaling;
 };
 struct DyParams {
-    int T, tok_per_group, n;
+    int T, strips_per_block, n;
     DyMember m[kMaxChunks];
     FillList fills;
 };
@@ -270,51 +313,60 @@ __global__ void __launch_bounds__(256, 3) k_lora_dy_tc(const DyParams p) {
     pdl_trigger();
     const DyMember m = p.m[blockIdx.z];
     const int N = m.N, R = m.R, r0 = m.r0, T = p.T;
-    const int c0 = blockIdx.x * TC;
+    const int n_strips = (N + TC - 1) / TC;
+    const int s0 = blockIdx.x * p.strips_per_block, s1 = min(n_strips, s0 + p.strips_per_block);
     const int lb = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, nb = gridDim.x * gridDim.y * gridDim.z;
-    if (c0 >= N) {      // a member with fewer column strips than the widest one
+    if (s0 >= n_strips) {      // a member with fewer column strips than the widest one
         do_fills(p.fills, lb, nb, threadIdx.x);
         return;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int tg0 = blockIdx.y * p.tok_per_group, tg1 = min(T, tg0 + p.tok_per_group);
+    const int t0 = blockIdx.y * TT;
     const int rc = min(16, R - r0);
-    float4 v[NI];
-    tile_load(m.dY, N, tg0, tg1, c0, v, tid);
-    for (int i = tid; i < 16 * (TC / 2); i += 256) {
-        const int r = i / (TC / 2), c = (i % (TC / 2)) * 2;
-        float a = 0.f, b = 0.f;
-        if (r < rc) {
-            const float *q = m.B + (int64_t)(r0 + r) * N + c0 + c;
-            if (c0 + c < N) a = __ldg(q);
-            if (c0 + c + 1 < N) b = __ldg(q + 1);
+    float4 v[NI], bv[2];
+    // this thread's two float4 of the strip's [16 x 128] tile of B: rank (tid + 256 i) / 32, columns 4 ((tid + 256 i) % 32)
+    auto b_load = [&](int c0) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int idx = tid + i * 256, r = idx >> 5;
+            bv[i] = ld4(m.B, r0 + r, N, c0 + (idx & 31) * 4, N, r < rc, m.vec_b != 0);
         }
-        *reinterpret_cast<uint32_t *>(Bs + r * GSB + c * 2) = pack_bf16(a, b);
+    };
+    tile_load(m.dY, N, t0, T, s0 * TC, v, tid);
+    b_load(s0 * TC);
+    {
+        const int row = tid >> 2;
+        const float4 lv = ld4(m.low + r0, t0 + row, R, (tid & 3) * 4, rc, t0 + row < T, m.vec_low != 0);
+        st_bf16x4(Ls + row * RSB + (tid & 3) * 8, lv);
     }
     const uint32_t gs = smem_u32(Gs), bs = smem_u32(Bs), ls = smem_u32(Ls);
-    float accB[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;    // dLow: token m-tile, half of the strip's columns
     const int cb = warp * 16;                                 // dB: this warp's two 8-column n-tiles
     uint16_t *dy16 = r0 == 0 ? m.dy16 : nullptr;
-    for (int ts = tg0; ts < tg1; ts += TT) {
+    for (int s = s0; s < s1; s++) {
+        const int c0 = s * TC;
         __syncthreads();
-        tile_store(v, ts, tg1, c0, Gs, dy16, m.ld16, tid);
-        if (ts + TT < tg1) tile_load(m.dY, N, ts + TT, tg1, c0, v, tid);     // next tile's loads fly during the MMAs below
-        rank_tile_store(m.low, R, ts, tg1, r0, rc, TT, Ls, tid);
-        __syncthreads();
-        {
-            float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        tile_store(v, t0, T, c0, Gs, dy16, m.ld16, tid);
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                uint32_t a[4], b[4];
-                ldsm_x4(lm_a_mk(gs, GSB, m0, kh + ks * 16, lane), a);
-                ldsm_x4(lm_b_nk(bs, GSB, 0, kh + ks * 16, lane), b);
-                mma_bf16(d[0], a, b[0], b[1]);
-                mma_bf16(d[1], a, b[2], b[3]);
-            }
-#pragma unroll
-            for (int i = 0; i < 2; i++) frag_atomic_add(m.dLow + r0, R, d[i], ts + m0 + g, tg1, i * 8 + 2 * t4, rc, 1.f);
+        for (int i = 0; i < 2; i++) {
+            const int idx = tid + i * 256;
+            st_bf16x4(Bs + (idx >> 5) * GSB + (idx & 31) * 8, bv[i]);
         }
+        if (s + 1 < s1) {      // the next strip's loads fly during the MMAs below
+            tile_load(m.dY, N, t0, T, (s + 1) * TC, v, tid);
+            b_load((s + 1) * TC);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t a[4], b[4];
+            ldsm_x4(lm_a_mk(gs, GSB, m0, kh + ks * 16, lane), a);
+            ldsm_x4(lm_b_nk(bs, GSB, 0, kh + ks * 16, lane), b);
+            mma_bf16(d[0], a, b[0], b[1]);
+            mma_bf16(d[1], a, b[2], b[3]);
+        }
+        float accB[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < TT / 16; ks++) {
             uint32_t a[4], b[4];
@@ -323,23 +375,27 @@ __global__ void __launch_bounds__(256, 3) k_lora_dy_tc(const DyParams p) {
             mma_bf16(accB[0], a, b[0], b[1]);
             mma_bf16(accB[1], a, b[2], b[3]);
         }
-    }
-    // accB rows = ranks, columns = strip columns
+        // accB rows = ranks, columns = strip columns
 #pragma unroll
-    for (int i = 0; i < 2; i++) frag_atomic_add(m.dB + (int64_t)r0 * N, N, accB[i], g, rc, c0 + cb + i * 8 + 2 * t4, N, m.scaling);
+        for (int i = 0; i < 2; i++)
+            frag_atomic_add(m.dB + (int64_t)r0 * N, N, accB[i], g, rc, c0 + cb + i * 8 + 2 * t4, N, m.scaling);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) frag_atomic_add(m.dLow + r0, R, d[i], t0 + m0 + g, T, i * 8 + 2 * t4, rc, 1.f);
     do_fills(p.fills, lb, nb, tid);
 }
 
 // ------------------------------------------------------------------------------------------------
 // dA_j[k, r] += s_j * sum_t X[t, k] * dLow_j[t, r] for up to kMaxChunks 16-rank chunks that share X: the block owns
-// a 128-column strip of X and a token group.  8 warps = 8 m-tiles of 16 columns; each covers both rank n-tiles of
-// every chunk over the 4 token k-steps of a tile.
+// a 128-column strip of X and a token group, walked in 64-token tiles with the next tile of X and of every dLow_j
+// in flight in registers.  8 warps = 8 m-tiles of 16 columns; each covers both rank n-tiles of every chunk over the
+// 4 token k-steps of a tile and keeps its sums in registers until the end.
 // ------------------------------------------------------------------------------------------------
 struct DaChunk {
     const float *dLow;
     float *dA;
     float scaling;
-    int R, r0;
+    int R, r0, vec;
 };
 struct DaParams {
     const float *X;
@@ -347,7 +403,7 @@ struct DaParams {
     DaChunk c[kMaxChunks];
 };
 
-__global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
+__global__ void __launch_bounds__(256, 2) k_lora_da_tc(const DaParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     uint8_t *Xs = dyn_smem;
     uint8_t *Ls = dyn_smem + kXsBytes;
@@ -364,18 +420,29 @@ __global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
 #pragma unroll
         for (int i = 0; i < 2; i++) acc[j][i][0] = acc[j][i][1] = acc[j][i][2] = acc[j][i][3] = 0.f;
     const uint32_t xs = smem_u32(Xs), ls = smem_u32(Ls);
-    float4 v[NI];
-    tile_load(p.X, K, tg0, tg1, k0, v, tid);
-    for (int ts = tg0; ts < tg1; ts += TT) {
-        __syncthreads();
-        tile_store(v, ts, tg1, k0, Xs, nullptr, 0, tid);
-        if (ts + TT < tg1) tile_load(p.X, K, ts + TT, tg1, k0, v, tid);      // next tile's loads fly during the MMAs below
+    float4 v[NI], lv[kMaxChunks];
+    // this thread's float4 of every chunk's [64 x 16] tile of dLow: token ts + tid / 4, ranks 4 (tid % 4)
+    auto l_load = [&](int ts) {
 #pragma unroll
         for (int j = 0; j < kMaxChunks; j++) {
             if (j < p.n) {
                 const DaChunk c = p.c[j];
-                rank_tile_store(c.dLow, c.R, ts, tg1, c.r0, min(16, c.R - c.r0), TT, Ls + j * kLsBytes, tid);
+                const int row = ts + (tid >> 2);
+                lv[j] = ld4(c.dLow + c.r0, row, c.R, (tid & 3) * 4, min(16, c.R - c.r0), row < tg1, c.vec != 0);
             }
+        }
+    };
+    tile_load(p.X, K, tg0, tg1, k0, v, tid);
+    l_load(tg0);
+    for (int ts = tg0; ts < tg1; ts += TT) {
+        __syncthreads();
+        tile_store(v, ts, tg1, k0, Xs, nullptr, 0, tid);
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; j++)
+            if (j < p.n) st_bf16x4(Ls + j * kLsBytes + (tid >> 2) * RSB + (tid & 3) * 8, lv[j]);
+        if (ts + TT < tg1) {      // the next tile's loads fly during the MMAs below
+            tile_load(p.X, K, ts + TT, tg1, k0, v, tid);
+            l_load(ts + TT);
         }
         __syncthreads();
 #pragma unroll
@@ -403,13 +470,9 @@ __global__ void __launch_bounds__(256, 3) k_lora_da_tc(const DaParams p) {
     }
 }
 
-// token groups so that (column strips x groups) covers the SMs about twice; groups are whole 64-token tiles
+// token groups so that (column strips x groups) covers the SMs about `waves` times; groups are whole 64-token tiles
 void pick_groups(int strips, int T, int &groups, int &tpg) {
-    static const int waves = [] {
-        const char *v = getenv("GT_LORA_WAVES");
-        return v ? atoi(v) : 2;
-    }();
-    groups = (waves * 148 + strips - 1) / (strips > 0 ? strips : 1);
+    groups = (3 * 148 + strips - 1) / (strips > 0 ? strips : 1);
     const int max_groups = (T + TT - 1) / TT;
     if (groups > max_groups) groups = max_groups;
     if (groups < 1) groups = 1;
@@ -417,6 +480,18 @@ void pick_groups(int strips, int T, int &groups, int &tpg) {
     tpg = (tpg + TT - 1) / TT * TT;
     groups = (T + tpg - 1) / tpg;
 }
+// strips per block for the kernels that walk strips: about three blocks per SM, at most 8 strips in a run
+int pick_strip_run(int strips_total, int T) {
+    const int tiles = (T + TT - 1) / TT;
+    int run = (strips_total * tiles + 3 * 148 - 1) / (3 * 148);
+    static const int forced = [] {
+        const char *v = getenv("GT_LORA_RUN");
+        return v ? atoi(v) : 0;
+    }();
+    if (forced > 0) run = forced;
+    return run < 1 ? 1 : (run > 8 ? 8 : run);
+}
+inline int is_vec(const void *p, int ld) { return ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld & 3) == 0) ? 1 : 0; }
 
 cudaError_t allow_dyn_smem() {
     static cudaError_t done = [] {
@@ -440,7 +515,7 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     if (T <= 0 || K <= 0 || n <= 0) return cudaSuccess;
     cudaError_t e = allow_dyn_smem();
     if (e != cudaSuccess) return e;
-    dim3 grid((T + TT - 1) / TT, (K + TC - 1) / TC);
+    const int strips = (K + TC - 1) / TC;
     XaParams p{};
     p.X = X;
     p.x16 = (uint16_t *)x16;      // written by the first launch only
@@ -448,10 +523,12 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     (void)fp16;      // bf16 math mode only: the shared-memory tile and the 16-bit copy are the same bf16 values
     p.T = T;
     p.K = K;
+    p.strips_per_block = pick_strip_run(strips, T);
+    dim3 grid((T + TT - 1) / TT, (strips + p.strips_per_block - 1) / p.strips_per_block);
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_xa_tc, grid, dim3(256), kXsBytes + p.n * kAsBytes, s, p);
+        cudaError_t le = launch_k(k_lora_xa_tc, grid, dim3(256), (size_t)(kXsBytes + p.n * kAsBytes), s, p);
         p.n = 0;
         p.x16 = nullptr;
         p.fills.n = 0;
@@ -459,7 +536,7 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     };
     for (int j = 0; j < n; j++)
         for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
-            p.c[p.n++] = XaChunk{jobs[j].A, jobs[j].low_zeroed, jobs[j].R, r0};
+            p.c[p.n++] = XaChunk{jobs[j].A, jobs[j].low_zeroed, jobs[j].R, r0, is_vec(jobs[j].A, jobs[j].R)};
             if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
         }
     return flush();
@@ -467,22 +544,21 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
 
 cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, const RowFill *fills, int n_fills, cudaStream_t s) {
     if (T <= 0 || n <= 0) return cudaSuccess;
+    (void)fp16;
     int strips_sum = 0, strips_max = 0;
     for (int j = 0; j < n; j++) {
         const int st = (jobs[j].N + TC - 1) / TC;
         strips_sum += st;
         strips_max = st > strips_max ? st : strips_max;
     }
-    int groups, tpg;
-    pick_groups(strips_sum, T, groups, tpg);
     DyParams p{};
     p.T = T;
-    (void)fp16;
-    p.tok_per_group = tpg;
+    p.strips_per_block = pick_strip_run(strips_sum, T);
+    const dim3 grid_xy((strips_max + p.strips_per_block - 1) / p.strips_per_block, (T + TT - 1) / TT);
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_dy_tc, dim3(strips_max, groups, p.n), dim3(256), 0, s, p);
+        cudaError_t le = launch_k(k_lora_dy_tc, dim3(grid_xy.x, grid_xy.y, p.n), dim3(256), (size_t)0, s, p);
         p.n = 0;
         p.fills.n = 0;
         return le;
@@ -498,6 +574,8 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
             DyMember m{};
             m.dY = b.dY; m.low = b.low; m.B = b.B; m.dB = b.dB; m.dLow = b.dLow_zeroed; m.dy16 = (uint16_t *)b.dy16;
             m.ld16 = b.ld16; m.N = b.N; m.R = b.R; m.r0 = r0; m.scaling = b.scaling;
+            m.vec_b = is_vec(b.B, b.N);
+            m.vec_low = is_vec(b.low, b.R);
             p.m[p.n++] = m;
             if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
         }
@@ -520,13 +598,13 @@ cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, i
     p.tok_per_group = tpg;
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_da_tc, dim3(strips, groups), dim3(256), kXsBytes + p.n * kLsBytes, s, p);
+        cudaError_t le = launch_k(k_lora_da_tc, dim3(strips, groups), dim3(256), (size_t)(kXsBytes + p.n * kLsBytes), s, p);
         p.n = 0;
         return le;
     };
     for (int j = 0; j < n; j++)
         for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
-            p.c[p.n++] = DaChunk{jobs[j].dLow, jobs[j].dA, jobs[j].scaling, jobs[j].R, r0};
+            p.c[p.n++] = DaChunk{jobs[j].dLow, jobs[j].dA, jobs[j].scaling, jobs[j].R, r0, is_vec(jobs[j].dLow, jobs[j].R)};
             if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
         }
     return flush();
