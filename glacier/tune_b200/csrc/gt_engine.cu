@@ -174,7 +174,7 @@ float *low_of(const gt_adapter *a) { return (float *)a->low.p; }
 float *dlow_of(const gt_adapter *a, int T) { return (float *)((char *)a->low.p + low_bytes(a, T)); }
 
 // low_j = X * A_j for every listed adapter (they share X), and optionally the 16-bit copy of X.  One memset per
-// adapter clears low (the TF32 kernel sums into it) and dLow of the same step; one kernel pass reads X.
+// adapter clears low (the warp-MMA kernel sums into it) and dLow of the same step; one kernel pass reads X.
 int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, void *x16, int fp16, int T, int K,
                 const RowFill *fills = nullptr, int n_fills = 0) {
     LoraXaJob jobs[kMaxGroup];
@@ -300,7 +300,7 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
                         float *zero_dx) {
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
-    const bool fast = e->math_mode == GT_MATH_BF16;      // TF32 warp-MMA reductions; exact fp32 otherwise
+    const bool fast = e->math_mode == GT_MATH_BF16;      // bf16 warp-MMA reductions; exact fp32 otherwise
     gt_adapter *fresh[kMaxGroup];
     int n_fresh = 0;
     for (int j = 0; j < n; j++) {
