@@ -430,6 +430,58 @@ def run_ours(args) -> None:
     eng.close()
 
 
+# ------------------------------------------------------------------------------------------------ M sweep
+def run_sweep(args) -> None:
+    """Token-count sweep of the Q4_K_M-mixed 7B projection set (v and down in Q6_K): device time of the projection
+    kernel alone, forward and dX, per projection and M, against the roofline that bounds it (weight streaming from
+    HBM for few tokens, the tensor pipe for many).  Prints one JSON line {"sweep": [...]}; a table goes to stderr."""
+    import torch
+    from glacier.tune_b200 import capi as G
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --sweep: no CUDA device")
+    peaks = measured_peaks()
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    eng = G.Engine(0, G.MATH_BF16, stream=stream.cuda_stream)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    rows = []
+    for name in ("q", "k", "v", "gate", "down"):
+        N, K = synth.QWEN7B_PROJ[name]
+        qt = synth.TYPE_Q6_K if name in ("v", "down") else synth.TYPE_Q4_K
+        c = synth.make_projection_case(qt, N, K, 1, synth.seed_for(2, 0, name))
+        w = eng.upload_weight(qt, c["w"], N, K)
+        wbytes = N * K // 256 * (144 if qt == synth.TYPE_Q4_K else 210)       # GGUF bytes: the algorithmic weight traffic
+        for M in args.sweep_m:
+            X = torch.randn((M, K), device="cuda")
+            dY = torch.randn((M, N), device="cuda")
+            Y = torch.empty((M, N), device="cuda")
+            dX = torch.zeros((M, K), device="cuda")
+            for direction in ("fwd", "dx"):
+                call = (lambda: eng.forward(w, None, X, Y)) if direction == "fwd" else (lambda: eng.backward(w, None, dY, None, dX))
+                for _ in range(3):
+                    call()
+                eng.profile_read(True)
+                eng.profile_enable(True)
+                for _ in range(7):
+                    flush.zero_()          # weights and activations come from HBM in every timed launch
+                    call()
+                pr = eng.profile_read(True)
+                eng.profile_enable(False)
+                us = 1e3 * pr["gemm_ms"] / max(1, pr["gemm_launches"])
+                tf = 2.0 * M * N * K / us / 1e6
+                gbs = wbytes / us / 1e3
+                rows.append({"proj": name, "qtype": "Q6_K" if qt == synth.TYPE_Q6_K else "Q4_K", "N": N, "K": K, "M": M,
+                             "dir": direction, "us": us, "tflops": tf, "frac_tensor": tf / peaks["bf16_tflops"],
+                             "weight_gbs": gbs, "frac_hbm": gbs / peaks["hbm_gbs"]})
+                print(f"{name:5s} {rows[-1]['qtype']} M={M:5d} {direction:3s}: {us:8.1f} us {tf:8.1f} TFLOP/s ({100 * tf / peaks['bf16_tflops']:5.1f} % of "
+                      f"{peaks['bf16_tflops']:.0f})  weights {gbs:7.1f} GB/s ({100 * gbs / peaks['hbm_gbs']:5.1f} % of {peaks['hbm_gbs']:.0f})",
+                      file=sys.stderr, flush=True)
+        w.free()
+    eng.close()
+    print(json.dumps({"sweep": rows, "peaks": peaks, "timing": "CUDA events around the projection kernel launch, mean of 7 after 3 "
+                      "warm-up launches, 256 MiB written between launches"}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -440,7 +492,12 @@ def main() -> None:
     ap.add_argument("--e2e-sync", action="store_true", help="end-to-end leg with synchronous host-buffer calls")
     ap.add_argument("--zero-dx", action="store_true", help="zero-fill dX before each backward and accumulate into it")
     ap.add_argument("--no-group", action="store_true", help="one call per projection instead of q,k,v and gate,up groups")
+    ap.add_argument("--sweep", action="store_true", help="token-count sweep of the Q4_K_M projection set instead of the step benchmark")
+    ap.add_argument("--sweep-m", type=int, nargs="+", default=[1, 16, 128, 512, 2048])
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -225,6 +225,40 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
     }
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
+    // Few tokens: the projection is bound by streaming the packed weights, which the warp-level kernel does several
+    // times faster than the CTA-wide tensor-core kernel; the adapter term is added by the exact rank-r kernel.
+    bool stream = e->math_mode == GT_MATH_BF16 && (reinterpret_cast<uintptr_t>(Xd) & 15) == 0;
+    for (int j = 0; j < n && stream; j++) stream = stream_fwd_ok(&w[j]->dev, T);
+    if (stream) {
+        gt_adapter *with[kMaxGroup];
+        int n_with = 0;
+        for (int j = 0; j < n; j++)
+            if (lora[j]) with[n_with++] = ad[j];
+        if (n_with) {
+            int rc = compute_low(e, with, n_with, Xd, nullptr, 0, T, K);
+            if (rc != GT_OK) return rc;
+        }
+        for (int j = 0; j < n; j++) {
+            const WeightDev &wd = w[j]->dev;
+            GT_LAUNCH(e, launch_fill_rows(Yd[j], wd.bias, T, wd.N, e->stream));      // the kernel adds into Y
+            cudaEvent_t ea = nullptr, eb = nullptr;
+            if (e->profile) {
+                ea = next_event(e);
+                eb = next_event(e);
+                if (ea) cudaEventRecord(ea, e->stream);
+            }
+            cudaError_t ce = launch_stream_fwd(&wd, Xd, Yd[j], T, e->sm_count, e->status, e->trace, e->stream);
+            if (e->profile && eb) cudaEventRecord(eb, e->stream);
+            e->gemm_launches += 1;
+            e->kernel_launches += 1;
+            e->gemm_flops += 2.0 * (double)T * (double)wd.N * (double)K;
+            if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "streaming forward launch failed: %s", cudaGetErrorString(ce));
+            if (lora[j])
+                GT_LAUNCH(e, launch_lora_delta_fp32(low_of(ad[j]), ad[j]->B, Yd[j], nullptr, T, wd.N, ad[j]->rank, ad[j]->scaling,
+                                                    ad[j]->b_nonzero, e->stream));
+        }
+        return GT_OK;
+    }
     GT_CUDA(e->x16.reserve((size_t)T * K * 2));
     UmmaLaunch m[kMaxGroup];
     for (int j = 0; j < n; j++) {

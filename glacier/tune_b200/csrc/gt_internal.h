@@ -16,6 +16,7 @@ struct WeightDev {
     float *bias = nullptr;        // [N] or null
     bool tma_ok = false;          // row-aligned and tensor maps built
     CUtensorMap tm_hdr, tm_q0, tm_q1;   // 2-D byte maps over [N, row_bytes], boxes of 64 rows
+    CUtensorMap tm_rows;                // Q4_K: 32-bit words over [N, row_bytes / 4], boxes of 16 rows x 288 bytes (two blocks)
 };
 
 // ---- CUDA-core kernels (gt_fp32_kernels.cu) -------------------------------------------------------------
@@ -134,6 +135,13 @@ struct EngineView {
     int *status;       // device int[4], bounded-wait codes of the tensor-core kernels
     void *mutex;       // std::mutex * serialising calls on the engine
 };
+// ---- weight-streaming forward projection for few tokens (gt_stream_gemm.cu): warp-level MMAs on the quantized
+// integers, scales applied per sub-block on the partial sums.  Q4_K, whole 256-wide rows, T <= stream_max_tokens().
+int stream_max_tokens();
+bool stream_fwd_ok(const WeightDev *w, int T);
+cudaError_t launch_stream_fwd(const WeightDev *w, const float *X, float *Y_prefilled, int T, int sm_count, int *status, void *trace,
+                              cudaStream_t s);
+
 // ---- launches with programmatic dependent launch (the kernel must call pdl_wait() before touching global memory).
 // Environment GT_PDL=1 turns the attribute on; the default is plain stream order.
 bool pdl_enabled();

@@ -71,6 +71,14 @@ __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---------------------------------------------------------------- bulk copy (untiled): global -> shared, bytes credited to an mbarrier
+// both addresses 16-byte aligned, size a multiple of 16 bytes
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // ---------------------------------------------------------------- TMA (tile mode, single CTA destination)
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void *tmap, int32_t c0, int32_t c1, uint32_t bar) {
     asm volatile(

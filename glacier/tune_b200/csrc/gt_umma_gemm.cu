@@ -662,6 +662,9 @@ cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
                              (uint64_t)w->row_bytes, 32, 64, CU_TENSOR_MAP_SWIZZLE_32B);
     else
         w->tm_q1 = w->tm_q0;
+    if (w->qtype == kTypeQ4K)      // whole packed rows for the few-token streaming kernel
+        ok = ok && encode_2d(&w->tm_rows, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w->data, (uint64_t)w->row_bytes / 4, (uint64_t)w->N,
+                             (uint64_t)w->row_bytes, 72, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) {
         if (err) *err = "cuTensorMapEncodeTiled failed for a weight tensor";
         return cudaErrorInvalidValue;

@@ -128,6 +128,45 @@ def test_projection_parity(G, eng, oracle, mode, qtype, N, K, T):
     assert oracle.rel_fro(y, y_cpu) < TOL[mode]
 
 
+STREAM_SHAPES = [
+    # few tokens, bf16 mode: the weight-streaming forward kernel (warp MMAs on the quantized integers)
+    (128, 256, 1), (200, 768, 5), (24, 512, 8), (512, 3584, 16), (1000, 1024, 9), (256, 18944, 16), (640, 2048, 13),
+]
+
+
+@pytest.mark.parametrize("N,K,T", STREAM_SHAPES)
+def test_few_token_forward_streaming_kernel(G, eng, oracle, N, K, T):
+    """T <= 16 in bf16 mode: Y against the fp64 oracle with and without bias / adapter, and linear in the batch: row t
+    of a T-token call equals the one-token call on that row (the kernel's per-token sums are independent)."""
+    import torch
+    c = S.make_projection_case(S.TYPE_Q4_K, N, K, T, seed=N + K + T, with_bias=True)
+    eng.set_math_mode(0)
+    yr, _, _, _ = _reference(oracle, c)
+    yb, _, _, _ = _reference(oracle, c, lora=False, bias=False)
+    w = eng.upload_weight(c["qtype"], c["w"], N, K, c["bias"])
+    w0 = eng.upload_weight(c["qtype"], c["w"], N, K)
+    ad = eng.create_adapter(K, N, c["rank"], c["alpha"])
+    ad.upload(c["a"], c["b"])
+    y = eng.forward(w, ad, c["x"])
+    y0 = eng.forward(w0, None, c["x"])
+    assert oracle.rel_fro(y, yr) < 2e-2, oracle.rel_fro(y, yr)
+    assert oracle.rel_fro(y0, yb) < 2e-2
+    # the weights enter exactly and only X is rounded: with bf16-representable X the result is fp32-accurate
+    xb = S.bf16_round(c["x"])
+    yx = eng.forward(w0, None, xb)
+    want = oracle.matmul_batch(c["qtype"], c["w"], xb, K, N, T, None, f64=True)
+    assert oracle.rel_fro(yx, want) < 1e-5, oracle.rel_fro(yx, want)
+    y1 = eng.forward(w0, None, np.ascontiguousarray(xb[T - 1:T]))
+    assert np.allclose(y1[0], yx[T - 1], rtol=1e-4, atol=1e-4 * np.abs(yx).max())
+    X = torch.from_numpy(c["x"]).cuda()
+    Y = torch.full((T, N), 3.0, device="cuda")
+    eng.forward(w, ad, X, Y)
+    eng.sync()
+    assert oracle.rel_fro(Y.cpu().numpy(), yr) < 2e-2
+    for h in (w, w0, ad):
+        h.free()
+
+
 @pytest.mark.parametrize("mode", [0, 2])
 def test_base_only_and_bias_free(G, eng, oracle, mode):
     c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 40, seed=77)
