@@ -22,7 +22,7 @@ EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
-    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group",
+    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
@@ -114,6 +114,11 @@ def _ptr(a, dtype=None):
     if not isinstance(a, np.ndarray) or not a.flags.c_contiguous or (dtype is not None and a.dtype != dtype):
         raise ValueError(f"host arrays must be C-contiguous numpy {dtype}")
     return a.ctypes.data_as(C.c_void_p), False
+
+
+def stream_max_tokens() -> int:
+    """Largest token count served by the few-token weight-streaming forward kernel (0: never)."""
+    return int(load_library().gt_stream_max_tokens())
 
 
 def supports(ggml_type: int, direction: int) -> bool:

@@ -963,6 +963,8 @@ int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const flo
     return backward_host(e, 1, &w, &ad, &dY, X, dX, T, flags);
 }
 
+int gt_stream_max_tokens(void) { return stream_max_tokens(); }
+
 int gt_proj_forward_group(gt_engine *e, int32_t n, const gt_weight *const *w, gt_adapter *const *ad, const float *X, float *const *Y,
                           int32_t T, int32_t flags) {
     if (!e || !w || !X || !Y) return fail(GT_ERR_INVALID, "gt_proj_forward_group: null argument");

@@ -122,6 +122,9 @@ public:
               "LoraAdapter.Backward");
     }
 
+    gt_weight *Weight() const { return w_; }
+    gt_adapter *Handle() const { return ad_; }
+
 private:
     GpuLoraEngine &engine_;
     gt_weight *w_ = nullptr;
@@ -129,5 +132,35 @@ private:
     int in_, out_, rank_;
     float scaling_;
 };
+
+// GpuLoraEngine.ForwardQKV / the gate,up half of ForwardFfn (GpuLoraEngine.Forward.cs:205-364): n (1..3) adapted
+// projections of the same input in one engine call.  outputs[j] receives projection j.
+inline void ForwardGroup(GpuLoraEngine &engine, LoraAdapter *const *projections, int n, const Tensor &x, Tensor *const *outputs,
+                         int seqLen) {
+    gt_weight *w[3];
+    gt_adapter *a[3];
+    float *y[3];
+    for (int j = 0; j < n && j < 3; j++) {
+        w[j] = projections[j]->Weight();
+        a[j] = projections[j]->Handle();
+        y[j] = outputs[j]->DataPointer;
+    }
+    Check(gt_proj_forward_group(engine.Handle(), n, w, a, x.DataPointer, y, seqLen, 0), "ForwardGroup");
+}
+// The q|k|v (gate|up) Backward calls of a block and the sum of their input gradients (TransformerBlock.cs:660-663,
+// 812-816): dXInput = sum_j (dY[j] W_j + adapter term j), written (not accumulated) by the call.
+inline void BackwardGroup(GpuLoraEngine &engine, LoraAdapter *const *projections, int n, const Tensor *const *dY, const Tensor &x,
+                          Tensor &dXInput) {
+    gt_weight *w[3];
+    gt_adapter *a[3];
+    const float *g[3];
+    for (int j = 0; j < n && j < 3; j++) {
+        w[j] = projections[j]->Weight();
+        a[j] = projections[j]->Handle();
+        g[j] = dY[j]->DataPointer;
+    }
+    Check(gt_proj_backward_group(engine.Handle(), n, w, a, g, x.DataPointer, dXInput.DataPointer, x.Shape[0], GT_FLAG_DX_ASSIGN),
+          "BackwardGroup");
+}
 
 }  // namespace Glacier::Tune

@@ -154,6 +154,11 @@ GT_API int gt_proj_forward(gt_engine *eng, const gt_weight *w, gt_adapter *adapt
 GT_API int gt_proj_backward(gt_engine *eng, const gt_weight *w, gt_adapter *adapter_or_null, const float *dY,
                             const float *X, float *dX_accum_or_null, int32_t T, int32_t flags);
 
+/* No counterpart in the reference.  Largest token count for which gt_proj_forward runs the few-token weight-streaming
+ * kernel on Q4_K weights instead of the CTA-wide tensor-core kernel (0 = never; environment GT_STREAM_MAX_T, 0..32,
+ * read once per process). */
+GT_API int gt_stream_max_tokens(void);
+
 /* Replaces: GpuLoraEngine.ForwardQKV and the gate/up half of ForwardFfn
  * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:205-245,247-364): n (1..3) projections of the SAME input X,
  * Y[j] = X * W_j^T + bias_j + scaling_j*(X*A_j)*B_j.  With device pointers and members of one quantization type the

@@ -151,11 +151,13 @@ def test_few_token_forward_streaming_kernel(G, eng, oracle, N, K, T):
     y0 = eng.forward(w0, None, c["x"])
     assert oracle.rel_fro(y, yr) < 2e-2, oracle.rel_fro(y, yr)
     assert oracle.rel_fro(y0, yb) < 2e-2
-    # the weights enter exactly and only X is rounded: with bf16-representable X the result is fp32-accurate
+    # streaming kernel: the weights enter exactly and only X is rounded, so with bf16-representable X the result is
+    # fp32-accurate; the tensor-core kernel (streaming switched off, or T above its limit) rounds the weights to bf16
     xb = S.bf16_round(c["x"])
     yx = eng.forward(w0, None, xb)
     want = oracle.matmul_batch(c["qtype"], c["w"], xb, K, N, T, None, f64=True)
-    assert oracle.rel_fro(yx, want) < 1e-5, oracle.rel_fro(yx, want)
+    tol = 1e-5 if T <= G.stream_max_tokens() else 2e-2
+    assert oracle.rel_fro(yx, want) < tol, oracle.rel_fro(yx, want)
     y1 = eng.forward(w0, None, np.ascontiguousarray(xb[T - 1:T]))
     assert np.allclose(y1[0], yx[T - 1], rtol=1e-4, atol=1e-4 * np.abs(yx).max())
     X = torch.from_numpy(c["x"]).cuda()
