@@ -157,34 +157,36 @@ __global__ void __launch_bounds__(kSThreads, 1) k_stream_fwd_q4k(const __grid_co
     stamp();
 
     // ---- stage X: one (token, 32-weight sub-block) item per thread and step
-    const int nsb = nb * 8;
-    for (int item = tid; item < TP * nsb; item += kSThreads) {
-        const int t = item / nsb, sb = item % nsb;
-        // sub-block sb = 2*group + h; weight e of it sits in byte e of the group's 32 quant bytes (low nibble for h = 0,
-        // high for h = 1); thread t4 = e / 8 holds bytes 8*t4 .. 8*t4+7: words (b0,b2) (b1,b3) of each 4-byte half
-        uint8_t *dst = Xs + (size_t)t * p.tok_stride + (sb >> 1) * 128 + (sb & 1) * 16;
-        if (t >= p.T) {      // padding tokens of the last n-tile
-            Ss[sb * TP + t] = 0.f;
+    // Consecutive lanes take consecutive float4 of a token row (coalesced); a sub-block of 32 values is 8 lanes.
+    // Sub-block sb = 2*group + h: weight e of it sits in byte e of the group's 32 quant bytes (low nibble for h = 0,
+    // high for h = 1); MMA thread t4 = e / 8 holds bytes 8*t4 .. 8*t4+7 and wants words (e0,e2) (e1,e3) (e4,e6) (e5,e7).
+    const int nf4 = nb * 64;      // float4 per token in this K split
+    constexpr int kStageMax = 12;  // float4 per thread: TP * blocks_per_cta * 64 / kSThreads, bounded by the 48 KB of staged X
+    float4 xv[kStageMax];
 #pragma unroll
-            for (int q = 0; q < 4; q++) *reinterpret_cast<uint4 *>(dst + q * 32) = make_uint4(0u, 0u, 0u, 0u);
-            continue;
-        }
-        const float4 *src = reinterpret_cast<const float4 *>(p.X + (int64_t)t * p.K + (int64_t)kb0 * 256 + sb * 32);
-        float4 v[8];
+    for (int i = 0; i < kStageMax; i++) {      // every load is in flight before the first one is used
+        const int item = tid + i * kSThreads;
+        const int t = item / nf4, f = item - t * nf4;
+        xv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (item < TP * nf4 && t < p.T) xv[i] = __ldg(reinterpret_cast<const float4 *>(p.X + (int64_t)t * p.K + (int64_t)kb0 * 256) + f);
+    }
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = __ldg(src + i);
-        float s = 0.f;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const float4 lo = v[2 * q], hi = v[2 * q + 1];      // weights 8q .. 8q+7 of the sub-block
-            const uint4 w4 = make_uint4(pack_bf16_s(lo.x, lo.z), pack_bf16_s(lo.y, lo.w), pack_bf16_s(hi.x, hi.z), pack_bf16_s(hi.y, hi.w));
-            *reinterpret_cast<uint4 *>(dst + q * 32) = w4;
+    for (int i = 0; i < kStageMax; i++) {
+        const int item = tid + i * kSThreads;
+        if (item < TP * nf4) {      // uniform over the CTA: TP * nf4 is a multiple of kSThreads
+            const int t = item / nf4, f = item - t * nf4;
+            const int sb = f >> 3, q = (f >> 1) & 3, hf = f & 1;
+            const float4 v = xv[i];
+            const uint2 w2 = make_uint2(pack_bf16_s(v.x, v.z), pack_bf16_s(v.y, v.w));
+            *reinterpret_cast<uint2 *>(Xs + (size_t)t * p.tok_stride + (sb >> 1) * 128 + q * 32 + (sb & 1) * 16 + hf * 8) = w2;
             // S sums the ROUNDED values, the ones the MMAs see
-            const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-            for (int k = 0; k < 4; k++) s += __uint_as_float(ws[k] << 16) + __uint_as_float(ws[k] & 0xFFFF0000u);
+            float s = __uint_as_float(w2.x << 16) + __uint_as_float(w2.x & 0xFFFF0000u) + __uint_as_float(w2.y << 16) +
+                      __uint_as_float(w2.y & 0xFFFF0000u);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if ((f & 7) == 0) Ss[sb * TP + t] = s;
         }
-        Ss[sb * TP + t] = s;
     }
     __syncthreads();
 
@@ -309,7 +311,7 @@ cudaError_t launch_nt(const StreamParams &p, dim3 grid, size_t smem, cudaStream_
 int stream_max_tokens() {
     static const int v = [] {
         const char *e = getenv("GT_STREAM_MAX_T");
-        const int n = e ? atoi(e) : 0;
+        const int n = e ? atoi(e) : 16;
         return n < 0 ? 0 : (n > 32 ? 32 : n);
     }();
     return v;
