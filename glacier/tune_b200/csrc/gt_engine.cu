@@ -68,7 +68,7 @@ struct Scratch {
 
 }  // namespace
 
-constexpr int kHostSlots = 3;
+constexpr int kHostSlots = 8;
 constexpr int kSlotIn = 4, kSlotOut = 3;      // forward: X -> Y_j; backward: dY_j, X -> dX
 struct HostSlot {
     Scratch in[kSlotIn], out[kSlotOut];
@@ -119,6 +119,8 @@ struct gt_adapter {
                                  // [low_T, rank] fp32 each
     int low_T = 0;
     bool dlow_clean = false;     // dLow is still all zero (cleared together with low, not yet summed into)
+    Scratch xkeep;               // host-buffer calls: device copy of the X of the last forward, for a backward that
+    int xkeep_T = 0;             // reuses it (GT_FLAG_REUSE_LOW) instead of uploading X again
 };
 
 namespace {
@@ -215,6 +217,7 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
     for (int j = 0; j < n; j++) {
         lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0 && ad[j]->scaling != 0.f;
         if (ad && ad[j] && !lora[j]) ad[j]->low_T = 0;      // nothing kept for a later backward to reuse
+        if (ad && ad[j]) ad[j]->xkeep_T = 0;                // a kept copy of an earlier X is stale now (the host path renews it)
     }
     if (!group_tensor_ok(e, n, w)) {
         for (int j = 0; j < n; j++) {
@@ -508,6 +511,16 @@ int forward_host(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *con
     if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->stream, sl.d2h_done, 0));         // ... and its outputs have left
     rc = forward_group_device(e, n, w, ad, (const float *)sl.in[0].p, Yd, T, flags);
     if (rc != GT_OK) return rc;
+    // the first adapted member keeps the staged X on the device: a backward that promises the same X
+    // (GT_FLAG_REUSE_LOW) reads it from there instead of uploading it again
+    for (int j = 0; j < n; j++) {
+        if (ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0) {
+            GT_CUDA(ad[j]->xkeep.reserve(bx));
+            GT_CUDA(cudaMemcpyAsync(ad[j]->xkeep.p, sl.in[0].p, bx, cudaMemcpyDeviceToDevice, e->stream));
+            ad[j]->xkeep_T = T;
+            break;
+        }
+    }
     GT_CUDA(cudaEventRecord(sl.compute_done, e->stream));
     GT_CUDA(cudaStreamWaitEvent(e->s_d2h, sl.compute_done, 0));
     for (int j = 0; j < n; j++)
@@ -525,7 +538,14 @@ int backward_host(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *co
     const size_t bx = (size_t)T * w[0]->dev.K * sizeof(float);
     const bool assign = (flags & GT_FLAG_DX_ASSIGN) != 0;
     bool need_x = false;
-    for (int j = 0; j < n; j++) need_x = need_x || (ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0);
+    const float *x_kept = nullptr;
+    for (int j = 0; j < n; j++) {
+        if (ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0) {
+            if (!need_x && (flags & GT_FLAG_REUSE_LOW) && ad[j]->xkeep.p && ad[j]->xkeep_T == T) x_kept = (const float *)ad[j]->xkeep.p;
+            need_x = true;
+        }
+    }
+    if (x_kept) need_x = false;      // X of the forward is still on the device
     const float *dYd[kMaxGroup];
     for (int j = 0; j < n; j++) {
         GT_CUDA(sl.in[j].reserve((size_t)T * w[j]->dev.N * sizeof(float)));
@@ -545,7 +565,7 @@ int backward_host(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *co
     GT_CUDA(cudaEventRecord(sl.h2d_done, e->s_h2d));
     GT_CUDA(cudaStreamWaitEvent(e->stream, sl.h2d_done, 0));
     if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->stream, sl.d2h_done, 0));
-    rc = backward_group_device(e, n, w, ad, dYd, need_x ? (const float *)sl.in[kSlotIn - 1].p : nullptr,
+    rc = backward_group_device(e, n, w, ad, dYd, x_kept ? x_kept : (need_x ? (const float *)sl.in[kSlotIn - 1].p : nullptr),
                                dX ? (float *)sl.out[0].p : nullptr, T, flags);
     if (rc != GT_OK) return rc;
     GT_CUDA(cudaEventRecord(sl.compute_done, e->stream));
@@ -852,6 +872,7 @@ int gt_adapter_free(gt_adapter *a) {
     }
     if (a->b_nonzero) cudaFree(a->b_nonzero);
     a->low.release();
+    a->xkeep.release();
     delete a;
     return GT_OK;
 }

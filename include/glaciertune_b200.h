@@ -70,7 +70,9 @@ enum gt_flags {
     GT_FLAG_NO_LORA = 2,     /* skip the adapter terms even when an adapter is given */
     GT_FLAG_REUSE_LOW = 4,   /* backward: X is the tensor the last forward through this adapter saw, so X*A kept from
                                 that call is reused instead of recomputed (the reference recomputes it,
-                                src/Glacier.Tune/Kernels/LoraKernels.cs:147-186; the value is the same) */
+                                src/Glacier.Tune/Kernels/LoraKernels.cs:147-186; the value is the same).  With host
+                                buffers the device copy of X staged by that forward is reused as well (X is not
+                                uploaded a second time; the adapter holds T x in_features floats for it) */
     GT_FLAG_HOST_ASYNC = 16, /* host buffers only, page-locked: the call returns once its copies and kernels are queued
                                 (uploads, kernels and downloads of consecutive calls overlap on separate streams); the
                                 outputs are valid, and the inputs may be changed, after gt_sync().  Without the flag a

@@ -263,6 +263,17 @@ def test_host_async_calls_complete_at_sync(G, eng, oracle):
     for j in range(2):
         da, db = ads[j].grads()
         assert oracle.rel_fro(da, rounds * das[j]) < 5e-3 and oracle.rel_fro(db, rounds * dbs[j]) < 5e-3
+    # a backward without GT_FLAG_REUSE_LOW uploads X again: same gradients as the one that reuses the kept copy
+    for ad in ads:
+        ad.zero_grads()
+    hdx2 = torch.full((130, 512), 4.0).pin_memory()
+    eng.forward_group(ws, ads, hx.numpy(), [y.numpy() for y in hys[0]], flags=fl)
+    eng.backward_group(ws, ads, [d.numpy() for d in hdy], hx.numpy(), hdx2.numpy(), flags=fl | G.FLAG_DX_ASSIGN)
+    eng.sync()
+    assert oracle.rel_fro(hdx2.numpy(), hdx[0].numpy()) < 1e-3
+    for j in range(2):
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(da, das[j]) < 5e-3 and oracle.rel_fro(db, dbs[j]) < 5e-3
     # synchronous host calls give the same numbers as the queued ones
     y_sync = [np.empty((130, c["N"]), np.float32) for c in cs]
     eng.forward_group(ws, ads, cs[0]["x"], y_sync)
