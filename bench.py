@@ -483,6 +483,55 @@ def run_sweep(args) -> None:
                       "warm-up launches, 256 MiB written between launches"}), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------ layer glue
+def run_glue(args) -> None:
+    """HBM throughput of the layer-glue kernels at the 7B layer's shapes (M = 512): algorithmic bytes / device time,
+    against the measured copy bandwidth.  One JSON line {"glue": [...]}; a table goes to stderr."""
+    import torch
+    from glacier.tune_b200 import capi as G
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --glue: no CUDA device")
+    peaks = measured_peaks()
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    eng = G.Engine(0, G.MATH_BF16, stream=stream.cuda_stream)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    T, H, F, HQ, HK, D = M_TOKENS, 3584, 18944, 28, 4, 128
+    t = lambda *shape: torch.randn(shape, device="cuda")        # noqa: E731
+    gate, up, dh, hid, dg, du = t(T, F), t(T, F), t(T, F), t(T, F), t(T, F), t(T, F)
+    x, w, y, dy, dx = t(T, H), torch.ones(H, device="cuda"), t(T, H), t(T, H), t(T, H)
+    q, k = t(T, HQ * D), t(T, HK * D)
+    cases = [
+        ("swiglu_forward [512, 18944]", lambda: eng.swiglu_forward(gate, up, hid), 3 * 4 * T * F),
+        ("swiglu_backward [512, 18944]", lambda: eng.swiglu_backward(dh, gate, up, dg, du), 5 * 4 * T * F),
+        ("rmsnorm_forward [512, 3584]", lambda: eng.rmsnorm_forward(x, w, y), 2 * 4 * T * H),
+        ("rmsnorm_backward [512, 3584]", lambda: eng.rmsnorm_backward(dy, x, w, dx), 3 * 4 * T * H),
+        ("rope q 28 + k 4 heads x 128", lambda: eng.rope(q, k, T, HQ, HK, D, 1e6), 2 * 4 * T * (HQ + HK) * D),
+        ("add [512, 3584]", lambda: eng.add(x, y, dx), 3 * 4 * T * H),
+    ]
+    rows = []
+    for name, call, nbytes in cases:
+        for _ in range(3):
+            call()
+        ts = []
+        for _ in range(9):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            call()
+            b.record(stream)
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        us = float(np.median(ts))
+        gbs = nbytes / us / 1e3
+        rows.append({"kernel": name, "us": us, "bytes": nbytes, "gbs": gbs, "frac_hbm": gbs / peaks["hbm_gbs"]})
+        print(f"{name:32s} {us:7.1f} us  {nbytes / 1e6:7.1f} MB  {gbs:7.1f} GB/s ({100 * gbs / peaks['hbm_gbs']:5.1f} % of {peaks['hbm_gbs']:.0f})",
+              file=sys.stderr, flush=True)
+    eng.close()
+    print(json.dumps({"glue": rows, "peaks": peaks, "timing": "CUDA events around one call, median of 9 after 3 warm-up calls, 256 MiB "
+                      "written between calls"}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -494,10 +543,14 @@ def main() -> None:
     ap.add_argument("--zero-dx", action="store_true", help="zero-fill dX before each backward and accumulate into it")
     ap.add_argument("--no-group", action="store_true", help="one call per projection instead of q,k,v and gate,up groups")
     ap.add_argument("--sweep", action="store_true", help="token-count sweep of the Q4_K_M projection set instead of the step benchmark")
+    ap.add_argument("--glue", action="store_true", help="HBM throughput of the layer-glue kernels instead of the step benchmark")
     ap.add_argument("--sweep-m", type=int, nargs="+", default=[1, 16, 128, 512, 2048])
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+        return
+    if args.glue:
+        run_glue(args)
         return
     if args.impl == "reference":
         run_reference(args)

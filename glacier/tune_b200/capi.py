@@ -22,7 +22,8 @@ EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
-    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens",
+    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
+    "gt_rmsnorm_backward", "gt_add",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
 ]
@@ -79,6 +80,13 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_proj_forward_group.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
     lib.gt_proj_backward_group.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_int32]
+    lib.gt_swiglu_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
+    lib.gt_swiglu_backward.argtypes = [C.c_void_p] * 6 + [C.c_int64]
+    lib.gt_add.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
+    lib.gt_rope.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float,
+                            C.c_int32, C.c_int32]
+    lib.gt_rmsnorm_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
+    lib.gt_rmsnorm_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
@@ -218,6 +226,33 @@ class Engine:
         _check(self.lib.gt_proj_backward_group(self.h, n, self._ptr_array(weights), ads, self._ptr_array(dYs), _ptr(X, np.float32)[0],
                                                _ptr(dX, np.float32)[0], dYs[0].shape[0], flags))
         return dX
+
+    # ---- layer glue (device tensors, asynchronous on the engine stream)
+    def swiglu_forward(self, gate, up, hidden):
+        _check(self.lib.gt_swiglu_forward(self.h, _ptr(gate)[0], _ptr(up)[0], _ptr(hidden)[0], gate.numel()))
+        return hidden
+
+    def swiglu_backward(self, d_hidden, gate, up, d_gate, d_up):
+        _check(self.lib.gt_swiglu_backward(self.h, _ptr(d_hidden)[0], _ptr(gate)[0], _ptr(up)[0], _ptr(d_gate)[0], _ptr(d_up)[0],
+                                           gate.numel()))
+        return d_gate, d_up
+
+    def add(self, a, b, out):
+        _check(self.lib.gt_add(self.h, _ptr(a)[0], _ptr(b)[0], _ptr(out)[0], a.numel()))
+        return out
+
+    def rope(self, q, k, T: int, heads_q: int, heads_kv: int, head_dim: int, freq_base: float = 1e6, freq_scale: float = 1.0,
+             rope_dim: int = -1, inverse: bool = False):
+        _check(self.lib.gt_rope(self.h, _ptr(q)[0], _ptr(k)[0], T, heads_q, heads_kv, head_dim, freq_base, freq_scale, rope_dim,
+                                1 if inverse else 0))
+
+    def rmsnorm_forward(self, x, w, y, eps: float = 1e-6):
+        _check(self.lib.gt_rmsnorm_forward(self.h, _ptr(x)[0], _ptr(w)[0], _ptr(y)[0], x.shape[0], x.shape[1], eps))
+        return y
+
+    def rmsnorm_backward(self, dy, x, w, dx, eps: float = 1e-6):
+        _check(self.lib.gt_rmsnorm_backward(self.h, _ptr(dy)[0], _ptr(x)[0], _ptr(w)[0], _ptr(dx)[0], x.shape[0], x.shape[1], eps))
+        return dx
 
     def launch_gemm_batch(self, w: "Weight", Y, X, batch: int, residual=None):
         yp, _ = _ptr(Y)

@@ -1,0 +1,300 @@
+// Layer glue between the projections, on device tensors (asynchronous on the engine stream): SwiGLU, RoPE, RMSNorm and
+// the residual add.  All of it is one pass over fp32 activations and bound by HBM bandwidth; the reference runs these
+// loops on the host between its GPU calls:
+//   SwiGLU   src/Glacier.Tune/Kernels/SwiGluKernel.cs:13-60
+//   RoPE     src/Glacier.Tune/Kernels/RoPEKernel.cs:12-126 (pairs (i, i + half), freq = base^(-2i/d), inverse = -sin)
+//   RMSNorm  ElementwiseKernels.RMSNorm / RMSNormBackward of Glacier.Tensor 1.1.0 (not in the repository; call sites
+//            src/Glacier.Tune/Model/TransformerBlock.cs:318,524,672,827, frozen weight: dW is never asked for)
+//   add      TensorOps.Add (residual connections, src/Glacier.Tune/Model/TransformerBlock.cs:675)
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <mutex>
+
+#include "../../../include/glaciertune_b200.h"
+#include "gt_internal.h"
+#include "gt_ptx.cuh"
+
+namespace {
+
+using gt::pdl_trigger;
+using gt::pdl_wait;
+
+__device__ __forceinline__ float sigmoidf_(float g) { return 1.0f / (1.0f + expf(-g)); }
+
+// vectorized when every pointer is 16-byte aligned; n4 = number of float4, tail handled by the scalar loop
+__global__ void __launch_bounds__(256) k_swiglu_fwd(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ hidden,
+                                                    int64_t n, int vec) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec) {
+        const int64_t n4 = n >> 2;
+        for (int64_t i = tid; i < n4; i += nth) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(gate) + i), u = __ldg(reinterpret_cast<const float4 *>(up) + i);
+            float4 h;
+            h.x = g.x * sigmoidf_(g.x) * u.x;
+            h.y = g.y * sigmoidf_(g.y) * u.y;
+            h.z = g.z * sigmoidf_(g.z) * u.z;
+            h.w = g.w * sigmoidf_(g.w) * u.w;
+            reinterpret_cast<float4 *>(hidden)[i] = h;
+        }
+        done = n4 << 2;
+    }
+    for (int64_t i = done + tid; i < n; i += nth) {
+        const float g = gate[i];
+        hidden[i] = g * sigmoidf_(g) * up[i];
+    }
+}
+
+__device__ __forceinline__ void swiglu_bwd1(float d, float g, float u, float &dg, float &du) {
+    const float sig = sigmoidf_(g);
+    du = d * (g * sig);
+    dg = d * u * (sig * (1.0f + g * (1.0f - sig)));
+}
+__global__ void __launch_bounds__(256) k_swiglu_bwd(const float *__restrict__ dh, const float *__restrict__ gate, const float *__restrict__ up,
+                                                    float *__restrict__ dgate, float *__restrict__ dup, int64_t n, int vec) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec) {
+        const int64_t n4 = n >> 2;
+        for (int64_t i = tid; i < n4; i += nth) {
+            const float4 d = __ldg(reinterpret_cast<const float4 *>(dh) + i), g = __ldg(reinterpret_cast<const float4 *>(gate) + i),
+                         u = __ldg(reinterpret_cast<const float4 *>(up) + i);
+            float4 a, b;
+            swiglu_bwd1(d.x, g.x, u.x, a.x, b.x);
+            swiglu_bwd1(d.y, g.y, u.y, a.y, b.y);
+            swiglu_bwd1(d.z, g.z, u.z, a.z, b.z);
+            swiglu_bwd1(d.w, g.w, u.w, a.w, b.w);
+            reinterpret_cast<float4 *>(dgate)[i] = a;
+            reinterpret_cast<float4 *>(dup)[i] = b;
+        }
+        done = n4 << 2;
+    }
+    for (int64_t i = done + tid; i < n; i += nth) swiglu_bwd1(dh[i], gate[i], up[i], dgate[i], dup[i]);
+}
+
+__global__ void __launch_bounds__(256) k_add(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int64_t n, int vec) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec) {
+        const int64_t n4 = n >> 2;
+        for (int64_t i = tid; i < n4; i += nth) {
+            const float4 x = __ldg(reinterpret_cast<const float4 *>(a) + i), y = __ldg(reinterpret_cast<const float4 *>(b) + i);
+            reinterpret_cast<float4 *>(out)[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+        }
+        done = n4 << 2;
+    }
+    for (int64_t i = done + tid; i < n; i += nth) out[i] = a[i] + b[i];
+}
+
+// One thread per (position, pair index i): cos / sin once, then every head of q and k at that position.  Consecutive
+// threads hold consecutive i, so each head's accesses are coalesced.  freq and theta follow the reference's fp32 order.
+__global__ void __launch_bounds__(256) k_rope(float *__restrict__ q, float *__restrict__ k, int T, int heads_q, int heads_kv, int head_dim,
+                                              float freq_base, float freq_scale, int eff, float sign) {
+    pdl_wait();
+    pdl_trigger();
+    const int half = eff >> 1;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)T * half) return;
+    const int pos = (int)(idx / half), i = (int)(idx % half);
+    const float base_freq = 1.0f / powf(freq_base, (float)(2 * i) / (float)eff);
+    const float theta = (float)pos * base_freq * freq_scale;
+    float s, c;
+    sincosf(theta, &s, &c);
+    s *= sign;
+    if (q) {
+        float *p = q + (int64_t)pos * heads_q * head_dim + i;
+        for (int h = 0; h < heads_q; h++, p += head_dim) {
+            const float v0 = p[0], v1 = p[half];
+            p[0] = v0 * c - v1 * s;
+            p[half] = v0 * s + v1 * c;
+        }
+    }
+    if (k) {
+        float *p = k + (int64_t)pos * heads_kv * head_dim + i;
+        for (int h = 0; h < heads_kv; h++, p += head_dim) {
+            const float v0 = p[0], v1 = p[half];
+            p[0] = v0 * c - v1 * s;
+            p[half] = v0 * s + v1 * c;
+        }
+    }
+}
+
+// block-wide sum of up to two values (256 threads)
+__device__ __forceinline__ void block_sum2(float &a, float &b) {
+    __shared__ float sa[8], sb[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();      // the arrays may still be read from an earlier call
+    if (lane == 0) {
+        sa[warp] = a;
+        sb[warp] = b;
+    }
+    __syncthreads();
+    a = 0.f;
+    b = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        a += sa[w];
+        b += sb[w];
+    }
+}
+
+// One block per token row; the row (H <= 16 * 256 floats kept in registers, longer rows re-read) is read once.
+constexpr int kRowRegs = 16;
+__global__ void __launch_bounds__(256) k_rmsnorm_fwd(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ y, int H,
+                                                     float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const float *xr = x + (int64_t)blockIdx.x * H;
+    float *yr = y + (int64_t)blockIdx.x * H;
+    float v[kRowRegs];
+    float ss = 0.f, unused = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowRegs; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < H ? xr[i] : 0.f;
+        ss += v[j] * v[j];
+    }
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) ss += xr[i] * xr[i];
+    block_sum2(ss, unused);
+    const float r = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < kRowRegs; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < H) yr[i] = v[j] * r * w[i];
+    }
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) yr[i] = xr[i] * r * w[i];
+}
+
+// dx = r * g - x * r^3 * mean(g * x), g = dy * w (frozen weight)
+__global__ void __launch_bounds__(256) k_rmsnorm_bwd(const float *__restrict__ dy, const float *__restrict__ x, const float *__restrict__ w,
+                                                     float *__restrict__ dx, int H, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const float *xr = x + (int64_t)blockIdx.x * H, *gr = dy + (int64_t)blockIdx.x * H;
+    float *dr = dx + (int64_t)blockIdx.x * H;
+    float xv[kRowRegs], gv[kRowRegs];
+    float ss = 0.f, gx = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowRegs; j++) {
+        const int i = threadIdx.x + j * 256;
+        xv[j] = i < H ? xr[i] : 0.f;
+        gv[j] = i < H ? gr[i] * w[i] : 0.f;
+        ss += xv[j] * xv[j];
+        gx += gv[j] * xv[j];
+    }
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) {
+        ss += xr[i] * xr[i];
+        gx += gr[i] * w[i] * xr[i];
+    }
+    block_sum2(ss, gx);
+    const float r = rsqrtf(ss / (float)H + eps);
+    const float coef = r * r * r * gx / (float)H;
+#pragma unroll
+    for (int j = 0; j < kRowRegs; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < H) dr[i] = r * gv[j] - xv[j] * coef;
+    }
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) dr[i] = r * gr[i] * w[i] - xr[i] * coef;
+}
+
+int aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+unsigned stream_blocks(int64_t n, int sm_count) {
+    const int64_t want = (n / 4 + 255) / 256;
+    const int64_t cap = (int64_t)sm_count * 8;
+    return (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+int cuda_fail(const char *what, cudaError_t e) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "%s: %s", what, cudaGetErrorString(e));
+    return gt::set_last_error(GT_ERR_CUDA, msg);
+}
+
+}  // namespace
+
+extern "C" int gt_swiglu_forward(gt_engine *eng, const float *gate, const float *up, float *hidden, int64_t n) {
+    if (!eng || !gate || !up || !hidden) return gt::set_last_error(GT_ERR_INVALID, "gt_swiglu_forward: null argument");
+    if (n <= 0) return GT_OK;
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    if (ce == cudaSuccess)
+        ce = gt::launch_k(k_swiglu_fwd, dim3(stream_blocks(n, ev.sm_count)), dim3(256), (size_t)0, ev.stream, gate, up, hidden, n,
+                          aligned16(gate) && aligned16(up) && aligned16(hidden) ? 1 : 0);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_swiglu_forward", ce);
+}
+
+extern "C" int gt_swiglu_backward(gt_engine *eng, const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up,
+                                  int64_t n) {
+    if (!eng || !d_hidden || !gate || !up || !d_gate || !d_up) return gt::set_last_error(GT_ERR_INVALID, "gt_swiglu_backward: null argument");
+    if (n <= 0) return GT_OK;
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    const int vec = aligned16(d_hidden) && aligned16(gate) && aligned16(up) && aligned16(d_gate) && aligned16(d_up) ? 1 : 0;
+    if (ce == cudaSuccess)
+        ce = gt::launch_k(k_swiglu_bwd, dim3(stream_blocks(n, ev.sm_count)), dim3(256), (size_t)0, ev.stream, d_hidden, gate, up, d_gate,
+                          d_up, n, vec);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_swiglu_backward", ce);
+}
+
+extern "C" int gt_add(gt_engine *eng, const float *a, const float *b, float *out, int64_t n) {
+    if (!eng || !a || !b || !out) return gt::set_last_error(GT_ERR_INVALID, "gt_add: null argument");
+    if (n <= 0) return GT_OK;
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    if (ce == cudaSuccess)
+        ce = gt::launch_k(k_add, dim3(stream_blocks(n, ev.sm_count)), dim3(256), (size_t)0, ev.stream, a, b, out, n,
+                          aligned16(a) && aligned16(b) && aligned16(out) ? 1 : 0);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_add", ce);
+}
+
+extern "C" int gt_rope(gt_engine *eng, float *q, float *k, int32_t T, int32_t heads_q, int32_t heads_kv, int32_t head_dim, float freq_base,
+                       float freq_scale, int32_t rope_dim, int32_t inverse) {
+    if (!eng || (!q && !k)) return gt::set_last_error(GT_ERR_INVALID, "gt_rope: null argument");
+    if (T <= 0) return GT_OK;
+    if (head_dim <= 0 || (q && heads_q <= 0) || (k && heads_kv <= 0) || freq_base <= 0.f)
+        return gt::set_last_error(GT_ERR_INVALID, "gt_rope: head counts, head_dim and freq_base must be positive");
+    const int eff = (rope_dim > 0 && rope_dim <= head_dim) ? rope_dim : head_dim;      // RoPEKernel.cs:55
+    if (eff / 2 <= 0) return GT_OK;
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    const int64_t items = (int64_t)T * (eff / 2);
+    if (ce == cudaSuccess)
+        ce = gt::launch_k(k_rope, dim3((unsigned)((items + 255) / 256)), dim3(256), (size_t)0, ev.stream, q, k, (int)T, (int)heads_q,
+                          (int)heads_kv, (int)head_dim, freq_base, freq_scale, eff, inverse ? -1.0f : 1.0f);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_rope", ce);
+}
+
+extern "C" int gt_rmsnorm_forward(gt_engine *eng, const float *x, const float *w, float *y, int32_t T, int32_t H, float eps) {
+    if (!eng || !x || !w || !y) return gt::set_last_error(GT_ERR_INVALID, "gt_rmsnorm_forward: null argument");
+    if (T <= 0 || H <= 0) return gt::set_last_error(GT_ERR_INVALID, "gt_rmsnorm_forward: T and H must be positive");
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    if (ce == cudaSuccess) ce = gt::launch_k(k_rmsnorm_fwd, dim3((unsigned)T), dim3(256), (size_t)0, ev.stream, x, w, y, (int)H, eps);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_rmsnorm_forward", ce);
+}
+
+extern "C" int gt_rmsnorm_backward(gt_engine *eng, const float *dy, const float *x, const float *w, float *dx, int32_t T, int32_t H, float eps) {
+    if (!eng || !dy || !x || !w || !dx) return gt::set_last_error(GT_ERR_INVALID, "gt_rmsnorm_backward: null argument");
+    if (T <= 0 || H <= 0) return gt::set_last_error(GT_ERR_INVALID, "gt_rmsnorm_backward: T and H must be positive");
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    if (ce == cudaSuccess) ce = gt::launch_k(k_rmsnorm_bwd, dim3((unsigned)T), dim3(256), (size_t)0, ev.stream, dy, x, w, dx, (int)H, eps);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_rmsnorm_backward", ce);
+}

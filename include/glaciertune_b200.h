@@ -173,6 +173,26 @@ GT_API int gt_proj_forward_group(gt_engine *eng, int32_t n, const gt_weight *con
 GT_API int gt_proj_backward_group(gt_engine *eng, int32_t n, const gt_weight *const *weights, gt_adapter *const *adapters_or_null,
                                   const float *const *dY, const float *X, float *dX_accum_or_null, int32_t T, int32_t flags);
 
+/* ---- layer glue on device tensors (asynchronous on the engine stream): what sits between the projections ---- */
+/* Replaces: SwiGluKernel.Forward (src/Glacier.Tune/Kernels/SwiGluKernel.cs:13-31): hidden = SiLU(gate) * up, n elements. */
+GT_API int gt_swiglu_forward(gt_engine *eng, const float *gate, const float *up, float *hidden, int64_t n);
+/* Replaces: SwiGluKernel.Backward (SwiGluKernel.cs:33-60): dUp = dH * SiLU(g), dGate = dH * u * sig * (1 + g (1 - sig));
+ * both outputs are assigned. */
+GT_API int gt_swiglu_backward(gt_engine *eng, const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up,
+                              int64_t n);
+/* Replaces: RoPEKernel.ForwardSequence / BackwardSequence (src/Glacier.Tune/Kernels/RoPEKernel.cs:12-126) without the
+ * ropeFreqs table: q [T, heads_q * head_dim] and k [T, heads_kv * head_dim] rotated in place (either may be NULL),
+ * pairs (i, i + rope_dim/2), rope_dim <= 0 means head_dim; inverse != 0 is the backward rotation. */
+GT_API int gt_rope(gt_engine *eng, float *q_or_null, float *k_or_null, int32_t T, int32_t heads_q, int32_t heads_kv, int32_t head_dim,
+                   float freq_base, float freq_scale, int32_t rope_dim, int32_t inverse);
+/* Replaces: ElementwiseKernels.RMSNorm / RMSNormBackward of Glacier.Tensor as called at
+ * src/Glacier.Tune/Model/TransformerBlock.cs:318,524,672,827 (frozen weight, dW never computed):
+ * y = x * rsqrt(mean(x^2) + eps) * w;  dx = r * (dy * w) - x * r^3 * mean(dy * w * x). */
+GT_API int gt_rmsnorm_forward(gt_engine *eng, const float *x, const float *w, float *y, int32_t T, int32_t H, float eps);
+GT_API int gt_rmsnorm_backward(gt_engine *eng, const float *dy, const float *x, const float *w, float *dx, int32_t T, int32_t H, float eps);
+/* Replaces: TensorOps.Add for the residual connections (TransformerBlock.cs:675): out = a + b (out may alias a or b). */
+GT_API int gt_add(gt_engine *eng, const float *a, const float *b, float *out, int64_t n);
+
 /* Replaces: GpuLoraEngine.LaunchGemmBatch(type, dY, dX, dW, kCols, mRows, batch, dBias, dResidual)
  * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:83-129): device pointers, asynchronous.
  * Y (may be NULL) = X*W^T + bias; residual (may be NULL) += X*W^T + bias, as the reference kernels do

@@ -601,3 +601,99 @@ double gt_oracle_clip_gradients(float *g, int64_t n, double max_norm) {
     }
     return norm;
 }
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Layer glue between the projections (the callers on either side of the path).
+ * --------------------------------------------------------------------------------------------------------- */
+
+/* SwiGLU forward: hidden = SiLU(gate) * up, element by element in fp32.
+ * src/Glacier.Tune/Kernels/SwiGluKernel.cs:13-31. */
+void gt_oracle_swiglu_forward(const float *gate, const float *up, float *hidden, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        const float g = gate[i], u = up[i];
+        const float sig = 1.0f / (1.0f + expf(-g));
+        const float silu = g * sig;
+        hidden[i] = silu * u;
+    }
+}
+
+/* SwiGLU backward: dUp = dH * SiLU(g); dGate = dH * u * sig * (1 + g * (1 - sig)).
+ * src/Glacier.Tune/Kernels/SwiGluKernel.cs:33-60 (both outputs are assigned, not accumulated). */
+void gt_oracle_swiglu_backward(const float *dh, const float *gate, const float *up, float *dgate, float *dup, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        const float d = dh[i], g = gate[i], u = up[i];
+        const float sig = 1.0f / (1.0f + expf(-g));
+        const float silu = g * sig;
+        dup[i] = d * silu;
+        const float dsilu = sig * (1.0f + g * (1.0f - sig));
+        dgate[i] = d * u * dsilu;
+    }
+}
+
+/* RoPE over a sequence, in place: for position pos and pair (i, i + half) of every head,
+ *   freq = 1 / pow(base, 2i / ropeDim) (fp32), theta = pos * freq * scale (fp32),
+ *   (v0, v1) -> (v0 cos - v1 s, v0 s + v1 cos), s = sin(theta), negated for the inverse (backward) rotation.
+ * src/Glacier.Tune/Kernels/RoPEKernel.cs:12-42 (sequence loops) and 44-126 (one position); ropeFreqs == null. */
+void gt_oracle_rope(float *q, float *k, int T, int heads_q, int heads_kv, int head_dim, float freq_base, float freq_scale,
+                    int rope_dim, int inverse) {
+    const int eff = (rope_dim > 0 && rope_dim <= head_dim) ? rope_dim : head_dim;
+    const int half = eff / 2;
+    if (half <= 0) return;
+    const float sign = inverse ? -1.0f : 1.0f;
+#pragma omp parallel for schedule(static)
+    for (int pos = 0; pos < T; pos++) {
+        float *pq = q ? q + (int64_t)pos * heads_q * head_dim : NULL;
+        float *pk = k ? k + (int64_t)pos * heads_kv * head_dim : NULL;
+        for (int i = 0; i < half; i++) {
+            const float base_freq = 1.0f / powf(freq_base, (float)(2 * i) / (float)eff);
+            const float theta = (float)pos * base_freq * freq_scale;
+            const float c = cosf(theta), s = sinf(theta) * sign;
+            for (int h = 0; pq && h < heads_q; h++) {
+                float *hd = pq + h * head_dim;
+                const float v0 = hd[i], v1 = hd[i + half];
+                hd[i] = v0 * c - v1 * s;
+                hd[i + half] = v0 * s + v1 * c;
+            }
+            for (int h = 0; pk && h < heads_kv; h++) {
+                float *hd = pk + h * head_dim;
+                const float v0 = hd[i], v1 = hd[i + half];
+                hd[i] = v0 * c - v1 * s;
+                hd[i + half] = v0 * s + v1 * c;
+            }
+        }
+    }
+}
+
+/* RMSNorm forward: y[t, :] = x[t, :] * rsqrt(mean(x[t, :]^2) + eps) * w.  The implementation the reference calls
+ * (ElementwiseKernels.RMSNorm, Glacier.Tensor 1.1.0, call sites src/Glacier.Tune/Model/TransformerBlock.cs:318,524) is not
+ * in the repository: this is the textbook definition, PARITY UNPINNED.  The mean is accumulated in fp64 here so that
+ * the oracle is the more accurate side. */
+void gt_oracle_rmsnorm_forward(const float *x, const float *w, float *y, int T, int H, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; t++) {
+        const float *xr = x + (int64_t)t * H;
+        double ss = 0.0;
+        for (int i = 0; i < H; i++) ss += (double)xr[i] * (double)xr[i];
+        const float r = (float)(1.0 / sqrt(ss / H + (double)eps));
+        for (int i = 0; i < H; i++) y[(int64_t)t * H + i] = xr[i] * r * w[i];
+    }
+}
+
+/* RMSNorm backward with frozen weight (the reference passes dW = null, TransformerBlock.cs:672,827):
+ *   g = dy * w;  dx = r * g - x * r^3 * mean(g * x),  r = rsqrt(mean(x^2) + eps).  PARITY UNPINNED (as above). */
+void gt_oracle_rmsnorm_backward(const float *dy, const float *x, const float *w, float *dx, int T, int H, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < T; t++) {
+        const float *xr = x + (int64_t)t * H, *gr = dy + (int64_t)t * H;
+        double ss = 0.0, gx = 0.0;
+        for (int i = 0; i < H; i++) {
+            ss += (double)xr[i] * (double)xr[i];
+            gx += (double)gr[i] * (double)w[i] * (double)xr[i];
+        }
+        const double r = 1.0 / sqrt(ss / H + (double)eps);
+        const double coef = r * r * r * gx / H;
+        for (int i = 0; i < H; i++) dx[(int64_t)t * H + i] = (float)(r * (double)gr[i] * (double)w[i] - (double)xr[i] * coef);
+    }
+}

@@ -231,3 +231,41 @@ def rel_fro(got, want) -> float:
     w = np.asarray(want, np.float64)
     den = np.linalg.norm(w)
     return float(np.linalg.norm(g - w) / (den if den > 0 else 1.0))
+
+
+# ---- layer glue (SwiGLU, RoPE, RMSNorm): see the C file for the reference lines each one restates
+def swiglu_forward(gate, up) -> np.ndarray:
+    gate, up = _f32(gate), _f32(up)
+    out = np.empty_like(gate)
+    lib().gt_oracle_swiglu_forward(_p(gate), _p(up), _p(out), C.c_int64(gate.size))
+    return out
+
+
+def swiglu_backward(dh, gate, up):
+    dh, gate, up = _f32(dh), _f32(gate), _f32(up)
+    dg, du = np.empty_like(gate), np.empty_like(gate)
+    lib().gt_oracle_swiglu_backward(_p(dh), _p(gate), _p(up), _p(dg), _p(du), C.c_int64(gate.size))
+    return dg, du
+
+
+def rope(q, k, T, heads_q, heads_kv, head_dim, freq_base=1e6, freq_scale=1.0, rope_dim=-1, inverse=False):
+    """Returns rotated copies of q [T, heads_q*head_dim] and k [T, heads_kv*head_dim] (either may be None)."""
+    q = None if q is None else _f32(q).copy()
+    k = None if k is None else _f32(k).copy()
+    lib().gt_oracle_rope(_p(q) if q is not None else None, _p(k) if k is not None else None, T, heads_q, heads_kv, head_dim,
+                         C.c_float(freq_base), C.c_float(freq_scale), rope_dim, 1 if inverse else 0)
+    return q, k
+
+
+def rmsnorm_forward(x, w, eps=1e-6) -> np.ndarray:
+    x, w = _f32(x), _f32(w)
+    y = np.empty_like(x)
+    lib().gt_oracle_rmsnorm_forward(_p(x), _p(w), _p(y), x.shape[0], x.shape[1], C.c_float(eps))
+    return y
+
+
+def rmsnorm_backward(dy, x, w, eps=1e-6) -> np.ndarray:
+    dy, x, w = _f32(dy), _f32(x), _f32(w)
+    dx = np.empty_like(x)
+    lib().gt_oracle_rmsnorm_backward(_p(dy), _p(x), _p(w), _p(dx), x.shape[0], x.shape[1], C.c_float(eps))
+    return dx
