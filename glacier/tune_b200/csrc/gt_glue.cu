@@ -93,37 +93,30 @@ __global__ void __launch_bounds__(256) k_add(const float *__restrict__ a, const 
     for (int64_t i = done + tid; i < n; i += nth) out[i] = a[i] + b[i];
 }
 
-// One thread per (position, pair index i): cos / sin once, then every head of q and k at that position.  Consecutive
-// threads hold consecutive i, so each head's accesses are coalesced.  freq and theta follow the reference's fp32 order.
+// One thread per (position, head, pair index i): consecutive threads hold consecutive i, so accesses are coalesced, and
+// there are enough threads in flight to cover the memory latency (cos / sin are recomputed per head, which is cheap
+// next to the two loads and two stores).  freq and theta follow the reference's fp32 order.
 __global__ void __launch_bounds__(256) k_rope(float *__restrict__ q, float *__restrict__ k, int T, int heads_q, int heads_kv, int head_dim,
                                               float freq_base, float freq_scale, int eff, float sign) {
     pdl_wait();
     pdl_trigger();
     const int half = eff >> 1;
+    const int heads = (q ? heads_q : 0) + (k ? heads_kv : 0);
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (int64_t)T * half) return;
-    const int pos = (int)(idx / half), i = (int)(idx % half);
+    if (idx >= (int64_t)T * heads * half) return;
+    const int i = (int)(idx % half);
+    const int h = (int)((idx / half) % heads);
+    const int pos = (int)(idx / ((int64_t)half * heads));
     const float base_freq = 1.0f / powf(freq_base, (float)(2 * i) / (float)eff);
     const float theta = (float)pos * base_freq * freq_scale;
     float s, c;
     sincosf(theta, &s, &c);
     s *= sign;
-    if (q) {
-        float *p = q + (int64_t)pos * heads_q * head_dim + i;
-        for (int h = 0; h < heads_q; h++, p += head_dim) {
-            const float v0 = p[0], v1 = p[half];
-            p[0] = v0 * c - v1 * s;
-            p[half] = v0 * s + v1 * c;
-        }
-    }
-    if (k) {
-        float *p = k + (int64_t)pos * heads_kv * head_dim + i;
-        for (int h = 0; h < heads_kv; h++, p += head_dim) {
-            const float v0 = p[0], v1 = p[half];
-            p[0] = v0 * c - v1 * s;
-            p[half] = v0 * s + v1 * c;
-        }
-    }
+    const int hq = q ? heads_q : 0;
+    float *p = h < hq ? q + ((int64_t)pos * heads_q + h) * head_dim + i : k + ((int64_t)pos * heads_kv + (h - hq)) * head_dim + i;
+    const float v0 = p[0], v1 = p[half];
+    p[0] = v0 * c - v1 * s;
+    p[half] = v0 * s + v1 * c;
 }
 
 // block-wide sum of up to two values (256 threads)
@@ -272,7 +265,7 @@ extern "C" int gt_rope(gt_engine *eng, float *q, float *k, int32_t T, int32_t he
     const gt::EngineView ev = gt::engine_view(eng);
     std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
     cudaError_t ce = cudaSetDevice(ev.device);
-    const int64_t items = (int64_t)T * (eff / 2);
+    const int64_t items = (int64_t)T * (eff / 2) * ((q ? heads_q : 0) + (k ? heads_kv : 0));
     if (ce == cudaSuccess)
         ce = gt::launch_k(k_rope, dim3((unsigned)((items + 255) / 256)), dim3(256), (size_t)0, ev.stream, q, k, (int)T, (int)heads_q,
                           (int)heads_kv, (int)head_dim, freq_base, freq_scale, eff, inverse ? -1.0f : 1.0f);
