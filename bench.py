@@ -213,12 +213,13 @@ def run_ours(args) -> None:
         w = eng.upload_weight(synth.TYPE_Q4_K, c["w"], N, K)
         ad = eng.create_adapter(K, N, RANK, ALPHA)
         ad.upload(c["a"], c["b"])
+        g0 = off
         dA = flat_grads[off: off + K * RANK]; off += K * RANK
         dB = flat_grads[off: off + RANK * N]; off += RANK * N
         ad.bind_grads(dA, dB)
         pin = lambda a: torch.from_numpy(a).pin_memory()   # noqa: E731
         hx, hdy = pin(c["x"]), pin(c["dy"])
-        layer.append(dict(name=n, N=N, K=K, w=w, ad=ad, hx=hx, hdy=hdy,
+        layer.append(dict(name=n, N=N, K=K, w=w, ad=ad, hx=hx, hdy=hdy, g0=g0, g1=off,
                           hy=torch.empty((M_TOKENS, N), dtype=torch.float32).pin_memory(),
                           hdx=torch.zeros((M_TOKENS, K), dtype=torch.float32).pin_memory(),
                           X=hx.to(dev), dY=hdy.to(dev), Y=torch.empty((M_TOKENS, N), dtype=torch.float32, device=dev),
@@ -239,7 +240,8 @@ def run_ours(args) -> None:
     for names in groups:
         ps = [by_name[n] for n in names]
         calls.append(dict(ws=[p["w"] for p in ps], ads=[p["ad"] for p in ps], X=ps[0]["X"], Ys=[p["Y"] for p in ps],
-                          dYs=[p["dY"] for p in ps], dX=ps[0]["dX"]))
+                          dYs=[p["dY"] for p in ps], dX=ps[0]["dX"],
+                          grads=flat_grads[ps[0]["g0"]: ps[-1]["g1"]]))      # the group's slice of the flat gradient buffer
 
     def step_resident():
         flat_grads.zero_()
@@ -259,7 +261,12 @@ def run_ours(args) -> None:
                 eng.backward_group(c["ws"], c["ads"], c["dYs"], c["X"], c["dX"], flags=bflags)
             else:
                 eng.backward(c["ws"][0], c["ads"][0], c["dYs"][0], c["X"], c["dX"], flags=bflags)
-        if world > 1:
+            # the group's gradients are final: their all-reduce runs beside the backward of the groups that follow
+            if world > 1 and not (not args.overlap):
+                eng.dp_allreduce_begin(c["grads"], 1.0 / world)
+        if world > 1 and not (not args.overlap):
+            eng.dp_allreduce_end()
+        if world > 1 and (not args.overlap):
             eng.dp_allreduce(flat_grads, 1.0 / world)
 
     # end to end: the same grouped calls on page-locked HOST buffers.  Every call stages its inputs to the device and its
@@ -541,6 +548,9 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
     ap.add_argument("--e2e-sync", action="store_true", help="end-to-end leg with synchronous host-buffer calls")
     ap.add_argument("--zero-dx", action="store_true", help="zero-fill dX before each backward and accumulate into it")
+    ap.add_argument("--overlap", action="store_true", help="one all-reduce per projection group beside the rest of the backward "
+                    "(gt_dp_allreduce_begin/_end) instead of one after it; measured slower on a single layer (four small "
+                    "collectives, and their CTAs cannot share an SM with a GEMM CTA)")
     ap.add_argument("--no-group", action="store_true", help="one call per projection instead of q,k,v and gate,up groups")
     ap.add_argument("--sweep", action="store_true", help="token-count sweep of the Q4_K_M projection set instead of the step benchmark")
     ap.add_argument("--glue", action="store_true", help="HBM throughput of the layer-glue kernels instead of the step benchmark")

@@ -25,7 +25,7 @@ EXPORTS = [
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
     "gt_rmsnorm_backward", "gt_add",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
-    "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_finalize", "gt_dp_unique_id",
+    "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
 
@@ -100,6 +100,8 @@ def load_library(path: str | None = None) -> C.CDLL:
         lib.gt_dp_unique_id.argtypes = [C.c_void_p, C.c_int32]
         lib.gt_dp_init.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32]
         lib.gt_dp_allreduce.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float]
+        lib.gt_dp_allreduce_begin.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float]
+        lib.gt_dp_allreduce_end.argtypes = [C.c_void_p]
         lib.gt_dp_finalize.argtypes = [C.c_void_p]
     if path is None:
         _lib = lib
@@ -304,6 +306,13 @@ class Engine:
 
     def dp_allreduce(self, g_dev, scale: float = 1.0):
         _check(self.lib.gt_dp_allreduce(self.h, _ptr(g_dev)[0], g_dev.numel(), scale))
+
+    def dp_allreduce_begin(self, g_dev, scale: float = 1.0):
+        """All-reduce of one slice on the side stream, beside the engine-stream work queued after this call."""
+        _check(self.lib.gt_dp_allreduce_begin(self.h, _ptr(g_dev)[0], g_dev.numel(), scale))
+
+    def dp_allreduce_end(self):
+        _check(self.lib.gt_dp_allreduce_end(self.h))
 
     def dp_finalize(self):
         _check(self.lib.gt_dp_finalize(self.h))

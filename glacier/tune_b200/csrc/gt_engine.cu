@@ -92,6 +92,10 @@ struct gt_engine {
     HostSlot slots[kHostSlots];
     int slot_next = 0;
     cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
+    // overlapped gradient exchange: collectives queued on a side stream between a fork and a join of the engine stream
+    cudaStream_t s_comm = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool comm_pending = false;
     ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
     int dp_world = 1, dp_rank = 0;
     // profiling: CUDA-event pairs around every tensor-core GEMM launch, and a count of kernel launches
@@ -464,6 +468,14 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
 }
 
 
+// the engine stream waits for the collectives begun on the side stream (gt_dp_allreduce_begin)
+int join_comm(gt_engine *e) {
+    if (!e->comm_pending) return GT_OK;
+    GT_CUDA(cudaStreamWaitEvent(e->stream, e->ev_join, 0));
+    e->comm_pending = false;
+    return GT_OK;
+}
+
 // ---- host-buffer calls -------------------------------------------------------------------------------------------
 int host_pipeline_init(gt_engine *e) {
     if (e->s_h2d) return GT_OK;
@@ -661,6 +673,12 @@ int gt_engine_destroy(gt_engine *e) {
         if (sl.compute_done) cudaEventDestroy(sl.compute_done);
         if (sl.d2h_done) cudaEventDestroy(sl.d2h_done);
     }
+    if (e->s_comm) {
+        cudaStreamSynchronize(e->s_comm);
+        cudaStreamDestroy(e->s_comm);
+    }
+    if (e->ev_fork) cudaEventDestroy(e->ev_fork);
+    if (e->ev_join) cudaEventDestroy(e->ev_join);
     if (e->s_h2d) cudaStreamDestroy(e->s_h2d);
     if (e->s_d2h) cudaStreamDestroy(e->s_d2h);
     if (e->status) cudaFree(e->status);
@@ -683,7 +701,9 @@ int gt_sync(gt_engine *e) {
     if (!e) return fail(GT_ERR_INVALID, "engine is null");
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    int rc = check_status(e);                                  // drains the engine stream
+    int rc = join_comm(e);                                     // collectives begun on the side stream
+    if (rc != GT_OK) return rc;
+    rc = check_status(e);                                      // drains the engine stream
     if (e->s_d2h) GT_CUDA(cudaStreamSynchronize(e->s_d2h));      // and the downloads of asynchronous host-buffer calls
     return rc;
 }
@@ -1127,21 +1147,56 @@ int gt_dp_init(gt_engine *e, int32_t world, int32_t rank, const void *unique_id,
     return GT_OK;
 }
 
+namespace {
+// all-reduce (+ scale) of g_dev on `st`; scale == 1/world lets the collective average, no extra pass
+int allreduce_on(gt_engine *e, float *g_dev, int64_t count, float scale, cudaStream_t st) {
+    if (e->comm) {
+        NcclApi &n = nccl_api();
+        const float inv = 1.0f / (float)e->dp_world;
+        const bool avg = scale == inv;
+        ncclResult_t r = n.AllReduce(g_dev, g_dev, (size_t)count, ncclFloat, avg ? ncclAvg : ncclSum, e->comm, st);
+        if (r != ncclSuccess) return fail(GT_ERR_NCCL, "ncclAllReduce: %s", n.GetErrorString(r));
+        if (avg) return GT_OK;
+    }
+    if (scale != 1.0f) GT_CUDA(launch_scale_clip(g_dev, count, scale, 0.0, e->clip, st));
+    return GT_OK;
+}
+}  // namespace
+
 int gt_dp_allreduce(gt_engine *e, float *g_dev, int64_t count, float scale) {
     if (!e || !g_dev || count < 0) return fail(GT_ERR_INVALID, "gt_dp_allreduce: bad argument");
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    if (e->comm) {
-        NcclApi &n = nccl_api();
-        // scale == 1/world is the common case (gradient averaging): let the collective average, no extra pass
-        const float inv = 1.0f / (float)e->dp_world;
-        const bool avg = scale == inv;
-        ncclResult_t r = n.AllReduce(g_dev, g_dev, (size_t)count, ncclFloat, avg ? ncclAvg : ncclSum, e->comm, e->stream);
-        if (r != ncclSuccess) return fail(GT_ERR_NCCL, "ncclAllReduce: %s", n.GetErrorString(r));
-        if (avg) return GT_OK;
+    int rc = join_comm(e);      // collectives of one communicator run in issue order
+    if (rc != GT_OK) return rc;
+    return allreduce_on(e, g_dev, count, scale, e->stream);
+}
+
+int gt_dp_allreduce_begin(gt_engine *e, float *g_dev, int64_t count, float scale) {
+    if (!e || !g_dev || count < 0) return fail(GT_ERR_INVALID, "gt_dp_allreduce_begin: bad argument");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (!e->s_comm) {
+        GT_CUDA(cudaStreamCreateWithFlags(&e->s_comm, cudaStreamNonBlocking));
+        GT_CUDA(cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming));
+        GT_CUDA(cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming));
     }
-    if (scale != 1.0f) GT_CUDA(launch_scale_clip(g_dev, count, scale, 0.0, e->clip, e->stream));
+    // fork: the side stream starts once everything queued on the engine stream so far (the kernels that produced
+    // these gradients) has finished; later engine-stream work runs beside the collective
+    GT_CUDA(cudaEventRecord(e->ev_fork, e->stream));
+    GT_CUDA(cudaStreamWaitEvent(e->s_comm, e->ev_fork, 0));
+    int rc = allreduce_on(e, g_dev, count, scale, e->s_comm);
+    if (rc != GT_OK) return rc;
+    GT_CUDA(cudaEventRecord(e->ev_join, e->s_comm));
+    e->comm_pending = true;
     return GT_OK;
+}
+
+int gt_dp_allreduce_end(gt_engine *e) {
+    if (!e) return fail(GT_ERR_INVALID, "engine is null");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return join_comm(e);
 }
 
 int gt_dp_finalize(gt_engine *e) {
@@ -1150,6 +1205,7 @@ int gt_dp_finalize(gt_engine *e) {
     if (e->comm) {
         cudaSetDevice(e->device);
         cudaStreamSynchronize(e->stream);
+        if (e->s_comm) cudaStreamSynchronize(e->s_comm);
         nccl_api().CommDestroy(e->comm);
         e->comm = nullptr;
     }

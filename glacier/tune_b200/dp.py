@@ -30,6 +30,24 @@ def flat_grad_layout(proj_shapes: Iterable[tuple[str, int, int]], rank: int, lay
     return entries, off
 
 
+BACKWARD_GROUPS = (("down",), ("gate", "up"), ("o",), ("q", "k", "v"))      # order in which a block's backward finishes them
+
+
+def group_buckets(entries, layer: int = 0, groups=BACKWARD_GROUPS):
+    """(offset, size) of each projection group's gradients inside the flat buffer, in backward order: the slices the
+    overlapped exchange (gt_dp_allreduce_begin) sends as soon as the group's backward has produced them.  The members of
+    a group are adjacent in the reference's parameter order, so every bucket is one contiguous slice."""
+    out = []
+    for g in groups:
+        a0 = entries[(layer, g[0])][0]
+        ob, nb = entries[(layer, g[-1])][2], entries[(layer, g[-1])][3]
+        for name in g[1:]:      # adjacency check
+            prev = g[g.index(name) - 1]
+            assert entries[(layer, name)][0] == entries[(layer, prev)][2] + entries[(layer, prev)][3], "group members must be adjacent"
+        out.append((a0, ob + nb - a0))
+    return out
+
+
 def share_unique_id(make_id, dist_module, src: int = 0) -> bytes:
     """Rank `src` creates the communicator id; every rank returns the same bytes (torch.distributed rendezvous)."""
     box = [make_id() if dist_module.get_rank() == src else None]

@@ -253,6 +253,13 @@ GT_API int gt_debug_set_trace(gt_engine *eng, void *dev_buf);
 GT_API int gt_dp_unique_id(void *out_id, int32_t nbytes);
 GT_API int gt_dp_init(gt_engine *eng, int32_t world, int32_t rank, const void *unique_id, int32_t nbytes);
 GT_API int gt_dp_allreduce(gt_engine *eng, float *g_dev, int64_t count, float scale);
+/* Overlapped form for per-bucket exchange (a layer's or a projection group's gradients as soon as its backward has
+ * produced them): _begin queues the all-reduce of one slice on a side stream that starts after the work queued on the
+ * engine stream so far, so that the backward kernels queued afterwards run beside it; _end makes the engine stream wait
+ * for every slice begun (gt_sync and gt_dp_allreduce do so too).  Every rank must begin the same slices in the same
+ * order.  Works inside a stream capture of the engine stream when _end is called before the capture ends. */
+GT_API int gt_dp_allreduce_begin(gt_engine *eng, float *g_dev, int64_t count, float scale);
+GT_API int gt_dp_allreduce_end(gt_engine *eng);
 GT_API int gt_dp_finalize(gt_engine *eng);
 
 #ifdef __cplusplus

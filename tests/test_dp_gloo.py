@@ -64,6 +64,19 @@ def test_flat_grad_layout_order_and_size():
             prev_end = ob + nb
 
 
+def test_group_buckets_tile_the_layer_buffer():
+    """The per-group slices of the overlapped exchange are contiguous, disjoint and cover the layer's gradients."""
+    from glacier.tune_b200 import dp, synth
+    shapes = [(n, *synth.QWEN7B_PROJ[n]) for n in dp.PROJ_ORDER]
+    entries, total = dp.flat_grad_layout(shapes, 16)
+    buckets = dp.group_buckets(entries)
+    assert sum(sz for _, sz in buckets) == total == 1441792
+    spans = sorted(buckets)
+    assert spans[0][0] == 0 and all(spans[i][0] + spans[i][1] == spans[i + 1][0] for i in range(len(spans) - 1))
+    # backward order: the down projection's slice is the last one in the buffer and the first one sent
+    assert buckets[0][0] + buckets[0][1] == total and buckets[-1][0] == 0
+
+
 def test_two_rank_gradient_averaging_equals_accumulation(tmp_path):
     world, port = 2, _free_port()
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
