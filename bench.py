@@ -262,11 +262,11 @@ def run_ours(args) -> None:
             else:
                 eng.backward(c["ws"][0], c["ads"][0], c["dYs"][0], c["X"], c["dX"], flags=bflags)
             # the group's gradients are final: their all-reduce runs beside the backward of the groups that follow
-            if world > 1 and not (not args.overlap):
+            if world > 1 and args.overlap:
                 eng.dp_allreduce_begin(c["grads"], 1.0 / world)
-        if world > 1 and not (not args.overlap):
+        if world > 1 and args.overlap:
             eng.dp_allreduce_end()
-        if world > 1 and (not args.overlap):
+        if world > 1 and not args.overlap:
             eng.dp_allreduce(flat_grads, 1.0 / world)
 
     # end to end: the same grouped calls on page-locked HOST buffers.  Every call stages its inputs to the device and its
