@@ -53,15 +53,10 @@ cudaError_t launch_any_nonzero(const float *B, int64_t n, int *flag, cudaStream_
 // scratch: 2 doubles on the device
 cudaError_t launch_scale_clip(float *g, int64_t n, float pre_scale, double max_norm, double *scratch, cudaStream_t s);
 
-// ---- LoRA products on TF32 warp MMAs for the bf16 math mode (gt_lora_tc.cu); same contracts as the fp32 versions,
-// except that `low` / `dLow` must be zero on entry (partial sums arrive by atomics)
-cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed, void *x16, int ldx16, int fp16, int T, int K,
-                              int R, cudaStream_t s);
-cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
-                              int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s);
-cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s);
-// Grouped forms: adapters of projections that share X go through one pass over it; the dY passes of several members
-// are one launch.  x16 / dy16 (may be null) receive the 16-bit copies.
+// ---- LoRA products on bf16 warp MMAs for the bf16 math mode (gt_lora_tc.cu); same contracts as the fp32 versions,
+// except that `low` / `dLow` must be zero on entry (partial sums arrive by atomics).  Adapters of projections that
+// share X go through one pass over it; the dY passes of several members are one launch.  x16 / dy16 (may be null)
+// receive the 16-bit copies.
 struct LoraXaJob {
     const float *A;
     float *low_zeroed;

@@ -610,24 +610,4 @@ cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, i
     return flush();
 }
 
-cudaError_t launch_lora_xa_tc(const float *X, const float *A, float *low_zeroed, void *x16, int ldx16, int fp16, int T, int K,
-                              int R, cudaStream_t s) {
-    if (R <= 0) return cudaSuccess;
-    const LoraXaJob job{A, low_zeroed, R};
-    return launch_lora_xa_group(X, &job, 1, x16, ldx16, fp16, T, K, nullptr, 0, s);
-}
-
-cudaError_t launch_lora_dy_tc(const float *dY, const float *low, const float *B, float *dB, float *dLow_zeroed, void *dy16,
-                              int ld16, int fp16, float scaling, int T, int N, int R, cudaStream_t s) {
-    if (N <= 0 || R <= 0) return cudaSuccess;
-    const LoraDyJob job{dY, low, B, dB, dLow_zeroed, dy16, ld16, scaling, N, R};
-    return launch_lora_dy_group(&job, 1, fp16, T, nullptr, 0, s);
-}
-
-cudaError_t launch_lora_da_tc(const float *X, const float *dLow, float *dA, float scaling, int T, int K, int R, cudaStream_t s) {
-    if (R <= 0) return cudaSuccess;
-    const LoraDaJob job{dLow, dA, scaling, R};
-    return launch_lora_da_group(X, &job, 1, T, K, s);
-}
-
 }  // namespace gt

@@ -282,6 +282,38 @@ def test_host_async_calls_complete_at_sync(G, eng, oracle):
     _free(ws, ads)
 
 
+def test_calls_from_several_host_threads(G, eng, oracle):
+    """The reference calls the engine from Parallel.Invoke (q | k | v, gate | up) and the engine serialises the calls
+    with a lock (TransformerBlock.cs:381-385, GpuLoraEngine.Forward.cs:121): three threads, host buffers, one engine."""
+    import threading
+    cs = _members(S.TYPE_Q4_K, (256, 128, 128), 512, 70, seed=61, adapted=(1, 1, 1), biased=(1, 1, 1))
+    eng.set_math_mode(0)
+    ws, ads = _upload(eng, cs)
+    ys, _, das, dbs = _reference(oracle, cs)
+    out = [None] * 3
+    errs = []
+
+    def work(j):
+        try:
+            for _ in range(3):
+                out[j] = eng.forward(ws[j], ads[j], cs[j]["x"])
+            eng.backward(ws[j], ads[j], cs[j]["dy"], cs[j]["x"], np.zeros((70, 512), np.float32))
+        except Exception as exc:      # noqa: BLE001
+            errs.append(exc)
+
+    threads = [threading.Thread(target=work, args=(j,)) for j in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errs, errs
+    for j in range(3):
+        assert oracle.rel_fro(out[j], ys[j]) < 2e-2
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(da, das[j]) < 5e-3 and oracle.rel_fro(db, dbs[j]) < 5e-3
+    _free(ws, ads)
+
+
 def test_group_error_paths(G, eng):
     import torch
     a = S.make_projection_case(S.TYPE_Q4_K, 128, 512, 8, seed=1)
