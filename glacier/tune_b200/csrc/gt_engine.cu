@@ -174,6 +174,26 @@ cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const cha
 
 constexpr int kMaxGroup = 3;
 
+// Members of one quantization type form one GEMM launch; a Q4_K_M mix (q, k in Q4_K, v in Q6_K) takes two.
+// order[] lists the member indices type by type, count[] the size of each run.
+int partition_by_type(int n, const gt_weight *const *w, int *order, int *count) {
+    int runs = 0, pos = 0;
+    bool taken[kMaxGroup] = {false, false, false};
+    for (int j = 0; j < n; j++) {
+        if (taken[j]) continue;
+        count[runs] = 0;
+        for (int i = j; i < n; i++) {
+            if (!taken[i] && w[i]->dev.qtype == w[j]->dev.qtype) {
+                taken[i] = true;
+                order[pos++] = i;
+                count[runs]++;
+            }
+        }
+        runs++;
+    }
+    return runs;
+}
+
 // The adapter's scratch holds low = X*A and dLow = dY*B^T of the current step side by side, [T, rank] fp32 each.
 size_t low_bytes(const gt_adapter *a, int T) { return ((size_t)T * a->rank * sizeof(float) + 255) & ~(size_t)255; }
 float *low_of(const gt_adapter *a) { return (float *)a->low.p; }
@@ -209,7 +229,7 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
 bool group_tensor_ok(const gt_engine *e, int n, const gt_weight *const *w) {
     if (n < 1 || n > kMaxGroup) return false;
     for (int j = 0; j < n; j++)
-        if (!tensor_path(e, w[j]) || w[j]->dev.qtype != w[0]->dev.qtype || w[j]->dev.K != w[0]->dev.K) return false;
+        if (!tensor_path(e, w[j]) || w[j]->dev.K != w[0]->dev.K) return false;      // quantization types may differ (Q4_K_M mixes)
     return true;
 }
 
@@ -288,15 +308,23 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         m[j].status = e->status;
         m[j].trace = e->trace;
     }
-    // split-K sums into the outputs: they start as the bias rows, written by the pass over X below
-    const int splits = umma_group_splits(m, n, e->sm_count);
+    // one launch per quantization type; split-K sums into the outputs: they start as the bias rows, written by the
+    // pass over X below
+    int order[kMaxGroup], count[kMaxGroup];
+    const int runs = partition_by_type(n, w, order, count);
+    UmmaLaunch run_m[kMaxGroup];      // members in launch order
     RowFill fills[kMaxGroup];
     int n_fills = 0;
-    for (int j = 0; j < n; j++) {
-        m[j].splits = splits;
-        if (splits > 1) {
-            fills[n_fills++] = RowFill{Yd[j], w[j]->dev.bias, w[j]->dev.N};
-            m[j].out_prefilled = 1;
+    for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
+        for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
+        const int splits = umma_group_splits(run_m + pos, count[r], e->sm_count);
+        for (int i = 0; i < count[r]; i++) {
+            const int j = order[pos + i];
+            m[j].splits = splits;
+            if (splits > 1) {
+                fills[n_fills++] = RowFill{Yd[j], w[j]->dev.bias, w[j]->dev.N};
+                m[j].out_prefilled = 1;
+            }
         }
     }
     gt_adapter *with[kMaxGroup];
@@ -312,9 +340,12 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
         for (int j = 0; j < n_fills; j++) GT_LAUNCH(e, launch_fill_rows(fills[j].dst, fills[j].bias, T, fills[j].N, e->stream));
     }
-    const char *msg = nullptr;
-    cudaError_t ce = timed_umma_group(e, m, n, &msg);
-    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
+        for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
+        const char *msg = nullptr;
+        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg);
+        if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    }
     return GT_OK;
 }
 
@@ -436,11 +467,18 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
         m[j].status = e->status;
         m[j].trace = e->trace;
     }
-    const int splits = umma_group_splits(m, n, e->sm_count);
-    for (int j = 0; j < n; j++) m[j].splits = splits;
-    const char *msg = nullptr;
-    cudaError_t ce = timed_umma_group(e, m, n, &msg);
-    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    // one launch per quantization type, all summing into the same dX
+    int order[kMaxGroup], count[kMaxGroup];
+    const int runs = partition_by_type(n, w, order, count);
+    UmmaLaunch run_m[kMaxGroup];
+    for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
+        for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
+        const int splits = umma_group_splits(run_m + pos, count[r], e->sm_count);
+        for (int i = 0; i < count[r]; i++) run_m[pos + i].splits = splits;
+        const char *msg = nullptr;
+        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg);
+        if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    }
     return GT_OK;
 }
 

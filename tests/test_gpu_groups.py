@@ -147,8 +147,43 @@ def test_group_equals_member_calls(G, eng, oracle):
     _free(ws, ads)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+def test_q4km_mixed_group(G, eng, oracle, mode):
+    """q, k in Q4_K and v in Q6_K (the Q4_K_M mix): one pass over X, one GEMM launch per quantization type, one dX."""
+    import torch
+    T, K = 200, 768
+    cs = []
+    for j, (qt, N) in enumerate(((S.TYPE_Q4_K, 384), (S.TYPE_Q4_K, 128), (S.TYPE_Q6_K, 128))):
+        c = S.make_projection_case(qt, N, K, T, seed=300 + j, with_bias=True)
+        if cs:
+            c["x"] = cs[0]["x"]
+        c["lora"], c["has_bias"] = True, j != 1
+        cs.append(c)
+    eng.set_math_mode(mode)
+    ws, ads = _upload(eng, cs)
+    X = torch.from_numpy(cs[0]["x"]).cuda()
+    Ys = [torch.empty((T, c["N"]), device="cuda") for c in cs]
+    dYs = [torch.from_numpy(c["dy"]).cuda() for c in cs]
+    dX = torch.full((T, K), 2.0, device="cuda")
+    eng.profile_read(True)
+    eng.profile_enable(True)
+    eng.forward_group(ws, ads, X, Ys)
+    eng.backward_group(ws, ads, dYs, X, dX, flags=G.FLAG_REUSE_LOW | G.FLAG_DX_ASSIGN)
+    eng.sync()
+    pr = eng.profile_read(True)
+    eng.profile_enable(False)
+    assert pr["gemm_launches"] == 4          # (q,k) + (v), forward and backward
+    ys, dxr, das, dbs = _reference(oracle, cs)
+    for j in range(3):
+        assert oracle.rel_fro(Ys[j].cpu().numpy(), ys[j]) < TOL[mode], j
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(da, das[j]) < LTOL[mode] and oracle.rel_fro(db, dbs[j]) < LTOL[mode], j
+    assert oracle.rel_fro(dX.cpu().numpy(), dxr) < TOL[mode]
+    _free(ws, ads)
+
+
 def test_group_host_buffers_and_mixed_types(G, eng, oracle):
-    """Host buffers and members of different quantization types are served member by member with the same results."""
+    """Host buffers and members of different quantization types give the same results as device tensors."""
     import torch
     a = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 40, seed=3, with_bias=True)
     b = S.make_projection_case(S.TYPE_Q6_K, 128, 512, 40, seed=4, with_bias=True)
