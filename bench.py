@@ -208,9 +208,10 @@ def run_ours(args) -> None:
     layer, off = [], 0
     for n in PROJ_ORDER:
         N, K = synth.QWEN7B_PROJ[n]
-        c = synth.make_projection_case(synth.TYPE_Q4_K, N, K, M_TOKENS, synth.seed_for(1, 0, n) + 100000 * rank, rank=RANK,
+        qt = synth.TYPE_Q6_K if (args.q4km and n in ("v", "down")) else synth.TYPE_Q4_K
+        c = synth.make_projection_case(qt, N, K, M_TOKENS, synth.seed_for(2 if args.q4km else 1, 0, n) + 100000 * rank, rank=RANK,
                                        alpha=ALPHA, x_bf16=True)
-        w = eng.upload_weight(synth.TYPE_Q4_K, c["w"], N, K)
+        w = eng.upload_weight(qt, c["w"], N, K)
         ad = eng.create_adapter(K, N, RANK, ALPHA)
         ad.upload(c["a"], c["b"])
         g0 = off
@@ -413,7 +414,8 @@ def run_ours(args) -> None:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens_per_gpu": M_TOKENS, "rank": RANK, "parallelism": f"dp{world}",
+            "config": {"workload": WORKLOAD.replace("in Q4_K", "in the Q4_K_M mix (v, down in Q6_K)") if args.q4km else WORKLOAD,
+                       "tokens_per_gpu": M_TOKENS, "rank": RANK, "parallelism": f"dp{world}",
                        "l2": "256 MiB written between timed steps; per-step inputs (131 MB weights + activations) exceed L2",
                        "launch": "cuda graph replay" if graph is not None else "eager",
                        "tokens_per_s": world * M_TOKENS * args.steps / (total_ms * 1e-3)},
@@ -551,6 +553,7 @@ def main() -> None:
     ap.add_argument("--overlap", action="store_true", help="one all-reduce per projection group beside the rest of the backward "
                     "(gt_dp_allreduce_begin/_end) instead of one after it; measured slower on a single layer (four small "
                     "collectives, and their CTAs cannot share an SM with a GEMM CTA)")
+    ap.add_argument("--q4km", action="store_true", help="v and down in Q6_K (the Q4_K_M mix of the second workload) instead of all Q4_K")
     ap.add_argument("--no-group", action="store_true", help="one call per projection instead of q,k,v and gate,up groups")
     ap.add_argument("--sweep", action="store_true", help="token-count sweep of the Q4_K_M projection set instead of the step benchmark")
     ap.add_argument("--glue", action="store_true", help="HBM throughput of the layer-glue kernels instead of the step benchmark")
