@@ -317,6 +317,35 @@ def test_host_async_calls_complete_at_sync(G, eng, oracle):
     _free(ws, ads)
 
 
+def test_group_with_different_ranks(G, eng, oracle):
+    """Members with ranks 16, 32 and 8: the chunk lists of the shared passes span several launches."""
+    import torch
+    T, K = 150, 512
+    cs = []
+    for j, (N, r) in enumerate(((256, 16), (128, 32), (128, 8))):
+        c = S.make_projection_case(S.TYPE_Q4_K, N, K, T, seed=700 + j, rank=r, alpha=2.0 * r)
+        if cs:
+            c["x"] = cs[0]["x"]
+        c["lora"], c["has_bias"] = True, False
+        cs.append(c)
+    eng.set_math_mode(0)
+    ws, ads = _upload(eng, cs)
+    X = torch.from_numpy(cs[0]["x"]).cuda()
+    Ys = [torch.empty((T, c["N"]), device="cuda") for c in cs]
+    dYs = [torch.from_numpy(c["dy"]).cuda() for c in cs]
+    dX = torch.zeros((T, K), device="cuda")
+    eng.forward_group(ws, ads, X, Ys)
+    eng.backward_group(ws, ads, dYs, X, dX, flags=G.FLAG_REUSE_LOW)
+    eng.sync()
+    ys, dxr, das, dbs = _reference(oracle, cs)
+    for j in range(3):
+        assert oracle.rel_fro(Ys[j].cpu().numpy(), ys[j]) < 2e-2, j
+        da, db = ads[j].grads()
+        assert oracle.rel_fro(da, das[j]) < 5e-3 and oracle.rel_fro(db, dbs[j]) < 5e-3, j
+    assert oracle.rel_fro(dX.cpu().numpy(), dxr) < 2e-2
+    _free(ws, ads)
+
+
 def test_calls_from_several_host_threads(G, eng, oracle):
     """The reference calls the engine from Parallel.Invoke (q | k | v, gate | up) and the engine serialises the calls
     with a lock (TransformerBlock.cs:381-385, GpuLoraEngine.Forward.cs:121): three threads, host buffers, one engine."""

@@ -109,6 +109,7 @@ SHAPES = [
     (S.TYPE_Q4_K, 128, 256, 1), (S.TYPE_Q4_K, 128, 256, 3), (S.TYPE_Q4_K, 200, 768, 17), (S.TYPE_Q4_K, 384, 1024, 512),
     (S.TYPE_Q4_K, 24, 256, 8), (S.TYPE_Q4_K, 256, 512, 600), (S.TYPE_Q4_K, 512, 3584, 128),
     (S.TYPE_Q6_K, 128, 256, 16), (S.TYPE_Q6_K, 200, 512, 33), (S.TYPE_Q6_K, 512, 3584, 512),
+    (S.TYPE_Q6_K, 256, 512, 2048), (S.TYPE_Q4_K, 384, 768, 1100),      # four and three token chunks
 ]
 
 
@@ -243,6 +244,18 @@ def test_backward_reusing_forward_low(G, eng, oracle):
         assert oracle.rel_fro(da, dar) < LTOL[mode] and oracle.rel_fro(db, dbr) < LTOL[mode]
         w.free()
         ad.free()
+
+
+@pytest.mark.parametrize("rank", [32, 40, 64])
+def test_ranks_above_sixteen(G, eng, oracle, rank):
+    """Ranks above 16 run as several 16-rank chunks in the LoRA passes and as a deeper rank-update stage in the GEMM."""
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 130, seed=rank, rank=rank, alpha=2.0 * rank)
+    for mode in (0, 2):
+        y, dx, da, db = _run(G, eng, c, mode, bias=False)
+        yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
+        errs = dict(Y=oracle.rel_fro(y, yr), dX=oracle.rel_fro(dx, dxr), dA=oracle.rel_fro(da, dar), dB=oracle.rel_fro(db, dbr))
+        assert errs["Y"] < TOL[mode] and errs["dX"] < TOL[mode], errs
+        assert errs["dA"] < LTOL[mode] and errs["dB"] < LTOL[mode], errs
 
 
 def test_rank8_adapter(G, eng, oracle):
