@@ -24,6 +24,10 @@
  *           restated here as exact-dequant fp32 GEMM / row dequant, which is what the
  *           reference's CPU-vs-GPU parity test ties them to
  *           (tests/Glacier.Tune.Tests/GradientAndGpuParityTests.cs:174-260).
+ *   Layer glue — SwiGLU and RoPE restate in-repo sources (src/Glacier.Tune/Kernels/SwiGluKernel.cs,
+ *           RoPEKernel.cs); the reference holds no known answers for them, the tests pin them by
+ *           closed forms, finite differences and the rotation's inverse.  RMSNorm lives in
+ *           Glacier.Tensor 1.1.0 (not vendored): textbook definition, PARITY UNPINNED.
  */
 #include <math.h>
 #include <stddef.h>
