@@ -22,7 +22,7 @@ EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
-    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
+    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
     "gt_rmsnorm_backward", "gt_add",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
@@ -80,6 +80,8 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_proj_forward_group.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
     lib.gt_proj_backward_group.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_int32]
+    lib.gt_ffn_forward.argtypes = [C.c_void_p] * 10 + [C.c_int32, C.c_int32]
+    lib.gt_ffn_backward.argtypes = [C.c_void_p] * 11 + [C.c_int32, C.c_int32]
     lib.gt_swiglu_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
     lib.gt_swiglu_backward.argtypes = [C.c_void_p] * 6 + [C.c_int64]
     lib.gt_add.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
@@ -227,6 +229,22 @@ class Engine:
         ads = self._ptr_array(adapters if adapters is not None else [None] * n)
         _check(self.lib.gt_proj_backward_group(self.h, n, self._ptr_array(weights), ads, self._ptr_array(dYs), _ptr(X, np.float32)[0],
                                                _ptr(dX, np.float32)[0], dYs[0].shape[0], flags))
+        return dX
+
+    def ffn_forward(self, w_gate, w_up, w_down, adapters, X, out_down, out_gate=None, out_up=None, out_hidden=None, flags: int = 0):
+        """ForwardFfn: down(SiLU(gate(X)) * up(X)) with the adapters' terms; optional outputs are skipped when None."""
+        xp, dev = _ptr(X, np.float32)
+        if dev:
+            flags |= FLAG_DEVICE_PTRS
+        ads = self._ptr_array(adapters) if adapters is not None else None
+        _check(self.lib.gt_ffn_forward(self.h, w_gate.h, w_up.h, w_down.h, ads, xp, _ptr(out_gate)[0], _ptr(out_up)[0],
+                                       _ptr(out_hidden)[0], _ptr(out_down)[0], X.shape[0], flags))
+        return out_down
+
+    def ffn_backward(self, w_gate, w_up, w_down, adapters, dY, X, gate, up, hidden, dX, flags: int = 0):
+        ads = self._ptr_array(adapters) if adapters is not None else None
+        _check(self.lib.gt_ffn_backward(self.h, w_gate.h, w_up.h, w_down.h, ads, _ptr(dY)[0], _ptr(X)[0], _ptr(gate)[0], _ptr(up)[0],
+                                        _ptr(hidden)[0], _ptr(dX)[0], dY.shape[0], flags | FLAG_DEVICE_PTRS))
         return dX
 
     # ---- layer glue (device tensors, asynchronous on the engine stream)

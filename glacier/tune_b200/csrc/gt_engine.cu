@@ -69,7 +69,7 @@ struct Scratch {
 }  // namespace
 
 constexpr int kHostSlots = 8;
-constexpr int kSlotIn = 4, kSlotOut = 3;      // forward: X -> Y_j; backward: dY_j, X -> dX
+constexpr int kSlotIn = 4, kSlotOut = 4;      // forward: X -> Y_j; backward: dY_j, X -> dX; FFN: X -> Y, gate, up, hidden
 struct HostSlot {
     Scratch in[kSlotIn], out[kSlotOut];
     cudaEvent_t h2d_done = nullptr, compute_done = nullptr, d2h_done = nullptr;
@@ -86,6 +86,7 @@ struct gt_engine {
     int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
     double *clip = nullptr;      // device double[2]
     Scratch x16, dy16, dlow, ytmp;
+    Scratch ffn[3];              // gate, up, hidden (forward) / dHidden, dGate, dUp (backward) of the fused FFN calls
     // Host-buffer calls: a ring of staging slots and two copy streams, so that the upload of one call, the kernels
     // of the previous one and the download of the one before run at the same time (GT_FLAG_HOST_ASYNC), and a
     // synchronous call still overlaps its own download with nothing in its way.
@@ -506,6 +507,47 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
 }
 
 
+// FFN block on device tensors: gate, up = projections of X (one group); hidden = SiLU(gate) * up; Y = down(hidden).
+// w / ad = {gate, up, down}.  gate_d / up_d / hidden_d may be null (engine scratch is used).
+int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *gate_d, float *up_d,
+                       float *hidden_d, float *Yd, int T, int flags) {
+    const int F = w[0]->dev.N;
+    const size_t bf = (size_t)T * F * sizeof(float);
+    float *bufs[3] = {gate_d, up_d, hidden_d};
+    for (int i = 0; i < 3; i++) {
+        if (!bufs[i]) {
+            GT_CUDA(e->ffn[i].reserve(bf));
+            bufs[i] = (float *)e->ffn[i].p;
+        }
+    }
+    float *gu[2] = {bufs[0], bufs[1]};
+    int rc = forward_group_device(e, 2, w, ad, Xd, gu, T, flags);
+    if (rc != GT_OK) return rc;
+    GT_LAUNCH(e, launch_swiglu_fwd(bufs[0], bufs[1], bufs[2], (int64_t)T * F, e->sm_count, e->stream));
+    float *yd = Yd;
+    return forward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, bufs[2], &yd, T, flags);
+}
+
+// The matching backward: dHidden = dY * W_down (+ adapter), (dGate, dUp) = SwiGLU'(dHidden, gate, up),
+// dX (+)= dGate * W_gate + dUp * W_up (+ adapters); adapter gradients accumulate.  Device tensors.
+int ffn_backward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *dYd, const float *Xd,
+                        const float *gate_d, const float *up_d, const float *hidden_d, float *dXd, int T, int flags) {
+    const int F = w[0]->dev.N;
+    const size_t bf = (size_t)T * F * sizeof(float);
+    for (int i = 0; i < 3; i++) GT_CUDA(e->ffn[i].reserve(bf));
+    float *dh = (float *)e->ffn[0].p, *dg = (float *)e->ffn[1].p, *du = (float *)e->ffn[2].p;
+    if (gate_d == dh || gate_d == dg || gate_d == du || up_d == dh || up_d == dg || up_d == du || hidden_d == dh || hidden_d == dg ||
+        hidden_d == du)
+        return fail(GT_ERR_INVALID, "gt_ffn_backward: gate, up and hidden must be the caller's buffers (the forward call was given NULL)");
+    const float *dy1 = dYd;
+    int rc = backward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, &dy1, hidden_d, dh, T,
+                                   (flags & ~GT_FLAG_DX_ASSIGN) | GT_FLAG_DX_ASSIGN);      // dHidden is written, not added to
+    if (rc != GT_OK) return rc;
+    GT_LAUNCH(e, launch_swiglu_bwd(dh, gate_d, up_d, dg, du, (int64_t)T * F, e->sm_count, e->stream));
+    const float *dgu[2] = {dg, du};
+    return backward_group_device(e, 2, w, ad, dgu, Xd, dXd, T, flags);
+}
+
 // the engine stream waits for the collectives begun on the side stream (gt_dp_allreduce_begin)
 int join_comm(gt_engine *e) {
     if (!e->comm_pending) return GT_OK;
@@ -702,7 +744,7 @@ int gt_engine_destroy(gt_engine *e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     if (e->s_h2d) cudaStreamSynchronize(e->s_h2d);
     if (e->s_d2h) cudaStreamSynchronize(e->s_d2h);
-    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp};
+    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->ffn[0], &e->ffn[1], &e->ffn[2]};
     for (Scratch *s : all) s->release();
     for (HostSlot &sl : e->slots) {
         for (Scratch &b : sl.in) b.release();
@@ -1043,6 +1085,83 @@ int gt_proj_backward(gt_engine *e, const gt_weight *w, gt_adapter *ad, const flo
 }
 
 int gt_stream_max_tokens(void) { return stream_max_tokens(); }
+
+namespace {
+int check_ffn(const gt_weight *wg, const gt_weight *wu, const gt_weight *wd, gt_adapter *const *ad, const char *who) {
+    if (!wg || !wu || !wd) return fail(GT_ERR_INVALID, "%s: null weight", who);
+    if (wg->dev.N != wu->dev.N || wg->dev.K != wu->dev.K)
+        return fail(GT_ERR_INVALID, "%s: gate [%d x %d] and up [%d x %d] differ in shape", who, wg->dev.N, wg->dev.K, wu->dev.N, wu->dev.K);
+    if (wd->dev.K != wg->dev.N || wd->dev.N != wg->dev.K)
+        return fail(GT_ERR_INVALID, "%s: down is [%d x %d], expected [%d x %d]", who, wd->dev.N, wd->dev.K, wg->dev.K, wg->dev.N);
+    const gt_weight *w[3] = {wg, wu, wd};
+    for (int j = 0; ad && j < 3; j++)
+        if (ad[j] && (ad[j]->in != w[j]->dev.K || ad[j]->out != w[j]->dev.N)) return fail(GT_ERR_INVALID, "%s: adapter %d does not match its weight", who, j);
+    return GT_OK;
+}
+}  // namespace
+
+int gt_ffn_forward(gt_engine *e, const gt_weight *w_gate, const gt_weight *w_up, const gt_weight *w_down, gt_adapter *const *adapters,
+                   const float *X, float *out_gate, float *out_up, float *out_hidden, float *out_down, int32_t T, int32_t flags) {
+    if (!e || !X || !out_down) return fail(GT_ERR_INVALID, "gt_ffn_forward: null argument");
+    if (T <= 0) return fail(GT_ERR_INVALID, "T must be positive (got %d)", T);
+    int rc = check_ffn(w_gate, w_up, w_down, adapters, "gt_ffn_forward");
+    if (rc != GT_OK) return rc;
+    const gt_weight *w[3] = {w_gate, w_up, w_down};
+    gt_adapter *ad[3] = {adapters ? adapters[0] : nullptr, adapters ? adapters[1] : nullptr, adapters ? adapters[2] : nullptr};
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    if (flags & GT_FLAG_DEVICE_PTRS) return ffn_forward_device(e, w, ad, X, out_gate, out_up, out_hidden, out_down, T, flags);
+    // host buffers: X goes up once, the intermediate tensors stay on the device; only the outputs that were asked for
+    // come back (the reference moves gate, up and hidden across PCIe up to five times per layer)
+    rc = host_pipeline_init(e);
+    if (rc != GT_OK) return rc;
+    HostSlot &sl = next_slot(e);
+    const int H = w_gate->dev.K, F = w_gate->dev.N;
+    const size_t bx = (size_t)T * H * sizeof(float), bf = (size_t)T * F * sizeof(float);
+    GT_CUDA(sl.in[0].reserve(bx));
+    GT_CUDA(sl.out[0].reserve(bx));
+    float *host_out[3] = {out_gate, out_up, out_hidden};
+    float *dev_out[3] = {nullptr, nullptr, nullptr};
+    for (int i = 0; i < 3; i++) {
+        if (host_out[i]) {
+            GT_CUDA(sl.out[1 + i].reserve(bf));
+            dev_out[i] = (float *)sl.out[1 + i].p;
+        }
+    }
+    if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->s_h2d, sl.compute_done, 0));
+    GT_CUDA(cudaMemcpyAsync(sl.in[0].p, X, bx, cudaMemcpyHostToDevice, e->s_h2d));
+    GT_CUDA(cudaEventRecord(sl.h2d_done, e->s_h2d));
+    GT_CUDA(cudaStreamWaitEvent(e->stream, sl.h2d_done, 0));
+    if (sl.used) GT_CUDA(cudaStreamWaitEvent(e->stream, sl.d2h_done, 0));
+    rc = ffn_forward_device(e, w, ad, (const float *)sl.in[0].p, dev_out[0], dev_out[1], dev_out[2], (float *)sl.out[0].p, T, flags);
+    if (rc != GT_OK) return rc;
+    GT_CUDA(cudaEventRecord(sl.compute_done, e->stream));
+    GT_CUDA(cudaStreamWaitEvent(e->s_d2h, sl.compute_done, 0));
+    GT_CUDA(cudaMemcpyAsync(out_down, sl.out[0].p, bx, cudaMemcpyDeviceToHost, e->s_d2h));
+    for (int i = 0; i < 3; i++)
+        if (host_out[i]) GT_CUDA(cudaMemcpyAsync(host_out[i], dev_out[i], bf, cudaMemcpyDeviceToHost, e->s_d2h));
+    GT_CUDA(cudaEventRecord(sl.d2h_done, e->s_d2h));
+    sl.used = true;
+    return finish_host_call(e, flags);
+}
+
+int gt_ffn_backward(gt_engine *e, const gt_weight *w_gate, const gt_weight *w_up, const gt_weight *w_down, gt_adapter *const *adapters,
+                    const float *dY, const float *X, const float *gate, const float *up, const float *hidden, float *dX, int32_t T,
+                    int32_t flags) {
+    if (!e || !dY || !gate || !up || !dX) return fail(GT_ERR_INVALID, "gt_ffn_backward: null argument");
+    if (T <= 0) return fail(GT_ERR_INVALID, "T must be positive (got %d)", T);
+    if (!(flags & GT_FLAG_DEVICE_PTRS)) return fail(GT_ERR_UNSUPPORTED, "gt_ffn_backward takes device tensors (GT_FLAG_DEVICE_PTRS)");
+    int rc = check_ffn(w_gate, w_up, w_down, adapters, "gt_ffn_backward");
+    if (rc != GT_OK) return rc;
+    const gt_weight *w[3] = {w_gate, w_up, w_down};
+    gt_adapter *ad[3] = {adapters ? adapters[0] : nullptr, adapters ? adapters[1] : nullptr, adapters ? adapters[2] : nullptr};
+    const bool lora = !(flags & GT_FLAG_NO_LORA);
+    if (lora && ((ad[0] || ad[1]) && !X)) return fail(GT_ERR_INVALID, "gt_ffn_backward: X is required for the gate / up adapter gradients");
+    if (lora && ad[2] && !hidden) return fail(GT_ERR_INVALID, "gt_ffn_backward: hidden is required for the down adapter gradients");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return ffn_backward_device(e, w, ad, dY, X, gate, up, hidden, dX, T, flags);
+}
 
 int gt_proj_forward_group(gt_engine *e, int32_t n, const gt_weight *const *w, gt_adapter *const *ad, const float *X, float *const *Y,
                           int32_t T, int32_t flags) {

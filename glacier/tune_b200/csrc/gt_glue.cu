@@ -216,6 +216,21 @@ int cuda_fail(const char *what, cudaError_t e) {
 
 }  // namespace
 
+namespace gt {
+// launchers for callers inside the library (the fused FFN calls): same kernels, caller holds the engine lock
+cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden, int64_t n, int sm_count, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    return launch_k(k_swiglu_fwd, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, gate, up, hidden, n,
+                    aligned16(gate) && aligned16(up) && aligned16(hidden) ? 1 : 0);
+}
+cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,
+                              cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    const int vec = aligned16(d_hidden) && aligned16(gate) && aligned16(up) && aligned16(d_gate) && aligned16(d_up) ? 1 : 0;
+    return launch_k(k_swiglu_bwd, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, d_hidden, gate, up, d_gate, d_up, n, vec);
+}
+}  // namespace gt
+
 extern "C" int gt_swiglu_forward(gt_engine *eng, const float *gate, const float *up, float *hidden, int64_t n) {
     if (!eng || !gate || !up || !hidden) return gt::set_last_error(GT_ERR_INVALID, "gt_swiglu_forward: null argument");
     if (n <= 0) return GT_OK;

@@ -137,6 +137,11 @@ bool stream_fwd_ok(const WeightDev *w, int T);
 cudaError_t launch_stream_fwd(const WeightDev *w, const float *X, float *Y_prefilled, int T, int sm_count, int *status, void *trace,
                               cudaStream_t s);
 
+// ---- layer glue launchers used inside the library (gt_glue.cu)
+cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden, int64_t n, int sm_count, cudaStream_t s);
+cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,
+                              cudaStream_t s);
+
 // ---- launches with programmatic dependent launch (the kernel must call pdl_wait() before touching global memory).
 // Environment GT_PDL=1 turns the attribute on; the default is plain stream order.
 bool pdl_enabled();

@@ -173,6 +173,22 @@ GT_API int gt_proj_forward_group(gt_engine *eng, int32_t n, const gt_weight *con
 GT_API int gt_proj_backward_group(gt_engine *eng, int32_t n, const gt_weight *const *weights, gt_adapter *const *adapters_or_null,
                                   const float *const *dY, const float *X, float *dX_accum_or_null, int32_t T, int32_t flags);
 
+/* Replaces: GpuLoraEngine.ForwardFfn(layer, norm2X, outGate?, outUp?, outHidden?, outDown, gateLora, upLora, downLora, seqLen)
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:247-364): gate and up projections of X as one group, hidden =
+ * SiLU(gate) * up, out_down = down projection of hidden, the adapters' terms included.  adapters = {gate, up, down}
+ * (the array or any entry may be NULL).  out_gate / out_up / out_hidden may be NULL: the tensors then live in engine
+ * scratch only.  With host buffers X goes up once and only the outputs that were asked for come back. */
+GT_API int gt_ffn_forward(gt_engine *eng, const gt_weight *w_gate, const gt_weight *w_up, const gt_weight *w_down,
+                          gt_adapter *const *adapters_or_null, const float *X, float *out_gate_or_null, float *out_up_or_null,
+                          float *out_hidden_or_null, float *out_down, int32_t T, int32_t flags);
+/* Replaces: the FFN half of TransformerBlock.Backward (src/Glacier.Tune/Model/TransformerBlock.cs:625-666): down.Backward,
+ * SwiGluKernel.Backward, gate.Backward and up.Backward into one input gradient.  Device tensors only
+ * (GT_FLAG_DEVICE_PTRS): gate, up, hidden are the tensors the forward produced; dX is accumulated into, or written with
+ * GT_FLAG_DX_ASSIGN; adapter gradients accumulate. */
+GT_API int gt_ffn_backward(gt_engine *eng, const gt_weight *w_gate, const gt_weight *w_up, const gt_weight *w_down,
+                           gt_adapter *const *adapters_or_null, const float *dY, const float *X, const float *gate, const float *up,
+                           const float *hidden, float *dX, int32_t T, int32_t flags);
+
 /* ---- layer glue on device tensors (asynchronous on the engine stream): what sits between the projections ---- */
 /* Replaces: SwiGluKernel.Forward (src/Glacier.Tune/Kernels/SwiGluKernel.cs:13-31): hidden = SiLU(gate) * up, n elements. */
 GT_API int gt_swiglu_forward(gt_engine *eng, const float *gate, const float *up, float *hidden, int64_t n);

@@ -153,3 +153,63 @@ def test_gpu_glue_argument_checks(eng):
         eng.rope(None, None, 4, 1, 1, 8)
     with pytest.raises(G.GtError):
         eng.rope(x, None, 1, 1, 1, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T", [9, 300])
+def test_gpu_ffn_block_forward_and_backward(eng, oracle, T):
+    """gt_ffn_forward / gt_ffn_backward against the oracle chained the way TransformerBlock does it: gate and up
+    projections, SwiGLU, down projection, and back.  bf16 mode tolerances; T = 9 takes the few-token forward kernels."""
+    import torch
+    from glacier.tune_b200 import capi as G, synth as S
+    H, F = 256, 768
+    eng.set_math_mode(0)
+    cg = S.make_projection_case(S.TYPE_Q4_K, F, H, T, seed=11)
+    cu = S.make_projection_case(S.TYPE_Q4_K, F, H, T, seed=12)
+    cd = S.make_projection_case(S.TYPE_Q6_K, H, F, T, seed=13)
+    x, dy = cg["x"], cd["dy"]
+    ws = [eng.upload_weight(c["qtype"], c["w"], c["N"], c["K"]) for c in (cg, cu, cd)]
+    ads = []
+    for c in (cg, cu, cd):
+        a = eng.create_adapter(c["K"], c["N"], 16, 32.0)
+        a.upload(c["a"], c["b"])
+        ads.append(a)
+    # oracle chain (fp32 CPU path)
+    proj = lambda c, xin: oracle.proj_forward(c["qtype"], c["w"], None, xin, c["K"], c["N"], T, c["a"], c["b"], 16, c["scaling"])   # noqa: E731
+    g_ref, u_ref = proj(cg, x), proj(cu, x)
+    h_ref = oracle.swiglu_forward(g_ref, u_ref)
+    y_ref = proj(cd, h_ref)
+    X = torch.from_numpy(x).cuda()
+    Gt, Ut, Ht = (torch.empty((T, F), device="cuda") for _ in range(3))
+    Y = torch.empty((T, H), device="cuda")
+    eng.ffn_forward(ws[0], ws[1], ws[2], ads, X, Y, Gt, Ut, Ht)
+    eng.sync()
+    assert oracle.rel_fro(Gt.cpu().numpy(), g_ref) < 2e-2 and oracle.rel_fro(Ut.cpu().numpy(), u_ref) < 2e-2
+    assert oracle.rel_fro(Ht.cpu().numpy(), h_ref) < 3e-2 and oracle.rel_fro(Y.cpu().numpy(), y_ref) < 3e-2
+    # intermediate tensors left in engine scratch: same result
+    Y2 = torch.empty_like(Y)
+    eng.ffn_forward(ws[0], ws[1], ws[2], ads, X, Y2)
+    eng.sync()
+    assert oracle.rel_fro(Y2.cpu().numpy(), Y.cpu().numpy()) < 1e-3
+    # host buffers, only the final output asked for
+    yh = np.empty((T, H), np.float32)
+    eng.ffn_forward(ws[0], ws[1], ws[2], ads, x, yh)
+    assert oracle.rel_fro(yh, y_ref) < 3e-2
+    # backward, on the device's own forward tensors so that only the backward arithmetic is compared
+    g_d, u_d, h_d = Gt.cpu().numpy(), Ut.cpu().numpy(), Ht.cpu().numpy()
+    back = lambda c, dyin, xin: oracle.proj_backward(c["qtype"], c["w"], dyin, xin, c["K"], c["N"], T, c["a"], c["b"], 16, c["scaling"])   # noqa: E731
+    dh_ref, dad, dbd = back(cd, dy, h_d)
+    dg_ref, du_ref = oracle.swiglu_backward(dh_ref, g_d, u_d)
+    dx_g, dag, dbg = back(cg, dg_ref, x)
+    dx_u, dau, dbu = back(cu, du_ref, x)
+    for a in ads:
+        a.zero_grads()
+    dX = torch.full((T, H), 5.0, device="cuda")
+    eng.ffn_backward(ws[0], ws[1], ws[2], ads, torch.from_numpy(dy).cuda(), X, Gt, Ut, Ht, dX, flags=G.FLAG_DX_ASSIGN)
+    eng.sync()
+    assert oracle.rel_fro(dX.cpu().numpy(), dx_g + dx_u) < 3e-2
+    for a, (da_ref, db_ref) in zip(ads, ((dag, dbg), (dau, dbu), (dad, dbd))):
+        da, db = a.grads()
+        assert oracle.rel_fro(da, da_ref) < 3e-2 and oracle.rel_fro(db, db_ref) < 3e-2
+    for h in ws + ads:
+        h.free()
