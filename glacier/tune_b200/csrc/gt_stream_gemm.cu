@@ -2,8 +2,8 @@
 //
 // With a handful of tokens every weight is used a handful of times, so the projection is bound by how fast the
 // packed K-quant bytes leave HBM, not by the tensor pipe, and the CTA-wide tcgen05 kernel (one MMA per ~200 clocks
-// whatever its size) cannot keep up.  Here each WARP streams 16 weight rows straight from global memory into
-// registers and multiplies them on warp-level m16n8k16 MMAs (weights = A operand, tokens = B operand):
+// whatever its size) cannot keep up.  Here each WARP streams 16 weight rows through its own shared-memory ring and
+// multiplies them on warp-level m16n8k16 MMAs (weights = A operand, tokens = B operand):
 //
 //   * the quantized integers go into the MMA as they are: a nibble q is dropped into a bf16 bit pattern 0x4300 | q
 //     (= 128 + q, exact), one LOP3 per pair of weights, no arithmetic per weight;
@@ -15,9 +15,9 @@
 //     bytes of qs) are the A fragments of four MMAs without any shuffle; X is staged once per CTA in shared memory
 //     in the matching order, together with S.
 //
-// Grid: (CTAs per K split, K splits), one CTA of 8 warps per SM.  The packed rows travel global -> shared memory as
-// bulk copies into a per-warp ring (three chunks of 16 rows x 288 bytes in flight per warp); partial sums leave
-// through fp32 atomics into a Y pre-filled with the bias.
+// Grid: (CTAs per K split, K splits), one CTA of 16 warps per SM.  The packed rows travel global -> shared memory as
+// tiled TMA copies into a per-warp ring (two chunks of 16 rows x 288 bytes in flight per warp, one copy per chunk);
+// partial sums leave through fp32 atomics into a Y pre-filled with the bias.
 // Replaces gemm_q4_k_batch of the reference at small batch (launched at src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:83-129).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -96,8 +96,8 @@ constexpr int kWarpRing = kRingStages * kStageBytes;
 // S [blocks_per_cta * 8 sub-blocks][TP]; per warp: scale scratch, a ring of packed weight rows, its barriers.
 //
 // Work of one K split = (16-row tile, chunk of two blocks) items in row-major order, cut into equal contiguous runs
-// over the warps of the split's CTAs; a warp walks its run with kRingStages chunks in flight (one bulk copy per row
-// and chunk, issued by lanes 0-15) and adds a tile's partial sums into Y whenever it leaves the tile.
+// over the warps of the split's CTAs; a warp walks its run with kRingStages chunks in flight (one tiled copy per
+// chunk, issued by lane 0) and adds a tile's partial sums into Y whenever it leaves the tile.
 template <int NT>
 __global__ void __launch_bounds__(kSThreads, 1) k_stream_fwd_q4k(const __grid_constant__ StreamParams p) {
     constexpr int TP = 8 * NT;
