@@ -12,11 +12,16 @@
 // (up to 512), so each weight is dequantized once per CTA and reused by every token:
 //   D[128 x tokens] (TMEM, fp32)  +=  Wtile[128 x 64] (SMEM, dequantized 16-bit)  x  act[tokens x 64]^T (SMEM via TMA)
 //
-// Warp roles (576 threads):
-//   warp 0      TMA producer: packed half-super-blocks of W (raw bytes) and 16-bit activation tiles
-//   warp 1      tcgen05.mma issuer (one thread); owns the TMEM allocation
-//   warps 2-17  two groups of 8 warps that dequantize alternate operand stages (raw blocks -> 128-byte-swizzled
-//               tiles); afterwards all 16 run the epilogue (tcgen05.ld -> bias -> global store / atomic add)
+// Warp roles (608 threads):
+//   warp 0        TMA producer: packed half-super-blocks of W (raw bytes) and 16-bit activation tiles
+//   warps 1, 18   tcgen05.mma issuers (one thread each, alternate stages, a turn token keeps the order fixed);
+//                 warp 1 owns the TMEM allocation
+//   warps 2-17    two groups of 8 warps that dequantize alternate operand stages (raw blocks -> 128-byte-swizzled
+//                 tiles); afterwards all 16 run the epilogue (tcgen05.ld -> bias -> global store / atomic add)
+//
+// One launch serves up to three member projections (forward: they share the activation tiles, each tile index belongs
+// to one member; backward: their contraction ranges are concatenated and all sum into one dX), each with its own
+// rank-update stage when it has an adapter.
 //
 // The dequantized tile image is the same for both directions: row = weight row n, 128 bytes = 64 consecutive
 // k, chunks XOR-swizzled by (row & 7).  Forward reads it as a K-major A operand (M = n, K = k); backward
