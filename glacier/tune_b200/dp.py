@@ -60,3 +60,14 @@ def average_gradients_reference(flat, dist_module) -> None:
     of the driver logic; the GPU path calls gt_dp_allreduce instead."""
     dist_module.all_reduce(flat)
     flat.mul_(1.0 / dist_module.get_world_size())
+
+
+def average_gradients_bucketed(flat, buckets, dist_module) -> None:
+    """The bucketed form of the same reduction: one all-reduce per (offset, size) slice in the given order, the order in
+    which a backward pass finishes them.  On GPUs each slice is a gt_dp_allreduce_begin call; the result is the same as
+    one all-reduce over the whole buffer."""
+    inv = 1.0 / dist_module.get_world_size()
+    for off, size in buckets:
+        part = flat[off: off + size]
+        dist_module.all_reduce(part)
+        part.mul_(inv)

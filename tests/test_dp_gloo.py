@@ -43,7 +43,11 @@ def _worker(rank, world, port, out_dir):
         oa, na, ob, nb = entries[(0, name)]
         flat[oa:oa + na] = torch.from_numpy(ga.reshape(-1))
         flat[ob:ob + nb] = torch.from_numpy(gb.reshape(-1))
+    bucketed = flat.clone()
     dp.average_gradients_reference(flat, dist)
+    # the per-bucket exchange (last projection first, as a backward pass finishes them) gives the same buffer
+    dp.average_gradients_bucketed(bucketed, dp.group_buckets(entries, groups=(("k",), ("q",))), dist)
+    assert torch.equal(bucketed, flat)
     np.save(os.path.join(out_dir, f"avg_{rank}.npy"), flat.numpy())
     dist.barrier()
     dist.destroy_process_group()
