@@ -15,7 +15,8 @@ struct WeightDev {
     int64_t row_bytes = 0;        // K/256 * block bytes when K % 256 == 0, else 0 (flat super-block stream)
     float *bias = nullptr;        // [N] or null
     bool tma_ok = false;          // row-aligned and tensor maps built
-    CUtensorMap tm_hdr, tm_q0, tm_q1;   // 2-D byte maps over [N, row_bytes], boxes of 64 rows
+    CUtensorMap tm_hdr, tm_q0, tm_q1;   // 2-D byte maps over [N, row_bytes], boxes of 64 rows (backward raw stages)
+    CUtensorMap tm_hdr_f, tm_q0_f, tm_q1_f;   // the same with boxes of 128 rows (forward raw stages: half as many copies)
     CUtensorMap tm_rows;                // Q4_K: 32-bit words over [N, row_bytes / 4], boxes of 16 rows x 288 bytes (two blocks)
 };
 

@@ -272,8 +272,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const Member &W = p.m[um];
                 const int xb = sb * QS::kBlockBytes;
                 mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
+                // one copy per region: the tensor maps handed to a forward launch have 128-row boxes, the backward
+                // ones 64-row boxes (issuing a copy costs the producer thread a few hundred clocks whatever its size)
 #pragma unroll
-                for (int rr = 0; rr < kRows; rr += 64) {
+                for (int rr = 0; rr < kRows; rr += kRows) {
                     tma_load_2d(rdst + rr * H, &W.tm_hdr, xb + QS::hdr_x(half), row0 + rr, rbar);
                     tma_load_2d(rdst + kRows * H + rr * 64, &W.tm_q0, xb + QS::q0_x(half), row0 + rr, rbar);
                     if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64) + rr * Q1, &W.tm_q1, xb + QS::q1_x(half), row0 + rr, rbar);
@@ -660,6 +662,15 @@ cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
     const int H = w->qtype == kTypeQ4K ? 16 : 32;
     bool ok = encode_2d(&w->tm_hdr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
                         (uint64_t)w->row_bytes, H, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode_2d(&w->tm_hdr_f, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                         (uint64_t)w->row_bytes, H, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode_2d(&w->tm_q0_f, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                         (uint64_t)w->row_bytes, 64, 128, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (w->qtype == kTypeQ6K)
+        ok = ok && encode_2d(&w->tm_q1_f, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                             (uint64_t)w->row_bytes, 32, 128, CU_TENSOR_MAP_SWIZZLE_32B);
+    else
+        w->tm_q1_f = w->tm_q0_f;
     ok = ok && encode_2d(&w->tm_q0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
                          (uint64_t)w->row_bytes, 64, 64, CU_TENSOR_MAP_SWIZZLE_64B);
     if (w->qtype == kTypeQ6K)
@@ -760,9 +771,9 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
         const UmmaLaunch &L = m[j];
         const WeightDev *w = L.w;
         Member &M = p.m[j];
-        M.tm_hdr = w->tm_hdr;
-        M.tm_q0 = w->tm_q0;
-        M.tm_q1 = w->tm_q1;
+        M.tm_hdr = L0.backward ? w->tm_hdr : w->tm_hdr_f;
+        M.tm_q0 = L0.backward ? w->tm_q0 : w->tm_q0_f;
+        M.tm_q1 = L0.backward ? w->tm_q1 : w->tm_q1_f;
         if (bwd || j == 0) {
             const int cols = bwd ? w->N : w->K;       // contraction length of the activation operand
             if (!encode_2d(&M.tm_act, dt, 2, L.act16, (uint64_t)cols, (uint64_t)L.T, (uint64_t)L.ld_act * 2, 64, (uint32_t)p.t_box,
