@@ -12,8 +12,9 @@
 // (up to 512), so each weight is dequantized once per CTA and reused by every token:
 //   D[128 x tokens] (TMEM, fp32)  +=  Wtile[128 x 64] (SMEM, dequantized 16-bit)  x  act[tokens x 64]^T (SMEM via TMA)
 //
-// Warp roles (608 threads):
-//   warp 0        TMA producer: packed half-super-blocks of W (raw bytes) and 16-bit activation tiles
+// Warp roles (640 threads):
+//   warp 0        TMA producer of the packed half-super-blocks of W (raw bytes)
+//   warp 19       TMA producer of the 16-bit activation tiles
 //   warps 1, 18   tcgen05.mma issuers (one thread each, alternate stages, a turn token keeps the order fixed);
 //                 warp 1 owns the TMEM allocation
 //   warps 2-17    two groups of 8 warps that dequantize alternate operand stages (raw blocks -> 128-byte-swizzled
@@ -56,7 +57,8 @@ constexpr int kXBytes = kNumA * kXStageBytes;
 constexpr int kRawBudget = 32768;
 constexpr int kMaxRaw = 8;
 constexpr int kDequantWarps = 16;   // two groups of 8
-constexpr int kThreads = 32 * (3 + kDequantWarps);   // + producer warp, + two MMA-issuer warps (1 and 18)
+constexpr int kThreads = 32 * (4 + kDequantWarps);   // + weight producer (0), two MMA issuers (1, 18), activation producer (19)
+constexpr int kIssuer2Warp = 18, kActProducerWarp = 19;
 
 constexpr int kOffX = 0;
 constexpr int kOffA = kOffX + kXBytes;
@@ -253,9 +255,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     };
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------------ TMA producer of the packed weights
+        // (issuing a tiled copy costs the issuing thread several hundred clocks: weights and activations have a
+        // producer thread each, on their own barriers)
         if (lane == 0) {
-            Ring raw, xs;
+            Ring raw;
             bool ok = true;
             for (int u = u0; u < u1 && ok; u++) {
                 ok = mbar_wait_bounded(bar(kBarRawEmpty + raw.idx), raw.phase ^ 1u, abort_flag, p.status, kCodeProducer + 1);
@@ -273,15 +277,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const int xb = sb * QS::kBlockBytes;
                 mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
                 // one copy per region: the tensor maps handed to a forward launch have 128-row boxes, the backward
-                // ones 64-row boxes (issuing a copy costs the producer thread a few hundred clocks whatever its size)
-#pragma unroll
-                for (int rr = 0; rr < kRows; rr += kRows) {
-                    tma_load_2d(rdst + rr * H, &W.tm_hdr, xb + QS::hdr_x(half), row0 + rr, rbar);
-                    tma_load_2d(rdst + kRows * H + rr * 64, &W.tm_q0, xb + QS::q0_x(half), row0 + rr, rbar);
-                    if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64) + rr * Q1, &W.tm_q1, xb + QS::q1_x(half), row0 + rr, rbar);
-                }
+                // ones 64-row boxes
+                tma_load_2d(rdst, &W.tm_hdr, xb + QS::hdr_x(half), row0, rbar);
+                tma_load_2d(rdst + kRows * H, &W.tm_q0, xb + QS::q0_x(half), row0, rbar);
+                if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64), &W.tm_q1, xb + QS::q1_x(half), row0, rbar);
                 trace(0, u - u0);
                 raw.advance(kNumRaw);
+            }
+        }
+    } else if (warp == kActProducerWarp) {
+        // ------------------------------------------------------------------ TMA producer of the activation tiles
+        if (lane == 0) {
+            Ring xs;
+            bool ok = true;
+            for (int u = u0; u < u1 && ok; u++) {
+                int um = mi, rb = 0;
+                if (BWD) um = unit_member(u, rb);
+                const Member &W = p.m[um];
                 for (int s = 0; s < kSub && ok; s++) {
                     ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
                     if (!ok) break;
@@ -299,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 xs.advance(kNumX);
             }
         }
-    } else if (warp == 1 || warp == kThreads / 32 - 1) {
+    } else if (warp == 1 || warp == kIssuer2Warp) {
         // ------------------------------------------------------------------ two MMA issuers (leader CTA only in pair mode)
         // Issuing is blocking (the queue in front of the tensor pipe is short) and every stage costs a barrier wait,
         // a fence and a commit: two threads take alternate stages, so one waits for its next stage while the other
