@@ -239,18 +239,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     }
 
     // activation tile of one stage: coordinate c0 along the contraction, this CTA's token rows
-    auto load_act_stage = [&](const CUtensorMap *tm, int c0, uint32_t xdst, uint32_t xbar_local) {
+    // Called by lanes 0..3 of the activation producer warp: lane 0 arms the barrier, lane i issues copy i (the copies
+    // of a stage are issued side by side; the barrier cannot complete before lane 0's arrival).
+    auto load_act_stage = [&](const CUtensorMap *tm, int c0, uint32_t xdst, uint32_t xbar_local, int li) {
         if (PAIR) {
             // leader arms the barrier for the bytes of both CTAs; each CTA loads its half of every MMA's tokens
-            if (leader) mbar_arrive_expect_tx(xbar_local, (uint32_t)(2 * n_mma * (MTOK / 2) * 128));
+            if (leader && li == 0) mbar_arrive_expect_tx(xbar_local, (uint32_t)(2 * n_mma * (MTOK / 2) * 128));
             const uint32_t lbar = mapa_cluster(xbar_local, 0);
-            for (int i = 0; i < n_mma; i++) {
-                const int ntok = min(MTOK, tb - MTOK * i);
-                tma_load_2d_pair(xdst + i * kMmaSlotBytes, tm, c0, tok0 + MTOK * i + (int)crank * (ntok >> 1), lbar);
+            if (li < n_mma) {
+                const int ntok = min(MTOK, tb - MTOK * li);
+                tma_load_2d_pair(xdst + li * kMmaSlotBytes, tm, c0, tok0 + MTOK * li + (int)crank * (ntok >> 1), lbar);
             }
         } else {
-            mbar_arrive_expect_tx(xbar_local, (uint32_t)(n_box * p.t_box * 128));
-            for (int b = 0; b < n_box; b++) tma_load_2d(xdst + b * p.t_box * 128, tm, c0, tok0 + b * p.t_box, xbar_local);
+            if (li == 0) mbar_arrive_expect_tx(xbar_local, (uint32_t)(n_box * p.t_box * 128));
+            if (li < n_box) tma_load_2d(xdst + li * p.t_box * 128, tm, c0, tok0 + li * p.t_box, xbar_local);
         }
     };
 
@@ -258,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         // ------------------------------------------------------------------ TMA producer of the packed weights
         // (issuing a tiled copy costs the issuing thread several hundred clocks: weights and activations have a
         // producer thread each, on their own barriers)
-        if (lane == 0) {
+        if (lane < 3) {      // lane 0 arms the barrier and copies the headers, lanes 1 and 2 copy the quant regions
             Ring raw;
             bool ok = true;
             for (int u = u0; u < u1 && ok; u++) {
@@ -275,19 +277,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 }
                 const Member &W = p.m[um];
                 const int xb = sb * QS::kBlockBytes;
-                mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
                 // one copy per region: the tensor maps handed to a forward launch have 128-row boxes, the backward
                 // ones 64-row boxes
-                tma_load_2d(rdst, &W.tm_hdr, xb + QS::hdr_x(half), row0, rbar);
-                tma_load_2d(rdst + kRows * H, &W.tm_q0, xb + QS::q0_x(half), row0, rbar);
-                if (Q1 > 0) tma_load_2d(rdst + kRows * (H + 64), &W.tm_q1, xb + QS::q1_x(half), row0, rbar);
-                trace(0, u - u0);
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
+                    tma_load_2d(rdst, &W.tm_hdr, xb + QS::hdr_x(half), row0, rbar);
+                    trace(0, u - u0);
+                } else if (lane == 1) {
+                    tma_load_2d(rdst + kRows * H, &W.tm_q0, xb + QS::q0_x(half), row0, rbar);
+                } else if (Q1 > 0) {
+                    tma_load_2d(rdst + kRows * (H + 64), &W.tm_q1, xb + QS::q1_x(half), row0, rbar);
+                }
                 raw.advance(kNumRaw);
             }
         }
     } else if (warp == kActProducerWarp) {
         // ------------------------------------------------------------------ TMA producer of the activation tiles
-        if (lane == 0) {
+        if (lane < 4) {
             Ring xs;
             bool ok = true;
             for (int u = u0; u < u1 && ok; u++) {
@@ -298,8 +304,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 2);
                     if (!ok) break;
                     load_act_stage(BWD ? &W.tm_act : &p.m[0].tm_act, BWD ? rb * 64 : (u * 2 + s) * 64, sbase + kOffX + xs.idx * kXStageBytes,
-                                   bar(kBarFull + xs.idx));
-                    trace(1, (u - u0) * kSub + s);
+                                   bar(kBarFull + xs.idx), lane);
+                    if (lane == 0) trace(1, (u - u0) * kSub + s);
                     xs.advance(kNumX);
                 }
             }
@@ -307,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 // rank-update stage: both operand tiles are built by the dequant warps; the producer only adds the
                 // arrival that stands for the TMA bytes in the other stages
                 ok = mbar_wait_bounded(bar(kBarEmpty + xs.idx), xs.phase ^ 1u, abort_flag, p.status, kCodeProducer + 3);
-                if (ok && leader) mbar_arrive(bar(kBarFull + xs.idx));
+                if (ok && leader && lane == 0) mbar_arrive(bar(kBarFull + xs.idx));
                 xs.advance(kNumX);
             }
         }
