@@ -36,7 +36,7 @@ UNIT = "TFLOP/s"
 WORKLOAD = "qwen2.5-7b layer projections q,k,v,o,gate,up,down in Q4_K, M=512, fwd+dX+LoRA grads (r=16)"
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised in
 # profiles/k_umma_gemm_gate_up_group_m512_full.md: the gate,up forward launch, the largest of the step
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 115.6e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 115.9e6
 
 
 def step_flops(names=PROJ_ORDER, m=M_TOKENS) -> float:
@@ -397,7 +397,7 @@ def run_ours(args) -> None:
             "frac_of_sustained": (gemm_tflops / peaks["bf16_tflops_sustained"]) if peaks["bf16_tflops_sustained"] else None,
             "timed_in": f"eager pass of {prof_steps} steps after the timed region (events around each GEMM launch)",
             "launches": prof["gemm_launches"], "avg_launch_us": 1e3 * prof["gemm_ms"] / max(1, prof["gemm_launches"]),
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_of": "gate,up forward launch, 2 x 18944x3584 at M=512 (algorithmic HBM bytes: 80.1e6 read + 77.6e6 fp32 output, of which 31.1e6 left the L2 before the kernel ended)",
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_of": "gate,up forward launch, 2 x 18944x3584 at M=512 (algorithmic HBM bytes: 80.1e6 read + 77.6e6 fp32 output, of which 31.4e6 left the L2 before the kernel ended)",
         }
         # CPU baseline: the oracle (a port of the reference's CPU path) on this host, one pass over the same layer
         from oracle import oracle as O
