@@ -510,6 +510,8 @@ def run_glue(args) -> None:
     gate, up, dh, hid, dg, du = t(T, F), t(T, F), t(T, F), t(T, F), t(T, F), t(T, F)
     x, w, y, dy, dx = t(T, H), torch.ones(H, device="cuda"), t(T, H), t(T, H), t(T, H)
     q, k = t(T, HQ * D), t(T, HK * D)
+    NP = 40_370_176
+    ap_, ag_, am_, av_ = t(NP), t(NP), torch.zeros(NP, device="cuda"), torch.zeros(NP, device="cuda")
     cases = [
         ("swiglu_forward [512, 18944]", lambda: eng.swiglu_forward(gate, up, hid), 3 * 4 * T * F),
         ("swiglu_backward [512, 18944]", lambda: eng.swiglu_backward(dh, gate, up, dg, du), 5 * 4 * T * F),
@@ -517,6 +519,8 @@ def run_glue(args) -> None:
         ("rmsnorm_backward [512, 3584]", lambda: eng.rmsnorm_backward(dy, x, w, dx), 3 * 4 * T * H),
         ("rope q 28 + k 4 heads x 128", lambda: eng.rope(q, k, T, HQ, HK, D, 1e6), 2 * 4 * T * (HQ + HK) * D),
         ("add [512, 3584]", lambda: eng.add(x, y, dx), 3 * 4 * T * H),
+        # all adapters of the 28-layer model as one flat buffer: p, g, m, v read, p, m, v written
+        ("adamw_step 40.4 M parameters", lambda: eng.adamw_step(ap_, ag_, am_, av_, 2e-4, 0.9, 0.999, 1e-8, 0.01, 3), 7 * 4 * NP),
     ]
     rows = []
     for name, call, nbytes in cases:

@@ -25,6 +25,7 @@ EXPORTS = [
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
     "gt_rmsnorm_backward", "gt_add",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
+    "gt_adamw_step", "gt_adapter_adamw_step",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
@@ -93,6 +94,8 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
+    lib.gt_adamw_step.argtypes = [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64] + [C.c_float] * 5 + [C.c_int32]
+    lib.gt_adapter_adamw_step.argtypes = [C.c_void_p] + [C.c_float] * 5 + [C.c_int32]
     lib.gt_debug_set_trace.argtypes = [C.c_void_p, C.c_void_p]
     lib.gt_debug_wait_selftest.argtypes = [C.c_void_p, C.c_int64]
     lib.gt_profile_enable.argtypes = [C.c_void_p, C.c_int]
@@ -299,6 +302,13 @@ class Engine:
         _check(self.lib.gt_grads_scale_clip(self.h, _ptr(g_dev)[0], g_dev.numel(), pre_scale, max_norm, C.byref(norm)))
         return norm.value
 
+    def adamw_step(self, p_dev, g_dev, m_dev, v_dev, lr, beta1, beta2, eps, weight_decay, step: int):
+        """One AdamW step in place on flat fp32 device tensors (queued on the engine stream)."""
+        n = p_dev.numel()
+        assert g_dev.numel() == n and m_dev.numel() == n and v_dev.numel() == n
+        _check(self.lib.gt_adamw_step(self.h, _ptr(p_dev)[0], _ptr(g_dev)[0], _ptr(m_dev)[0], _ptr(v_dev)[0], n, lr, beta1, beta2, eps,
+                                      weight_decay, step))
+
     def wait_selftest(self, limit_cycles: int = 2_000_000):
         _check(self.lib.gt_debug_wait_selftest(self.h, limit_cycles))
 
@@ -374,6 +384,10 @@ class Adapter:
 
     def set_alpha(self, alpha: float):
         _check(self.eng.lib.gt_adapter_set_alpha(self.h, alpha))
+
+    def adamw_step(self, lr, beta1, beta2, eps, weight_decay, step: int):
+        """A, B <- AdamW(A, B; dA, dB) on the device; the moments live in the adapter."""
+        _check(self.eng.lib.gt_adapter_adamw_step(self.h, lr, beta1, beta2, eps, weight_decay, step))
 
     def bind_grads(self, dA_dev, dB_dev):
         _check(self.eng.lib.gt_adapter_bind_grads(self.h, _ptr(dA_dev)[0], _ptr(dB_dev)[0]))

@@ -126,6 +126,7 @@ struct gt_adapter {
     bool dlow_clean = false;     // dLow is still all zero (cleared together with low, not yet summed into)
     Scratch xkeep;               // host-buffer calls: device copy of the X of the last forward, for a backward that
     int xkeep_T = 0;             // reuses it (GT_FLAG_REUSE_LOW) instead of uploading X again
+    Scratch moments;             // AdamW state [mA | vA | mB | vB], allocated and zeroed by the first optimizer step
 };
 
 namespace {
@@ -973,6 +974,7 @@ int gt_adapter_free(gt_adapter *a) {
     if (a->b_nonzero) cudaFree(a->b_nonzero);
     a->low.release();
     a->xkeep.release();
+    a->moments.release();
     delete a;
     return GT_OK;
 }
@@ -1020,6 +1022,28 @@ int gt_adapter_grads_zero(gt_adapter *a) {
     GT_CUDA(cudaSetDevice(e->device));
     GT_CUDA(cudaMemsetAsync(a->dA, 0, (size_t)a->in * a->rank * sizeof(float), e->stream));
     GT_CUDA(cudaMemsetAsync(a->dB, 0, (size_t)a->rank * a->out * sizeof(float), e->stream));
+    return GT_OK;
+}
+
+int gt_adapter_adamw_step(gt_adapter *a, float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    if (step < 1) return fail(GT_ERR_INVALID, "gt_adapter_adamw_step: step counts from 1 (got %d)", step);
+    if (!(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f))
+        return fail(GT_ERR_INVALID, "gt_adapter_adamw_step: beta1 and beta2 must lie in [0, 1)");
+    gt_engine *e = a->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    const int64_t na = (int64_t)a->in * a->rank, nb = (int64_t)a->rank * a->out;
+    const int64_t na_pad = (na + 3) & ~(int64_t)3, nb_pad = (nb + 3) & ~(int64_t)3;      // keeps every segment 16-byte aligned
+    if (!a->moments.p) {
+        const size_t bytes = (size_t)(2 * na_pad + 2 * nb_pad) * sizeof(float);
+        GT_CUDA(a->moments.reserve(bytes));
+        GT_CUDA(cudaMemsetAsync(a->moments.p, 0, bytes, e->stream));
+    }
+    float *mA = static_cast<float *>(a->moments.p), *vA = mA + na_pad, *mB = vA + na_pad, *vB = mB + nb_pad;
+    gt::AdamwSeg sa{a->A, a->dA, mA, vA, na, 0}, sb{a->B, a->dB, mB, vB, nb, 0};
+    GT_CUDA(gt::launch_adamw(sa, sb, lr, beta1, beta2, eps, weight_decay, (int)step, e->sm_count, e->stream));
+    GT_CUDA(launch_any_nonzero(a->B, nb, a->b_nonzero, e->stream));      // B has changed: refresh the "B == 0" shortcut flag
     return GT_OK;
 }
 

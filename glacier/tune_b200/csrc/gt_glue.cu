@@ -6,8 +6,11 @@
 //   RMSNorm  ElementwiseKernels.RMSNorm / RMSNormBackward of Glacier.Tensor 1.1.0 (not in the repository; call sites
 //            src/Glacier.Tune/Model/TransformerBlock.cs:318,524,672,827, frozen weight: dW is never asked for)
 //   add      TensorOps.Add (residual connections, src/Glacier.Tune/Model/TransformerBlock.cs:675)
+//   AdamW    the optimizer step on the adapter matrices (AdamW of Glacier.Tensor 1.1.0, not in the repository; built
+//            and stepped in src/Glacier.Tune/Trainer/LoraTrainer.cs:56-62,230): textbook decoupled weight decay
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdio>
 #include <mutex>
 
@@ -45,6 +48,43 @@ __global__ void __launch_bounds__(256) k_swiglu_fwd(const float *__restrict__ ga
     for (int64_t i = done + tid; i < n; i += nth) {
         const float g = gate[i];
         hidden[i] = g * sigmoidf_(g) * up[i];
+    }
+}
+
+// AdamW over up to two flat segments (an adapter's A and B) in one launch: 16 B of parameter, gradient and both
+// moments read and 12 B written per element, nothing else.  c1 = 1/(1-beta1^t), c2 = 1/(1-beta2^t), decay = 1-lr*wd.
+struct AdamwHyper {
+    float lr, beta1, beta2, eps, decay, c1, c2;
+};
+__device__ __forceinline__ void adamw1(float &p, float g, float &m, float &v, const AdamwHyper &h) {
+    m = h.beta1 * m + (1.0f - h.beta1) * g;
+    v = h.beta2 * v + (1.0f - h.beta2) * g * g;
+    p = p * h.decay - h.lr * (m * h.c1) / (sqrtf(v * h.c2) + h.eps);
+}
+__global__ void __launch_bounds__(256) k_adamw(gt::AdamwSeg s0, gt::AdamwSeg s1, AdamwHyper h) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+#pragma unroll
+    for (int si = 0; si < 2; si++) {
+        const gt::AdamwSeg s = si == 0 ? s0 : s1;
+        int64_t done = 0;
+        if (s.vec) {
+            const int64_t n4 = s.n >> 2;
+            for (int64_t i = tid; i < n4; i += nth) {
+                float4 p = reinterpret_cast<float4 *>(s.p)[i], m = reinterpret_cast<float4 *>(s.m)[i], v = reinterpret_cast<float4 *>(s.v)[i];
+                const float4 g = __ldg(reinterpret_cast<const float4 *>(s.g) + i);
+                adamw1(p.x, g.x, m.x, v.x, h);
+                adamw1(p.y, g.y, m.y, v.y, h);
+                adamw1(p.z, g.z, m.z, v.z, h);
+                adamw1(p.w, g.w, m.w, v.w, h);
+                reinterpret_cast<float4 *>(s.p)[i] = p;
+                reinterpret_cast<float4 *>(s.m)[i] = m;
+                reinterpret_cast<float4 *>(s.v)[i] = v;
+            }
+            done = n4 << 2;
+        }
+        for (int64_t i = done + tid; i < s.n; i += nth) adamw1(s.p[i], s.g[i], s.m[i], s.v[i], h);
     }
 }
 
@@ -229,6 +269,19 @@ cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const fl
     const int vec = aligned16(d_hidden) && aligned16(gate) && aligned16(up) && aligned16(d_gate) && aligned16(d_up) ? 1 : 0;
     return launch_k(k_swiglu_bwd, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, d_hidden, gate, up, d_gate, d_up, n, vec);
 }
+cudaError_t launch_adamw(AdamwSeg s0, AdamwSeg s1, float lr, float beta1, float beta2, float eps, float weight_decay, int step, int sm_count,
+                         cudaStream_t s) {
+    if (s0.n <= 0 && s1.n <= 0) return cudaSuccess;
+    AdamwHyper h;
+    h.lr = lr, h.beta1 = beta1, h.beta2 = beta2, h.eps = eps;
+    h.decay = 1.0f - lr * weight_decay;
+    h.c1 = (float)(1.0 / (1.0 - pow((double)beta1, (double)step)));
+    h.c2 = (float)(1.0 / (1.0 - pow((double)beta2, (double)step)));
+    AdamwSeg *segs[2] = {&s0, &s1};
+    for (AdamwSeg *g : segs) g->vec = g->n > 0 && aligned16(g->p) && aligned16(g->g) && aligned16(g->m) && aligned16(g->v) ? 1 : 0;
+    const int64_t n = (s0.n > s1.n ? s0.n : s1.n);
+    return launch_k(k_adamw, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, s0, s1, h);
+}
 }  // namespace gt
 
 extern "C" int gt_swiglu_forward(gt_engine *eng, const float *gate, const float *up, float *hidden, int64_t n) {
@@ -305,4 +358,19 @@ extern "C" int gt_rmsnorm_backward(gt_engine *eng, const float *dy, const float 
     cudaError_t ce = cudaSetDevice(ev.device);
     if (ce == cudaSuccess) ce = gt::launch_k(k_rmsnorm_bwd, dim3((unsigned)T), dim3(256), (size_t)0, ev.stream, dy, x, w, dx, (int)H, eps);
     return ce == cudaSuccess ? GT_OK : cuda_fail("gt_rmsnorm_backward", ce);
+}
+
+extern "C" int gt_adamw_step(gt_engine *eng, float *p, const float *g, float *m, float *v, int64_t n, float lr, float beta1, float beta2,
+                             float eps, float weight_decay, int32_t step) {
+    if (!eng || !p || !g || !m || !v) return gt::set_last_error(GT_ERR_INVALID, "gt_adamw_step: null argument");
+    if (step < 1) return gt::set_last_error(GT_ERR_INVALID, "gt_adamw_step: step counts from 1");
+    if (!(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f))
+        return gt::set_last_error(GT_ERR_INVALID, "gt_adamw_step: beta1 and beta2 must lie in [0, 1)");
+    if (n <= 0) return GT_OK;
+    const gt::EngineView ev = gt::engine_view(eng);
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
+    cudaError_t ce = cudaSetDevice(ev.device);
+    gt::AdamwSeg s0{p, g, m, v, n, 0}, s1{nullptr, nullptr, nullptr, nullptr, 0, 0};
+    if (ce == cudaSuccess) ce = gt::launch_adamw(s0, s1, lr, beta1, beta2, eps, weight_decay, (int)step, ev.sm_count, ev.stream);
+    return ce == cudaSuccess ? GT_OK : cuda_fail("gt_adamw_step", ce);
 }

@@ -140,6 +140,16 @@ cudaError_t launch_stream_fwd(const WeightDev *w, const float *X, float *Y_prefi
 
 // ---- layer glue launchers used inside the library (gt_glue.cu)
 cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden, int64_t n, int sm_count, cudaStream_t s);
+// one flat segment of an AdamW launch: parameters, gradients and both moments, n elements (vec is set by the launcher)
+struct AdamwSeg {
+    float *p;
+    const float *g;
+    float *m, *v;
+    int64_t n;
+    int vec;
+};
+cudaError_t launch_adamw(AdamwSeg s0, AdamwSeg s1, float lr, float beta1, float beta2, float eps, float weight_decay, int step, int sm_count,
+                         cudaStream_t s);
 cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,
                               cudaStream_t s);
 

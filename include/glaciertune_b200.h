@@ -240,6 +240,19 @@ GT_API int gt_launch_gemm_bwd_static(gt_engine *eng, const gt_weight *w, float *
 GT_API int gt_grads_scale_clip(gt_engine *eng, float *g_dev, int64_t n, float pre_scale, double max_norm,
                                double *norm_out);
 
+/* Replaces: the optimizer step of the trainer - `new AdamW(params, lr, beta1, beta2, eps, weightDecay)`, `.Step()`
+ * (src/Glacier.Tune/Trainer/LoraTrainer.cs:56-62,230; AdamW itself is in Glacier.Tensor 1.1.0, not in the
+ * repository: textbook decoupled weight decay, parity unpinned against the reference, pinned against
+ * torch.optim.AdamW by the tests).  `step` counts from 1 and selects the bias corrections:
+ *   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  p *= 1 - lr wd;  p -= lr (m/(1-b1^t)) / (sqrt(v/(1-b2^t)) + eps)
+ * gt_adamw_step works on flat device buffers (p, m, v updated in place; m and v start as zeros).
+ * gt_adapter_adamw_step updates an adapter's A and B from its gradient accumulators (wherever they are bound) in one
+ * launch and keeps both moments inside the adapter (zero before its first step); the learning-rate schedule stays
+ * with the caller.  Both are asynchronous on the engine stream. */
+GT_API int gt_adamw_step(gt_engine *eng, float *p_dev, const float *g_dev, float *m_dev, float *v_dev, int64_t n, float lr, float beta1,
+                         float beta2, float eps, float weight_decay, int32_t step);
+GT_API int gt_adapter_adamw_step(gt_adapter *ad, float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step);
+
 /* Profiling (the reference only has Stopwatch breakdowns at Debug level,
  * src/Glacier.Tune/Model/TransformerBlock.cs:311-312,582-586).  While enabled, every tensor-core GEMM launch is
  * bracketed by CUDA events on the engine stream.  gt_profile_read synchronises and returns the summed GEMM time,

@@ -701,3 +701,26 @@ void gt_oracle_rmsnorm_backward(const float *dy, const float *x, const float *w,
         for (int i = 0; i < H; i++) dx[(int64_t)t * H + i] = (float)(r * (double)gr[i] * (double)w[i] - (double)xr[i] * coef);
     }
 }
+
+/* AdamW step with decoupled weight decay on a flat parameter buffer; `step` counts from 1.
+ * The reference takes the optimizer from Glacier.Tensor 1.1.0 (`new AdamW(params, lr, beta1, beta2, eps, weightDecay)`,
+ * `.Step()`, src/Glacier.Tune/Trainer/LoraTrainer.cs:56-62,230), whose source is not in the repository: this is the
+ * textbook rule (Loshchilov & Hutter), PARITY UNPINNED against the reference, pinned against torch.optim.AdamW by
+ * the CPU tests:
+ *   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  p *= 1 - lr wd;  p -= lr (m / (1-b1^t)) / (sqrt(v / (1-b2^t)) + eps)
+ * Moments and parameters are fp32; the two bias corrections are evaluated in fp64 once per step. */
+void gt_oracle_adamw_step(float *p, const float *g, float *m, float *v, int64_t n, float lr, float beta1, float beta2,
+                          float eps, float weight_decay, int step) {
+    const float c1 = (float)(1.0 / (1.0 - pow((double)beta1, (double)step)));
+    const float c2 = (float)(1.0 / (1.0 - pow((double)beta2, (double)step)));
+    const float decay = 1.0f - lr * weight_decay;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        const float gi = g[i];
+        const float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+        const float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        p[i] = p[i] * decay - lr * (mi * c1) / (sqrtf(vi * c2) + eps);
+    }
+}

@@ -269,3 +269,13 @@ def rmsnorm_backward(dy, x, w, eps=1e-6) -> np.ndarray:
     dx = np.empty_like(x)
     lib().gt_oracle_rmsnorm_backward(_p(dy), _p(x), _p(w), _p(dx), x.shape[0], x.shape[1], C.c_float(eps))
     return dx
+
+
+def adamw_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step):
+    """One AdamW step in place on the fp32 arrays p, m, v (gradient g); step counts from 1."""
+    for a in (p, m, v):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    g = _f32(g)
+    lib().gt_oracle_adamw_step(_p(p), _p(g), _p(m), _p(v), C.c_int64(p.size), C.c_float(lr), C.c_float(beta1),
+                               C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay), C.c_int(step))
+
