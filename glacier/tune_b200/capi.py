@@ -25,7 +25,7 @@ EXPORTS = [
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
     "gt_rmsnorm_backward", "gt_add",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
-    "gt_adamw_step", "gt_adapter_adamw_step",
+    "gt_adamw_step", "gt_adapter_adamw_step", "gt_adapters_adamw_step",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
 ]
 
@@ -96,6 +96,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_grads_scale_clip.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_double, C.POINTER(C.c_double)]
     lib.gt_adamw_step.argtypes = [C.c_void_p] + [C.c_void_p] * 4 + [C.c_int64] + [C.c_float] * 5 + [C.c_int32]
     lib.gt_adapter_adamw_step.argtypes = [C.c_void_p] + [C.c_float] * 5 + [C.c_int32]
+    lib.gt_adapters_adamw_step.argtypes = [C.c_void_p, C.c_int32, C.c_void_p] + [C.c_float] * 5 + [C.c_int32]
     lib.gt_debug_set_trace.argtypes = [C.c_void_p, C.c_void_p]
     lib.gt_debug_wait_selftest.argtypes = [C.c_void_p, C.c_int64]
     lib.gt_profile_enable.argtypes = [C.c_void_p, C.c_int]
@@ -308,6 +309,10 @@ class Engine:
         assert g_dev.numel() == n and m_dev.numel() == n and v_dev.numel() == n
         _check(self.lib.gt_adamw_step(self.h, _ptr(p_dev)[0], _ptr(g_dev)[0], _ptr(m_dev)[0], _ptr(v_dev)[0], n, lr, beta1, beta2, eps,
                                       weight_decay, step))
+
+    def adapters_adamw_step(self, adapters, lr, beta1, beta2, eps, weight_decay, step: int):
+        """AdamW on the A and B of every adapter in the list, eight adapters per launch."""
+        _check(self.lib.gt_adapters_adamw_step(self.h, len(adapters), self._ptr_array(adapters), lr, beta1, beta2, eps, weight_decay, step))
 
     def wait_selftest(self, limit_cycles: int = 2_000_000):
         _check(self.lib.gt_debug_wait_selftest(self.h, limit_cycles))

@@ -1025,26 +1025,41 @@ int gt_adapter_grads_zero(gt_adapter *a) {
     return GT_OK;
 }
 
-int gt_adapter_adamw_step(gt_adapter *a, float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step) {
-    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
-    if (step < 1) return fail(GT_ERR_INVALID, "gt_adapter_adamw_step: step counts from 1 (got %d)", step);
+int gt_adapters_adamw_step(gt_engine *e, int32_t n, gt_adapter *const *ads, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, int32_t step) {
+    if (!e || (n > 0 && !ads)) return fail(GT_ERR_INVALID, "gt_adapters_adamw_step: null argument");
+    if (step < 1) return fail(GT_ERR_INVALID, "gt_adapters_adamw_step: step counts from 1 (got %d)", step);
     if (!(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f))
-        return fail(GT_ERR_INVALID, "gt_adapter_adamw_step: beta1 and beta2 must lie in [0, 1)");
-    gt_engine *e = a->eng;
+        return fail(GT_ERR_INVALID, "gt_adapters_adamw_step: beta1 and beta2 must lie in [0, 1)");
+    for (int i = 0; i < n; i++) {
+        if (!ads[i]) return fail(GT_ERR_INVALID, "gt_adapters_adamw_step: adapter %d is null", i);
+        if (ads[i]->eng != e) return fail(GT_ERR_INVALID, "gt_adapters_adamw_step: adapter %d belongs to another engine", i);
+    }
+    if (n <= 0) return GT_OK;
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
-    const int64_t na = (int64_t)a->in * a->rank, nb = (int64_t)a->rank * a->out;
-    const int64_t na_pad = (na + 3) & ~(int64_t)3, nb_pad = (nb + 3) & ~(int64_t)3;      // keeps every segment 16-byte aligned
-    if (!a->moments.p) {
-        const size_t bytes = (size_t)(2 * na_pad + 2 * nb_pad) * sizeof(float);
-        GT_CUDA(a->moments.reserve(bytes));
-        GT_CUDA(cudaMemsetAsync(a->moments.p, 0, bytes, e->stream));
+    std::vector<gt::AdamwSeg> segs;
+    segs.reserve((size_t)2 * n);
+    for (int i = 0; i < n; i++) {
+        gt_adapter *a = ads[i];
+        const int64_t na = (int64_t)a->in * a->rank, nb = (int64_t)a->rank * a->out;
+        const int64_t na_pad = (na + 3) & ~(int64_t)3, nb_pad = (nb + 3) & ~(int64_t)3;      // keeps every segment 16-byte aligned
+        if (!a->moments.p) {
+            const size_t bytes = (size_t)(2 * na_pad + 2 * nb_pad) * sizeof(float);
+            GT_CUDA(a->moments.reserve(bytes));
+            GT_CUDA(cudaMemsetAsync(a->moments.p, 0, bytes, e->stream));
+        }
+        float *mA = static_cast<float *>(a->moments.p), *vA = mA + na_pad, *mB = vA + na_pad, *vB = mB + nb_pad;
+        segs.push_back(gt::AdamwSeg{a->A, a->dA, mA, vA, nullptr, na, 0});
+        segs.push_back(gt::AdamwSeg{a->B, a->dB, mB, vB, a->b_nonzero, nb, 0});     // B may leave zero: raise the delta's flag
     }
-    float *mA = static_cast<float *>(a->moments.p), *vA = mA + na_pad, *mB = vA + na_pad, *vB = mB + nb_pad;
-    gt::AdamwSeg sa{a->A, a->dA, mA, vA, na, 0}, sb{a->B, a->dB, mB, vB, nb, 0};
-    GT_CUDA(gt::launch_adamw(sa, sb, lr, beta1, beta2, eps, weight_decay, (int)step, e->sm_count, e->stream));
-    GT_CUDA(launch_any_nonzero(a->B, nb, a->b_nonzero, e->stream));      // B has changed: refresh the "B == 0" shortcut flag
+    GT_CUDA(gt::launch_adamw(segs.data(), (int)segs.size(), lr, beta1, beta2, eps, weight_decay, (int)step, e->sm_count, e->stream));
     return GT_OK;
+}
+
+int gt_adapter_adamw_step(gt_adapter *a, float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    return gt_adapters_adamw_step(a->eng, 1, &a, lr, beta1, beta2, eps, weight_decay, step);
 }
 
 int gt_adapter_set_alpha(gt_adapter *a, float alpha) {

@@ -51,24 +51,31 @@ __global__ void __launch_bounds__(256) k_swiglu_fwd(const float *__restrict__ ga
     }
 }
 
-// AdamW over up to two flat segments (an adapter's A and B) in one launch: 16 B of parameter, gradient and both
-// moments read and 12 B written per element, nothing else.  c1 = 1/(1-beta1^t), c2 = 1/(1-beta2^t), decay = 1-lr*wd.
+// AdamW over up to kAdamwSegs flat segments (the A and B of several adapters) in one launch: 16 B of parameter,
+// gradient and both moments read and 12 B written per element, nothing else.  c1 = 1/(1-beta1^t), c2 = 1/(1-beta2^t),
+// decay = 1-lr*wd.  A segment with a flag pointer raises the flag when it leaves a non-zero parameter behind (the
+// adapter's "B may be non-zero" word; it is never lowered here: a B that an update returned to exactly zero would
+// only cost the delta's arithmetic, not change a result).
 struct AdamwHyper {
     float lr, beta1, beta2, eps, decay, c1, c2;
+};
+struct AdamwBatch {
+    gt::AdamwSeg seg[gt::kAdamwSegs];
+    int n;
 };
 __device__ __forceinline__ void adamw1(float &p, float g, float &m, float &v, const AdamwHyper &h) {
     m = h.beta1 * m + (1.0f - h.beta1) * g;
     v = h.beta2 * v + (1.0f - h.beta2) * g * g;
     p = p * h.decay - h.lr * (m * h.c1) / (sqrtf(v * h.c2) + h.eps);
 }
-__global__ void __launch_bounds__(256) k_adamw(gt::AdamwSeg s0, gt::AdamwSeg s1, AdamwHyper h) {
+__global__ void __launch_bounds__(256) k_adamw(const __grid_constant__ AdamwBatch b, AdamwHyper h) {
     pdl_wait();
     pdl_trigger();
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
-#pragma unroll
-    for (int si = 0; si < 2; si++) {
-        const gt::AdamwSeg s = si == 0 ? s0 : s1;
+    for (int si = 0; si < b.n; si++) {
+        const gt::AdamwSeg &s = b.seg[si];
         int64_t done = 0;
+        bool nz = false;
         if (s.vec) {
             const int64_t n4 = s.n >> 2;
             for (int64_t i = tid; i < n4; i += nth) {
@@ -78,13 +85,18 @@ __global__ void __launch_bounds__(256) k_adamw(gt::AdamwSeg s0, gt::AdamwSeg s1,
                 adamw1(p.y, g.y, m.y, v.y, h);
                 adamw1(p.z, g.z, m.z, v.z, h);
                 adamw1(p.w, g.w, m.w, v.w, h);
+                nz |= p.x != 0.f || p.y != 0.f || p.z != 0.f || p.w != 0.f;
                 reinterpret_cast<float4 *>(s.p)[i] = p;
                 reinterpret_cast<float4 *>(s.m)[i] = m;
                 reinterpret_cast<float4 *>(s.v)[i] = v;
             }
             done = n4 << 2;
         }
-        for (int64_t i = done + tid; i < s.n; i += nth) adamw1(s.p[i], s.g[i], s.m[i], s.v[i], h);
+        for (int64_t i = done + tid; i < s.n; i += nth) {
+            adamw1(s.p[i], s.g[i], s.m[i], s.v[i], h);
+            nz |= s.p[i] != 0.f;
+        }
+        if (s.flag != nullptr && nz) *s.flag = 1;      // every writer stores the same value
     }
 }
 
@@ -269,18 +281,29 @@ cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const fl
     const int vec = aligned16(d_hidden) && aligned16(gate) && aligned16(up) && aligned16(d_gate) && aligned16(d_up) ? 1 : 0;
     return launch_k(k_swiglu_bwd, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, d_hidden, gate, up, d_gate, d_up, n, vec);
 }
-cudaError_t launch_adamw(AdamwSeg s0, AdamwSeg s1, float lr, float beta1, float beta2, float eps, float weight_decay, int step, int sm_count,
-                         cudaStream_t s) {
-    if (s0.n <= 0 && s1.n <= 0) return cudaSuccess;
+cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                         int sm_count, cudaStream_t s) {
     AdamwHyper h;
     h.lr = lr, h.beta1 = beta1, h.beta2 = beta2, h.eps = eps;
     h.decay = 1.0f - lr * weight_decay;
     h.c1 = (float)(1.0 / (1.0 - pow((double)beta1, (double)step)));
     h.c2 = (float)(1.0 / (1.0 - pow((double)beta2, (double)step)));
-    AdamwSeg *segs[2] = {&s0, &s1};
-    for (AdamwSeg *g : segs) g->vec = g->n > 0 && aligned16(g->p) && aligned16(g->g) && aligned16(g->m) && aligned16(g->v) ? 1 : 0;
-    const int64_t n = (s0.n > s1.n ? s0.n : s1.n);
-    return launch_k(k_adamw, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, s0, s1, h);
+    for (int i0 = 0; i0 < n; i0 += kAdamwSegs) {
+        AdamwBatch b;
+        b.n = 0;
+        int64_t longest = 0;
+        for (int i = i0; i < n && i < i0 + kAdamwSegs; i++) {
+            if (segs[i].n <= 0) continue;
+            AdamwSeg &g = b.seg[b.n++];
+            g = segs[i];
+            g.vec = aligned16(g.p) && aligned16(g.g) && aligned16(g.m) && aligned16(g.v) ? 1 : 0;
+            longest = g.n > longest ? g.n : longest;
+        }
+        if (b.n == 0) continue;
+        const cudaError_t ce = launch_k(k_adamw, dim3(stream_blocks(longest, sm_count)), dim3(256), (size_t)0, s, b, h);
+        if (ce != cudaSuccess) return ce;
+    }
+    return cudaSuccess;
 }
 }  // namespace gt
 
@@ -370,7 +393,7 @@ extern "C" int gt_adamw_step(gt_engine *eng, float *p, const float *g, float *m,
     const gt::EngineView ev = gt::engine_view(eng);
     std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
     cudaError_t ce = cudaSetDevice(ev.device);
-    gt::AdamwSeg s0{p, g, m, v, n, 0}, s1{nullptr, nullptr, nullptr, nullptr, 0, 0};
-    if (ce == cudaSuccess) ce = gt::launch_adamw(s0, s1, lr, beta1, beta2, eps, weight_decay, (int)step, ev.sm_count, ev.stream);
+    const gt::AdamwSeg seg{p, g, m, v, nullptr, n, 0};
+    if (ce == cudaSuccess) ce = gt::launch_adamw(&seg, 1, lr, beta1, beta2, eps, weight_decay, (int)step, ev.sm_count, ev.stream);
     return ce == cudaSuccess ? GT_OK : cuda_fail("gt_adamw_step", ce);
 }

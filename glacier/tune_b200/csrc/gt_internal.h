@@ -140,16 +140,19 @@ cudaError_t launch_stream_fwd(const WeightDev *w, const float *X, float *Y_prefi
 
 // ---- layer glue launchers used inside the library (gt_glue.cu)
 cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden, int64_t n, int sm_count, cudaStream_t s);
-// one flat segment of an AdamW launch: parameters, gradients and both moments, n elements (vec is set by the launcher)
+// one flat segment of an AdamW launch: parameters, gradients and both moments, n elements; flag (optional) is set to 1
+// when a parameter of the segment is non-zero after the step (vec is filled in by the launcher)
 struct AdamwSeg {
     float *p;
     const float *g;
     float *m, *v;
+    int *flag;
     int64_t n;
     int vec;
 };
-cudaError_t launch_adamw(AdamwSeg s0, AdamwSeg s1, float lr, float beta1, float beta2, float eps, float weight_decay, int step, int sm_count,
-                         cudaStream_t s);
+constexpr int kAdamwSegs = 16;      // segments per launch (8 adapters)
+cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                         int sm_count, cudaStream_t s);
 cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,
                               cudaStream_t s);
 

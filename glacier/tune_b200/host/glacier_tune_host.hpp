@@ -110,6 +110,11 @@ public:
     void GetParameters(float *A, float *B) { Check(gt_adapter_download(ad_, A, B), "gt_adapter_download"); }
     void GetGradients(float *dA, float *dB) { Check(gt_adapter_grads_download(ad_, dA, dB), "gt_adapter_grads_download"); }
     void ZeroGrad() { Check(gt_adapter_grads_zero(ad_), "gt_adapter_grads_zero"); }
+    // The trainer's optimizer step on this adapter's A and B (AdamW.Step, LoraTrainer.cs:230), on the device;
+    // step counts the optimizer steps taken so far, starting at 1.
+    void OptimizerStep(float lr, float beta1, float beta2, float eps, float weightDecay, int step) {
+        Check(gt_adapter_adamw_step(ad_, lr, beta1, beta2, eps, weightDecay, step), "gt_adapter_adamw_step");
+    }
 
     // LoraAdapter.cs:128-184: output = x W^T + bias + scaling (x A) B (delta skipped while B == 0).
     void Forward(GgufType, const Tensor &x, Tensor &output, int seqLen) {

@@ -132,3 +132,53 @@ def test_gpu_adapter_trains_on_device(eng, oracle):
             assert np.count_nonzero(B_dev) > 0.9 * B.size                          # the delta is switched on
     w.free()
     ad.free()
+
+
+@pytest.mark.gpu
+def test_gpu_many_adapters_in_one_call(eng, oracle):
+    """gt_adapters_adamw_step over 19 adapters of mixed shapes (three launches of eight) leaves every A, B bit-identical
+    to 19 single-adapter calls and equal to the CPU restatement to rounding."""
+    import torch
+    rng = np.random.default_rng(9)
+    shapes = [(64 + 8 * i, 40 + 4 * i, (8, 16, 5)[i % 3]) for i in range(19)]           # (in, out, rank); rank 5: odd sizes
+    h = dict(lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+    sets, grads, cpu = [], [], []
+    for which in range(2):
+        ads, gs = [], []
+        for K, N, R in shapes:
+            ad = eng.create_adapter(K, N, R, 2.0 * R)
+            A0 = np.random.default_rng(K).standard_normal((K, R)).astype(np.float32)
+            ad.upload(A0, np.zeros((R, N), np.float32))
+            g = (torch.zeros(K * R, device="cuda"), torch.zeros(R * N, device="cuda"))
+            ad.bind_grads(*g)                                                          # gradients live in tensors of the test
+            ads.append(ad)
+            gs.append(g)
+            if which == 0:
+                cpu.append([A0.copy(), np.zeros((R, N), np.float32)] + [np.zeros((K, R), np.float32), np.zeros((K, R), np.float32),
+                                                                          np.zeros((R, N), np.float32), np.zeros((R, N), np.float32)])
+        sets.append(ads)
+        grads.append(gs)
+    for step in (1, 2, 3):
+        for i, (K, N, R) in enumerate(shapes):
+            ga, gb = rng.standard_normal((K, R)).astype(np.float32), rng.standard_normal((R, N)).astype(np.float32)
+            for gs in grads:
+                gs[i][0].copy_(torch.from_numpy(ga.reshape(-1)))
+                gs[i][1].copy_(torch.from_numpy(gb.reshape(-1)))
+            A, B, mA, vA, mB, vB = cpu[i]
+            oracle.adamw_step(A, ga, mA, vA, step=step, **h)
+            oracle.adamw_step(B, gb, mB, vB, step=step, **h)
+        torch.cuda.synchronize()
+        eng.adapters_adamw_step(sets[0], step=step, **h)
+        for ad in sets[1]:
+            ad.adamw_step(step=step, **h)
+        eng.sync()
+    for i, (a0, a1) in enumerate(zip(*sets)):
+        A0, B0 = a0.download()
+        A1, B1 = a1.download()
+        assert np.array_equal(A0, A1) and np.array_equal(B0, B1)
+        assert oracle.rel_fro(A0, cpu[i][0]) < 1e-6 and oracle.rel_fro(B0, cpu[i][1]) < 1e-5
+    for ads in sets:
+        for ad in ads:
+            ad.free()
+    with pytest.raises(Exception):
+        eng.adapters_adamw_step([None], step=1, **h)
