@@ -311,7 +311,7 @@ class Engine:
                                       weight_decay, step))
 
     def adapters_adamw_step(self, adapters, lr, beta1, beta2, eps, weight_decay, step: int):
-        """AdamW on the A and B of every adapter in the list, eight adapters per launch."""
+        """AdamW on the A and B of every adapter in the list, sixteen adapters per launch."""
         _check(self.lib.gt_adapters_adamw_step(self.h, len(adapters), self._ptr_array(adapters), lr, beta1, beta2, eps, weight_decay, step))
 
     def wait_selftest(self, limit_cycles: int = 2_000_000):

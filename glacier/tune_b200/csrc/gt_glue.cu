@@ -61,6 +61,7 @@ struct AdamwHyper {
 };
 struct AdamwBatch {
     gt::AdamwSeg seg[gt::kAdamwSegs];
+    int64_t start[gt::kAdamwSegs + 1];      // prefix sum of the segments' work units: a float4 (vec) or one element
     int n;
 };
 __device__ __forceinline__ void adamw1(float &p, float g, float &m, float &v, const AdamwHyper &h) {
@@ -68,35 +69,51 @@ __device__ __forceinline__ void adamw1(float &p, float g, float &m, float &v, co
     v = h.beta2 * v + (1.0f - h.beta2) * g * g;
     p = p * h.decay - h.lr * (m * h.c1) / (sqrtf(v * h.c2) + h.eps);
 }
+// One grid-stride loop over the units of ALL segments (not one loop per segment: the segments of an adapter are a
+// few hundred KB each, and sixteen dependent rounds of DRAM latency would bound the launch).
 __global__ void __launch_bounds__(256) k_adamw(const __grid_constant__ AdamwBatch b, AdamwHyper h) {
     pdl_wait();
     pdl_trigger();
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
-    for (int si = 0; si < b.n; si++) {
+    const int64_t total = b.start[b.n];
+    const int lane = threadIdx.x & 31;
+    for (int64_t u = tid; u < total; u += nth) {
+        int si = 0;
+        while (si + 1 < b.n && u >= b.start[si + 1]) si++;
         const gt::AdamwSeg &s = b.seg[si];
-        int64_t done = 0;
-        bool nz = false;
+        const int64_t i = u - b.start[si];
+        bool nz;
         if (s.vec) {
-            const int64_t n4 = s.n >> 2;
-            for (int64_t i = tid; i < n4; i += nth) {
-                float4 p = reinterpret_cast<float4 *>(s.p)[i], m = reinterpret_cast<float4 *>(s.m)[i], v = reinterpret_cast<float4 *>(s.v)[i];
-                const float4 g = __ldg(reinterpret_cast<const float4 *>(s.g) + i);
-                adamw1(p.x, g.x, m.x, v.x, h);
-                adamw1(p.y, g.y, m.y, v.y, h);
-                adamw1(p.z, g.z, m.z, v.z, h);
-                adamw1(p.w, g.w, m.w, v.w, h);
-                nz |= p.x != 0.f || p.y != 0.f || p.z != 0.f || p.w != 0.f;
-                reinterpret_cast<float4 *>(s.p)[i] = p;
-                reinterpret_cast<float4 *>(s.m)[i] = m;
-                reinterpret_cast<float4 *>(s.v)[i] = v;
-            }
-            done = n4 << 2;
-        }
-        for (int64_t i = done + tid; i < s.n; i += nth) {
+            float4 p = reinterpret_cast<float4 *>(s.p)[i], m = reinterpret_cast<float4 *>(s.m)[i], v = reinterpret_cast<float4 *>(s.v)[i];
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(s.g) + i);
+            adamw1(p.x, g.x, m.x, v.x, h);
+            adamw1(p.y, g.y, m.y, v.y, h);
+            adamw1(p.z, g.z, m.z, v.z, h);
+            adamw1(p.w, g.w, m.w, v.w, h);
+            nz = p.x != 0.f || p.y != 0.f || p.z != 0.f || p.w != 0.f;
+            reinterpret_cast<float4 *>(s.p)[i] = p;
+            reinterpret_cast<float4 *>(s.m)[i] = m;
+            reinterpret_cast<float4 *>(s.v)[i] = v;
+        } else {
             adamw1(s.p[i], s.g[i], s.m[i], s.v[i], h);
-            nz |= s.p[i] != 0.f;
+            nz = s.p[i] != 0.f;
         }
-        if (s.flag != nullptr && nz) *s.flag = 1;      // every writer stores the same value
+        // one flag store per warp and segment: the lanes of a warp that are in the same segment vote
+        const unsigned peers = __match_any_sync(__activemask(), si);
+        const bool any = __any_sync(peers, nz);
+        if (any && s.flag != nullptr && lane == __ffs(peers) - 1) *s.flag = 1;
+    }
+    // the last n % 4 elements of the vectorized segments
+    if (blockIdx.x == 0) {
+        for (int si = 0; si < b.n; si++) {
+            const gt::AdamwSeg &s = b.seg[si];
+            const int rem = s.vec ? (int)(s.n & 3) : 0;
+            if ((int)threadIdx.x < rem) {
+                const int64_t i = (s.n & ~(int64_t)3) + threadIdx.x;
+                adamw1(s.p[i], s.g[i], s.m[i], s.v[i], h);
+                if (s.flag != nullptr && s.p[i] != 0.f) *s.flag = 1;
+            }
+        }
     }
 }
 
@@ -291,15 +308,19 @@ cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, flo
     for (int i0 = 0; i0 < n; i0 += kAdamwSegs) {
         AdamwBatch b;
         b.n = 0;
-        int64_t longest = 0;
+        b.start[0] = 0;
         for (int i = i0; i < n && i < i0 + kAdamwSegs; i++) {
             if (segs[i].n <= 0) continue;
-            AdamwSeg &g = b.seg[b.n++];
+            AdamwSeg &g = b.seg[b.n];
             g = segs[i];
             g.vec = aligned16(g.p) && aligned16(g.g) && aligned16(g.m) && aligned16(g.v) ? 1 : 0;
-            longest = g.n > longest ? g.n : longest;
+            b.start[b.n + 1] = b.start[b.n] + (g.vec ? g.n >> 2 : g.n);
+            b.n++;
         }
         if (b.n == 0) continue;
+        for (int i = b.n; i < kAdamwSegs; i++) b.start[i + 1] = b.start[b.n];
+        // units are float4 for aligned segments: size the grid for 4 elements per unit
+        const int64_t longest = b.start[b.n] * 4;
         const cudaError_t ce = launch_k(k_adamw, dim3(stream_blocks(longest, sm_count)), dim3(256), (size_t)0, s, b, h);
         if (ce != cudaSuccess) return ce;
     }

@@ -150,7 +150,7 @@ struct AdamwSeg {
     int64_t n;
     int vec;
 };
-constexpr int kAdamwSegs = 16;      // segments per launch (8 adapters)
+constexpr int kAdamwSegs = 32;      // segments per launch (16 adapters)
 cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
                          int sm_count, cudaStream_t s);
 cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,

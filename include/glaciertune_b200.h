@@ -248,8 +248,8 @@ GT_API int gt_grads_scale_clip(gt_engine *eng, float *g_dev, int64_t n, float pr
  * gt_adamw_step works on flat device buffers (p, m, v updated in place; m and v start as zeros).
  * gt_adapter_adamw_step updates an adapter's A and B from its gradient accumulators (wherever they are bound) in one
  * launch and keeps both moments inside the adapter (zero before its first step); the learning-rate schedule stays
- * with the caller.  gt_adapters_adamw_step does the same for n adapters of one engine, eight adapters per launch
- * (the 196 adapters of a 28-layer model: 25 launches).  All three are asynchronous on the engine stream. */
+ * with the caller.  gt_adapters_adamw_step does the same for n adapters of one engine, sixteen adapters per launch
+ * (the 196 adapters of a 28-layer model: 13 launches).  All three are asynchronous on the engine stream. */
 GT_API int gt_adamw_step(gt_engine *eng, float *p_dev, const float *g_dev, float *m_dev, float *v_dev, int64_t n, float lr, float beta1,
                          float beta2, float eps, float weight_decay, int32_t step);
 GT_API int gt_adapter_adamw_step(gt_adapter *ad, float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step);

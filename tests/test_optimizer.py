@@ -136,7 +136,7 @@ def test_gpu_adapter_trains_on_device(eng, oracle):
 
 @pytest.mark.gpu
 def test_gpu_many_adapters_in_one_call(eng, oracle):
-    """gt_adapters_adamw_step over 19 adapters of mixed shapes (three launches of eight) leaves every A, B bit-identical
+    """gt_adapters_adamw_step over 19 adapters of mixed shapes (two launches: sixteen adapters each at most) leaves every A, B bit-identical
     to 19 single-adapter calls and equal to the CPU restatement to rounding."""
     import torch
     rng = np.random.default_rng(9)
