@@ -34,9 +34,19 @@ PROJ_ORDER = ["q", "k", "v", "o", "gate", "up", "down"]
 METRIC = "q4k_gemm_fwd_dx_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = "qwen2.5-7b layer projections q,k,v,o,gate,up,down in Q4_K, M=512, fwd+dX+LoRA grads (r=16)"
-# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised in
-# profiles/k_umma_gemm_gate_up_group_m512_full.md: the gate,up forward launch, the largest of the step
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, the gate,up forward
+# launch (the largest of the step): a constant taken from one `ncu --set full` capture of that launch, not re-measured
+# by this script.  84.5e6 read (80.1e6 algorithmic: both members' packed weights once + the bf16 activations) and
+# 31.4e6 of the 77.6e6 fp32 output written back before the kernel ended (the rest was still in L2).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 115.9e6
+L2_NOTE = "256 MiB written between timed steps; per-step inputs (131 MB weights + activations) exceed L2"
+GROUPS = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]]
+
+
+def workload_config(n_gpus: int, q4km: bool = False) -> dict:
+    """The `config` object of the JSON line: the same keys and values in the GPU arm and in the reference arm."""
+    return {"workload": WORKLOAD.replace("in Q4_K", "in the Q4_K_M mix (v, down in Q6_K)") if q4km else WORKLOAD,
+            "tokens_per_gpu": M_TOKENS, "rank": RANK, "parallelism": f"dp{n_gpus}", "l2": L2_NOTE}
 
 
 def step_flops(names=PROJ_ORDER, m=M_TOKENS) -> float:
@@ -61,6 +71,45 @@ def cpu_layer_pass(O, cases) -> float:
         O.proj_forward(c["qtype"], c["w"], None, c["x"], c["K"], c["N"], c["T"], c["a"], c["b"], RANK, c["scaling"])
         O.proj_backward(c["qtype"], c["w"], c["dy"], c["x"], c["K"], c["N"], c["T"], c["a"], c["b"], RANK, c["scaling"])
     return time.perf_counter() - t0
+
+
+def parity_against_oracle(O, eng, layer, groups, flat_grads, q4km: bool) -> dict:
+    """After the timed region: the device tensors the last step left behind (every Y, each group's dX, the flat gradient
+    buffer) against the CPU path on the same seeded inputs, plus bit-equality of sampled dequantized weight rows.
+    Relative Frobenius errors, worst over the projections; gate 2e-2 (bf16-MMA mode)."""
+    by_name = {p["name"]: p for p in layer}
+    worst = {"Y": 0.0, "dX": 0.0, "dA": 0.0, "dB": 0.0}
+    bit_exact = True
+    grads = flat_grads.cpu().numpy()
+    for names in groups:
+        ps = [by_name[n] for n in names]
+        x = ps[0]["hx"].numpy()                       # the group's shared input
+        K = ps[0]["K"]
+        dx_ref = np.zeros((M_TOKENS, K), np.float32)
+        for p in ps:
+            c = p["case"]
+            y_ref = O.proj_forward(c["qtype"], c["w"], None, x, K, p["N"], M_TOKENS, c["a"], c["b"], RANK, c["scaling"])
+            _, da_ref, db_ref = O.proj_backward(c["qtype"], c["w"], c["dy"], x, K, p["N"], M_TOKENS, c["a"], c["b"], RANK,
+                                                c["scaling"], dx=dx_ref)
+            worst["Y"] = max(worst["Y"], O.rel_fro(p["Y"].cpu().numpy(), y_ref))
+            g0 = p["g0"]
+            da = grads[g0: g0 + K * RANK].reshape(K, RANK)
+            db = grads[g0 + K * RANK: g0 + K * RANK + RANK * p["N"]].reshape(RANK, p["N"])
+            worst["dA"] = max(worst["dA"], O.rel_fro(da, da_ref))
+            worst["dB"] = max(worst["dB"], O.rel_fro(db, db_ref))
+            rows = [0, p["N"] // 2 + 1, p["N"] - 1]
+            for r in rows:
+                got = eng.dequant_rows(p["w"], r, 1)
+                want = O.dequant_rows(c["qtype"], c["w"], K, r, 1)
+                bit_exact = bit_exact and bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+        worst["dX"] = max(worst["dX"], O.rel_fro(ps[0]["dX"].cpu().numpy(), dx_ref))
+    out = {k: float(v) for k, v in worst.items()}
+    out["dequant_bit_exact"] = bit_exact
+    out["gate"] = 2e-2
+    out["ok"] = bool(bit_exact and all(v < 2e-2 for v in worst.values()))
+    out["checked"] = ("all seven projections of the last timed step (Y, group dX, dA, dB) against the CPU path, fp32; "
+                      "three dequantized rows per weight bit for bit" + ("; Q4_K_M mix" if q4km else ""))
+    return out
 
 
 def make_cpu_cases(names, seed_base=0):
@@ -100,7 +149,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens": M_TOKENS, "rank": RANK},
+        "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -220,7 +269,7 @@ def run_ours(args) -> None:
         ad.bind_grads(dA, dB)
         pin = lambda a: torch.from_numpy(a).pin_memory()   # noqa: E731
         hx, hdy = pin(c["x"]), pin(c["dy"])
-        layer.append(dict(name=n, N=N, K=K, w=w, ad=ad, hx=hx, hdy=hdy, g0=g0, g1=off,
+        layer.append(dict(name=n, N=N, K=K, w=w, ad=ad, hx=hx, hdy=hdy, g0=g0, g1=off, case=c if rank == 0 else None,
                           hy=torch.empty((M_TOKENS, N), dtype=torch.float32).pin_memory(),
                           hdx=torch.zeros((M_TOKENS, K), dtype=torch.float32).pin_memory(),
                           X=hx.to(dev), dY=hdy.to(dev), Y=torch.empty((M_TOKENS, N), dtype=torch.float32, device=dev),
@@ -236,7 +285,7 @@ def run_ours(args) -> None:
     # q,k,v read the same normed hidden state and gate,up the same FFN input (TransformerBlock.Forward): each group is
     # one call that shares the input and sums the members' input gradients into one buffer
     by_name = {p["name"]: p for p in layer}
-    groups = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]] if not args.no_group else [[n] for n in PROJ_ORDER]
+    groups = GROUPS if not args.no_group else [[n] for n in PROJ_ORDER]
     calls = []
     for names in groups:
         ps = [by_name[n] for n in names]
@@ -244,7 +293,7 @@ def run_ours(args) -> None:
                           dYs=[p["dY"] for p in ps], dX=ps[0]["dX"],
                           grads=flat_grads[ps[0]["g0"]: ps[-1]["g1"]]))      # the group's slice of the flat gradient buffer
 
-    def step_resident():
+    def step_resident(exchange: bool = True):
         flat_grads.zero_()
         for c in calls:
             if len(c["ws"]) > 1:
@@ -263,11 +312,11 @@ def run_ours(args) -> None:
             else:
                 eng.backward(c["ws"][0], c["ads"][0], c["dYs"][0], c["X"], c["dX"], flags=bflags)
             # the group's gradients are final: their all-reduce runs beside the backward of the groups that follow
-            if world > 1 and args.overlap:
+            if world > 1 and args.overlap and exchange:
                 eng.dp_allreduce_begin(c["grads"], 1.0 / world)
-        if world > 1 and args.overlap:
+        if world > 1 and args.overlap and exchange:
             eng.dp_allreduce_end()
-        if world > 1 and not args.overlap:
+        if world > 1 and not args.overlap and exchange:
             eng.dp_allreduce(flat_grads, 1.0 / world)
 
     # end to end: the same grouped calls on page-locked HOST buffers.  Every call stages its inputs to the device and its
@@ -347,8 +396,22 @@ def run_ours(args) -> None:
         run_step()
         ends[i].record(stream)
     barrier()
+    # A second, long measurement of the same step for the clock record: the K timed steps above last a few
+    # milliseconds, less than one nvidia-smi sample, so the sampler mostly sees the warm-up.  `sustained_steps` steps
+    # (about half a second) between event pairs per step, L2 flushed as above; reported beside the headline with
+    # time x median SM clock.
+    sus_n = max(args.steps, int(args.sustained_steps))
+    sus_a = [torch.cuda.Event(enable_timing=True) for _ in range(sus_n)]
+    sus_b = [torch.cuda.Event(enable_timing=True) for _ in range(sus_n)]
+    for i in range(sus_n):
+        l2_flush.zero_()
+        sus_a[i].record(stream)
+        run_step()
+        sus_b[i].record(stream)
+    barrier()
     clocks = sampler.stop() if rank == 0 else {}
     eng.sync()
+    sus_ms = sum(a.elapsed_time(b) for a, b in zip(sus_a, sus_b))
     # Per-kernel numbers for the roofline: the same steps once more with eager launches, every tensor-core GEMM
     # bracketed by CUDA events on the launching stream, L2 flushed between steps as above.
     eng.profile_read(reset=True)
@@ -362,17 +425,29 @@ def run_ours(args) -> None:
     eng.profile_enable(False)
     launches_per_step = prof["kernel_launches"] // max(1, prof_steps)
     total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([total_ms, sus_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
+    total_ms, sus_ms = float(t[0].item()), float(t[1].item())
     fl = step_flops()
     value = world * fl * args.steps / (total_ms * 1e-3) / 1e12
 
     _log("timed region done")
+    # ---- parity of what the timed steps computed (rank 0): the device tensors of the last step against the CPU path
+    parity = None
+    if rank == 0 and not args.no_parity:
+        from oracle import oracle as O
+        O.build()
+        O.set_threads(os.cpu_count() or 1)       # torchrun pins OMP_NUM_THREADS=1
+        step_resident(exchange=False)            # one eager step of this rank alone: its outputs are what is compared
+        eng.sync()
+        parity = parity_against_oracle(O, eng, layer, groups, flat_grads, args.q4km)
+        _log(f"parity {parity}")
+    barrier()
     # ---- end to end through the C ABI with host buffers (H2D of the inputs, D2H of the results, every step)
-    e2e_steps = max(1, min(args.steps, 8))
-    step_host()
+    e2e_steps = max(1, int(args.e2e_steps))
+    for _ in range(5):
+        step_host()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -397,7 +472,9 @@ def run_ours(args) -> None:
             "frac_of_sustained": (gemm_tflops / peaks["bf16_tflops_sustained"]) if peaks["bf16_tflops_sustained"] else None,
             "timed_in": f"eager pass of {prof_steps} steps after the timed region (events around each GEMM launch)",
             "launches": prof["gemm_launches"], "avg_launch_us": 1e3 * prof["gemm_ms"] / max(1, prof["gemm_launches"]),
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_of": "gate,up forward launch, 2 x 18944x3584 at M=512 (algorithmic HBM bytes: 80.1e6 read + 77.6e6 fp32 output, of which 31.4e6 left the L2 before the kernel ended)",
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+            "traffic_source": "constant from one ncu --set full capture of this launch (dram__bytes_read.sum + dram__bytes_write.sum); not re-measured by this run",
+            "traffic_of": "gate,up forward launch, 2 x 18944x3584 at M=512 (algorithmic HBM bytes: 80.1e6 read + 77.6e6 fp32 output, of which 31.4e6 left the L2 before the kernel ended)",
         }
         # CPU baseline: the oracle (a port of the reference's CPU path) on this host, one pass over the same layer
         from oracle import oracle as O
@@ -410,22 +487,28 @@ def run_ours(args) -> None:
             names = ["q", "k", "v", "o"]
         cpu_s = cpu_layer_pass(O, make_cpu_cases(names))
         cpu_val = step_flops(names) / cpu_s / 1e12
+        ms_step = total_ms / args.steps
+        sus_ms_step = sus_ms / sus_n
+        sm_mhz = clocks.get("sm_mhz") if isinstance(clocks, dict) else None
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD.replace("in Q4_K", "in the Q4_K_M mix (v, down in Q6_K)") if args.q4km else WORKLOAD,
-                       "tokens_per_gpu": M_TOKENS, "rank": RANK, "parallelism": f"dp{world}",
-                       "l2": "256 MiB written between timed steps; per-step inputs (131 MB weights + activations) exceed L2",
-                       "launch": "cuda graph replay" if graph is not None else "eager",
-                       "tokens_per_s": world * M_TOKENS * args.steps / (total_ms * 1e-3)},
+            "config": workload_config(world, args.q4km),
+            "detail": {"launch": "cuda graph replay" if graph is not None else "eager", "warmup_run": n_warm,
+                       "tokens_per_s_through_one_layer": world * M_TOKENS * args.steps / (total_ms * 1e-3),
+                       "sustained": {"steps": sus_n, "ms_per_step": sus_ms_step,
+                                     "value": world * fl / (sus_ms_step * 1e-3) / 1e12,
+                                     "ms_x_sm_mhz": (sus_ms_step * sm_mhz) if sm_mhz else None},
+                       "ms_x_sm_mhz": (ms_step * sm_mhz) if sm_mhz else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
+                    "steps": e2e_steps, "warmup": 5, "ms_per_step": 1e3 * e2e_s / e2e_steps,
                     "calls": "grouped host-buffer calls, " + ("synchronous" if args.e2e_sync else "queued (GT_FLAG_HOST_ASYNC) + gt_sync per step")},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline,
             "cpu_baseline": {"value": cpu_val, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
                              "sample": f"one pass over projections {','.join(names)} ({step_flops(names) / 1e9:.1f} GFLOP), fp32 OpenMP"},
+            "parity": parity,
             "clocks": clocks,
         }
         emit(json.dumps(line))
@@ -562,6 +645,9 @@ def main() -> None:
     ap.add_argument("--sweep", action="store_true", help="token-count sweep of the Q4_K_M projection set instead of the step benchmark")
     ap.add_argument("--glue", action="store_true", help="HBM throughput of the layer-glue kernels instead of the step benchmark")
     ap.add_argument("--sweep-m", type=int, nargs="+", default=[1, 16, 128, 512, 2048])
+    ap.add_argument("--e2e-steps", type=int, default=50, help="timed steps of the end-to-end (host-buffer) leg, after 5 warm steps")
+    ap.add_argument("--sustained-steps", type=int, default=800, help="steps of the second, long measurement that the clock samples cover")
+    ap.add_argument("--no-parity", action="store_true", help="skip the comparison of the last step's outputs with the CPU path")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)

@@ -22,7 +22,7 @@ EXPORTS = [
     "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
-    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
+    "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_params_changed", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
     "gt_rmsnorm_backward", "gt_add",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_adamw_step", "gt_adapter_adamw_step", "gt_adapters_adamw_step",
@@ -73,6 +73,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     for name in ("gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_bind_grads"):
         getattr(lib, name).argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.gt_adapter_grads_zero.argtypes = [C.c_void_p]
+    lib.gt_adapter_params_changed.argtypes = [C.c_void_p]
     lib.gt_adapter_set_alpha.argtypes = [C.c_void_p, C.c_float]
     lib.gt_adapter_device_ptrs.argtypes = [C.c_void_p] + [C.POINTER(C.c_void_p)] * 4
     lib.gt_proj_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
@@ -401,6 +402,10 @@ class Adapter:
         ps = [C.c_void_p() for _ in range(4)]
         _check(self.eng.lib.gt_adapter_device_ptrs(self.h, *[C.byref(p) for p in ps]))
         return [p.value for p in ps]
+
+    def params_changed(self):
+        """A or B were written through the device pointers: refresh the B == 0 flag, drop the kept X*A."""
+        _check(self.eng.lib.gt_adapter_params_changed(self.h))
 
     def free(self):
         if self.h:

@@ -96,6 +96,11 @@ struct gt_engine {
     // overlapped gradient exchange: collectives queued on a side stream between a fork and a join of the engine stream
     cudaStream_t s_comm = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    // dA = s * X^T * dLow needs only the pass over dY, not the dX GEMM that follows it: it runs on a side stream beside
+    // that GEMM (fork after the dY pass, join after the GEMM launch), so its launch gap and tail hide under the GEMM
+    cudaStream_t s_aux = nullptr;
+    cudaEvent_t ev_aux_fork = nullptr, ev_aux_join = nullptr;
+    bool aux_pending = false;
     bool comm_pending = false;
     ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
     int dp_world = 1, dp_rank = 0;
@@ -369,9 +374,31 @@ int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float
 
 // The adapter half of a backward: dB += s*low^T*dY, dLow = dY*B^T, dA += s*X^T*dLow for every member with an adapter
 // (one launch per product in the bf16 mode), and the 16-bit copy of each dY where dy16[j] is given.
+int aux_init(gt_engine *e) {
+    if (e->s_aux) return GT_OK;
+    GT_CUDA(cudaStreamCreateWithFlags(&e->s_aux, cudaStreamNonBlocking));
+    GT_CUDA(cudaEventCreateWithFlags(&e->ev_aux_fork, cudaEventDisableTiming));
+    GT_CUDA(cudaEventCreateWithFlags(&e->ev_aux_join, cudaEventDisableTiming));
+    return GT_OK;
+}
+// the engine stream waits for a dA pass that was put on the side stream
+int aux_join(gt_engine *e) {
+    if (!e->aux_pending) return GT_OK;
+    GT_CUDA(cudaStreamWaitEvent(e->stream, e->ev_aux_join, 0));
+    e->aux_pending = false;
+    return GT_OK;
+}
+bool side_da_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("GT_SIDE_DA");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
 int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const bool *lora,
                         const float *const *dYd, const float *Xd, void *const *dy16, const int *ld16, int T, bool reuse_low,
-                        float *zero_dx) {
+                        float *zero_dx, bool side_da = false) {
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
     const bool fast = e->math_mode == GT_MATH_BF16;      // bf16 warp-MMA reductions; exact fp32 otherwise
@@ -410,7 +437,17 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
     if (!nl) return GT_OK;
     if (fast) {
         GT_LAUNCH(e, launch_lora_dy_group(dy, nl, fp16, T, zero_dx ? &zero : nullptr, zero_dx ? 1 : 0, e->stream));
-        GT_LAUNCH(e, launch_lora_da_group(Xd, da, nl, T, K, e->stream));
+        cudaStream_t da_stream = e->stream;
+        if (side_da && e->s_aux) {
+            GT_CUDA(cudaEventRecord(e->ev_aux_fork, e->stream));
+            GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));
+            da_stream = e->s_aux;
+        }
+        GT_LAUNCH(e, launch_lora_da_group(Xd, da, nl, T, K, da_stream));
+        if (da_stream != e->stream) {
+            GT_CUDA(cudaEventRecord(e->ev_aux_join, e->s_aux));
+            e->aux_pending = true;
+        }
     } else {
         for (int j = 0; j < nl; j++) {
             GT_LAUNCH(e, launch_lora_bwd_dy(dy[j].dY, dy[j].low, dy[j].B, dy[j].dB, dy[j].dLow_zeroed, dy[j].dy16, dy[j].ld16, fp16,
@@ -447,8 +484,6 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
     }
     GT_CUDA(e->dy16.reserve(dy_total));
     for (int j = 0; j < n; j++) dy16[j] = (char *)e->dy16.p + dy_off[j];
-    int rc = lora_backward_group(e, n, w, ad, lora, dYd, Xd, dy16, ld16, T, reuse_low, assign ? dXd : nullptr);
-    if (rc != GT_OK) return rc;
     UmmaLaunch m[kMaxGroup];
     for (int j = 0; j < n; j++) {
         const WeightDev &wd = w[j]->dev;
@@ -460,28 +495,42 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
         m[j].T = T;
         m[j].out = dXd;
         m[j].ld_out = K;
-        if (lora[j]) {
-            m[j].lora_act = dlow_of(ad[j], T);
-            m[j].lora_scale = ad[j]->scaling;
-            m[j].lora_w = ad[j]->A;
-            m[j].rank = ad[j]->rank;
-        }
         m[j].status = e->status;
         m[j].trace = e->trace;
     }
-    // one launch per quantization type, all summing into the same dX
-    int order[kMaxGroup], count[kMaxGroup];
+    // one launch per quantization type, all summing into the same dX.  "dX =": when the first launch has one CTA per
+    // output tile (no split-K) it writes dX with plain stores and nothing has to clear the buffer first; otherwise the
+    // pass over dY (or a fill of its own) clears it and every launch adds.
+    int order[kMaxGroup], count[kMaxGroup], run_splits[kMaxGroup];
     const int runs = partition_by_type(n, w, order, count);
     UmmaLaunch run_m[kMaxGroup];
     for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
         for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
-        const int splits = umma_group_splits(run_m + pos, count[r], e->sm_count);
-        for (int i = 0; i < count[r]; i++) run_m[pos + i].splits = splits;
+        run_splits[r] = umma_group_splits(run_m + pos, count[r], e->sm_count);
+    }
+    const bool store_first = assign && run_splits[0] == 1;
+    int rc = lora_backward_group(e, n, w, ad, lora, dYd, Xd, dy16, ld16, T, reuse_low, (assign && !store_first) ? dXd : nullptr,
+                                 side_da_enabled() && !e->profile);      // profiling times each GEMM alone on the device
+    if (rc != GT_OK) return rc;
+    for (int j = 0; j < n; j++) {
+        if (lora[j]) {
+            m[j].lora_act = dlow_of(ad[j], T);      // the adapter's scratch is allocated by now
+            m[j].lora_scale = ad[j]->scaling;
+            m[j].lora_w = ad[j]->A;
+            m[j].rank = ad[j]->rank;
+        }
+    }
+    for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
+        for (int i = 0; i < count[r]; i++) {
+            run_m[pos + i] = m[order[pos + i]];
+            run_m[pos + i].splits = run_splits[r];
+        }
+        run_m[pos].out_assign = (r == 0 && store_first) ? 1 : 0;
         const char *msg = nullptr;
         cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg);
         if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
     }
-    return GT_OK;
+    return aux_join(e);      // the dA pass on the side stream is part of this call
 }
 
 // dX += dY*W (+ lora term); dA, dB accumulate.  Device pointers.
@@ -682,6 +731,7 @@ bool pdl_enabled() {
 EngineView engine_view(gt_engine *e) { return EngineView{e->device, e->math_mode, e->sm_count, e->stream, e->status, &e->mu}; }
 const WeightDev *weight_view(const gt_weight *w) { return &w->dev; }
 int set_last_error(int code, const char *text) { return fail(code, "%s", text); }
+int engine_join_comm(gt_engine *e) { return join_comm(e); }
 }  // namespace gt
 
 extern "C" {
@@ -730,6 +780,7 @@ int gt_engine_create(const gt_config *cfg, gt_engine **out) {
     }
     cudaError_t ce = cudaMalloc((void **)&e->status, 4 * sizeof(int));
     if (ce == cudaSuccess) ce = cudaMalloc((void **)&e->clip, 2 * sizeof(double));
+    if (ce == cudaSuccess && aux_init(e) != GT_OK) ce = cudaErrorUnknown;      // side stream of the dA passes
     if (ce == cudaSuccess) ce = cudaMemset(e->status, 0, 4 * sizeof(int));
     if (ce != cudaSuccess) {
         gt_engine_destroy(e);
@@ -758,6 +809,12 @@ int gt_engine_destroy(gt_engine *e) {
         cudaStreamSynchronize(e->s_comm);
         cudaStreamDestroy(e->s_comm);
     }
+    if (e->s_aux) {
+        cudaStreamSynchronize(e->s_aux);
+        cudaStreamDestroy(e->s_aux);
+    }
+    if (e->ev_aux_fork) cudaEventDestroy(e->ev_aux_fork);
+    if (e->ev_aux_join) cudaEventDestroy(e->ev_aux_join);
     if (e->ev_fork) cudaEventDestroy(e->ev_fork);
     if (e->ev_join) cudaEventDestroy(e->ev_join);
     if (e->s_h2d) cudaStreamDestroy(e->s_h2d);
@@ -1038,6 +1095,8 @@ int gt_adapters_adamw_step(gt_engine *e, int32_t n, gt_adapter *const *ads, floa
     if (n <= 0) return GT_OK;
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
+    int jrc = join_comm(e);      // the update reads gradients that a pending exchange may still be writing
+    if (jrc != GT_OK) return jrc;
     std::vector<gt::AdamwSeg> segs;
     segs.reserve((size_t)2 * n);
     for (int i = 0; i < n; i++) {
@@ -1073,9 +1132,29 @@ int gt_adapter_set_alpha(gt_adapter *a, float alpha) {
 int gt_adapter_device_ptrs(gt_adapter *a, float **A, float **B, float **dA, float **dB) {
     if (!a) return fail(GT_ERR_INVALID, "adapter is null");
     if (A) *A = a->A;
-    if (B) *B = a->B;
     if (dA) *dA = a->dA;
     if (dB) *dB = a->dB;
+    if (B) {
+        // The caller may now write B behind the library's back (a resident optimizer): the "B is all zero" flag that
+        // lets the forward skip the adapter term can no longer be trusted, so it is raised (a stale 1 costs arithmetic,
+        // never correctness).  gt_adapter_params_changed() recomputes it from the values.
+        gt_engine *e = a->eng;
+        std::lock_guard<std::mutex> lk(e->mu);
+        GT_CUDA(cudaSetDevice(e->device));
+        GT_CUDA(cudaMemsetAsync(a->b_nonzero, 1, sizeof(int), e->stream));      // 0x01010101: non-zero
+        *B = a->B;
+    }
+    return GT_OK;
+}
+
+int gt_adapter_params_changed(gt_adapter *a) {
+    if (!a) return fail(GT_ERR_INVALID, "adapter is null");
+    gt_engine *e = a->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    GT_CUDA(launch_any_nonzero(a->B, (int64_t)a->rank * a->out, a->b_nonzero, e->stream));
+    a->low_T = 0;        // X*A kept from an earlier forward was computed with the old A
+    a->xkeep_T = 0;
     return GT_OK;
 }
 
@@ -1269,6 +1348,8 @@ int gt_grads_scale_clip(gt_engine *e, float *g_dev, int64_t n, float pre_scale, 
     if (!e || !g_dev || n < 0) return fail(GT_ERR_INVALID, "gt_grads_scale_clip: bad argument");
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
+    int jrc = join_comm(e);      // gradient slices still being exchanged on the side stream come first
+    if (jrc != GT_OK) return jrc;
     GT_CUDA(launch_scale_clip(g_dev, n, pre_scale, max_norm, e->clip, e->stream));
     double h[2] = {0, 0};
     GT_CUDA(cudaMemcpyAsync(h, e->clip, sizeof(h), cudaMemcpyDeviceToHost, e->stream));
@@ -1354,7 +1435,7 @@ int allreduce_on(gt_engine *e, float *g_dev, int64_t count, float scale, cudaStr
         if (r != ncclSuccess) return fail(GT_ERR_NCCL, "ncclAllReduce: %s", n.GetErrorString(r));
         if (avg) return GT_OK;
     }
-    if (scale != 1.0f) GT_CUDA(launch_scale_clip(g_dev, count, scale, 0.0, e->clip, st));
+    if (scale != 1.0f) GT_CUDA(launch_scale(g_dev, count, scale, st));      // plain scale: no norm, no shared scratch
     return GT_OK;
 }
 }  // namespace

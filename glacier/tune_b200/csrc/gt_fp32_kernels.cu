@@ -528,12 +528,23 @@ __global__ void k_scale_sumsq(float *__restrict__ g, int64_t n, float pre_scale,
 }
 __global__ void k_clip_apply(float *__restrict__ g, int64_t n, double max_norm, double *scratch) {
     const double norm = sqrt(scratch[0]);
-    const bool bad = isnan(norm) || isinf(norm);
+    // ClipGradients returns at once when maxNorm <= 0 (LoraTrainer.cs:398): the gradients stay as they are, even
+    // non-finite ones; only a positive maxNorm zeroes them on a non-finite norm (LoraTrainer.cs:417-424)
+    const bool bad = max_norm > 0.0 && (isnan(norm) || isinf(norm));
     if (blockIdx.x == 0 && threadIdx.x == 0) scratch[1] = bad ? 0.0 : norm;
     if (!bad && !(max_norm > 0.0 && norm > max_norm)) return;
     const float sc = bad ? 0.f : (float)(max_norm / (norm + 1e-6));
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         g[i] = bad ? 0.f : g[i] * sc;
+}
+__global__ void k_scale(float *__restrict__ g, int64_t n, float scale) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) g[i] *= scale;
+}
+cudaError_t launch_scale(float *g, int64_t n, float scale, cudaStream_t s) {
+    if (n <= 0 || scale == 1.0f) return cudaSuccess;
+    const unsigned blocks = (unsigned)((n + 255) / 256 > 148 * 8 ? 148 * 8 : (n + 255) / 256);
+    k_scale<<<blocks, 256, 0, s>>>(g, n, scale);
+    return cudaGetLastError();
 }
 cudaError_t launch_scale_clip(float *g, int64_t n, float pre_scale, double max_norm, double *scratch, cudaStream_t s) {
     cudaError_t e = cudaMemsetAsync(scratch, 0, 2 * sizeof(double), s);

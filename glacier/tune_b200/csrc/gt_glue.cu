@@ -414,6 +414,7 @@ extern "C" int gt_adamw_step(gt_engine *eng, float *p, const float *g, float *m,
     const gt::EngineView ev = gt::engine_view(eng);
     std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
     cudaError_t ce = cudaSetDevice(ev.device);
+    if (ce == cudaSuccess && gt::engine_join_comm(eng) != GT_OK) return GT_ERR_CUDA;      // a pending gradient exchange comes first
     const gt::AdamwSeg seg{p, g, m, v, nullptr, n, 0};
     if (ce == cudaSuccess) ce = gt::launch_adamw(&seg, 1, lr, beta1, beta2, eps, weight_decay, (int)step, ev.sm_count, ev.stream);
     return ce == cudaSuccess ? GT_OK : cuda_fail("gt_adamw_step", ce);

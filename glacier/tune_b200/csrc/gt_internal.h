@@ -4,7 +4,29 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace gt {
+
+// cudaFuncSetAttribute (dynamic shared memory above 48 KB) applies to the CURRENT device only: an engine on a second
+// device of the same process needs its own call.  One PerDeviceOnce per kernel (or group of kernels) remembers on
+// which devices `fn` has run; thread-safe.
+struct PerDeviceOnce {
+    std::mutex mu;
+    bool done[64] = {};
+};
+template <typename F>
+cudaError_t per_device_once(PerDeviceOnce &st, F &&fn) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return fn();
+    std::lock_guard<std::mutex> lk(st.mu);
+    if (st.done[dev]) return cudaSuccess;
+    e = fn();
+    if (e == cudaSuccess) st.done[dev] = true;
+    return e;
+}
 
 // Device copy of one frozen base tensor.
 struct WeightDev {
@@ -53,6 +75,8 @@ cudaError_t launch_add_inplace(float *dst, const float *src, int64_t n, cudaStre
 cudaError_t launch_any_nonzero(const float *B, int64_t n, int *flag, cudaStream_t s);
 // scratch: 2 doubles on the device
 cudaError_t launch_scale_clip(float *g, int64_t n, float pre_scale, double max_norm, double *scratch, cudaStream_t s);
+// g *= scale (no norm, no scratch)
+cudaError_t launch_scale(float *g, int64_t n, float scale, cudaStream_t s);
 
 // ---- LoRA products on bf16 warp MMAs for the bf16 math mode (gt_lora_tc.cu); same contracts as the fp32 versions,
 // except that `low` / `dLow` must be zero on entry (partial sums arrive by atomics).  Adapters of projections that
@@ -100,6 +124,8 @@ struct UmmaLaunch {
     int ld_out = 0;
     const float *bias = nullptr;   // forward only
     int out_prefilled = 0;         // forward: out already holds bias/zero, accumulate with atomics (split-K)
+    int out_assign = 0;            // backward, member 0: out is overwritten ("dX ="); honoured with plain stores when
+                                   // splits == 1, otherwise the caller must have cleared out
     // fused LoRA rank-update (optional)
     const float *lora_act = nullptr;    // fp32 [T, R]: X*A (forward) or dY*B^T (backward)
     float lora_scale = 1.f;             // alpha / r, applied when the tile is rounded to 16 bits
@@ -181,4 +207,5 @@ namespace gt {
 EngineView engine_view(gt_engine *e);
 const WeightDev *weight_view(const gt_weight *w);
 int set_last_error(int code, const char *text);     // records the text for gt_last_error(), returns code
+int engine_join_comm(gt_engine *e);                 // engine stream waits for gradient exchanges begun on the side stream (lock held)
 }  // namespace gt

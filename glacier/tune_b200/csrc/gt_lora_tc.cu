@@ -147,6 +147,38 @@ __device__ __forceinline__ void tile_store(const float4 (&v)[NI], int t0, int t_
         *reinterpret_cast<uint2 *>(tile + r * GSB + c * 2) = pk;
     }
 }
+// The same tile through a two-slot ring in shared memory filled with 16-byte cp.async copies: a block keeps the loads of
+// its next TWO tiles in flight while it works on the current one (with one tile of prefetch in registers the loop ran
+// at one round of DRAM latency per tile).  Thread `tid` owns pieces tid + 256 i of a slot, writes them (cp.async) and
+// reads them back itself, so a slot needs no barrier; only interior, 16-byte-aligned tiles take this path.
+constexpr int kRingSlotBytes = TT * TC * 4;       // 32 KiB: one fp32 tile
+constexpr int kRingBytes = 2 * kRingSlotBytes;
+__device__ __forceinline__ void tile_issue(const float *__restrict__ src, int ncols, int t0, int t_end, int c0, uint32_t slot, int tid) {
+#pragma unroll
+    for (int i = 0; i < NI; i++) {
+        const int idx = tid + i * 256;
+        const int r = idx / (TC / 4), c = (idx % (TC / 4)) * 4;
+        const int t = t0 + r;
+        const bool ok = t < t_end;
+        const float *p = src + (int64_t)(ok ? t : t0) * ncols + c0 + c;      // rows past the end: zero-filled, nothing read
+        const uint32_t nbytes = ok ? 16u : 0u;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(slot + (uint32_t)idx * 16u), "l"(p), "r"(nbytes) : "memory");
+    }
+}
+__device__ __forceinline__ void ring_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ring_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void tile_take(uint32_t slot, float4 (&v)[NI], int tid) {
+#pragma unroll
+    for (int i = 0; i < NI; i++) {
+        const uint32_t a = slot + (uint32_t)(tid + i * 256) * 16u;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v[i].x), "=f"(v[i].y), "=f"(v[i].z), "=f"(v[i].w) : "r"(a) : "memory");
+    }
+}
+// every tile of columns [c_begin, c_end) of src[., ncols] is interior and 16-byte aligned
+__device__ __forceinline__ bool ring_ok(int enabled, const float *src, int ncols, int c_end) {
+    return enabled != 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ncols & 3) == 0 && c_end <= ncols;
+}
+
 // fp32 accumulator fragment of a 16 x 8 tile (rows m0 + g / + 8, columns n0 + 2*t4 / + 1) added into dst[rows, ld]
 __device__ __forceinline__ void frag_atomic_add(float *dst, int64_t ld, const float (&d)[4], int row_a, int row_end, int col, int col_end,
                                                 float scale) {
@@ -194,7 +226,7 @@ struct XaChunk {
 struct XaParams {
     const float *X;
     uint16_t *x16;
-    int ldx16, T, K, n, strips_per_block;
+    int ldx16, T, K, n, strips_per_block, ring;
     XaChunk c[kMaxChunks];
     FillList fills;
 };
@@ -204,13 +236,15 @@ constexpr int kLsBytes = TT * RSB;            // per chunk, k_lora_da_tc / k_lor
 
 __global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
-    uint8_t *Xs = dyn_smem;
-    uint8_t *As = dyn_smem + kXsBytes;
+    uint8_t *Xs = dyn_smem + kRingBytes;
+    uint8_t *As = Xs + kXsBytes;
+    const uint32_t ring = smem_u32(dyn_smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int T = p.T, K = p.K;
     const int t0 = blockIdx.x * TT;
     const int n_strips = (K + TC - 1) / TC;
     const int s0 = blockIdx.y * p.strips_per_block, s1 = min(n_strips, s0 + p.strips_per_block);
+    const bool use_ring = ring_ok(p.ring, p.X, K, s1 * TC);
     pdl_wait();
     pdl_trigger();
     float4 v[NI], av[kMaxChunks][2];
@@ -228,7 +262,14 @@ __global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
             }
         }
     };
-    tile_load(p.X, K, t0, T, s0 * TC, v, tid);
+    if (use_ring) {
+        tile_issue(p.X, K, t0, T, s0 * TC, ring, tid);
+        ring_commit();
+        if (s0 + 1 < s1) tile_issue(p.X, K, t0, T, (s0 + 1) * TC, ring + kRingSlotBytes, tid);
+        ring_commit();
+    } else {
+        tile_load(p.X, K, t0, T, s0 * TC, v, tid);
+    }
     a_load(s0 * TC);
     float d[kMaxChunks][2][4];
 #pragma unroll
@@ -238,8 +279,17 @@ __global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
     const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;
     const uint32_t xs = smem_u32(Xs), as = smem_u32(As);
     for (int s = s0; s < s1; s++) {
+        const uint32_t slot = ring + (uint32_t)((s - s0) & 1) * kRingSlotBytes;
+        if (use_ring) {
+            ring_wait_all_but_one();
+            tile_take(slot, v, tid);
+        }
         __syncthreads();
         tile_store(v, t0, T, s * TC, Xs, p.x16, p.ldx16, tid);
+        if (use_ring) {      // the slot's values are in registers and used: refill it with the tile after the next one
+            if (s + 2 < s1) tile_issue(p.X, K, t0, T, (s + 2) * TC, slot, tid);
+            ring_commit();
+        }
 #pragma unroll
         for (int j = 0; j < kMaxChunks; j++) {
             if (j < p.n) {
@@ -251,7 +301,7 @@ __global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
             }
         }
         if (s + 1 < s1) {      // the next strip's loads fly during the MMAs below
-            tile_load(p.X, K, t0, T, (s + 1) * TC, v, tid);
+            if (!use_ring) tile_load(p.X, K, t0, T, (s + 1) * TC, v, tid);
             a_load((s + 1) * TC);
         }
         __syncthreads();
@@ -300,15 +350,18 @@ struct DyMember {
     float scaling;
 };
 struct DyParams {
-    int T, strips_per_block, n;
+    int T, strips_per_block, n, ring;
     DyMember m[kMaxChunks];
     FillList fills;
 };
 
-__global__ void __launch_bounds__(256, 3) k_lora_dy_tc(const DyParams p) {
-    __shared__ __align__(16) uint8_t Gs[TT * GSB];
-    __shared__ __align__(16) uint8_t Bs[16 * GSB];      // B[r0.., c0..] as [16][128]
-    __shared__ __align__(16) uint8_t Ls[TT * RSB];      // low tile [64][16]
+constexpr int kDySmemBytes = kRingBytes + TT * GSB + 16 * GSB + TT * RSB;
+__global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t *Gs = dyn_smem + kRingBytes;      // dY tile, bf16
+    uint8_t *Bs = Gs + TT * GSB;              // B[r0.., c0..] as [16][128]
+    uint8_t *Ls = Bs + 16 * GSB;              // low tile [64][16]
+    const uint32_t ring = smem_u32(dyn_smem);
     pdl_wait();
     pdl_trigger();
     const DyMember m = p.m[blockIdx.z];
@@ -332,7 +385,15 @@ __global__ void __launch_bounds__(256, 3) k_lora_dy_tc(const DyParams p) {
             bv[i] = ld4(m.B, r0 + r, N, c0 + (idx & 31) * 4, N, r < rc, m.vec_b != 0);
         }
     };
-    tile_load(m.dY, N, t0, T, s0 * TC, v, tid);
+    const bool use_ring = ring_ok(p.ring, m.dY, N, s1 * TC);
+    if (use_ring) {
+        tile_issue(m.dY, N, t0, T, s0 * TC, ring, tid);
+        ring_commit();
+        if (s0 + 1 < s1) tile_issue(m.dY, N, t0, T, (s0 + 1) * TC, ring + kRingSlotBytes, tid);
+        ring_commit();
+    } else {
+        tile_load(m.dY, N, t0, T, s0 * TC, v, tid);
+    }
     b_load(s0 * TC);
     {
         const int row = tid >> 2;
@@ -346,15 +407,24 @@ __global__ void __launch_bounds__(256, 3) k_lora_dy_tc(const DyParams p) {
     uint16_t *dy16 = r0 == 0 ? m.dy16 : nullptr;
     for (int s = s0; s < s1; s++) {
         const int c0 = s * TC;
+        const uint32_t slot = ring + (uint32_t)((s - s0) & 1) * kRingSlotBytes;
+        if (use_ring) {
+            ring_wait_all_but_one();
+            tile_take(slot, v, tid);
+        }
         __syncthreads();
         tile_store(v, t0, T, c0, Gs, dy16, m.ld16, tid);
+        if (use_ring) {
+            if (s + 2 < s1) tile_issue(m.dY, N, t0, T, (s + 2) * TC, slot, tid);
+            ring_commit();
+        }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             const int idx = tid + i * 256;
             st_bf16x4(Bs + (idx >> 5) * GSB + (idx & 31) * 8, bv[i]);
         }
         if (s + 1 < s1) {      // the next strip's loads fly during the MMAs below
-            tile_load(m.dY, N, t0, T, (s + 1) * TC, v, tid);
+            if (!use_ring) tile_load(m.dY, N, t0, T, (s + 1) * TC, v, tid);
             b_load((s + 1) * TC);
         }
         __syncthreads();
@@ -399,14 +469,15 @@ struct DaChunk {
 };
 struct DaParams {
     const float *X;
-    int T, K, n, tok_per_group;
+    int T, K, n, tok_per_group, ring;
     DaChunk c[kMaxChunks];
 };
 
 __global__ void __launch_bounds__(256, 2) k_lora_da_tc(const DaParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
-    uint8_t *Xs = dyn_smem;
-    uint8_t *Ls = dyn_smem + kXsBytes;
+    uint8_t *Xs = dyn_smem + kRingBytes;
+    uint8_t *Ls = Xs + kXsBytes;
+    const uint32_t ring = smem_u32(dyn_smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int T = p.T, K = p.K;
     const int k0 = blockIdx.x * TC;
@@ -432,16 +503,33 @@ __global__ void __launch_bounds__(256, 2) k_lora_da_tc(const DaParams p) {
             }
         }
     };
-    tile_load(p.X, K, tg0, tg1, k0, v, tid);
+    const bool use_ring = ring_ok(p.ring, p.X, K, k0 + TC);
+    if (use_ring) {
+        tile_issue(p.X, K, tg0, tg1, k0, ring, tid);
+        ring_commit();
+        if (tg0 + TT < tg1) tile_issue(p.X, K, tg0 + TT, tg1, k0, ring + kRingSlotBytes, tid);
+        ring_commit();
+    } else {
+        tile_load(p.X, K, tg0, tg1, k0, v, tid);
+    }
     l_load(tg0);
-    for (int ts = tg0; ts < tg1; ts += TT) {
+    for (int ts = tg0, it = 0; ts < tg1; ts += TT, it++) {
+        const uint32_t slot = ring + (uint32_t)(it & 1) * kRingSlotBytes;
+        if (use_ring) {
+            ring_wait_all_but_one();
+            tile_take(slot, v, tid);
+        }
         __syncthreads();
         tile_store(v, ts, tg1, k0, Xs, nullptr, 0, tid);
+        if (use_ring) {
+            if (ts + 2 * TT < tg1) tile_issue(p.X, K, ts + 2 * TT, tg1, k0, slot, tid);
+            ring_commit();
+        }
 #pragma unroll
         for (int j = 0; j < kMaxChunks; j++)
             if (j < p.n) st_bf16x4(Ls + j * kLsBytes + (tid >> 2) * RSB + (tid & 3) * 8, lv[j]);
         if (ts + TT < tg1) {      // the next tile's loads fly during the MMAs below
-            tile_load(p.X, K, ts + TT, tg1, k0, v, tid);
+            if (!use_ring) tile_load(p.X, K, ts + TT, tg1, k0, v, tid);
             l_load(ts + TT);
         }
         __syncthreads();
@@ -491,15 +579,25 @@ int pick_strip_run(int strips_total, int T) {
     if (forced > 0) run = forced;
     return run < 1 ? 1 : (run > 8 ? 8 : run);
 }
+// GT_LORA_RING=0 turns the cp.async ring off (one tile of prefetch in registers instead): a measurement knob
+int ring_enabled() {
+    static const int on = [] {
+        const char *v = getenv("GT_LORA_RING");
+        return (v && v[0] == '0') ? 0 : 1;
+    }();
+    return on;
+}
 inline int is_vec(const void *p, int ld) { return ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld & 3) == 0) ? 1 : 0; }
 
 cudaError_t allow_dyn_smem() {
-    static cudaError_t done = [] {
-        cudaError_t e = cudaFuncSetAttribute(k_lora_xa_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kXsBytes + kMaxChunks * kAsBytes));
+    static PerDeviceOnce configured;
+    return per_device_once(configured, [] {
+        cudaError_t e = cudaFuncSetAttribute(k_lora_xa_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kRingBytes + kXsBytes + kMaxChunks * kAsBytes));
         if (e != cudaSuccess) return e;
-        return cudaFuncSetAttribute(k_lora_da_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kXsBytes + kMaxChunks * kLsBytes));
-    }();
-    return done;
+        e = cudaFuncSetAttribute(k_lora_dy_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDySmemBytes);
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(k_lora_da_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kRingBytes + kXsBytes + kMaxChunks * kLsBytes));
+    });
 }
 
 }  // namespace
@@ -524,11 +622,12 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     p.T = T;
     p.K = K;
     p.strips_per_block = pick_strip_run(strips, T);
+    p.ring = ring_enabled();
     dim3 grid((T + TT - 1) / TT, (strips + p.strips_per_block - 1) / p.strips_per_block);
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_xa_tc, grid, dim3(256), (size_t)(kXsBytes + p.n * kAsBytes), s, p);
+        cudaError_t le = launch_k(k_lora_xa_tc, grid, dim3(256), (size_t)(kRingBytes + kXsBytes + p.n * kAsBytes), s, p);
         p.n = 0;
         p.x16 = nullptr;
         p.fills.n = 0;
@@ -545,6 +644,8 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
 cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, const RowFill *fills, int n_fills, cudaStream_t s) {
     if (T <= 0 || n <= 0) return cudaSuccess;
     (void)fp16;
+    cudaError_t ae = allow_dyn_smem();
+    if (ae != cudaSuccess) return ae;
     int strips_sum = 0, strips_max = 0;
     for (int j = 0; j < n; j++) {
         const int st = (jobs[j].N + TC - 1) / TC;
@@ -554,11 +655,12 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
     DyParams p{};
     p.T = T;
     p.strips_per_block = pick_strip_run(strips_sum, T);
+    p.ring = ring_enabled();
     const dim3 grid_xy((strips_max + p.strips_per_block - 1) / p.strips_per_block, (T + TT - 1) / TT);
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_dy_tc, dim3(grid_xy.x, grid_xy.y, p.n), dim3(256), (size_t)0, s, p);
+        cudaError_t le = launch_k(k_lora_dy_tc, dim3(grid_xy.x, grid_xy.y, p.n), dim3(256), (size_t)kDySmemBytes, s, p);
         p.n = 0;
         p.fills.n = 0;
         return le;
@@ -596,9 +698,10 @@ cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, i
     p.T = T;
     p.K = K;
     p.tok_per_group = tpg;
+    p.ring = ring_enabled();
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_da_tc, dim3(strips, groups), dim3(256), (size_t)(kXsBytes + p.n * kLsBytes), s, p);
+        cudaError_t le = launch_k(k_lora_da_tc, dim3(strips, groups), dim3(256), (size_t)(kRingBytes + kXsBytes + p.n * kLsBytes), s, p);
         p.n = 0;
         return le;
     };

@@ -60,6 +60,9 @@ extern "C" int gt_launch_gemm_bwd_static(gt_engine *eng, const gt_weight *w, flo
     using namespace gt;
     if (!eng || !w || !dDX_accum || !dDY) return set_last_error(GT_ERR_INVALID, "gt_launch_gemm_bwd_static: null argument");
     if (batch <= 0) return set_last_error(GT_ERR_INVALID, "gt_launch_gemm_bwd_static: batch must be positive");
+    // the engine's lock is taken before anything else of the engine is read (the math mode may be changed by another
+    // thread through gt_engine_set_math_mode)
+    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(engine_view(eng).mutex));
     const EngineView ev = engine_view(eng);
     const WeightDev *wd = weight_view(w);
     if (ev.math_mode == GT_MATH_FP32 || !wd->tma_ok)
@@ -76,7 +79,6 @@ extern "C" int gt_launch_gemm_bwd_static(gt_engine *eng, const gt_weight *w, flo
                  batch, wd->N, need, kStaticScratchBytes);
         return set_last_error(GT_ERR_UNSUPPORTED, msg);
     }
-    std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
     cudaError_t ce = cudaSetDevice(ev.device);
     void *scratch = nullptr;
     if (ce == cudaSuccess) ce = scratch_for_device(ev.device, &scratch);

@@ -297,12 +297,9 @@ __global__ void __launch_bounds__(kSThreads, 1) k_stream_fwd_q4k(const __grid_co
 
 template <int NT>
 cudaError_t launch_nt(const StreamParams &p, dim3 grid, size_t smem, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_stream_fwd_q4k<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static PerDeviceOnce configured;
+    cudaError_t ce = per_device_once(configured, [] { return cudaFuncSetAttribute(k_stream_fwd_q4k<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); });
+    if (ce != cudaSuccess) return ce;
     return launch_k(k_stream_fwd_q4k<NT>, grid, dim3(kSThreads), smem, s, p);
 }
 

@@ -96,7 +96,7 @@ struct Params {
     int T, K;
     int t_box;       // token rows per activation TMA box
     int splits, units;
-    int atomic_out;  // 1: red.add into out, 0: plain store (+bias)
+    int atomic_out;  // 1: red.add into out, 0: plain store (forward: + bias)
     int tmem_cols;
 };
 
@@ -542,8 +542,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                         if (tl < tb && t < p.T) {
                             float *dst = out_base + (int64_t)t * ld_out + orow;
                             const float val = __uint_as_float(v[j]);
-                            if (BWD || p.atomic_out) atomicAdd(dst, val);
-                            else *dst = val + bv;
+                            if (p.atomic_out) atomicAdd(dst, val);
+                            else *dst = val + bv;       // this CTA alone owns the tile (backward: bv is 0)
                         }
                     }
                 }
@@ -594,16 +594,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    // function-local static with an initialiser: looked up once, safely from any number of threads
+    static const EncodeTiledFn fn = [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
+            return reinterpret_cast<EncodeTiledFn>(p);
+        return static_cast<EncodeTiledFn>(nullptr);
+    }();
     return fn;
 }
 
@@ -622,13 +621,10 @@ bool encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, int esize, const void *b
 
 template <int QT, typename T16, bool BWD, bool PAIR, int MTOK>
 cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
-    static bool configured = false;
+    static PerDeviceOnce configured;      // one per kernel instantiation
     auto kern = k_umma_gemm<QT, T16, BWD, PAIR, MTOK>;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    cudaError_t ce = per_device_once(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes); });
+    if (ce != cudaSuccess) return ce;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kThreads);
@@ -768,7 +764,11 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     const int tmax = L0.T < kMaxTok ? L0.T : kMaxTok;
     // CTA pairs pay off once the activation tile is the bulk of what an SM pulls from L2; small token counts are
     // weight-streaming bound and stay on single CTAs
-    static const int pair_min = getenv("GT_PAIR_MIN") ? atoi(getenv("GT_PAIR_MIN")) : 256;
+    // (a single CTA stages at most 256 token rows per operand stage, so the knob is clamped to [32, 256])
+    static const int pair_min = [] {
+        const int v = getenv("GT_PAIR_MIN") ? atoi(getenv("GT_PAIR_MIN")) : 256;
+        return v < 32 ? 32 : (v > 256 ? 256 : v);
+    }();
     const bool pair = tmax >= pair_min;
     const int tb = pair ? (tmax + 31) & ~31 : (tmax + 15) & ~15;
     // pair mode: TMA box rows = half of an MMA's token columns (64 with four 128-column accumulators)
@@ -828,7 +828,9 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     p.K = L0.w->K;
     p.units = bwd ? first : L0.w->K / 128;
     p.splits = L0.splits < 1 ? 1 : (L0.splits > p.units ? p.units : L0.splits);
-    p.atomic_out = bwd ? 1 : (p.splits > 1 || L0.out_prefilled ? 1 : 0);
+    // plain stores when one CTA owns each output tile and the output is to be written, not added to: a forward without
+    // split-K, and a backward without split-K whose caller asked for "dX =" (out_assign)
+    p.atomic_out = bwd ? ((p.splits > 1 || !L0.out_assign) ? 1 : 0) : (p.splits > 1 || L0.out_prefilled ? 1 : 0);
     const int tiles = bwd ? L0.w->K / kTileW : first;
     dim3 grid(tiles, p.splits, (L0.T + kMaxTok - 1) / kMaxTok);
     const int qt = L0.w->qtype;

@@ -133,8 +133,18 @@ GT_API int gt_adapter_grads_download(gt_adapter *ad, float *dA_in_by_rank, float
 GT_API int gt_adapter_grads_zero(gt_adapter *ad);
 /* Replaces: LoraAdapter.UpdateAlpha (src/Glacier.Tune/Model/LoraAdapter.cs:74-77). */
 GT_API int gt_adapter_set_alpha(gt_adapter *ad, float alpha);
-/* Device addresses of A, B, dA, dB (fp32) for a resident optimizer or a gradient all-reduce. */
+/* Device addresses of A, B, dA, dB (fp32) for a resident optimizer or a gradient all-reduce (any of the four may be
+ * NULL).  Asking for B raises the adapter's "B may be non-zero" flag, because the library can no longer know when B
+ * leaves its all-zero initial state (LoraAdapter.IsZeroDelta, src/Glacier.Tune/Model/LoraAdapter.cs:48-72): from then
+ * on every forward evaluates the adapter term.  A caller that writes A or B through these pointers calls
+ * gt_adapter_params_changed afterwards. */
 GT_API int gt_adapter_device_ptrs(gt_adapter *ad, float **A, float **B, float **dA, float **dB);
+/* Replaces: the scan of B inside LoraAdapter.IsZeroDelta (src/Glacier.Tune/Model/LoraAdapter.cs:48-72), which the
+ * reference repeats on the host at every forward; here the answer is cached in a device flag.  This call tells the
+ * library that A or B changed behind its back (written through the device pointers): the flag is recomputed from the
+ * values on the engine stream and X*A kept from an earlier forward is dropped.  Not needed after gt_adapter_upload or
+ * the library's own AdamW steps. */
+GT_API int gt_adapter_params_changed(gt_adapter *ad);
 /* Point the adapter's gradient accumulators into a caller-owned device buffer (one flat allocation per
  * model in the reference's parameter order, src/Glacier.Tune/Model/TransformerBlock.cs:167-174). */
 GT_API int gt_adapter_bind_grads(gt_adapter *ad, float *dA_dev, float *dB_dev);

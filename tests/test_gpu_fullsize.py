@@ -1,0 +1,156 @@
+"""GPU parity at the workloads' full sizes: every Qwen2.5-7B layer projection with its r=16 adapter through the grouped
+C-ABI calls, Y / dX / dA / dB against the CPU restatement of the reference's CPU path (oracle.proj_forward /
+proj_backward: LoraAdapter.Forward / Backward, src/Glacier.Tune/Model/LoraAdapter.cs:128-260).
+
+  * the all-Q4_K layer at M = 512 (the benchmark's workload), in the bf16 mode and in the fp16 validation mode;
+  * the Q4_K_M mix (v and down in Q6_K) swept over M = 1, 16, 128, 512, 2048 (weight streaming to compute bound).
+
+Gates: relative Frobenius error <= 2e-2 in bf16-MMA mode, <= 1e-3 in the fp16 mode (the workload definition's).
+The CPU side takes a few seconds per layer pass on the host cores.
+"""
+import numpy as np
+import pytest
+
+from glacier.tune_b200 import synth as S
+
+pytestmark = pytest.mark.gpu
+
+RANK, ALPHA = 16, 32.0
+GROUPS = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]]
+TOL = {0: 2e-2, 1: 1e-3}
+
+
+@pytest.fixture(scope="module")
+def G():
+    from glacier.tune_b200 import capi
+    return capi
+
+
+@pytest.fixture(scope="module")
+def eng(G):
+    e = G.Engine(0, G.MATH_BF16)
+    yield e
+    e.close()
+
+
+def _qtype(mix: bool, name: str) -> int:
+    return S.TYPE_Q6_K if (mix and name in ("v", "down")) else S.TYPE_Q4_K
+
+
+def _make_layer(mix: bool):
+    """Weights and adapters of one layer (seeded as the workload definition says); activations are drawn per M."""
+    layer = {}
+    cfg = 2 if mix else 1
+    for name, (N, K) in S.QWEN7B_PROJ.items():
+        qt = _qtype(mix, name)
+        seed = S.seed_for(cfg, 0, name)
+        rng = np.random.default_rng(seed + 500_000)
+        a = np.ascontiguousarray((rng.standard_normal((RANK, K), dtype=np.float32) * np.float32(0.02)).T)
+        b = np.ascontiguousarray((rng.standard_normal((N, RANK), dtype=np.float32) * np.float32(0.02)).T)
+        layer[name] = dict(qtype=qt, N=N, K=K, w=S.make_weight(qt, N, K, seed), a=a, b=b)
+    return layer
+
+
+def _upload(eng, layer):
+    for p in layer.values():
+        p["wh"] = eng.upload_weight(p["qtype"], p["w"], p["N"], p["K"])
+        p["ad"] = eng.create_adapter(p["K"], p["N"], RANK, ALPHA)
+        p["ad"].upload(p["a"], p["b"])
+
+
+def _free(layer):
+    for p in layer.values():
+        p["wh"].free()
+        p["ad"].free()
+
+
+def _check_layer(G, eng, oracle, layer, M, mode, seed):
+    """All four groups of the layer at M tokens, forward and backward, against the CPU path.  Returns the worst errors."""
+    import torch
+    eng.set_math_mode(mode)
+    rng = np.random.default_rng(seed)
+    worst = dict(Y=0.0, dX=0.0, dA=0.0, dB=0.0)
+    scaling = ALPHA / RANK
+    for names in GROUPS:
+        ps = [layer[n] for n in names]
+        K = ps[0]["K"]
+        x = S.bf16_round(rng.standard_normal((M, K), dtype=np.float32))
+        dys = [rng.standard_normal((M, p["N"]), dtype=np.float32) for p in ps]
+        X = torch.from_numpy(x).cuda()
+        dYs = [torch.from_numpy(d).cuda() for d in dys]
+        Ys = [torch.empty((M, p["N"]), dtype=torch.float32, device="cuda") for p in ps]
+        dX = torch.full((M, K), 7.0, dtype=torch.float32, device="cuda")       # stale contents: the call assigns
+        for p in ps:
+            p["ad"].zero_grads()
+        eng.forward_group([p["wh"] for p in ps], [p["ad"] for p in ps], X, Ys)
+        eng.backward_group([p["wh"] for p in ps], [p["ad"] for p in ps], dYs, X, dX, flags=G.FLAG_REUSE_LOW | G.FLAG_DX_ASSIGN)
+        eng.sync()
+        dx_ref = np.zeros((M, K), np.float32)
+        for p, dy, Y in zip(ps, dys, Ys):
+            y_ref = oracle.proj_forward(p["qtype"], p["w"], None, x, K, p["N"], M, p["a"], p["b"], RANK, scaling)
+            _, da_ref, db_ref = oracle.proj_backward(p["qtype"], p["w"], dy, x, K, p["N"], M, p["a"], p["b"], RANK, scaling, dx=dx_ref)
+            da, db = p["ad"].grads()
+            errs = dict(Y=oracle.rel_fro(Y.cpu().numpy(), y_ref), dA=oracle.rel_fro(da, da_ref), dB=oracle.rel_fro(db, db_ref))
+            for k, v in errs.items():
+                assert v < TOL[mode], (names, p["N"], M, mode, k, v)
+                worst[k] = max(worst[k], v)
+        e = oracle.rel_fro(dX.cpu().numpy(), dx_ref)
+        assert e < TOL[mode], (names, M, mode, "dX", e)
+        worst["dX"] = max(worst["dX"], e)
+    return worst
+
+
+@pytest.fixture(scope="module")
+def layer_q4k(eng):
+    layer = _make_layer(mix=False)
+    _upload(eng, layer)
+    yield layer
+    _free(layer)
+
+
+@pytest.fixture(scope="module")
+def layer_mix(eng):
+    layer = _make_layer(mix=True)
+    _upload(eng, layer)
+    yield layer
+    _free(layer)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_q4k_layer_m512_all_projections_with_adapters(G, eng, oracle, layer_q4k, mode):
+    """The benchmark's step - q,k,v | o | gate,up | down in Q4_K at M = 512, r = 16 - compared output by output."""
+    worst = _check_layer(G, eng, oracle, layer_q4k, 512, mode, seed=9001)
+    print(f"full-size Q4_K layer, mode {mode}: " + " ".join(f"{k}={v:.2e}" for k, v in worst.items()))
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 512, 2048])
+def test_q4km_mix_layer_token_sweep(G, eng, oracle, layer_mix, M):
+    """v and down in Q6_K, the others in Q4_K, at every token count of the sweep (bf16 mode)."""
+    worst = _check_layer(G, eng, oracle, layer_mix, M, 0, seed=9100 + M)
+    print(f"full-size Q4_K_M layer, M={M}: " + " ".join(f"{k}={v:.2e}" for k, v in worst.items()))
+
+
+def test_q6k_down_projection_fp16_mode_m512(G, eng, oracle, layer_mix):
+    """down 3584 x 18944 in Q6_K (the deepest contraction of the layer) in the fp16 validation mode: <= 1e-3."""
+    import torch
+    eng.set_math_mode(1)
+    p = layer_mix["down"]
+    M, K, N = 512, p["K"], p["N"]
+    rng = np.random.default_rng(9300)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    dy = rng.standard_normal((M, N), dtype=np.float32)
+    X, dY = torch.from_numpy(x).cuda(), torch.from_numpy(dy).cuda()
+    Y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    dX = torch.zeros((M, K), dtype=torch.float32, device="cuda")
+    p["ad"].zero_grads()
+    eng.forward(p["wh"], p["ad"], X, Y)
+    eng.backward(p["wh"], p["ad"], dY, X, dX)
+    eng.sync()
+    s = ALPHA / RANK
+    y_ref = oracle.proj_forward(p["qtype"], p["w"], None, x, K, N, M, p["a"], p["b"], RANK, s)
+    dx_ref, da_ref, db_ref = oracle.proj_backward(p["qtype"], p["w"], dy, x, K, N, M, p["a"], p["b"], RANK, s)
+    da, db = p["ad"].grads()
+    errs = dict(Y=oracle.rel_fro(Y.cpu().numpy(), y_ref), dX=oracle.rel_fro(dX.cpu().numpy(), dx_ref),
+                dA=oracle.rel_fro(da, da_ref), dB=oracle.rel_fro(db, db_ref))
+    assert all(v < 1e-3 for v in errs.values()), errs
+    eng.set_math_mode(0)

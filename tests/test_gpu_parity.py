@@ -82,8 +82,11 @@ def test_dequant_bit_exact(G, eng, oracle, qtype, N, K):
     w.free()
 
 
-def test_dequant_golden_fixture(G, eng):
-    d = np.load(os.path.join(GOLDEN, "dequant_golden.npz"))
+@pytest.mark.parametrize("fixture", ["dequant_golden.npz", "gguf_dequant_golden.npz"])
+def test_dequant_golden_fixture(G, eng, fixture):
+    """dequant_golden.npz comes from the numpy mirror; gguf_dequant_golden.npz from gguf.quants.dequantize, the GGUF
+    project's own decoder (tests/golden/make_gguf_golden.py): the CUDA row decoder must match both bit for bit."""
+    d = np.load(os.path.join(GOLDEN, fixture))
     for qtype, key in ((S.TYPE_Q4_K, "q4k"), (S.TYPE_Q6_K, "q6k")):
         blocks = d[f"{key}_blocks"]
         nb = blocks.shape[0]
@@ -392,3 +395,112 @@ def test_cpp_host_mirror(G, eng, oracle, tmp_path):
     yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
     assert oracle.rel_fro(y.reshape(32, 256), yr) < 2e-2 and oracle.rel_fro(dx.reshape(32, 512), dxr) < 2e-2
     assert oracle.rel_fro(da.reshape(512, 16), dar) < LTOL[0] and oracle.rel_fro(db.reshape(16, 256), dbr) < LTOL[0]
+
+
+def test_b_written_through_device_pointer_is_seen_by_the_forward(G, eng, oracle):
+    """A resident optimizer writes B through gt_adapter_device_ptrs, starting from the standard B = 0 initial state:
+    the forward must include the adapter term afterwards (asking for B's address raises the 'B may be non-zero'
+    flag; gt_adapter_params_changed recomputes it)."""
+    import torch
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 48, seed=61)
+    for mode in (0, 2):
+        eng.set_math_mode(mode)
+        w = eng.upload_weight(c["qtype"], c["w"], 256, 512)
+        ad = eng.create_adapter(512, 256, 16, 32.0)
+        ad.upload(c["a"], np.zeros_like(c["b"]))
+        y0 = eng.forward(w, ad, c["x"])                              # B == 0: base projection only
+        yb, _, _, _ = _reference(oracle, c, lora=False, bias=False)
+        assert oracle.rel_fro(y0, yb) < TOL[mode]
+        _, pb, _, _ = ad.device_ptrs()
+        b_dev = torch.from_numpy(c["b"]).cuda()
+        _memcpy_d2d(pb, b_dev)                                        # what a resident optimizer would do
+        yl, _, _, _ = _reference(oracle, c, bias=False)
+        y1 = eng.forward(w, ad, c["x"])                               # flag raised by device_ptrs: delta included
+        assert oracle.rel_fro(y1, yl) < TOL[mode], oracle.rel_fro(y1, yl)
+        ad.params_changed()
+        y2 = eng.forward(w, ad, c["x"])
+        assert oracle.rel_fro(y2, yl) < TOL[mode]
+        # and back to zero: after params_changed the delta is skipped again (bit-equal to the base projection)
+        _memcpy_d2d(pb, torch.zeros_like(b_dev))
+        ad.params_changed()
+        y3 = eng.forward(w, ad, c["x"])
+        assert np.array_equal(y3, y0)
+        w.free()
+        ad.free()
+    eng.set_math_mode(0)
+
+
+def _memcpy_d2d(dst_ptr: int, src_tensor):
+    """cudaMemcpy(dst_ptr, src_tensor): a raw device address has no torch view, so the copy goes through the CUDA
+    runtime that torch has already loaded."""
+    import ctypes
+    import torch
+    try:
+        rt = ctypes.CDLL("libcudart.so.12")
+    except OSError:
+        pytest.skip("libcudart.so.12 cannot be opened by name")
+    rt.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    rt.cudaMemcpy.restype = ctypes.c_int
+    torch.cuda.synchronize()
+    err = rt.cudaMemcpy(dst_ptr, src_tensor.data_ptr(), src_tensor.numel() * src_tensor.element_size(), 3)    # 3 = DeviceToDevice
+    assert err == 0, err
+    torch.cuda.synchronize()
+
+
+def test_clip_with_nonpositive_max_norm_leaves_gradients_alone(G, eng):
+    """ClipGradients(maxNorm <= 0) returns 0 and touches nothing, non-finite values included
+    (src/Glacier.Tune/Trainer/LoraTrainer.cs:398)."""
+    import torch
+    g = torch.ones(1000, device="cuda")
+    g[3] = float("nan")
+    g[5] = float("inf")
+    assert eng.grads_scale_clip(g, 1.0, 0.0) == 0.0
+    h = g.cpu().numpy()
+    assert np.isnan(h[3]) and np.isinf(h[5]) and np.all(np.delete(h, [3, 5]) == 1.0)
+    # a positive max_norm zeroes everything on a non-finite norm (LoraTrainer.cs:417-424)
+    assert eng.grads_scale_clip(g, 1.0, 1.0) == 0.0 and float(g.abs().sum()) == 0.0
+
+
+def test_run_twice_reproducibility(G, eng, oracle):
+    """Same inputs twice.  Outputs that one CTA writes with plain stores are bit-identical run to run: the forward
+    without split-K (enough row tiles to fill the GPU) and dX under GT_FLAG_DX_ASSIGN without split-K.  Outputs that
+    several CTAs sum with fp32 atomics (split-K partial tiles, dA, dB) may differ in the last bits from the order of the
+    additions: they are held to 1e-5 relative here, far inside the parity gates."""
+    import torch
+    eng.set_math_mode(0)
+    N, K, T = 148 * 128, 512, 256          # 148 row tiles: one wave, no split-K in the forward
+    c = S.make_projection_case(S.TYPE_Q4_K, N, K, T, seed=71)
+    w = eng.upload_weight(c["qtype"], c["w"], N, K)
+    ad = eng.create_adapter(K, N, 16, 32.0)
+    ad.upload(c["a"], c["b"])
+    X, dY = torch.from_numpy(c["x"]).cuda(), torch.from_numpy(c["dy"]).cuda()
+    outs = []
+    for _ in range(2):
+        Y = torch.empty((T, N), device="cuda")
+        dX = torch.empty((T, K), device="cuda")
+        ad.zero_grads()
+        eng.forward(w, ad, X, Y)
+        eng.backward(w, ad, dY, X, dX, flags=G.FLAG_DX_ASSIGN)
+        eng.sync()
+        da, db = ad.grads()
+        outs.append((Y.cpu().numpy(), dX.cpu().numpy(), da, db))
+    assert np.array_equal(outs[0][0], outs[1][0])            # forward, plain stores: bit-identical
+    for i in (1, 2, 3):
+        assert oracle.rel_fro(outs[0][i], outs[1][i]) < 1e-5
+    w.free()
+    ad.free()
+    # dX with one CTA per output tile (K / 128 = 148 column tiles, no split): plain stores, bit-identical
+    N2, K2 = 512, 148 * 128
+    c2 = S.make_projection_case(S.TYPE_Q4_K, N2, K2, T, seed=72)
+    w2 = eng.upload_weight(c2["qtype"], c2["w"], N2, K2)
+    dY2 = torch.from_numpy(c2["dy"]).cuda()
+    got = []
+    for _ in range(2):
+        dX2 = torch.full((T, K2), 5.0, device="cuda")
+        eng.backward(w2, None, dY2, None, dX2, flags=G.FLAG_DX_ASSIGN)
+        eng.sync()
+        got.append(dX2.cpu().numpy())
+    assert np.array_equal(got[0], got[1])
+    dxr = oracle.base_backward_f64(c2["qtype"], c2["w"], c2["dy"], K2, N2, T)
+    assert oracle.rel_fro(got[0], dxr) < 2e-2
+    w2.free()

@@ -195,3 +195,37 @@ def test_golden_fixtures(oracle):
     dx, ga, gb = oracle.proj_backward(qtype, p["w"], p["dy"], p["x"], K, N, T, p["a"], p["b"], R, s)
     for got, key in ((y, "y"), (dx, "dx"), (ga, "da"), (gb, "db")):
         assert oracle.rel_fro(got, p[key]) < 1e-6, key
+
+
+def test_decoders_match_gguf_golden_fixture(oracle):
+    """Q4_K and Q6_K decode pinned to the GGUF project's own decoder: the committed vectors were produced by
+    gguf.quants.dequantize (tests/golden/make_gguf_golden.py).  C oracle and numpy mirror must match them bit for bit."""
+    d = np.load(os.path.join(GOLDEN, "gguf_dequant_golden.npz"))
+    for qtype, key, mirror in ((S.TYPE_Q4_K, "q4k", oracle.np_dequant_q4k), (S.TYPE_Q6_K, "q6k", oracle.np_dequant_q6k)):
+        blocks, want = d[f"{key}_blocks"], d[f"{key}_weights"]
+        got_c = oracle.dequant_blocks(qtype, blocks).reshape(want.shape)
+        got_np = mirror(blocks).reshape(want.shape)
+        assert np.array_equal(got_c.view(np.uint32), want.view(np.uint32)), key
+        assert np.array_equal(got_np.view(np.uint32), want.view(np.uint32)), key
+
+
+def test_decoders_match_gguf_package_live(oracle):
+    """The same comparison against the installed gguf package on fresh seeded blocks (skipped where it is absent),
+    and a check that the committed fixture is what the generator script writes today."""
+    pytest.importorskip("gguf")
+    sys_path_root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_gguf_golden", os.path.join(sys_path_root, "tests", "golden", "make_gguf_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    q4, q6 = gen.draw_blocks()
+    w4, w6 = gen.gguf_decode(q4, q6)
+    d = np.load(os.path.join(GOLDEN, "gguf_dequant_golden.npz"))
+    assert np.array_equal(q4, d["q4k_blocks"]) and np.array_equal(q6, d["q6k_blocks"])
+    assert np.array_equal(w4.view(np.uint32), d["q4k_weights"].view(np.uint32))
+    assert np.array_equal(w6.view(np.uint32), d["q6k_weights"].view(np.uint32))
+    rng = np.random.default_rng(77)
+    q4, q6 = S.make_q4k_blocks(257, rng), S.make_q6k_blocks(257, rng)
+    w4, w6 = gen.gguf_decode(q4, q6)
+    assert np.array_equal(oracle.dequant_blocks(S.TYPE_Q4_K, q4).reshape(w4.shape).view(np.uint32), w4.view(np.uint32))
+    assert np.array_equal(oracle.dequant_blocks(S.TYPE_Q6_K, q6).reshape(w6.shape).view(np.uint32), w6.view(np.uint32))

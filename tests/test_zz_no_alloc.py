@@ -38,11 +38,25 @@ def test_static_scratch_backward_matches_regular_entry_point():
             want = base.clone()
             got = base.clone()
             eng.launch_gemm_bwd(w, want, dY, T)
-            eng.launch_gemm_bwd_static(w, got, dY, T)
+            eng.launch_gemm_bwd_static(w, got, dY, T)      # first call on this device: looks the array's address up
             eng.sync()
             torch.cuda.synchronize()
             assert _rel(got.cpu().numpy(), want.cpu().numpy()) < TOL
             assert float((got - base).abs().max()) > 0.0          # it really accumulated something
+            # and against the CPU restatement of the reference's input-gradient product (bf16 operands: 2e-2)
+            from oracle import oracle as O
+            O.build()
+            ref = O.base_backward_f64(qtype, c["w"], c["dy"], K, N, T)
+            assert _rel(got.cpu().numpy().astype(np.float64) - 0.25, ref) < 2e-2
+            # the point of the entry point: a call takes no device memory (free memory is the same before and after)
+            again = base.clone()
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info()
+            eng.launch_gemm_bwd_static(w, again, dY, T)
+            eng.sync()
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, (free_before, free_after)
+            assert _rel(again.cpu().numpy(), want.cpu().numpy()) < TOL
             w.free()
         # a size beyond the fixed array is refused with a clear message and launches nothing
         N, K, T = 18944, 256, 512
