@@ -348,6 +348,15 @@ def run_ours(args) -> None:
 
     # ---- device-resident timing.  The clock sampler starts before the warm-up, and the warm-up runs for at
     # least half a second so that the clocks have ramped and nvidia-smi has samples taken under load.
+    if args.launch_list:
+        # a short eager run for a profiler's launch list: W warm-up steps, K steps, no timing, no other legs
+        for _ in range(args.warmup + args.steps):
+            l2_flush.zero_()
+            step_resident()
+        eng.sync()
+        emit(json.dumps({"launch_list": True, "steps": args.steps, "warmup": args.warmup, "config": workload_config(world, args.q4km)}))
+        eng.close()
+        return
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -647,6 +656,7 @@ def main() -> None:
     ap.add_argument("--sweep-m", type=int, nargs="+", default=[1, 16, 128, 512, 2048])
     ap.add_argument("--e2e-steps", type=int, default=50, help="timed steps of the end-to-end (host-buffer) leg, after 5 warm steps")
     ap.add_argument("--sustained-steps", type=int, default=800, help="steps of the second, long measurement that the clock samples cover")
+    ap.add_argument("--launch-list", action="store_true", help="eager warm-up + steps only (for a profiler's launch list); prints no benchmark value")
     ap.add_argument("--no-parity", action="store_true", help="skip the comparison of the last step's outputs with the CPU path")
     args = ap.parse_args()
     if args.sweep:

@@ -13,7 +13,7 @@ import numpy as np
 
 from . import build as _build
 
-TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
+TYPE_F32, TYPE_F16, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 12, 14
 MATH_BF16, MATH_FP16, MATH_FP32 = 0, 1, 2
 DIR_FORWARD, DIR_BACKWARD = 0, 1
 FLAG_DEVICE_PTRS, FLAG_NO_LORA, FLAG_REUSE_LOW, FLAG_DX_ASSIGN, FLAG_HOST_ASYNC = 1, 2, 4, 8, 16
@@ -23,7 +23,7 @@ EXPORTS = [
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_params_changed", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
-    "gt_rmsnorm_backward", "gt_add",
+    "gt_rmsnorm_backward", "gt_add", "gt_lm_head_loss", "gt_lm_head_logits", "gt_embedding_forward", "gt_attention_forward", "gt_attention_backward", "gt_supports_attention",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_adamw_step", "gt_adapter_adamw_step", "gt_adapters_adamw_step",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
@@ -91,6 +91,12 @@ def load_library(path: str | None = None) -> C.CDLL:
                             C.c_int32, C.c_int32]
     lib.gt_rmsnorm_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
     lib.gt_rmsnorm_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float]
+    lib.gt_lm_head_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
+    lib.gt_lm_head_logits.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
+    lib.gt_embedding_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]
+    lib.gt_attention_forward.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 4
+    lib.gt_attention_backward.argtypes = [C.c_void_p] * 10 + [C.c_int32] * 4
+    lib.gt_supports_attention.argtypes = [C.c_int32, C.c_int32]
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
@@ -278,6 +284,49 @@ class Engine:
     def rmsnorm_backward(self, dy, x, w, dx, eps: float = 1e-6):
         _check(self.lib.gt_rmsnorm_backward(self.h, _ptr(dy)[0], _ptr(x)[0], _ptr(w)[0], _ptr(dx)[0], x.shape[0], x.shape[1], eps))
         return dx
+
+    # ---- attention (device tensors)
+    def attention_forward(self, q, k, v, out, lse, T: int, heads_q: int, heads_kv: int, head_dim: int = 128):
+        _check(self.lib.gt_attention_forward(self.h, _ptr(q)[0], _ptr(k)[0], _ptr(v)[0], _ptr(out)[0], _ptr(lse)[0], T, heads_q, heads_kv, head_dim))
+        return out
+
+    def attention_backward(self, d_out, q, k, v, out, lse, dq, dk, dv, T: int, heads_q: int, heads_kv: int, head_dim: int = 128):
+        _check(self.lib.gt_attention_backward(self.h, _ptr(d_out)[0], _ptr(q)[0], _ptr(k)[0], _ptr(v)[0], _ptr(out)[0], _ptr(lse)[0],
+                                              _ptr(dq)[0], _ptr(dk)[0], _ptr(dv)[0], T, heads_q, heads_kv, head_dim))
+        return dq, dk, dv
+
+    # ---- LM head
+    def lm_head_loss(self, w: "Weight", hidden, labels, want_grad: bool = True, loss_dev=None, valid_dev=None, d_hidden=None):
+        """Streaming cross-entropy over the LM head.  Host numpy in -> (loss, valid, dHidden or None); device tensors
+        (hidden, labels int32, loss_dev [1] fp32, valid_dev [1] int32 or None, d_hidden or None) -> queued, returns None."""
+        hp, dev = _ptr(hidden, np.float32)
+        T = hidden.shape[0]
+        if dev:
+            _check(self.lib.gt_lm_head_loss(self.h, w.h, hp, _ptr(labels)[0], T, _ptr(loss_dev)[0], _ptr(valid_dev)[0],
+                                            _ptr(d_hidden)[0], FLAG_DEVICE_PTRS))
+            return None
+        labels = np.ascontiguousarray(labels, np.int32)
+        loss, valid = C.c_float(), C.c_int32()
+        dh = np.empty((T, w.K), np.float32) if want_grad else None
+        _check(self.lib.gt_lm_head_loss(self.h, w.h, hp, _ptr(labels)[0], T, C.cast(C.byref(loss), C.c_void_p), C.cast(C.byref(valid), C.c_void_p),
+                                        _ptr(dh)[0], 0))
+        return loss.value, valid.value, dh
+
+    def lm_head_logits(self, w: "Weight", hidden, logits):
+        _check(self.lib.gt_lm_head_logits(self.h, w.h, _ptr(hidden)[0], _ptr(logits)[0], hidden.shape[0], FLAG_DEVICE_PTRS))
+        return logits
+
+    def embedding(self, w: "Weight", tokens, out=None):
+        """Rows tokens[t] of the embedding tensor as fp32 (host numpy or device tensors)."""
+        tp, dev = _ptr(tokens)
+        T = tokens.shape[0]
+        if not dev:
+            tokens = np.ascontiguousarray(tokens, np.int32)
+            tp = _ptr(tokens)[0]
+            if out is None:
+                out = np.empty((T, w.K), np.float32)
+        _check(self.lib.gt_embedding_forward(self.h, w.h, tp, T, _ptr(out)[0], FLAG_DEVICE_PTRS if dev else 0))
+        return out
 
     def launch_gemm_batch(self, w: "Weight", Y, X, batch: int, residual=None):
         yp, _ = _ptr(Y)

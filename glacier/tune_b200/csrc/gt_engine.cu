@@ -14,127 +14,25 @@
 #include <new>
 #include <vector>
 
-#include "../../../include/glaciertune_b200.h"
-#include "gt_internal.h"
-#include "gt_quant.cuh"
+#include "gt_engine_priv.h"
 
 using namespace gt;
 
+namespace gt {
 namespace {
-
 thread_local char g_err[512] = "";
-
-int fail(int code, const char *fmt, ...) {
+}
+int failf(int code, const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
 }
+}  // namespace gt
+#define fail gt::failf
 
-#define GT_CUDA(call)                                                                                   \
-    do {                                                                                                \
-        cudaError_t _e = (call);                                                                        \
-        if (_e != cudaSuccess) return fail(GT_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(_e)); \
-    } while (0)
-
-#define GT_LAUNCH(eng, call) \
-    do {                       \
-        GT_CUDA(call);         \
-        (eng)->kernel_launches += 1; \
-    } while (0)
-
-// grow-only device buffer (the reference engine grows its scratch x2 on demand and never shrinks:
-// src/Glacier.Tune/Gpu/GpuLoraEngine.Memory.cs:7-114)
-struct Scratch {
-    void *p = nullptr;
-    size_t cap = 0;
-    cudaError_t reserve(size_t bytes) {
-        if (bytes <= cap) return cudaSuccess;
-        if (p) cudaFree(p);
-        p = nullptr;
-        cap = 0;
-        size_t want = bytes + bytes / 4;
-        cudaError_t e = cudaMalloc(&p, want);
-        if (e == cudaSuccess) cap = want;
-        return e;
-    }
-    void release() {
-        if (p) cudaFree(p);
-        p = nullptr;
-        cap = 0;
-    }
-};
-
-}  // namespace
-
-constexpr int kHostSlots = 8;
-constexpr int kSlotIn = 4, kSlotOut = 4;      // forward: X -> Y_j; backward: dY_j, X -> dX; FFN: X -> Y, gate, up, hidden
-struct HostSlot {
-    Scratch in[kSlotIn], out[kSlotOut];
-    cudaEvent_t h2d_done = nullptr, compute_done = nullptr, d2h_done = nullptr;
-    bool used = false;
-};
-
-struct gt_engine {
-    int device = 0;
-    int math_mode = GT_MATH_BF16;
-    int sm_count = 148;
-    cudaStream_t stream = nullptr;
-    bool own_stream = false;
-    std::mutex mu;
-    int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
-    double *clip = nullptr;      // device double[2]
-    Scratch x16, dy16, dlow, ytmp;
-    Scratch ffn[3];              // gate, up, hidden (forward) / dHidden, dGate, dUp (backward) of the fused FFN calls
-    // Host-buffer calls: a ring of staging slots and two copy streams, so that the upload of one call, the kernels
-    // of the previous one and the download of the one before run at the same time (GT_FLAG_HOST_ASYNC), and a
-    // synchronous call still overlaps its own download with nothing in its way.
-    HostSlot slots[kHostSlots];
-    int slot_next = 0;
-    cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
-    // overlapped gradient exchange: collectives queued on a side stream between a fork and a join of the engine stream
-    cudaStream_t s_comm = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-    // dA = s * X^T * dLow needs only the pass over dY, not the dX GEMM that follows it: it runs on a side stream beside
-    // that GEMM (fork after the dY pass, join after the GEMM launch), so its launch gap and tail hide under the GEMM
-    cudaStream_t s_aux = nullptr;
-    cudaEvent_t ev_aux_fork = nullptr, ev_aux_join = nullptr;
-    bool aux_pending = false;
-    bool comm_pending = false;
-    ncclComm_t comm = nullptr;    // data-parallel communicator (gt_dp_init)
-    int dp_world = 1, dp_rank = 0;
-    // profiling: CUDA-event pairs around every tensor-core GEMM launch, and a count of kernel launches
-    bool profile = false;
-    std::vector<cudaEvent_t> ev_pool;
-    size_t ev_used = 0;
-    double gemm_flops = 0.0;
-    int64_t gemm_launches = 0, kernel_launches = 0;
-    void *trace = nullptr;       // device timeline buffer handed to the next GEMM launches (gt_debug_set_trace)
-};
-
-struct gt_weight {
-    gt_engine *eng = nullptr;
-    WeightDev dev;
-};
-
-struct gt_adapter {
-    gt_engine *eng = nullptr;
-    int in = 0, out = 0, rank = 0;
-    float alpha = 0.f, scaling = 0.f;
-    float *A = nullptr, *B = nullptr, *dA = nullptr, *dB = nullptr;
-    bool own_grads = true;
-    int *b_nonzero = nullptr;    // device flag: any(B != 0), refreshed whenever B is uploaded
-    Scratch low;                 // low = X*A of the last forward / backward through this adapter, then dLow = dY*B^T;
-                                 // [low_T, rank] fp32 each
-    int low_T = 0;
-    bool dlow_clean = false;     // dLow is still all zero (cleared together with low, not yet summed into)
-    Scratch xkeep;               // host-buffer calls: device copy of the X of the last forward, for a backward that
-    int xkeep_T = 0;             // reuses it (GT_FLAG_REUSE_LOW) instead of uploading X again
-    Scratch moments;             // AdamW state [mA | vA | mB | vB], allocated and zeroed by the first optimizer step
-};
-
-namespace {
+namespace gt {
 
 int check_status(gt_engine *e) {
     int h[4] = {0, 0, 0, 0};
@@ -179,7 +77,6 @@ cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const cha
     return ce;
 }
 
-constexpr int kMaxGroup = 3;
 
 // Members of one quantization type form one GEMM launch; a Q4_K_M mix (q, k in Q4_K, v in Q6_K) takes two.
 // order[] lists the member indices type by type, count[] the size of each run.
@@ -741,7 +638,7 @@ const char *gt_version(void) { return "glaciertune_b200 0.1 (sm_100a)"; }
 
 int gt_supports(int ggml_type, int direction) {
     if (direction != GT_DIR_FORWARD && direction != GT_DIR_BACKWARD) return 0;
-    return (ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K || ggml_type == GT_TYPE_F32) ? 1 : 0;
+    return (ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K || ggml_type == GT_TYPE_F32 || ggml_type == GT_TYPE_F16) ? 1 : 0;
 }
 
 int gt_engine_create(const gt_config *cfg, gt_engine **out) {
@@ -796,7 +693,7 @@ int gt_engine_destroy(gt_engine *e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     if (e->s_h2d) cudaStreamSynchronize(e->s_h2d);
     if (e->s_d2h) cudaStreamSynchronize(e->s_d2h);
-    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->ffn[0], &e->ffn[1], &e->ffn[2]};
+    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->ffn[0], &e->ffn[1], &e->ffn[2], &e->ce, &e->ce_host, &e->attn};
     for (Scratch *s : all) s->release();
     for (HostSlot &sl : e->slots) {
         for (Scratch &b : sl.in) b.release();
@@ -904,6 +801,8 @@ int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_
     int64_t expect;
     if (ggml_type == GT_TYPE_F32) {
         expect = nelem * 4;
+    } else if (ggml_type == GT_TYPE_F16) {
+        expect = nelem * 2;
     } else {
         if (nelem % 256 != 0 || in_features % 32 != 0)
             return fail(GT_ERR_INVALID, "K-quant tensor [%d, %d] is not a whole number of 256-weight super-blocks", out_features,
@@ -945,7 +844,8 @@ int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_
         gt_weight_free(w);
         return fail(ce == cudaErrorMemoryAllocation ? GT_ERR_OOM : GT_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(ce));
     }
-    if (ggml_type != GT_TYPE_F32 && in_features % 256 == 0) d.row_bytes = (int64_t)(in_features / 256) * dev_block_bytes(ggml_type);
+    if (ggml_type == GT_TYPE_F16) d.row_bytes = (int64_t)in_features * 2;
+    else if (ggml_type != GT_TYPE_F32 && in_features % 256 == 0) d.row_bytes = (int64_t)(in_features / 256) * dev_block_bytes(ggml_type);
     const char *msg = nullptr;
     if (umma_init_weight_maps(&d, &msg) != cudaSuccess) {
         gt_weight_free(w);

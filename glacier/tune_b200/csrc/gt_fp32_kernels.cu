@@ -49,6 +49,7 @@ cudaError_t launch_dequant_rows(int qt, const uint8_t *w, int K, int64_t row0, i
     const unsigned blocks = (unsigned)((total + threads - 1) / threads > 148 * 16 ? 148 * 16 : (total + threads - 1) / threads);
     if (qt == kTypeQ4K) k_dequant_rows<kTypeQ4K><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     else if (qt == kTypeQ6K) k_dequant_rows<kTypeQ6K><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
+    else if (qt == kTypeF16) k_dequant_rows<kTypeF16><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     else k_dequant_rows<kTypeF32><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     return cudaGetLastError();
 }
@@ -170,6 +171,7 @@ cudaError_t launch_gemm_fp32_fwd(int qt, const uint8_t *w, const float *X, float
     dim3 grid((N + FT - 1) / FT, (T + FT - 1) / FT);
     if (qt == kTypeQ4K) k_gemm_fp32_fwd<kTypeQ4K><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     else if (qt == kTypeQ6K) k_gemm_fp32_fwd<kTypeQ6K><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
+    else if (qt == kTypeF16) k_gemm_fp32_fwd<kTypeF16><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     else k_gemm_fp32_fwd<kTypeF32><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     return cudaGetLastError();
 }
@@ -178,6 +180,7 @@ cudaError_t launch_gemm_fp32_bwd(int qt, const uint8_t *w, const float *dY, floa
     dim3 grid((K + FT - 1) / FT, (T + FT - 1) / FT);
     if (qt == kTypeQ4K) k_gemm_fp32_bwd<kTypeQ4K><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     else if (qt == kTypeQ6K) k_gemm_fp32_bwd<kTypeQ6K><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
+    else if (qt == kTypeF16) k_gemm_fp32_bwd<kTypeF16><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     else k_gemm_fp32_bwd<kTypeF32><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     return cudaGetLastError();
 }

@@ -135,6 +135,9 @@ struct UmmaLaunch {
     int splits = 1;
     int *status = nullptr;              // device int[4]
     void *trace = nullptr;              // optional device int64[12*128] timeline buffer
+    // a window of the weight's rows [row_base, row_base + rows) instead of all of them (rows == 0: the whole tensor):
+    // the vocabulary tiles of the LM head.  `out` / `act16` then belong to the window (column 0 = row row_base).
+    int row_base = 0, rows = 0;
 };
 int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count);
 // Returns cudaSuccess or an error; `err` receives a description on failure of a non-CUDA kind.

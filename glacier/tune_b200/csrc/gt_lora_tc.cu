@@ -558,9 +558,13 @@ __global__ void __launch_bounds__(256, 2) k_lora_da_tc(const DaParams p) {
     }
 }
 
-// token groups so that (column strips x groups) covers the SMs about `waves` times; groups are whole 64-token tiles
+// Two blocks are resident per SM (registers and the 64 KiB ring): a launch should fit ONE wave of kSlots blocks, or a
+// second, nearly empty wave doubles its time (400 blocks of 3 strips on 296 slots ran as 2 x 3 strips; 296 blocks of 4
+// strips run as 1 x 4).
+constexpr int kSlots = 2 * 148;
+// token groups so that (column strips x groups) fills one wave; groups are whole 64-token tiles
 void pick_groups(int strips, int T, int &groups, int &tpg) {
-    groups = (3 * 148 + strips - 1) / (strips > 0 ? strips : 1);
+    groups = kSlots / (strips > 0 ? strips : 1);
     const int max_groups = (T + TT - 1) / TT;
     if (groups > max_groups) groups = max_groups;
     if (groups < 1) groups = 1;
@@ -568,16 +572,18 @@ void pick_groups(int strips, int T, int &groups, int &tpg) {
     tpg = (tpg + TT - 1) / TT * TT;
     groups = (T + tpg - 1) / tpg;
 }
-// strips per block for the kernels that walk strips: about three blocks per SM, at most 8 strips in a run
-int pick_strip_run(int strips_total, int T) {
+// strips per block for the kernels that walk strips: the smallest run for which every member's chunks x token tiles x
+// members fit one wave (`strips_max` = strips of the widest member, `members` = grid.z)
+int pick_strip_run(int strips_max, int members, int T) {
     const int tiles = (T + TT - 1) / TT;
-    int run = (strips_total * tiles + 3 * 148 - 1) / (3 * 148);
+    int run = 1;
+    while (run < strips_max && ((strips_max + run - 1) / run) * tiles * members > kSlots) run++;
     static const int forced = [] {
         const char *v = getenv("GT_LORA_RUN");
         return v ? atoi(v) : 0;
     }();
     if (forced > 0) run = forced;
-    return run < 1 ? 1 : (run > 8 ? 8 : run);
+    return run < 1 ? 1 : run;
 }
 // GT_LORA_RING=0 turns the cp.async ring off (one tile of prefetch in registers instead): a measurement knob
 int ring_enabled() {
@@ -621,7 +627,7 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
     (void)fp16;      // bf16 math mode only: the shared-memory tile and the 16-bit copy are the same bf16 values
     p.T = T;
     p.K = K;
-    p.strips_per_block = pick_strip_run(strips, T);
+    p.strips_per_block = pick_strip_run(strips, 1, T);
     p.ring = ring_enabled();
     dim3 grid((T + TT - 1) / TT, (strips + p.strips_per_block - 1) / p.strips_per_block);
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
@@ -652,9 +658,14 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
         strips_sum += st;
         strips_max = st > strips_max ? st : strips_max;
     }
+    // members per launch (grid.z): every 16-rank chunk of every member is one, up to kMaxChunks per launch
+    int n_chunks = 0;
+    for (int j = 0; j < n; j++) n_chunks += (jobs[j].R + 15) / 16;
+    const int n_launch_members = n_chunks < kMaxChunks ? (n_chunks > 0 ? n_chunks : 1) : kMaxChunks;
+    (void)strips_sum;
     DyParams p{};
     p.T = T;
-    p.strips_per_block = pick_strip_run(strips_sum, T);
+    p.strips_per_block = pick_strip_run(strips_max, n_launch_members, T);
     p.ring = ring_enabled();
     const dim3 grid_xy((strips_max + p.strips_per_block - 1) / p.strips_per_block, (T + TT - 1) / TT);
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch

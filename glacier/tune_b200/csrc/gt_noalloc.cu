@@ -65,7 +65,7 @@ extern "C" int gt_launch_gemm_bwd_static(gt_engine *eng, const gt_weight *w, flo
     std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(engine_view(eng).mutex));
     const EngineView ev = engine_view(eng);
     const WeightDev *wd = weight_view(w);
-    if (ev.math_mode == GT_MATH_FP32 || !wd->tma_ok)
+    if (ev.math_mode == GT_MATH_FP32 || !wd->tma_ok || (wd->qtype != kTypeQ4K && wd->qtype != kTypeQ6K))
         return set_last_error(GT_ERR_UNSUPPORTED,
                               "gt_launch_gemm_bwd_static serves K-quant weights with in_features % 256 == 0 in the bf16/fp16 "
                               "math modes only; use gt_launch_gemm_bwd");

@@ -19,6 +19,7 @@
 namespace gt {
 
 constexpr int kTypeF32 = 0;
+constexpr int kTypeF16 = 1;       // plain fp16 rows (embedding and LM-head tensors)
 constexpr int kTypeQ4K = 12;
 constexpr int kTypeQ6K = 14;
 constexpr int kQ4KBlockBytes = 144;
@@ -82,6 +83,8 @@ template <int QT>
 __device__ __forceinline__ float decode_flat(const uint8_t *w, int64_t e) {
     if constexpr (QT == kTypeF32) {
         return ((const float *)w)[e];
+    } else if constexpr (QT == kTypeF16) {
+        return __half2float(((const __half *)w)[e]);
     } else if constexpr (QT == kTypeQ4K) {
         return q4k_decode_elem(w + (e >> 8) * kQ4KBlockBytes, (int)(e & 255));
     } else {
@@ -114,6 +117,17 @@ struct QuantStage<kTypeQ6K> {
     __host__ __device__ static constexpr int hdr_x(int /*half*/) { return 0; }
     __host__ __device__ static constexpr int q0_x(int half) { return 32 + 64 * half; }
     __host__ __device__ static constexpr int q1_x(int half) { return 160 + 32 * half; }
+};
+
+// fp16 rows need no staging area and no decoder: TMA writes them straight into the operand stage.  The constants only
+// keep the kernel's (unused) packed-block ring well-formed.
+template <>
+struct QuantStage<kTypeF16> {
+    static constexpr int kHdrBytes = 16, kQ0Bytes = 64, kQ1Bytes = 0;
+    static constexpr int kBlockBytes = 512;
+    __host__ __device__ static constexpr int hdr_x(int) { return 0; }
+    __host__ __device__ static constexpr int q0_x(int) { return 0; }
+    __host__ __device__ static constexpr int q1_x(int) { return 0; }
 };
 
 template <typename T16>
@@ -176,7 +190,9 @@ __device__ __forceinline__ void dequant32_to_swizzled_row(const uint8_t *hdr_row
                                                           const uint8_t *q1_row, int rsw0, int rsw1, int half, int grp,
                                                           uint32_t dst_row, int swz, int chunk0) {
     constexpr bool kFast = std::is_same<T16, __nv_bfloat16>::value;
-    if constexpr (QT == kTypeQ4K) {
+    if constexpr (QT == kTypeF16) {
+        // never called: fp16 tiles are written by TMA
+    } else if constexpr (QT == kTypeQ4K) {
         const uint4 h = *reinterpret_cast<const uint4 *>(hdr_row);
         const float d = half_bits_to_f32(h.x & 0xFFFFu);
         const float dmin = half_bits_to_f32(h.x >> 16);

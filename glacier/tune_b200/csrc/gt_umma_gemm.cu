@@ -85,6 +85,7 @@ struct Member {
     const float *lora_act;              // fp32 [T, R]: X*A (forward) or dY*B^T (backward); scaled by lora_scale in the kernel
     const int *lora_flag;
     float lora_scale;
+    int row_base;                       // first weight row of the window this launch works on (0: the whole tensor)
     int rank, N, ld_out;
     int first, count;                   // forward: first tile / tiles of this member; backward: first unit / units
 };
@@ -125,6 +126,9 @@ template <int QT, typename T16, bool BWD, bool PAIR, int MTOK>
 __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant__ Params p) {
     using QS = QuantStage<QT>;
     constexpr int H = QS::kHdrBytes, Q1 = QS::kQ1Bytes;
+    // fp16 weights: no packed-block ring and no dequantization - the weight producer's TMA copies land in the operand
+    // stage itself (128-byte swizzle = the tile image the dequantizer would have written)
+    constexpr bool kDirect = QT == kTypeF16;
     constexpr int kRows = BWD ? 64 : 128;      // weight rows per raw stage
     constexpr int kSub = BWD ? 1 : 2;          // operand stages produced per raw stage
     constexpr int kNumX = kNumA;
@@ -186,7 +190,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             // full: the (leader's) producer arrival carrying the TMA bytes + one arrival per dequant warp (of both CTAs)
             // (every dequant warp counts twice in a normal stage, where one group of 8 produces; once in the rank-update
             // stage, where both groups produce)
-            mbar_init(bar(kBarFull + i), 1 + (PAIR ? 32 : 16));
+            // (fp16 weights: the activation producer and the weight producer, one arrival each)
+            mbar_init(bar(kBarFull + i), kDirect ? 2 : 1 + (PAIR ? 32 : 16));
             mbar_init(bar(kBarEmpty + i), 1);                    // tcgen05.commit of the stage's MMAs
         }
         mbar_init(bar(kBarAcc), 2);        // both MMA issuers commit to it
@@ -260,7 +265,39 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         // ------------------------------------------------------------------ TMA producer of the packed weights
         // (issuing a tiled copy costs the issuing thread several hundred clocks: weights and activations have a
         // producer thread each, on their own barriers)
-        if (lane < 3) {      // lane 0 arms the barrier and copies the headers, lanes 1 and 2 copy the quant regions
+        if (kDirect) {
+            // fp16 rows: lane 0 waits for the operand stage, arms the (leader's) full barrier for the bytes of both
+            // CTAs and copies this CTA's 128 rows x 64 columns; backward: lanes 0 and 1 copy the two 64-column images
+            if (lane < (BWD ? 2 : 1)) {
+                Ring as;
+                bool ok = true;
+                for (int u = u0; u < u1 && ok; u++) {
+                    int um = mi, rb = 0;
+                    if (BWD) um = unit_member(u, rb);
+                    const Member &W = p.m[um];
+                    for (int s = 0; s < kSub && ok; s++) {
+                        ok = mbar_wait_bounded(bar(kBarEmpty + as.idx), as.phase ^ 1u, abort_flag, p.status, kCodeProducer + 1);
+                        if (!ok) break;
+                        const uint32_t adst = sbase + kOffA + as.idx * kAStageBytes;
+                        const uint32_t fbar_local = bar(kBarFull + as.idx);
+                        const uint32_t fbar = PAIR ? mapa_cluster(fbar_local, 0) : fbar_local;
+                        if (lane == 0 && leader) mbar_arrive_expect_tx(fbar_local, (uint32_t)((PAIR ? 2 : 1) * kAStageBytes));
+                        if (BWD) {
+                            // image `lane`: weight rows rb*64.., columns tile*128 + 64*lane ..
+                            const int x = (tile * kTileW + 64 * lane) * 2, y = W.row_base + rb * 64;
+                            if (PAIR) tma_load_2d_pair(adst + lane * 8192, &W.tm_q0, x, y, fbar);
+                            else tma_load_2d(adst + lane * 8192, &W.tm_q0, x, y, fbar);
+                        } else {
+                            const int x = (u * 2 + s) * 64 * 2, y = W.row_base + ltile * kTileW;
+                            if (PAIR) tma_load_2d_pair(adst, &W.tm_q0, x, y, fbar);
+                            else tma_load_2d(adst, &W.tm_q0, x, y, fbar);
+                        }
+                        if (lane == 0) trace(0, (u - u0) * kSub + s);
+                        as.advance(kNumA);
+                    }
+                }
+            }
+        } else if (lane < 3) {      // lane 0 arms the barrier and copies the headers, lanes 1 and 2 copy the quant regions
             Ring raw;
             bool ok = true;
             for (int u = u0; u < u1 && ok; u++) {
@@ -276,6 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     sb = u >> 1; half = u & 1; row0 = ltile * kTileW;
                 }
                 const Member &W = p.m[um];
+                row0 += W.row_base;
                 const int xb = sb * QS::kBlockBytes;
                 // one copy per region: the tensor maps handed to a forward launch have 128-row boxes, the backward
                 // ones 64-row boxes
@@ -423,7 +461,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             if (dt == 0) trace(4 + 3 * g, n);
             return true;
         };
-        if (!BWD) {
+        if (kDirect) {
+            // nothing to dequantize
+        } else if (!BWD) {
             // raw stage = 128 rows x half block; group g dequantizes its 64-column half (sub-stage g)
             const int row = dt & 127, hn = dt >> 7;
             for (int ui = 0; ui < nu && ok; ui++) {
@@ -669,6 +709,23 @@ cudaError_t launch_bounded_wait_selftest(int *status, long long limit_cycles, cu
 
 cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
     w->tma_ok = false;
+    if (w->qtype == kTypeF16) {
+        // fp16 rows: 128-byte-swizzled boxes of 64 columns x 128 rows (forward) / 64 rows (backward), written straight
+        // into the operand stages
+        if (w->K % 128 != 0 || w->row_bytes == 0) return cudaSuccess;
+        bool ok16 = encode_2d(&w->tm_q0_f, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                              (uint64_t)w->row_bytes, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        ok16 = ok16 && encode_2d(&w->tm_q0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                                 (uint64_t)w->row_bytes, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (!ok16) {
+            if (err) *err = "cuTensorMapEncodeTiled failed for an fp16 weight tensor";
+            return cudaErrorInvalidValue;
+        }
+        w->tm_hdr = w->tm_q1 = w->tm_q0;
+        w->tm_hdr_f = w->tm_q1_f = w->tm_q0_f;
+        w->tma_ok = true;
+        return cudaSuccess;
+    }
     if (w->qtype != kTypeQ4K && w->qtype != kTypeQ6K) return cudaSuccess;
     if (w->K % 256 != 0 || w->row_bytes == 0) return cudaSuccess;   // flat streams run on the CUDA-core path
     const int H = w->qtype == kTypeQ4K ? 16 : 32;
@@ -701,6 +758,8 @@ cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
     return cudaSuccess;
 }
 
+static int eff_rows(const UmmaLaunch &L) { return L.rows > 0 ? L.rows : L.w->N; }
+
 static int pick_splits(int tiles, int units, int T, int sm_count) {
     const int chunks = (T + kMaxTok - 1) / kMaxTok;
     int s = sm_count / (tiles * chunks > 0 ? tiles * chunks : 1);
@@ -723,6 +782,8 @@ bool umma_group_ok(const UmmaLaunch *m, int n) {
         const WeightDev *w = m[j].w;
         if (!w || !w->tma_ok || w->qtype != m[0].w->qtype || w->K != m[0].w->K) return false;
         if (m[j].rank > 64) return false;
+        if (w->qtype == kTypeF16 && (!m[j].fp16 || m[j].rank > 0)) return false;      // fp16 rows: fp16 MMA operands, no adapter stage
+        if (m[j].row_base < 0 || m[j].row_base + eff_rows(m[j]) > w->N) return false;
         if (m[j].backward != m[0].backward || m[j].fp16 != m[0].fp16 || m[j].T != m[0].T) return false;
         if (m[0].backward && m[j].out != m[0].out) return false;       // one shared dX
     }
@@ -736,11 +797,12 @@ int umma_group_splits(const UmmaLaunch *m, int n, int sm_count) {
     int tiles = 0, units = 0;
     for (int j = 0; j < n; j++) {
         const WeightDev *w = m[j].w;
+        const int rows = eff_rows(m[j]);
         if (bwd) {
-            units += (w->N + 63) / 64;
+            units += (rows + 63) / 64;
             tiles = w->K / kTileW;
         } else {
-            int t = (w->N + kTileW - 1) / kTileW;
+            int t = (rows + kTileW - 1) / kTileW;
             if (pair) t = (t + 1) & ~1;
             tiles += t;
             units = w->K / 128;
@@ -790,8 +852,10 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
         M.tm_hdr = L0.backward ? w->tm_hdr : w->tm_hdr_f;
         M.tm_q0 = L0.backward ? w->tm_q0 : w->tm_q0_f;
         M.tm_q1 = L0.backward ? w->tm_q1 : w->tm_q1_f;
+        const int rows = eff_rows(L);
+        M.row_base = L.row_base;
         if (bwd || j == 0) {
-            const int cols = bwd ? w->N : w->K;       // contraction length of the activation operand
+            const int cols = bwd ? rows : w->K;       // contraction length of the activation operand
             if (!encode_2d(&M.tm_act, dt, 2, L.act16, (uint64_t)cols, (uint64_t)L.T, (uint64_t)L.ld_act * 2, 64, (uint32_t)p.t_box,
                            CU_TENSOR_MAP_SWIZZLE_128B)) {
                 if (err) *err = "cuTensorMapEncodeTiled failed for the activation operand";
@@ -803,7 +867,7 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
         M.out = L.out;
         M.ld_out = L.ld_out;
         M.bias = L.bias;
-        M.N = w->N;
+        M.N = rows;
         if (L.rank > 0 && L.lora_act && L.lora_w) {
             M.rank = L.rank;
             M.lora_w = L.lora_w;
@@ -813,9 +877,9 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
         }
         int count;
         if (bwd) {
-            count = (w->N + 63) / 64;
+            count = (rows + 63) / 64;
         } else {
-            count = (w->N + kTileW - 1) / kTileW;
+            count = (rows + kTileW - 1) / kTileW;
             if (pair) count = (count + 1) & ~1;      // a pair owns two adjacent tiles of ONE member; a padding tile is all out of range
         }
         M.first = first;
@@ -834,6 +898,7 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     const int tiles = bwd ? L0.w->K / kTileW : first;
     dim3 grid(tiles, p.splits, (L0.T + kMaxTok - 1) / kMaxTok);
     const int qt = L0.w->qtype;
+    if (qt == kTypeF16) return bwd ? launch_one<kTypeF16, __half, true>(p, grid, pair, s) : launch_one<kTypeF16, __half, false>(p, grid, pair, s);
     if (qt == kTypeQ4K) {
         if (!L0.fp16) return bwd ? launch_one<kTypeQ4K, __nv_bfloat16, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __nv_bfloat16, false>(p, grid, pair, s);
         return bwd ? launch_one<kTypeQ4K, __half, true>(p, grid, pair, s) : launch_one<kTypeQ4K, __half, false>(p, grid, pair, s);

@@ -43,7 +43,7 @@ typedef struct gt_weight gt_weight;
 typedef struct gt_adapter gt_adapter;
 
 /* ggml tensor type ids, as in the reference's GgufType */
-enum { GT_TYPE_F32 = 0, GT_TYPE_Q4_K = 12, GT_TYPE_Q6_K = 14 };
+enum { GT_TYPE_F32 = 0, GT_TYPE_F16 = 1, GT_TYPE_Q4_K = 12, GT_TYPE_Q6_K = 14 };
 
 enum gt_status {
     GT_OK = 0,
@@ -102,7 +102,9 @@ GT_API int gt_engine_set_math_mode(gt_engine *eng, int math_mode);
 GT_API int gt_sync(gt_engine *eng);
 
 /* Replaces: SupportsForwardGemm / SupportsBackwardGemm
- * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:13-14, GpuLoraEngine.Backward.cs:12-13).  Returns 1 or 0. */
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:13-14, GpuLoraEngine.Backward.cs:12-13).  Returns 1 or 0.
+ * Q4_K and Q6_K run on the tensor cores; F32 and F16 projections run on the exact fp32 CUDA-core kernels (F16 tensors
+ * are meant for the embedding and the LM head, whose calls below use the tensor cores). */
 GT_API int gt_supports(int ggml_type, int direction);
 
 /* Replaces: UploadBaseWeights (src/Glacier.Tune/Gpu/GpuLoraEngine.cs:240-321) for one tensor, and the
@@ -218,6 +220,50 @@ GT_API int gt_rmsnorm_forward(gt_engine *eng, const float *x, const float *w, fl
 GT_API int gt_rmsnorm_backward(gt_engine *eng, const float *dy, const float *x, const float *w, float *dx, int32_t T, int32_t H, float eps);
 /* Replaces: TensorOps.Add for the residual connections (TransformerBlock.cs:675): out = a + b (out may alias a or b). */
 GT_API int gt_add(gt_engine *eng, const float *a, const float *b, float *out, int64_t n);
+
+/* ---- causal attention with grouped KV heads (device tensors, asynchronous on the engine stream) ------------------ */
+/* Replaces: GpuLoraEngine.SupportsAttention(seqLen, headDim) (src/Glacier.Tune/Gpu/GpuLoraEngine.cs:111).  1 or 0. */
+GT_API int gt_supports_attention(int32_t T, int32_t head_dim);
+/* Replaces: GpuLoraEngine.ForwardAttention (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:433-513, kernel
+ * tune_attn_causal_gqa_fwd, src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:527-596) and CausalAttentionKernel.Forward
+ * (src/Glacier.Tune/Kernels/CausalAttentionKernel.cs:17-78): out = softmax(q k^T / sqrt(head_dim), causal) v with
+ * head h reading KV head h / (heads_q / heads_kv).  q, out: [T, heads_q, head_dim]; k, v: [T, heads_kv, head_dim],
+ * fp32, 16-byte aligned; head_dim 128.  Instead of the reference's attnProbs [heads_q, T, T] the call keeps
+ * lse [heads_q, T] (base-2 log-sum-exp of the scaled scores) for the backward.  RoPE is not applied here: call
+ * gt_rope on q and k first (the reference engine rotates inside ForwardAttention). */
+GT_API int gt_attention_forward(gt_engine *eng, const float *q, const float *k, const float *v, float *out, float *lse, int32_t T,
+                                int32_t heads_q, int32_t heads_kv, int32_t head_dim);
+/* Replaces: GpuLoraEngine.BackwardAttention (src/Glacier.Tune/Gpu/GpuLoraEngine.Backward.cs:354-459, kernels
+ * tune_attn_causal_gqa_bwd_dq_ds / _bwd_dk_dv, tune_bwd.cu:598-717) and CausalAttentionKernel.Backward
+ * (CausalAttentionKernel.cs:80-213): dq, dk, dv are overwritten (the reference clears them first).  q, k, v, out and
+ * lse are the forward's tensors (q and k rotated); the probabilities are recomputed tile by tile, no [heads_q, T, T]
+ * buffer exists.  The gradients are those of the rotated q and k: apply gt_rope(..., inverse = 1) to dq and dk next. */
+GT_API int gt_attention_backward(gt_engine *eng, const float *d_out, const float *q, const float *k, const float *v, const float *out,
+                                 const float *lse, float *dq, float *dk, float *dv, int32_t T, int32_t heads_q, int32_t heads_kv,
+                                 int32_t head_dim);
+
+/* ---- LM head: streaming cross-entropy, logits, embedding lookup -------------------------------------------------- */
+/* Replaces: FusedCrossEntropyLoss.ComputeLossAndGradients / ComputeLoss
+ * (src/Glacier.Tune/Kernels/FusedCrossEntropyLoss.cs:22-168,170-364) with the engine calls they drive,
+ * GpuLoraEngine.ComputeTiledLmHeadLoss / ComputeTiledLmHeadLossAndGradients
+ * (src/Glacier.Tune/Gpu/GpuLoraEngine.Backward.cs:98-352): the loss of the LM head over `hidden` [T, in] against
+ * `labels` [T] (int32; a label outside [0, vocab) is ignored, as -100 is), mean over the valid tokens, and - when
+ * d_hidden is not NULL - its gradient with respect to hidden, [T, in] (zero rows for ignored tokens).  The vocabulary
+ * is walked in tiles with an online log-sum-exp on the device; the [T, vocab] logits are never formed and nothing
+ * visits the host.  lm_head is an F16 tensor [vocab, in] (in % 128 == 0); the GEMMs run with fp16 operands and fp32
+ * accumulation in every math mode.  valid_out (may be NULL) receives the number of valid tokens.
+ * With GT_FLAG_DEVICE_PTRS hidden, labels, loss_out (one float), valid_out (one int32) and d_hidden are device
+ * pointers and the call only queues work; otherwise all five are host pointers and the call is complete on return. */
+GT_API int gt_lm_head_loss(gt_engine *eng, const gt_weight *lm_head, const float *hidden, const int32_t *labels, int32_t T,
+                           float *loss_out, int32_t *valid_out_or_null, float *d_hidden_or_null, int32_t flags);
+/* Replaces: GpuLoraEngine.ComputeLmHeadLogits (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:50-81): the full
+ * logits[T, vocab] = hidden * W^T for evaluation.  Device tensors (GT_FLAG_DEVICE_PTRS), vocab % 4 == 0. */
+GT_API int gt_lm_head_logits(gt_engine *eng, const gt_weight *lm_head, const float *hidden, float *logits, int32_t T, int32_t flags);
+/* Replaces: the embedding loop of GgufLoraModel.ForwardLossAndBackward, QuantKernels.ExtractEmbedding per token
+ * (src/Glacier.Tune/Model/GgufLoraModel.cs:456-462): out[t, :] = fp32 row tokens[t] of the embedding tensor (any
+ * uploaded type).  A token outside [0, vocab) is an error on the host-pointer path (the reference throws,
+ * GgufLoraModel.cs:443-452) and yields a zero row on the device-pointer path. */
+GT_API int gt_embedding_forward(gt_engine *eng, const gt_weight *embedding, const int32_t *tokens, int32_t T, float *out, int32_t flags);
 
 /* Replaces: GpuLoraEngine.LaunchGemmBatch(type, dY, dX, dW, kCols, mRows, batch, dBias, dResidual)
  * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:83-129): device pointers, asynchronous.

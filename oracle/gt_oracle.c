@@ -44,6 +44,7 @@
 
 /* ggml type ids used by the reference's GgufType enum for the types on this path */
 #define GT_TYPE_F32 0
+#define GT_TYPE_F16 1
 #define GT_TYPE_Q4_K 12
 #define GT_TYPE_Q6_K 14
 
@@ -202,6 +203,9 @@ int64_t gt_oracle_block_bytes(int type) {
     return 0;
 }
 
+/* tensor types the row-wise routines accept: F32, F16 (plain rows) and the two K-quants */
+static int type_ok(int type) { return type == GT_TYPE_F32 || type == GT_TYPE_F16 || gt_oracle_block_bytes(type) != 0; }
+
 /* Dequantize `nblocks` consecutive super-blocks (a flat stream). */
 int gt_oracle_dequant_blocks(int type, const uint8_t *blocks, int64_t nblocks, float *dst) {
     const int64_t bb = gt_oracle_block_bytes(type);
@@ -227,6 +231,11 @@ static void dequant_row(int type, const uint8_t *w, int64_t row, int K, float *d
         memcpy(dst, (const float *)w + row * K, (size_t)K * 4);
         return;
     }
+    if (type == GT_TYPE_F16) {
+        const uint16_t *h = (const uint16_t *)w + row * K;
+        for (int k = 0; k < K; k++) dst[k] = half_bits_to_float(h[k]);
+        return;
+    }
     int64_t e0 = row * (int64_t)K;
     int64_t b0 = e0 / GT_QK_K, b1 = (e0 + K - 1) / GT_QK_K;
     float tmp[GT_QK_K];
@@ -249,7 +258,7 @@ static void dequant_row(int type, const uint8_t *w, int64_t row, int K, float *d
 }
 
 int gt_oracle_dequant_rows(int type, const uint8_t *w, int K, int64_t row0, int64_t nrows, float *dst) {
-    if (type != GT_TYPE_F32 && gt_oracle_block_bytes(type) == 0) return -1;
+    if (!type_ok(type)) return -1;
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < nrows; r++) dequant_row(type, w, row0 + r, K, dst + r * (int64_t)K);
     return 0;
@@ -330,7 +339,7 @@ static void dot_rows_f32(const float *x, const float *wt, int K, int nr, float *
 
 int gt_oracle_matmul_batch(int type, const uint8_t *w, const float *x, float *y, int K, int N, int T,
                            const float *bias) {
-    if (type != GT_TYPE_F32 && gt_oracle_block_bytes(type) == 0) return -1;
+    if (!type_ok(type)) return -1;
     enum { TILE = 64 };
     float *tile = (float *)aligned_alloc(64, (size_t)TILE * K * sizeof(float));
     if (!tile) return -2;
@@ -353,7 +362,7 @@ int gt_oracle_matmul_batch(int type, const uint8_t *w, const float *x, float *y,
 /* Same product accumulated in fp64: the arbiter for tolerance checks (not a reference path). */
 int gt_oracle_matmul_batch_f64(int type, const uint8_t *w, const float *x, double *y, int K, int N, int T,
                                const float *bias) {
-    if (type != GT_TYPE_F32 && gt_oracle_block_bytes(type) == 0) return -1;
+    if (!type_ok(type)) return -1;
     enum { TILE = 64 };
     float *tile = (float *)aligned_alloc(64, (size_t)TILE * K * sizeof(float));
     if (!tile) return -2;
@@ -448,7 +457,7 @@ int gt_oracle_proj_forward(int type, const uint8_t *w, const float *bias, const 
 int gt_oracle_accumulate_base_backward(int type, const uint8_t *w, const float *dy, float *dx, int T, int K,
                                        int N) {
     if (!w || !dy || !dx || T <= 0 || K <= 0 || N <= 0) return 0;
-    if (type != GT_TYPE_F32 && gt_oracle_block_bytes(type) == 0) return -1;
+    if (!type_ok(type)) return -1;
     enum { TILE = 64, COLB = 256 };
     const int col_blocks = (K + COLB - 1) / COLB;
     const int64_t slices = (int64_t)T * col_blocks;
@@ -489,7 +498,7 @@ int gt_oracle_accumulate_base_backward(int type, const uint8_t *w, const float *
 
 /* fp64 arbiter for dX (no accumulate-into semantics: writes the product only). */
 int gt_oracle_base_backward_f64(int type, const uint8_t *w, const float *dy, double *dx, int T, int K, int N) {
-    if (type != GT_TYPE_F32 && gt_oracle_block_bytes(type) == 0) return -1;
+    if (!type_ok(type)) return -1;
     memset(dx, 0, (size_t)T * K * sizeof(double));
     enum { TILE = 64 };
     float *tile = (float *)aligned_alloc(64, (size_t)TILE * K * sizeof(float));
@@ -723,4 +732,199 @@ void gt_oracle_adamw_step(float *p, const float *g, float *m, float *v, int64_t 
         v[i] = vi;
         p[i] = p[i] * decay - lr * (mi * c1) / (sqrtf(vi * c2) + eps);
     }
+}
+
+
+/* ---------------------------------------------------------------------------------------------
+ * Streaming cross-entropy over the LM head with its input gradient:
+ * FusedCrossEntropyLoss.ComputeLossAndGradients, CPU branch
+ * (src/Glacier.Tune/Kernels/FusedCrossEntropyLoss.cs:170-364; the loss-only form :22-168 is the same first pass).
+ *   valid tokens: 0 <= label < vocab; loss = mean over them of (logsumexp - target logit)
+ *   pass 1, vocabulary tiles of `tile` rows: logits tile by MatMulBatch; running max in fp32, running sum of
+ *           exp(logit - max) in fp64, rescaled by exp(old max - new max) when the max moves
+ *   pass 2: logits tile again; dLogit = (exp(logit - lse) - [v == target]) / valid; dHidden += dLogit * W tile
+ *           (AccumulateBaseBackward)
+ * d_hidden (may be NULL: loss only) is [T, H]; rows of ignored tokens are zero.  Returns the loss.
+ * ------------------------------------------------------------------------------------------- */
+float gt_oracle_cross_entropy(int type, const uint8_t *w, const float *hidden, const int32_t *labels, int T, int H, int V,
+                              int tile, float *d_hidden, int32_t *valid_out) {
+    if (valid_out) *valid_out = 0;
+    if (d_hidden) memset(d_hidden, 0, (size_t)T * H * sizeof(float));
+    if (!type_ok(type) || T <= 0) return 0.f;
+    int *idx = (int *)malloc((size_t)T * sizeof(int));
+    int nv = 0;
+    for (int t = 0; t < T; t++)
+        if (labels[t] >= 0 && labels[t] < V) idx[nv++] = t;
+    if (valid_out) *valid_out = nv;
+    if (nv == 0) {
+        free(idx);
+        return 0.f;
+    }
+    const float inv_valid = 1.0f / (float)nv;
+    if (tile > V) tile = V;
+    if (tile < 1) tile = 1;
+    const int n_tiles = (V + tile - 1) / tile;
+    float *xh = (float *)aligned_alloc(64, (((size_t)nv * H * sizeof(float)) + 63) & ~(size_t)63);
+    float *gh = (float *)aligned_alloc(64, (((size_t)nv * H * sizeof(float)) + 63) & ~(size_t)63);
+    float *lg = (float *)aligned_alloc(64, (((size_t)nv * tile * sizeof(float)) + 63) & ~(size_t)63);
+    float *rmax = (float *)malloc((size_t)nv * sizeof(float));
+    double *rsum = (double *)malloc((size_t)nv * sizeof(double));
+    float *tlog = (float *)malloc((size_t)nv * sizeof(float));
+    double *lse = (double *)malloc((size_t)nv * sizeof(double));
+    for (int i = 0; i < nv; i++) {
+        memcpy(xh + (size_t)i * H, hidden + (size_t)idx[i] * H, (size_t)H * sizeof(float));
+        rmax[i] = -INFINITY;
+        rsum[i] = 0.0;
+        tlog[i] = 0.f;
+    }
+    memset(gh, 0, (size_t)nv * H * sizeof(float));
+    const int64_t row_bytes = type == GT_TYPE_F32 ? (int64_t)H * 4 : (type == GT_TYPE_F16 ? (int64_t)H * 2 : (int64_t)H / GT_QK_K * gt_oracle_block_bytes(type));
+    for (int tl = 0; tl < n_tiles; tl++) {
+        const int v0 = tl * tile, vc = V - v0 < tile ? V - v0 : tile;
+        gt_oracle_matmul_batch(type, w + (int64_t)v0 * row_bytes, xh, lg, H, vc, nv, NULL);
+#pragma omp parallel for schedule(static)
+        for (int i = 0; i < nv; i++) {
+            const float *l = lg + (size_t)i * vc;
+            const int y = labels[idx[i]];
+            if (y >= v0 && y < v0 + vc) tlog[i] = l[y - v0];
+            float tmax = -INFINITY;
+            for (int v = 0; v < vc; v++) tmax = l[v] > tmax ? l[v] : tmax;
+            const float mnew = rmax[i] > tmax ? rmax[i] : tmax;
+            double tsum = 0.0;
+            for (int v = 0; v < vc; v++) tsum += (double)expf(l[v] - mnew);
+            if (isinf(rmax[i])) rsum[i] = tsum;
+            else rsum[i] = rsum[i] * exp((double)rmax[i] - (double)mnew) + tsum;
+            rmax[i] = mnew;
+        }
+    }
+    double total = 0.0;
+    for (int i = 0; i < nv; i++) {
+        lse[i] = (double)rmax[i] + log(rsum[i]);
+        total += lse[i] - (double)tlog[i];
+    }
+    if (d_hidden) {
+        for (int tl = 0; tl < n_tiles; tl++) {
+            const int v0 = tl * tile, vc = V - v0 < tile ? V - v0 : tile;
+            gt_oracle_matmul_batch(type, w + (int64_t)v0 * row_bytes, xh, lg, H, vc, nv, NULL);
+#pragma omp parallel for schedule(static)
+            for (int i = 0; i < nv; i++) {
+                float *l = lg + (size_t)i * vc;
+                const int y = labels[idx[i]];
+                for (int v = 0; v < vc; v++) {
+                    if (v0 + v == y) l[v] = (float)(exp((double)l[v] - lse[i]) - 1.0) * inv_valid;
+                    else l[v] = expf((float)((double)l[v] - lse[i])) * inv_valid;
+                }
+            }
+            gt_oracle_accumulate_base_backward(type, w + (int64_t)v0 * row_bytes, lg, gh, nv, H, vc);
+        }
+        for (int i = 0; i < nv; i++) memcpy(d_hidden + (size_t)idx[i] * H, gh + (size_t)i * H, (size_t)H * sizeof(float));
+    }
+    free(idx); free(xh); free(gh); free(lg); free(rmax); free(rsum); free(tlog); free(lse);
+    return (float)(total * (double)inv_valid);
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Causal multi-head attention with grouped KV heads, forward and backward:
+ * CausalAttentionKernel.Forward / Backward (src/Glacier.Tune/Kernels/CausalAttentionKernel.cs:17-213).
+ * q, out, d_out, dq: [T, heads_q, head_dim]; k, v, dk, dv: [T, heads_kv, head_dim]; probs: [heads_q, T, T] (the
+ * reference's storage of the softmax rows; upper triangle zero).  scale = 1 / sqrt(head_dim); head h reads KV
+ * head h / (heads_q / heads_kv).  The backward overwrites dq, dk, dv.
+ * ------------------------------------------------------------------------------------------- */
+void gt_oracle_attention_forward(const float *q, const float *k, const float *v, float *out, float *probs, int T, int HQ, int HK, int D) {
+    const int ratio = HQ / HK;
+    const float scale = 1.0f / sqrtf((float)D);
+#pragma omp parallel for schedule(dynamic)
+    for (int h = 0; h < HQ; h++) {
+        const int kh = h / ratio;
+        float *ph = probs + (size_t)h * T * T;
+        for (int i = 0; i < T; i++) {
+            const float *qv = q + ((size_t)i * HQ + h) * D;
+            float *pr = ph + (size_t)i * T;
+            float mx = -INFINITY;
+            for (int j = 0; j <= i; j++) {
+                const float *kv = k + ((size_t)j * HK + kh) * D;
+                float sc = 0.f;
+                for (int d = 0; d < D; d++) sc += qv[d] * kv[d];
+                sc *= scale;
+                pr[j] = sc;
+                if (sc > mx) mx = sc;
+            }
+            for (int j = i + 1; j < T; j++) pr[j] = 0.f;
+            float se = 0.f;
+            for (int j = 0; j <= i; j++) {
+                const float e = expf(pr[j] - mx);
+                pr[j] = e;
+                se += e;
+            }
+            const float inv = se > 0.f ? 1.0f / se : 0.f;
+            for (int j = 0; j <= i; j++) pr[j] *= inv;
+            float *ov = out + ((size_t)i * HQ + h) * D;
+            for (int d = 0; d < D; d++) ov[d] = 0.f;
+            for (int j = 0; j <= i; j++) {
+                const float p = pr[j];
+                const float *vv = v + ((size_t)j * HK + kh) * D;
+                for (int d = 0; d < D; d++) ov[d] += p * vv[d];
+            }
+        }
+    }
+}
+
+void gt_oracle_attention_backward(const float *d_out, const float *q, const float *k, const float *v, const float *probs, float *dq,
+                                  float *dk, float *dv, int T, int HQ, int HK, int D) {
+    const int ratio = HQ / HK;
+    const float scale = 1.0f / sqrtf((float)D);
+    memset(dq, 0, (size_t)T * HQ * D * sizeof(float));
+    memset(dk, 0, (size_t)T * HK * D * sizeof(float));
+    memset(dv, 0, (size_t)T * HK * D * sizeof(float));
+    float *wk = (float *)calloc((size_t)HQ * T * D, sizeof(float));
+    float *wv = (float *)calloc((size_t)HQ * T * D, sizeof(float));
+#pragma omp parallel for schedule(dynamic)
+    for (int h = 0; h < HQ; h++) {
+        const int kh = h / ratio;
+        const float *ph = probs + (size_t)h * T * T;
+        float *hk = wk + (size_t)h * T * D, *hv = wv + (size_t)h * T * D;
+        float *dp = (float *)malloc((size_t)T * sizeof(float));
+        float *ds = (float *)malloc((size_t)T * sizeof(float));
+        for (int i = 0; i < T; i++) {
+            const float *dov = d_out + ((size_t)i * HQ + h) * D;
+            const float *pr = ph + (size_t)i * T;
+            float dot = 0.f;
+            for (int j = 0; j <= i; j++) {
+                const float *vv = v + ((size_t)j * HK + kh) * D;
+                float x = 0.f;
+                for (int d = 0; d < D; d++) x += dov[d] * vv[d];
+                dp[j] = x;
+                dot += pr[j] * x;
+            }
+            for (int j = 0; j <= i; j++) ds[j] = pr[j] * (dp[j] - dot) * scale;
+            float *dqv = dq + ((size_t)i * HQ + h) * D;
+            const float *qv = q + ((size_t)i * HQ + h) * D;
+            for (int j = 0; j <= i; j++) {
+                const float s = ds[j], p = pr[j];
+                const float *kv = k + ((size_t)j * HK + kh) * D;
+                float *a = hk + (size_t)j * D, *b = hv + (size_t)j * D;
+                for (int d = 0; d < D; d++) {
+                    dqv[d] += s * kv[d];
+                    a[d] += s * qv[d];
+                    b[d] += p * dov[d];
+                }
+            }
+        }
+        free(dp);
+        free(ds);
+    }
+#pragma omp parallel for schedule(static)
+    for (int kh = 0; kh < HK; kh++)
+        for (int j = 0; j < T; j++) {
+            float *a = dk + ((size_t)j * HK + kh) * D, *b = dv + ((size_t)j * HK + kh) * D;
+            for (int h = kh * ratio; h < (kh + 1) * ratio; h++) {
+                const float *sa = wk + ((size_t)h * T + j) * D, *sb = wv + ((size_t)h * T + j) * D;
+                for (int d = 0; d < D; d++) {
+                    a[d] += sa[d];
+                    b[d] += sb[d];
+                }
+            }
+        }
+    free(wk);
+    free(wv);
 }

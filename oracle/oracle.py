@@ -6,8 +6,8 @@ TEST INFRASTRUCTURE ONLY.  Imported by ``tests/``, by ``__graft_entry__.smoke()`
 The numpy functions restate the same reference lines as the C file, independently, so the two can be
 checked against each other:
   Q4_K decode  src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:28-33,43-51,209-211,234-240
-  Q6_K decode  src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:35-40,279-289,311-315   (parity unpinned: the
-               reference has no Q6_K test or CPU source)
+  Q6_K decode  src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:35-40,279-289,311-315   (the reference has no Q6_K test or
+               CPU source; pinned instead to gguf.quants.dequantize, tests/golden/make_gguf_golden.py)
 """
 from __future__ import annotations
 
@@ -20,7 +20,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libgt_oracle.so")
 
-TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
+TYPE_F32, TYPE_F16, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 12, 14
 BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q6_K: 210}
 
 _lib = None
@@ -47,6 +47,11 @@ def lib() -> C.CDLL:
         _lib.gt_oracle_clip_gradients.restype = C.c_double
         _lib.gt_oracle_clip_gradients.argtypes = [C.c_void_p, C.c_int64, C.c_double]
         _lib.gt_oracle_block_bytes.restype = C.c_int64
+        _lib.gt_oracle_cross_entropy.restype = C.c_float
+        _lib.gt_oracle_cross_entropy.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                 C.c_void_p, C.c_void_p]
+        _lib.gt_oracle_attention_forward.argtypes = [C.c_void_p] * 5 + [C.c_int] * 4
+        _lib.gt_oracle_attention_backward.argtypes = [C.c_void_p] * 8 + [C.c_int] * 4
     return _lib
 
 
@@ -108,7 +113,11 @@ def quantize_row_q4k(src) -> np.ndarray:
 
 
 def _w(qtype, w):
-    return _f32(w).reshape(-1) if qtype == TYPE_F32 else _u8(w).reshape(-1)
+    if qtype == TYPE_F32:
+        return _f32(w).reshape(-1)
+    if qtype == TYPE_F16:
+        return np.ascontiguousarray(w, dtype=np.float16).reshape(-1)
+    return _u8(w).reshape(-1)
 
 
 def matmul_batch(qtype, w, x, K, N, T, bias=None, f64=False) -> np.ndarray:
@@ -279,3 +288,35 @@ def adamw_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step):
     lib().gt_oracle_adamw_step(_p(p), _p(g), _p(m), _p(v), C.c_int64(p.size), C.c_float(lr), C.c_float(beta1),
                                C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay), C.c_int(step))
 
+
+
+# ---- LM head and attention: see the C file for the reference lines each one restates
+def cross_entropy(qtype, w, hidden, labels, V, tile=4096, want_grad=True):
+    """FusedCrossEntropyLoss.ComputeLossAndGradients on the CPU path: (loss, valid count, dHidden or None).
+    w is the [V, H] LM head (F32 / F16 / K-quant bytes), hidden [T, H], labels int32 [T] (ignored outside [0, V))."""
+    wb, hidden = _w(qtype, w), _f32(hidden)
+    labels = np.ascontiguousarray(labels, dtype=np.int32)
+    T, H = hidden.shape
+    dh = np.empty((T, H), np.float32) if want_grad else None
+    valid = C.c_int32(0)
+    loss = lib().gt_oracle_cross_entropy(C.c_int(qtype), _p(wb), _p(hidden), _p(labels), T, H, V, tile, _p(dh), C.byref(valid))
+    return float(loss), int(valid.value), dh
+
+
+def attention_forward(q, k, v, heads_q, heads_kv, head_dim):
+    """CausalAttentionKernel.Forward: q [T, heads_q*head_dim], k / v [T, heads_kv*head_dim] -> (out, probs [heads_q, T, T])."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    T = q.shape[0]
+    out = np.empty_like(q)
+    probs = np.empty((heads_q, T, T), np.float32)
+    lib().gt_oracle_attention_forward(_p(q), _p(k), _p(v), _p(out), _p(probs), T, heads_q, heads_kv, head_dim)
+    return out, probs
+
+
+def attention_backward(d_out, q, k, v, probs, heads_q, heads_kv, head_dim):
+    """CausalAttentionKernel.Backward -> (dq, dk, dv)."""
+    d_out, q, k, v, probs = _f32(d_out), _f32(q), _f32(k), _f32(v), _f32(probs)
+    T = q.shape[0]
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    lib().gt_oracle_attention_backward(_p(d_out), _p(q), _p(k), _p(v), _p(probs), _p(dq), _p(dk), _p(dv), T, heads_q, heads_kv, head_dim)
+    return dq, dk, dv

@@ -462,10 +462,11 @@ def test_clip_with_nonpositive_max_norm_leaves_gradients_alone(G, eng):
 
 
 def test_run_twice_reproducibility(G, eng, oracle):
-    """Same inputs twice.  Outputs that one CTA writes with plain stores are bit-identical run to run: the forward
-    without split-K (enough row tiles to fill the GPU) and dX under GT_FLAG_DX_ASSIGN without split-K.  Outputs that
-    several CTAs sum with fp32 atomics (split-K partial tiles, dA, dB) may differ in the last bits from the order of the
-    additions: they are held to 1e-5 relative here, far inside the parity gates."""
+    """Same inputs twice.  Outputs that one CTA writes with plain stores are bit-identical run to run: the base forward
+    without split-K (enough row tiles to fill the GPU) and the base dX under GT_FLAG_DX_ASSIGN without split-K.
+    Whatever several CTAs sum with fp32 atomics - split-K partial tiles, X*A and dY*B^T (and through them the adapter
+    terms of Y and dX), dA, dB - may differ in the last bits from the order of the additions: held to 1e-5 relative
+    here, far inside the parity gates."""
     import torch
     eng.set_math_mode(0)
     N, K, T = 148 * 128, 512, 256          # 148 row tiles: one wave, no split-K in the forward
@@ -477,15 +478,17 @@ def test_run_twice_reproducibility(G, eng, oracle):
     outs = []
     for _ in range(2):
         Y = torch.empty((T, N), device="cuda")
+        Y0 = torch.empty((T, N), device="cuda")
         dX = torch.empty((T, K), device="cuda")
         ad.zero_grads()
+        eng.forward(w, None, X, Y0)
         eng.forward(w, ad, X, Y)
         eng.backward(w, ad, dY, X, dX, flags=G.FLAG_DX_ASSIGN)
         eng.sync()
         da, db = ad.grads()
-        outs.append((Y.cpu().numpy(), dX.cpu().numpy(), da, db))
-    assert np.array_equal(outs[0][0], outs[1][0])            # forward, plain stores: bit-identical
-    for i in (1, 2, 3):
+        outs.append((Y0.cpu().numpy(), Y.cpu().numpy(), dX.cpu().numpy(), da, db))
+    assert np.array_equal(outs[0][0], outs[1][0])            # base forward, plain stores: bit-identical
+    for i in (1, 2, 3, 4):
         assert oracle.rel_fro(outs[0][i], outs[1][i]) < 1e-5
     w.free()
     ad.free()
