@@ -23,7 +23,7 @@ EXPORTS = [
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_params_changed", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
-    "gt_rmsnorm_backward", "gt_add", "gt_lm_head_loss", "gt_lm_head_logits", "gt_embedding_forward", "gt_attention_forward", "gt_attention_backward", "gt_supports_attention",
+    "gt_rmsnorm_backward", "gt_add", "gt_lm_head_loss", "gt_lm_head_logits", "gt_embedding_forward", "gt_attention_forward", "gt_attention_backward", "gt_supports_attention", "gt_model_create", "gt_model_destroy", "gt_model_set_block", "gt_model_set_head", "gt_model_bind_grads", "gt_model_loss", "gt_model_forward_backward", "gt_model_optimizer_step",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_adamw_step", "gt_adapter_adamw_step", "gt_adapters_adamw_step",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
@@ -34,6 +34,12 @@ class GtError(RuntimeError):
     def __init__(self, code: int, msg: str):
         super().__init__(f"glaciertune_b200 error {code}: {msg}")
         self.code = code
+
+
+class GtModelConfig(C.Structure):
+    _fields_ = [("n_layers", C.c_int32), ("hidden", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32), ("rms_eps", C.c_float), ("rope_theta", C.c_float),
+                ("max_tokens", C.c_int32), ("checkpoint", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class GtConfig(C.Structure):
@@ -97,6 +103,14 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_attention_forward.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 4
     lib.gt_attention_backward.argtypes = [C.c_void_p] * 10 + [C.c_int32] * 4
     lib.gt_supports_attention.argtypes = [C.c_int32, C.c_int32]
+    lib.gt_model_create.argtypes = [C.c_void_p, C.POINTER(GtModelConfig), C.POINTER(C.c_void_p)]
+    lib.gt_model_destroy.argtypes = [C.c_void_p]
+    lib.gt_model_set_block.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.gt_model_set_head.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.gt_model_bind_grads.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int64)]
+    lib.gt_model_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32]
+    lib.gt_model_forward_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]
+    lib.gt_model_optimizer_step.argtypes = [C.c_void_p] + [C.c_float] * 6 + [C.c_double, C.c_int32, C.POINTER(C.c_double)]
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_launch_gemm_bwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
@@ -459,4 +473,76 @@ class Adapter:
     def free(self):
         if self.h:
             self.eng.lib.gt_adapter_free(self.h)
+            self.h = None
+
+
+PROJ_NAMES = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+class Model:
+    """The device-resident training step (replaces GgufLoraModel.ForwardLossAndBackward + the trainer's step tail).
+
+    ``blocks`` is a list of dicts per layer: {"w": [7 Weight], "ad": [7 Adapter or None], "norm1": fp32 [hidden],
+    "norm2": fp32 [hidden]} in the order q, k, v, o, gate, up, down."""
+
+    def __init__(self, eng: Engine, n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_tokens, rms_eps=1e-6,
+                 rope_theta=1e6, checkpoint=True):
+        self.eng = eng
+        cfg = GtModelConfig(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, ffn=ffn,
+                            vocab=vocab, rms_eps=rms_eps, rope_theta=rope_theta, max_tokens=max_tokens, checkpoint=1 if checkpoint else 0)
+        h = C.c_void_p()
+        _check(eng.lib.gt_model_create(eng.h, C.byref(cfg), C.byref(h)))
+        self.h = h
+        self.n_layers = n_layers
+        self._keep = []
+
+    def set_block(self, layer: int, weights, adapters, norm1, norm2):
+        n1 = np.ascontiguousarray(norm1, np.float32)
+        n2 = np.ascontiguousarray(norm2, np.float32)
+        self._keep.append((weights, adapters))
+        _check(self.eng.lib.gt_model_set_block(self.h, layer, Engine._ptr_array(weights),
+                                               Engine._ptr_array(adapters) if adapters is not None else None, _ptr(n1)[0], _ptr(n2)[0]))
+
+    def set_head(self, embedding: "Weight", out_norm, lm_head: "Weight"):
+        on = np.ascontiguousarray(out_norm, np.float32)
+        self._keep.append((embedding, lm_head))
+        _check(self.eng.lib.gt_model_set_head(self.h, embedding.h, _ptr(on)[0], lm_head.h))
+
+    def bind_grads(self):
+        """Returns (device address, element count) of the flat gradient buffer."""
+        p, n = C.c_void_p(), C.c_int64()
+        _check(self.eng.lib.gt_model_bind_grads(self.h, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def loss(self, tokens, labels):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        labels = np.ascontiguousarray(labels, np.int32)
+        loss, valid = C.c_float(), C.c_int32()
+        _check(self.eng.lib.gt_model_loss(self.h, _ptr(tokens)[0], _ptr(labels)[0], tokens.shape[0], C.cast(C.byref(loss), C.c_void_p),
+                                          C.cast(C.byref(valid), C.c_void_p), 0))
+        return loss.value, valid.value
+
+    def forward_backward(self, tokens, labels, loss_dev=None):
+        """Host int32 arrays -> loss (synchronous); device tensors (+ optional loss_dev [1]) -> queued, returns None."""
+        tp, dev = _ptr(tokens)
+        if dev:
+            _check(self.eng.lib.gt_model_forward_backward(self.h, tp, _ptr(labels)[0], tokens.shape[0], _ptr(loss_dev)[0], FLAG_DEVICE_PTRS))
+            return None
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        labels = np.ascontiguousarray(labels, np.int32)
+        loss = C.c_float()
+        _check(self.eng.lib.gt_model_forward_backward(self.h, _ptr(tokens)[0], _ptr(labels)[0], tokens.shape[0],
+                                                      C.cast(C.byref(loss), C.c_void_p), 0))
+        return loss.value
+
+    def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, grad_scale=1.0, max_norm=1.0, step=1,
+                       want_norm=False):
+        norm = C.c_double()
+        _check(self.eng.lib.gt_model_optimizer_step(self.h, lr, beta1, beta2, eps, weight_decay, grad_scale, max_norm, step,
+                                                    C.byref(norm) if want_norm else None))
+        return norm.value if want_norm else None
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.eng.lib.gt_model_destroy(self.h)
             self.h = None

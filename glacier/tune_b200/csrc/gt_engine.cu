@@ -70,6 +70,7 @@ cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const cha
         if (a) cudaEventRecord(a, e->stream);
     }
     cudaError_t ce = launch_umma_group(m, n, e->stream, msg);
+    if (ce != cudaSuccess) cudaGetLastError();      // a refused launch must not linger as the thread's "last error"
     if (e->profile && b) cudaEventRecord(b, e->stream);
     e->gemm_launches += 1;
     e->kernel_launches += 1;
@@ -1349,10 +1350,10 @@ int gt_dp_allreduce(gt_engine *e, float *g_dev, int64_t count, float scale) {
     return allreduce_on(e, g_dev, count, scale, e->stream);
 }
 
-int gt_dp_allreduce_begin(gt_engine *e, float *g_dev, int64_t count, float scale) {
-    if (!e || !g_dev || count < 0) return fail(GT_ERR_INVALID, "gt_dp_allreduce_begin: bad argument");
-    std::lock_guard<std::mutex> lk(e->mu);
-    GT_CUDA(cudaSetDevice(e->device));
+}  // extern "C"
+namespace gt {
+// queue the all-reduce of one slice on the side stream, after everything queued on the engine stream so far (lock held)
+int allreduce_begin_locked(gt_engine *e, float *g_dev, int64_t count, float scale) {
     if (!e->s_comm) {
         GT_CUDA(cudaStreamCreateWithFlags(&e->s_comm, cudaStreamNonBlocking));
         GT_CUDA(cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming));
@@ -1367,6 +1368,15 @@ int gt_dp_allreduce_begin(gt_engine *e, float *g_dev, int64_t count, float scale
     GT_CUDA(cudaEventRecord(e->ev_join, e->s_comm));
     e->comm_pending = true;
     return GT_OK;
+}
+}  // namespace gt
+extern "C" {
+
+int gt_dp_allreduce_begin(gt_engine *e, float *g_dev, int64_t count, float scale) {
+    if (!e || !g_dev || count < 0) return fail(GT_ERR_INVALID, "gt_dp_allreduce_begin: bad argument");
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    return allreduce_begin_locked(e, g_dev, count, scale);
 }
 
 int gt_dp_allreduce_end(gt_engine *e) {

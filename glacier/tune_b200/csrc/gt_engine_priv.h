@@ -140,6 +140,7 @@ int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *cons
 int ffn_backward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *dYd, const float *Xd,
                         const float *gate_d, const float *up_d, const float *hidden_d, float *dXd, int T, int flags);
 int join_comm(gt_engine *e);
+int allreduce_begin_locked(gt_engine *e, float *g_dev, int64_t count, float scale);
 // LM head and embedding on device tensors (gt_lmhead.cu); loss_dev / valid_dev are device scalars (may be null)
 int lm_head_loss_on_device(gt_engine *e, const gt_weight *w, const float *hidden, const int *labels, int T, float *loss_dev, int *valid_dev,
                            float *d_hidden);

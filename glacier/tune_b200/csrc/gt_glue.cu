@@ -298,6 +298,24 @@ cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const fl
     const int vec = aligned16(d_hidden) && aligned16(gate) && aligned16(up) && aligned16(d_gate) && aligned16(d_up) ? 1 : 0;
     return launch_k(k_swiglu_bwd, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, d_hidden, gate, up, d_gate, d_up, n, vec);
 }
+cudaError_t launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    return launch_k(k_add, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, a, b, out, n, aligned16(a) && aligned16(b) && aligned16(out) ? 1 : 0);
+}
+cudaError_t launch_rope(float *q, float *k, int T, int heads_q, int heads_kv, int head_dim, float freq_base, float freq_scale, int rope_dim,
+                        int inverse, cudaStream_t s) {
+    const int eff = (rope_dim > 0 && rope_dim <= head_dim) ? rope_dim : head_dim;      // RoPEKernel.cs:55
+    if (T <= 0 || eff / 2 <= 0) return cudaSuccess;
+    const int64_t items = (int64_t)T * (eff / 2) * ((q ? heads_q : 0) + (k ? heads_kv : 0));
+    return launch_k(k_rope, dim3((unsigned)((items + 255) / 256)), dim3(256), (size_t)0, s, q, k, T, heads_q, heads_kv, head_dim, freq_base,
+                    freq_scale, eff, inverse ? -1.0f : 1.0f);
+}
+cudaError_t launch_rmsnorm_fwd(const float *x, const float *w, float *y, int T, int H, float eps, cudaStream_t s) {
+    return launch_k(k_rmsnorm_fwd, dim3((unsigned)T), dim3(256), (size_t)0, s, x, w, y, H, eps);
+}
+cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, float *dx, int T, int H, float eps, cudaStream_t s) {
+    return launch_k(k_rmsnorm_bwd, dim3((unsigned)T), dim3(256), (size_t)0, s, dy, x, w, dx, H, eps);
+}
 cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
                          int sm_count, cudaStream_t s) {
     AdamwHyper h;

@@ -185,6 +185,12 @@ cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, flo
 cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,
                               cudaStream_t s);
 
+cudaError_t launch_add(const float *a, const float *b, float *out, int64_t n, int sm_count, cudaStream_t s);
+cudaError_t launch_rope(float *q, float *k, int T, int heads_q, int heads_kv, int head_dim, float freq_base, float freq_scale, int rope_dim,
+                        int inverse, cudaStream_t s);
+cudaError_t launch_rmsnorm_fwd(const float *x, const float *w, float *y, int T, int H, float eps, cudaStream_t s);
+cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, float *dx, int T, int H, float eps, cudaStream_t s);
+
 // ---- launches with programmatic dependent launch (the kernel must call pdl_wait() before touching global memory).
 // Environment GT_PDL=1 turns the attribute on; the default is plain stream order.
 bool pdl_enabled();

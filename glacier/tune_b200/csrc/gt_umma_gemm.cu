@@ -801,6 +801,7 @@ int umma_group_splits(const UmmaLaunch *m, int n, int sm_count) {
         if (bwd) {
             units += (rows + 63) / 64;
             tiles = w->K / kTileW;
+            if (pair) tiles = (tiles + 1) & ~1;
         } else {
             int t = (rows + kTileW - 1) / kTileW;
             if (pair) t = (t + 1) & ~1;
@@ -895,7 +896,10 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     // plain stores when one CTA owns each output tile and the output is to be written, not added to: a forward without
     // split-K, and a backward without split-K whose caller asked for "dX =" (out_assign)
     p.atomic_out = bwd ? ((p.splits > 1 || !L0.out_assign) ? 1 : 0) : (p.splits > 1 || L0.out_prefilled ? 1 : 0);
-    const int tiles = bwd ? L0.w->K / kTileW : first;
+    // backward: one tile per 128 input columns; a CTA pair needs an even count (fp16 tensors may have in_features %
+    // 256 == 128): the padding tile reads zero-filled weights and stores nothing
+    int tiles = bwd ? L0.w->K / kTileW : first;
+    if (bwd && pair) tiles = (tiles + 1) & ~1;
     dim3 grid(tiles, p.splits, (L0.T + kMaxTok - 1) / kMaxTok);
     const int qt = L0.w->qtype;
     if (qt == kTypeF16) return bwd ? launch_one<kTypeF16, __half, true>(p, grid, pair, s) : launch_one<kTypeF16, __half, false>(p, grid, pair, s);

@@ -41,6 +41,7 @@ extern "C" {
 typedef struct gt_engine gt_engine;
 typedef struct gt_weight gt_weight;
 typedef struct gt_adapter gt_adapter;
+typedef struct gt_model gt_model;
 
 /* ggml tensor type ids, as in the reference's GgufType */
 enum { GT_TYPE_F32 = 0, GT_TYPE_F16 = 1, GT_TYPE_Q4_K = 12, GT_TYPE_Q6_K = 14 };
@@ -311,6 +312,54 @@ GT_API int gt_adamw_step(gt_engine *eng, float *p_dev, const float *g_dev, float
 GT_API int gt_adapter_adamw_step(gt_adapter *ad, float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step);
 GT_API int gt_adapters_adamw_step(gt_engine *eng, int32_t n, gt_adapter *const *adapters, float lr, float beta1, float beta2, float eps,
                                   float weight_decay, int32_t step);
+
+/* ---- the training step of a whole model, device resident -------------------------------------------------------- */
+typedef struct gt_model_config {
+    int32_t n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab;
+    float rms_eps;        /* RMSNorm epsilon (ModelWeights.RmsNormEps)                                           */
+    float rope_theta;     /* RoPE frequency base (rope_freq_base)                                                 */
+    int32_t max_tokens;   /* longest sequence a step may carry; every activation buffer is allocated for it       */
+    int32_t checkpoint;   /* != 0: activation checkpointing - keep only the block inputs, recompute in the backward */
+    int32_t reserved[4];
+} gt_model_config;
+
+/* Replaces: the construction of GgufLoraModel's layer list (src/Glacier.Tune/Model/GgufLoraModel.cs:60-130) for the
+ * step driver below.  Allocates every activation buffer of a step once (nothing is allocated per step).  The weights
+ * and adapters are the caller's handles; the model only refers to them. */
+GT_API int gt_model_create(gt_engine *eng, const gt_model_config *cfg, gt_model **out);
+GT_API int gt_model_destroy(gt_model *m);
+/* weights / adapters: seven entries in the reference's order q, k, v, o, gate, up, down
+ * (src/Glacier.Tune/Model/TransformerBlock.cs:149-165); adapter entries (or the array) may be NULL.  attn_norm and
+ * ffn_norm are host arrays [hidden] (ModelWeights.AttnNormWeight / FfnNormWeight).  q/k/v biases ride in their weights. */
+GT_API int gt_model_set_block(gt_model *m, int32_t layer, const gt_weight *const *weights, gt_adapter *const *adapters_or_null,
+                              const float *attn_norm, const float *ffn_norm);
+/* embedding [vocab, hidden] (any uploaded type), out_norm host [hidden], lm_head F16 [vocab, hidden]. */
+GT_API int gt_model_set_head(gt_model *m, const gt_weight *embedding, const float *out_norm, const gt_weight *lm_head);
+/* Binds the gradient accumulators of every adapter into ONE flat device buffer in the reference's parameter order
+ * (layer -> q, k, v, o, gate, up, down -> A, B; TransformerBlock.cs:167-174) - what the data-parallel all-reduce, the
+ * clip and the optimizer step run over.  Call after every block is set; returns the buffer and its length. */
+GT_API int gt_model_bind_grads(gt_model *m, float **grads_dev_or_null, int64_t *count_or_null);
+/* Replaces: GgufLoraModel.ComputeLoss (src/Glacier.Tune/Model/GgufLoraModel.cs:370-426): forward only, mean
+ * cross-entropy over the valid labels.  tokens, labels: int32 [T]. */
+GT_API int gt_model_loss(gt_model *m, const int32_t *tokens, const int32_t *labels, int32_t T, float *loss_out, int32_t *valid_out_or_null,
+                         int32_t flags);
+/* Replaces: GgufLoraModel.ForwardLossAndBackward(inputTokens, targetTokens, checkpointActivations)
+ * (src/Glacier.Tune/Model/GgufLoraModel.cs:428-557) with TransformerBlock.Forward / Backward
+ * (src/Glacier.Tune/Model/TransformerBlock.cs:307-595,625-840): embedding, the blocks, final RMSNorm, streaming
+ * cross-entropy, and the reverse pass; the adapters' gradients ACCUMULATE.  With a data-parallel communicator on the
+ * engine (gt_dp_init) and a bound gradient buffer, each block's gradients are all-reduced (averaged over the ranks) on
+ * the side stream as soon as its backward is queued, last block first.
+ * Host pointers (default): tokens / labels are host arrays and the call returns the loss (complete on return; an input
+ * token outside the vocabulary is GT_ERR_INVALID as the reference throws).  GT_FLAG_DEVICE_PTRS: tokens, labels and
+ * loss_out (one float, may be NULL) are device pointers and the call only queues work. */
+GT_API int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t *labels, int32_t T, float *loss_out, int32_t flags);
+/* Replaces: the tail of a training step in LoraTrainer (src/Glacier.Tune/Trainer/LoraTrainer.cs:217-231):
+ * ScaleAccumulatedGradients(grad_scale) -> ClipGradients(max_norm; <= 0: no clipping) -> AdamW step on every adapter
+ * -> ZeroGrad, all on the device over the flat gradient buffer, after every pending gradient exchange.  `step` counts
+ * from 1.  norm_out (may be NULL) receives the pre-clip global norm and makes the call synchronous; without it the
+ * call only queues work. */
+GT_API int gt_model_optimizer_step(gt_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, float grad_scale,
+                                   double max_norm, int32_t step, double *norm_out_or_null);
 
 /* Profiling (the reference only has Stopwatch breakdowns at Debug level,
  * src/Glacier.Tune/Model/TransformerBlock.cs:311-312,582-586).  While enabled, every tensor-core GEMM launch is

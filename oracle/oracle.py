@@ -97,7 +97,7 @@ def dequant_blocks(qtype: int, blocks) -> np.ndarray:
 
 
 def dequant_rows(qtype: int, w, K: int, row0: int, nrows: int) -> np.ndarray:
-    wb = _u8(w).reshape(-1) if qtype != TYPE_F32 else _f32(w).reshape(-1)
+    wb = _w(qtype, w)
     out = np.empty((nrows, K), np.float32)
     rc = lib().gt_oracle_dequant_rows(C.c_int(qtype), _p(wb), C.c_int(K), C.c_int64(row0), C.c_int64(nrows), _p(out))
     assert rc == 0
@@ -320,3 +320,119 @@ def attention_backward(d_out, q, k, v, probs, heads_q, heads_kv, head_dim):
     dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
     lib().gt_oracle_attention_backward(_p(d_out), _p(q), _p(k), _p(v), _p(probs), _p(dq), _p(dk), _p(dv), T, heads_q, heads_kv, head_dim)
     return dq, dk, dv
+
+
+# ---- the whole step on the CPU path: TransformerBlock.Forward / Backward and GgufLoraModel.ForwardLossAndBackward
+# (src/Glacier.Tune/Model/TransformerBlock.cs:307-595,625-840, src/Glacier.Tune/Model/GgufLoraModel.cs:428-557) chained
+# from the restated operators above.  A model is a dict:
+#   cfg: n_heads, n_kv_heads, head_dim, rms_eps, rope_theta, vocab, hidden
+#   layers: list of {"norm1", "norm2": fp32 [hidden], "proj": {name: {"qtype", "w", "N", "K", "bias" or None, "a", "b",
+#           "rank", "scaling"}}} for name in q, k, v, o, gate, up, down
+#   embed: (qtype, tensor), out_norm: fp32 [hidden], lm_head: (qtype, tensor)
+PROJ_NAMES = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def _pf(p, x):
+    T = x.shape[0]
+    return proj_forward(p["qtype"], p["w"], p.get("bias"), x, p["K"], p["N"], T, p.get("a"), p.get("b"), p.get("rank", 0), p.get("scaling", 0.0))
+
+
+def _pb(p, dy, x, grads):
+    """LoraAdapter.Backward into a zero-filled dX (AutogradScratchWorkspace.Wrap); dA / dB accumulate in grads[name]."""
+    T = x.shape[0]
+    ga, gb = grads if grads is not None else (None, None)
+    dx, ga, gb = proj_backward(p["qtype"], p["w"], dy, x, p["K"], p["N"], T, p.get("a"), p.get("b"), p.get("rank", 0), p.get("scaling", 0.0),
+                               ga=ga, gb=gb)
+    return dx
+
+
+def block_forward(cfg, layer, x):
+    """Returns (out, state) - state holds what TransformerBlock.Backward reads (BlockActivationState)."""
+    T = x.shape[0]
+    P = layer["proj"]
+    HQ, HK, D = cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"]
+    n1 = rmsnorm_forward(x, layer["norm1"], cfg["rms_eps"])
+    q, k, v = _pf(P["q"], n1), _pf(P["k"], n1), _pf(P["v"], n1)
+    q, k = rope(q, k, T, HQ, HK, D, cfg["rope_theta"])
+    attn, probs = attention_forward(q, k, v, HQ, HK, D)
+    x1 = x + _pf(P["o"], attn)
+    n2 = rmsnorm_forward(x1, layer["norm2"], cfg["rms_eps"])
+    gate, up = _pf(P["gate"], n2), _pf(P["up"], n2)
+    hidden = swiglu_forward(gate, up)
+    out = x1 + _pf(P["down"], hidden)
+    return out, dict(n1=n1, q=q, k=k, v=v, probs=probs, attn=attn, x1=x1, n2=n2, gate=gate, up=up, hidden=hidden)
+
+
+def block_backward(cfg, layer, d_out, st, x_in, grads):
+    """grads: {name: (dA, dB)} accumulated in place.  Returns dX of the block input."""
+    P = layer["proj"]
+    T = x_in.shape[0]
+    HQ, HK, D = cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"]
+    d_hidden = _pb(P["down"], d_out, st["hidden"], grads.get("down"))
+    d_gate, d_up = swiglu_backward(d_hidden, st["gate"], st["up"])
+    d_n2 = _pb(P["gate"], d_gate, st["n2"], grads.get("gate")) + _pb(P["up"], d_up, st["n2"], grads.get("up"))
+    d_x1 = d_out + rmsnorm_backward(d_n2, st["x1"], layer["norm2"], cfg["rms_eps"])
+    d_attn = _pb(P["o"], d_x1, st["attn"], grads.get("o"))
+    dq, dk, dv = attention_backward(d_attn, st["q"], st["k"], st["v"], st["probs"], HQ, HK, D)
+    dq, dk = rope(dq, dk, T, HQ, HK, D, cfg["rope_theta"], inverse=True)
+    d_n1 = _pb(P["q"], dq, st["n1"], grads.get("q")) + _pb(P["k"], dk, st["n1"], grads.get("k"))
+    d_n1 = d_n1 + _pb(P["v"], dv, st["n1"], grads.get("v"))
+    return d_x1 + rmsnorm_backward(d_n1, x_in, layer["norm1"], cfg["rms_eps"])
+
+
+def new_grads(model):
+    """Zero dA / dB accumulators for every adapted projection, {layer: {name: (dA, dB)}}."""
+    out = []
+    for layer in model["layers"]:
+        g = {}
+        for name in PROJ_NAMES:
+            p = layer["proj"][name]
+            if p.get("a") is not None:
+                g[name] = (np.zeros((p["K"], p["rank"]), np.float32), np.zeros((p["rank"], p["N"]), np.float32))
+        out.append(g)
+    return out
+
+
+def flat_grads(model, grads) -> np.ndarray:
+    """The reference's parameter order: layer -> q, k, v, o, gate, up, down -> A, B."""
+    parts = []
+    for g in grads:
+        for name in PROJ_NAMES:
+            if name in g:
+                parts += [g[name][0].reshape(-1), g[name][1].reshape(-1)]
+    return np.concatenate(parts) if parts else np.zeros(0, np.float32)
+
+
+def model_forward(model, tokens):
+    cfg = model["cfg"]
+    et, ew = model["embed"]
+    H = cfg["hidden"]
+    x = np.concatenate([dequant_rows(et, ew, H, int(t), 1) for t in tokens]).astype(np.float32)
+    xs, states = [], []
+    for layer in model["layers"]:
+        xs.append(x)
+        x, st = block_forward(cfg, layer, x)
+        states.append(st)
+    return x, xs, states
+
+
+def model_loss(model, tokens, labels):
+    cfg = model["cfg"]
+    x, _, _ = model_forward(model, tokens)
+    fn = rmsnorm_forward(x, model["out_norm"], cfg["rms_eps"])
+    lt, lw = model["lm_head"]
+    loss, valid, _ = cross_entropy(lt, lw, fn, labels, cfg["vocab"], want_grad=False)
+    return loss, valid
+
+
+def model_forward_backward(model, tokens, labels, grads):
+    """GgufLoraModel.ForwardLossAndBackward: returns the loss; grads (new_grads) accumulate."""
+    cfg = model["cfg"]
+    x, xs, states = model_forward(model, tokens)
+    fn = rmsnorm_forward(x, model["out_norm"], cfg["rms_eps"])
+    lt, lw = model["lm_head"]
+    loss, _, d_fn = cross_entropy(lt, lw, fn, labels, cfg["vocab"])
+    dx = rmsnorm_backward(d_fn, x, model["out_norm"], cfg["rms_eps"])
+    for l in range(len(model["layers"]) - 1, -1, -1):
+        dx = block_backward(cfg, model["layers"][l], dx, states[l], xs[l], grads[l])
+    return loss

@@ -52,7 +52,13 @@ def test_attention_forward_backward_parity(G, eng, oracle, mode, T, HQ, HK):
     want, probs = oracle.attention_forward(q, k, v, HQ, HK, D)
     wdq, wdk, wdv = oracle.attention_backward(g, q, k, v, probs, HQ, HK, D)
     errs = dict(out=oracle.rel_fro(out, want), dq=oracle.rel_fro(dq, wdq), dk=oracle.rel_fro(dk, wdk), dv=oracle.rel_fro(dv, wdv))
-    assert all(e < TOL[mode] for e in errs.values()), errs
+    if T == 1:
+        # one key: the softmax is the constant 1, so dq and dk are zero up to rounding on both sides - compare absolutely
+        scale = float(np.abs(g).max() * np.abs(v).max())
+        assert errs["out"] < TOL[mode] and errs["dv"] < TOL[mode], errs
+        assert np.abs(dq).max() < TOL[mode] * scale and np.abs(dk).max() < TOL[mode] * scale
+    else:
+        assert all(e < TOL[mode] for e in errs.values()), errs
     eng.set_math_mode(0)
 
 
