@@ -471,6 +471,19 @@ def run_ours(args) -> None:
     h2d, d2h = e2e_h2d, e2e_d2h     # per group: X (forward) and every dY (backward) up; every Y and one dX down
 
     _log("e2e done")
+    # ---- the 28-layer training step (tokens/s): every rank takes part (per-block gradient exchange at N > 1)
+    train = None
+    if not args.no_train_step:
+        def _max(v):
+            t_ = torch.tensor([float(v)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            return float(t_.item())
+        try:
+            train = run_train_step(G, eng, dev, stream, world, rank, args.train_steps, 2, args.train_layers, barrier, _max)
+        except Exception as exc:  # noqa: BLE001 - the headline line must still print; the failure is reported in it
+            train = {"error": f"{type(exc).__name__}: {exc}"}
+        _log(f"train step {train}")
     if rank == 0:
         peaks = measured_peaks()
         gemm_tflops = prof["gemm_flops"] / (prof["gemm_ms"] * 1e-3) / 1e12 if prof["gemm_ms"] > 0 else 0.0
@@ -518,6 +531,7 @@ def run_ours(args) -> None:
             "cpu_baseline": {"value": cpu_val, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
                              "sample": f"one pass over projections {','.join(names)} ({step_flops(names) / 1e9:.1f} GFLOP), fp32 OpenMP"},
             "parity": parity,
+            "train_step": train,
             "clocks": clocks,
         }
         emit(json.dumps(line))
@@ -531,6 +545,144 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
     eng.close()
 
+
+
+# ------------------------------------------------------------------------------------------------ 28-layer training step
+STEP_WORKLOAD = ("qwen2.5-7b-architecture LoRA training step: 28 layers, hidden 3584, 28/4 heads x 128, FFN 18944, vocab 152064, "
+                 "Q4_K_M-mixed base (v, down in Q6_K), fp16 embedding and LM head, r=16 on q,k,v,o,gate,up,down, one 512-token "
+                 "sequence per GPU, activation checkpointing, streaming cross-entropy, clip 1.0, AdamW lr 2e-4")
+STEP_CFG = dict(n_layers=28, hidden=3584, n_heads=28, n_kv_heads=4, head_dim=128, ffn=18944, vocab=152064)
+ADAMW = dict(lr=2e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+
+
+def step_projection_flops(n_layers: int, checkpoint: bool = True) -> float:
+    """Base-term FLOPs of the projections in one step: forward (twice with checkpoint recompute) + dX."""
+    per_layer_fwd = step_flops() / 2.0
+    return n_layers * per_layer_fwd * (3.0 if checkpoint else 2.0)
+
+
+def build_step_model(G, eng, dev, n_layers: int, rank: int, max_tokens: int):
+    """The config-3 model on the device: seeded synthetic weights (one layer's K-quant bytes drawn on the host, the other
+    layers' quant fields derived from them by a seeded XOR - scales and mins shared), A ~ N(0, 1/sqrt(in)), B = 0."""
+    import torch
+    c = STEP_CFG
+    m = G.Model(eng, n_layers, c["hidden"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["ffn"], c["vocab"], max_tokens,
+                rms_eps=1e-6, rope_theta=1e6, checkpoint=True)
+    base = {}
+    for n in PROJ_ORDER:
+        N, K = synth.QWEN7B_PROJ[n]
+        qt = synth.TYPE_Q6_K if n in ("v", "down") else synth.TYPE_Q4_K
+        base[n] = (qt, N, K, synth.make_weight(qt, N, K, synth.seed_for(3, 0, n)))
+    keep = []
+    rng = np.random.default_rng(3000 + rank)
+    ones = np.ones(c["hidden"], np.float32)
+    for l in range(n_layers):
+        ws, ads = [], []
+        for n in PROJ_ORDER:
+            qt, N, K, w0 = base[n]
+            w = w0
+            if l > 0:
+                bb = 144 if qt == synth.TYPE_Q4_K else 210
+                blocks = w0.reshape(-1, bb).copy()
+                lo, hi = (16, 144) if qt == synth.TYPE_Q4_K else (0, 192)       # the quant bytes of a block
+                mask = np.random.default_rng(7919 * l + synth.PROJ_ORDINAL[n]).integers(0, 256, hi - lo, dtype=np.uint8)
+                blocks[:, lo:hi] ^= mask
+                w = blocks.reshape(-1)
+            bias = np.zeros(N, np.float32) if n in ("q", "k", "v") else None      # qwen2 carries q/k/v biases (zero here)
+            ws.append(eng.upload_weight(qt, w, N, K, bias))
+            ad = eng.create_adapter(K, N, RANK, ALPHA)
+            ad.upload((rng.standard_normal((K, RANK)) / np.sqrt(K)).astype(np.float32), np.zeros((RANK, N), np.float32))
+            ads.append(ad)
+        m.set_block(l, ws, ads, ones, ones)
+        keep.append((ws, ads))
+    heads = []
+    for seed in (11, 12):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed + 100 * rank)
+        t = (torch.randn((c["vocab"], c["hidden"]), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.float16)
+        heads.append(eng.upload_weight(G.TYPE_F16, t.cpu().numpy(), c["vocab"], c["hidden"]))
+        del t
+    m.set_head(heads[0], ones, heads[1])
+    _, n_grads = m.bind_grads()
+    torch.cuda.empty_cache()
+    return m, keep, heads, n_grads
+
+
+def run_train_step(G, eng, dev, stream, world: int, rank: int, steps: int, warmup: int, n_layers: int, barrier, allreduce_max) -> dict:
+    """The full training step on this rank's own sequence; with a communicator on the engine every block's gradients
+    are averaged over the ranks beside the backward of the blocks below.  Returns the measurements (rank 0 prints)."""
+    import torch
+    T = M_TOKENS
+    t_build = time.perf_counter()
+    model, keep, heads, n_grads = build_step_model(G, eng, dev, n_layers, rank, T)
+    build_s = time.perf_counter() - t_build
+    rng = np.random.default_rng(4000 + rank)
+    tokens = rng.integers(0, STEP_CFG["vocab"], T).astype(np.int32)
+    labels = np.roll(tokens, -1).astype(np.int32)
+    labels[-1] = -100
+    tok_d, lab_d = torch.from_numpy(tokens).to(dev), torch.from_numpy(labels).to(dev)
+    total = warmup + steps
+    losses = torch.zeros(total + 1, dtype=torch.float32, device=dev)
+
+    def one_step(i):
+        model.forward_backward(tok_d, lab_d, loss_dev=losses[i:i + 1])
+        model.optimizer_step(step=i + 1, max_norm=1.0, **ADAMW)
+
+    for i in range(warmup):
+        one_step(i)
+    eng.sync()
+    barrier()
+    a = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    b = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        a[i].record(stream)
+        one_step(warmup + i)
+        b[i].record(stream)
+    barrier()
+    eng.sync()
+    ms = allreduce_max(sum(x.elapsed_time(y) for x, y in zip(a, b)))
+    # share of the tensor-core GEMMs (projections and LM head), one eager step with events around each launch
+    eng.profile_read(reset=True)
+    eng.profile_enable(True)
+    model.forward_backward(tok_d, lab_d, loss_dev=losses[total:total + 1])
+    eng.sync()
+    prof = eng.profile_read(reset=True)
+    eng.profile_enable(False)
+    model.optimizer_step(step=total + 1, max_norm=1.0, **ADAMW)
+    # end to end: host token ids in, loss back on the host, every step
+    barrier()
+    e2e_n = max(2, min(steps, 5))
+    t0 = time.perf_counter()
+    host_losses = []
+    for i in range(e2e_n):
+        host_losses.append(model.forward_backward(tokens, labels))
+        model.optimizer_step(step=total + 2 + i, max_norm=1.0, **ADAMW)
+    eng.sync()
+    barrier()
+    e2e_s = allreduce_max(time.perf_counter() - t0)
+    ls = [float(v) for v in losses.cpu().numpy()[:total]]
+    ms_step = ms / steps
+    out = {
+        "workload": STEP_WORKLOAD if n_layers == 28 else STEP_WORKLOAD.replace("28 layers", f"{n_layers} layers"),
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+        "tokens_per_s": world * T * 1e3 / ms_step,
+        "projection_tflops": world * step_projection_flops(n_layers) / (ms_step * 1e-3) / 1e12,
+        "gemm_ms_per_step": prof["gemm_ms"], "gemm_launches_per_step": prof["gemm_launches"],
+        "gemm_tflops": prof["gemm_flops"] / (prof["gemm_ms"] * 1e-3) / 1e12 if prof["gemm_ms"] > 0 else 0.0,
+        "kernel_launches_per_step": prof["kernel_launches"],
+        "lora_parameters": n_grads, "gradient_exchange": ("per-block ncclAllReduce(avg) on a side stream, last block first" if world > 1 else "none"),
+        "loss_first_steps": ls[:10], "loss_finite": bool(np.all(np.isfinite(ls))),
+        "e2e": {"tokens_per_s": world * T * e2e_n / e2e_s, "ms_per_step": 1e3 * e2e_s / e2e_n, "steps": e2e_n,
+                "h2d_bytes_per_step": 2 * T * 4, "d2h_bytes_per_step": 12, "loss": host_losses[-1]},
+        "build_s": build_s,
+    }
+    model.close()
+    for ws, ads in keep:
+        for h in ws + ads:
+            h.free()
+    for h in heads:
+        h.free()
+    return out
 
 # ------------------------------------------------------------------------------------------------ M sweep
 def run_sweep(args) -> None:
@@ -656,6 +808,9 @@ def main() -> None:
     ap.add_argument("--sweep-m", type=int, nargs="+", default=[1, 16, 128, 512, 2048])
     ap.add_argument("--e2e-steps", type=int, default=50, help="timed steps of the end-to-end (host-buffer) leg, after 5 warm steps")
     ap.add_argument("--sustained-steps", type=int, default=800, help="steps of the second, long measurement that the clock samples cover")
+    ap.add_argument("--no-train-step", action="store_true", help="skip the 28-layer training-step leg (tokens/s)")
+    ap.add_argument("--train-steps", type=int, default=10, help="timed steps of the training-step leg")
+    ap.add_argument("--train-layers", type=int, default=28, help="layers of the training-step model (28 = the workload)")
     ap.add_argument("--launch-list", action="store_true", help="eager warm-up + steps only (for a profiler's launch list); prints no benchmark value")
     ap.add_argument("--no-parity", action="store_true", help="skip the comparison of the last step's outputs with the CPU path")
     args = ap.parse_args()

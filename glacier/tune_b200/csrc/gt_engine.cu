@@ -74,7 +74,7 @@ cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const cha
     if (e->profile && b) cudaEventRecord(b, e->stream);
     e->gemm_launches += 1;
     e->kernel_launches += 1;
-    for (int j = 0; j < n; j++) e->gemm_flops += 2.0 * (double)m[j].T * (double)m[j].w->N * (double)m[j].w->K;
+    for (int j = 0; j < n; j++) e->gemm_flops += 2.0 * (double)m[j].T * (double)(m[j].rows > 0 ? m[j].rows : m[j].w->N) * (double)m[j].w->K;
     return ce;
 }
 
