@@ -348,6 +348,25 @@ def run_ours(args) -> None:
 
     # ---- device-resident timing.  The clock sampler starts before the warm-up, and the warm-up runs for at
     # least half a second so that the clocks have ramped and nvidia-smi has samples taken under load.
+    if args.launch_list and args.workload == "step":
+        # the training step of a few layers for a profiler's launch list (the LM head stays full size)
+        import torch as _t
+        model, keep, heads, _ = build_step_model(G, eng, dev, args.train_layers, rank, M_TOKENS)
+        rng_ = np.random.default_rng(4000)
+        tok = rng_.integers(0, STEP_CFG["vocab"], M_TOKENS).astype(np.int32)
+        lab = np.roll(tok, -1).astype(np.int32)
+        lab[-1] = -100
+        tok_d, lab_d = _t.from_numpy(tok).to(dev), _t.from_numpy(lab).to(dev)
+        loss_d = _t.zeros(1, device=dev)
+        for i in range(args.warmup + args.steps):
+            model.forward_backward(tok_d, lab_d, loss_dev=loss_d)
+            model.optimizer_step(step=i + 1, max_norm=1.0, **ADAMW)
+        eng.sync()
+        emit(json.dumps({"launch_list": True, "workload": "step", "layers": args.train_layers, "steps": args.steps, "warmup": args.warmup,
+                         "loss": float(loss_d.item())}))
+        model.close()
+        eng.close()
+        return
     if args.launch_list:
         # a short eager run for a profiler's launch list: W warm-up steps, K steps, no timing, no other legs
         for _ in range(args.warmup + args.steps):
@@ -811,6 +830,8 @@ def main() -> None:
     ap.add_argument("--no-train-step", action="store_true", help="skip the 28-layer training-step leg (tokens/s)")
     ap.add_argument("--train-steps", type=int, default=10, help="timed steps of the training-step leg")
     ap.add_argument("--train-layers", type=int, default=28, help="layers of the training-step model (28 = the workload)")
+    ap.add_argument("--workload", choices=["layer", "step"], default="layer",
+                    help="layer: the seven projections of one layer (the headline metric); step: the 28-layer training step (tokens/s)")
     ap.add_argument("--launch-list", action="store_true", help="eager warm-up + steps only (for a profiler's launch list); prints no benchmark value")
     ap.add_argument("--no-parity", action="store_true", help="skip the comparison of the last step's outputs with the CPU path")
     args = ap.parse_args()

@@ -15,7 +15,8 @@
 // Tiles of 64 queries x 64 keys; the products run on warp-level m16n8k16 MMAs (bf16 operands in the bf16 math mode,
 // fp16 in the validation modes) with fp32 accumulation and fp32 softmax statistics.  Attention is about 3 % of a
 // layer's FLOPs at 512 tokens; the CTA-wide tcgen05 path is kept for the projections.
-//   k_attn_fwd      grid (query tiles, heads_q): online softmax over the key tiles at or left of the diagonal
+//   k_attn_fwd      grid (query tile pairs, heads_q): online softmax over the key tiles at or left of the diagonal,
+//                   four compute warps and four fetch warps per block
 //   k_attn_delta    rowsum(dO * out) per (head, query)
 //   k_attn_bwd_dq   grid (query tiles, heads_q): dq of one tile, summed over its key tiles in registers
 //   k_attn_bwd_dkv  grid (key tiles, heads_q): dk, dv of one key tile for ONE query head, summed over the query tiles
@@ -102,113 +103,139 @@ __device__ __forceinline__ void load_tile(const float *__restrict__ src, int64_t
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ------------------------------------------------------------------------------------------------ forward
-// 4 warps, 16 queries each.  Scores are kept in the base-2 domain: q is scaled by log2(e) / sqrt(head_dim) when it is
-// rounded, probabilities are exp2(s - m).  lse2[h, t] = m + log2(sum) is what the backward needs.
+// 8 warps: warps 0-3 compute (16 queries each), warps 4-7 fetch - while the compute warps work on key tile j out of one
+// shared-memory buffer, the fetch warps read key / value tile j + 1 from global memory, round it and store it into the
+// other buffer, so the load latency hides under the MMAs.  A block takes query tile i and its mirror n - 1 - i one after
+// the other: every block then walks n + 1 key tiles, the grid is n / 2 x heads blocks (112 at 512 tokens and 28 heads:
+// one wave of the 148 SMs, one block per SM).
+// Scores are kept in the base-2 domain: q is scaled by log2(e) / sqrt(head_dim) when it is rounded, probabilities are
+// exp2(s - m).  lse2[h, t] = m + log2(sum) is what the backward needs.
+constexpr int kFwdSmem = 5 * 64 * SD;      // Q + two (K, V) buffers
 template <typename T16>
-__global__ void __launch_bounds__(128) k_attn_fwd(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+__global__ void __launch_bounds__(256) k_attn_fwd(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                   float *__restrict__ out, float *__restrict__ lse2, int T, int HQ, int HK) {
     extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t *Qs = smem, *Ks = smem + BQ * SD, *Vs = Ks + BK * SD;
+    uint8_t *Qs = smem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int it = blockIdx.x, h = blockIdx.y, kh = h / (HQ / HK);
-    const int q0 = it * BQ;
+    const bool compute = warp < 4;
+    const int h = blockIdx.y, kh = h / (HQ / HK);
+    const int n_qt = (T + BQ - 1) / BQ;
     const int64_t ldq = (int64_t)HQ * D, ldk = (int64_t)HK * D;
-    load_tile<T16, 128>(q, ldq, h * D, q0, T, kLog2e * rsqrtf((float)D), Qs, tid);
-    __syncthreads();
-    const uint32_t qs = smem_u32(Qs), ks = smem_u32(Ks), vs = smem_u32(Vs);
-    uint32_t qf[D / 16][4];
-#pragma unroll
-    for (int kk = 0; kk < D / 16; kk++) ldsm4(a_mk(qs, SD, warp * 16, kk * 16, lane), qf[kk]);
-    float o[D / 8][4];
-#pragma unroll
-    for (int n = 0; n < D / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    const int row[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
-    for (int jt = 0; jt <= it; jt++) {
-        const int k0 = jt * BK;
+    const uint32_t qs = smem_u32(Qs);
+    auto kbuf = [&](int b) { return smem + (1 + 2 * b) * 64 * SD; };
+    auto vbuf = [&](int b) { return smem + (2 + 2 * b) * 64 * SD; };
+    for (int pass = 0; pass < 2; pass++) {
+        const int it = pass == 0 ? (int)blockIdx.x : n_qt - 1 - (int)blockIdx.x;
+        if (pass == 1 && it <= (int)blockIdx.x) break;      // odd tile count: the middle tile is done once
+        const int q0 = it * BQ;
+        __syncthreads();      // the previous pass has finished with every buffer
+        load_tile<T16, 256>(q, ldq, h * D, q0, T, kLog2e * rsqrtf((float)D), Qs, tid);
+        load_tile<T16, 256>(k, ldk, kh * D, 0, T, 1.f, kbuf(0), tid);
+        load_tile<T16, 256>(v, ldk, kh * D, 0, T, 1.f, vbuf(0), tid);
         __syncthreads();
-        load_tile<T16, 128>(k, ldk, kh * D, k0, T, 1.f, Ks, tid);
-        load_tile<T16, 128>(v, ldk, kh * D, k0, T, 1.f, Vs, tid);
-        __syncthreads();
-        float s[BK / 8][4];
+        uint32_t qf[D / 16][4];
+        float o[D / 8][4];
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        const int row[2] = {q0 + (warp & 3) * 16 + g, q0 + (warp & 3) * 16 + g + 8};
+        if (compute) {
 #pragma unroll
-        for (int n = 0; n < BK / 8; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+            for (int kk = 0; kk < D / 16; kk++) ldsm4(a_mk(qs, SD, warp * 16, kk * 16, lane), qf[kk]);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; kk++) {
+            for (int n = 0; n < D / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        }
+        for (int jt = 0; jt <= it; jt++) {
+            const int k0 = jt * BK;
+            if (!compute) {
+                if (jt + 1 <= it) {
+                    load_tile<T16, 128>(k, ldk, kh * D, k0 + BK, T, 1.f, kbuf((jt + 1) & 1), tid - 128);
+                    load_tile<T16, 128>(v, ldk, kh * D, k0 + BK, T, 1.f, vbuf((jt + 1) & 1), tid - 128);
+                }
+            } else {
+                const uint32_t ks = smem_u32(kbuf(jt & 1)), vs = smem_u32(vbuf(jt & 1));
+                float s[BK / 8][4];
 #pragma unroll
-            for (int n = 0; n < BK / 8; n += 2) {
-                uint32_t b[4];
-                ldsm4(b_nk(ks, SD, n * 8, kk * 16, lane), b);
-                mma16<T16>(s[n], qf[kk], b[0], b[1]);
-                mma16<T16>(s[n + 1], qf[kk], b[2], b[3]);
+                for (int n = 0; n < BK / 8; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+#pragma unroll
+                    for (int n = 0; n < BK / 8; n += 2) {
+                        uint32_t b[4];
+                        ldsm4(b_nk(ks, SD, n * 8, kk * 16, lane), b);
+                        mma16<T16>(s[n], qf[kk], b[0], b[1]);
+                        mma16<T16>(s[n + 1], qf[kk], b[2], b[3]);
+                    }
+                }
+                // causal mask (only the diagonal tile has masked entries) and keys beyond T
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int n = 0; n < BK / 8; n++) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const int key = k0 + n * 8 + 2 * t4 + (c & 1);
+                        const int r = c >> 1;
+                        if (key > row[r] || key >= T) s[n][c] = -INFINITY;
+                        mx[r] = fmaxf(mx[r], s[n][c]);
+                    }
+                }
+                float corr[2];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    const float mn = fmaxf(m[r], mx[r]);
+                    corr[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - mn);
+                    m[r] = mn;
+                }
+                float ps[2] = {0.f, 0.f};
+                uint32_t pf[BK / 16][4];
+#pragma unroll
+                for (int n = 0; n < BK / 8; n++) {
+                    const float p0 = m[0] == -INFINITY ? 0.f : exp2f(s[n][0] - m[0]), p1 = m[0] == -INFINITY ? 0.f : exp2f(s[n][1] - m[0]);
+                    const float p2 = m[1] == -INFINITY ? 0.f : exp2f(s[n][2] - m[1]), p3 = m[1] == -INFINITY ? 0.f : exp2f(s[n][3] - m[1]);
+                    ps[0] += p0 + p1;
+                    ps[1] += p2 + p3;
+                    pf[n >> 1][(n & 1) * 2] = pk<T16>(p0, p1);
+                    pf[n >> 1][(n & 1) * 2 + 1] = pk<T16>(p2, p3);
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++) l[r] = l[r] * corr[r] + ps[r];
+#pragma unroll
+                for (int n = 0; n < D / 8; n++) {
+                    o[n][0] *= corr[0];
+                    o[n][1] *= corr[0];
+                    o[n][2] *= corr[1];
+                    o[n][3] *= corr[1];
+                }
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; kk++) {
+#pragma unroll
+                    for (int n = 0; n < D / 8; n += 2) {
+                        uint32_t b[4];
+                        ldsm4t(b_kn(vs, SD, n * 8, kk * 16, lane), b);
+                        mma16<T16>(o[n], pf[kk], b[0], b[1]);
+                        mma16<T16>(o[n + 1], pf[kk], b[2], b[3]);
+                    }
+                }
+            }
+            __syncthreads();      // tile j + 1 is in place, tile j's buffer is free
+        }
+        if (compute) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+                l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                if (row[r] >= T) continue;
+                const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+                float *dst = out + (int64_t)row[r] * ldq + h * D;
+#pragma unroll
+                for (int n = 0; n < D / 8; n++)
+                    *reinterpret_cast<float2 *>(dst + n * 8 + 2 * t4) = make_float2(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+                if (t4 == 0) lse2[(int64_t)h * T + row[r]] = m[r] + log2f(l[r]);
             }
         }
-        // causal mask (only the diagonal tile has masked entries) and keys beyond T
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int n = 0; n < BK / 8; n++) {
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const int key = k0 + n * 8 + 2 * t4 + (c & 1);
-                const int r = c >> 1;
-                if (key > row[r] || key >= T) s[n][c] = -INFINITY;
-                mx[r] = fmaxf(mx[r], s[n][c]);
-            }
-        }
-        float corr[2];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float mn = fmaxf(m[r], mx[r]);
-            corr[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - mn);
-            m[r] = mn;
-        }
-        float ps[2] = {0.f, 0.f};
-        uint32_t pf[BK / 16][4];
-#pragma unroll
-        for (int n = 0; n < BK / 8; n++) {
-            const float p0 = m[0] == -INFINITY ? 0.f : exp2f(s[n][0] - m[0]), p1 = m[0] == -INFINITY ? 0.f : exp2f(s[n][1] - m[0]);
-            const float p2 = m[1] == -INFINITY ? 0.f : exp2f(s[n][2] - m[1]), p3 = m[1] == -INFINITY ? 0.f : exp2f(s[n][3] - m[1]);
-            ps[0] += p0 + p1;
-            ps[1] += p2 + p3;
-            pf[n >> 1][(n & 1) * 2] = pk<T16>(p0, p1);
-            pf[n >> 1][(n & 1) * 2 + 1] = pk<T16>(p2, p3);
-        }
-#pragma unroll
-        for (int r = 0; r < 2; r++) l[r] = l[r] * corr[r] + ps[r];
-#pragma unroll
-        for (int n = 0; n < D / 8; n++) {
-            o[n][0] *= corr[0];
-            o[n][1] *= corr[0];
-            o[n][2] *= corr[1];
-            o[n][3] *= corr[1];
-        }
-#pragma unroll
-        for (int kk = 0; kk < BK / 16; kk++) {
-#pragma unroll
-            for (int n = 0; n < D / 8; n += 2) {
-                uint32_t b[4];
-                ldsm4t(b_kn(vs, SD, n * 8, kk * 16, lane), b);
-                mma16<T16>(o[n], pf[kk], b[0], b[1]);
-                mma16<T16>(o[n + 1], pf[kk], b[2], b[3]);
-            }
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        if (row[r] >= T) continue;
-        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
-        float *dst = out + (int64_t)row[r] * ldq + h * D;
-#pragma unroll
-        for (int n = 0; n < D / 8; n++)
-            *reinterpret_cast<float2 *>(dst + n * 8 + 2 * t4) = make_float2(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
-        if (t4 == 0) lse2[(int64_t)h * T + row[r]] = m[r] + log2f(l[r]);
     }
 }
 
@@ -413,7 +440,7 @@ __global__ void k_attn_reduce_kv(const float *__restrict__ wk, const float *__re
 PerDeviceOnce g_attn_attr;
 template <typename T16>
 cudaError_t attn_allow_smem() {
-    cudaError_t e = cudaFuncSetAttribute(k_attn_fwd<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * SD);
+    cudaError_t e = cudaFuncSetAttribute(k_attn_fwd<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_bwd_dq<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_bwd_dkv<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     return e;
@@ -438,9 +465,10 @@ int attention_forward_on_device(gt_engine *e, const float *q, const float *k, co
         cudaError_t a = attn_allow_smem<__nv_bfloat16>();
         return a == cudaSuccess ? attn_allow_smem<__half>() : a;
     }));
-    const dim3 grid((T + BQ - 1) / BQ, HQ);
-    if (e->math_mode == GT_MATH_BF16) k_attn_fwd<__nv_bfloat16><<<grid, 128, 3 * 64 * SD, e->stream>>>(q, k, v, out, lse, T, HQ, HK);
-    else k_attn_fwd<__half><<<grid, 128, 3 * 64 * SD, e->stream>>>(q, k, v, out, lse, T, HQ, HK);
+    const int n_qt = (T + BQ - 1) / BQ;
+    const dim3 grid((n_qt + 1) / 2, HQ);      // a block takes query tile i and its mirror n - 1 - i
+    if (e->math_mode == GT_MATH_BF16) k_attn_fwd<__nv_bfloat16><<<grid, 256, kFwdSmem, e->stream>>>(q, k, v, out, lse, T, HQ, HK);
+    else k_attn_fwd<__half><<<grid, 256, kFwdSmem, e->stream>>>(q, k, v, out, lse, T, HQ, HK);
     GT_LAUNCH(e, cudaGetLastError());
     return GT_OK;
 }

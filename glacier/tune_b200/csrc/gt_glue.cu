@@ -162,30 +162,35 @@ __global__ void __launch_bounds__(256) k_add(const float *__restrict__ a, const 
     for (int64_t i = done + tid; i < n; i += nth) out[i] = a[i] + b[i];
 }
 
-// One thread per (position, head, pair index i): consecutive threads hold consecutive i, so accesses are coalesced, and
-// there are enough threads in flight to cover the memory latency (cos / sin are recomputed per head, which is cheap
-// next to the two loads and two stores).  freq and theta follow the reference's fp32 order.
+// One block per position: the first threads evaluate cos / sin of the position's angles once into shared memory (powf
+// and a sincosf of a large angle, repeated per head, cost more than the memory traffic), then all threads walk the
+// (head, pair) items of q and k with coalesced accesses.  freq and theta follow the reference's fp32 order.
+constexpr int kRopeMaxHalf = 256;
 __global__ void __launch_bounds__(256) k_rope(float *__restrict__ q, float *__restrict__ k, int T, int heads_q, int heads_kv, int head_dim,
                                               float freq_base, float freq_scale, int eff, float sign) {
+    __shared__ float cs[kRopeMaxHalf], sn[kRopeMaxHalf];
     pdl_wait();
     pdl_trigger();
     const int half = eff >> 1;
-    const int heads = (q ? heads_q : 0) + (k ? heads_kv : 0);
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (int64_t)T * heads * half) return;
-    const int i = (int)(idx % half);
-    const int h = (int)((idx / half) % heads);
-    const int pos = (int)(idx / ((int64_t)half * heads));
-    const float base_freq = 1.0f / powf(freq_base, (float)(2 * i) / (float)eff);
-    const float theta = (float)pos * base_freq * freq_scale;
-    float s, c;
-    sincosf(theta, &s, &c);
-    s *= sign;
-    const int hq = q ? heads_q : 0;
-    float *p = h < hq ? q + ((int64_t)pos * heads_q + h) * head_dim + i : k + ((int64_t)pos * heads_kv + (h - hq)) * head_dim + i;
-    const float v0 = p[0], v1 = p[half];
-    p[0] = v0 * c - v1 * s;
-    p[half] = v0 * s + v1 * c;
+    const int pos = blockIdx.x;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float base_freq = 1.0f / powf(freq_base, (float)(2 * i) / (float)eff);
+        const float theta = (float)pos * base_freq * freq_scale;
+        float s, c;
+        sincosf(theta, &s, &c);
+        cs[i] = c;
+        sn[i] = s * sign;
+    }
+    __syncthreads();
+    const int hq = q ? heads_q : 0, heads = hq + (k ? heads_kv : 0);
+    for (int it = threadIdx.x; it < heads * half; it += blockDim.x) {
+        const int h = it / half, i = it - h * half;
+        float *p = h < hq ? q + ((int64_t)pos * heads_q + h) * head_dim + i : k + ((int64_t)pos * heads_kv + (h - hq)) * head_dim + i;
+        const float c = cs[i], s = sn[i];
+        const float v0 = p[0], v1 = p[half];
+        p[0] = v0 * c - v1 * s;
+        p[half] = v0 * s + v1 * c;
+    }
 }
 
 // block-wide sum of up to two values (256 threads)
@@ -239,20 +244,57 @@ __global__ void __launch_bounds__(256) k_rmsnorm_fwd(const float *__restrict__ x
     for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) yr[i] = xr[i] * r * w[i];
 }
 
+// sum = a + b (written out: the residual stream), y = RMSNorm(sum) * w: the residual add and the norm that follows it
+// in one pass (TransformerBlock.cs:518-528: x1 = x + o, then norm2X = RMSNorm(x1)).  The sum is formed once in fp32 and
+// both outputs use it, so the values equal the two separate kernels'.
+__global__ void __launch_bounds__(256) k_add_rmsnorm_fwd(const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ w,
+                                                         float *__restrict__ sum, float *__restrict__ y, int H, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const float *ar = a + (int64_t)blockIdx.x * H, *br = b + (int64_t)blockIdx.x * H;
+    float *sr = sum + (int64_t)blockIdx.x * H, *yr = y + (int64_t)blockIdx.x * H;
+    float v[kRowRegs];
+    float ss = 0.f, unused = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowRegs; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < H ? ar[i] + br[i] : 0.f;
+        if (i < H) sr[i] = v[j];
+        ss += v[j] * v[j];
+    }
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) {
+        const float t = ar[i] + br[i];
+        sr[i] = t;
+        ss += t * t;
+    }
+    block_sum2(ss, unused);
+    const float r = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < kRowRegs; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < H) yr[i] = v[j] * r * w[i];
+    }
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) yr[i] = sr[i] * r * w[i];
+}
+
 // dx = r * g - x * r^3 * mean(g * x), g = dy * w (frozen weight)
+// (+ residual when given: the gradient that bypasses the norm on the residual connection, TransformerBlock.cs:675,838)
 __global__ void __launch_bounds__(256) k_rmsnorm_bwd(const float *__restrict__ dy, const float *__restrict__ x, const float *__restrict__ w,
-                                                     float *__restrict__ dx, int H, float eps) {
+                                                     const float *residual, float *dx, int H, float eps) {
     pdl_wait();
     pdl_trigger();
     const float *xr = x + (int64_t)blockIdx.x * H, *gr = dy + (int64_t)blockIdx.x * H;
+    const float *rr = residual ? residual + (int64_t)blockIdx.x * H : nullptr;
     float *dr = dx + (int64_t)blockIdx.x * H;
-    float xv[kRowRegs], gv[kRowRegs];
+    // (the residual may alias dx: its values are taken before anything is stored)
+    float xv[kRowRegs], gv[kRowRegs], rv[kRowRegs];
     float ss = 0.f, gx = 0.f;
 #pragma unroll
     for (int j = 0; j < kRowRegs; j++) {
         const int i = threadIdx.x + j * 256;
         xv[j] = i < H ? xr[i] : 0.f;
         gv[j] = i < H ? gr[i] * w[i] : 0.f;
+        rv[j] = (rr && i < H) ? rr[i] : 0.f;
         ss += xv[j] * xv[j];
         gx += gv[j] * xv[j];
     }
@@ -266,9 +308,9 @@ __global__ void __launch_bounds__(256) k_rmsnorm_bwd(const float *__restrict__ d
 #pragma unroll
     for (int j = 0; j < kRowRegs; j++) {
         const int i = threadIdx.x + j * 256;
-        if (i < H) dr[i] = r * gv[j] - xv[j] * coef;
+        if (i < H) dr[i] = r * gv[j] - xv[j] * coef + rv[j];
     }
-    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) dr[i] = r * gr[i] * w[i] - xr[i] * coef;
+    for (int i = threadIdx.x + kRowRegs * 256; i < H; i += 256) dr[i] = r * gr[i] * w[i] - xr[i] * coef + (rr ? rr[i] : 0.f);
 }
 
 int aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -306,15 +348,19 @@ cudaError_t launch_rope(float *q, float *k, int T, int heads_q, int heads_kv, in
                         int inverse, cudaStream_t s) {
     const int eff = (rope_dim > 0 && rope_dim <= head_dim) ? rope_dim : head_dim;      // RoPEKernel.cs:55
     if (T <= 0 || eff / 2 <= 0) return cudaSuccess;
-    const int64_t items = (int64_t)T * (eff / 2) * ((q ? heads_q : 0) + (k ? heads_kv : 0));
-    return launch_k(k_rope, dim3((unsigned)((items + 255) / 256)), dim3(256), (size_t)0, s, q, k, T, heads_q, heads_kv, head_dim, freq_base,
-                    freq_scale, eff, inverse ? -1.0f : 1.0f);
+    if (eff / 2 > kRopeMaxHalf) return cudaErrorInvalidValue;      // rotary dimensions above 512 are not served
+    return launch_k(k_rope, dim3((unsigned)T), dim3(256), (size_t)0, s, q, k, T, heads_q, heads_kv, head_dim, freq_base, freq_scale, eff,
+                    inverse ? -1.0f : 1.0f);
 }
 cudaError_t launch_rmsnorm_fwd(const float *x, const float *w, float *y, int T, int H, float eps, cudaStream_t s) {
     return launch_k(k_rmsnorm_fwd, dim3((unsigned)T), dim3(256), (size_t)0, s, x, w, y, H, eps);
 }
-cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, float *dx, int T, int H, float eps, cudaStream_t s) {
-    return launch_k(k_rmsnorm_bwd, dim3((unsigned)T), dim3(256), (size_t)0, s, dy, x, w, dx, H, eps);
+cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, const float *residual, float *dx, int T, int H, float eps,
+                               cudaStream_t s) {
+    return launch_k(k_rmsnorm_bwd, dim3((unsigned)T), dim3(256), (size_t)0, s, dy, x, w, residual, dx, H, eps);
+}
+cudaError_t launch_add_rmsnorm_fwd(const float *a, const float *b, const float *w, float *sum, float *y, int T, int H, float eps, cudaStream_t s) {
+    return launch_k(k_add_rmsnorm_fwd, dim3((unsigned)T), dim3(256), (size_t)0, s, a, b, w, sum, y, H, eps);
 }
 cudaError_t launch_adamw(const AdamwSeg *segs, int n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
                          int sm_count, cudaStream_t s) {
@@ -395,10 +441,8 @@ extern "C" int gt_rope(gt_engine *eng, float *q, float *k, int32_t T, int32_t he
     const gt::EngineView ev = gt::engine_view(eng);
     std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
     cudaError_t ce = cudaSetDevice(ev.device);
-    const int64_t items = (int64_t)T * (eff / 2) * ((q ? heads_q : 0) + (k ? heads_kv : 0));
     if (ce == cudaSuccess)
-        ce = gt::launch_k(k_rope, dim3((unsigned)((items + 255) / 256)), dim3(256), (size_t)0, ev.stream, q, k, (int)T, (int)heads_q,
-                          (int)heads_kv, (int)head_dim, freq_base, freq_scale, eff, inverse ? -1.0f : 1.0f);
+        ce = gt::launch_rope(q, k, (int)T, (int)heads_q, (int)heads_kv, (int)head_dim, freq_base, freq_scale, (int)rope_dim, (int)inverse, ev.stream);
     return ce == cudaSuccess ? GT_OK : cuda_fail("gt_rope", ce);
 }
 
@@ -418,7 +462,7 @@ extern "C" int gt_rmsnorm_backward(gt_engine *eng, const float *dy, const float 
     const gt::EngineView ev = gt::engine_view(eng);
     std::lock_guard<std::mutex> lk(*static_cast<std::mutex *>(ev.mutex));
     cudaError_t ce = cudaSetDevice(ev.device);
-    if (ce == cudaSuccess) ce = gt::launch_k(k_rmsnorm_bwd, dim3((unsigned)T), dim3(256), (size_t)0, ev.stream, dy, x, w, dx, (int)H, eps);
+    if (ce == cudaSuccess) ce = gt::launch_rmsnorm_bwd(dy, x, w, nullptr, dx, (int)T, (int)H, eps, ev.stream);
     return ce == cudaSuccess ? GT_OK : cuda_fail("gt_rmsnorm_backward", ce);
 }
 

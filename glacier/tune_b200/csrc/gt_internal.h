@@ -189,7 +189,11 @@ cudaError_t launch_add(const float *a, const float *b, float *out, int64_t n, in
 cudaError_t launch_rope(float *q, float *k, int T, int heads_q, int heads_kv, int head_dim, float freq_base, float freq_scale, int rope_dim,
                         int inverse, cudaStream_t s);
 cudaError_t launch_rmsnorm_fwd(const float *x, const float *w, float *y, int T, int H, float eps, cudaStream_t s);
-cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, float *dx, int T, int H, float eps, cudaStream_t s);
+// dx = RMSNorm backward (+ residual, which may be null and may alias dx)
+cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, const float *residual, float *dx, int T, int H, float eps,
+                               cudaStream_t s);
+// sum = a + b (sum may alias a or b), y = RMSNorm(sum) * w
+cudaError_t launch_add_rmsnorm_fwd(const float *a, const float *b, const float *w, float *sum, float *y, int T, int H, float eps, cudaStream_t s);
 
 // ---- launches with programmatic dependent launch (the kernel must call pdl_wait() before touching global memory).
 // Environment GT_PDL=1 turns the attribute on; the default is plain stream order.

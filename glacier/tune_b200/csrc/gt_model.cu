@@ -69,13 +69,17 @@ int check_ready(const gt_model *m, const char *who) {
     return GT_OK;
 }
 
-// One block forward on the engine stream.  out may alias nothing; s receives the state.
-int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockState &s, int T) {
+// One block forward on the engine stream; s receives the state.  n1_ready: s.n1 already holds RMSNorm(x_in) (the block
+// before wrote it together with its output).  next_norm / next_n1 (may be null): the norm weight and destination of
+// the norm that follows this block's output - the next block's attention norm or the model's output norm - computed
+// in the same pass as the residual add.
+int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockState &s, int T, bool n1_ready, const float *next_norm,
+                  float *next_n1) {
     gt_engine *e = m->eng;
     const gt_model_config &c = m->cfg;
     const LayerDev &L = m->layers[l];
     const int H = c.hidden;
-    GT_LAUNCH(e, launch_rmsnorm_fwd(x_in, L.norm1, s.n1, T, H, c.rms_eps, e->stream));
+    if (!n1_ready) GT_LAUNCH(e, launch_rmsnorm_fwd(x_in, L.norm1, s.n1, T, H, c.rms_eps, e->stream));
     float *qkv[3] = {s.q, s.k, s.v};
     int rc = forward_group_device(e, 3, L.w + kQ, L.ad + kQ, s.n1, qkv, T, 0);
     if (rc != GT_OK) return rc;
@@ -85,13 +89,13 @@ int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockStat
     float *o = m->tmp_h;
     rc = forward_group_device(e, 1, L.w + kO, L.ad + kO, s.attn, &o, T, 0);
     if (rc != GT_OK) return rc;
-    GT_LAUNCH(e, launch_add(x_in, o, s.x1, (int64_t)T * H, e->sm_count, e->stream));
-    GT_LAUNCH(e, launch_rmsnorm_fwd(s.x1, L.norm2, s.n2, T, H, c.rms_eps, e->stream));
+    GT_LAUNCH(e, launch_add_rmsnorm_fwd(x_in, o, L.norm2, s.x1, s.n2, T, H, c.rms_eps, e->stream));      // x1 = x + o; n2 = norm(x1)
     const gt_weight *fw[3] = {L.w[kGate], L.w[kUp], L.w[kDown]};
     gt_adapter *fa[3] = {L.ad[kGate], L.ad[kUp], L.ad[kDown]};
     rc = ffn_forward_device(e, fw, fa, s.n2, s.gate, s.up, s.hidden, m->tmp_h, T, 0);
     if (rc != GT_OK) return rc;
-    GT_LAUNCH(e, launch_add(s.x1, m->tmp_h, x_out, (int64_t)T * H, e->sm_count, e->stream));
+    if (next_norm && next_n1) GT_LAUNCH(e, launch_add_rmsnorm_fwd(s.x1, m->tmp_h, next_norm, x_out, next_n1, T, H, c.rms_eps, e->stream));
+    else GT_LAUNCH(e, launch_add(s.x1, m->tmp_h, x_out, (int64_t)T * H, e->sm_count, e->stream));
     return GT_OK;
 }
 
@@ -104,12 +108,11 @@ int block_backward(gt_model *m, int l, const float *d_out, const float *x_in, co
     const int flags = GT_FLAG_REUSE_LOW | GT_FLAG_DX_ASSIGN;
     const gt_weight *fw[3] = {L.w[kGate], L.w[kUp], L.w[kDown]};
     gt_adapter *fa[3] = {L.ad[kGate], L.ad[kUp], L.ad[kDown]};
-    // A. FFN: down, SwiGLU, gate | up -> dNorm2X; RMSNorm2 backward; residual
+    // A. FFN: down, SwiGLU, gate | up -> dNorm2X; RMSNorm2 backward + residual: dX1 = dOut + dNorm(dNorm2X)
     int rc = ffn_backward_device(e, fw, fa, d_out, s.n2, s.gate, s.up, s.hidden, m->dn, T, flags);
     if (rc != GT_OK) return rc;
-    GT_LAUNCH(e, launch_rmsnorm_bwd(m->dn, s.x1, L.norm2, m->dx1, T, H, c.rms_eps, e->stream));
-    GT_LAUNCH(e, launch_add(d_out, m->dx1, m->dx1, (int64_t)T * H, e->sm_count, e->stream));
-    // B. attention: o projection, attention, RoPE, q | k | v -> dNorm1X; RMSNorm1 backward; residual
+    GT_LAUNCH(e, launch_rmsnorm_bwd(m->dn, s.x1, L.norm2, d_out, m->dx1, T, H, c.rms_eps, e->stream));
+    // B. attention: o projection, attention, RoPE, q | k | v -> dNorm1X; RMSNorm1 backward + residual
     const float *dy_o = m->dx1;
     rc = backward_group_device(e, 1, L.w + kO, L.ad + kO, &dy_o, s.attn, m->dattn, T, flags);
     if (rc != GT_OK) return rc;
@@ -119,8 +122,7 @@ int block_backward(gt_model *m, int l, const float *d_out, const float *x_in, co
     const float *dqkv[3] = {m->dq, m->dk, m->dv};
     rc = backward_group_device(e, 3, L.w + kQ, L.ad + kQ, dqkv, s.n1, m->dn, T, flags);
     if (rc != GT_OK) return rc;
-    GT_LAUNCH(e, launch_rmsnorm_bwd(m->dn, x_in, L.norm1, d_in, T, H, c.rms_eps, e->stream));
-    GT_LAUNCH(e, launch_add(m->dx1, d_in, d_in, (int64_t)T * H, e->sm_count, e->stream));
+    GT_LAUNCH(e, launch_rmsnorm_bwd(m->dn, x_in, L.norm1, m->dx1, d_in, T, H, c.rms_eps, e->stream));
     return GT_OK;
 }
 
@@ -140,10 +142,13 @@ int forward_all(gt_model *m, int T, bool keep_states) {
     const int L = (int)m->layers.size();
     for (int l = 0; l < L; l++) {
         BlockState &s = m->st[keep_states ? l : 0];
-        rc = block_forward(m, l, m->x[l], m->x[l + 1], s, T);
+        // the norm that follows this block's output rides on its last residual add: the next block's attention norm
+        // (into that block's state; with one shared state set its n1 has been consumed by then) or the output norm
+        const float *next_w = l + 1 < L ? m->layers[l + 1].norm1 : m->out_norm;
+        float *next_n1 = l + 1 < L ? m->st[keep_states ? l + 1 : 0].n1 : m->fnorm;
+        rc = block_forward(m, l, m->x[l], m->x[l + 1], s, T, l > 0, next_w, next_n1);
         if (rc != GT_OK) return rc;
     }
-    GT_LAUNCH(e, launch_rmsnorm_fwd(m->x[L], m->out_norm, m->fnorm, T, m->cfg.hidden, m->cfg.rms_eps, e->stream));
     return GT_OK;
 }
 
@@ -374,13 +379,13 @@ int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t 
     // loss and its gradient with respect to the normed final hidden state, then through the final RMSNorm
     rc = lm_head_loss_on_device(e, m->lm_head, m->fnorm, m->labels, T, m->loss, m->valid, m->dfnorm);
     if (rc != GT_OK) return rc;
-    GT_LAUNCH(e, launch_rmsnorm_bwd(m->dfnorm, m->x[L], m->out_norm, m->dx_a, T, H, m->cfg.rms_eps, e->stream));
+    GT_LAUNCH(e, launch_rmsnorm_bwd(m->dfnorm, m->x[L], m->out_norm, nullptr, m->dx_a, T, H, m->cfg.rms_eps, e->stream));
     float *d_cur = m->dx_a, *d_next = m->dx_b;
     const float inv_world = 1.0f / (float)e->dp_world;
     for (int l = L - 1; l >= 0; l--) {
         BlockState &s = m->st[ckpt ? 0 : l];
         if (ckpt) {      // recompute this block's forward into the one state set (its output lands in tmp space, unused)
-            rc = block_forward(m, l, m->x[l], m->dfnorm, s, T);
+            rc = block_forward(m, l, m->x[l], m->dfnorm, s, T, false, nullptr, nullptr);
             if (rc != GT_OK) return rc;
         }
         rc = block_backward(m, l, d_cur, m->x[l], s, d_next, T);

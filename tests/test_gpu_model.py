@@ -142,7 +142,7 @@ def test_forward_backward_matches_cpu_chain(G, oracle, mode, checkpoint, mix, T)
     assert np.array_equal(_device_grads(handles), got)
     # gradients accumulate over micro-batches (LoraTrainer gradient accumulation): a second pass doubles them
     m.forward_backward(tokens, labels)
-    assert oracle.rel_fro(_device_grads(handles), 2 * got) < 1e-3      # fp32 atomics: the order of the additions varies
+    assert oracle.rel_fro(_device_grads(handles), 2 * got) < (5e-3 if mode == 0 else 1e-3)      # fp32 atomics: the order of the additions varies (and with it the 16-bit rounding of X*A)
     _free(m, handles, heads)
     eng.close()
 
