@@ -19,7 +19,7 @@ DIR_FORWARD, DIR_BACKWARD = 0, 1
 FLAG_DEVICE_PTRS, FLAG_NO_LORA, FLAG_REUSE_LOW, FLAG_DX_ASSIGN, FLAG_HOST_ASYNC = 1, 2, 4, 8, 16
 
 EXPORTS = [
-    "gt_last_error", "gt_version", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
+    "gt_last_error", "gt_version", "gt_set_logger", "gt_engine_create", "gt_engine_destroy", "gt_engine_set_math_mode", "gt_sync",
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_params_changed", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
@@ -44,7 +44,7 @@ class GtModelConfig(C.Structure):
 
 class GtConfig(C.Structure):
     _fields_ = [("device", C.c_int32), ("math_mode", C.c_int32), ("stream", C.c_void_p), ("max_tokens", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("max_features", C.c_int32)]
 
 
 _lib = None
@@ -153,6 +153,24 @@ def _ptr(a, dtype=None):
     return a.ctypes.data_as(C.c_void_p), False
 
 
+LOG_FN = C.CFUNCTYPE(None, C.c_int, C.c_char_p, C.c_void_p)
+_logger_keepalive = None
+
+
+def set_logger(fn=None) -> None:
+    """Install fn(level: int, message: str) as the library's log callback (None removes it)."""
+    global _logger_keepalive
+    lib = load_library()
+    lib.gt_set_logger.argtypes = [C.c_void_p, C.c_void_p]
+    if fn is None:
+        lib.gt_set_logger(None, None)
+        _logger_keepalive = None
+        return
+    cb = LOG_FN(lambda level, msg, user: fn(int(level), msg.decode(errors="replace")))
+    lib.gt_set_logger(C.cast(cb, C.c_void_p), None)
+    _logger_keepalive = cb
+
+
 def stream_max_tokens() -> int:
     """Largest token count served by the few-token weight-streaming forward kernel (0: never)."""
     return int(load_library().gt_stream_max_tokens())
@@ -165,9 +183,10 @@ def supports(ggml_type: int, direction: int) -> bool:
 class Engine:
     """One CUDA context user: stream, scratch, math mode (replaces GpuLoraEngine's construction)."""
 
-    def __init__(self, device: int = 0, math_mode: int = MATH_BF16, stream: int | None = None):
+    def __init__(self, device: int = 0, math_mode: int = MATH_BF16, stream: int | None = None, max_tokens: int = 0, max_features: int = 0):
         self.lib = load_library()
-        cfg = GtConfig(device=device, math_mode=math_mode, stream=C.c_void_p(stream) if stream else None, max_tokens=0)
+        cfg = GtConfig(device=device, math_mode=math_mode, stream=C.c_void_p(stream) if stream else None, max_tokens=max_tokens,
+                       max_features=max_features)
         h = C.c_void_p()
         _check(self.lib.gt_engine_create(C.byref(cfg), C.byref(h)))
         self.h = h

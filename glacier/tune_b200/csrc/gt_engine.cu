@@ -21,12 +21,32 @@ using namespace gt;
 namespace gt {
 namespace {
 thread_local char g_err[512] = "";
+std::mutex g_log_mu;
+gt_log_fn g_log_fn = nullptr;
+void *g_log_user = nullptr;
+}  // namespace
+void logf(int level, const char *fmt, ...) {
+    gt_log_fn fn;
+    void *user;
+    {
+        std::lock_guard<std::mutex> lk(g_log_mu);
+        fn = g_log_fn;
+        user = g_log_user;
+    }
+    if (!fn) return;
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    fn(level, buf, user);
 }
 int failf(int code, const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
+    logf(GT_LOG_ERROR, "%s", g_err);
     return code;
 }
 }  // namespace gt
@@ -635,6 +655,13 @@ int engine_join_comm(gt_engine *e) { return join_comm(e); }
 extern "C" {
 
 const char *gt_last_error(void) { return g_err; }
+
+int gt_set_logger(gt_log_fn fn, void *user) {
+    std::lock_guard<std::mutex> lk(g_log_mu);
+    g_log_fn = fn;
+    g_log_user = user;
+    return GT_OK;
+}
 const char *gt_version(void) { return "glaciertune_b200 0.1 (sm_100a)"; }
 
 int gt_supports(int ggml_type, int direction) {
@@ -679,6 +706,17 @@ int gt_engine_create(const gt_config *cfg, gt_engine **out) {
     cudaError_t ce = cudaMalloc((void **)&e->status, 4 * sizeof(int));
     if (ce == cudaSuccess) ce = cudaMalloc((void **)&e->clip, 2 * sizeof(double));
     if (ce == cudaSuccess && aux_init(e) != GT_OK) ce = cudaErrorUnknown;      // side stream of the dA passes
+    // scratch sized up front, so that no projection call of up to max_tokens tokens on tensors of up to max_features
+    // input / output features allocates (a group's outputs together count as one tensor: q | k | v, gate | up)
+    e->max_tokens = (cfg && cfg->max_tokens > 0) ? cfg->max_tokens : 0;
+    if (ce == cudaSuccess && cfg && cfg->max_tokens > 0 && cfg->max_features > 0) {
+        const size_t T = (size_t)cfg->max_tokens, F = (size_t)cfg->max_features;
+        ce = e->x16.reserve(T * F * 2);
+        if (ce == cudaSuccess) ce = e->dy16.reserve(T * (F + 64) * 2 + 3 * 256);
+        for (int i = 0; i < 3 && ce == cudaSuccess; i++) ce = e->ffn[i].reserve(T * F * sizeof(float));
+        if (ce == cudaSuccess) logf(GT_LOG_INFO, "engine on device %d: scratch reserved for %zu tokens x %zu features (%.1f MB)", dev, T, F,
+                                    (double)(e->x16.cap + e->dy16.cap + 3 * e->ffn[0].cap) / 1e6);
+    }
     if (ce == cudaSuccess) ce = cudaMemset(e->status, 0, 4 * sizeof(int));
     if (ce != cudaSuccess) {
         gt_engine_destroy(e);
@@ -852,6 +890,8 @@ int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_
         gt_weight_free(w);
         return fail(GT_ERR_CUDA, "%s", msg ? msg : "tensor map creation failed");
     }
+    logf(GT_LOG_DEBUG, "weight [%d, %d] type %d uploaded: %.2f MB on device %d%s", out_features, in_features, ggml_type, (double)d.nbytes / 1e6,
+         e->device, d.tma_ok ? "" : " (CUDA-core path only)");
     *out = w;
     return GT_OK;
 }
@@ -911,6 +951,7 @@ int gt_adapter_create(gt_engine *e, int32_t in_features, int32_t out_features, i
     if (ce == cudaSuccess) ce = cudaMemsetAsync(a->dA, 0, na, e->stream);
     if (ce == cudaSuccess) ce = cudaMemsetAsync(a->dB, 0, nb, e->stream);
     if (ce == cudaSuccess) ce = cudaMemsetAsync(a->b_nonzero, 0, sizeof(int), e->stream);
+    if (ce == cudaSuccess && e->max_tokens > 0) ce = a->low.reserve(2 * low_bytes(a, e->max_tokens));      // X*A | dY*B^T of a step
     if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
     if (ce != cudaSuccess) {
         gt_adapter_free(a);

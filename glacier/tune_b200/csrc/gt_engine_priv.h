@@ -15,8 +15,10 @@
 #include "gt_quant.cuh"
 
 namespace gt {
-// records the text for gt_last_error() (per thread) and returns `code`
+// records the text for gt_last_error() (per thread), passes it to the logger, and returns `code`
 int failf(int code, const char *fmt, ...);
+// message to the callback installed with gt_set_logger (nothing when none is installed)
+void logf(int level, const char *fmt, ...);
 }  // namespace gt
 
 #define GT_CUDA(call)                                                                                        \
@@ -66,6 +68,7 @@ struct HostSlot {
 
 struct gt_engine {
     int device = 0;
+    int max_tokens = 0;          // gt_config.max_tokens: adapters reserve their per-step scratch for it at creation
     int math_mode = GT_MATH_BF16;
     int sm_count = 148;
     cudaStream_t stream = nullptr;

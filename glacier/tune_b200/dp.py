@@ -48,6 +48,17 @@ def group_buckets(entries, layer: int = 0, groups=BACKWARD_GROUPS):
     return out
 
 
+def layer_buckets(entries, layers: int, proj_order=PROJ_ORDER):
+    """(offset, size) of each layer's gradients inside the flat buffer, LAST layer first: the slices the training-step
+    driver (gt_model_forward_backward) all-reduces as soon as a block's backward is queued, beside the backward of
+    the blocks below it.  A layer's seven adapters are adjacent in the reference's parameter order."""
+    out = []
+    for layer in range(layers - 1, -1, -1):
+        first, last = entries[(layer, proj_order[0])], entries[(layer, proj_order[-1])]
+        out.append((first[0], last[2] + last[3] - first[0]))
+    return out
+
+
 def share_unique_id(make_id, dist_module, src: int = 0) -> bytes:
     """Rank `src` creates the communicator id; every rank returns the same bytes (torch.distributed rendezvous)."""
     box = [make_id() if dist_module.get_rank() == src else None]

@@ -87,9 +87,21 @@ typedef struct gt_config {
     int32_t device;       /* CUDA device ordinal                                              */
     int32_t math_mode;    /* gt_math_mode                                                     */
     void *stream;         /* cudaStream_t to run on, or NULL: the engine creates its own      */
-    int32_t max_tokens;   /* scratch is sized for this many tokens up front (0: 512); grows   */
-    int32_t reserved;
+    int32_t max_tokens;   /* with max_features: engine scratch (16-bit operand copies, FFN intermediates) and every
+                             adapter's per-step scratch are allocated for this many tokens at creation, so that no later
+                             projection call up to that size allocates; 0: allocate (and grow) on demand, as the
+                             reference does (src/Glacier.Tune/Gpu/GpuLoraEngine.Memory.cs:7-114)        */
+    int32_t max_features; /* largest in/out feature count of a projection, a group's outputs counted together
+                             (q|k|v, gate|up: 2 x 18944 for the 7B layer); 0: nothing reserved up front      */
 } gt_config;
+
+/* Log callback (the reference logs through GlacierDiagnostics, e.g. src/Glacier.Tune/Gpu/GpuLoraEngine.cs:251,320 and
+ * the CPU-fallback warning at src/Glacier.Tune/Model/GgufLoraModel.cs:76-80).  The library calls it, from the calling
+ * thread, with every error text it records and with informational messages (uploads, reserved scratch); without a
+ * callback it is silent.  Process-wide. */
+enum gt_log_level { GT_LOG_DEBUG = 0, GT_LOG_INFO = 1, GT_LOG_ERROR = 2 };
+typedef void (*gt_log_fn)(int level, const char *message, void *user);
+GT_API int gt_set_logger(gt_log_fn fn_or_null, void *user);
 
 GT_API const char *gt_last_error(void);
 GT_API const char *gt_version(void);

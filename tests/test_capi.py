@@ -71,3 +71,31 @@ def test_package_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "gt_oracle" not in src and "from oracle" not in src and "import oracle" not in src, f
+
+
+def test_logger_receives_the_error_texts():
+    """gt_set_logger: every recorded error text reaches the callback (and nothing is printed without one)."""
+    from glacier.tune_b200 import capi
+    lib = capi.load_library()
+    seen = []
+    capi.set_logger(lambda level, msg: seen.append((level, msg)))
+    try:
+        assert lib.gt_sync(None) == -1
+        assert seen and seen[-1][0] == 2 and "null" in seen[-1][1]
+    finally:
+        capi.set_logger(None)
+    n = len(seen)
+    assert lib.gt_sync(None) == -1
+    assert len(seen) == n          # callback removed
+
+
+def test_new_entry_points_reject_null_arguments():
+    from glacier.tune_b200 import capi
+    lib = capi.load_library()
+    assert lib.gt_lm_head_loss(None, None, None, None, 4, None, None, None, 0) == -1
+    assert lib.gt_attention_forward(None, None, None, None, None, None, 4, 2, 1, 128) == -1
+    assert lib.gt_model_create(None, None, None) == -1
+    assert lib.gt_model_forward_backward(None, None, None, 4, None, 0) == -1
+    assert lib.gt_model_destroy(None) == 0
+    assert lib.gt_supports_attention(512, 128) == 1 and lib.gt_supports_attention(512, 96) == 0
+    assert capi.supports(capi.TYPE_F16, capi.DIR_FORWARD)

@@ -142,3 +142,91 @@ def test_lost_rank_surfaces_as_an_error_not_a_hang(tmp_path):
         if p.is_alive():
             p.kill()
     assert outcome.startswith("error"), outcome
+
+
+def _tiny_model(O, seed):
+    """Two blocks of the workload's architecture at toy size, in the oracle's dict form (same on every rank)."""
+    rng = np.random.default_rng(seed)
+    H, HQ, HK, D, F, V, R = 256, 2, 1, 128, 256, 300, 8
+    cfg = dict(n_heads=HQ, n_kv_heads=HK, head_dim=D, rms_eps=1e-6, rope_theta=1e6, vocab=V, hidden=H, ffn=F)
+    shapes = dict(q=(HQ * D, H), k=(HK * D, H), v=(HK * D, H), o=(H, HQ * D), gate=(F, H), up=(F, H), down=(H, F))
+    layers = []
+    for l in range(2):
+        P = {}
+        for j, (name, (N, K)) in enumerate(shapes.items()):
+            P[name] = dict(qtype=synth.TYPE_Q6_K, w=synth.make_weight(synth.TYPE_Q6_K, N, K, seed + 10 * l + j), N=N, K=K, bias=None,
+                           a=(rng.standard_normal((K, R)) / np.sqrt(K)).astype(np.float32),
+                           b=(rng.standard_normal((R, N)) * 0.02).astype(np.float32), rank=R, scaling=2.0)
+        layers.append(dict(norm1=np.full(H, 0.4, np.float32), norm2=np.full(H, 0.4, np.float32), proj=P))
+    return dict(cfg=cfg, layers=layers, embed=(O.TYPE_F16, (rng.standard_normal((V, H)) * 0.02).astype(np.float16)),
+                out_norm=np.ones(H, np.float32), lm_head=(O.TYPE_F16, (rng.standard_normal((V, H)) * 0.02).astype(np.float16)))
+
+
+def _rank_batch(rank, V, T=10):
+    rng = np.random.default_rng(500 + rank)
+    tokens = rng.integers(0, V, T).astype(np.int32)
+    labels = np.roll(tokens, -1).astype(np.int32)
+    labels[-1] = -100
+    return tokens, labels
+
+
+def _step_worker(rank, world, port, out_dir):
+    """One data-parallel training step per rank on the CPU chain: own sequence -> gradients -> per-layer exchange (last
+    layer first) -> clip -> AdamW.  What gt_model_forward_backward + gt_model_optimizer_step do on the GPUs."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import oracle as O
+    model = _tiny_model(O, 42)
+    tokens, labels = _rank_batch(rank, model["cfg"]["vocab"])
+    grads = O.new_grads(model)
+    loss = O.model_forward_backward(model, tokens, labels, grads)
+    flat = torch.from_numpy(O.flat_grads(model, grads).copy())
+    shapes = [(n, model["layers"][0]["proj"][n]["N"], model["layers"][0]["proj"][n]["K"]) for n in dp.PROJ_ORDER]
+    entries, total = dp.flat_grad_layout(shapes, 8, layers=2)
+    assert total == flat.numel()
+    buckets = dp.layer_buckets(entries, 2)
+    assert buckets[0][0] + buckets[0][1] == total and buckets[-1][0] == 0       # last layer first, together the whole buffer
+    dp.average_gradients_bucketed(flat, buckets, dist)
+    g = flat.numpy()
+    norm = O.clip_gradients(g, 1.0)
+    off = 0
+    for layer in model["layers"]:
+        for name in dp.PROJ_ORDER:
+            for key in ("a", "b"):
+                p = layer["proj"][name][key]
+                O.adamw_step(p.reshape(-1), g[off:off + p.size], np.zeros(p.size, np.float32), np.zeros(p.size, np.float32),
+                             lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=1)
+                off += p.size
+    params = np.concatenate([layer["proj"][n][k].reshape(-1) for layer in model["layers"] for n in dp.PROJ_ORDER for k in ("a", "b")])
+    np.save(os.path.join(out_dir, f"params_{rank}.npy"), params)
+    np.save(os.path.join(out_dir, f"meta_{rank}.npy"), np.array([loss, norm], np.float64))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_training_step_keeps_replicas_identical(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_step_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    p0, p1 = (np.load(tmp_path / f"params_{r}.npy") for r in range(world))
+    assert np.array_equal(p0, p1)                         # every rank took the same optimizer step
+    m0, m1 = (np.load(tmp_path / f"meta_{r}.npy") for r in range(world))
+    assert m0[1] == m1[1] and m0[0] != m1[0]              # same global norm after the exchange, different local losses
+    # single process: accumulate both sequences' gradients, scale by 1/2, clip, step (LoraTrainer.cs:217-231)
+    from oracle import oracle as O
+    model = _tiny_model(O, 42)
+    grads = O.new_grads(model)
+    for r in range(world):
+        O.model_forward_backward(model, *_rank_batch(r, model["cfg"]["vocab"]), grads)
+    g = O.flat_grads(model, grads) * np.float32(0.5)
+    norm = O.clip_gradients(g, 1.0)
+    assert abs(norm - m0[1]) < 1e-5 * norm
+    off = 0
+    for layer in model["layers"]:
+        for name in dp.PROJ_ORDER:
+            for key in ("a", "b"):
+                p = layer["proj"][name][key]
+                O.adamw_step(p.reshape(-1), g[off:off + p.size], np.zeros(p.size, np.float32), np.zeros(p.size, np.float32),
+                             lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=1)
+                off += p.size
+    want = np.concatenate([layer["proj"][n][k].reshape(-1) for layer in model["layers"] for n in dp.PROJ_ORDER for k in ("a", "b")])
+    assert np.allclose(p0, want, rtol=1e-5, atol=1e-6)

@@ -507,3 +507,27 @@ def test_run_twice_reproducibility(G, eng, oracle):
     dxr = oracle.base_backward_f64(c2["qtype"], c2["w"], c2["dy"], K2, N2, T)
     assert oracle.rel_fro(got[0], dxr) < 2e-2
     w2.free()
+
+
+def test_reserved_scratch_makes_steady_state_allocation_free(G):
+    """gt_config.max_tokens / max_features: after engine, weight and adapter creation a projection call of that size
+    takes no device memory (the reference grows its scratch on demand inside the call)."""
+    import torch
+    N, K, T = 512, 768, 200
+    c = S.make_projection_case(S.TYPE_Q4_K, N, K, T, seed=91)
+    e = G.Engine(0, G.MATH_BF16, max_tokens=T, max_features=max(N, K))
+    w = e.upload_weight(c["qtype"], c["w"], N, K)
+    ad = e.create_adapter(K, N, 16, 32.0)
+    ad.upload(c["a"], c["b"])
+    X, dY = torch.from_numpy(c["x"]).cuda(), torch.from_numpy(c["dy"]).cuda()
+    Y, dX = torch.empty((T, N), device="cuda"), torch.empty((T, K), device="cuda")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    e.forward(w, ad, X, Y)
+    e.backward(w, ad, dY, X, dX, flags=G.FLAG_REUSE_LOW | G.FLAG_DX_ASSIGN)
+    e.sync()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, (free0, free1)
+    w.free()
+    ad.free()
+    e.close()
