@@ -82,14 +82,15 @@ cudaEvent_t next_event(gt_engine *e) {
 }
 
 // launch the tensor-core GEMM (one launch for all members), bracketed by events when profiling is on
-cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg) {
+cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on) {
+    cudaStream_t st = on ? on : e->stream;
     cudaEvent_t a = nullptr, b = nullptr;
     if (e->profile) {
         a = next_event(e);
         b = next_event(e);
         if (a) cudaEventRecord(a, e->stream);
     }
-    cudaError_t ce = launch_umma_group(m, n, e->stream, msg);
+    cudaError_t ce = launch_umma_group(m, n, st, msg);
     if (ce != cudaSuccess) cudaGetLastError();      // a refused launch must not linger as the thread's "last error"
     if (e->profile && b) cudaEventRecord(b, e->stream);
     e->gemm_launches += 1;
@@ -265,21 +266,96 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         GT_LAUNCH(e, launch_cast16(Xd, e->x16.p, T, K, K, fp16, e->stream));
         for (int j = 0; j < n_fills; j++) GT_LAUNCH(e, launch_fill_rows(fills[j].dst, fills[j].bias, T, fills[j].N, e->stream));
     }
+    // A Q4_K_M mix gives two launches (q, k in Q4_K | v in Q6_K) that read the same X and write different outputs: the
+    // second one runs on the side stream beside the first (neither fills the GPU by itself)
+    const bool side = runs > 1 && e->s_aux && !e->profile && side_da_enabled();
+    if (side) {
+        GT_CUDA(cudaEventRecord(e->ev_aux_fork, e->stream));
+        GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));
+    }
     for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
         for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
         const char *msg = nullptr;
-        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg);
+        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg, (side && r > 0) ? e->s_aux : nullptr);
         if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    }
+    if (side) {
+        GT_CUDA(cudaEventRecord(e->ev_aux_join, e->s_aux));
+        GT_CUDA(cudaStreamWaitEvent(e->stream, e->ev_aux_join, 0));
     }
     return GT_OK;
 }
 
 // out[T, N] = act * W^T (+bias) (+ lora) on the engine stream, device pointers.
+// the base product of a paired-row tensor on the tensor path (see the paired-row kernels in gt_fp32_kernels.cu)
+bool paired_path(const gt_engine *e, const gt_weight *w) { return e->math_mode != GT_MATH_FP32 && w->has_paired; }
+
+int paired_forward_base(gt_engine *e, const gt_weight *w, const float *Xd, float *Yd, int T) {
+    const WeightDev &wd = w->dev, &pv = w->paired;
+    const int fp16 = e->math_mode == GT_MATH_FP16;
+    GT_CUDA(e->x16.reserve((size_t)2 * T * pv.K * 2));
+    GT_CUDA(e->pair_tmp.reserve((size_t)2 * T * pv.N * sizeof(float)));
+    GT_LAUNCH(e, launch_pair_expand16(Xd, e->x16.p, T, wd.K, fp16, e->stream));
+    UmmaLaunch L;
+    L.w = &pv;
+    L.fp16 = fp16;
+    L.act16 = e->x16.p;
+    L.ld_act = pv.K;
+    L.T = 2 * T;
+    L.out = (float *)e->pair_tmp.p;
+    L.ld_out = pv.N;
+    L.status = e->status;
+    L.trace = e->trace;
+    L.splits = umma_group_splits(&L, 1, e->sm_count);
+    if (L.splits > 1) {
+        GT_LAUNCH(e, launch_fill_rows(L.out, nullptr, 2 * T, pv.N, e->stream));
+        L.out_prefilled = 1;
+    }
+    const char *msg = nullptr;
+    cudaError_t ce = timed_umma_group(e, &L, 1, &msg);
+    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    GT_LAUNCH(e, launch_pair_interleave(L.out, wd.bias, Yd, T, wd.N, e->stream));
+    return GT_OK;
+}
+
+int paired_backward_base(gt_engine *e, const gt_weight *w, const float *dYd, float *dXd, int T, bool assign) {
+    const WeightDev &wd = w->dev, &pv = w->paired;
+    const int fp16 = e->math_mode == GT_MATH_FP16;
+    const int ld16 = round8(pv.N);
+    GT_CUDA(e->dy16.reserve((size_t)2 * T * ld16 * 2));
+    GT_CUDA(e->pair_tmp.reserve((size_t)2 * T * pv.K * sizeof(float)));
+    GT_LAUNCH(e, launch_pair_gather16(dYd, e->dy16.p, T, wd.N, ld16, fp16, e->stream));
+    UmmaLaunch L;
+    L.w = &pv;
+    L.backward = 1;
+    L.fp16 = fp16;
+    L.act16 = e->dy16.p;
+    L.ld_act = ld16;
+    L.T = 2 * T;
+    L.out = (float *)e->pair_tmp.p;
+    L.ld_out = pv.K;
+    L.status = e->status;
+    L.trace = e->trace;
+    L.splits = umma_group_splits(&L, 1, e->sm_count);
+    if (L.splits == 1) L.out_assign = 1;
+    else GT_LAUNCH(e, launch_fill_rows(L.out, nullptr, 2 * T, pv.K, e->stream));
+    const char *msg = nullptr;
+    cudaError_t ce = timed_umma_group(e, &L, 1, &msg);
+    if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+    GT_LAUNCH(e, launch_pair_fold(L.out, dXd, T, wd.K, assign ? 1 : 0, e->stream));
+    return GT_OK;
+}
+
 int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora) {
     if (tensor_path(e, w)) return forward_group_device(e, 1, &w, &ad, Xd, &Yd, T, use_lora ? 0 : GT_FLAG_NO_LORA);
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
-    GT_LAUNCH(e, launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
+    if (paired_path(e, w)) {
+        int prc = paired_forward_base(e, w, Xd, Yd, T);
+        if (prc != GT_OK) return prc;
+    } else {
+        GT_LAUNCH(e, launch_gemm_fp32_fwd(wd.qtype, wd.data, Xd, Yd, nullptr, wd.bias, T, N, K, e->stream));
+    }
     if (use_lora) {
         int rc = compute_low(e, &ad, 1, Xd, nullptr, 0, T, K);
         if (rc != GT_OK) return rc;
@@ -444,11 +520,22 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
             run_m[pos + i].splits = run_splits[r];
         }
         run_m[pos].out_assign = (r == 0 && store_first) ? 1 : 0;
+        // launches of the other quantization types add into the same dX with atomics: beside the first one on the side
+        // stream (behind the dA pass there), unless the first one writes dX with plain stores
+        const bool side = r > 0 && !store_first && e->s_aux && !e->profile && side_da_enabled();
+        if (side && !e->aux_pending) {      // no dA pass was forked: fork now (the pass over dY is complete by stream order)
+            GT_CUDA(cudaEventRecord(e->ev_aux_fork, e->stream));
+            GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));
+        }
         const char *msg = nullptr;
-        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg);
+        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg, side ? e->s_aux : nullptr);
         if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "backward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
+        if (side) {
+            GT_CUDA(cudaEventRecord(e->ev_aux_join, e->s_aux));
+            e->aux_pending = true;
+        }
     }
-    return aux_join(e);      // the dA pass on the side stream is part of this call
+    return aux_join(e);      // the dA pass and the side launches are part of this call
 }
 
 // dX += dY*W (+ lora term); dA, dB accumulate.  Device pointers.
@@ -461,7 +548,13 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
     // exact fp32 kernels (validation mode, weights outside the tensor-core layout) or adapter gradients only
     const WeightDev &wd = w->dev;
     const int N = wd.N, K = wd.K;
-    if (assign && dXd) GT_LAUNCH(e, launch_fill_rows(dXd, nullptr, T, K, e->stream));
+    const bool paired = paired_path(e, w) && dXd;
+    if (paired) {      // the base product writes (or adds into) dX itself
+        int prc = paired_backward_base(e, w, dYd, dXd, T, assign);
+        if (prc != GT_OK) return prc;
+    } else if (assign && dXd) {
+        GT_LAUNCH(e, launch_fill_rows(dXd, nullptr, T, K, e->stream));
+    }
     if (use_lora) {
         const bool lora = true;
         void *no16 = nullptr;
@@ -470,7 +563,7 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
         if (rc != GT_OK) return rc;
         if (dXd) GT_LAUNCH(e, launch_lora_dx_fp32(dlow_of(ad, T), ad->A, dXd, ad->scaling, T, K, ad->rank, e->stream));
     }
-    if (dXd) GT_LAUNCH(e, launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
+    if (dXd && !paired) GT_LAUNCH(e, launch_gemm_fp32_bwd(wd.qtype, wd.data, dYd, dXd, T, N, K, e->stream));
     return GT_OK;
 }
 
@@ -732,7 +825,7 @@ int gt_engine_destroy(gt_engine *e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     if (e->s_h2d) cudaStreamSynchronize(e->s_h2d);
     if (e->s_d2h) cudaStreamSynchronize(e->s_d2h);
-    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->ffn[0], &e->ffn[1], &e->ffn[2], &e->ce, &e->ce_host, &e->attn};
+    Scratch *all[] = {&e->x16, &e->dy16, &e->dlow, &e->ytmp, &e->pair_tmp, &e->ffn[0], &e->ffn[1], &e->ffn[2], &e->ce, &e->ce_host, &e->attn};
     for (Scratch *s : all) s->release();
     for (HostSlot &sl : e->slots) {
         for (Scratch &b : sl.in) b.release();
@@ -890,8 +983,18 @@ int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_
         gt_weight_free(w);
         return fail(GT_ERR_CUDA, "%s", msg ? msg : "tensor map creation failed");
     }
+    if (!d.tma_ok && (ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K) && in_features % 256 == 128 && out_features % 2 == 0) {
+        WeightDev &v = w->paired;
+        v = d;
+        v.bias = nullptr;
+        v.N = out_features / 2;
+        v.K = 2 * in_features;
+        v.row_bytes = (int64_t)(v.K / 256) * dev_block_bytes(ggml_type);
+        const char *pm = nullptr;
+        w->has_paired = umma_init_weight_maps(&v, &pm) == cudaSuccess && v.tma_ok;
+    }
     logf(GT_LOG_DEBUG, "weight [%d, %d] type %d uploaded: %.2f MB on device %d%s", out_features, in_features, ggml_type, (double)d.nbytes / 1e6,
-         e->device, d.tma_ok ? "" : " (CUDA-core path only)");
+         e->device, d.tma_ok ? "" : (w->has_paired ? " (tensor path through the paired-row view)" : " (CUDA-core path only)"));
     *out = w;
     return GT_OK;
 }

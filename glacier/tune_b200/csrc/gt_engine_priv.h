@@ -76,7 +76,7 @@ struct gt_engine {
     std::mutex mu;
     int *status = nullptr;       // device int[4]; [0] = first bounded-wait timeout code
     double *clip = nullptr;      // device double[2]
-    Scratch x16, dy16, dlow, ytmp;
+    Scratch x16, dy16, dlow, ytmp, pair_tmp;
     Scratch ce, ce_host;         // LM-head cross-entropy: logits / probability tiles and per-token state; host staging
     Scratch attn;                // attention: log-sum-exp rows and the dO.O row sums
     Scratch ffn[3];              // gate, up, hidden (forward) / dHidden, dGate, dUp (backward) of the fused FFN calls
@@ -109,6 +109,10 @@ struct gt_engine {
 struct gt_weight {
     gt_engine *eng = nullptr;
     gt::WeightDev dev;
+    // K-quant tensor with in_features % 256 == 128 and an even row count: the same bytes seen as [N / 2, 2 K], whole
+    // super-blocks per row, with tensor maps (shares dev.data; owns nothing)
+    gt::WeightDev paired;
+    bool has_paired = false;
 };
 
 struct gt_adapter {
@@ -132,7 +136,9 @@ namespace gt {
 constexpr int kMaxGroup = 3;
 int check_status(gt_engine *e);
 bool tensor_path(const gt_engine *e, const gt_weight *w);
-cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg);
+// launch (bracketed by events while profiling) on the engine stream, or on `on` when given
+cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on = nullptr);
+bool side_da_enabled();
 // device-pointer forms of the projection calls; the caller holds the engine lock and has made the device current
 int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
                          int T, int flags);

@@ -209,6 +209,77 @@ cudaError_t launch_cast16(const float *src, void *dst, int rows, int cols, int l
     return launch_k(k_cast16, dim3(blocks), dim3(256), 0, s, src, (uint16_t *)dst, rows, cols, ld_dst, fp16);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Paired rows: a K-quant tensor whose rows are HALF a whole number of super-blocks (in_features % 256 == 128, the
+// 4864 x 896 case: 3.5 blocks per row) is, as a byte stream, also the tensor W2 [out / 2, 2 * in] whose row s is row 2s
+// followed by row 2s + 1 - and W2 has whole super-blocks per row, so the TMA / tensor-core kernel can read it.
+//   forward   Y[t, 2s + h] = X[t] . W[2s + h]  =  X2[2t + h] . W2[s]   with X2[2t] = [X[t] | 0], X2[2t + 1] = [0 | X[t]]
+//   backward  dX[t] = sum_s dY[t, 2s] W2[s, :in] + dY[t, 2s + 1] W2[s, in:]  =  Z[2t, :in] + Z[2t + 1, in:],
+//             Z = dY2 W2 with dY2[2t + h, s] = dY[t, 2s + h]
+// Half of the MMA work multiplies zeros; what it buys is the tensor path for a shape that otherwise runs on CUDA cores.
+// ------------------------------------------------------------------------------------------------
+// x2 [2T, 2K] 16-bit from X [T, K] fp32
+__global__ void k_pair_expand16(const float *__restrict__ X, uint16_t *__restrict__ x2, int T, int K, int fp16) {
+    const int64_t total = (int64_t)2 * T * 2 * K;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % (2 * K));
+        const int64_t r = i / (2 * K);
+        const int h = (int)(r & 1);
+        const int64_t t = r >> 1;
+        const bool live = (c >= K) == (h == 1);
+        const float v = live ? X[t * K + (c - h * K)] : 0.f;
+        x2[i] = fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    }
+}
+// Y [T, N] (+)= tmp [2T, N / 2] interleaved, + bias
+__global__ void k_pair_interleave(const float *__restrict__ tmp, const float *__restrict__ bias, float *__restrict__ Y, int T, int N) {
+    const int64_t total = (int64_t)T * N;
+    const int half = N >> 1;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int n = (int)(i % N);
+        const int64_t t = i / N;
+        Y[i] = tmp[(2 * t + (n & 1)) * half + (n >> 1)] + (bias ? bias[n] : 0.f);
+    }
+}
+// dy2 [2T, ld] 16-bit: dy2[2t + h, s] = dY[t, 2s + h]; columns at and beyond N / 2 are zero
+__global__ void k_pair_gather16(const float *__restrict__ dY, uint16_t *__restrict__ dy2, int T, int N, int ld, int fp16) {
+    const int64_t total = (int64_t)2 * T * ld;
+    const int half = N >> 1;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int s = (int)(i % ld);
+        const int64_t r = i / ld;
+        const float v = s < half ? dY[(r >> 1) * N + 2 * s + (int)(r & 1)] : 0.f;
+        dy2[i] = fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    }
+}
+// dX [T, K] (= or +=) Z[2t, :K] + Z[2t + 1, K:]
+__global__ void k_pair_fold(const float *__restrict__ Z, float *__restrict__ dX, int T, int K, int assign) {
+    const int64_t total = (int64_t)T * K;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int k = (int)(i % K);
+        const int64_t t = i / K;
+        const float v = Z[(2 * t) * 2 * K + k] + Z[(2 * t + 1) * 2 * K + K + k];
+        dX[i] = assign ? v : dX[i] + v;
+    }
+}
+static unsigned pair_blocks(int64_t total) { return (unsigned)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256); }
+cudaError_t launch_pair_expand16(const float *X, void *x2, int T, int K, int fp16, cudaStream_t s) {
+    k_pair_expand16<<<pair_blocks((int64_t)4 * T * K), 256, 0, s>>>(X, (uint16_t *)x2, T, K, fp16);
+    return cudaGetLastError();
+}
+cudaError_t launch_pair_interleave(const float *tmp, const float *bias, float *Y, int T, int N, cudaStream_t s) {
+    k_pair_interleave<<<pair_blocks((int64_t)T * N), 256, 0, s>>>(tmp, bias, Y, T, N);
+    return cudaGetLastError();
+}
+cudaError_t launch_pair_gather16(const float *dY, void *dy2, int T, int N, int ld, int fp16, cudaStream_t s) {
+    k_pair_gather16<<<pair_blocks((int64_t)2 * T * ld), 256, 0, s>>>(dY, (uint16_t *)dy2, T, N, ld, fp16);
+    return cudaGetLastError();
+}
+cudaError_t launch_pair_fold(const float *Z, float *dX, int T, int K, int assign, cudaStream_t s) {
+    k_pair_fold<<<pair_blocks((int64_t)T * K), 256, 0, s>>>(Z, dX, T, K, assign);
+    return cudaGetLastError();
+}
+
 __global__ void k_fill_rows(float *__restrict__ Y, const float *__restrict__ bias, int T, int N) {
     pdl_wait();
     pdl_trigger();

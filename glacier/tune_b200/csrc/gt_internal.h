@@ -67,6 +67,11 @@ cudaError_t launch_lora_bwd_x(const float *X, const float *dLow, float *dA, floa
 cudaError_t launch_lora_dx_fp32(const float *dLow, const float *A, float *dX, float scaling, int T, int K, int R,
                                 cudaStream_t s);
 cudaError_t launch_cast16(const float *src, void *dst, int rows, int cols, int ld_dst, int fp16, cudaStream_t s);
+// paired-row view of a tensor with in_features % 256 == 128 (see gt_fp32_kernels.cu)
+cudaError_t launch_pair_expand16(const float *X, void *x2, int T, int K, int fp16, cudaStream_t s);
+cudaError_t launch_pair_interleave(const float *tmp, const float *bias, float *Y, int T, int N, cudaStream_t s);
+cudaError_t launch_pair_gather16(const float *dY, void *dy2, int T, int N, int ld, int fp16, cudaStream_t s);
+cudaError_t launch_pair_fold(const float *Z, float *dX, int T, int K, int assign, cudaStream_t s);
 // Y[t, :] = bias (or 0)
 cudaError_t launch_fill_rows(float *Y, const float *bias, int T, int N, cudaStream_t s);
 // residual += Y
