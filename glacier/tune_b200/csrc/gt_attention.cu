@@ -20,7 +20,7 @@
 //   k_attn_delta    rowsum(dO * out) per (head, query)
 //   k_attn_bwd_dq   grid (query tiles, heads_q): dq of one tile, summed over its key tiles in registers
 //   k_attn_bwd_dkv  grid (key tiles, heads_q): dk, dv of one key tile for ONE query head, summed over the query tiles
-//                   in registers, written to a per-query-head workspace
+//                   in registers, written to a per-query-head workspace (both: eight compute + four fetch warps)
 //   k_attn_reduce_kv sums the query heads of each KV group (fixed order: results do not change from run to run)
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -252,7 +252,7 @@ __global__ void k_attn_delta(const float *__restrict__ d_out, const float *__res
     if (lane == 0) delta[(int64_t)h * T + t] = s;
 }
 
-// Shared first phase of both backward kernels, 8 warps: warp = query m-tile (warp & 3) x key half (warp >> 2).
+// Shared first phase of both backward kernels, 8 compute warps: warp = query m-tile (warp & 3) x key half (warp >> 2).
 //   S2 = Qs Ks^T (base-2 scores, Qs pre-scaled), P = exp2(S2 - lse2), dP = dOs Vs^T, dS = P (dP - delta) / sqrt(D)
 // P and dS go to shared memory as [query][key] 16-bit tiles (zero where masked).
 template <typename T16>
@@ -304,47 +304,66 @@ __device__ __forceinline__ void bwd_scores(uint32_t qs, uint32_t ks, uint32_t vs
     }
 }
 
-constexpr int kBwdSmem = 4 * 64 * SD + 2 * 64 * SP;
+// Both backward kernels: 8 compute warps + 4 fetch warps (384 threads).  The tiles that change from iteration to
+// iteration (key / value tiles in the dq kernel, query / dO tiles in the dk, dv kernel) are double-buffered: the fetch
+// warps load, round and store the next pair while the compute warps work on the current one.
+constexpr int kBwdSmem = 6 * 64 * SD + 2 * 64 * SP;
+__device__ __forceinline__ void compute_warps_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-// dq[query tile] = sum over key tiles j <= i of dS K.  8 warps: query m-tile (warp & 3) x half of head_dim (warp >> 2).
+// dq[query tile] = sum over key tiles j <= i of dS K.  Compute warps: query m-tile (warp & 3) x half of head_dim (warp >> 2).
 template <typename T16>
-__global__ void __launch_bounds__(256) k_attn_bwd_dq(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
+__global__ void __launch_bounds__(384) k_attn_bwd_dq(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
                                                      const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
                                                      float *__restrict__ dq, int T, int HQ, int HK) {
     extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t *Qs = smem, *dOs = Qs + 64 * SD, *Ks = dOs + 64 * SD, *Vs = Ks + 64 * SD, *Ps = Vs + 64 * SD, *dSs = Ps + 64 * SP;
+    uint8_t *Qs = smem, *dOs = Qs + 64 * SD, *Ps = smem + 6 * 64 * SD, *dSs = Ps + 64 * SP;
+    auto kbuf = [&](int b) { return smem + (2 + 2 * b) * 64 * SD; };
+    auto vbuf = [&](int b) { return smem + (3 + 2 * b) * 64 * SD; };
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const bool compute = warp < 8;
     const int it = blockIdx.x, h = blockIdx.y, kh = h / (HQ / HK);
     const int q0 = it * BQ;
     const int64_t ldq = (int64_t)HQ * D, ldk = (int64_t)HK * D;
-    load_tile<T16, 256>(q, ldq, h * D, q0, T, kLog2e * rsqrtf((float)D), Qs, tid);
-    load_tile<T16, 256>(d_out, ldq, h * D, q0, T, 1.f, dOs, tid);
-    const uint32_t qs = smem_u32(Qs), dos = smem_u32(dOs), ks = smem_u32(Ks), vs = smem_u32(Vs), dss = smem_u32(dSs);
-    const int m0 = (warp & 3) * 16, dh = (warp >> 2) * 64;
+    if (compute) {
+        load_tile<T16, 256>(q, ldq, h * D, q0, T, kLog2e * rsqrtf((float)D), Qs, tid);
+        load_tile<T16, 256>(d_out, ldq, h * D, q0, T, 1.f, dOs, tid);
+    } else {
+        load_tile<T16, 128>(k, ldk, kh * D, 0, T, 1.f, kbuf(0), tid - 256);
+        load_tile<T16, 128>(v, ldk, kh * D, 0, T, 1.f, vbuf(0), tid - 256);
+    }
+    __syncthreads();
+    const uint32_t qs = smem_u32(Qs), dos = smem_u32(dOs), dss = smem_u32(dSs);
+    const int m0 = (warp & 3) * 16, dh = ((warp >> 2) & 1) * 64;
     float acc[8][4];
 #pragma unroll
     for (int n = 0; n < 8; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
     for (int jt = 0; jt <= it; jt++) {
         const int k0 = jt * BK;
-        __syncthreads();
-        load_tile<T16, 256>(k, ldk, kh * D, k0, T, 1.f, Ks, tid);
-        load_tile<T16, 256>(v, ldk, kh * D, k0, T, 1.f, Vs, tid);
-        __syncthreads();
-        bwd_scores<T16>(qs, ks, vs, dos, Ps, dSs, lse2 + (int64_t)h * T, delta + (int64_t)h * T, q0, k0, T, warp, lane);
-        __syncthreads();
+        if (!compute) {
+            if (jt + 1 <= it) {
+                load_tile<T16, 128>(k, ldk, kh * D, k0 + BK, T, 1.f, kbuf((jt + 1) & 1), tid - 256);
+                load_tile<T16, 128>(v, ldk, kh * D, k0 + BK, T, 1.f, vbuf((jt + 1) & 1), tid - 256);
+            }
+        } else {
+            const uint32_t ks = smem_u32(kbuf(jt & 1)), vs = smem_u32(vbuf(jt & 1));
+            bwd_scores<T16>(qs, ks, vs, dos, Ps, dSs, lse2 + (int64_t)h * T, delta + (int64_t)h * T, q0, k0, T, warp, lane);
+            compute_warps_sync();
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; kk++) {
-            uint32_t a[4];
-            ldsm4(a_mk(dss, SP, m0, kk * 16, lane), a);
+            for (int kk = 0; kk < BK / 16; kk++) {
+                uint32_t a[4];
+                ldsm4(a_mk(dss, SP, m0, kk * 16, lane), a);
 #pragma unroll
-            for (int n = 0; n < 8; n += 2) {
-                uint32_t b[4];
-                ldsm4t(b_kn(ks, SD, dh + n * 8, kk * 16, lane), b);
-                mma16<T16>(acc[n], a, b[0], b[1]);
-                mma16<T16>(acc[n + 1], a, b[2], b[3]);
+                for (int n = 0; n < 8; n += 2) {
+                    uint32_t b[4];
+                    ldsm4t(b_kn(ks, SD, dh + n * 8, kk * 16, lane), b);
+                    mma16<T16>(acc[n], a, b[0], b[1]);
+                    mma16<T16>(acc[n + 1], a, b[2], b[3]);
+                }
             }
         }
+        __syncthreads();      // the next tiles are in place; P / dS and this iteration's buffers are free
     }
+    if (!compute) return;
 #pragma unroll
     for (int r = 0; r < 2; r++) {
         const int qi = q0 + m0 + g + 8 * r;
@@ -356,52 +375,67 @@ __global__ void __launch_bounds__(256) k_attn_bwd_dq(const float *__restrict__ d
 }
 
 // dk, dv of one key tile for one query head, summed over the query tiles i >= j, into the per-head workspace
-// wk, wv [heads_q, T, head_dim].  8 warps: key m-tile (warp & 3) x half of head_dim (warp >> 2).
+// wk, wv [heads_q, T, head_dim].  Compute warps: key m-tile (warp & 3) x half of head_dim (warp >> 2).
 template <typename T16>
-__global__ void __launch_bounds__(256) k_attn_bwd_dkv(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
+__global__ void __launch_bounds__(384) k_attn_bwd_dkv(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
                                                       const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
                                                       float *__restrict__ wk, float *__restrict__ wv, int T, int HQ, int HK) {
     extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t *Qs = smem, *dOs = Qs + 64 * SD, *Ks = dOs + 64 * SD, *Vs = Ks + 64 * SD, *Ps = Vs + 64 * SD, *dSs = Ps + 64 * SP;
+    uint8_t *Ks = smem, *Vs = Ks + 64 * SD, *Ps = smem + 6 * 64 * SD, *dSs = Ps + 64 * SP;
+    auto qbuf = [&](int b) { return smem + (2 + 2 * b) * 64 * SD; };
+    auto obuf = [&](int b) { return smem + (3 + 2 * b) * 64 * SD; };
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const bool compute = warp < 8;
     const int jt = blockIdx.x, h = blockIdx.y, kh = h / (HQ / HK);
     const int k0 = jt * BK;
     const int64_t ldq = (int64_t)HQ * D, ldk = (int64_t)HK * D;
-    load_tile<T16, 256>(k, ldk, kh * D, k0, T, 1.f, Ks, tid);
-    load_tile<T16, 256>(v, ldk, kh * D, k0, T, 1.f, Vs, tid);
-    const uint32_t qs = smem_u32(Qs), dos = smem_u32(dOs), ks = smem_u32(Ks), vs = smem_u32(Vs), ps = smem_u32(Ps), dss = smem_u32(dSs);
-    const int m0 = (warp & 3) * 16, dh = (warp >> 2) * 64;
+    const float qscale = kLog2e * rsqrtf((float)D);
+    if (compute) {
+        load_tile<T16, 256>(k, ldk, kh * D, k0, T, 1.f, Ks, tid);
+        load_tile<T16, 256>(v, ldk, kh * D, k0, T, 1.f, Vs, tid);
+    } else {
+        load_tile<T16, 128>(q, ldq, h * D, jt * BQ, T, qscale, qbuf(0), tid - 256);
+        load_tile<T16, 128>(d_out, ldq, h * D, jt * BQ, T, 1.f, obuf(0), tid - 256);
+    }
+    __syncthreads();
+    const uint32_t ks = smem_u32(Ks), vs = smem_u32(Vs), ps = smem_u32(Ps), dss = smem_u32(dSs);
+    const int m0 = (warp & 3) * 16, dh = ((warp >> 2) & 1) * 64;
     float ak[8][4], av[8][4];
 #pragma unroll
     for (int n = 0; n < 8; n++) ak[n][0] = ak[n][1] = ak[n][2] = ak[n][3] = av[n][0] = av[n][1] = av[n][2] = av[n][3] = 0.f;
     const int n_qt = (T + BQ - 1) / BQ;
-    const float qscale = kLog2e * rsqrtf((float)D);
     for (int it = jt; it < n_qt; it++) {
-        const int q0 = it * BQ;
-        __syncthreads();
-        load_tile<T16, 256>(q, ldq, h * D, q0, T, qscale, Qs, tid);
-        load_tile<T16, 256>(d_out, ldq, h * D, q0, T, 1.f, dOs, tid);
-        __syncthreads();
-        bwd_scores<T16>(qs, ks, vs, dos, Ps, dSs, lse2 + (int64_t)h * T, delta + (int64_t)h * T, q0, k0, T, warp, lane);
-        __syncthreads();
+        const int q0 = it * BQ, b = (it - jt) & 1;
+        if (!compute) {
+            if (it + 1 < n_qt) {
+                load_tile<T16, 128>(q, ldq, h * D, q0 + BQ, T, qscale, qbuf(b ^ 1), tid - 256);
+                load_tile<T16, 128>(d_out, ldq, h * D, q0 + BQ, T, 1.f, obuf(b ^ 1), tid - 256);
+            }
+        } else {
+            const uint32_t qs = smem_u32(qbuf(b)), dos = smem_u32(obuf(b));
+            bwd_scores<T16>(qs, ks, vs, dos, Ps, dSs, lse2 + (int64_t)h * T, delta + (int64_t)h * T, q0, k0, T, warp, lane);
+            compute_warps_sync();
 #pragma unroll
-        for (int kk = 0; kk < BQ / 16; kk++) {
-            uint32_t ap[4], as[4];
-            ldsm4t(a_km(ps, SP, m0, kk * 16, lane), ap);       // P^T: m = key, k = query
-            ldsm4t(a_km(dss, SP, m0, kk * 16, lane), as);      // dS^T
+            for (int kk = 0; kk < BQ / 16; kk++) {
+                uint32_t ap[4], as[4];
+                ldsm4t(a_km(ps, SP, m0, kk * 16, lane), ap);       // P^T: m = key, k = query
+                ldsm4t(a_km(dss, SP, m0, kk * 16, lane), as);      // dS^T
 #pragma unroll
-            for (int n = 0; n < 8; n += 2) {
-                uint32_t bo[4], bq[4];
-                ldsm4t(b_kn(dos, SD, dh + n * 8, kk * 16, lane), bo);
-                ldsm4t(b_kn(qs, SD, dh + n * 8, kk * 16, lane), bq);
-                mma16<T16>(av[n], ap, bo[0], bo[1]);
-                mma16<T16>(av[n + 1], ap, bo[2], bo[3]);
-                mma16<T16>(ak[n], as, bq[0], bq[1]);
-                mma16<T16>(ak[n + 1], as, bq[2], bq[3]);
+                for (int n = 0; n < 8; n += 2) {
+                    uint32_t bo[4], bq[4];
+                    ldsm4t(b_kn(dos, SD, dh + n * 8, kk * 16, lane), bo);
+                    ldsm4t(b_kn(qs, SD, dh + n * 8, kk * 16, lane), bq);
+                    mma16<T16>(av[n], ap, bo[0], bo[1]);
+                    mma16<T16>(av[n + 1], ap, bo[2], bo[3]);
+                    mma16<T16>(ak[n], as, bq[0], bq[1]);
+                    mma16<T16>(ak[n + 1], as, bq[2], bq[3]);
+                }
             }
         }
+        __syncthreads();
     }
-    // Qs held q * log2(e) / sqrt(D): dk = dS^T q needs the plain q
+    if (!compute) return;
+    // the query tiles held q * log2(e) / sqrt(D): dk = dS^T q needs the plain q
     const float unscale = 1.0f / qscale;
 #pragma unroll
     for (int r = 0; r < 2; r++) {
@@ -491,13 +525,13 @@ int attention_backward_on_device(gt_engine *e, const float *d_out, const float *
     GT_LAUNCH(e, cudaGetLastError());
     const dim3 gq((T + BQ - 1) / BQ, HQ), gk((T + BK - 1) / BK, HQ);
     if (e->math_mode == GT_MATH_BF16) {
-        k_attn_bwd_dq<__nv_bfloat16><<<gq, 256, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, dq, T, HQ, HK);
+        k_attn_bwd_dq<__nv_bfloat16><<<gq, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, dq, T, HQ, HK);
         GT_LAUNCH(e, cudaGetLastError());
-        k_attn_bwd_dkv<__nv_bfloat16><<<gk, 256, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, wk, wv, T, HQ, HK);
+        k_attn_bwd_dkv<__nv_bfloat16><<<gk, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, wk, wv, T, HQ, HK);
     } else {
-        k_attn_bwd_dq<__half><<<gq, 256, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, dq, T, HQ, HK);
+        k_attn_bwd_dq<__half><<<gq, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, dq, T, HQ, HK);
         GT_LAUNCH(e, cudaGetLastError());
-        k_attn_bwd_dkv<__half><<<gk, 256, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, wk, wv, T, HQ, HK);
+        k_attn_bwd_dkv<__half><<<gk, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, wk, wv, T, HQ, HK);
     }
     GT_LAUNCH(e, cudaGetLastError());
     const int64_t n4 = (int64_t)T * HK * D / 4;
