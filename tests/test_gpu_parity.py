@@ -531,3 +531,29 @@ def test_reserved_scratch_makes_steady_state_allocation_free(G):
     w.free()
     ad.free()
     e.close()
+
+
+def test_engines_on_two_devices_in_one_process(G, oracle):
+    """Kernel attributes (dynamic shared memory above 48 KB) are per device: an engine on a second GPU of the same
+    process must work after one on the first.  Each engine uses its own local memory only.  Needs two GPUs."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    c = S.make_projection_case(S.TYPE_Q4_K, 256, 512, 300, seed=97)
+    yr, dxr, dar, dbr = _reference(oracle, c, bias=False)
+    for dev in (0, 1):
+        e = G.Engine(dev, G.MATH_BF16)
+        w = e.upload_weight(c["qtype"], c["w"], 256, 512)
+        ad = e.create_adapter(512, 256, 16, 32.0)
+        ad.upload(c["a"], c["b"])
+        y = e.forward(w, ad, c["x"])
+        dx = np.zeros((300, 512), np.float32)
+        e.backward(w, ad, c["dy"], c["x"], dx)
+        da, db = ad.grads()
+        y8 = e.forward(w, None, np.ascontiguousarray(c["x"][:8]))      # the few-token streaming kernel too
+        assert oracle.rel_fro(y, yr) < 2e-2 and oracle.rel_fro(dx, dxr) < 2e-2, dev
+        assert oracle.rel_fro(da, dar) < 5e-3 and oracle.rel_fro(db, dbr) < 5e-3, dev
+        assert y8.shape == (8, 256)
+        w.free()
+        ad.free()
+        e.close()
