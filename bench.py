@@ -580,13 +580,21 @@ def step_projection_flops(n_layers: int, checkpoint: bool = True) -> float:
     return n_layers * per_layer_fwd * (3.0 if checkpoint else 2.0)
 
 
-def build_step_model(G, eng, dev, n_layers: int, rank: int, max_tokens: int):
+def build_step_model(G, eng, dev, n_layers: int, rank: int, max_tokens: int, checkpoint: bool = True, reuse=None):
     """The config-3 model on the device: seeded synthetic weights (one layer's K-quant bytes drawn on the host, the other
     layers' quant fields derived from them by a seeded XOR - scales and mins shared), A ~ N(0, 1/sqrt(in)), B = 0."""
     import torch
     c = STEP_CFG
     m = G.Model(eng, n_layers, c["hidden"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["ffn"], c["vocab"], max_tokens,
-                rms_eps=1e-6, rope_theta=1e6, checkpoint=True)
+                rms_eps=1e-6, rope_theta=1e6, checkpoint=checkpoint)
+    if reuse is not None:      # a second model over the same weight and adapter handles (e.g. without checkpointing)
+        keep, heads = reuse
+        ones = np.ones(c["hidden"], np.float32)
+        for l, (ws, ads) in enumerate(keep):
+            m.set_block(l, ws, ads, ones, ones)
+        m.set_head(heads[0], ones, heads[1])
+        _, n_grads = m.bind_grads()
+        return m, keep, heads, n_grads
     base = {}
     for n in PROJ_ORDER:
         N, K = synth.QWEN7B_PROJ[n]
@@ -681,6 +689,34 @@ def run_train_step(G, eng, dev, stream, world: int, rank: int, steps: int, warmu
     e2e_s = allreduce_max(time.perf_counter() - t0)
     ls = [float(v) for v in losses.cpu().numpy()[:total]]
     ms_step = ms / steps
+    # the same step WITHOUT activation checkpointing (not the workload's configuration; reported beside it): 180 GB of HBM
+    # hold every block's state (4.3 GB at 512 tokens), so the recomputed forward - a third of the projection work - goes
+    no_ckpt = None
+    try:
+        model.close()
+        model = None
+        m2, _, _, _ = build_step_model(G, eng, dev, n_layers, rank, T, checkpoint=False, reuse=(keep, heads))
+        for i in range(2):
+            m2.forward_backward(tok_d, lab_d, loss_dev=losses[total:total + 1])
+            m2.optimizer_step(step=100 + i, max_norm=1.0, **ADAMW)
+        eng.sync()
+        barrier()
+        n2 = max(3, steps // 2)
+        a2 = [torch.cuda.Event(enable_timing=True) for _ in range(n2)]
+        b2 = [torch.cuda.Event(enable_timing=True) for _ in range(n2)]
+        for i in range(n2):
+            a2[i].record(stream)
+            m2.forward_backward(tok_d, lab_d, loss_dev=losses[total:total + 1])
+            m2.optimizer_step(step=102 + i, max_norm=1.0, **ADAMW)
+            b2[i].record(stream)
+        barrier()
+        eng.sync()
+        ms2 = allreduce_max(sum(x.elapsed_time(y) for x, y in zip(a2, b2))) / n2
+        no_ckpt = {"ms_per_step": ms2, "tokens_per_s": world * T * 1e3 / ms2, "steps": n2,
+                   "note": "activation checkpointing off: every block's state kept in HBM, no recomputed forward"}
+        m2.close()
+    except Exception as exc:  # noqa: BLE001
+        no_ckpt = {"error": f"{type(exc).__name__}: {exc}"}
     out = {
         "workload": STEP_WORKLOAD if n_layers == 28 else STEP_WORKLOAD.replace("28 layers", f"{n_layers} layers"),
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
@@ -693,9 +729,11 @@ def run_train_step(G, eng, dev, stream, world: int, rank: int, steps: int, warmu
         "loss_first_steps": ls[:10], "loss_finite": bool(np.all(np.isfinite(ls))),
         "e2e": {"tokens_per_s": world * T * e2e_n / e2e_s, "ms_per_step": 1e3 * e2e_s / e2e_n, "steps": e2e_n,
                 "h2d_bytes_per_step": 2 * T * 4, "d2h_bytes_per_step": 12, "loss": host_losses[-1]},
+        "without_checkpointing": no_ckpt,
         "build_s": build_s,
     }
-    model.close()
+    if model is not None:
+        model.close()
     for ws, ads in keep:
         for h in ws + ads:
             h.free()

@@ -9,6 +9,8 @@
 //   AdamW    the optimizer step on the adapter matrices (AdamW of Glacier.Tensor 1.1.0, not in the repository; built
 //            and stepped in src/Glacier.Tune/Trainer/LoraTrainer.cs:56-62,230): textbook decoupled weight decay
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <cmath>
 #include <cstdio>
@@ -48,6 +50,36 @@ __global__ void __launch_bounds__(256) k_swiglu_fwd(const float *__restrict__ ga
     for (int64_t i = done + tid; i < n; i += nth) {
         const float g = gate[i];
         hidden[i] = g * sigmoidf_(g) * up[i];
+    }
+}
+
+// The same with a 16-bit copy written in the same pass (and the fp32 tensor only when it is wanted): the down
+// projection's tensor-core GEMM reads the 16-bit copy, so SiLU(gate) * up never has to be read back in fp32 to be cast
+// (GpuLoraEngine.ForwardFfn fuses the activation into its gate / up kernel, gemm_q4_k_swiglu_batch,
+// src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:152-183,282-285; here the gate and up tiles of a token live in different
+// CTAs of the GEMM, so the activation is folded into the pass that prepares the down projection's operand instead).
+__global__ void __launch_bounds__(256) k_swiglu_fwd16(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ hidden,
+                                                      uint16_t *__restrict__ h16, int64_t n4, int fp16) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n4; i += nth) {
+        const float4 g = __ldg(reinterpret_cast<const float4 *>(gate) + i), u = __ldg(reinterpret_cast<const float4 *>(up) + i);
+        float4 h;
+        h.x = g.x * sigmoidf_(g.x) * u.x;
+        h.y = g.y * sigmoidf_(g.y) * u.y;
+        h.z = g.z * sigmoidf_(g.z) * u.z;
+        h.w = g.w * sigmoidf_(g.w) * u.w;
+        if (hidden) reinterpret_cast<float4 *>(hidden)[i] = h;
+        uint2 pk;
+        if (fp16) {
+            __half2 a = __floats2half2_rn(h.x, h.y), b = __floats2half2_rn(h.z, h.w);
+            pk = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+        } else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(h.x, h.y), b = __floats2bfloat162_rn(h.z, h.w);
+            pk = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+        }
+        reinterpret_cast<uint2 *>(h16)[i] = pk;
     }
 }
 
@@ -333,6 +365,12 @@ cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden,
     if (n <= 0) return cudaSuccess;
     return launch_k(k_swiglu_fwd, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, gate, up, hidden, n,
                     aligned16(gate) && aligned16(up) && aligned16(hidden) ? 1 : 0);
+}
+cudaError_t launch_swiglu_fwd16(const float *gate, const float *up, float *hidden, void *h16, int64_t n, int fp16, int sm_count, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    if ((n & 3) != 0 || !aligned16(gate) || !aligned16(up) || (hidden && !aligned16(hidden)) || (reinterpret_cast<uintptr_t>(h16) & 7) != 0)
+        return cudaErrorInvalidValue;
+    return launch_k(k_swiglu_fwd16, dim3(stream_blocks(n, sm_count)), dim3(256), (size_t)0, s, gate, up, hidden, (uint16_t *)h16, n >> 2, fp16);
 }
 cudaError_t launch_swiglu_bwd(const float *d_hidden, const float *gate, const float *up, float *d_gate, float *d_up, int64_t n, int sm_count,
                               cudaStream_t s) {

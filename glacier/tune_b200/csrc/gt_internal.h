@@ -114,6 +114,8 @@ struct RowFill {
 };
 cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, void *x16, int ldx16, int fp16, int T, int K,
                                  const RowFill *fills, int n_fills, cudaStream_t s);
+// the same from an input that already exists as bf16 [T, ld16] (K % 8 == 0, 16-byte aligned): no copy is written
+cudaError_t launch_lora_xa16_group(const void *X16, int ld16, const LoraXaJob *jobs, int n, int T, int K, cudaStream_t s);
 cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, const RowFill *fills, int n_fills, cudaStream_t s);
 cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s);
 
@@ -174,6 +176,10 @@ cudaError_t launch_stream_fwd(const WeightDev *w, const float *X, float *Y_prefi
 
 // ---- layer glue launchers used inside the library (gt_glue.cu)
 cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden, int64_t n, int sm_count, cudaStream_t s);
+// hidden = SiLU(gate) * up written as fp32 (hidden, may be null) and as 16-bit (h16: bf16, or fp16 when fp16 != 0) in one
+// pass; n % 4 == 0 and 16-byte-aligned pointers
+cudaError_t launch_swiglu_fwd16(const float *gate, const float *up, float *hidden_or_null, void *h16, int64_t n, int fp16, int sm_count,
+                                cudaStream_t s);
 // one flat segment of an AdamW launch: parameters, gradients and both moments, n elements; flag (optional) is set to 1
 // when a parameter of the segment is non-zero after the step (vec is filled in by the launcher)
 struct AdamwSeg {

@@ -332,6 +332,115 @@ __global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// The same product from an input that already exists as bf16: low_j[T, R_j] += X16[T, K] * A_j.  Used where the pass
+// that produced X wrote its 16-bit copy itself (the SwiGLU kernel emits bf16(SiLU(gate) * up) for the down projection),
+// so this pass reads 2 bytes per element instead of 4 and writes no copy.  Same tiling as k_lora_xa_tc; the tile
+// travels global -> registers -> shared memory as 16-byte pieces (8 values), the next strip's pieces in flight during
+// the MMAs.  Needs K % 8 == 0 and a 16-byte-aligned X16.
+// ------------------------------------------------------------------------------------------------
+struct Xa16Params {
+    const uint16_t *X16;
+    int ld, T, K, n, strips_per_block;
+    XaChunk c[kMaxChunks];
+};
+constexpr int NI16 = (TT * TC / 8) / 256;      // 16-byte pieces per thread and tile
+__device__ __forceinline__ void tile_load16(const uint16_t *__restrict__ src, int ld, int K, int t0, int T, int c0, uint4 (&v)[NI16], int tid) {
+#pragma unroll
+    for (int i = 0; i < NI16; i++) {
+        const int idx = tid + i * 256;
+        const int r = idx / (TC / 8), c = (idx % (TC / 8)) * 8;
+        const int t = t0 + r;
+        v[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (t < T && c0 + c < K) v[i] = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)t * ld + c0 + c));
+    }
+}
+__device__ __forceinline__ void tile_store16(const uint4 (&v)[NI16], uint8_t *tile, int tid) {
+#pragma unroll
+    for (int i = 0; i < NI16; i++) {
+        const int idx = tid + i * 256;
+        const int r = idx / (TC / 8), c = (idx % (TC / 8)) * 8;
+        *reinterpret_cast<uint4 *>(tile + r * GSB + c * 2) = v[i];
+    }
+}
+__global__ void __launch_bounds__(256, 2) k_lora_xa16_tc(const Xa16Params p) {
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t *Xs = dyn_smem;
+    uint8_t *As = Xs + kXsBytes;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int T = p.T, K = p.K;
+    const int t0 = blockIdx.x * TT;
+    const int n_strips = (K + TC - 1) / TC;
+    const int s0 = blockIdx.y * p.strips_per_block, s1 = min(n_strips, s0 + p.strips_per_block);
+    pdl_wait();
+    pdl_trigger();
+    uint4 v[NI16];
+    float4 av[kMaxChunks][2];
+    auto a_load = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; j++) {
+            if (j < p.n) {
+                const XaChunk c = p.c[j];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int idx = tid + i * 256, row = k0 + (idx >> 2);
+                    av[j][i] = ld4(c.A + c.r0, row, c.R, (idx & 3) * 4, min(16, c.R - c.r0), row < K, c.vec != 0);
+                }
+            }
+        }
+    };
+    tile_load16(p.X16, p.ld, K, t0, T, s0 * TC, v, tid);
+    a_load(s0 * TC);
+    float d[kMaxChunks][2][4];
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) d[j][i][0] = d[j][i][1] = d[j][i][2] = d[j][i][3] = 0.f;
+    const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;
+    const uint32_t xs = smem_u32(Xs), as = smem_u32(As);
+    for (int s = s0; s < s1; s++) {
+        __syncthreads();
+        tile_store16(v, Xs, tid);
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; j++) {
+            if (j < p.n) {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int idx = tid + i * 256;
+                    st_bf16x4(As + j * kAsBytes + (idx >> 2) * RSB + (idx & 3) * 8, av[j][i]);
+                }
+            }
+        }
+        if (s + 1 < s1) {
+            tile_load16(p.X16, p.ld, K, t0, T, (s + 1) * TC, v, tid);
+            a_load((s + 1) * TC);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t a[4];
+            ldsm_x4(lm_a_mk(xs, GSB, m0, kh + ks * 16, lane), a);
+#pragma unroll
+            for (int j = 0; j < kMaxChunks; j++) {
+                if (j < p.n) {
+                    uint32_t b[4];
+                    ldsm_x4_t(lm_b_kn(as + j * kAsBytes, RSB, 0, kh + ks * 16, lane), b);
+                    mma_bf16(d[j][0], a, b[0], b[1]);
+                    mma_bf16(d[j][1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++) {
+        if (j >= p.n) break;
+        const XaChunk c = p.c[j];
+        const int rc = min(16, c.R - c.r0);
+#pragma unroll
+        for (int i = 0; i < 2; i++) frag_atomic_add(c.low + c.r0, c.R, d[j][i], t0 + m0 + g, T, i * 8 + 2 * t4, rc, 1.f);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // One pass over dY_m per member m = blockIdx.z.  A block owns one 64-token tile and a run of 128-column strips of
 // dY: it walks the strips with the next strip's dY tile and B tile in flight in registers.
 //   dLow[t, r] += sum_c dY[t, c] * B[r, c]      kept in registers across the strips, one atomic add per element and
@@ -637,6 +746,36 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
         p.n = 0;
         p.x16 = nullptr;
         p.fills.n = 0;
+        return le;
+    };
+    for (int j = 0; j < n; j++)
+        for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
+            p.c[p.n++] = XaChunk{jobs[j].A, jobs[j].low_zeroed, jobs[j].R, r0, is_vec(jobs[j].A, jobs[j].R)};
+            if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
+        }
+    return flush();
+}
+
+cudaError_t launch_lora_xa16_group(const void *X16, int ld16, const LoraXaJob *jobs, int n, int T, int K, cudaStream_t s) {
+    if (T <= 0 || K <= 0 || n <= 0) return cudaSuccess;
+    if ((K & 7) != 0 || (ld16 & 7) != 0 || (reinterpret_cast<uintptr_t>(X16) & 15) != 0) return cudaErrorInvalidValue;
+    static PerDeviceOnce configured;
+    cudaError_t e = per_device_once(configured, [] {
+        return cudaFuncSetAttribute(k_lora_xa16_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kXsBytes + kMaxChunks * kAsBytes));
+    });
+    if (e != cudaSuccess) return e;
+    const int strips = (K + TC - 1) / TC;
+    Xa16Params p{};
+    p.X16 = (const uint16_t *)X16;
+    p.ld = ld16;
+    p.T = T;
+    p.K = K;
+    p.strips_per_block = pick_strip_run(strips, 1, T);
+    dim3 grid((T + TT - 1) / TT, (strips + p.strips_per_block - 1) / p.strips_per_block);
+    auto flush = [&]() -> cudaError_t {
+        if (p.n == 0) return cudaSuccess;
+        cudaError_t le = launch_k(k_lora_xa16_tc, grid, dim3(256), (size_t)(kXsBytes + p.n * kAsBytes), s, p);
+        p.n = 0;
         return le;
     };
     for (int j = 0; j < n; j++)
