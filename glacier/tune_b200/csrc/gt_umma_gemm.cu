@@ -17,8 +17,8 @@
 //   warp 19       TMA producer of the 16-bit activation tiles
 //   warps 1, 18   tcgen05.mma issuers (one thread each, alternate stages, a turn token keeps the order fixed);
 //                 warp 1 owns the TMEM allocation
-//   warps 2-17    two groups of 8 warps that dequantize alternate operand stages (raw blocks -> 128-byte-swizzled
-//                 tiles); afterwards all 16 run the epilogue (tcgen05.ld -> bias -> global store / atomic add)
+//   warps 2-17    four groups of 4 warps that dequantize every fourth operand stage each (raw blocks -> 128-byte-
+//                 swizzled tiles); afterwards all 16 run the epilogue (tcgen05.ld -> bias -> global store / atomic add)
 //
 // One launch serves up to three member projections (forward: they share the activation tiles, each tile index belongs
 // to one member; backward: their contraction ranges are concatenated and all sum into one dX), each with its own
@@ -50,28 +50,29 @@ constexpr int kChunk = 64;         // contraction elements per operand stage (on
 constexpr int kMaxTok = 512;       // tokens per CTA = TMEM columns
 constexpr int kAStageBytes = kTileW * kChunk * 2;   // 16 KiB
 constexpr int kNumA = 4;            // operand stages (dequantized weight tile + activation tile)
-constexpr int kXStageBytes = 32768; // activation tile of a stage: a CTA holds at most 256 token rows of 128 bytes
-constexpr int kXBytes = kNumA * kXStageBytes;
-// Raw (still packed) weight blocks come from HBM, whose latency is several operand-stage times: the raw ring gets
-// all the shared memory that is left, cut into as many stages as the format's stage size allows (up to 8).
-constexpr int kRawBudget = 32768;
-constexpr int kMaxRaw = 8;
+// Shared memory of a CTA: [activation stages | dequantized weight stages | ring of packed weight blocks | barriers].
+// An activation stage holds XROWS token rows of 128 bytes (a kernel template parameter: 256 rows, or 128 in the
+// few-token variant).  Raw (still packed) weight blocks come from HBM, whose latency under load is several operand-stage
+// times (about 2.5 k clocks): the raw ring gets all the shared memory that is left, cut into as many stages as the
+// format's stage size allows (up to kMaxRaw) - 32 KB beside 256-row activation stages, 96 KB beside 128-row ones,
+// where nothing but the bytes in flight bounds the kernel.
+constexpr int kOffX = 0;
+constexpr int kOffBar = kNumA * 32768 + kNumA * kAStageBytes + 32768;
+constexpr int kMaxRaw = 16;
+constexpr int kBarBytes = 512;
 constexpr int kDequantWarps = 16;   // two groups of 8
 constexpr int kThreads = 32 * (4 + kDequantWarps);   // + weight producer (0), two MMA issuers (1, 18), activation producer (19)
 constexpr int kIssuer2Warp = 18, kActProducerWarp = 19;
-
-constexpr int kOffX = 0;
-constexpr int kOffA = kOffX + kXBytes;
-constexpr int kOffRaw = kOffA + kNumA * kAStageBytes;
-constexpr int kOffBar = kOffRaw + kRawBudget;
-constexpr int kSmemBytes = kOffBar + 256 + 1024;   // + slack for 1024-byte alignment
+constexpr int kSmemBytes = kOffBar + kBarBytes + 1024;   // + slack for 1024-byte alignment
 
 // barrier slots (8 bytes each) inside the kOffBar region
 // (an operand stage = dequantized weight tile + activation tile; both share one slot index and one full/empty pair)
-constexpr int kBarRawFull = 0, kBarRawEmpty = kMaxRaw, kBarFull = 2 * kMaxRaw, kBarEmpty = kBarFull + kNumA,
+constexpr int kMaxRawBars = 24;     // (slot, class) barriers of the raw ring, see kCls in the kernel
+constexpr int kBarRawFull = 0, kBarRawEmpty = kMaxRawBars, kBarFull = 2 * kMaxRawBars, kBarEmpty = kBarFull + kNumA,
               kBarAcc = kBarEmpty + kNumA, kBarTurn = kBarAcc + 1, kNumBars = kBarTurn + 2;
 constexpr int kOffTmemSlot = kNumBars * 8;       // u32
 constexpr int kOffAbort = kOffTmemSlot + 4;      // int
+static_assert(kOffAbort + 4 <= kBarBytes, "barrier region too small");
 
 // One launch serves up to kMaxMembers projections that share their input (forward: q,k,v or gate,up read the same X,
 // each writes its own Y) or their output (backward: dX += sum over members of dY_m * W_m).
@@ -122,10 +123,17 @@ struct Ring {
 //               the activation bytes each SM pulls from L2 per FLOP.  The even-ranked CTA (leader) issues the MMAs;
 //               its "full" barriers collect the arrivals and TMA bytes of both CTAs, and its commits release the
 //               stages in both.
-template <int QT, typename T16, bool BWD, bool PAIR, int MTOK>
+// XROWS = token rows of an activation stage (256, or 128 in the few-token variant: tokens <= 128, single CTA, the
+//         shared memory saved goes to the ring of packed weight blocks).
+template <int QT, typename T16, bool BWD, bool PAIR, int MTOK, int XROWS>
 __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant__ Params p) {
     using QS = QuantStage<QT>;
     constexpr int H = QS::kHdrBytes, Q1 = QS::kQ1Bytes;
+    static_assert(XROWS == 256 || XROWS == 128, "activation stage: 256 or 128 token rows per CTA");
+    constexpr int kXStageBytes = XROWS * 128;
+    constexpr int kOffA = kOffX + kNumA * kXStageBytes;
+    constexpr int kOffRaw = kOffA + kNumA * kAStageBytes;
+    constexpr int kRawBudget = kOffBar - kOffRaw;
     // fp16 weights: no packed-block ring and no dequantization - the weight producer's TMA copies land in the operand
     // stage itself (128-byte swizzle = the tile image the dequantizer would have written)
     constexpr bool kDirect = QT == kTypeF16;
@@ -133,7 +141,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     constexpr int kSub = BWD ? 1 : 2;          // operand stages produced per raw stage
     constexpr int kNumX = kNumA;
     constexpr int kRawStageBytes = (kRows * (H + 64 + Q1) + 1023) & ~1023;
-    constexpr int kNumRaw = kRawBudget / kRawStageBytes < kMaxRaw ? kRawBudget / kRawStageBytes : kMaxRaw;
+    // Ring of packed blocks.  An mbarrier wait names a phase by its parity, so whoever waits on a barrier must visit
+    // EVERY phase of it, one after the other (a waiter two phases behind would take the phase before last for the one
+    // it wants).  The dequant groups walk the raw stages with stride kStride (forward: two groups share a raw stage, the
+    // pairs alternate; backward: the four groups take every fourth stage).  Where kStride does not divide the number
+    // of slots, a slot gets one full / empty barrier pair per residue class r % kStride of the stages it holds: a
+    // barrier (slot, class) then sees the stages r0, r0 + kLcm, r0 + 2 kLcm, ... and always the same waiters.  The
+    // producer teams (stride kTeams, a divisor of kStride) wait for the stage that held the slot before.
+    constexpr int kStride = BWD ? 4 : 2;
+    constexpr int kFit = kRawBudget / kRawStageBytes;
+    constexpr int kNumRaw = kFit < kMaxRaw ? (kFit < 1 ? 1 : kFit) : kMaxRaw;
+    constexpr int kCls = kNumRaw % kStride == 0 ? 1 : kStride;
+    constexpr int kLcm = kNumRaw % kStride == 0 ? kNumRaw : (kNumRaw % 2 == 0 ? 2 * kNumRaw : kStride * kNumRaw);
+    constexpr int kTeams = kStride;      // weight-producer teams (three lanes each)
+    static_assert(kDirect || kNumRaw * kCls <= kMaxRawBars, "not enough barrier slots for the raw ring");
+    static_assert(kLcm % kNumRaw == 0 && kLcm % kStride == 0, "kLcm is a common multiple");
     // MTOK = token columns per MMA (the accumulator is cut into 512 / MTOK independent tiles that the issuer visits
     // round-robin); kMmaSlotBytes = smem bytes of one MMA's activation rows in a stage
     constexpr int kMmaSlotBytes = (PAIR ? MTOK / 2 : MTOK) * 128;
@@ -144,6 +166,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + kOffBar;
     auto bar = [&](int slot) -> uint32_t { return bar0 + 8u * (uint32_t)slot; };
+    // raw stage r (counted from this CTA's first one): its barrier index inside the full / empty arrays, and its phase
+    auto raw_bar = [&](int r) -> int { return (r % kNumRaw) * kCls + (kCls > 1 ? r % kStride : 0); };
+    auto raw_phase = [&](int r) -> uint32_t { return (uint32_t)(r / kLcm) & 1u; };
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + kOffBar + kOffAbort);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kOffBar + kOffTmemSlot);
 
@@ -182,14 +207,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     };
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kNumRaw; i++) {
+        for (int i = 0; i < kNumRaw * kCls; i++) {
             mbar_init(bar(kBarRawFull + i), 1);
-            mbar_init(bar(kBarRawEmpty + i), BWD ? 8 : 16);      // one arrival per warp that read the stage
+            mbar_init(bar(kBarRawEmpty + i), BWD ? 4 : 8);       // one arrival per warp that read the stage
         }
         for (int i = 0; i < kNumA; i++) {
             // full: the (leader's) producer arrival carrying the TMA bytes + one arrival per dequant warp (of both CTAs)
-            // (every dequant warp counts twice in a normal stage, where one group of 8 produces; once in the rank-update
-            // stage, where both groups produce)
+            // (a dequant warp counts four times in a normal stage, where one group of 4 warps produces; once in the
+            // rank-update stage, where all 16 produce)
             // (fp16 weights: the activation producer and the weight producer, one arrival each)
             mbar_init(bar(kBarFull + i), kDirect ? 2 : 1 + (PAIR ? 32 : 16));
             mbar_init(bar(kBarEmpty + i), 1);                    // tcgen05.commit of the stage's MMAs
@@ -297,14 +322,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     }
                 }
             }
-        } else if (lane < 3) {      // lane 0 arms the barrier and copies the headers, lanes 1 and 2 copy the quant regions
-            Ring raw;
+        } else if (lane < 3 * kTeams) {
+            // Teams of three lanes (lane 0 of a team arms the barrier and copies the headers, lanes 1 and 2 copy the
+            // quant regions); team t issues the raw stages r = t (mod kTeams).  Issuing a tiled copy holds the issuing
+            // thread for several hundred clocks: with one team the issue rate alone (one raw stage per ~800 clocks) paced
+            // the few-token shapes.  kTeams <= kNumRaw, so a team never waits for a slot whose previous stage is issued
+            // in the same round.
+            const int team = lane / 3, li = lane - 3 * team;
             bool ok = true;
-            for (int u = u0; u < u1 && ok; u++) {
-                ok = mbar_wait_bounded(bar(kBarRawEmpty + raw.idx), raw.phase ^ 1u, abort_flag, p.status, kCodeProducer + 1);
+            for (int u = u0 + team; u < u1 && ok; u += kTeams) {
+                const int r = u - u0, ri = r % kNumRaw;
+                // the slot's previous stage has been read
+                if (r >= kNumRaw)
+                    ok = mbar_wait_bounded(bar(kBarRawEmpty + raw_bar(r - kNumRaw)), raw_phase(r - kNumRaw), abort_flag, p.status, kCodeProducer + 1);
                 if (!ok) break;
-                const uint32_t rdst = sbase + kOffRaw + raw.idx * kRawStageBytes;
-                const uint32_t rbar = bar(kBarRawFull + raw.idx);
+                const uint32_t rdst = sbase + kOffRaw + ri * kRawStageBytes;
+                const uint32_t rbar = bar(kBarRawFull + raw_bar(r));
                 int sb, half, row0, um = mi, rb = 0;
                 if (BWD) {
                     um = unit_member(u, rb);
@@ -317,16 +350,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const int xb = sb * QS::kBlockBytes;
                 // one copy per region: the tensor maps handed to a forward launch have 128-row boxes, the backward
                 // ones 64-row boxes
-                if (lane == 0) {
+                if (li == 0) {
                     mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
                     tma_load_2d(rdst, &W.tm_hdr, xb + QS::hdr_x(half), row0, rbar);
-                    trace(0, u - u0);
-                } else if (lane == 1) {
+                    if (lane == 0) trace(0, r / kTeams);
+                } else if (li == 1) {
                     tma_load_2d(rdst + kRows * H, &W.tm_q0, xb + QS::q0_x(half), row0, rbar);
                 } else if (Q1 > 0) {
                     tma_load_2d(rdst + kRows * (H + 64), &W.tm_q1, xb + QS::q1_x(half), row0, rbar);
                 }
-                raw.advance(kNumRaw);
             }
         }
     } else if (warp == kActProducerWarp) {
@@ -434,8 +466,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         }
     } else {
         // ------------------------------------------------------------------ dequant warps, then epilogue
-        const int dt = (threadIdx.x - 64) & 255;        // thread index inside its 8-warp group
-        const int g = (warp - 2) >> 3;                  // group 0 / 1: alternate operand stages
+        // Four groups of four warps; group g4 produces the operand stages n = g4 (mod 4), always into A slot g4, so
+        // four stages are being dequantized at any time (one stage is a chain of waits, shared-memory round trips and
+        // a proxy fence, about a thousand clocks whatever the number of threads working on it: the groups hide each
+        // other's latency).  A thread produces 64 weights of a stage as two independent 32-weight runs.
+        const int dt = (threadIdx.x - 64) & 127;        // thread index inside its 4-warp group
+        const int g4 = (warp - 2) >> 2;                 // group 0..3
         const int nu = u1 - u0;
         bool ok = true;
         // "operand stage ready": on the barrier of the CTA that issues the MMAs
@@ -445,51 +481,66 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 else mbar_arrive_n(bar(kBarFull + ai), count);
             }
         };
-        // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i % kNumRaw
-        auto produce = [&](int n, const uint8_t *rs, int row, int grp, int half, uint32_t dst_off, int chunk0) -> bool {
+        // operand stage n lives in A slot n % kNumA with phase (n / kNumA) & 1; raw stage i in slot i % kNumRaw.
+        // Runs r = 0, 1 of this thread: 32-weight group grp[r] of the row, written at dst_off[r] + chunk0[r].
+        auto produce = [&](int n, const uint8_t *rs, int row, int half, const int (&grp)[2], const uint32_t (&dst_off)[2],
+                           const int (&chunk0)[2]) -> bool {
             const int ai = n % kNumA;
             if (!mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 2))
                 return false;
-            if (dt == 0) trace(3 + 3 * g, n >> (BWD ? 0 : 0));
+            if (dt == 0 && g4 < 2) trace(3 + 3 * g4, n);
             const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
-            dequant32_to_swizzled_row<QT, T16>(rs + row * H, rs + kRows * H + row * 64,
-                                               rs + kRows * (H + 64) + row * (Q1 > 0 ? Q1 : 1), (row >> 1) & 3, (row >> 2) & 1,
-                                               half, grp, a_addr + dst_off, row & 7, chunk0);
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+                dequant32_to_swizzled_row<QT, T16>(rs + row * H, rs + kRows * H + row * 64,
+                                                   rs + kRows * (H + 64) + row * (Q1 > 0 ? Q1 : 1), (row >> 1) & 3, (row >> 2) & 1,
+                                                   half, grp[r], a_addr + dst_off[r], row & 7, chunk0[r]);
             fence_proxy_async_smem();
             __syncwarp();
-            signal_a_full(ai, 2);
-            if (dt == 0) trace(4 + 3 * g, n);
+            signal_a_full(ai, 4);
+            if (dt == 0 && g4 < 2) trace(4 + 3 * g4, n);
             return true;
         };
         if (kDirect) {
             // nothing to dequantize
         } else if (!BWD) {
-            // raw stage = 128 rows x half block; group g dequantizes its 64-column half (sub-stage g)
-            const int row = dt & 127, hn = dt >> 7;
-            for (int ui = 0; ui < nu && ok; ui++) {
+            // raw stage = 128 rows x half block = two operand stages (its 64-column halves); groups 0, 1 take the even
+            // raw stages, groups 2, 3 the odd ones; a thread owns one row of its group's half
+            const int row = dt, sub = g4 & 1;
+            const int grp[2] = {2 * sub, 2 * sub + 1};
+            const uint32_t dst_off[2] = {(uint32_t)(row * 128), (uint32_t)(row * 128)};
+            const int chunk0[2] = {0, 4};
+            for (int ui = g4 >> 1; ui < nu && ok; ui += 2) {
                 const int ri = ui % kNumRaw;
-                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui / kNumRaw) & 1u, abort_flag, p.status, kCodeDequant + 1);
+                ok = mbar_wait_bounded(bar(kBarRawFull + raw_bar(ui)), raw_phase(ui), abort_flag, p.status, kCodeDequant + 1);
                 if (!ok) break;
-                if (dt == 0) trace(2 + 3 * g, 2 * ui + g);
+                if (dt == 0 && g4 < 2) trace(2 + 3 * g4, 2 * ui + sub);
                 const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
-                ok = produce(2 * ui + g, rs, row, 2 * g + hn, (u0 + ui) & 1, (uint32_t)(row * 128), 4 * hn);
+                ok = produce(2 * ui + sub, rs, row, (u0 + ui) & 1, grp, dst_off, chunk0);
                 if (!ok) break;
-                if (lane == 0) mbar_arrive(bar(kBarRawEmpty + ri));
+                if (lane == 0) mbar_arrive(bar(kBarRawEmpty + raw_bar(ui)));
             }
         } else {
-            // raw stage = 64 rows x half block = one operand stage; the groups take alternate stages
-            const int row = dt & 63, grp = dt >> 6;
-            for (int ui = g; ui < nu && ok; ui += 2) {
+            // raw stage = 64 rows x half block = one operand stage (two 64-column images); group g4 takes the stages
+            // ui = g4 (mod 4); a thread owns one row of one image
+            const int row = dt & 63, im = dt >> 6;
+            const int grp[2] = {2 * im, 2 * im + 1};
+            const uint32_t dst_off[2] = {(uint32_t)(im * 8192 + row * 128), (uint32_t)(im * 8192 + row * 128)};
+            const int chunk0[2] = {0, 4};
+            for (int ui = g4; ui < nu && ok; ui += 4) {
                 const int ri = ui % kNumRaw;
-                ok = mbar_wait_bounded(bar(kBarRawFull + ri), (uint32_t)(ui / kNumRaw) & 1u, abort_flag, p.status, kCodeDequant + 1);
+                ok = mbar_wait_bounded(bar(kBarRawFull + raw_bar(ui)), raw_phase(ui), abort_flag, p.status, kCodeDequant + 1);
                 if (!ok) break;
-                if (dt == 0) trace(2 + 3 * g, ui);
+                if (dt == 0 && g4 < 2) trace(2 + 3 * g4, ui);
                 const uint8_t *rs = smem + kOffRaw + ri * kRawStageBytes;
-                ok = produce(ui, rs, row, grp, tile & 1, (uint32_t)((grp >> 1) * 8192 + row * 128), 4 * (grp & 1));
+                ok = produce(ui, rs, row, tile & 1, grp, dst_off, chunk0);
                 if (!ok) break;
-                if (lane == 0) mbar_arrive(bar(kBarRawEmpty + ri));
+                if (lane == 0) mbar_arrive(bar(kBarRawEmpty + raw_bar(ui)));
             }
         }
+        // the rank-update stages are built by two halves of 8 warps (256 threads) each
+        const int g = g4 >> 1;
+        const int dt2 = (g4 & 1) * 128 + dt;
         for (int lj = 0; lj < n_lora && ok; lj++) {
             // rank-update stage: group 0 builds the weight-side tile from B (forward) / A (backward), group 1 the
             // activation-side tile from the fp32 low-rank activations, both rounded to T16 here
@@ -506,9 +557,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     for (int i = 0; i < n_mma; i++) {
                         const int ntok = min(MTOK, tb - MTOK * i);
                         const int rows = PAIR ? (ntok >> 1) : ntok;
-                        if (dt < rows) {
-                            const int t = tok0 + MTOK * i + (PAIR ? (int)crank * rows : 0) + dt;
-                            const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + dt * 128);
+                        if (dt2 < rows) {
+                            const int t = tok0 + MTOK * i + (PAIR ? (int)crank * rows : 0) + dt2;
+                            const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + dt2 * 128);
                             for (int j = 0; j * 8 < rank_pad; j++) {
                                 float v[8];
 #pragma unroll
@@ -516,15 +567,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                                     const int r = 8 * j + q;
                                     v[q] = (r < L.rank && t < p.T) ? L.lora_act[(int64_t)t * L.rank + r] * L.lora_scale : 0.f;
                                 }
-                                st_shared_v4(row_addr + (uint32_t)((j ^ (dt & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
+                                st_shared_v4(row_addr + (uint32_t)((j ^ (dt2 & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
                                              pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
                             }
                         }
                     }
                 } else if (!BWD) {
                     // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
-                    const int row = dt & 127, nn = ltile * kTileW + row;
-                    for (int j = dt >> 7; j * 8 < rank_pad; j += 2) {
+                    const int row = dt2 & 127, nn = ltile * kTileW + row;
+                    for (int j = dt2 >> 7; j * 8 < rank_pad; j += 2) {
                         float v[8];
 #pragma unroll
                         for (int i = 0; i < 8; i++) {
@@ -536,8 +587,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     }
                 } else {
                     // image(kcol >> 6)[row = r][col = kcol & 63] = A[k, r]
-                    const int kcol = dt & 127, c = kcol & 63, k = tile * kTileW + kcol;
-                    for (int r = dt >> 7; r < rank_pad; r += 2) {
+                    const int kcol = dt2 & 127, c = kcol & 63, k = tile * kTileW + kcol;
+                    for (int r = dt2 >> 7; r < rank_pad; r += 2) {
                         const float v = (r < L.rank && k < p.K) ? L.lora_w[(int64_t)k * L.rank + r] : 0.f;
                         const uint32_t addr =
                             a_addr + (uint32_t)((kcol >> 6) * 8192 + r * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
@@ -659,10 +710,10 @@ bool encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, int esize, const void *b
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int QT, typename T16, bool BWD, bool PAIR, int MTOK>
+template <int QT, typename T16, bool BWD, bool PAIR, int MTOK, int XROWS>
 cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
     static PerDeviceOnce configured;      // one per kernel instantiation
-    auto kern = k_umma_gemm<QT, T16, BWD, PAIR, MTOK>;
+    auto kern = k_umma_gemm<QT, T16, BWD, PAIR, MTOK, XROWS>;
     cudaError_t ce = per_device_once(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes); });
     if (ce != cudaSuccess) return ce;
     cudaLaunchConfig_t cfg = {};
@@ -691,11 +742,15 @@ cudaError_t launch_variant(const Params &p, dim3 grid, cudaStream_t s) {
 
 template <int QT, typename T16, bool BWD>
 cudaError_t launch_one(const Params &p, dim3 grid, bool pair, cudaStream_t s) {
+    // few tokens: the deep ring of packed blocks (fp16 rows have no packed ring)
+    static const bool deep = !(getenv("GT_DEEP_RING") && atoi(getenv("GT_DEEP_RING")) == 0);
     if (pair) {
-        if (p.t_box == 64) return launch_variant<QT, T16, BWD, true, 128>(p, grid, s);
-        return launch_variant<QT, T16, BWD, true, 256>(p, grid, s);
+        if (p.t_box == 64) return launch_variant<QT, T16, BWD, true, 128, 256>(p, grid, s);
+        if (QT != kTypeF16 && deep && p.T <= 256) return launch_variant<QT, T16, BWD, true, 256, 128>(p, grid, s);
+        return launch_variant<QT, T16, BWD, true, 256, 256>(p, grid, s);
     }
-    return launch_variant<QT, T16, BWD, false, 256>(p, grid, s);
+    if (QT != kTypeF16 && deep && p.T <= 128) return launch_variant<QT, T16, BWD, false, 256, 128>(p, grid, s);
+    return launch_variant<QT, T16, BWD, false, 256, 256>(p, grid, s);
 }
 
 }  // namespace
@@ -790,10 +845,20 @@ bool umma_group_ok(const UmmaLaunch *m, int n) {
     return true;
 }
 
+// CTA pairs pay off once the activation tile is the bulk of what an SM pulls from L2, and they halve the MMA
+// instructions per weight; pair mode needs 16 token columns per CTA half (the knob is clamped to [32, 256])
+static int pair_min_tokens() {
+    static const int pair_min = [] {
+        const int v = getenv("GT_PAIR_MIN") ? atoi(getenv("GT_PAIR_MIN")) : 256;
+        return v < 32 ? 32 : (v > 256 ? 256 : v);
+    }();
+    return pair_min;
+}
+
 int umma_group_splits(const UmmaLaunch *m, int n, int sm_count) {
     const bool bwd = m[0].backward != 0;
     const int tmax = m[0].T < kMaxTok ? m[0].T : kMaxTok;
-    const bool pair = tmax >= 256;
+    const bool pair = tmax >= pair_min_tokens();
     int tiles = 0, units = 0;
     for (int j = 0; j < n; j++) {
         const WeightDev *w = m[j].w;
@@ -825,14 +890,7 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     Params p;
     memset(&p, 0, sizeof(p));
     const int tmax = L0.T < kMaxTok ? L0.T : kMaxTok;
-    // CTA pairs pay off once the activation tile is the bulk of what an SM pulls from L2; small token counts are
-    // weight-streaming bound and stay on single CTAs
-    // (a single CTA stages at most 256 token rows per operand stage, so the knob is clamped to [32, 256])
-    static const int pair_min = [] {
-        const int v = getenv("GT_PAIR_MIN") ? atoi(getenv("GT_PAIR_MIN")) : 256;
-        return v < 32 ? 32 : (v > 256 ? 256 : v);
-    }();
-    const bool pair = tmax >= pair_min;
+    const bool pair = tmax >= pair_min_tokens();
     const int tb = pair ? (tmax + 31) & ~31 : (tmax + 15) & ~15;
     // pair mode: TMA box rows = half of an MMA's token columns (64 with four 128-column accumulators)
     static const int mtok = getenv("GT_MMA_TOK") ? atoi(getenv("GT_MMA_TOK")) : 256;

@@ -465,8 +465,9 @@ def test_run_twice_reproducibility(G, eng, oracle):
     """Same inputs twice.  Outputs that one CTA writes with plain stores are bit-identical run to run: the base forward
     without split-K (enough row tiles to fill the GPU) and the base dX under GT_FLAG_DX_ASSIGN without split-K.
     Whatever several CTAs sum with fp32 atomics - split-K partial tiles, X*A and dY*B^T (and through them the adapter
-    terms of Y and dX), dA, dB - may differ in the last bits from the order of the additions: held to 1e-5 relative
-    here, far inside the parity gates."""
+    terms of Y and dX), dA, dB - may differ in the last bits from the order of the additions: Y and dX are held to 1e-5
+    relative here.  dA and dB are products of low / dLow ROUNDED TO bf16: a last-bit difference of an fp32 sum can move
+    its bf16 rounding by a whole bf16 step (2^-9), so they are held to 2e-4, still a hundred times inside the gates."""
     import torch
     eng.set_math_mode(0)
     N, K, T = 148 * 128, 512, 256          # 148 row tiles: one wave, no split-K in the forward
@@ -488,8 +489,10 @@ def test_run_twice_reproducibility(G, eng, oracle):
         da, db = ad.grads()
         outs.append((Y0.cpu().numpy(), Y.cpu().numpy(), dX.cpu().numpy(), da, db))
     assert np.array_equal(outs[0][0], outs[1][0])            # base forward, plain stores: bit-identical
-    for i in (1, 2, 3, 4):
+    for i in (1, 2):
         assert oracle.rel_fro(outs[0][i], outs[1][i]) < 1e-5
+    for i in (3, 4):
+        assert oracle.rel_fro(outs[0][i], outs[1][i]) < 2e-4
     w.free()
     ad.free()
     # dX with one CTA per output tile (K / 128 = 148 column tiles, no split): plain stores, bit-identical
