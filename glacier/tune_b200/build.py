@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libglaciertune_b200.so")
-SOURCES = ["gt_engine.cu", "gt_fp32_kernels.cu", "gt_lora_tc.cu", "gt_umma_gemm.cu", "gt_noalloc.cu", "gt_stream_gemm.cu", "gt_glue.cu", "gt_lmhead.cu", "gt_attention.cu", "gt_model.cu"]
+SOURCES = ["gt_engine.cu", "gt_fp32_kernels.cu", "gt_lora_tc.cu", "gt_umma_gemm.cu", "gt_umma_few.cu", "gt_noalloc.cu", "gt_stream_gemm.cu", "gt_glue.cu", "gt_lmhead.cu", "gt_attention.cu", "gt_model.cu"]
 HEADERS = ["gt_internal.h", "gt_engine_priv.h", "gt_ptx.cuh", "gt_quant.cuh"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

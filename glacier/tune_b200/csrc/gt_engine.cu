@@ -522,7 +522,7 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
         run_m[pos].out_assign = (r == 0 && store_first) ? 1 : 0;
         // launches of the other quantization types add into the same dX with atomics: beside the first one on the side
         // stream (behind the dA pass there), unless the first one writes dX with plain stores
-        const bool side = r > 0 && !store_first && e->s_aux && !e->profile && side_da_enabled();
+        const bool side = r > 0 && !store_first && e->s_aux && !e->profile && side_da_enabled() && !umma_group_few(run_m + pos, count[r]);
         if (side && !e->aux_pending) {      // no dA pass was forked: fork now (the pass over dY is complete by stream order)
             GT_CUDA(cudaEventRecord(e->ev_aux_fork, e->stream));
             GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));

@@ -40,6 +40,7 @@ struct WeightDev {
     CUtensorMap tm_hdr, tm_q0, tm_q1;   // 2-D byte maps over [N, row_bytes], boxes of 64 rows (backward raw stages)
     CUtensorMap tm_hdr_f, tm_q0_f, tm_q1_f;   // the same with boxes of 128 rows (forward raw stages: half as many copies)
     CUtensorMap tm_rows;                // Q4_K: 32-bit words over [N, row_bytes / 4], boxes of 16 rows x 288 bytes (two blocks)
+    CUtensorMap tm_blk_f, tm_blk_b;     // whole super-blocks: boxes of one block x 256 rows / x 64 rows (few-token kernel)
 };
 
 // ---- CUDA-core kernels (gt_fp32_kernels.cu) -------------------------------------------------------------
@@ -149,6 +150,15 @@ struct UmmaLaunch {
 int umma_pick_splits(const WeightDev *w, int backward, int T, int sm_count);
 // Returns cudaSuccess or an error; `err` receives a description on failure of a non-CUDA kind.
 cudaError_t launch_umma_gemm(const UmmaLaunch &L, cudaStream_t s, const char **err);
+// The few-token kernel (gt_umma_few.cu): up to 128 tokens, one member per launch, no fused adapter term.
+bool umma_few_ok(const UmmaLaunch &L);
+// launch_umma_group will serve these members with the few-token kernel; their adapter terms then follow on kernels that
+// update the output with plain read-modify-writes, so such a launch must not run beside another one into the same output
+bool umma_group_few(const UmmaLaunch *m, int n);
+void umma_few_shape(const UmmaLaunch &L, int *tiles, int *units);
+cudaError_t launch_umma_few(const UmmaLaunch &L, cudaStream_t s, const char **err);
+bool tmap_encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, const void *base, uint64_t d0, uint64_t d1, uint64_t stride1_bytes,
+                    uint32_t b0, uint32_t b1, CUtensorMapSwizzle swz);
 // Up to three projections in one launch (see gt_umma_gemm.cu); umma_group_ok tells whether they qualify.
 bool umma_group_ok(const UmmaLaunch *m, int n);
 int umma_group_splits(const UmmaLaunch *m, int n, int sm_count);

@@ -148,8 +148,11 @@ __device__ __forceinline__ float byte_to_magic(uint32_t v, int i) {
     return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540u + (uint32_t)i));
 }
 
+// (no "memory" clobber: the compiler may keep packed-block loads and header arithmetic in registers across these
+// stores, e.g. between the two 32-weight runs a thread decodes from one row; volatile keeps them in program order
+// ahead of the proxy fence, which does clobber memory)
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d));
 }
 
 __device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t c) {

@@ -308,7 +308,7 @@ cudaError_t launch_nt(const StreamParams &p, dim3 grid, size_t smem, cudaStream_
 int stream_max_tokens() {
     static const int v = [] {
         const char *e = getenv("GT_STREAM_MAX_T");
-        const int n = e ? atoi(e) : 16;
+        const int n = e ? atoi(e) : 8;      // from 9 tokens on the tensor-core few-token kernel is faster
         return n < 0 ? 0 : (n > 32 ? 32 : n);
     }();
     return v;

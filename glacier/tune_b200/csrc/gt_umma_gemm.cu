@@ -100,6 +100,7 @@ struct Params {
     int splits, units;
     int atomic_out;  // 1: red.add into out, 0: plain store (forward: + bias)
     int tmem_cols;
+    int par_ok;      // 0: keep the two MMA issuers on the turn token at every token count (GT_MMA_PAR=0)
 };
 
 // status codes written on a bounded-wait timeout: 100*role + barrier kind
@@ -185,9 +186,16 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     // Few tokens (single-CTA mode): the four k-steps of a stage go to separate accumulators, so they do not wait on
     // each other's accumulation (a dependent MMA costs ~250 clocks whatever its size); the epilogue adds them up.
     const int acc_stride = (tb + 31) & ~31;
-    const int n_acc = PAIR ? 1 : (acc_stride <= 128 ? 4 : (acc_stride <= 256 ? 2 : 1));
+    const int n_acc = n_mma > 1 ? 1 : (acc_stride <= 128 ? 4 : (acc_stride <= 256 ? 2 : 1));
     const int u0 = (int)((int64_t)p.units * split / p.splits);
     const int u1 = (int)((int64_t)p.units * (split + 1) / p.splits);
+    // Up to 128 tokens (single-CTA mode) the kernel is bound by how fast MMAs can be ISSUED (an MMA of 16..128 token
+    // columns costs its issuing thread about as much as a full-width one): the two issuers then work side by side, each
+    // on its own set of partial accumulators (no turn token; every accumulator still receives its MMAs from one thread
+    // in a fixed order, so results do not change from run to run).  Needs a main stage for either issuer.
+    const bool par = !PAIR && p.par_ok != 0 && acc_stride <= 128 && (u1 - u0) * (BWD ? 1 : 2) >= 2;
+    const int n_acc_per = par ? (acc_stride <= 64 ? 4 : 2) : n_acc;      // partial accumulators per issuer
+    const int n_acc_sum = par ? 2 * n_acc_per : n_acc;                   // ... that the epilogue adds up
     // forward: the member that owns this tile; backward: every CTA works on all members, unit by unit
     int mi = 0;
     if (!BWD)
@@ -213,8 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         }
         for (int i = 0; i < kNumA; i++) {
             // full: the (leader's) producer arrival carrying the TMA bytes + one arrival per dequant warp (of both CTAs)
-            // (a dequant warp counts four times in a normal stage, where one group of 4 warps produces; once in the
-            // rank-update stage, where all 16 produce)
+            // (a dequant warp counts four times: one group of 4 warps produces a stage, rank-update stages included)
             // (fp16 weights: the activation producer and the weight producer, one arrival each)
             mbar_init(bar(kBarFull + i), kDirect ? 2 : 1 + (PAIR ? 32 : 16));
             mbar_init(bar(kBarEmpty + i), 1);                    // tcgen05.commit of the stage's MMAs
@@ -427,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const uint32_t a_lo0 = (((sbase + kOffA + si * kAStageBytes) & 0x3FFFFu) >> 4) | kALoField;
                 const uint32_t b_lo0 = (((sbase + kOffX + si * kXStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
                 const int ksteps = n < n_main ? 4 : ((p.m[lora_m[n - n_main]].rank + 15) >> 4);
-                if (n > 0) {
+                if (n > 0 && !par) {
                     // take the turn: the other issuer has queued stage n - 1 (by now this thread has already waited for
                     // its own operands, which is the latency the second issuer hides)
                     const uint32_t turn_phase = (uint32_t)(who == 1 ? (n >> 1) : ((n >> 1) - 1)) & 1u;
@@ -435,29 +442,34 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     if (!ok) break;
                 }
                 if (who == 0) trace(8, n);
-                const uint32_t first = n == 0 ? 0u : 1u;     // the very first MMA into an accumulator overwrites it
+                const uint32_t first = n == (par ? who : 0) ? 0u : 1u;     // the very first MMA into an accumulator overwrites it
                 // k-step-major order: consecutive MMAs alternate between the accumulators (measured faster than
                 // finishing one accumulator's k-steps first)
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++) {
                     if (ks < ksteps) {
                         const uint32_t a_lo = a_lo0 + ks * kAStep;
-                        if (PAIR) {
+                        if (PAIR && n_mma > 1) {
 #pragma unroll
                             for (int i = 0; i < kMaxMma; i++)
                                 if (i < n_mma)
                                     umma_f16_ss_lohi<true>(tmem_base + i * MTOK, a_lo, kDescHi, b_lo0 + i * (kMmaSlotBytes >> 4) + ks * 2,
                                                            kDescHi, idesc[i], ks == 0 ? first : 1u);
+                        } else if (PAIR) {
+                            // one MMA per k-step (tokens <= MTOK): each k-step into its own partial accumulator
+                            const int a = ks % n_acc;
+                            umma_f16_ss_lohi<true>(tmem_base + a * acc_stride, a_lo, kDescHi, b_lo0 + ks * 2, kDescHi, idesc[0],
+                                                   ks < n_acc ? first : 1u);
                         } else {
                             // few tokens: one MMA per k-step, each k-step into its own partial accumulator
-                            const int a = ks % n_acc;
+                            const int a = (par ? who * n_acc_per : 0) + ks % n_acc_per;
                             umma_f16_ss_lohi<false>(tmem_base + a * acc_stride, a_lo, kDescHi, b_lo0 + ks * 2, kDescHi, idesc[0],
-                                                    ks < n_acc ? first : 1u);
+                                                    ks < n_acc_per ? first : 1u);
                         }
                     }
                 }
                 if (PAIR) umma_commit_pair(bar(kBarEmpty + si)); else umma_commit(bar(kBarEmpty + si));
-                mbar_arrive(bar(kBarTurn + (who ^ 1)));
+                if (!par) mbar_arrive(bar(kBarTurn + (who ^ 1)));
                 if (who == 0) trace(9, n);
             }
             if (ok) {
@@ -538,68 +550,70 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 if (lane == 0) mbar_arrive(bar(kBarRawEmpty + raw_bar(ui)));
             }
         }
-        // the rank-update stages are built by two halves of 8 warps (256 threads) each
-        const int g = g4 >> 1;
-        const int dt2 = (g4 & 1) * 128 + dt;
+        // A rank-update stage is built by the group that owns its slot (n % 4), like any other stage of that slot: the
+        // group has seen every phase of the slot's barriers.  (A group that never waited on a slot could take a phase
+        // two behind for the one it wants - parity waits cannot tell them apart - and the two MMA issuers may be many
+        // stages apart when they run side by side.)
         for (int lj = 0; lj < n_lora && ok; lj++) {
-            // rank-update stage: group 0 builds the weight-side tile from B (forward) / A (backward), group 1 the
-            // activation-side tile from the fp32 low-rank activations, both rounded to T16 here
+            // weight-side tile from B (forward) / A (backward), activation-side tile from the fp32 low-rank activations,
+            // both rounded to T16 here
             const Member &L = p.m[lora_m[lj]];
             const int rank_pad = (L.rank + 15) & ~15;
             const int n = (BWD ? 1 : 2) * nu + lj;
             const int ai = n % kNumA;
+            if (ai != g4) continue;
             ok = mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
-            if (ok) {
-                const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
-                if (g == 1) {
-                    // one thread per token row of this CTA's activation tile: rank_pad/8 chunks of a 128-byte row
-                    const uint32_t x_addr = sbase + kOffX + ai * kXStageBytes;
-                    for (int i = 0; i < n_mma; i++) {
-                        const int ntok = min(MTOK, tb - MTOK * i);
-                        const int rows = PAIR ? (ntok >> 1) : ntok;
-                        if (dt2 < rows) {
-                            const int t = tok0 + MTOK * i + (PAIR ? (int)crank * rows : 0) + dt2;
-                            const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + dt2 * 128);
-                            for (int j = 0; j * 8 < rank_pad; j++) {
-                                float v[8];
+            if (!ok) break;
+            const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
+            {
+                // token rows of this CTA's activation tile: rank_pad/8 chunks of a 128-byte row
+                const uint32_t x_addr = sbase + kOffX + ai * kXStageBytes;
+                for (int i = 0; i < n_mma; i++) {
+                    const int ntok = min(MTOK, tb - MTOK * i);
+                    const int rows = PAIR ? (ntok >> 1) : ntok;
+                    for (int rr = dt; rr < rows; rr += 128) {
+                        const int t = tok0 + MTOK * i + (PAIR ? (int)crank * rows : 0) + rr;
+                        const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + rr * 128);
+                        for (int j = 0; j * 8 < rank_pad; j++) {
+                            float v[8];
 #pragma unroll
-                                for (int q = 0; q < 8; q++) {
-                                    const int r = 8 * j + q;
-                                    v[q] = (r < L.rank && t < p.T) ? L.lora_act[(int64_t)t * L.rank + r] * L.lora_scale : 0.f;
-                                }
-                                st_shared_v4(row_addr + (uint32_t)((j ^ (dt2 & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
-                                             pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
+                            for (int q = 0; q < 8; q++) {
+                                const int r = 8 * j + q;
+                                v[q] = (r < L.rank && t < p.T) ? L.lora_act[(int64_t)t * L.rank + r] * L.lora_scale : 0.f;
                             }
+                            st_shared_v4(row_addr + (uint32_t)((j ^ (rr & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
+                                         pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
                         }
-                    }
-                } else if (!BWD) {
-                    // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
-                    const int row = dt2 & 127, nn = ltile * kTileW + row;
-                    for (int j = dt2 >> 7; j * 8 < rank_pad; j += 2) {
-                        float v[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const int r = 8 * j + i;
-                            v[i] = (r < L.rank && nn < L.N) ? L.lora_w[(int64_t)r * L.N + nn] : 0.f;
-                        }
-                        st_shared_v4(a_addr + (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4)), pack2<T16>(v[0], v[1]),
-                                     pack2<T16>(v[2], v[3]), pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
-                    }
-                } else {
-                    // image(kcol >> 6)[row = r][col = kcol & 63] = A[k, r]
-                    const int kcol = dt2 & 127, c = kcol & 63, k = tile * kTileW + kcol;
-                    for (int r = dt2 >> 7; r < rank_pad; r += 2) {
-                        const float v = (r < L.rank && k < p.K) ? L.lora_w[(int64_t)k * L.rank + r] : 0.f;
-                        const uint32_t addr =
-                            a_addr + (uint32_t)((kcol >> 6) * 8192 + r * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
-                        const uint32_t bits = pack2<T16>(v, 0.f) & 0xFFFFu;
-                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)bits) : "memory");
                     }
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                signal_a_full(ai, 1);
             }
+            if (!BWD) {
+                // image[row = n][col = r] = B[r, n]; chunks of 8 ranks
+                const int row = dt, nn = ltile * kTileW + row;
+                for (int j = 0; j * 8 < rank_pad; j++) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int r = 8 * j + i;
+                        v[i] = (r < L.rank && nn < L.N) ? L.lora_w[(int64_t)r * L.N + nn] : 0.f;
+                    }
+                    st_shared_v4(a_addr + (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4)), pack2<T16>(v[0], v[1]),
+                                 pack2<T16>(v[2], v[3]), pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
+                }
+            } else {
+                // image(kcol >> 6)[row = r][col = kcol & 63] = A[k, r]
+                const int kcol = dt, c = kcol & 63, k = tile * kTileW + kcol;
+                for (int r = 0; r < rank_pad; r++) {
+                    const float v = (r < L.rank && k < p.K) ? L.lora_w[(int64_t)k * L.rank + r] : 0.f;
+                    const uint32_t addr =
+                        a_addr + (uint32_t)((kcol >> 6) * 8192 + r * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
+                    const uint32_t bits = pack2<T16>(v, 0.f) & 0xFFFFu;
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)bits) : "memory");
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            signal_a_full(ai, 4);
         }
         // epilogue: TMEM lane = weight row / column of this tile, TMEM column = token
         if (ok) ok = mbar_wait_bounded(bar(kBarAcc), 0u, abort_flag, p.status, kCodeEpilogue + 1, 16000000000ll);
@@ -618,7 +632,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
-                for (int a = 1; a < n_acc; a++) {      // partial accumulators of the few-token mode
+                for (int a = 1; a < n_acc_sum; a++) {      // partial accumulators of the few-token mode
                     uint32_t w2[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * acc_stride + c * 32), w2);
                     tmem_ld_wait();
@@ -757,6 +771,11 @@ cudaError_t launch_one(const Params &p, dim3 grid, bool pair, cudaStream_t s) {
 
 bool umma_available() { return get_encode_fn() != nullptr; }
 
+bool tmap_encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, const void *base, uint64_t d0, uint64_t d1, uint64_t stride1_bytes,
+                    uint32_t b0, uint32_t b1, CUtensorMapSwizzle swz) {
+    return encode_2d(tm, dt, 0, base, d0, d1, stride1_bytes, b0, b1, swz);
+}
+
 cudaError_t launch_bounded_wait_selftest(int *status, long long limit_cycles, cudaStream_t s) {
     k_bounded_wait_selftest<<<1, 64, 0, s>>>(status, limit_cycles);
     return cudaGetLastError();
@@ -802,6 +821,13 @@ cudaError_t umma_init_weight_maps(WeightDev *w, const char **err) {
                              (uint64_t)w->row_bytes, 32, 64, CU_TENSOR_MAP_SWIZZLE_32B);
     else
         w->tm_q1 = w->tm_q0;
+    {   // whole super-blocks for the few-token tensor-core kernel
+        const uint32_t bb = w->qtype == kTypeQ4K ? (uint32_t)kQ4KBlockBytes : (uint32_t)kQ6KDevBlockBytes;
+        ok = ok && encode_2d(&w->tm_blk_f, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                             (uint64_t)w->row_bytes, bb, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
+        ok = ok && encode_2d(&w->tm_blk_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->data, (uint64_t)w->row_bytes, (uint64_t)w->N,
+                             (uint64_t)w->row_bytes, bb, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
     if (w->qtype == kTypeQ4K)      // whole packed rows for the few-token streaming kernel
         ok = ok && encode_2d(&w->tm_rows, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w->data, (uint64_t)w->row_bytes / 4, (uint64_t)w->N,
                              (uint64_t)w->row_bytes, 72, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -855,8 +881,37 @@ static int pair_min_tokens() {
     return pair_min;
 }
 
+// every member qualifies for the few-token kernel (gt_umma_few.cu)
+static bool few_group(const UmmaLaunch *m, int n) {
+    for (int j = 0; j < n; j++)
+        if (!umma_few_ok(m[j])) return false;
+    return true;
+}
+bool umma_group_few(const UmmaLaunch *m, int n) { return few_group(m, n); }
+
 int umma_group_splits(const UmmaLaunch *m, int n, int sm_count) {
     const bool bwd = m[0].backward != 0;
+    if (few_group(m, n)) {
+        // one launch per member, all with the same split count: forward sized for the members' tiles together (they run
+        // back to back), backward for the longest contraction
+        int tiles = 0, units = 0;
+        for (int j = 0; j < n; j++) {
+            int t, u;
+            umma_few_shape(m[j], &t, &u);
+            if (bwd) {
+                tiles = t;
+                units = u > units ? u : units;
+            } else {
+                tiles += t;
+                units = u;
+            }
+        }
+        // forward: a raw stage is eight weight stages, one per CTA is enough; backward: two (four weight stages)
+        int sp = sm_count / (tiles > 0 ? tiles : 1);
+        const int cap = bwd ? (units / 2 > 1 ? units / 2 : 1) : units;
+        if (sp > cap) sp = cap;
+        return sp < 1 ? 1 : sp;
+    }
     const int tmax = m[0].T < kMaxTok ? m[0].T : kMaxTok;
     const bool pair = tmax >= pair_min_tokens();
     int tiles = 0, units = 0;
@@ -887,6 +942,26 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     const UmmaLaunch &L0 = m[0];
     if (L0.T <= 0) return cudaSuccess;
     const bool bwd = L0.backward != 0;
+    if (few_group(m, n)) {
+        // up to 128 tokens: the kernel with the weights on the wide operand, one launch per member; the adapter terms
+        // follow on the exact rank-r kernels
+        for (int j = 0; j < n; j++) {
+            UmmaLaunch L = m[j];
+            L.splits = L0.splits;
+            if (bwd && j > 0) L.out_assign = 0;      // the members' products add up in one dX
+            cudaError_t ce = launch_umma_few(L, s, err);
+            if (ce != cudaSuccess) return ce;
+        }
+        for (int j = 0; j < n; j++) {
+            const UmmaLaunch &L = m[j];
+            if (L.rank <= 0 || !L.lora_act || !L.lora_w) continue;
+            const int rows = eff_rows(L);
+            cudaError_t ce = bwd ? launch_lora_dx_fp32(L.lora_act, L.lora_w, L.out, L.lora_scale, L.T, L.w->K, L.rank, s)
+                                 : launch_lora_delta_fp32(L.lora_act, L.lora_w, L.out, nullptr, L.T, rows, L.rank, L.lora_scale, L.lora_flag, s);
+            if (ce != cudaSuccess) return ce;
+        }
+        return cudaSuccess;
+    }
     Params p;
     memset(&p, 0, sizeof(p));
     const int tmax = L0.T < kMaxTok ? L0.T : kMaxTok;
@@ -895,12 +970,17 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     // pair mode: TMA box rows = half of an MMA's token columns (64 with four 128-column accumulators)
     static const int mtok = getenv("GT_MMA_TOK") ? atoi(getenv("GT_MMA_TOK")) : 256;
     p.t_box = pair ? (mtok == 128 ? 64 : 128) : (tb < 128 ? tb : 128);
-    // single-CTA mode keeps up to four partial accumulators side by side (see n_acc in the kernel)
+    // one MMA per k-step (tokens <= its width): up to four partial accumulators side by side (see n_acc in the kernel)
     const int stride = (tb + 31) & ~31;
-    const int need_cols = pair ? tb : (stride <= 128 ? 4 * stride : (stride <= 256 ? 2 * stride : stride));
+    const int mma_w = pair ? (mtok == 128 ? 128 : 256) : 512;
+    // (up to 128 tokens on a single CTA: two sets of them, one per MMA issuer)
+    const int need_cols = tb > mma_w ? tb
+                                     : (!pair && stride <= 64 ? 8 * stride : (stride <= 128 ? 4 * stride : (stride <= 256 ? 2 * stride : stride)));
     int tc = 32;
     while (tc < need_cols) tc <<= 1;
     p.tmem_cols = tc;
+    static const int par_ok = getenv("GT_MMA_PAR") ? atoi(getenv("GT_MMA_PAR")) : 1;
+    p.par_ok = par_ok;
     const CUtensorMapDataType dt = L0.fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     p.n_members = n;
     int first = 0;
