@@ -38,7 +38,7 @@ WORKLOAD = "qwen2.5-7b layer projections q,k,v,o,gate,up,down in Q4_K, M=512, fw
 # launch (the largest of the step): a constant taken from one `ncu --set full` capture of that launch, not re-measured
 # by this script.  84.5e6 read (80.1e6 algorithmic: both members' packed weights once + the bf16 activations) and
 # 31.4e6 of the 77.6e6 fp32 output written back before the kernel ended (the rest was still in L2).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 115.9e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 115.7e6
 L2_NOTE = "256 MiB written between timed steps; per-step inputs (131 MB weights + activations) exceed L2"
 GROUPS = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]]
 
@@ -515,7 +515,7 @@ def run_ours(args) -> None:
             "launches": prof["gemm_launches"], "avg_launch_us": 1e3 * prof["gemm_ms"] / max(1, prof["gemm_launches"]),
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
             "traffic_source": "constant from one ncu --set full capture of this launch (dram__bytes_read.sum + dram__bytes_write.sum); not re-measured by this run",
-            "traffic_of": "gate,up forward launch, 2 x 18944x3584 at M=512 (algorithmic HBM bytes: 80.1e6 read + 77.6e6 fp32 output, of which 31.4e6 left the L2 before the kernel ended)",
+            "traffic_of": "gate,up forward launch, 2 x 18944x3584 at M=512 (algorithmic HBM bytes: 80.1e6 read + 77.6e6 fp32 output, of which 31.1e6 left the L2 before the kernel ended)",
         }
         # CPU baseline: the oracle (a port of the reference's CPU path) on this host, one pass over the same layer
         from oracle import oracle as O
@@ -796,15 +796,26 @@ def run_sweep(args) -> None:
                 e1.synchronize()
                 us = 1e3 * e0.elapsed_time(e1) / (passes * copies)
                 graph.reset()
+                # the GEMM launch alone (the engine's events around it; each event pair costs a few microseconds, which
+                # shows at few tokens): the figure to hold against the tensor roofline at many tokens, where the call also
+                # spends time casting its activations
+                eng.profile_read(True)
+                eng.profile_enable(True)
+                for w in ws[:4]:
+                    one(w)
+                pr = eng.profile_read(True)
+                eng.profile_enable(False)
+                kernel_us = 1e3 * pr["gemm_ms"] / max(1, pr["gemm_launches"])
                 tf = 2.0 * M * N * K / us / 1e6
                 gbs = wbytes / us / 1e3
                 rows.append({"proj": name, "qtype": "Q6_K" if qt == synth.TYPE_Q6_K else "Q4_K", "N": N, "K": K, "M": M,
                              "dir": direction, "us": us, "tflops": tf, "frac_tensor": tf / peaks["bf16_tflops"],
                              "weight_gbs": gbs, "frac_hbm": gbs / peaks["hbm_gbs"], "copies": copies,
-                             "l2_resident": copies * wbytes < L2_BYTES})
+                             "l2_resident": copies * wbytes < L2_BYTES, "kernel_us": kernel_us,
+                             "kernel_tflops": 2.0 * M * N * K / kernel_us / 1e6})
                 print(f"{name:5s} {rows[-1]['qtype']} M={M:5d} {direction:3s}: {us:8.1f} us {tf:8.1f} TFLOP/s ({100 * tf / peaks['bf16_tflops']:5.1f} % of "
                       f"{peaks['bf16_tflops']:.0f})  weights {gbs:7.1f} GB/s ({100 * gbs / peaks['hbm_gbs']:5.1f} % of {peaks['hbm_gbs']:.0f})"
-                      f"{'  [weights fit L2]' if rows[-1]['l2_resident'] else ''}", file=sys.stderr, flush=True)
+                      f"  kernel {kernel_us:7.1f} us{'  [weights fit L2]' if rows[-1]['l2_resident'] else ''}", file=sys.stderr, flush=True)
         for w in ws:
             w.free()
     eng.close()
@@ -812,7 +823,7 @@ def run_sweep(args) -> None:
                       "timing": "whole projection call (16-bit cast of the activations, output fill where split-K adds into it, GEMM "
                                 "kernel), device pointers, no adapter: CUDA events around 3 passes over `copies` copies of the weight "
                                 "tensor called back to back (together larger than the 126 MB L2 unless marked l2_resident), replayed from a CUDA "
-                                "graph, time per call"}),
+                                "graph, time per call; kernel_us = the engine's CUDA events around the GEMM launch alone, mean of 4 calls"}),
           flush=True)
 
 

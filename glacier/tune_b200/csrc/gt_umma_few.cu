@@ -1,4 +1,4 @@
-// Frozen-base K-quant projection GEMMs for up to 128 tokens on the sm_100a tensor cores.
+// Frozen-base Q4_K projection GEMMs for a few tokens (up to 64) on the sm_100a tensor cores.
 //
 //   forward   out[T, N]  (+)= act[T, K] * W[N, K]^T (+ bias)
 //   backward  out[T, K]  (+)= act[T, N] * W[N, K]
@@ -420,7 +420,10 @@ int umma_few_max_tokens() {
 
 bool umma_few_ok(const UmmaLaunch &L) {
     const WeightDev *w = L.w;
-    if (!w || !w->tma_ok || (w->qtype != kTypeQ4K && w->qtype != kTypeQ6K)) return false;
+    // Q4_K only: a Q6_K stage ring (224-byte blocks) leaves room for four weight stages and two raw stages, and measured
+    // slower than gt_umma_gemm.cu's 128-token variant (down projection forward at 16 tokens: 43 us against 34 us per call;
+    // dX 30 us either way)
+    if (!w || !w->tma_ok || w->qtype != kTypeQ4K) return false;
     if (L.T < 1 || L.T > umma_few_max_tokens() || (w->K % 256) != 0) return false;
     const int rows = L.rows > 0 ? L.rows : w->N;
     // the contraction must give either MMA issuer a stage: forward K >= 128 always does; backward needs 64 rows
@@ -475,12 +478,8 @@ cudaError_t launch_umma_few(const UmmaLaunch &L, cudaStream_t s, const char **er
     p.splits = L.splits < 1 ? 1 : (L.splits > units ? units : L.splits);
     p.atomic_out = bwd ? ((p.splits > 1 || !L.out_assign) ? 1 : 0) : ((p.splits > 1 || L.out_prefilled) ? 1 : 0);
     const dim3 grid(tiles, p.splits);
-    if (w->qtype == kTypeQ4K) {
-        if (!L.fp16) return bwd ? launch_few_variant<kTypeQ4K, __nv_bfloat16, true>(p, grid, s) : launch_few_variant<kTypeQ4K, __nv_bfloat16, false>(p, grid, s);
-        return bwd ? launch_few_variant<kTypeQ4K, __half, true>(p, grid, s) : launch_few_variant<kTypeQ4K, __half, false>(p, grid, s);
-    }
-    if (!L.fp16) return bwd ? launch_few_variant<kTypeQ6K, __nv_bfloat16, true>(p, grid, s) : launch_few_variant<kTypeQ6K, __nv_bfloat16, false>(p, grid, s);
-    return bwd ? launch_few_variant<kTypeQ6K, __half, true>(p, grid, s) : launch_few_variant<kTypeQ6K, __half, false>(p, grid, s);
+    if (!L.fp16) return bwd ? launch_few_variant<kTypeQ4K, __nv_bfloat16, true>(p, grid, s) : launch_few_variant<kTypeQ4K, __nv_bfloat16, false>(p, grid, s);
+    return bwd ? launch_few_variant<kTypeQ4K, __half, true>(p, grid, s) : launch_few_variant<kTypeQ4K, __half, false>(p, grid, s);
 }
 
 }  // namespace gt

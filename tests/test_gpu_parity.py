@@ -139,9 +139,9 @@ STREAM_SHAPES = [
 
 
 FEW_SHAPES = [
-    # up to 64 tokens: the tensor-core kernel with the weights on the wide operand, both types, both directions.
-    # (qtype, N, K, T): one row tile and several, a last tile of 256 rows that is mostly out of range, the shortest
-    # contraction (one super-block), split-K and no split-K, the 7B shapes
+    # up to 64 tokens: Q4_K runs on the tensor-core kernel with the weights on the wide operand, Q6_K on the 128-token
+    # variant of the main kernel; both directions.  (qtype, N, K, T): one row tile and several, a last tile of 256 rows
+    # that is mostly out of range, the shortest contraction (one super-block), split-K and no split-K, the 7B shapes
     (S.TYPE_Q4_K, 256, 256, 9), (S.TYPE_Q4_K, 300, 512, 33), (S.TYPE_Q6_K, 64, 768, 16), (S.TYPE_Q6_K, 1000, 1024, 64),
     (S.TYPE_Q4_K, 3584, 3584, 16), (S.TYPE_Q6_K, 512, 3584, 40), (S.TYPE_Q4_K, 18944, 3584, 17), (S.TYPE_Q6_K, 3584, 18944, 64),
 ]
