@@ -148,6 +148,23 @@ int compute_low(gt_engine *e, gt_adapter *const *ads, int n, const float *Xd, vo
     return GT_OK;
 }
 
+// The same from an X that already exists as bf16 [T, K] (bf16 mode only): low_j = X16 * A_j, no copy is written.
+int compute_low16(gt_engine *e, gt_adapter *const *ads, int n, const void *X16, int T, int K, const RowFill *fills = nullptr,
+                  int n_fills = 0) {
+    LoraXaJob jobs[kMaxGroup];
+    for (int j = 0; j < n; j++) {
+        gt_adapter *a = ads[j];
+        GT_CUDA(a->low.reserve(2 * low_bytes(a, T)));
+        GT_CUDA(cudaMemsetAsync(a->low.p, 0, 2 * low_bytes(a, T), e->stream));
+        a->low_T = T;
+        a->dlow_clean = true;
+        jobs[j] = LoraXaJob{a->A, low_of(a), a->rank};
+    }
+    for (int j = 0; j < n_fills; j++) GT_LAUNCH(e, launch_fill_rows(fills[j].dst, fills[j].bias, T, fills[j].N, e->stream));
+    if (n) GT_LAUNCH(e, launch_lora_xa16_group(X16, K, jobs, n, T, K, e->stream));
+    return GT_OK;
+}
+
 int forward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *Xd, float *Yd, int T, bool use_lora);
 int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const float *dYd, const float *Xd, float *dXd, int T,
                     bool use_lora, bool reuse_low, bool assign);
@@ -161,8 +178,10 @@ bool group_tensor_ok(const gt_engine *e, int n, const gt_weight *const *w) {
 
 // Y_j = X * W_j^T (+ bias_j) (+ lora_j) for 1..3 projections that read the same X.  Tensor-core path: one pass over X
 // (16-bit copy + every adapter's X*A), one GEMM launch.  Anything else runs member by member.
+// x16_ready (bf16 mode, members on the tensor path): the input already exists as bf16 [T, K] - nothing is cast, the
+// adapters' X*A reads that copy, Xd may be null.
 int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
-                         int T, int flags) {
+                         int T, int flags, const void *x16_ready) {
     bool lora[kMaxGroup];
     for (int j = 0; j < n; j++) {
         lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0 && ad[j]->scaling != 0.f;
@@ -180,7 +199,7 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
     const int fp16 = e->math_mode == GT_MATH_FP16;
     // Few tokens: the projection is bound by streaming the packed weights, which the warp-level kernel does several
     // times faster than the CTA-wide tensor-core kernel; the adapter term is added by the exact rank-r kernel.
-    bool stream = e->math_mode == GT_MATH_BF16 && (reinterpret_cast<uintptr_t>(Xd) & 15) == 0;
+    bool stream = !x16_ready && e->math_mode == GT_MATH_BF16 && (reinterpret_cast<uintptr_t>(Xd) & 15) == 0;
     for (int j = 0; j < n && stream; j++) stream = stream_fwd_ok(&w[j]->dev, T);
     if (stream) {
         gt_adapter *with[kMaxGroup];
@@ -212,14 +231,15 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         }
         return GT_OK;
     }
-    GT_CUDA(e->x16.reserve((size_t)T * K * 2));
+    if (!x16_ready) GT_CUDA(e->x16.reserve((size_t)T * K * 2));
+    const void *act16 = x16_ready ? x16_ready : e->x16.p;
     UmmaLaunch m[kMaxGroup];
     for (int j = 0; j < n; j++) {
         const WeightDev &wd = w[j]->dev;
         m[j].w = &wd;
         m[j].backward = 0;
         m[j].fp16 = fp16;
-        m[j].act16 = e->x16.p;
+        m[j].act16 = act16;
         m[j].ld_act = K;
         m[j].T = T;
         m[j].out = Yd[j];
@@ -257,7 +277,12 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
     int n_with = 0;
     for (int j = 0; j < n; j++)
         if (lora[j]) with[n_with++] = ad[j];
-    if (n_with) {
+    if (x16_ready) {
+        int rc = compute_low16(e, with, n_with, x16_ready, T, K, fills, n_fills);
+        if (rc != GT_OK) return rc;
+        for (int j = 0; j < n; j++)
+            if (lora[j]) m[j].lora_act = low_of(ad[j]);
+    } else if (n_with) {
         int rc = compute_low(e, with, n_with, Xd, e->x16.p, fp16, T, K, fills, n_fills);
         if (rc != GT_OK) return rc;
         for (int j = 0; j < n; j++)
@@ -392,7 +417,7 @@ bool side_da_enabled() {
 
 int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const bool *lora,
                         const float *const *dYd, const float *Xd, void *const *dy16, const int *ld16, int T, bool reuse_low,
-                        float *zero_dx, bool side_da = false) {
+                        float *zero_dx, bool side_da = false, const void *X16 = nullptr) {
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
     const bool fast = e->math_mode == GT_MATH_BF16;      // bf16 warp-MMA reductions; exact fp32 otherwise
@@ -408,7 +433,7 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
         }
     }
     if (n_fresh) {
-        int rc = compute_low(e, fresh, n_fresh, Xd, nullptr, 0, T, K);
+        int rc = X16 ? compute_low16(e, fresh, n_fresh, X16, T, K) : compute_low(e, fresh, n_fresh, Xd, nullptr, 0, T, K);
         if (rc != GT_OK) return rc;
     }
     LoraDyJob dy[kMaxGroup];
@@ -437,7 +462,8 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
             GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));
             da_stream = e->s_aux;
         }
-        GT_LAUNCH(e, launch_lora_da_group(Xd, da, nl, T, K, da_stream));
+        if (X16) GT_LAUNCH(e, launch_lora_da16_group(X16, K, da, nl, T, K, da_stream));
+        else GT_LAUNCH(e, launch_lora_da_group(Xd, da, nl, T, K, da_stream));
         if (da_stream != e->stream) {
             GT_CUDA(cudaEventRecord(e->ev_aux_join, e->s_aux));
             e->aux_pending = true;
@@ -453,8 +479,9 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
 }
 
 // dX += sum_j dY_j * W_j (+ lora terms); dA_j, dB_j accumulate.  Tensor-core path: one GEMM launch for the group.
+// X16 (bf16 mode, members on the tensor path): the forward input as bf16 [T, K] instead of the fp32 Xd (which may be null).
 int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dYd,
-                          const float *Xd, float *dXd, int T, int flags) {
+                          const float *Xd, float *dXd, int T, int flags, const void *X16) {
     bool lora[kMaxGroup];
     for (int j = 0; j < n; j++) lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0;
     const bool reuse_low = (flags & GT_FLAG_REUSE_LOW) != 0;
@@ -504,7 +531,8 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
     }
     const bool store_first = assign && run_splits[0] == 1;
     int rc = lora_backward_group(e, n, w, ad, lora, dYd, Xd, dy16, ld16, T, reuse_low, (assign && !store_first) ? dXd : nullptr,
-                                 side_da_enabled() && !e->profile);      // profiling times each GEMM alone on the device
+                                 side_da_enabled() && !e->profile,       // profiling times each GEMM alone on the device
+                                 e->math_mode == GT_MATH_BF16 ? X16 : nullptr);
     if (rc != GT_OK) return rc;
     for (int j = 0; j < n; j++) {
         if (lora[j]) {
@@ -514,6 +542,13 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
             m[j].rank = ad[j]->rank;
         }
     }
+    // A run served by the few-token kernel adds its adapter terms to dX with plain read-modify-writes: then no run of
+    // this call may work on the side stream (the runs' types differ, so some may be few-token launches and some not)
+    bool any_few = false;
+    for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
+        for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
+        any_few = any_few || umma_group_few(run_m + pos, count[r]);
+    }
     for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
         for (int i = 0; i < count[r]; i++) {
             run_m[pos + i] = m[order[pos + i]];
@@ -522,7 +557,7 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
         run_m[pos].out_assign = (r == 0 && store_first) ? 1 : 0;
         // launches of the other quantization types add into the same dX with atomics: beside the first one on the side
         // stream (behind the dA pass there), unless the first one writes dX with plain stores
-        const bool side = r > 0 && !store_first && e->s_aux && !e->profile && side_da_enabled() && !umma_group_few(run_m + pos, count[r]);
+        const bool side = r > 0 && !store_first && e->s_aux && !e->profile && side_da_enabled() && !any_few;
         if (side && !e->aux_pending) {      // no dA pass was forked: fork now (the pass over dY is complete by stream order)
             GT_CUDA(cudaEventRecord(e->ev_aux_fork, e->stream));
             GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));
@@ -570,13 +605,23 @@ int backward_device(gt_engine *e, const gt_weight *w, gt_adapter *ad, const floa
 
 // FFN block on device tensors: gate, up = projections of X (one group); hidden = SiLU(gate) * up; Y = down(hidden).
 // w / ad = {gate, up, down}.  gate_d / up_d / hidden_d may be null (engine scratch is used).
+// The SwiGLU pass can write the down projection's 16-bit operand itself: bf16 mode, down on the tensor path, more tokens
+// than the few-token kernels take (they stage fp32 activations themselves), ffn a multiple of 8.
+bool ffn_hidden16_ok(const gt_engine *e, const gt_weight *const *w, int T) {
+    static const bool on = !(getenv("GT_SWIGLU_FOLD") && atoi(getenv("GT_SWIGLU_FOLD")) == 0);
+    const gt_weight *down = w[2];
+    return on && e->math_mode == GT_MATH_BF16 && tensor_path(e, down) && T > 64 && (down->dev.K % 8) == 0;
+}
+
 int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *gate_d, float *up_d,
-                       float *hidden_d, float *Yd, int T, int flags) {
+                       float *hidden_d, float *Yd, int T, int flags, void *hidden16) {
     const int F = w[0]->dev.N;
     const size_t bf = (size_t)T * F * sizeof(float);
+    const bool fold = ffn_hidden16_ok(e, w, T);
+    if (hidden16 && !fold) return fail(GT_ERR_INVALID, "ffn_forward_device: a 16-bit hidden tensor needs ffn_hidden16_ok()");
     float *bufs[3] = {gate_d, up_d, hidden_d};
     for (int i = 0; i < 3; i++) {
-        if (!bufs[i]) {
+        if (!bufs[i] && !(i == 2 && fold)) {      // folded: the fp32 product is written only where the caller wants it
             GT_CUDA(e->ffn[i].reserve(bf));
             bufs[i] = (float *)e->ffn[i].p;
         }
@@ -584,25 +629,39 @@ int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *cons
     float *gu[2] = {bufs[0], bufs[1]};
     int rc = forward_group_device(e, 2, w, ad, Xd, gu, T, flags);
     if (rc != GT_OK) return rc;
-    GT_LAUNCH(e, launch_swiglu_fwd(bufs[0], bufs[1], bufs[2], (int64_t)T * F, e->sm_count, e->stream));
     float *yd = Yd;
+    if (fold) {
+        // SiLU(gate) * up goes out as the bf16 operand of the down projection (and as fp32 only if asked for): the separate
+        // pass that would read the fp32 product back to round it does not run
+        void *h16 = hidden16;
+        if (!h16) {
+            GT_CUDA(e->x16.reserve((size_t)T * F * 2));
+            h16 = e->x16.p;
+        }
+        GT_LAUNCH(e, launch_swiglu_fwd16(bufs[0], bufs[1], bufs[2], h16, (int64_t)T * F, 0, e->sm_count, e->stream));
+        return forward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, bufs[2], &yd, T, flags, h16);
+    }
+    GT_LAUNCH(e, launch_swiglu_fwd(bufs[0], bufs[1], bufs[2], (int64_t)T * F, e->sm_count, e->stream));
     return forward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, bufs[2], &yd, T, flags);
 }
 
 // The matching backward: dHidden = dY * W_down (+ adapter), (dGate, dUp) = SwiGLU'(dHidden, gate, up),
 // dX (+)= dGate * W_gate + dUp * W_up (+ adapters); adapter gradients accumulate.  Device tensors.
 int ffn_backward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *dYd, const float *Xd,
-                        const float *gate_d, const float *up_d, const float *hidden_d, float *dXd, int T, int flags) {
+                        const float *gate_d, const float *up_d, const float *hidden_d, float *dXd, int T, int flags,
+                        const void *hidden16) {
     const int F = w[0]->dev.N;
     const size_t bf = (size_t)T * F * sizeof(float);
+    if (hidden16 && !ffn_hidden16_ok(e, w, T))
+        return fail(GT_ERR_INVALID, "ffn_backward_device: a 16-bit hidden tensor needs ffn_hidden16_ok()");
     for (int i = 0; i < 3; i++) GT_CUDA(e->ffn[i].reserve(bf));
     float *dh = (float *)e->ffn[0].p, *dg = (float *)e->ffn[1].p, *du = (float *)e->ffn[2].p;
-    if (gate_d == dh || gate_d == dg || gate_d == du || up_d == dh || up_d == dg || up_d == du || hidden_d == dh || hidden_d == dg ||
-        hidden_d == du)
+    if (gate_d == dh || gate_d == dg || gate_d == du || up_d == dh || up_d == dg || up_d == du ||
+        (hidden_d && (hidden_d == dh || hidden_d == dg || hidden_d == du)))
         return fail(GT_ERR_INVALID, "gt_ffn_backward: gate, up and hidden must be the caller's buffers (the forward call was given NULL)");
     const float *dy1 = dYd;
     int rc = backward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, &dy1, hidden_d, dh, T,
-                                   (flags & ~GT_FLAG_DX_ASSIGN) | GT_FLAG_DX_ASSIGN);      // dHidden is written, not added to
+                                   (flags & ~GT_FLAG_DX_ASSIGN) | GT_FLAG_DX_ASSIGN, hidden16);      // dHidden is written, not added to
     if (rc != GT_OK) return rc;
     GT_LAUNCH(e, launch_swiglu_bwd(dh, gate_d, up_d, dg, du, (int64_t)T * F, e->sm_count, e->stream));
     const float *dgu[2] = {dg, du};

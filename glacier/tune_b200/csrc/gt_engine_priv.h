@@ -140,14 +140,19 @@ bool tensor_path(const gt_engine *e, const gt_weight *w);
 cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on = nullptr);
 bool side_da_enabled();
 // device-pointer forms of the projection calls; the caller holds the engine lock and has made the device current
+// (x16_ready / X16: the input as bf16 [T, K] where the caller has it - bf16 mode, tensor path; the fp32 X may then be null)
 int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
-                         int T, int flags);
+                         int T, int flags, const void *x16_ready = nullptr);
 int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dYd,
-                          const float *Xd, float *dXd, int T, int flags);
+                          const float *Xd, float *dXd, int T, int flags, const void *X16 = nullptr);
+// SiLU(gate) * up can be kept as bf16 only (hidden16: [T, ffn] bf16, hidden_d null) when ffn_hidden16_ok(): the SwiGLU pass
+// then writes the down projection's 16-bit operand itself and the adapter products of the down projection read that copy.
+bool ffn_hidden16_ok(const gt_engine *e, const gt_weight *const *w, int T);
 int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *gate_d, float *up_d,
-                       float *hidden_d, float *Yd, int T, int flags);
+                       float *hidden_d, float *Yd, int T, int flags, void *hidden16 = nullptr);
 int ffn_backward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *dYd, const float *Xd,
-                        const float *gate_d, const float *up_d, const float *hidden_d, float *dXd, int T, int flags);
+                        const float *gate_d, const float *up_d, const float *hidden_d, float *dXd, int T, int flags,
+                        const void *hidden16 = nullptr);
 int join_comm(gt_engine *e);
 int allreduce_begin_locked(gt_engine *e, float *g_dev, int64_t count, float scale);
 // LM head and embedding on device tensors (gt_lmhead.cu); loss_dev / valid_dev are device scalars (may be null)

@@ -118,6 +118,8 @@ cudaError_t launch_lora_xa_group(const float *X, const LoraXaJob *jobs, int n, v
 // the same from an input that already exists as bf16 [T, ld16] (K % 8 == 0, 16-byte aligned): no copy is written
 cudaError_t launch_lora_xa16_group(const void *X16, int ld16, const LoraXaJob *jobs, int n, int T, int K, cudaStream_t s);
 cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, const RowFill *fills, int n_fills, cudaStream_t s);
+// dA from an X that exists as bf16 [T, ld16] (K % 8 == 0, 16-byte aligned)
+cudaError_t launch_lora_da16_group(const void *X16, int ld16, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s);
 cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s);
 
 // ---- tcgen05 kernels (gt_umma_gemm.cu) ------------------------------------------------------------------

@@ -667,6 +667,79 @@ __global__ void __launch_bounds__(256, 2) k_lora_da_tc(const DaParams p) {
     }
 }
 
+// The same from an X that exists as bf16 (see k_lora_xa16_tc): 2 bytes per element read, no rounding pass.
+struct Da16Params {
+    const uint16_t *X16;
+    int ld, T, K, n, tok_per_group;
+    DaChunk c[kMaxChunks];
+};
+__global__ void __launch_bounds__(256, 2) k_lora_da16_tc(const Da16Params p) {
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t *Xs = dyn_smem;
+    uint8_t *Ls = Xs + kXsBytes;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int T = p.T, K = p.K;
+    const int k0 = blockIdx.x * TC;
+    const int tg0 = blockIdx.y * p.tok_per_group, tg1 = min(T, tg0 + p.tok_per_group);
+    const int m0 = warp * 16;
+    pdl_wait();
+    pdl_trigger();
+    float acc[kMaxChunks][2][4];
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) acc[j][i][0] = acc[j][i][1] = acc[j][i][2] = acc[j][i][3] = 0.f;
+    const uint32_t xs = smem_u32(Xs), ls = smem_u32(Ls);
+    uint4 v[NI16];
+    float4 lv[kMaxChunks];
+    auto l_load = [&](int ts) {
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; j++) {
+            if (j < p.n) {
+                const DaChunk c = p.c[j];
+                const int row = ts + (tid >> 2);
+                lv[j] = ld4(c.dLow + c.r0, row, c.R, (tid & 3) * 4, min(16, c.R - c.r0), row < tg1, c.vec != 0);
+            }
+        }
+    };
+    tile_load16(p.X16, p.ld, K, tg0, tg1, k0, v, tid);
+    l_load(tg0);
+    for (int ts = tg0; ts < tg1; ts += TT) {
+        __syncthreads();
+        tile_store16(v, Xs, tid);
+#pragma unroll
+        for (int j = 0; j < kMaxChunks; j++)
+            if (j < p.n) st_bf16x4(Ls + j * kLsBytes + (tid >> 2) * RSB + (tid & 3) * 8, lv[j]);
+        if (ts + TT < tg1) {      // the next tile's loads fly during the MMAs below
+            tile_load16(p.X16, p.ld, K, ts + TT, tg1, k0, v, tid);
+            l_load(ts + TT);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < TT / 16; ks++) {
+            uint32_t a[4];
+            ldsm_x4_t(lm_a_km(xs, GSB, m0, ks * 16, lane), a);       // X^T: m = column of X, k = token
+#pragma unroll
+            for (int j = 0; j < kMaxChunks; j++) {
+                if (j < p.n) {
+                    uint32_t b[4];
+                    ldsm_x4_t(lm_b_kn(ls + j * kLsBytes, RSB, 0, ks * 16, lane), b);
+                    mma_bf16(acc[j][0], a, b[0], b[1]);
+                    mma_bf16(acc[j][1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxChunks; j++) {
+        if (j >= p.n) break;
+        const DaChunk c = p.c[j];
+        const int rc = min(16, c.R - c.r0);
+#pragma unroll
+        for (int i = 0; i < 2; i++) frag_atomic_add(c.dA + c.r0, c.R, acc[j][i], k0 + m0 + g, K, i * 8 + 2 * t4, rc, c.scaling);
+    }
+}
+
 // Two blocks are resident per SM (registers and the 64 KiB ring): a launch should fit ONE wave of kSlots blocks, or a
 // second, nearly empty wave doubles its time (400 blocks of 3 strips on 296 slots ran as 2 x 3 strips; 296 blocks of 4
 // strips run as 1 x 4).
@@ -852,6 +925,37 @@ cudaError_t launch_lora_da_group(const float *X, const LoraDaJob *jobs, int n, i
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
         cudaError_t le = launch_k(k_lora_da_tc, dim3(strips, groups), dim3(256), (size_t)(kRingBytes + kXsBytes + p.n * kLsBytes), s, p);
+        p.n = 0;
+        return le;
+    };
+    for (int j = 0; j < n; j++)
+        for (int r0 = 0; r0 < jobs[j].R; r0 += 16) {
+            p.c[p.n++] = DaChunk{jobs[j].dLow, jobs[j].dA, jobs[j].scaling, jobs[j].R, r0, is_vec(jobs[j].dLow, jobs[j].R)};
+            if (p.n == kMaxChunks && (e = flush()) != cudaSuccess) return e;
+        }
+    return flush();
+}
+
+cudaError_t launch_lora_da16_group(const void *X16, int ld16, const LoraDaJob *jobs, int n, int T, int K, cudaStream_t s) {
+    if (T <= 0 || K <= 0 || n <= 0) return cudaSuccess;
+    if ((K & 7) != 0 || (ld16 & 7) != 0 || (reinterpret_cast<uintptr_t>(X16) & 15) != 0) return cudaErrorInvalidValue;
+    static PerDeviceOnce configured;
+    cudaError_t e = per_device_once(configured, [] {
+        return cudaFuncSetAttribute(k_lora_da16_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kXsBytes + kMaxChunks * kLsBytes));
+    });
+    if (e != cudaSuccess) return e;
+    const int strips = (K + TC - 1) / TC;
+    int groups, tpg;
+    pick_groups(strips, T, groups, tpg);
+    Da16Params p{};
+    p.X16 = (const uint16_t *)X16;
+    p.ld = ld16;
+    p.T = T;
+    p.K = K;
+    p.tok_per_group = tpg;
+    auto flush = [&]() -> cudaError_t {
+        if (p.n == 0) return cudaSuccess;
+        cudaError_t le = launch_k(k_lora_da16_tc, dim3(strips, groups), dim3(256), (size_t)(kXsBytes + p.n * kLsBytes), s, p);
         p.n = 0;
         return le;
     };

@@ -92,7 +92,9 @@ int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockStat
     GT_LAUNCH(e, launch_add_rmsnorm_fwd(x_in, o, L.norm2, s.x1, s.n2, T, H, c.rms_eps, e->stream));      // x1 = x + o; n2 = norm(x1)
     const gt_weight *fw[3] = {L.w[kGate], L.w[kUp], L.w[kDown]};
     gt_adapter *fa[3] = {L.ad[kGate], L.ad[kUp], L.ad[kDown]};
-    rc = ffn_forward_device(e, fw, fa, s.n2, s.gate, s.up, s.hidden, m->tmp_h, T, 0);
+    // SiLU(gate) * up is kept as bf16 only where the engine can work from that (the buffer is sized for fp32 either way)
+    const bool h16 = ffn_hidden16_ok(e, fw, T);
+    rc = ffn_forward_device(e, fw, fa, s.n2, s.gate, s.up, h16 ? nullptr : s.hidden, m->tmp_h, T, 0, h16 ? (void *)s.hidden : nullptr);
     if (rc != GT_OK) return rc;
     if (next_norm && next_n1) GT_LAUNCH(e, launch_add_rmsnorm_fwd(s.x1, m->tmp_h, next_norm, x_out, next_n1, T, H, c.rms_eps, e->stream));
     else GT_LAUNCH(e, launch_add(s.x1, m->tmp_h, x_out, (int64_t)T * H, e->sm_count, e->stream));
@@ -109,7 +111,9 @@ int block_backward(gt_model *m, int l, const float *d_out, const float *x_in, co
     const gt_weight *fw[3] = {L.w[kGate], L.w[kUp], L.w[kDown]};
     gt_adapter *fa[3] = {L.ad[kGate], L.ad[kUp], L.ad[kDown]};
     // A. FFN: down, SwiGLU, gate | up -> dNorm2X; RMSNorm2 backward + residual: dX1 = dOut + dNorm(dNorm2X)
-    int rc = ffn_backward_device(e, fw, fa, d_out, s.n2, s.gate, s.up, s.hidden, m->dn, T, flags);
+    const bool h16 = ffn_hidden16_ok(e, fw, T);
+    int rc = ffn_backward_device(e, fw, fa, d_out, s.n2, s.gate, s.up, h16 ? nullptr : s.hidden, m->dn, T, flags,
+                                 h16 ? (const void *)s.hidden : nullptr);
     if (rc != GT_OK) return rc;
     GT_LAUNCH(e, launch_rmsnorm_bwd(m->dn, s.x1, L.norm2, d_out, m->dx1, T, H, c.rms_eps, e->stream));
     // B. attention: o projection, attention, RoPE, q | k | v -> dNorm1X; RMSNorm1 backward + residual

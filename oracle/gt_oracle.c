@@ -17,8 +17,11 @@
  *           (src/Glacier.Tune/Export/GgufMerger.cs:666-757,
  *            tests/Glacier.Tune.Tests/GgufMergerQuantizationTests.cs:118-191), which fixes the
  *           nibble order.
- *   Q6_K  — PARITY UNPINNED: the reference holds no test, fixture or CPU source for Q6_K; the
- *           only statement of the layout is the CUDA kernel src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:263-332.
+ *   Q6_K  — the reference holds no test, fixture or CPU source for Q6_K (the only statement of the layout in it is
+ *           the CUDA kernel src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:263-332); pinned against the format's own
+ *           implementation instead: gguf.quants.dequantize (package gguf 0.19.0) on seeded blocks, bit for bit, with
+ *           the generating script and its outputs in tests/golden/ (make_gguf_golden.py, gguf_dequant_golden.npz).
+ *           The same fixture pins Q4_K a second time.
  *   LoRA  — pinned by tests/Glacier.Tune.Tests/KernelTests.cs:133-202 (fast path vs naive, 1e-4).
  *   QuantKernels.MatMulBatch / ExtractEmbedding live in Glacier.Inference 1.8.0 (not vendored):
  *           restated here as exact-dequant fp32 GEMM / row dequant, which is what the

@@ -5,7 +5,9 @@ loop that cannot take the device-wide synchronisation an allocation implies, or 
 a pool.  For them the library keeps the 16-bit operand copy of the input-gradient GEMM in a fixed 4 MiB array
 instead of the engine's grow-only buffer.  This file checks, through the C ABI, that the variant returns what
 gt_launch_gemm_bwd returns on two calls in a row (the second one smaller, so stale contents of the shared array
-would show), that it accumulates into dDX like the regular call, and that it refuses sizes beyond its array.
+would show), that it accumulates into dDX like the regular call, that it agrees with the CPU path within the
+bf16 gate, that the device's free memory is the same before and after a call at a batch no earlier call has seen,
+and that it refuses sizes beyond its array.
 It is collected last so that a run stopping at the first failure has already run every other test.
 """
 import numpy as np
