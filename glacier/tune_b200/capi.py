@@ -13,7 +13,7 @@ import numpy as np
 
 from . import build as _build
 
-TYPE_F32, TYPE_F16, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 12, 14
+TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 2, 8, 12, 14
 MATH_BF16, MATH_FP16, MATH_FP32 = 0, 1, 2
 DIR_FORWARD, DIR_BACKWARD = 0, 1
 FLAG_DEVICE_PTRS, FLAG_NO_LORA, FLAG_REUSE_LOW, FLAG_DX_ASSIGN, FLAG_HOST_ASYNC = 1, 2, 4, 8, 16

@@ -818,7 +818,9 @@ const char *gt_version(void) { return "glaciertune_b200 0.1 (sm_100a)"; }
 
 int gt_supports(int ggml_type, int direction) {
     if (direction != GT_DIR_FORWARD && direction != GT_DIR_BACKWARD) return 0;
-    return (ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K || ggml_type == GT_TYPE_F32 || ggml_type == GT_TYPE_F16) ? 1 : 0;
+    // Q4_0 and Q8_0 (the reference's other Supports*Gemm types) run on the exact CUDA-core kernels in every math mode
+    return (ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K || ggml_type == GT_TYPE_F32 || ggml_type == GT_TYPE_F16 ||
+            ggml_type == GT_TYPE_Q4_0 || ggml_type == GT_TYPE_Q8_0) ? 1 : 0;
 }
 
 int gt_engine_create(const gt_config *cfg, gt_engine **out) {
@@ -994,6 +996,10 @@ int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_
         expect = nelem * 4;
     } else if (ggml_type == GT_TYPE_F16) {
         expect = nelem * 2;
+    } else if (ggml_type == GT_TYPE_Q4_0 || ggml_type == GT_TYPE_Q8_0) {
+        if (in_features % 32 != 0)
+            return fail(GT_ERR_INVALID, "tensor [%d, %d] is not a whole number of 32-weight blocks per row", out_features, in_features);
+        expect = nelem / 32 * (ggml_type == GT_TYPE_Q4_0 ? kQ40BlockBytes : kQ80BlockBytes);
     } else {
         if (nelem % 256 != 0 || in_features % 32 != 0)
             return fail(GT_ERR_INVALID, "K-quant tensor [%d, %d] is not a whole number of 256-weight super-blocks", out_features,
@@ -1036,7 +1042,8 @@ int gt_weight_upload(gt_engine *e, int ggml_type, const void *host_bytes, int64_
         return fail(ce == cudaErrorMemoryAllocation ? GT_ERR_OOM : GT_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(ce));
     }
     if (ggml_type == GT_TYPE_F16) d.row_bytes = (int64_t)in_features * 2;
-    else if (ggml_type != GT_TYPE_F32 && in_features % 256 == 0) d.row_bytes = (int64_t)(in_features / 256) * dev_block_bytes(ggml_type);
+    else if ((ggml_type == GT_TYPE_Q4_K || ggml_type == GT_TYPE_Q6_K) && in_features % 256 == 0)
+        d.row_bytes = (int64_t)(in_features / 256) * dev_block_bytes(ggml_type);
     const char *msg = nullptr;
     if (umma_init_weight_maps(&d, &msg) != cudaSuccess) {
         gt_weight_free(w);

@@ -50,6 +50,8 @@ cudaError_t launch_dequant_rows(int qt, const uint8_t *w, int K, int64_t row0, i
     if (qt == kTypeQ4K) k_dequant_rows<kTypeQ4K><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     else if (qt == kTypeQ6K) k_dequant_rows<kTypeQ6K><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     else if (qt == kTypeF16) k_dequant_rows<kTypeF16><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
+    else if (qt == kTypeQ40) k_dequant_rows<kTypeQ40><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
+    else if (qt == kTypeQ80) k_dequant_rows<kTypeQ80><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     else k_dequant_rows<kTypeF32><<<blocks, threads, 0, s>>>(w, K, row0, nrows, out);
     return cudaGetLastError();
 }
@@ -172,6 +174,8 @@ cudaError_t launch_gemm_fp32_fwd(int qt, const uint8_t *w, const float *X, float
     if (qt == kTypeQ4K) k_gemm_fp32_fwd<kTypeQ4K><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     else if (qt == kTypeQ6K) k_gemm_fp32_fwd<kTypeQ6K><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     else if (qt == kTypeF16) k_gemm_fp32_fwd<kTypeF16><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
+    else if (qt == kTypeQ40) k_gemm_fp32_fwd<kTypeQ40><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
+    else if (qt == kTypeQ80) k_gemm_fp32_fwd<kTypeQ80><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     else k_gemm_fp32_fwd<kTypeF32><<<grid, 256, 0, s>>>(w, X, Y, residual, bias, T, N, K);
     return cudaGetLastError();
 }
@@ -181,6 +185,8 @@ cudaError_t launch_gemm_fp32_bwd(int qt, const uint8_t *w, const float *dY, floa
     if (qt == kTypeQ4K) k_gemm_fp32_bwd<kTypeQ4K><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     else if (qt == kTypeQ6K) k_gemm_fp32_bwd<kTypeQ6K><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     else if (qt == kTypeF16) k_gemm_fp32_bwd<kTypeF16><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
+    else if (qt == kTypeQ40) k_gemm_fp32_bwd<kTypeQ40><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
+    else if (qt == kTypeQ80) k_gemm_fp32_bwd<kTypeQ80><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     else k_gemm_fp32_bwd<kTypeF32><<<grid, 256, 0, s>>>(w, dY, dX, T, N, K);
     return cudaGetLastError();
 }

@@ -273,6 +273,8 @@ int embedding_on_device(gt_engine *e, const gt_weight *w, const int *tokens, int
     switch (wd.qtype) {
         case kTypeF16: k_embed_rows<kTypeF16><<<T, 256, 0, e->stream>>>(wd.data, wd.K, wd.N, tokens, out, bad_dev); break;
         case kTypeF32: k_embed_rows<kTypeF32><<<T, 256, 0, e->stream>>>(wd.data, wd.K, wd.N, tokens, out, bad_dev); break;
+        case kTypeQ40: k_embed_rows<kTypeQ40><<<T, 256, 0, e->stream>>>(wd.data, wd.K, wd.N, tokens, out, bad_dev); break;
+        case kTypeQ80: k_embed_rows<kTypeQ80><<<T, 256, 0, e->stream>>>(wd.data, wd.K, wd.N, tokens, out, bad_dev); break;
         case kTypeQ4K: k_embed_rows<kTypeQ4K><<<T, 256, 0, e->stream>>>(wd.data, wd.K, wd.N, tokens, out, bad_dev); break;
         case kTypeQ6K: k_embed_rows<kTypeQ6K><<<T, 256, 0, e->stream>>>(wd.data, wd.K, wd.N, tokens, out, bad_dev); break;
         default: return failf(GT_ERR_UNSUPPORTED, "embedding type %d is not supported", wd.qtype);

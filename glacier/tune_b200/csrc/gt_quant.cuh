@@ -20,11 +20,15 @@ namespace gt {
 
 constexpr int kTypeF32 = 0;
 constexpr int kTypeF16 = 1;       // plain fp16 rows (embedding and LM-head tensors)
+constexpr int kTypeQ40 = 2;       // 32 weights in 18 bytes: half d; u8 qs[16]   (exact CUDA-core kernels only)
+constexpr int kTypeQ80 = 8;       // 32 weights in 34 bytes: half d; i8 qs[32]   (exact CUDA-core kernels only)
 constexpr int kTypeQ4K = 12;
 constexpr int kTypeQ6K = 14;
 constexpr int kQ4KBlockBytes = 144;
 constexpr int kQ6KGgufBlockBytes = 210;
 constexpr int kQ6KDevBlockBytes = 224;
+constexpr int kQ40BlockBytes = 18;
+constexpr int kQ80BlockBytes = 34;
 
 __host__ __device__ constexpr int dev_block_bytes(int qt) {
     return qt == kTypeQ4K ? kQ4KBlockBytes : (qt == kTypeQ6K ? kQ6KDevBlockBytes : 0);
@@ -78,13 +82,29 @@ __device__ __forceinline__ float q6k_dev_decode_elem(const uint8_t *blk, int c) 
     const int sc = (int)(int8_t)blk[step * 8 + (lane >> 4) + quad * 2];
     return d * (float)sc * (float)q;
 }
-// Element e of the flat row-major element stream of a tensor (block = e / 256).
+// Q4_0 (src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:23-26,151-163): weight i of a block = d * (nibble - 8), nibble = low half
+// of qs[i] for i < 16, high half of qs[i - 16] otherwise.  Q8_0 (tune_bwd.cu:18-21,375-376): d * qs[i].  Blocks are 18 /
+// 34 bytes, so the fp16 scale sits at an even address only: it is read as two bytes.
+__device__ __forceinline__ float q40_decode_elem(const uint8_t *blk, int c) {
+    const float d = half_bits_to_f32((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
+    const int q = (int)((blk[2 + (c & 15)] >> ((c >> 4) << 2)) & 0x0F) - 8;
+    return d * (float)q;
+}
+__device__ __forceinline__ float q80_decode_elem(const uint8_t *blk, int c) {
+    const float d = half_bits_to_f32((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
+    return d * (float)(int8_t)blk[2 + c];
+}
+// Element e of the flat row-major element stream of a tensor (block = e / 256 for the K-quants, e / 32 for Q4_0 / Q8_0).
 template <int QT>
 __device__ __forceinline__ float decode_flat(const uint8_t *w, int64_t e) {
     if constexpr (QT == kTypeF32) {
         return ((const float *)w)[e];
     } else if constexpr (QT == kTypeF16) {
         return __half2float(((const __half *)w)[e]);
+    } else if constexpr (QT == kTypeQ40) {
+        return q40_decode_elem(w + (e >> 5) * kQ40BlockBytes, (int)(e & 31));
+    } else if constexpr (QT == kTypeQ80) {
+        return q80_decode_elem(w + (e >> 5) * kQ80BlockBytes, (int)(e & 31));
     } else if constexpr (QT == kTypeQ4K) {
         return q4k_decode_elem(w + (e >> 8) * kQ4KBlockBytes, (int)(e & 255));
     } else {

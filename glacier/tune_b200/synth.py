@@ -19,8 +19,8 @@ from __future__ import annotations
 
 import numpy as np
 
-TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
-BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q6_K: 210}
+TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 0, 2, 8, 12, 14
+BLOCK_BYTES = {TYPE_Q4_K: 144, TYPE_Q6_K: 210, TYPE_Q4_0: 18, TYPE_Q8_0: 34}
 PROJ_ORDINAL = {"q": 0, "k": 1, "v": 2, "o": 3, "gate": 4, "up": 5, "down": 6}
 
 # (out_features N, in_features K) of the Qwen2.5-7B layer projections
@@ -89,10 +89,30 @@ def make_q6k_blocks(nblocks: int, rng: np.random.Generator) -> np.ndarray:
     return out
 
 
+def make_q40_blocks(nblocks: int, rng: np.random.Generator) -> np.ndarray:
+    """[nblocks, 18] uint8: fp16 d, then 16 bytes of nibbles (weights 0-15 low, 16-31 high)."""
+    out = np.empty((nblocks, 18), np.uint8)
+    out[:, 0:2] = rng.uniform(2e-3, 2e-2, nblocks).astype(np.float16).view(np.uint8).reshape(nblocks, 2)
+    out[:, 2:18] = rng.integers(0, 256, (nblocks, 16), dtype=np.uint8)
+    return out
+
+
+def make_q80_blocks(nblocks: int, rng: np.random.Generator) -> np.ndarray:
+    """[nblocks, 34] uint8: fp16 d, then 32 int8."""
+    out = np.empty((nblocks, 34), np.uint8)
+    out[:, 0:2] = rng.uniform(1e-4, 1e-3, nblocks).astype(np.float16).view(np.uint8).reshape(nblocks, 2)
+    out[:, 2:34] = rng.integers(-127, 128, (nblocks, 32), dtype=np.int8).view(np.uint8)
+    return out
+
+
 def make_weight(qtype: int, N: int, K: int, seed: int) -> np.ndarray:
-    """Quantized [N, K] weight as a flat uint8 byte stream of N*K/256 super-blocks (row-major)."""
-    assert (N * K) % 256 == 0, "weight element count must be a whole number of super-blocks"
+    """Quantized [N, K] weight as a flat uint8 byte stream of N*K/256 super-blocks (row-major); Q4_0 / Q8_0: N*K/32
+    blocks, rows whole numbers of blocks."""
     rng = np.random.default_rng(seed)
+    if qtype in (TYPE_Q4_0, TYPE_Q8_0):
+        assert K % 32 == 0
+        return (make_q40_blocks(N * K // 32, rng) if qtype == TYPE_Q4_0 else make_q80_blocks(N * K // 32, rng)).reshape(-1)
+    assert (N * K) % 256 == 0, "weight element count must be a whole number of super-blocks"
     nb = N * K // 256
     blocks = make_q4k_blocks(nb, rng) if qtype == TYPE_Q4_K else make_q6k_blocks(nb, rng)
     return blocks.reshape(-1)

@@ -44,7 +44,7 @@ typedef struct gt_adapter gt_adapter;
 typedef struct gt_model gt_model;
 
 /* ggml tensor type ids, as in the reference's GgufType */
-enum { GT_TYPE_F32 = 0, GT_TYPE_F16 = 1, GT_TYPE_Q4_K = 12, GT_TYPE_Q6_K = 14 };
+enum { GT_TYPE_F32 = 0, GT_TYPE_F16 = 1, GT_TYPE_Q4_0 = 2, GT_TYPE_Q8_0 = 8, GT_TYPE_Q4_K = 12, GT_TYPE_Q6_K = 14 };
 
 enum gt_status {
     GT_OK = 0,
@@ -116,8 +116,10 @@ GT_API int gt_sync(gt_engine *eng);
 
 /* Replaces: SupportsForwardGemm / SupportsBackwardGemm
  * (src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:13-14, GpuLoraEngine.Backward.cs:12-13).  Returns 1 or 0.
- * Q4_K and Q6_K run on the tensor cores; F32 and F16 projections run on the exact fp32 CUDA-core kernels (F16 tensors
- * are meant for the embedding and the LM head, whose calls below use the tensor cores). */
+ * Q4_K and Q6_K run on the tensor cores; F32, F16, Q4_0 and Q8_0 projections (the reference's other types: gemm_q4_0_batch,
+ * gemm_q8_0_bwd, gemm_q4_0_bwd, src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:131-190,335-460) run on the exact fp32 CUDA-core
+ * kernels in every math mode (F16 tensors are meant for the embedding and the LM head, whose calls below use the tensor
+ * cores). */
 GT_API int gt_supports(int ggml_type, int direction);
 
 /* Replaces: UploadBaseWeights (src/Glacier.Tune/Gpu/GpuLoraEngine.cs:240-321) for one tensor, and the

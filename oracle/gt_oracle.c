@@ -48,6 +48,8 @@
 /* ggml type ids used by the reference's GgufType enum for the types on this path */
 #define GT_TYPE_F32 0
 #define GT_TYPE_F16 1
+#define GT_TYPE_Q4_0 2
+#define GT_TYPE_Q8_0 8
 #define GT_TYPE_Q4_K 12
 #define GT_TYPE_Q6_K 14
 
@@ -206,8 +208,26 @@ int64_t gt_oracle_block_bytes(int type) {
     return 0;
 }
 
-/* tensor types the row-wise routines accept: F32, F16 (plain rows) and the two K-quants */
-static int type_ok(int type) { return type == GT_TYPE_F32 || type == GT_TYPE_F16 || gt_oracle_block_bytes(type) != 0; }
+/* Q4_0 (src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:23-26,151-163): 32 weights in 18 bytes, half d then 16 bytes; weight i is
+ * d * (nibble - 8) with the low nibble of qs[i] for i < 16 and the high nibble of qs[i - 16] otherwise.
+ * Q8_0 (tune_bwd.cu:18-21,375-376): 32 weights in 34 bytes, half d then 32 int8; weight i is d * qs[i].
+ * The reference holds no test or fixture for either; both are pinned against gguf.quants.dequantize (tests/golden). */
+static void dequant_block_q40(const uint8_t *blk, float *dst) {
+    const float d = half_bits_to_float((uint16_t)(blk[0] | (blk[1] << 8)));
+    for (int i = 0; i < 32; i++) {
+        const int q = (int)((blk[2 + (i & 15)] >> ((i >> 4) << 2)) & 0x0F) - 8;
+        dst[i] = d * (float)q;
+    }
+}
+static void dequant_block_q80(const uint8_t *blk, float *dst) {
+    const float d = half_bits_to_float((uint16_t)(blk[0] | (blk[1] << 8)));
+    for (int i = 0; i < 32; i++) dst[i] = d * (float)(int8_t)blk[2 + i];
+}
+
+/* tensor types the row-wise routines accept: F32, F16 (plain rows), the two K-quants, Q4_0 and Q8_0 */
+static int type_ok(int type) {
+    return type == GT_TYPE_F32 || type == GT_TYPE_F16 || type == GT_TYPE_Q4_0 || type == GT_TYPE_Q8_0 || gt_oracle_block_bytes(type) != 0;
+}
 
 /* Dequantize `nblocks` consecutive super-blocks (a flat stream). */
 int gt_oracle_dequant_blocks(int type, const uint8_t *blocks, int64_t nblocks, float *dst) {
@@ -237,6 +257,15 @@ static void dequant_row(int type, const uint8_t *w, int64_t row, int K, float *d
     if (type == GT_TYPE_F16) {
         const uint16_t *h = (const uint16_t *)w + row * K;
         for (int k = 0; k < K; k++) dst[k] = half_bits_to_float(h[k]);
+        return;
+    }
+    if (type == GT_TYPE_Q4_0 || type == GT_TYPE_Q8_0) {      /* K % 32 == 0: rows are whole 32-weight blocks */
+        const int64_t b32 = type == GT_TYPE_Q4_0 ? 18 : 34;
+        const uint8_t *r = w + row * (int64_t)(K / 32) * b32;
+        for (int b = 0; b < K / 32; b++) {
+            if (type == GT_TYPE_Q4_0) dequant_block_q40(r + b * b32, dst + b * 32);
+            else dequant_block_q80(r + b * b32, dst + b * 32);
+        }
         return;
     }
     int64_t e0 = row * (int64_t)K;
@@ -781,7 +810,11 @@ float gt_oracle_cross_entropy(int type, const uint8_t *w, const float *hidden, c
         tlog[i] = 0.f;
     }
     memset(gh, 0, (size_t)nv * H * sizeof(float));
-    const int64_t row_bytes = type == GT_TYPE_F32 ? (int64_t)H * 4 : (type == GT_TYPE_F16 ? (int64_t)H * 2 : (int64_t)H / GT_QK_K * gt_oracle_block_bytes(type));
+    const int64_t row_bytes = type == GT_TYPE_F32   ? (int64_t)H * 4
+                              : type == GT_TYPE_F16 ? (int64_t)H * 2
+                              : type == GT_TYPE_Q4_0 ? (int64_t)H / 32 * 18
+                              : type == GT_TYPE_Q8_0 ? (int64_t)H / 32 * 34
+                                                     : (int64_t)H / GT_QK_K * gt_oracle_block_bytes(type);
     for (int tl = 0; tl < n_tiles; tl++) {
         const int v0 = tl * tile, vc = V - v0 < tile ? V - v0 : tile;
         gt_oracle_matmul_batch(type, w + (int64_t)v0 * row_bytes, xh, lg, H, vc, nv, NULL);

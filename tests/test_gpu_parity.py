@@ -138,6 +138,31 @@ STREAM_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("mode", [0, 2])
+@pytest.mark.parametrize("qtype", [S.TYPE_Q4_0, S.TYPE_Q8_0])
+def test_q40_q80_projections_on_the_exact_kernels(G, eng, oracle, qtype, mode):
+    """The reference engine's other GEMM types (gemm_q4_0_batch, gemm_q8_0_bwd, gemm_q4_0_bwd,
+    src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:131-190,335-460): rows decode bit for bit, and Y, dX, dA, dB agree with the
+    fp64 oracle - to fp32 accuracy in the fp32 mode; in the bf16 mode the base products still run on the exact CUDA-core
+    kernels and only the adapter products are bf16 warp MMAs."""
+    N, K, T = 96, 320, 37
+    assert G.load_library().gt_supports(qtype, 0) == 1 and G.load_library().gt_supports(qtype, 1) == 1
+    c = S.make_projection_case(qtype, N, K, T, seed=N + K + qtype, with_bias=True)
+    eng.set_math_mode(mode)
+    w = eng.upload_weight(qtype, c["w"], N, K)
+    got = eng.dequant_rows(w, 0, N)
+    want = oracle.dequant_rows(qtype, c["w"], K, 0, N)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    w.free()
+    y_ref, dx_ref, da_ref, db_ref = _reference(oracle, c)
+    y, dx, da, db = _run(G, eng, c, mode)
+    tol_base, tol_lora = (1e-5, 1e-5) if mode == 2 else (2e-3, LTOL[0])
+    for a, b, tol in ((y, y_ref, tol_base), (dx, dx_ref, tol_base), (da, da_ref, tol_lora), (db, db_ref, tol_lora)):
+        assert oracle.rel_fro(a, b) < tol, oracle.rel_fro(a, b)
+    with pytest.raises(G.GtError):
+        eng.upload_weight(qtype, c["w"][:-1], N, K)            # byte size must match the shape
+
+
 FEW_SHAPES = [
     # up to 64 tokens: Q4_K runs on the tensor-core kernel with the weights on the wide operand, Q6_K on the 128-token
     # variant of the main kernel; both directions.  (qtype, N, K, T): one row tile and several, a last tile of 256 rows

@@ -209,6 +209,47 @@ def test_decoders_match_gguf_golden_fixture(oracle):
         assert np.array_equal(got_np.view(np.uint32), want.view(np.uint32)), key
 
 
+def test_q40_q80_decoders_match_gguf_golden_fixture(oracle):
+    """Q4_0 and Q8_0 (the reference's other GEMM types, src/Glacier.Tune/Gpu/Kernels/tune_bwd.cu:18-26): the C oracle's row
+    decoder against vectors produced by gguf.quants.dequantize, bit for bit; and against the generator when gguf is here."""
+    d = np.load(os.path.join(GOLDEN, "gguf_dequant_golden_q40_q80.npz"))
+    for qtype, key in ((S.TYPE_Q4_0, "q40"), (S.TYPE_Q8_0, "q80")):
+        blocks, want = d[f"{key}_blocks"], d[f"{key}_weights"]
+        nb = len(blocks)
+        K = 256                                    # rows of 8 blocks
+        got = oracle.dequant_rows(qtype, blocks.reshape(-1), K, 0, nb * 32 // K)
+        assert np.array_equal(got.reshape(-1).view(np.uint32), want.reshape(-1).view(np.uint32)), key
+    try:
+        import gguf  # noqa: F401
+    except ImportError:
+        return
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("make_gguf_golden", os.path.join(root, "tests", "golden", "make_gguf_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    q40, q80 = gen.draw_small_blocks()
+    w40, w80 = gen.gguf_decode_small(q40, q80)
+    assert np.array_equal(q40, d["q40_blocks"]) and np.array_equal(q80, d["q80_blocks"])
+    assert np.array_equal(w40.view(np.uint32), d["q40_weights"].view(np.uint32))
+    assert np.array_equal(w80.view(np.uint32), d["q80_weights"].view(np.uint32))
+
+
+def test_q40_q80_projection_oracle_matches_dense_numpy(oracle):
+    """Forward and backward of the CPU path on Q4_0 / Q8_0 weights against a dense fp64 product of the decoded rows."""
+    rng = np.random.default_rng(3)
+    N, K, T = 48, 96, 7
+    for qtype in (S.TYPE_Q4_0, S.TYPE_Q8_0):
+        w = S.make_weight(qtype, N, K, seed=11)
+        W = oracle.dequant_rows(qtype, w, K, 0, N).astype(np.float64)
+        x = rng.standard_normal((T, K), dtype=np.float32)
+        dy = rng.standard_normal((T, N), dtype=np.float32)
+        y = oracle.matmul_batch(qtype, w, x, K, N, T, None, f64=True)
+        assert np.allclose(y, x.astype(np.float64) @ W.T, rtol=1e-12, atol=1e-12)
+        dx = oracle.base_backward_f64(qtype, w, dy, K, N, T)
+        assert np.allclose(dx, dy.astype(np.float64) @ W, rtol=1e-12, atol=1e-12)
+
+
 def test_decoders_match_gguf_package_live(oracle):
     """The same comparison against the installed gguf package on fresh seeded blocks (skipped where it is absent),
     and a check that the committed fixture is what the generator script writes today."""
