@@ -630,6 +630,17 @@ int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *cons
     int rc = forward_group_device(e, 2, w, ad, Xd, gu, T, flags);
     if (rc != GT_OK) return rc;
     float *yd = Yd;
+    if (!Yd) {
+        // activation only (the recomputed forward of a checkpointed block: the down projection's output is the stored
+        // input of the next block, nobody reads it again); X*A of the down adapter, kept from the first forward, stays valid
+        if (fold) {
+            if (!hidden16) return GT_OK;      // nowhere to keep the product
+            GT_LAUNCH(e, launch_swiglu_fwd16(bufs[0], bufs[1], bufs[2], hidden16, (int64_t)T * F, 0, e->sm_count, e->stream));
+        } else {
+            GT_LAUNCH(e, launch_swiglu_fwd(bufs[0], bufs[1], bufs[2], (int64_t)T * F, e->sm_count, e->stream));
+        }
+        return GT_OK;
+    }
     if (fold) {
         // SiLU(gate) * up goes out as the bf16 operand of the down projection (and as fp32 only if asked for): the separate
         // pass that would read the fp32 product back to round it does not run

@@ -72,7 +72,8 @@ int check_ready(const gt_model *m, const char *who) {
 // One block forward on the engine stream; s receives the state.  n1_ready: s.n1 already holds RMSNorm(x_in) (the block
 // before wrote it together with its output).  next_norm / next_n1 (may be null): the norm weight and destination of
 // the norm that follows this block's output - the next block's attention norm or the model's output norm - computed
-// in the same pass as the residual add.
+// in the same pass as the residual add.  x_out == nullptr: the state only (the recomputed forward of a checkpointed block) -
+// the down projection and the residual add after it are left out, their result is the stored input of the next block.
 int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockState &s, int T, bool n1_ready, const float *next_norm,
                   float *next_n1) {
     gt_engine *e = m->eng;
@@ -94,8 +95,9 @@ int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockStat
     gt_adapter *fa[3] = {L.ad[kGate], L.ad[kUp], L.ad[kDown]};
     // SiLU(gate) * up is kept as bf16 only where the engine can work from that (the buffer is sized for fp32 either way)
     const bool h16 = ffn_hidden16_ok(e, fw, T);
-    rc = ffn_forward_device(e, fw, fa, s.n2, s.gate, s.up, h16 ? nullptr : s.hidden, m->tmp_h, T, 0, h16 ? (void *)s.hidden : nullptr);
-    if (rc != GT_OK) return rc;
+    rc = ffn_forward_device(e, fw, fa, s.n2, s.gate, s.up, h16 ? nullptr : s.hidden, x_out ? m->tmp_h : nullptr, T, 0,
+                            h16 ? (void *)s.hidden : nullptr);
+    if (rc != GT_OK || !x_out) return rc;
     if (next_norm && next_n1) GT_LAUNCH(e, launch_add_rmsnorm_fwd(s.x1, m->tmp_h, next_norm, x_out, next_n1, T, H, c.rms_eps, e->stream));
     else GT_LAUNCH(e, launch_add(s.x1, m->tmp_h, x_out, (int64_t)T * H, e->sm_count, e->stream));
     return GT_OK;
@@ -388,8 +390,8 @@ int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t 
     const float inv_world = 1.0f / (float)e->dp_world;
     for (int l = L - 1; l >= 0; l--) {
         BlockState &s = m->st[ckpt ? 0 : l];
-        if (ckpt) {      // recompute this block's forward into the one state set (its output lands in tmp space, unused)
-            rc = block_forward(m, l, m->x[l], m->dfnorm, s, T, false, nullptr, nullptr);
+        if (ckpt) {      // recompute this block's state into the one state set (not its output: that is x[l + 1], still there)
+            rc = block_forward(m, l, m->x[l], nullptr, s, T, false, nullptr, nullptr);
             if (rc != GT_OK) return rc;
         }
         rc = block_backward(m, l, d_cur, m->x[l], s, d_next, T);
