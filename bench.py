@@ -569,7 +569,9 @@ def run_ours(args) -> None:
 # ------------------------------------------------------------------------------------------------ 28-layer training step
 STEP_WORKLOAD = ("qwen2.5-7b-architecture LoRA training step: 28 layers, hidden 3584, 28/4 heads x 128, FFN 18944, vocab 152064, "
                  "Q4_K_M-mixed base (v, down in Q6_K), fp16 embedding and LM head, r=16 on q,k,v,o,gate,up,down, one 512-token "
-                 "sequence per GPU, activation checkpointing, streaming cross-entropy, clip 1.0, AdamW lr 2e-4")
+                 "sequence per GPU, activation checkpointing (block inputs kept; each block's state is recomputed before its "
+                 "backward, up to but not including the down projection, whose output is the next block's kept input), "
+                 "streaming cross-entropy, clip 1.0, AdamW lr 2e-4")
 STEP_CFG = dict(n_layers=28, hidden=3584, n_heads=28, n_kv_heads=4, head_dim=128, ffn=18944, vocab=152064)
 ADAMW = dict(lr=2e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
 
