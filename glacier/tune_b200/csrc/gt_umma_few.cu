@@ -89,7 +89,6 @@ struct FewParams {
     int row_base, ld_out;
     int units, splits;                  // raw stages along the contraction, K splits
     int atomic_out;
-    int debug;                          // timing experiments only (wrong results): 1 = skip the dequant arithmetic, 2 = skip the MMAs
 };
 
 enum { kFewProducer = 600, kFewMma = 700, kFewDequant = 800, kFewEpilogue = 900 };
@@ -229,10 +228,8 @@ __global__ void __launch_bounds__(kThreadsF, 1) k_umma_few(const __grid_constant
                 // this issuer's half of the activation tile: k-steps 2 who, 2 who + 1 of its 128-byte rows
                 const uint32_t a_lo = (((sbase + kOffXf + xi * kXSlotBytes) & 0x3FFFFu) >> 4) + (uint32_t)(who * 4) | (1u << 16);
                 const uint32_t b_lo = (((sbase + kOffWf + si * kWSlotBytes) & 0x3FFFFu) >> 4) | kBLoField;
-                if (p.debug != 2) {
-                    umma_f16_ss_lohi<false>(d_tmem, a_lo, kHi128, b_lo, kBHi, idesc, n == who ? 0u : 1u);
-                    umma_f16_ss_lohi<false>(d_tmem, a_lo + 2, kHi128, b_lo + kBStep, kBHi, idesc, 1u);
-                }
+                umma_f16_ss_lohi<false>(d_tmem, a_lo, kHi128, b_lo, kBHi, idesc, n == who ? 0u : 1u);
+                umma_f16_ss_lohi<false>(d_tmem, a_lo + 2, kHi128, b_lo + kBStep, kBHi, idesc, 1u);
                 umma_commit(bar(kBEmpty + si));
                 umma_commit(bar(kBXEmpty + xi));
                 if (who == 0) trace(9, n >> 1);
@@ -275,7 +272,6 @@ __global__ void __launch_bounds__(kThreadsF, 1) k_umma_few(const __grid_constant
                     ok = wait_slot(n) && wait_slot(n + 1);
                     if (!ok) break;
                     if (dt == 0 && g2 == 0) trace(3, 2 * ui + pp);
-                    if (p.debug != 1)
 #pragma unroll
                     for (int e = 0; e < 2; e++)
                         dequant32_to_swizzled_row<QT, T16>(rr + QS::hdr_x(half), rr + QS::q0_x(half), rr + QS::q1_x(half), 0, 0, half,
@@ -302,7 +298,6 @@ __global__ void __launch_bounds__(kThreadsF, 1) k_umma_few(const __grid_constant
                 if (dt == 0 && g2 == 0) trace(3, ui >> 1);
                 const uint8_t *rr = smem + kOffRawF + ri * kRawStageBytes + row * BB;
                 const uint32_t w_addr = w_slot(n + st) + (uint32_t)(j * 4096 + r * 128);
-                if (p.debug != 1)
 #pragma unroll
                 for (int e = 0; e < 2; e++)
                     dequant32_to_swizzled_row<QT, T16>(rr + QS::hdr_x(hb), rr + QS::q0_x(hb), rr + QS::q1_x(hb), 0, 0, hb, 2 * (j & 1) + e,
@@ -465,8 +460,6 @@ cudaError_t launch_umma_few(const UmmaLaunch &L, cudaStream_t s, const char **er
     p.bias = L.bias;
     p.status = L.status;
     p.trace = (long long *)L.trace;
-    static const int debug = getenv("GT_FEW_DEBUG") ? atoi(getenv("GT_FEW_DEBUG")) : 0;
-    p.debug = debug;
     p.T = L.T;
     p.K = w->K;
     p.N = rows;

@@ -956,6 +956,10 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
             const UmmaLaunch &L = m[j];
             if (L.rank <= 0 || !L.lora_act || !L.lora_w) continue;
             const int rows = eff_rows(L);
+            if (L.ld_out != (bwd ? L.w->K : rows)) {      // the rank-r kernels take dense outputs
+                if (err) *err = "few-token launch with an adapter needs a dense output tensor";
+                return cudaErrorInvalidValue;
+            }
             cudaError_t ce = bwd ? launch_lora_dx_fp32(L.lora_act, L.lora_w, L.out, L.lora_scale, L.T, L.w->K, L.rank, s)
                                  : launch_lora_delta_fp32(L.lora_act, L.lora_w, L.out, nullptr, L.T, rows, L.rank, L.lora_scale, L.lora_flag, s);
             if (ce != cudaSuccess) return ce;
