@@ -154,3 +154,35 @@ def test_q6k_down_projection_fp16_mode_m512(G, eng, oracle, layer_mix):
                 dA=oracle.rel_fro(da, da_ref), dB=oracle.rel_fro(db, db_ref))
     assert all(v < 1e-3 for v in errs.values()), errs
     eng.set_math_mode(0)
+
+
+@pytest.mark.parametrize("M", [8, 16, 64, 128, 256, 512])
+def test_repeated_layer_calls_stay_consistent(G, eng, layer_mix, M):
+    """Every group of the Q4_K_M layer, forward and backward, 12 times over on the same inputs: no call may report a
+    kernel error and every repetition must reproduce the first one to within what the order of fp32 atomic additions
+    and bf16 roundings of the adapter products can move (1e-3 here; a stage overwritten while it is still read, a missed
+    barrier phase or two launches racing on one output show up as errors of percent size, in one run out of several)."""
+    import torch
+    eng.set_math_mode(0)
+    rng = np.random.default_rng(4242 + M)
+    for names in GROUPS:
+        ps = [layer_mix[n] for n in names]
+        K = ps[0]["K"]
+        X = torch.from_numpy(S.bf16_round(rng.standard_normal((M, K), dtype=np.float32))).cuda()
+        dYs = [torch.from_numpy(rng.standard_normal((M, p["N"]), dtype=np.float32)).cuda() for p in ps]
+        first = None
+        for rep in range(12):
+            Ys = [torch.empty((M, p["N"]), dtype=torch.float32, device="cuda") for p in ps]
+            dX = torch.full((M, K), 3.0, dtype=torch.float32, device="cuda")
+            for p in ps:
+                p["ad"].zero_grads()
+            eng.forward_group([p["wh"] for p in ps], [p["ad"] for p in ps], X, Ys)
+            eng.backward_group([p["wh"] for p in ps], [p["ad"] for p in ps], dYs, X, dX, flags=G.FLAG_REUSE_LOW | G.FLAG_DX_ASSIGN)
+            eng.sync()
+            out = [y.clone() for y in Ys] + [dX]
+            if first is None:
+                first = out
+                continue
+            for a, b in zip(out, first):
+                err = float(torch.linalg.norm(a - b) / torch.linalg.norm(b))
+                assert err < 1e-3, (names, M, rep, err)
