@@ -100,7 +100,39 @@ __device__ __forceinline__ void load_tile(const float *__restrict__ src, int64_t
     }
 }
 
+// Two tiles at once (key and value tile of one step): all loads are issued before the first is used, one round trip.
+template <typename T16, int NT>
+__device__ __forceinline__ void load_tile_pair(const float *__restrict__ a, const float *__restrict__ b, int64_t ld, int col0, int t0, int T,
+                                               uint8_t *dst_a, uint8_t *dst_b, int tid) {
+    constexpr int NI = (64 * D / 4) / NT;
+    float4 va[NI], vb[NI];
+#pragma unroll
+    for (int i = 0; i < NI; i++) {
+        const int idx = tid + i * NT;
+        const int r = idx >> 5, c = (idx & 31) * 4;
+        const int t = t0 + r;
+        va[i] = vb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < T) {
+            va[i] = __ldg(reinterpret_cast<const float4 *>(a + (int64_t)t * ld + col0 + c));
+            vb[i] = __ldg(reinterpret_cast<const float4 *>(b + (int64_t)t * ld + col0 + c));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NI; i++) {
+        const int idx = tid + i * NT;
+        const int r = idx >> 5, c = (idx & 31) * 4;
+        *reinterpret_cast<uint2 *>(dst_a + r * SD + c * 2) = make_uint2(pk<T16>(va[i].x, va[i].y), pk<T16>(va[i].z, va[i].w));
+        *reinterpret_cast<uint2 *>(dst_b + r * SD + c * 2) = make_uint2(pk<T16>(vb[i].x, vb[i].y), pk<T16>(vb[i].z, vb[i].w));
+    }
+}
+
 constexpr float kLog2e = 1.4426950408889634f;
+// 2^x on the special-function unit (2 ulp; 2^-inf = 0): the probabilities are rounded to 16 bits right after
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // ------------------------------------------------------------------------------------------------ forward
 // 8 warps: warps 0-3 compute (16 queries each), warps 4-7 fetch - while the compute warps work on key tile j out of one
@@ -147,10 +179,7 @@ __global__ void __launch_bounds__(256) k_attn_fwd(const float *__restrict__ q, c
         for (int jt = 0; jt <= it; jt++) {
             const int k0 = jt * BK;
             if (!compute) {
-                if (jt + 1 <= it) {
-                    load_tile<T16, 128>(k, ldk, kh * D, k0 + BK, T, 1.f, kbuf((jt + 1) & 1), tid - 128);
-                    load_tile<T16, 128>(v, ldk, kh * D, k0 + BK, T, 1.f, vbuf((jt + 1) & 1), tid - 128);
-                }
+                if (jt + 1 <= it) load_tile_pair<T16, 128>(k, v, ldk, kh * D, k0 + BK, T, kbuf((jt + 1) & 1), vbuf((jt + 1) & 1), tid - 128);
             } else {
                 const uint32_t ks = smem_u32(kbuf(jt & 1)), vs = smem_u32(vbuf(jt & 1));
                 float s[BK / 8][4];
@@ -166,33 +195,40 @@ __global__ void __launch_bounds__(256) k_attn_fwd(const float *__restrict__ q, c
                         mma16<T16>(s[n + 1], qf[kk], b[2], b[3]);
                     }
                 }
-                // causal mask (only the diagonal tile has masked entries) and keys beyond T
+                // causal mask: only the diagonal tile has masked entries; keys beyond T only in the last tile
+                if (jt == it || k0 + BK > T) {
+#pragma unroll
+                    for (int n = 0; n < BK / 8; n++) {
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const int key = k0 + n * 8 + 2 * t4 + (c & 1);
+                            if (key > row[c >> 1] || key >= T) s[n][c] = -INFINITY;
+                        }
+                    }
+                }
                 float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
                 for (int n = 0; n < BK / 8; n++) {
-#pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        const int key = k0 + n * 8 + 2 * t4 + (c & 1);
-                        const int r = c >> 1;
-                        if (key > row[r] || key >= T) s[n][c] = -INFINITY;
-                        mx[r] = fmaxf(mx[r], s[n][c]);
-                    }
+                    mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+                    mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
                 }
                 float corr[2];
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                    const float mn = fmaxf(m[r], mx[r]);
-                    corr[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - mn);
+                    // a finite floor keeps (-inf) - (-inf) out of the exponent (a row sees key 0 from the first tile on,
+                    // so its maximum is finite anyway)
+                    const float mn = fmaxf(fmaxf(m[r], mx[r]), -3.0e38f);
+                    corr[r] = ex2(m[r] - mn);
                     m[r] = mn;
                 }
                 float ps[2] = {0.f, 0.f};
                 uint32_t pf[BK / 16][4];
 #pragma unroll
                 for (int n = 0; n < BK / 8; n++) {
-                    const float p0 = m[0] == -INFINITY ? 0.f : exp2f(s[n][0] - m[0]), p1 = m[0] == -INFINITY ? 0.f : exp2f(s[n][1] - m[0]);
-                    const float p2 = m[1] == -INFINITY ? 0.f : exp2f(s[n][2] - m[1]), p3 = m[1] == -INFINITY ? 0.f : exp2f(s[n][3] - m[1]);
+                    const float p0 = ex2(s[n][0] - m[0]), p1 = ex2(s[n][1] - m[0]);
+                    const float p2 = ex2(s[n][2] - m[1]), p3 = ex2(s[n][3] - m[1]);
                     ps[0] += p0 + p1;
                     ps[1] += p2 + p3;
                     pf[n >> 1][(n & 1) * 2] = pk<T16>(p0, p1);
@@ -200,12 +236,15 @@ __global__ void __launch_bounds__(256) k_attn_fwd(const float *__restrict__ q, c
                 }
 #pragma unroll
                 for (int r = 0; r < 2; r++) l[r] = l[r] * corr[r] + ps[r];
+                // the running maxima move in the first tiles and then rarely: rescale the accumulator only when one did
+                if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-                for (int n = 0; n < D / 8; n++) {
-                    o[n][0] *= corr[0];
-                    o[n][1] *= corr[0];
-                    o[n][2] *= corr[1];
-                    o[n][3] *= corr[1];
+                    for (int n = 0; n < D / 8; n++) {
+                        o[n][0] *= corr[0];
+                        o[n][1] *= corr[0];
+                        o[n][2] *= corr[1];
+                        o[n][3] *= corr[1];
+                    }
                 }
 #pragma unroll
                 for (int kk = 0; kk < BK / 16; kk++) {
@@ -295,7 +334,7 @@ __device__ __forceinline__ void bwd_scores(uint32_t qs, uint32_t ks, uint32_t vs
             for (int c = 0; c < 2; c++) {
                 const int key = k0 + nh + n * 8 + 2 * t4 + c;
                 const bool ok = q_ok && key <= qi && key < T;
-                p[c] = ok ? exp2f(s[n][2 * r + c] - ls) : 0.f;
+                p[c] = ok ? ex2(s[n][2 * r + c] - ls) : 0.f;
                 ds[c] = ok ? p[c] * (dp[n][2 * r + c] - dl) * scale : 0.f;
             }
             const int off = (m0 + g + 8 * r) * SP + (nh + n * 8 + 2 * t4) * 2;
