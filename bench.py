@@ -499,7 +499,7 @@ def run_ours(args) -> None:
                 dist.all_reduce(t_, op=dist.ReduceOp.MAX)
             return float(t_.item())
         try:
-            train = run_train_step(G, eng, dev, stream, world, rank, args.train_steps, 2, args.train_layers, barrier, _max)
+            train = run_train_step(G, eng, dev, stream, world, rank, args.train_steps, 3, args.train_layers, barrier, _max)
         except Exception as exc:  # noqa: BLE001 - the headline line must still print; the failure is reported in it
             train = {"error": f"{type(exc).__name__}: {exc}"}
         _log(f"train step {train}")
@@ -670,6 +670,7 @@ def run_train_step(G, eng, dev, stream, world: int, rank: int, steps: int, warmu
     barrier()
     eng.sync()
     ms = allreduce_max(sum(x.elapsed_time(y) for x, y in zip(a, b)))
+    graph_info = model.step_info()      # the timed steps were replays of the captured step (all but the first two calls)
     # share of the tensor-core GEMMs (projections and LM head), one eager step with events around each launch
     eng.profile_read(reset=True)
     eng.profile_enable(True)
@@ -698,9 +699,9 @@ def run_train_step(G, eng, dev, stream, world: int, rank: int, steps: int, warmu
         model.close()
         model = None
         m2, _, _, _ = build_step_model(G, eng, dev, n_layers, rank, T, checkpoint=False, reuse=(keep, heads))
-        for i in range(2):
+        for i in range(3):
             m2.forward_backward(tok_d, lab_d, loss_dev=losses[total:total + 1])
-            m2.optimizer_step(step=100 + i, max_norm=1.0, **ADAMW)
+            m2.optimizer_step(step=99 + i, max_norm=1.0, **ADAMW)
         eng.sync()
         barrier()
         n2 = max(3, steps // 2)
@@ -727,6 +728,8 @@ def run_train_step(G, eng, dev, stream, world: int, rank: int, steps: int, warmu
         "gemm_ms_per_step": prof["gemm_ms"], "gemm_launches_per_step": prof["gemm_launches"],
         "gemm_tflops": prof["gemm_flops"] / (prof["gemm_ms"] * 1e-3) / 1e12 if prof["gemm_ms"] > 0 else 0.0,
         "kernel_launches_per_step": prof["kernel_launches"],
+        "cuda_graph": {"timed_steps_replayed": bool(graph_info["graph_ready"] and graph_info["replays"] >= steps),
+                       "kernels_per_replay": graph_info["kernels_per_replay"]},
         "lora_parameters": n_grads, "gradient_exchange": ("per-block ncclAllReduce(avg) on a side stream, last block first" if world > 1 else "none"),
         "loss_first_steps": ls[:10], "loss_finite": bool(np.all(np.isfinite(ls))),
         "e2e": {"tokens_per_s": world * T * e2e_n / e2e_s, "ms_per_step": 1e3 * e2e_s / e2e_n, "steps": e2e_n,

@@ -23,7 +23,7 @@ EXPORTS = [
     "gt_supports", "gt_weight_upload", "gt_weight_free", "gt_dequant_rows", "gt_adapter_create", "gt_adapter_free",
     "gt_adapter_upload", "gt_adapter_download", "gt_adapter_grads_download", "gt_adapter_grads_zero",
     "gt_adapter_set_alpha", "gt_adapter_device_ptrs", "gt_adapter_params_changed", "gt_adapter_bind_grads", "gt_proj_forward", "gt_proj_backward", "gt_proj_forward_group", "gt_proj_backward_group", "gt_stream_max_tokens", "gt_ffn_forward", "gt_ffn_backward", "gt_swiglu_forward", "gt_swiglu_backward", "gt_rope", "gt_rmsnorm_forward",
-    "gt_rmsnorm_backward", "gt_add", "gt_lm_head_loss", "gt_lm_head_logits", "gt_embedding_forward", "gt_attention_forward", "gt_attention_backward", "gt_supports_attention", "gt_model_create", "gt_model_destroy", "gt_model_set_block", "gt_model_set_head", "gt_model_bind_grads", "gt_model_loss", "gt_model_forward_backward", "gt_model_optimizer_step",
+    "gt_rmsnorm_backward", "gt_add", "gt_lm_head_loss", "gt_lm_head_logits", "gt_embedding_forward", "gt_attention_forward", "gt_attention_backward", "gt_supports_attention", "gt_model_create", "gt_model_destroy", "gt_model_set_block", "gt_model_set_head", "gt_model_bind_grads", "gt_model_loss", "gt_model_forward_backward", "gt_model_step_info", "gt_model_optimizer_step",
     "gt_launch_gemm_batch", "gt_launch_gemm_bwd", "gt_launch_gemm_bwd_static", "gt_grads_scale_clip",
     "gt_adamw_step", "gt_adapter_adamw_step", "gt_adapters_adamw_step",
     "gt_profile_enable", "gt_profile_read", "gt_debug_set_trace", "gt_debug_wait_selftest", "gt_dp_init", "gt_dp_allreduce", "gt_dp_allreduce_begin", "gt_dp_allreduce_end", "gt_dp_finalize", "gt_dp_unique_id",
@@ -39,7 +39,7 @@ class GtError(RuntimeError):
 class GtModelConfig(C.Structure):
     _fields_ = [("n_layers", C.c_int32), ("hidden", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
                 ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32), ("rms_eps", C.c_float), ("rope_theta", C.c_float),
-                ("max_tokens", C.c_int32), ("checkpoint", C.c_int32), ("reserved", C.c_int32 * 4)]
+                ("max_tokens", C.c_int32), ("checkpoint", C.c_int32), ("no_graph", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 class GtConfig(C.Structure):
@@ -110,6 +110,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.gt_model_bind_grads.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int64)]
     lib.gt_model_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32]
     lib.gt_model_forward_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]
+    lib.gt_model_step_info.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     lib.gt_model_optimizer_step.argtypes = [C.c_void_p] + [C.c_float] * 6 + [C.c_double, C.c_int32, C.POINTER(C.c_double)]
     lib.gt_launch_gemm_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
     lib.gt_launch_gemm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
@@ -505,10 +506,11 @@ class Model:
     "norm2": fp32 [hidden]} in the order q, k, v, o, gate, up, down."""
 
     def __init__(self, eng: Engine, n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_tokens, rms_eps=1e-6,
-                 rope_theta=1e6, checkpoint=True):
+                 rope_theta=1e6, checkpoint=True, graph=True):
         self.eng = eng
         cfg = GtModelConfig(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, ffn=ffn,
-                            vocab=vocab, rms_eps=rms_eps, rope_theta=rope_theta, max_tokens=max_tokens, checkpoint=1 if checkpoint else 0)
+                            vocab=vocab, rms_eps=rms_eps, rope_theta=rope_theta, max_tokens=max_tokens, checkpoint=1 if checkpoint else 0,
+                            no_graph=0 if graph else 1)
         h = C.c_void_p()
         _check(eng.lib.gt_model_create(eng.h, C.byref(cfg), C.byref(h)))
         self.h = h
@@ -553,6 +555,12 @@ class Model:
         _check(self.eng.lib.gt_model_forward_backward(self.h, _ptr(tokens)[0], _ptr(labels)[0], tokens.shape[0],
                                                       C.cast(C.byref(loss), C.c_void_p), 0))
         return loss.value
+
+    def step_info(self) -> dict:
+        """Whether a captured step stands ready, how many calls were replays, kernels per replay."""
+        ready, n, k = C.c_int32(), C.c_int64(), C.c_int64()
+        _check(self.eng.lib.gt_model_step_info(self.h, C.byref(ready), C.byref(n), C.byref(k)))
+        return {"graph_ready": bool(ready.value), "replays": n.value, "kernels_per_replay": k.value}
 
     def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, grad_scale=1.0, max_norm=1.0, step=1,
                        want_norm=False):

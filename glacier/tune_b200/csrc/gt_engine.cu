@@ -1290,6 +1290,7 @@ int gt_adapter_bind_grads(gt_adapter *a, float *dA_dev, float *dB_dev) {
         if (a->dB) cudaFree(a->dB);
     }
     a->own_grads = false;
+    gt::layout_generation().fetch_add(1);
     a->dA = dA_dev;
     a->dB = dB_dev;
     return GT_OK;
@@ -1543,6 +1544,7 @@ int gt_dp_init(gt_engine *e, int32_t world, int32_t rank, const void *unique_id,
     }
     e->dp_world = world;
     e->dp_rank = rank;
+    drop_step_graphs(e);
     return GT_OK;
 }
 
@@ -1614,6 +1616,7 @@ int gt_dp_finalize(gt_engine *e) {
         cudaSetDevice(e->device);
         cudaStreamSynchronize(e->stream);
         if (e->s_comm) cudaStreamSynchronize(e->s_comm);
+        drop_step_graphs(e);
         nccl_api().CommDestroy(e->comm);
         e->comm = nullptr;
     }

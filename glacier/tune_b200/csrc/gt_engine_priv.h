@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <nccl.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -36,11 +37,19 @@ void logf(int level, const char *fmt, ...);
 namespace gt {
 // grow-only device buffer (the reference engine grows its scratch x2 on demand and never shrinks:
 // src/Glacier.Tune/Gpu/GpuLoraEngine.Memory.cs:7-114)
+// Counts every event that moves a device buffer the library's kernels are pointed at (a scratch buffer that grew, an
+// adapter whose gradient accumulators were rebound): a captured CUDA graph of a step is only replayed while the
+// count it was captured under still stands.
+inline std::atomic<uint64_t> &layout_generation() {
+    static std::atomic<uint64_t> g{0};
+    return g;
+}
 struct Scratch {
     void *p = nullptr;
     size_t cap = 0;
     cudaError_t reserve(size_t bytes) {
         if (bytes <= cap) return cudaSuccess;
+        layout_generation().fetch_add(1);
         if (p) cudaFree(p);
         p = nullptr;
         cap = 0;
@@ -50,6 +59,7 @@ struct Scratch {
         return e;
     }
     void release() {
+        if (p) layout_generation().fetch_add(1);
         if (p) cudaFree(p);
         p = nullptr;
         cap = 0;
@@ -104,6 +114,7 @@ struct gt_engine {
     double gemm_flops = 0.0;
     int64_t gemm_launches = 0, kernel_launches = 0;
     void *trace = nullptr;       // device timeline buffer handed to the next GEMM launches (gt_debug_set_trace)
+    std::vector<gt_model *> models;      // models that may hold a captured step of this engine (see gt_model.cu)
 };
 
 struct gt_weight {
@@ -155,6 +166,8 @@ int ffn_backward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *con
                         const void *hidden16 = nullptr);
 int join_comm(gt_engine *e);
 int allreduce_begin_locked(gt_engine *e, float *g_dev, int64_t count, float scale);
+// forget the captured step of every model of this engine (before the communicator its collectives belong to goes away)
+void drop_step_graphs(gt_engine *e);
 // LM head and embedding on device tensors (gt_lmhead.cu); loss_dev / valid_dev are device scalars (may be null)
 int lm_head_loss_on_device(gt_engine *e, const gt_weight *w, const float *hidden, const int *labels, int T, float *loss_dev, int *valid_dev,
                            float *d_hidden);

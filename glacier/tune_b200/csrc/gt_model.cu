@@ -55,11 +55,33 @@ struct gt_model {
     float *grads = nullptr;            // flat gradient buffer (reference parameter order), or null until bound
     int64_t n_grads = 0;
     std::vector<gt_adapter *> adapters;      // in parameter order
+    // The step's device work (embedding .. last block's backward and gradient exchange) as a CUDA graph: the first call
+    // with a given shape runs eagerly (every scratch buffer reaches its size), the second is captured from the same code
+    // and launched, later ones replay it while nothing it points at has moved (StepKey).  A replay costs the host one
+    // launch instead of ~1400 and leaves no launch gaps between the short kernels.
+    struct StepKey {
+        int T = 0, world = 0, math = 0;
+        uint64_t gen = 0;
+        const void *comm = nullptr;
+        bool operator==(const StepKey &o) const { return T == o.T && world == o.world && math == o.math && gen == o.gen && comm == o.comm; }
+    };
+    cudaGraphExec_t step_exec = nullptr;
+    int64_t step_replays = 0;
+    StepKey step_key, warm_key;
+    bool warm = false;
+    bool graph_off = false;            // configuration, GT_STEP_GRAPH=0, or a capture that failed
+    int64_t step_launches = 0;         // kernels of the captured step (the engine's launch count, per replay)
 };
 
 namespace {
 
 size_t a256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+void drop_graph(gt_model *m) {
+    if (m->step_exec) cudaGraphExecDestroy(m->step_exec);
+    m->step_exec = nullptr;
+    m->warm = false;
+}
 
 int check_ready(const gt_model *m, const char *who) {
     if (!m) return failf(GT_ERR_INVALID, "%s: model is null", who);
@@ -180,6 +202,12 @@ int finish_loss(gt_model *m, float *loss_out, int32_t *valid_out, int flags) {
 
 }  // namespace
 
+namespace gt {
+void drop_step_graphs(gt_engine *e) {
+    for (gt_model *m : e->models) drop_graph(m);
+}
+}  // namespace gt
+
 extern "C" {
 
 int gt_model_create(gt_engine *e, const gt_model_config *cfg, gt_model **out) {
@@ -235,6 +263,8 @@ int gt_model_create(gt_engine *e, const gt_model_config *cfg, gt_model **out) {
     m->loss = take(256);
     m->valid = (int *)take(256);
     m->bad = (int *)take(256);
+    m->graph_off = cfg->no_graph != 0;
+    e->models.push_back(m);
     *out = m;
     return GT_OK;
 }
@@ -247,6 +277,12 @@ int gt_model_destroy(gt_model *m) {
         cudaSetDevice(e->device);
         cudaStreamSynchronize(e->stream);
         if (e->s_comm) cudaStreamSynchronize(e->s_comm);
+        drop_graph(m);
+        for (size_t i = 0; i < e->models.size(); i++)
+            if (e->models[i] == m) {
+                e->models.erase(e->models.begin() + (long)i);
+                break;
+            }
         for (LayerDev &L : m->layers) {
             if (L.norm1) cudaFree(L.norm1);
             if (L.norm2) cudaFree(L.norm2);
@@ -287,6 +323,7 @@ int gt_model_set_block(gt_model *m, int32_t layer, const gt_weight *const *weigh
     if (m->grads) return failf(GT_ERR_INVALID, "gt_model_set_block: the gradient buffer is already bound; set every block first");
     gt_engine *e = m->eng;
     std::lock_guard<std::mutex> lk(e->mu);
+    drop_graph(m);      // a captured step points at what this call replaces
     GT_CUDA(cudaSetDevice(e->device));
     LayerDev &L = m->layers[layer];
     for (int j = 0; j < kProj; j++) {
@@ -309,6 +346,7 @@ int gt_model_set_head(gt_model *m, const gt_weight *embedding, const float *out_
         return failf(GT_ERR_UNSUPPORTED, "gt_model_set_head: the LM head must be an F16 tensor with hidden %% 128 == 0");
     gt_engine *e = m->eng;
     std::lock_guard<std::mutex> lk(e->mu);
+    drop_graph(m);      // a captured step points at what this call replaces
     GT_CUDA(cudaSetDevice(e->device));
     m->embedding = embedding;
     m->lm_head = lm_head;
@@ -331,6 +369,7 @@ int gt_model_bind_grads(gt_model *m, float **grads_dev, int64_t *count) {
         float *g = nullptr;
         {
             std::lock_guard<std::mutex> lk(e->mu);
+            drop_graph(m);      // a captured step points at what this call replaces
             GT_CUDA(cudaSetDevice(e->device));
             GT_CUDA(cudaMalloc((void **)&g, (size_t)(n > 0 ? n : 1) * sizeof(float)));
             GT_CUDA(cudaMemsetAsync(g, 0, (size_t)(n > 0 ? n : 1) * sizeof(float), e->stream));
@@ -369,18 +408,14 @@ int gt_model_loss(gt_model *m, const int32_t *tokens, const int32_t *labels, int
     return finish_loss(m, loss_out, valid_out, flags);
 }
 
-int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t *labels, int32_t T, float *loss_out, int32_t flags) {
-    int rc = check_ready(m, "gt_model_forward_backward");
-    if (rc != GT_OK) return rc;
-    if (!tokens || !labels) return failf(GT_ERR_INVALID, "gt_model_forward_backward: null argument");
-    if (T <= 0 || T > m->cfg.max_tokens) return failf(GT_ERR_INVALID, "gt_model_forward_backward: T = %d outside (0, %d]", T, m->cfg.max_tokens);
+namespace {
+// Everything of a training step between the staged inputs and the read-back of the loss, queued on the engine stream
+// (and its side streams); no host synchronisation, no allocation once the buffers have their size.
+int step_body(gt_model *m, int T) {
     gt_engine *e = m->eng;
-    std::lock_guard<std::mutex> lk(e->mu);
-    GT_CUDA(cudaSetDevice(e->device));
     const bool ckpt = m->cfg.checkpoint != 0;
     const int L = (int)m->layers.size(), H = m->cfg.hidden;
-    rc = stage_inputs(m, tokens, labels, T, flags);
-    if (rc == GT_OK) rc = forward_all(m, T, !ckpt);
+    int rc = forward_all(m, T, !ckpt);
     if (rc != GT_OK) return rc;
     // loss and its gradient with respect to the normed final hidden state, then through the final RMSNorm
     rc = lm_head_loss_on_device(e, m->lm_head, m->fnorm, m->labels, T, m->loss, m->valid, m->dfnorm);
@@ -405,7 +440,104 @@ int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t 
             if (rc != GT_OK) return rc;
         }
     }
+    return GT_OK;
+}
+
+bool step_graph_allowed(const gt_model *m) {
+    static const bool env_on = !(getenv("GT_STEP_GRAPH") && atoi(getenv("GT_STEP_GRAPH")) == 0);
+    const gt_engine *e = m->eng;
+    return env_on && !m->graph_off && !e->profile && !e->trace;
+}
+
+// Captures step_body into a graph.  On any failure the capture is closed, the error state cleared and the model keeps to
+// eager launches from then on; nothing has run in that case (a capture only records).
+bool capture_step(gt_model *m, int T) {
+    gt_engine *e = m->eng;
+    if (cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    const int64_t launches0 = e->kernel_launches;
+    int rc = step_body(m, T);
+    if (rc == GT_OK) rc = join_comm(e);      // the side stream of the gradient exchange rejoins inside the graph
+    cudaGraph_t g = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+    e->comm_pending = false;
+    if (rc != GT_OK || ce != cudaSuccess || !g) {
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+        e->kernel_launches = launches0;
+        return false;
+    }
+    m->step_launches = e->kernel_launches - launches0;
+    e->kernel_launches = launches0;
+    cudaGraphExec_t exec = nullptr;
+    ce = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (ce != cudaSuccess || !exec) {
+        cudaGetLastError();
+        return false;
+    }
+    m->step_exec = exec;
+    return true;
+}
+}  // namespace
+
+int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t *labels, int32_t T, float *loss_out, int32_t flags) {
+    int rc = check_ready(m, "gt_model_forward_backward");
+    if (rc != GT_OK) return rc;
+    if (!tokens || !labels) return failf(GT_ERR_INVALID, "gt_model_forward_backward: null argument");
+    if (T <= 0 || T > m->cfg.max_tokens) return failf(GT_ERR_INVALID, "gt_model_forward_backward: T = %d outside (0, %d]", T, m->cfg.max_tokens);
+    gt_engine *e = m->eng;
+    std::lock_guard<std::mutex> lk(e->mu);
+    GT_CUDA(cudaSetDevice(e->device));
+    rc = stage_inputs(m, tokens, labels, T, flags);
+    if (rc != GT_OK) return rc;
+    bool queued = false;
+    if (step_graph_allowed(m)) {
+        gt_model::StepKey key;
+        key.T = T;
+        key.world = e->dp_world;
+        key.math = e->math_mode;
+        key.comm = e->comm;
+        key.gen = gt::layout_generation().load();
+        if (m->step_exec && !(m->step_key == key)) drop_graph(m);
+        if (!m->step_exec && m->warm && m->warm_key == key) {
+            if (capture_step(m, T)) {
+                m->step_key = key;
+            } else {
+                m->graph_off = true;
+                gt::logf(GT_LOG_INFO, "gt_model: the step could not be captured into a CUDA graph; launching eagerly");
+            }
+        }
+        if (m->step_exec) {
+            GT_CUDA(cudaGraphLaunch(m->step_exec, e->stream));
+            e->kernel_launches += m->step_launches;
+            m->step_replays += 1;
+            queued = true;
+        }
+    }
+    if (!queued) {
+        rc = step_body(m, T);
+        if (rc != GT_OK) return rc;
+        // a later call with this shape may be captured, if this one moved no buffer
+        m->warm_key.T = T;
+        m->warm_key.world = e->dp_world;
+        m->warm_key.math = e->math_mode;
+        m->warm_key.comm = e->comm;
+        m->warm_key.gen = gt::layout_generation().load();
+        m->warm = true;
+    }
     return finish_loss(m, loss_out, nullptr, flags);
+}
+
+int gt_model_step_info(gt_model *m, int32_t *graph_ready, int64_t *replays, int64_t *kernels_per_replay) {
+    if (!m) return failf(GT_ERR_INVALID, "gt_model_step_info: model is null");
+    std::lock_guard<std::mutex> lk(m->eng->mu);
+    if (graph_ready) *graph_ready = m->step_exec ? 1 : 0;
+    if (replays) *replays = m->step_replays;
+    if (kernels_per_replay) *kernels_per_replay = m->step_exec ? m->step_launches : 0;
+    return GT_OK;
 }
 
 int gt_model_optimizer_step(gt_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, float grad_scale, double max_norm,

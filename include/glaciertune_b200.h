@@ -334,7 +334,8 @@ typedef struct gt_model_config {
     float rope_theta;     /* RoPE frequency base (rope_freq_base)                                                 */
     int32_t max_tokens;   /* longest sequence a step may carry; every activation buffer is allocated for it       */
     int32_t checkpoint;   /* != 0: activation checkpointing - keep only the block inputs, recompute in the backward */
-    int32_t reserved[4];
+    int32_t no_graph;     /* != 0: gt_model_forward_backward always launches its kernels one by one (see there)    */
+    int32_t reserved[3];
 } gt_model_config;
 
 /* Replaces: the construction of GgufLoraModel's layer list (src/Glacier.Tune/Model/GgufLoraModel.cs:60-130) for the
@@ -365,8 +366,17 @@ GT_API int gt_model_loss(gt_model *m, const int32_t *tokens, const int32_t *labe
  * the side stream as soon as its backward is queued, last block first.
  * Host pointers (default): tokens / labels are host arrays and the call returns the loss (complete on return; an input
  * token outside the vocabulary is GT_ERR_INVALID as the reference throws).  GT_FLAG_DEVICE_PTRS: tokens, labels and
- * loss_out (one float, may be NULL) are device pointers and the call only queues work. */
+ * loss_out (one float, may be NULL) are device pointers and the call only queues work.
+ * The device work of a step is the same every time, so from the third call with one token count on it is replayed from a
+ * CUDA graph captured during the second (one launch on the host instead of ~1400, no launch gaps between the short
+ * kernels); the graph is dropped when a buffer it points at moves (a scratch buffer grows, gt_model_set_*,
+ * gt_model_bind_grads, gt_dp_init / gt_dp_finalize, another math mode) and is not used while gt_profile_enable or
+ * gt_debug_set_trace is on, with gt_model_config.no_graph, or with GT_STEP_GRAPH=0 in the environment. */
 GT_API int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t *labels, int32_t T, float *loss_out, int32_t flags);
+/* State of the captured step (no counterpart in the reference, whose step is a host loop): whether a graph stands ready
+ * for the next call, how many calls have been replays so far, and how many kernels one replay launches.  Any pointer
+ * may be NULL. */
+GT_API int gt_model_step_info(gt_model *m, int32_t *graph_ready, int64_t *replays, int64_t *kernels_per_replay);
 /* Replaces: the tail of a training step in LoraTrainer (src/Glacier.Tune/Trainer/LoraTrainer.cs:217-231):
  * ScaleAccumulatedGradients(grad_scale) -> ClipGradients(max_norm; <= 0: no clipping) -> AdamW step on every adapter
  * -> ZeroGrad, all on the device over the flat gradient buffer, after every pending gradient exchange.  `step` counts

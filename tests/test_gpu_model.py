@@ -67,10 +67,10 @@ def _make_model(oracle, n_layers=2, H=256, HQ=2, HK=1, F=512, V=1000, R=16, mix=
                 lm_head=(oracle.TYPE_F16, head))
 
 
-def _to_device(G, eng, model, max_tokens, checkpoint=True):
+def _to_device(G, eng, model, max_tokens, checkpoint=True, graph=True):
     cfg = model["cfg"]
     m = G.Model(eng, len(model["layers"]), cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"],
-                max_tokens, cfg["rms_eps"], cfg["rope_theta"], checkpoint=checkpoint)
+                max_tokens, cfg["rms_eps"], cfg["rope_theta"], checkpoint=checkpoint, graph=graph)
     handles = []
     for l, layer in enumerate(model["layers"]):
         ws, ads = [], []
@@ -163,6 +163,66 @@ def test_checkpointing_changes_nothing(G, oracle):
     # by up to 5e-4 in the first block's q, k, v gradients at this size (measured over repeated runs); recomputing the
     # forward adds nothing to that.
     assert oracle.rel_fro(out[0][1], out[1][1]) < 2e-3
+    eng.close()
+
+
+@pytest.mark.parametrize("mix", [False, True])
+def test_captured_step_matches_eager_launches(G, oracle, mix):
+    """From the third call on gt_model_forward_backward replays a CUDA graph of the step.  Four accumulating passes and
+    then three optimizer steps, once with the graph and once with one launch per kernel: same losses, same accumulated
+    gradients (up to the run-to-run spread of the fp32 atomic sums), and the graph must in fact have been used."""
+    eng = G.Engine(0, G.MATH_FP16)
+    model = _make_model(oracle, mix=mix, seed=21)
+    tokens, labels = _tokens(np.random.default_rng(3), model["cfg"]["vocab"], 64)
+    out = []
+    for graph in (True, False):
+        m, handles, heads, _ = _to_device(G, eng, model, max_tokens=64, graph=graph)
+        losses = [m.forward_backward(tokens, labels) for _ in range(4)]
+        grads = _device_grads(handles)
+        for step in range(1, 4):
+            m.optimizer_step(step=step, max_norm=1.0, **HYPER)
+            losses.append(m.forward_backward(tokens, labels))
+        info = m.step_info()
+        # (the call after the first eager one captures, unless a buffer still moved in between - then the one after)
+        assert info["graph_ready"] == graph and (5 <= info["replays"] <= 6 if graph else info["replays"] == 0)
+        assert (info["kernels_per_replay"] > 50) == graph
+        out.append((np.array(losses), grads))
+        _free(m, handles, heads)
+    assert np.all(np.isfinite(out[0][0])) and out[0][0][-1] < out[0][0][0]
+    assert np.max(np.abs(out[0][0][:4] - out[0][0][0])) < 1e-5 * out[0][0][0]      # the same pass four times
+    assert np.max(np.abs(out[0][0] - out[1][0]) / np.abs(out[1][0])) < 1e-4
+    assert oracle.rel_fro(out[0][1], out[1][1]) < 2e-3
+    eng.close()
+
+
+def test_captured_step_follows_the_token_count(G, oracle):
+    """Another token count drops the captured step and captures a new one; profiling switches replay off for the call.
+    The loss of every call equals the loss of the same call on a model that never captures."""
+    eng = G.Engine(0, G.MATH_FP16)
+    model = _make_model(oracle, seed=22)
+    rng = np.random.default_rng(4)
+    seqs = {T: _tokens(rng, model["cfg"]["vocab"], T) for T in (64, 40)}
+    plan = [64, 64, 64, 40, 40, 40, 40, 64, 64, 64]
+    res = []
+    for graph in (True, False):
+        m, handles, heads, _ = _to_device(G, eng, model, max_tokens=64, graph=graph)
+        losses, replays = [], []
+        for i, T in enumerate(plan):
+            if i == 8:
+                eng.profile_enable(True)
+            losses.append(m.forward_backward(*seqs[T]))
+            if i == 8:
+                eng.profile_enable(False)
+            replays.append(m.step_info()["replays"])
+        res.append((losses, replays))
+        _free(m, handles, heads)
+    # a new token count (calls 3 and 7) and profiling (call 8) launch eagerly; the call after an eager one captures the
+    # step and launches the new graph, which counts as a replay
+    r = res[0][1]
+    assert r[0] == 0 and r[2] >= 1 and r[3] == r[2] and r[6] >= r[3] + 2 and r[7] == r[6] and r[8] == r[7] and r[9] == r[8] + 1
+    assert res[1][1] == [0] * 10
+    for a, b in zip(res[0][0], res[1][0]):
+        assert abs(a - b) < 1e-5 * abs(b)
     eng.close()
 
 
