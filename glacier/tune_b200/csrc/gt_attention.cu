@@ -18,15 +18,19 @@
 //   k_attn_fwd      grid (query tile pairs, heads_q): online softmax over the key tiles at or left of the diagonal,
 //                   four compute warps and four fetch warps per block
 //   k_attn_delta    rowsum(dO * out) per (head, query)
-//   k_attn_bwd_dq   grid (heads_q, query tiles): dq of one tile, summed over its key tiles in registers
-//   k_attn_bwd_dkv  grid (heads_q, key tiles): dk, dv of one key tile for ONE query head, summed over the query tiles
-//                   in registers, written to a per-query-head workspace (both: eight compute + four fetch warps)
+//   k_attn_bwd      grid (2 * heads_q, tiles), eight compute + four fetch warps; even blocks: dq of one query tile, summed
+//                   over its key tiles in registers; odd blocks: dk, dv of one key tile for ONE query head, summed over the
+//                   query tiles in registers, written to a per-query-head workspace
 //   k_attn_reduce_kv sums the query heads of each KV group (fixed order: results do not change from run to run)
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "gt_engine_priv.h"
 #include "gt_ptx.cuh"
+
+using gt::launch_k;
+using gt::pdl_trigger;
+using gt::pdl_wait;
 
 using namespace gt;
 
@@ -147,6 +151,8 @@ constexpr int kFwdSmem = 5 * 64 * SD;      // Q + two (K, V) buffers
 template <typename T16>
 __global__ void __launch_bounds__(256) k_attn_fwd(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                   float *__restrict__ out, float *__restrict__ lse2, int T, int HQ, int HK) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t *Qs = smem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
@@ -281,6 +287,8 @@ __global__ void __launch_bounds__(256) k_attn_fwd(const float *__restrict__ q, c
 
 // delta[h, t] = sum_d dO[t, h, d] * out[t, h, d]; one warp per (t, h)
 __global__ void k_attn_delta(const float *__restrict__ d_out, const float *__restrict__ out, float *__restrict__ delta, int T, int HQ) {
+    pdl_wait();
+    pdl_trigger();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (w >= T * HQ) return;
     const int t = w / HQ, h = w % HQ;
@@ -352,19 +360,16 @@ __device__ __forceinline__ void compute_warps_sync() { asm volatile("bar.sync 1,
 
 // dq[query tile] = sum over key tiles j <= i of dS K.  Compute warps: query m-tile (warp & 3) x half of head_dim (warp >> 2).
 template <typename T16>
-__global__ void __launch_bounds__(384) k_attn_bwd_dq(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
-                                                     const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
-                                                     float *__restrict__ dq, int T, int HQ, int HK) {
+__device__ __forceinline__ void attn_bwd_dq_block(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
+                                                  const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
+                                                  float *__restrict__ dq, int T, int HQ, int HK, int h, int it) {
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t *Qs = smem, *dOs = Qs + 64 * SD, *Ps = smem + 6 * 64 * SD, *dSs = Ps + 64 * SP;
     auto kbuf = [&](int b) { return smem + (2 + 2 * b) * 64 * SD; };
     auto vbuf = [&](int b) { return smem + (3 + 2 * b) * 64 * SD; };
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const bool compute = warp < 8;
-    // grid (heads, query tiles): blocks are handed out head by head within a tile rank, the longest tiles (the last
-    // queries see every key tile) first - 224 blocks of 1..8 key tiles on 148 SMs finish in 8.7 tile times that way,
-    // against 13.4 when every head's tiles are dealt shortest first
-    const int h = blockIdx.x, it = (int)gridDim.y - 1 - (int)blockIdx.y, kh = h / (HQ / HK);
+    const int kh = h / (HQ / HK);
     const int q0 = it * BQ;
     const int64_t ldq = (int64_t)HQ * D, ldk = (int64_t)HK * D;
     if (compute) {
@@ -420,17 +425,16 @@ __global__ void __launch_bounds__(384) k_attn_bwd_dq(const float *__restrict__ d
 // dk, dv of one key tile for one query head, summed over the query tiles i >= j, into the per-head workspace
 // wk, wv [heads_q, T, head_dim].  Compute warps: key m-tile (warp & 3) x half of head_dim (warp >> 2).
 template <typename T16>
-__global__ void __launch_bounds__(384) k_attn_bwd_dkv(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
-                                                      const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
-                                                      float *__restrict__ wk, float *__restrict__ wv, int T, int HQ, int HK) {
+__device__ __forceinline__ void attn_bwd_dkv_block(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
+                                                   const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
+                                                   float *__restrict__ wk, float *__restrict__ wv, int T, int HQ, int HK, int h, int jt) {
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t *Ks = smem, *Vs = Ks + 64 * SD, *Ps = smem + 6 * 64 * SD, *dSs = Ps + 64 * SP;
     auto qbuf = [&](int b) { return smem + (2 + 2 * b) * 64 * SD; };
     auto obuf = [&](int b) { return smem + (3 + 2 * b) * 64 * SD; };
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const bool compute = warp < 8;
-    // grid (heads, key tiles): key tile 0 is seen by every query tile and goes first (see k_attn_bwd_dq)
-    const int h = blockIdx.x, jt = blockIdx.y, kh = h / (HQ / HK);
+    const int kh = h / (HQ / HK);
     const int k0 = jt * BK;
     const int64_t ldq = (int64_t)HQ * D, ldk = (int64_t)HK * D;
     const float qscale = kLog2e * rsqrtf((float)D);
@@ -494,9 +498,28 @@ __global__ void __launch_bounds__(384) k_attn_bwd_dkv(const float *__restrict__ 
     }
 }
 
+// One launch for both halves of the backward: grid (2 * heads, tiles), even blockIdx.x = the dq block of head x / 2, odd =
+// its dk, dv block.  blockIdx.y is the tile's rank by length, longest first (the last query tile sees every key tile,
+// key tile 0 is seen by every query tile): blocks are handed out rank by rank, head by head, so the 448 blocks of 1..8
+// tile steps pack the 148 SMs with one short tail - each half alone (224 blocks) left a tail of its own, and dealt
+// shortest first a half took 13.4 tile times instead of 8.7.
+static_assert(BQ == BK, "the dq and dk, dv blocks share one tile grid");
+template <typename T16>
+__global__ void __launch_bounds__(384) k_attn_bwd(const float *__restrict__ d_out, const float *__restrict__ q, const float *__restrict__ k,
+                                                  const float *__restrict__ v, const float *__restrict__ lse2, const float *__restrict__ delta,
+                                                  float *__restrict__ dq, float *__restrict__ wk, float *__restrict__ wv, int T, int HQ, int HK) {
+    pdl_wait();
+    pdl_trigger();
+    const int h = blockIdx.x >> 1, rank = blockIdx.y;
+    if (blockIdx.x & 1) attn_bwd_dkv_block<T16>(d_out, q, k, v, lse2, delta, wk, wv, T, HQ, HK, h, rank);
+    else attn_bwd_dq_block<T16>(d_out, q, k, v, lse2, delta, dq, T, HQ, HK, h, (int)gridDim.y - 1 - rank);
+}
+
 // dk[t, kh, :] = sum over the query heads of group kh of wk[h, t, :] (same for dv), heads in ascending order
 __global__ void k_attn_reduce_kv(const float *__restrict__ wk, const float *__restrict__ wv, float *__restrict__ dk, float *__restrict__ dv, int T,
                                  int HQ, int HK) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t n4 = (int64_t)T * HK * D / 4;
     const int ratio = HQ / HK;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
@@ -519,8 +542,7 @@ PerDeviceOnce g_attn_attr;
 template <typename T16>
 cudaError_t attn_allow_smem() {
     cudaError_t e = cudaFuncSetAttribute(k_attn_fwd<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_bwd_dq<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_bwd_dkv<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_attn_bwd<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     return e;
 }
 
@@ -545,9 +567,8 @@ int attention_forward_on_device(gt_engine *e, const float *q, const float *k, co
     }));
     const int n_qt = (T + BQ - 1) / BQ;
     const dim3 grid((n_qt + 1) / 2, HQ);      // a block takes query tile i and its mirror n - 1 - i
-    if (e->math_mode == GT_MATH_BF16) k_attn_fwd<__nv_bfloat16><<<grid, 256, kFwdSmem, e->stream>>>(q, k, v, out, lse, T, HQ, HK);
-    else k_attn_fwd<__half><<<grid, 256, kFwdSmem, e->stream>>>(q, k, v, out, lse, T, HQ, HK);
-    GT_LAUNCH(e, cudaGetLastError());
+    if (e->math_mode == GT_MATH_BF16) GT_LAUNCH(e, launch_k(k_attn_fwd<__nv_bfloat16>, grid, dim3(256), kFwdSmem, e->stream, q, k, v, out, lse, T, HQ, HK));
+    else GT_LAUNCH(e, launch_k(k_attn_fwd<__half>, grid, dim3(256), kFwdSmem, e->stream, q, k, v, out, lse, T, HQ, HK));
     return GT_OK;
 }
 
@@ -565,22 +586,14 @@ int attention_backward_on_device(gt_engine *e, const float *d_out, const float *
     GT_CUDA(e->attn.reserve(n_delta + 2 * n_w));
     float *delta = (float *)e->attn.p;
     float *wk = (float *)((char *)e->attn.p + n_delta), *wv = wk + (size_t)HQ * T * D;
-    k_attn_delta<<<(T * HQ * 32 + 255) / 256, 256, 0, e->stream>>>(d_out, out, delta, T, HQ);
-    GT_LAUNCH(e, cudaGetLastError());
-    const dim3 gq(HQ, (T + BQ - 1) / BQ), gk(HQ, (T + BK - 1) / BK);
-    if (e->math_mode == GT_MATH_BF16) {
-        k_attn_bwd_dq<__nv_bfloat16><<<gq, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, dq, T, HQ, HK);
-        GT_LAUNCH(e, cudaGetLastError());
-        k_attn_bwd_dkv<__nv_bfloat16><<<gk, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, wk, wv, T, HQ, HK);
-    } else {
-        k_attn_bwd_dq<__half><<<gq, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, dq, T, HQ, HK);
-        GT_LAUNCH(e, cudaGetLastError());
-        k_attn_bwd_dkv<__half><<<gk, 384, kBwdSmem, e->stream>>>(d_out, q, k, v, lse, delta, wk, wv, T, HQ, HK);
-    }
-    GT_LAUNCH(e, cudaGetLastError());
+    GT_LAUNCH(e, launch_k(k_attn_delta, dim3((T * HQ * 32 + 255) / 256), dim3(256), 0, e->stream, d_out, out, delta, T, HQ));
+    const dim3 gb(2 * HQ, (T + BQ - 1) / BQ);
+    if (e->math_mode == GT_MATH_BF16)
+        GT_LAUNCH(e, launch_k(k_attn_bwd<__nv_bfloat16>, gb, dim3(384), kBwdSmem, e->stream, d_out, q, k, v, lse, delta, dq, wk, wv, T, HQ, HK));
+    else
+        GT_LAUNCH(e, launch_k(k_attn_bwd<__half>, gb, dim3(384), kBwdSmem, e->stream, d_out, q, k, v, lse, delta, dq, wk, wv, T, HQ, HK));
     const int64_t n4 = (int64_t)T * HK * D / 4;
-    k_attn_reduce_kv<<<(unsigned)((n4 + 255) / 256), 256, 0, e->stream>>>(wk, wv, dk, dv, T, HQ, HK);
-    GT_LAUNCH(e, cudaGetLastError());
+    GT_LAUNCH(e, launch_k(k_attn_reduce_kv, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, e->stream, (const float *)wk, (const float *)wv, dk, dv, T, HQ, HK));
     return GT_OK;
 }
 

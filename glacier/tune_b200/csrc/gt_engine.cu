@@ -804,8 +804,11 @@ int backward_host(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *co
 namespace gt {
 bool pdl_enabled() {
     static const bool on = [] {
-        const char *v = getenv("GT_PDL");      // off by default: measured no gain on the layer step (the GEMM CTAs hold
-        return v && v[0] == '1';               // the whole shared memory, so a dependent CTA cannot become resident early)
+        // on unless GT_PDL=0.  Nothing on the seven projections alone (a GEMM CTA holds the whole shared memory, so a
+        // dependent CTA cannot become resident early), 2 ms of the 28-layer training step, whose ~1000 short kernels
+        // between the GEMMs otherwise pay a launch gap each.
+        const char *v = getenv("GT_PDL");
+        return !(v && v[0] == '0');
     }();
     return on;
 }

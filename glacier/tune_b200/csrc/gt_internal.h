@@ -219,7 +219,7 @@ cudaError_t launch_rmsnorm_bwd(const float *dy, const float *x, const float *w, 
 cudaError_t launch_add_rmsnorm_fwd(const float *a, const float *b, const float *w, float *sum, float *y, int T, int H, float eps, cudaStream_t s);
 
 // ---- launches with programmatic dependent launch (the kernel must call pdl_wait() before touching global memory).
-// Environment GT_PDL=1 turns the attribute on; the default is plain stream order.
+// On by default; environment GT_PDL=0 launches in plain stream order.
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
 cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {

@@ -446,7 +446,14 @@ int step_body(gt_model *m, int T) {
 bool step_graph_allowed(const gt_model *m) {
     static const bool env_on = !(getenv("GT_STEP_GRAPH") && atoi(getenv("GT_STEP_GRAPH")) == 0);
     const gt_engine *e = m->eng;
-    return env_on && !m->graph_off && !e->profile && !e->trace;
+    if (!env_on || m->graph_off || e->profile || e->trace) return false;
+    // the caller is capturing the engine stream itself: the kernels go into that graph one by one
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(e->stream, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return cs == cudaStreamCaptureStatusNone;
 }
 
 // Captures step_body into a graph.  On any failure the capture is closed, the error state cleared and the model keeps to
