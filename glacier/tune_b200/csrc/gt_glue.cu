@@ -199,8 +199,8 @@ __global__ void __launch_bounds__(256) k_add(const float *__restrict__ a, const 
 // (head, pair) items of q and k with coalesced accesses.  freq and theta follow the reference's fp32 order.
 constexpr int kRopeMaxHalf = 256;
 __global__ void __launch_bounds__(256) k_rope(float *__restrict__ q, float *__restrict__ k, int T, int heads_q, int heads_kv, int head_dim,
-                                              float freq_base, float freq_scale, int eff, float sign) {
-    __shared__ float cs[kRopeMaxHalf], sn[kRopeMaxHalf];
+                                              float freq_base, float freq_scale, int eff, float sign, int vec) {
+    __shared__ __align__(16) float cs[kRopeMaxHalf], sn[kRopeMaxHalf];
     pdl_wait();
     pdl_trigger();
     const int half = eff >> 1;
@@ -215,6 +215,18 @@ __global__ void __launch_bounds__(256) k_rope(float *__restrict__ q, float *__re
     }
     __syncthreads();
     const int hq = q ? heads_q : 0, heads = hq + (k ? heads_kv : 0);
+    if (vec) {      // four pairs per thread: 16-byte loads and stores of both halves
+        const int hq4 = half >> 2;
+        for (int it = threadIdx.x; it < heads * hq4; it += blockDim.x) {
+            const int h = it / hq4, i = (it - h * hq4) << 2;
+            float *p = h < hq ? q + ((int64_t)pos * heads_q + h) * head_dim + i : k + ((int64_t)pos * heads_kv + (h - hq)) * head_dim + i;
+            const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + half);
+            const float4 c = *reinterpret_cast<const float4 *>(cs + i), s = *reinterpret_cast<const float4 *>(sn + i);
+            *reinterpret_cast<float4 *>(p) = make_float4(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y, a.z * c.z - b.z * s.z, a.w * c.w - b.w * s.w);
+            *reinterpret_cast<float4 *>(p + half) = make_float4(a.x * s.x + b.x * c.x, a.y * s.y + b.y * c.y, a.z * s.z + b.z * c.z, a.w * s.w + b.w * c.w);
+        }
+        return;
+    }
     for (int it = threadIdx.x; it < heads * half; it += blockDim.x) {
         const int h = it / half, i = it - h * half;
         float *p = h < hq ? q + ((int64_t)pos * heads_q + h) * head_dim + i : k + ((int64_t)pos * heads_kv + (h - hq)) * head_dim + i;
@@ -387,8 +399,10 @@ cudaError_t launch_rope(float *q, float *k, int T, int heads_q, int heads_kv, in
     const int eff = (rope_dim > 0 && rope_dim <= head_dim) ? rope_dim : head_dim;      // RoPEKernel.cs:55
     if (T <= 0 || eff / 2 <= 0) return cudaSuccess;
     if (eff / 2 > kRopeMaxHalf) return cudaErrorInvalidValue;      // rotary dimensions above 512 are not served
+    // 16-byte accesses where every head's halves start on a 16-byte boundary
+    const int vec = (eff / 2) % 4 == 0 && head_dim % 4 == 0 && (!q || aligned16(q)) && (!k || aligned16(k)) ? 1 : 0;
     return launch_k(k_rope, dim3((unsigned)T), dim3(256), (size_t)0, s, q, k, T, heads_q, heads_kv, head_dim, freq_base, freq_scale, eff,
-                    inverse ? -1.0f : 1.0f);
+                    inverse ? -1.0f : 1.0f, vec);
 }
 cudaError_t launch_rmsnorm_fwd(const float *x, const float *w, float *y, int T, int H, float eps, cudaStream_t s) {
     return launch_k(k_rmsnorm_fwd, dim3((unsigned)T), dim3(256), (size_t)0, s, x, w, y, H, eps);

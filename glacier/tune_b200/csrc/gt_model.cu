@@ -425,7 +425,10 @@ int step_body(gt_model *m, int T) {
     const float inv_world = 1.0f / (float)e->dp_world;
     for (int l = L - 1; l >= 0; l--) {
         BlockState &s = m->st[ckpt ? 0 : l];
-        if (ckpt) {      // recompute this block's state into the one state set (not its output: that is x[l + 1], still there)
+        // recompute this block's state into the one state set (not its output: that is x[l + 1], still there).  The last
+        // block needs none: the forward pass ended with it, so the state set still holds its tensors (its attention norm
+        // came with the residual add of the block before, its own last add wrote the output norm elsewhere)
+        if (ckpt && l != L - 1) {
             rc = block_forward(m, l, m->x[l], nullptr, s, T, false, nullptr, nullptr);
             if (rc != GT_OK) return rc;
         }
