@@ -244,10 +244,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             tmem_relinquish();
         }
     }
-    // Everything above touches only this CTA's shared memory, TMEM and the kernel parameters, so under a programmatic
-    // dependent launch it overlaps the tail of the previous kernel in the stream; global memory is first read (and
-    // written) below, after that kernel has completed.  The next kernel may then be scheduled behind this one.
-    pdl_wait();
+    // Programmatic dependent launch: this CTA may start while the kernel before it in the stream (the pass that wrote
+    // the 16-bit activations, the low-rank activations and the output's bias / zero fill) still runs; every kernel
+    // before THAT one has completed, because it passed its own wait before it let this one be scheduled.  The packed
+    // weights, the adapter matrices and the adapter's non-zero flag are not written by that pass, so the weight producer
+    // and the dequant warps start at once and the first operand stages are ready when the activations arrive; whoever
+    // touches what the pass wrote waits for it first: the activation producer before its first copy, the dequant warps
+    // before the rank-update stage and the epilogue.  The next kernel may be scheduled behind this one right away.
     pdl_trigger();
     // rank-update stages (split 0 only): forward one for this tile's member, backward one per member with an adapter
     int lora_m[kMaxMembers];
@@ -373,6 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         if (lane < 4) {
             Ring xs;
             bool ok = true;
+            pdl_wait();      // the activations come from the kernel before this one
             for (int u = u0; u < u1 && ok; u++) {
                 int um = mi, rb = 0;
                 if (BWD) um = unit_member(u, rb);
@@ -550,6 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 if (lane == 0) mbar_arrive(bar(kBarRawEmpty + raw_bar(ui)));
             }
         }
+        pdl_wait();      // from here on: the low-rank activations, the bias, the output
         // A rank-update stage is built by the group that owns its slot (n % 4), like any other stage of that slot: the
         // group has seen every phase of the slot's barriers.  (A group that never waited on a slot could take a phase
         // two behind for the one it wants - parity waits cannot tell them apart - and the two MMA issuers may be many
