@@ -441,7 +441,8 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
     int nl = 0;
     for (int j = 0; j < n; j++) {
         if (!lora[j]) {
-            if (dy16[j]) GT_LAUNCH(e, launch_cast16(dYd[j], dy16[j], T, w[j]->dev.N, ld16[j], fp16, e->stream));
+            // (a null dY_j: its 16-bit copy is in place already)
+            if (dy16[j] && dYd[j]) GT_LAUNCH(e, launch_cast16(dYd[j], dy16[j], T, w[j]->dev.N, ld16[j], fp16, e->stream));
             continue;
         }
         gt_adapter *a = ad[j];
@@ -480,13 +481,25 @@ int lora_backward_group(gt_engine *e, int n, const gt_weight *const *w, gt_adapt
 
 // dX += sum_j dY_j * W_j (+ lora terms); dA_j, dB_j accumulate.  Tensor-core path: one GEMM launch for the group.
 // X16 (bf16 mode, members on the tensor path): the forward input as bf16 [T, K] instead of the fp32 Xd (which may be null).
+// where the 16-bit copies of a group's dY_j live inside the engine's dy16 scratch
+static size_t dy16_layout(int n, const gt_weight *const *w, int T, size_t *off, int *ld) {
+    size_t total = 0;
+    for (int j = 0; j < n; j++) {
+        ld[j] = round8(w[j]->dev.N);
+        off[j] = total;
+        total += ((size_t)T * ld[j] * 2 + 255) & ~(size_t)255;
+    }
+    return total;
+}
+
 int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dYd,
-                          const float *Xd, float *dXd, int T, int flags, const void *X16) {
+                          const float *Xd, float *dXd, int T, int flags, const void *X16, bool dy16_ready) {
     bool lora[kMaxGroup];
     for (int j = 0; j < n; j++) lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0;
     const bool reuse_low = (flags & GT_FLAG_REUSE_LOW) != 0;
     const bool assign = (flags & GT_FLAG_DX_ASSIGN) != 0 && dXd;
     if (!group_tensor_ok(e, n, w) || !dXd) {
+        if (dy16_ready) return fail(GT_ERR_INVALID, "backward_group_device: 16-bit gradients need the tensor path");
         for (int j = 0; j < n; j++) {
             int rc = backward_device(e, w[j], ad ? ad[j] : nullptr, dYd[j], Xd, dXd, T, lora[j], reuse_low, assign && j == 0);
             if (rc != GT_OK) return rc;
@@ -495,14 +508,12 @@ int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_ada
     }
     const int K = w[0]->dev.K;
     const int fp16 = e->math_mode == GT_MATH_FP16;
-    size_t dy_off[kMaxGroup], dy_total = 0;
+    size_t dy_off[kMaxGroup];
     int ld16[kMaxGroup];
     void *dy16[kMaxGroup];
-    for (int j = 0; j < n; j++) {
-        ld16[j] = round8(w[j]->dev.N);
-        dy_off[j] = dy_total;
-        dy_total += ((size_t)T * ld16[j] * 2 + 255) & ~(size_t)255;
-    }
+    const size_t dy_total = dy16_layout(n, w, T, dy_off, ld16);
+    if (dy16_ready && (e->dy16.cap < dy_total || e->math_mode != GT_MATH_BF16 || !group_tensor_ok(e, n, w) || !dXd))
+        return fail(GT_ERR_INVALID, "backward_group_device: the 16-bit gradients are not where this call reads them");
     GT_CUDA(e->dy16.reserve(dy_total));
     for (int j = 0; j < n; j++) dy16[j] = (char *)e->dy16.p + dy_off[j];
     UmmaLaunch m[kMaxGroup];
@@ -613,6 +624,14 @@ bool ffn_hidden16_ok(const gt_engine *e, const gt_weight *const *w, int T) {
     return on && e->math_mode == GT_MATH_BF16 && tensor_path(e, down) && T > 64 && (down->dev.K % 8) == 0;
 }
 
+// The SwiGLU backward can write dGate, dUp as the bf16 operands of the gate,up transpose GEMM directly (no fp32 pair, no
+// cast pass): bf16 mode, both on the tensor path with the same row length, a multiple of 8 (their 16-bit rows are then
+// dense), more tokens than any few-token kernel takes.
+bool ffn_dy16_ok(const gt_engine *e, const gt_weight *const *w, int T) {
+    static const bool on = !(getenv("GT_SWIGLU_FOLD") && atoi(getenv("GT_SWIGLU_FOLD")) == 0);
+    return on && e->math_mode == GT_MATH_BF16 && group_tensor_ok(e, 2, w) && T > 128 && w[0]->dev.N == w[1]->dev.N && (w[0]->dev.N % 8) == 0;
+}
+
 int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *gate_d, float *up_d,
                        float *hidden_d, float *Yd, int T, int flags, void *hidden16) {
     const int F = w[0]->dev.N;
@@ -674,6 +693,16 @@ int ffn_backward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *con
     int rc = backward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, &dy1, hidden_d, dh, T,
                                    (flags & ~GT_FLAG_DX_ASSIGN) | GT_FLAG_DX_ASSIGN, hidden16);      // dHidden is written, not added to
     if (rc != GT_OK) return rc;
+    if (ffn_dy16_ok(e, w, T) && dXd) {
+        // dGate, dUp as bf16 only, written where the group's transpose GEMM and adapter passes read their 16-bit dY
+        size_t off[2];
+        int ld[2];
+        GT_CUDA(e->dy16.reserve(dy16_layout(2, w, T, off, ld)));
+        GT_LAUNCH(e, launch_swiglu_bwd16(dh, gate_d, up_d, (char *)e->dy16.p + off[0], (char *)e->dy16.p + off[1], (int64_t)T * F, e->sm_count,
+                                         e->stream));
+        const float *none[2] = {nullptr, nullptr};
+        return backward_group_device(e, 2, w, ad, none, Xd, dXd, T, flags, nullptr, true);
+    }
     GT_LAUNCH(e, launch_swiglu_bwd(dh, gate_d, up_d, dg, du, (int64_t)T * F, e->sm_count, e->stream));
     const float *dgu[2] = {dg, du};
     return backward_group_device(e, 2, w, ad, dgu, Xd, dXd, T, flags);

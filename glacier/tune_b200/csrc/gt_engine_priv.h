@@ -155,7 +155,7 @@ bool side_da_enabled();
 int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
                          int T, int flags, const void *x16_ready = nullptr);
 int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dYd,
-                          const float *Xd, float *dXd, int T, int flags, const void *X16 = nullptr);
+                          const float *Xd, float *dXd, int T, int flags, const void *X16 = nullptr, bool dy16_ready = false);
 // SiLU(gate) * up can be kept as bf16 only (hidden16: [T, ffn] bf16, hidden_d null) when ffn_hidden16_ok(): the SwiGLU pass
 // then writes the down projection's 16-bit operand itself and the adapter products of the down projection read that copy.
 bool ffn_hidden16_ok(const gt_engine *e, const gt_weight *const *w, int T);

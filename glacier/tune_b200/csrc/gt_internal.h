@@ -93,7 +93,7 @@ struct LoraXaJob {
     float *low_zeroed;
     int R;
 };
-struct LoraDyJob {
+struct LoraDyJob {      // dY == nullptr: dy16 already holds bf16(dY) and is read instead (bf16 mode)
     const float *dY, *low, *B;
     float *dB, *dLow_zeroed;
     void *dy16;
@@ -191,6 +191,9 @@ cudaError_t launch_swiglu_fwd(const float *gate, const float *up, float *hidden,
 // hidden = SiLU(gate) * up written as fp32 (hidden, may be null) and as 16-bit (h16: bf16, or fp16 when fp16 != 0) in one
 // pass; n % 4 == 0 and 16-byte-aligned pointers
 cudaError_t launch_swiglu_fwd16(const float *gate, const float *up, float *hidden_or_null, void *h16, int64_t n, int fp16, int sm_count,
+                                cudaStream_t s);
+// dGate, dUp as bf16 only (the operands of the gate,up transpose GEMM); n % 4 == 0, 16-byte-aligned inputs
+cudaError_t launch_swiglu_bwd16(const float *d_hidden, const float *gate, const float *up, void *d_gate16, void *d_up16, int64_t n, int sm_count,
                                 cudaStream_t s);
 // one flat segment of an AdamW launch: parameters, gradients and both moments, n elements; flag (optional) is set to 1
 // when a parameter of the segment is non-zero after the step (vec is filled in by the launcher)

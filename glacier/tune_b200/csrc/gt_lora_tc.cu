@@ -338,11 +338,6 @@ __global__ void __launch_bounds__(256, 2) k_lora_xa_tc(const XaParams p) {
 // travels global -> registers -> shared memory as 16-byte pieces (8 values), the next strip's pieces in flight during
 // the MMAs.  Needs K % 8 == 0 and a 16-byte-aligned X16.
 // ------------------------------------------------------------------------------------------------
-struct Xa16Params {
-    const uint16_t *X16;
-    int ld, T, K, n, strips_per_block;
-    XaChunk c[kMaxChunks];
-};
 constexpr int NI16 = (TT * TC / 8) / 256;      // 16-byte pieces per thread and tile
 __device__ __forceinline__ void tile_load16(const uint16_t *__restrict__ src, int ld, int K, int t0, int T, int c0, uint4 (&v)[NI16], int tid) {
 #pragma unroll
@@ -362,6 +357,11 @@ __device__ __forceinline__ void tile_store16(const uint4 (&v)[NI16], uint8_t *ti
         *reinterpret_cast<uint4 *>(tile + r * GSB + c * 2) = v[i];
     }
 }
+struct Xa16Params {
+    const uint16_t *X16;
+    int ld, T, K, n, strips_per_block;
+    XaChunk c[kMaxChunks];
+};
 __global__ void __launch_bounds__(256, 2) k_lora_xa16_tc(const Xa16Params p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     uint8_t *Xs = dyn_smem;
@@ -464,7 +464,10 @@ struct DyParams {
     FillList fills;
 };
 
+// IN16: the members' dY exists as bf16 already (dy16, written by the pass that produced it): the tile is read from there,
+// 2 bytes per element, and no copy is written.
 constexpr int kDySmemBytes = kRingBytes + TT * GSB + 16 * GSB + TT * RSB;
+template <bool IN16>
 __global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     uint8_t *Gs = dyn_smem + kRingBytes;      // dY tile, bf16
@@ -485,7 +488,8 @@ __global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.y * TT;
     const int rc = min(16, R - r0);
-    float4 v[NI], bv[2];
+    float4 v[NI], bv[2];      // (the fp32 tile's registers are dead code with IN16, and the other way round)
+    uint4 v16[NI16];
     // this thread's two float4 of the strip's [16 x 128] tile of B: rank (tid + 256 i) / 32, columns 4 ((tid + 256 i) % 32)
     auto b_load = [&](int c0) {
 #pragma unroll
@@ -494,8 +498,10 @@ __global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
             bv[i] = ld4(m.B, r0 + r, N, c0 + (idx & 31) * 4, N, r < rc, m.vec_b != 0);
         }
     };
-    const bool use_ring = ring_ok(p.ring, m.dY, N, s1 * TC);
-    if (use_ring) {
+    const bool use_ring = !IN16 && ring_ok(p.ring, m.dY, N, s1 * TC);
+    if constexpr (IN16) {
+        tile_load16(m.dy16, m.ld16, N, t0, T, s0 * TC, v16, tid);
+    } else if (use_ring) {
         tile_issue(m.dY, N, t0, T, s0 * TC, ring, tid);
         ring_commit();
         if (s0 + 1 < s1) tile_issue(m.dY, N, t0, T, (s0 + 1) * TC, ring + kRingSlotBytes, tid);
@@ -513,7 +519,7 @@ __global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
     float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const int m0 = (warp >> 1) * 16, kh = (warp & 1) * 64;    // dLow: token m-tile, half of the strip's columns
     const int cb = warp * 16;                                 // dB: this warp's two 8-column n-tiles
-    uint16_t *dy16 = r0 == 0 ? m.dy16 : nullptr;
+    uint16_t *dy16 = (!IN16 && r0 == 0) ? m.dy16 : nullptr;
     for (int s = s0; s < s1; s++) {
         const int c0 = s * TC;
         const uint32_t slot = ring + (uint32_t)((s - s0) & 1) * kRingSlotBytes;
@@ -522,7 +528,8 @@ __global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
             tile_take(slot, v, tid);
         }
         __syncthreads();
-        tile_store(v, t0, T, c0, Gs, dy16, m.ld16, tid);
+        if constexpr (IN16) tile_store16(v16, Gs, tid);
+        else tile_store(v, t0, T, c0, Gs, dy16, m.ld16, tid);
         if (use_ring) {
             if (s + 2 < s1) tile_issue(m.dY, N, t0, T, (s + 2) * TC, slot, tid);
             ring_commit();
@@ -533,7 +540,8 @@ __global__ void __launch_bounds__(256, 2) k_lora_dy_tc(const DyParams p) {
             st_bf16x4(Bs + (idx >> 5) * GSB + (idx & 31) * 8, bv[i]);
         }
         if (s + 1 < s1) {      // the next strip's loads fly during the MMAs below
-            if (!use_ring) tile_load(m.dY, N, t0, T, (s + 1) * TC, v, tid);
+            if constexpr (IN16) tile_load16(m.dy16, m.ld16, N, t0, T, (s + 1) * TC, v16, tid);
+            else if (!use_ring) tile_load(m.dY, N, t0, T, (s + 1) * TC, v, tid);
             b_load((s + 1) * TC);
         }
         __syncthreads();
@@ -782,7 +790,8 @@ cudaError_t allow_dyn_smem() {
     return per_device_once(configured, [] {
         cudaError_t e = cudaFuncSetAttribute(k_lora_xa_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kRingBytes + kXsBytes + kMaxChunks * kAsBytes));
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(k_lora_dy_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDySmemBytes);
+        e = cudaFuncSetAttribute(k_lora_dy_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDySmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_lora_dy_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDySmemBytes);
         if (e != cudaSuccess) return e;
         return cudaFuncSetAttribute(k_lora_da_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kRingBytes + kXsBytes + kMaxChunks * kLsBytes));
     });
@@ -875,6 +884,12 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
     for (int j = 0; j < n; j++) n_chunks += (jobs[j].R + 15) / 16;
     const int n_launch_members = n_chunks < kMaxChunks ? (n_chunks > 0 ? n_chunks : 1) : kMaxChunks;
     (void)strips_sum;
+    // all members read fp32 dY, or all read the bf16 copy they were given (16-byte rows: N % 8 == 0)
+    const bool in16 = jobs[0].dY == nullptr;
+    for (int j = 0; j < n; j++)
+        if ((jobs[j].dY == nullptr) != in16 || (in16 && (!jobs[j].dy16 || jobs[j].N % 8 != 0 || jobs[j].ld16 % 8 != 0 ||
+                                                         (reinterpret_cast<uintptr_t>(jobs[j].dy16) & 15) != 0)))
+            return cudaErrorInvalidValue;
     DyParams p{};
     p.T = T;
     p.strips_per_block = pick_strip_run(strips_max, n_launch_members, T);
@@ -883,7 +898,8 @@ cudaError_t launch_lora_dy_group(const LoraDyJob *jobs, int n, int fp16, int T, 
     set_fills(p.fills, fills, n_fills, T);      // carried by the first launch
     auto flush = [&]() -> cudaError_t {
         if (p.n == 0) return cudaSuccess;
-        cudaError_t le = launch_k(k_lora_dy_tc, dim3(grid_xy.x, grid_xy.y, p.n), dim3(256), (size_t)kDySmemBytes, s, p);
+        cudaError_t le = in16 ? launch_k(k_lora_dy_tc<true>, dim3(grid_xy.x, grid_xy.y, p.n), dim3(256), (size_t)kDySmemBytes, s, p)
+                              : launch_k(k_lora_dy_tc<false>, dim3(grid_xy.x, grid_xy.y, p.n), dim3(256), (size_t)kDySmemBytes, s, p);
         p.n = 0;
         p.fills.n = 0;
         return le;

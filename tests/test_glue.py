@@ -156,10 +156,11 @@ def test_gpu_glue_argument_checks(eng):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("T", [9, 300])
+@pytest.mark.parametrize("T", [9, 100, 300])
 def test_gpu_ffn_block_forward_and_backward(eng, oracle, T):
     """gt_ffn_forward / gt_ffn_backward against the oracle chained the way TransformerBlock does it: gate and up
-    projections, SwiGLU, down projection, and back.  bf16 mode tolerances; T = 9 takes the few-token forward kernels."""
+    projections, SwiGLU, down projection, and back.  bf16 mode tolerances; T = 9 takes the few-token forward kernels,
+    T = 100 keeps SiLU(gate) * up as bf16 only, T = 300 also dGate and dUp."""
     import torch
     from glacier.tune_b200 import capi as G, synth as S
     H, F = 256, 768
