@@ -351,7 +351,8 @@ def run_ours(args) -> None:
     if args.launch_list and args.workload == "step":
         # the training step of a few layers for a profiler's launch list (the LM head stays full size)
         import torch as _t
-        model, keep, heads, _ = build_step_model(G, eng, dev, args.train_layers, rank, M_TOKENS)
+        # (one launch per kernel: a profiler lists the kernels of a graph replay less readably)
+        model, keep, heads, _ = build_step_model(G, eng, dev, args.train_layers, rank, M_TOKENS, graph=False)
         rng_ = np.random.default_rng(4000)
         tok = rng_.integers(0, STEP_CFG["vocab"], M_TOKENS).astype(np.int32)
         lab = np.roll(tok, -1).astype(np.int32)
@@ -582,13 +583,13 @@ def step_projection_flops(n_layers: int, checkpoint: bool = True) -> float:
     return n_layers * per_layer_fwd * (3.0 if checkpoint else 2.0)
 
 
-def build_step_model(G, eng, dev, n_layers: int, rank: int, max_tokens: int, checkpoint: bool = True, reuse=None):
+def build_step_model(G, eng, dev, n_layers: int, rank: int, max_tokens: int, checkpoint: bool = True, reuse=None, graph: bool = True):
     """The config-3 model on the device: seeded synthetic weights (one layer's K-quant bytes drawn on the host, the other
     layers' quant fields derived from them by a seeded XOR - scales and mins shared), A ~ N(0, 1/sqrt(in)), B = 0."""
     import torch
     c = STEP_CFG
     m = G.Model(eng, n_layers, c["hidden"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["ffn"], c["vocab"], max_tokens,
-                rms_eps=1e-6, rope_theta=1e6, checkpoint=checkpoint)
+                rms_eps=1e-6, rope_theta=1e6, checkpoint=checkpoint, graph=graph)
     if reuse is not None:      # a second model over the same weight and adapter handles (e.g. without checkpointing)
         keep, heads = reuse
         ones = np.ones(c["hidden"], np.float32)
