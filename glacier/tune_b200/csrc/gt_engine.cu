@@ -82,7 +82,7 @@ cudaEvent_t next_event(gt_engine *e) {
 }
 
 // launch the tensor-core GEMM (one launch for all members), bracketed by events when profiling is on
-cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on) {
+cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on, const UmmaDual *dual) {
     cudaStream_t st = on ? on : e->stream;
     cudaEvent_t a = nullptr, b = nullptr;
     if (e->profile) {
@@ -90,7 +90,7 @@ cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const cha
         b = next_event(e);
         if (a) cudaEventRecord(a, e->stream);
     }
-    cudaError_t ce = launch_umma_group(m, n, st, msg);
+    cudaError_t ce = launch_umma_group(m, n, st, msg, dual);
     if (ce != cudaSuccess) cudaGetLastError();      // a refused launch must not linger as the thread's "last error"
     if (e->profile && b) cudaEventRecord(b, e->stream);
     e->gemm_launches += 1;
@@ -180,14 +180,18 @@ bool group_tensor_ok(const gt_engine *e, int n, const gt_weight *const *w) {
 // (16-bit copy + every adapter's X*A), one GEMM launch.  Anything else runs member by member.
 // x16_ready (bf16 mode, members on the tensor path): the input already exists as bf16 [T, K] - nothing is cast, the
 // adapters' X*A reads that copy, Xd may be null.
+// dual_h16 (two members that ffn_dual_ok() accepted): the launch is the dual forward - it also writes
+// SiLU(Y_0) * Y_1 as 16-bit values to dual_h16 [T, out], and either Y_j may be null.
 int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
-                         int T, int flags, const void *x16_ready) {
+                         int T, int flags, const void *x16_ready, void *dual_h16) {
     bool lora[kMaxGroup];
     for (int j = 0; j < n; j++) {
         lora[j] = ad && ad[j] && !(flags & GT_FLAG_NO_LORA) && ad[j]->rank > 0 && ad[j]->scaling != 0.f;
         if (ad && ad[j] && !lora[j]) ad[j]->low_T = 0;      // nothing kept for a later backward to reuse
         if (ad && ad[j]) ad[j]->xkeep_T = 0;                // a kept copy of an earlier X is stale now (the host path renews it)
     }
+    if (dual_h16 && (n != 2 || !group_tensor_ok(e, n, w) || T <= 128))
+        return fail(GT_ERR_INVALID, "forward_group_device: the dual forward was asked for a group it does not serve");
     if (!group_tensor_ok(e, n, w)) {
         for (int j = 0; j < n; j++) {
             int rc = forward_device(e, w[j], ad ? ad[j] : nullptr, Xd, Yd[j], T, lora[j]);
@@ -263,7 +267,7 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
     int n_fills = 0;
     for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
         for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
-        const int splits = umma_group_splits(run_m + pos, count[r], e->sm_count);
+        const int splits = dual_h16 ? 1 : umma_group_splits(run_m + pos, count[r], e->sm_count);
         for (int i = 0; i < count[r]; i++) {
             const int j = order[pos + i];
             m[j].splits = splits;
@@ -298,10 +302,16 @@ int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adap
         GT_CUDA(cudaEventRecord(e->ev_aux_fork, e->stream));
         GT_CUDA(cudaStreamWaitEvent(e->s_aux, e->ev_aux_fork, 0));
     }
+    UmmaDual dual;
+    if (dual_h16) {
+        dual.h16 = dual_h16;
+        dual.ld_h16 = w[0]->dev.N;
+        if (runs != 1) return fail(GT_ERR_INVALID, "forward_group_device: the dual forward needs one quantization type");
+    }
     for (int r = 0, pos = 0; r < runs; pos += count[r], r++) {
         for (int i = 0; i < count[r]; i++) run_m[pos + i] = m[order[pos + i]];
         const char *msg = nullptr;
-        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg, (side && r > 0) ? e->s_aux : nullptr);
+        cudaError_t ce = timed_umma_group(e, run_m + pos, count[r], &msg, (side && r > 0) ? e->s_aux : nullptr, dual_h16 ? &dual : nullptr);
         if (ce != cudaSuccess) return fail(GT_ERR_CUDA, "forward GEMM launch failed: %s", msg ? msg : cudaGetErrorString(ce));
     }
     if (side) {
@@ -632,12 +642,38 @@ bool ffn_dy16_ok(const gt_engine *e, const gt_weight *const *w, int T) {
     return on && e->math_mode == GT_MATH_BF16 && group_tensor_ok(e, 2, w) && T > 128 && w[0]->dev.N == w[1]->dev.N && (w[0]->dev.N % 8) == 0;
 }
 
+// gate | up in ONE launch whose epilogue forms SiLU(gate) * up (the reference's gemm_q4_k_swiglu_batch,
+// GpuLoraEngine.Forward.cs:152-183,282-285): both of one quantization type on the tensor path, enough 64-feature tiles to
+// fill the GPU without split-K, adapter ranks up to 32.  GT_FFN_DUAL=0 keeps the separate SwiGLU pass.
+bool ffn_dual_ok(const gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, int T, int flags) {
+    static const bool on = !(getenv("GT_FFN_DUAL") && atoi(getenv("GT_FFN_DUAL")) == 0);
+    if (!on || !ffn_hidden16_ok(e, w, T) || !group_tensor_ok(e, 2, w) || w[0]->dev.qtype != w[1]->dev.qtype || T <= 128) return false;
+    UmmaLaunch m[2];
+    for (int j = 0; j < 2; j++) {
+        m[j].w = &w[j]->dev;
+        m[j].T = T;
+        m[j].fp16 = e->math_mode == GT_MATH_FP16;
+        m[j].rank = (ad && ad[j] && !(flags & GT_FLAG_NO_LORA)) ? ad[j]->rank : 0;
+    }
+    return umma_dual_ok(m, e->sm_count);
+}
+
 int ffn_forward_device(gt_engine *e, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *gate_d, float *up_d,
                        float *hidden_d, float *Yd, int T, int flags, void *hidden16) {
     const int F = w[0]->dev.N;
     const size_t bf = (size_t)T * F * sizeof(float);
     const bool fold = ffn_hidden16_ok(e, w, T);
     if (hidden16 && !fold) return fail(GT_ERR_INVALID, "ffn_forward_device: a 16-bit hidden tensor needs ffn_hidden16_ok()");
+    if (hidden16 && !hidden_d && ffn_dual_ok(e, w, ad, T, flags)) {
+        // The caller keeps the product as bf16 only, in a buffer of its own: the gate | up launch writes it from its epilogue.
+        // gate and up themselves are written where the caller gave a place for them (a backward needs them; a forward
+        // pass whose state is recomputed later does not).
+        float *gu[2] = {gate_d, up_d};
+        int rc = forward_group_device(e, 2, w, ad, Xd, gu, T, flags, nullptr, hidden16);
+        if (rc != GT_OK || !Yd) return rc;
+        float *yd = Yd;
+        return forward_group_device(e, 1, w + 2, ad ? ad + 2 : nullptr, nullptr, &yd, T, flags, hidden16);
+    }
     float *bufs[3] = {gate_d, up_d, hidden_d};
     for (int i = 0; i < 3; i++) {
         if (!bufs[i] && !(i == 2 && fold)) {      // folded: the fp32 product is written only where the caller wants it

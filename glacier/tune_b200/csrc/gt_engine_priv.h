@@ -148,12 +148,13 @@ constexpr int kMaxGroup = 3;
 int check_status(gt_engine *e);
 bool tensor_path(const gt_engine *e, const gt_weight *w);
 // launch (bracketed by events while profiling) on the engine stream, or on `on` when given
-cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on = nullptr);
+cudaError_t timed_umma_group(gt_engine *e, const UmmaLaunch *m, int n, const char **msg, cudaStream_t on = nullptr,
+                             const UmmaDual *dual = nullptr);
 bool side_da_enabled();
 // device-pointer forms of the projection calls; the caller holds the engine lock and has made the device current
 // (x16_ready / X16: the input as bf16 [T, K] where the caller has it - bf16 mode, tensor path; the fp32 X may then be null)
 int forward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *Xd, float *const *Yd,
-                         int T, int flags, const void *x16_ready = nullptr);
+                         int T, int flags, const void *x16_ready = nullptr, void *dual_h16 = nullptr);
 int backward_group_device(gt_engine *e, int n, const gt_weight *const *w, gt_adapter *const *ad, const float *const *dYd,
                           const float *Xd, float *dXd, int T, int flags, const void *X16 = nullptr, bool dy16_ready = false);
 // SiLU(gate) * up can be kept as bf16 only (hidden16: [T, ffn] bf16, hidden_d null) when ffn_hidden16_ok(): the SwiGLU pass

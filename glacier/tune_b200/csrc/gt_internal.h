@@ -164,7 +164,13 @@ bool tmap_encode_2d(CUtensorMap *tm, CUtensorMapDataType dt, const void *base, u
 // Up to three projections in one launch (see gt_umma_gemm.cu); umma_group_ok tells whether they qualify.
 bool umma_group_ok(const UmmaLaunch *m, int n);
 int umma_group_splits(const UmmaLaunch *m, int n, int sm_count);
-cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const char **err);
+// dual forward (gate | up, SwiGLU product in the epilogue): see umma_dual_ok
+struct UmmaDual {
+    void *h16 = nullptr;      // 16-bit [T, ld_h16] in the launch's operand format, or null
+    int ld_h16 = 0;
+};
+bool umma_dual_ok(const UmmaLaunch *m, int sm_count);
+cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const char **err, const UmmaDual *dual = nullptr);
 cudaError_t umma_init_weight_maps(WeightDev *w, const char **err);
 bool umma_available();
 cudaError_t launch_bounded_wait_selftest(int *status, long long limit_cycles, cudaStream_t s);

@@ -96,8 +96,10 @@ int check_ready(const gt_model *m, const char *who) {
 // the norm that follows this block's output - the next block's attention norm or the model's output norm - computed
 // in the same pass as the residual add.  x_out == nullptr: the state only (the recomputed forward of a checkpointed block) -
 // the down projection and the residual add after it are left out, their result is the stored input of the next block.
+// keep_gu = false: nothing will read this pass's gate and up tensors (the block's state is recomputed before its backward),
+// so where the FFN can do without them they are not written.
 int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockState &s, int T, bool n1_ready, const float *next_norm,
-                  float *next_n1) {
+                  float *next_n1, bool keep_gu = true) {
     gt_engine *e = m->eng;
     const gt_model_config &c = m->cfg;
     const LayerDev &L = m->layers[l];
@@ -117,8 +119,9 @@ int block_forward(gt_model *m, int l, const float *x_in, float *x_out, BlockStat
     gt_adapter *fa[3] = {L.ad[kGate], L.ad[kUp], L.ad[kDown]};
     // SiLU(gate) * up is kept as bf16 only where the engine can work from that (the buffer is sized for fp32 either way)
     const bool h16 = ffn_hidden16_ok(e, fw, T);
-    rc = ffn_forward_device(e, fw, fa, s.n2, s.gate, s.up, h16 ? nullptr : s.hidden, x_out ? m->tmp_h : nullptr, T, 0,
-                            h16 ? (void *)s.hidden : nullptr);
+    const bool drop_gu = !keep_gu && h16 && x_out;      // (without the 16-bit product the SwiGLU pass reads them from the state)
+    rc = ffn_forward_device(e, fw, fa, s.n2, drop_gu ? nullptr : s.gate, drop_gu ? nullptr : s.up, h16 ? nullptr : s.hidden,
+                            x_out ? m->tmp_h : nullptr, T, 0, h16 ? (void *)s.hidden : nullptr);
     if (rc != GT_OK || !x_out) return rc;
     if (next_norm && next_n1) GT_LAUNCH(e, launch_add_rmsnorm_fwd(s.x1, m->tmp_h, next_norm, x_out, next_n1, T, H, c.rms_eps, e->stream));
     else GT_LAUNCH(e, launch_add(s.x1, m->tmp_h, x_out, (int64_t)T * H, e->sm_count, e->stream));
@@ -174,7 +177,8 @@ int forward_all(gt_model *m, int T, bool keep_states) {
         // (into that block's state; with one shared state set its n1 has been consumed by then) or the output norm
         const float *next_w = l + 1 < L ? m->layers[l + 1].norm1 : m->out_norm;
         float *next_n1 = l + 1 < L ? m->st[keep_states ? l + 1 : 0].n1 : m->fnorm;
-        rc = block_forward(m, l, m->x[l], m->x[l + 1], s, T, l > 0, next_w, next_n1);
+        // with one shared state set only the last block's state survives until its backward
+        rc = block_forward(m, l, m->x[l], m->x[l + 1], s, T, l > 0, next_w, next_n1, keep_states || l == L - 1);
         if (rc != GT_OK) return rc;
     }
     return GT_OK;

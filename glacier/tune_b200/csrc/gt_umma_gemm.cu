@@ -101,7 +101,16 @@ struct Params {
     int atomic_out;  // 1: red.add into out, 0: plain store (forward: + bias)
     int tmem_cols;
     int par_ok;      // 0: keep the two MMA issuers on the turn token at every token count (GT_MMA_PAR=0)
+    // Dual forward (gate | up with the SwiGLU product in the epilogue; replaces gemm_q4_k_swiglu_batch,
+    // src/Glacier.Tune/Gpu/GpuLoraEngine.Forward.cs:152-183): two members of the same shape, no split-K.  A CTA's tile
+    // holds 64 rows of member 0 and the SAME 64 rows of member 1, laid out so that TMEM lanes 32 q + l and 32 q + 16 + l
+    // (l < 16) are the two members' row 16 q + l: one warp shuffle brings gate and up of a feature together.
+    int dual;
+    void *h16;       // T16 [T, ld_h16]: SiLU(gate) * up, or null
+    int ld_h16;
 };
+// dual forward: row r of the packed-weight stage (member r / 64, feature r % 64) -> row of the operand tile / TMEM lane
+__host__ __device__ inline int dual_row(int r) { return ((r & 63) >> 4) * 32 + (r >> 6) * 16 + (r & 15); }
 
 // status codes written on a bounded-wait timeout: 100*role + barrier kind
 enum { kCodeProducer = 100, kCodeMma = 200, kCodeDequant = 300, kCodeEpilogue = 400 };
@@ -255,8 +264,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
     // rank-update stages (split 0 only): forward one for this tile's member, backward one per member with an adapter
     int lora_m[kMaxMembers];
     int n_lora = 0;
+    int dual_pad[2] = {0, 0};      // dual forward: 16-padded ranks of the two members inside the one rank-update stage
     if (split == 0) {
-        if (!BWD) {
+        if (!BWD && p.dual) {
+            for (int j = 0; j < 2; j++)
+                if (p.m[j].rank > 0 && (p.m[j].lora_flag == nullptr || *p.m[j].lora_flag != 0)) dual_pad[j] = (p.m[j].rank + 15) & ~15;
+            if (dual_pad[0] + dual_pad[1] > 0) lora_m[n_lora++] = 0;
+        } else if (!BWD) {
             if (M.rank > 0 && (M.lora_flag == nullptr || *M.lora_flag != 0)) lora_m[n_lora++] = mi;
         } else {
             for (int j = 0; j < p.n_members; j++)
@@ -332,13 +346,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                     }
                 }
             }
-        } else if (lane < 3 * kTeams) {
+        } else if (lane < ((!BWD && p.dual) ? 6 : 3) * kTeams) {
             // Teams of three lanes (lane 0 of a team arms the barrier and copies the headers, lanes 1 and 2 copy the
             // quant regions); team t issues the raw stages r = t (mod kTeams).  Issuing a tiled copy holds the issuing
             // thread for several hundred clocks: with one team the issue rate alone (one raw stage per ~800 clocks) paced
             // the few-token shapes.  kTeams <= kNumRaw, so a team never waits for a slot whose previous stage is issued
             // in the same round.
-            const int team = lane / 3, li = lane - 3 * team;
+            // (dual forward: six lanes, one per region and member)
+            const int lpt = (!BWD && p.dual) ? 6 : 3;
+            const int team = lane / lpt, li = lane - lpt * team;
             bool ok = true;
             for (int u = u0 + team; u < u1 && ok; u += kTeams) {
                 const int r = u - u0, ri = r % kNumRaw;
@@ -358,6 +374,23 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const Member &W = p.m[um];
                 row0 += W.row_base;
                 const int xb = sb * QS::kBlockBytes;
+                if (!BWD && p.dual) {
+                    // 64 rows of either member (64-row boxes): member 1's rows land behind member 0's in every region
+                    const int reg = li % 3, mm = li / 3;
+                    const int region = reg == 0 ? 0 : (reg == 1 ? kRows * H : kRows * (H + 64));
+                    const int row_bytes = reg == 0 ? H : (reg == 1 ? 64 : Q1);
+                    const int x = xb + (reg == 0 ? QS::hdr_x(half) : (reg == 1 ? QS::q0_x(half) : QS::q1_x(half)));
+                    if (li == 0) {
+                        mbar_arrive_expect_tx(rbar, (uint32_t)(kRows * (H + 64 + Q1)));
+                        if (lane == 0) trace(0, r / kTeams);
+                    }
+                    if (reg < 2 || Q1 > 0) {
+                        const Member &Wm = p.m[mm];
+                        const CUtensorMap *tm = reg == 0 ? &Wm.tm_hdr : (reg == 1 ? &Wm.tm_q0 : &Wm.tm_q1);
+                        tma_load_2d(rdst + region + mm * 64 * row_bytes, tm, x, Wm.row_base + ltile * 64, rbar);
+                    }
+                    continue;
+                }
                 // one copy per region: the tensor maps handed to a forward launch have 128-row boxes, the backward
                 // ones 64-row boxes
                 if (li == 0) {
@@ -437,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
                 const int si = n % kNumA;
                 const uint32_t a_lo0 = (((sbase + kOffA + si * kAStageBytes) & 0x3FFFFu) >> 4) | kALoField;
                 const uint32_t b_lo0 = (((sbase + kOffX + si * kXStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
-                const int ksteps = n < n_main ? 4 : ((p.m[lora_m[n - n_main]].rank + 15) >> 4);
+                const int ksteps = n < n_main ? 4 : ((!BWD && p.dual) ? (dual_pad[0] + dual_pad[1]) >> 4 : ((p.m[lora_m[n - n_main]].rank + 15) >> 4));
                 if (n > 0 && !par) {
                     // take the turn: the other issuer has queued stage n - 1 (by now this thread has already waited for
                     // its own operands, which is the latency the second issuer hides)
@@ -524,7 +557,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             // raw stages, groups 2, 3 the odd ones; a thread owns one row of its group's half
             const int row = dt, sub = g4 & 1;
             const int grp[2] = {2 * sub, 2 * sub + 1};
-            const uint32_t dst_off[2] = {(uint32_t)(row * 128), (uint32_t)(row * 128)};
+            const int prow = p.dual ? dual_row(row) : row;      // (prow & 7 == row & 7: the swizzle phase stays the row's)
+            const uint32_t dst_off[2] = {(uint32_t)(prow * 128), (uint32_t)(prow * 128)};
             const int chunk0[2] = {0, 4};
             for (int ui = g4 >> 1; ui < nu && ok; ui += 2) {
                 const int ri = ui % kNumRaw;
@@ -563,13 +597,59 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
             // weight-side tile from B (forward) / A (backward), activation-side tile from the fp32 low-rank activations,
             // both rounded to T16 here
             const Member &L = p.m[lora_m[lj]];
-            const int rank_pad = (L.rank + 15) & ~15;
+            const int rank_pad = (!BWD && p.dual) ? dual_pad[0] + dual_pad[1] : (L.rank + 15) & ~15;
             const int n = (BWD ? 1 : 2) * nu + lj;
             const int ai = n % kNumA;
             if (ai != g4) continue;
             ok = mbar_wait_bounded(bar(kBarEmpty + ai), ((uint32_t)(n / kNumA) & 1u) ^ 1u, abort_flag, p.status, kCodeDequant + 3);
             if (!ok) break;
             const uint32_t a_addr = sbase + kOffA + ai * kAStageBytes;
+            if (!BWD && p.dual) {
+                // one stage for both members: contraction columns [0, pad0) are member 0's ranks, [pad0, pad0 + pad1) member
+                // 1's; a member's weight-side rows are zero in the other member's columns
+                const uint32_t x_addr = sbase + kOffX + ai * kXStageBytes;
+                for (int i = 0; i < n_mma; i++) {
+                    const int ntok = min(MTOK, tb - MTOK * i);
+                    const int rows = PAIR ? (ntok >> 1) : ntok;
+                    for (int rr = dt; rr < rows; rr += 128) {
+                        const int t = tok0 + MTOK * i + (PAIR ? (int)crank * rows : 0) + rr;
+                        const uint32_t row_addr = x_addr + (uint32_t)(i * kMmaSlotBytes + rr * 128);
+                        for (int j = 0; j * 8 < rank_pad; j++) {
+                            const int mm = 8 * j < dual_pad[0] ? 0 : 1;
+                            const Member &Lm = p.m[mm];
+                            const int rbase = 8 * j - (mm ? dual_pad[0] : 0);
+                            float v[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                const int r = rbase + q;
+                                v[q] = (r < Lm.rank && t < p.T) ? Lm.lora_act[(int64_t)t * Lm.rank + r] * Lm.lora_scale : 0.f;
+                            }
+                            st_shared_v4(row_addr + (uint32_t)((j ^ (rr & 7)) << 4), pack2<T16>(v[0], v[1]), pack2<T16>(v[2], v[3]),
+                                         pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
+                        }
+                    }
+                }
+                {
+                    const int row = dt, mm = row >> 6, nn = ltile * 64 + (row & 63), prow = dual_row(row);
+                    const Member &Lm = p.m[mm];
+                    for (int j = 0; j * 8 < rank_pad; j++) {
+                        const bool mine = (8 * j < dual_pad[0]) == (mm == 0) && dual_pad[mm] > 0;
+                        const int rbase = 8 * j - (mm ? dual_pad[0] : 0);
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const int r = rbase + i;
+                            v[i] = (mine && r < Lm.rank && nn < Lm.N) ? Lm.lora_w[(int64_t)r * Lm.N + nn] : 0.f;
+                        }
+                        st_shared_v4(a_addr + (uint32_t)(prow * 128 + ((j ^ (prow & 7)) << 4)), pack2<T16>(v[0], v[1]),
+                                     pack2<T16>(v[2], v[3]), pack2<T16>(v[4], v[5]), pack2<T16>(v[6], v[7]));
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                signal_a_full(ai, 4);
+                continue;
+            }
             {
                 // token rows of this CTA's activation tile: rank_pad/8 chunks of a 128-byte row
                 const uint32_t x_addr = sbase + kOffX + ai * kXStageBytes;
@@ -623,16 +703,107 @@ __global__ void __launch_bounds__(kThreads, 1) k_umma_gemm(const __grid_constant
         // epilogue: TMEM lane = weight row / column of this tile, TMEM column = token
         if (ok) ok = mbar_wait_bounded(bar(kBarAcc), 0u, abort_flag, p.status, kCodeEpilogue + 1, 16000000000ll);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: take the epilogue only as a whole warp
+        if (!BWD && p.dual) {
+            // the dual epilogue's warps meet at named barriers: all sixteen take it, or none (a warp whose wait gave up has
+            // raised the CTA's abort flag)
+            asm volatile("bar.sync 5, 512;" ::: "memory");
+            ok = *abort_flag == 0;
+        }
         if (ok) {
             tc_fence_after_sync();
             if (threadIdx.x == 64) trace(11, 1);
             const int quad = warp & 3, cgrp = (warp - 2) >> 2;     // TMEM lane quadrant; column group 0..3
+            if (!BWD && p.dual) {
+                // Lanes 0..15 of the warp hold member 0 (gate), lanes 16..31 member 1 (up) of the same 16 features.  The four
+                // warps of a column group stage their 32 tokens x 64 features in shared memory (the operand stages are free:
+                // every MMA has completed) and write them out a whole row of the tile per instruction - 128 bytes of the
+                // 16-bit product, 256 of gate or up; straight from the registers a warp would write 32- and 64-byte pieces,
+                // and the drain of the tile is bound by the number of requests, not by their bytes.  Shared memory is
+                // addressed by 32-bit offsets with immediate displacements: the loops below are bound by instruction issue.
+                const int mm = lane >> 4;
+                const int fcol = quad * 16 + (lane & 15);
+                const int f0 = ltile * 64;
+                const Member &Mm = p.m[mm];
+                const bool tile_ok = f0 < Mm.N;      // out_features % 64 == 0: a tile is all in range or (pair padding) all out
+                const float bvm = (Mm.bias && tile_ok) ? Mm.bias[f0 + fcol] : 0.f;
+                float *const out_g = p.m[0].out, *const out_u = p.m[1].out;
+                const bool stage_gu = out_g != nullptr || out_u != nullptr;
+                const int ld_gu = p.m[0].ld_out;
+                T16 *const h16 = reinterpret_cast<T16 *>(p.h16);
+                // staging of this column group: [32][64] 16-bit product | [32][64] fp32 gate | [32][64] fp32 up
+                const uint32_t stg = sbase + kOffX + (uint32_t)cgrp * 20480u;
+                const uint32_t st_x = stg + (mm ? 12288u : 4096u) + (uint32_t)fcol * 4u;      // this lane's member, row j
+                const uint32_t st_h = stg + (uint32_t)(mm * 64 + fcol) * 2u;                  // product of token j + mm
+                const uint32_t ld_h = stg + (uint32_t)(quad * 8) * 128u + (uint32_t)lane * 4u;
+                const uint32_t ld_g = stg + 4096u + (uint32_t)(quad * 8) * 256u + (uint32_t)lane * 8u;
+                const int nchd = (tb + 31) >> 5;
+                const int tok_lim = min(tb, p.T - tok0);      // token rows of this CTA that exist
+                for (int c = cgrp; c < nchd; c += 4) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+                    tmem_ld_wait();
+                    for (int a = 1; a < n_acc_sum; a++) {
+                        uint32_t w2[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * acc_stride + c * 32), w2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int jx = 0; jx < 32; jx++) v[jx] = __float_as_uint(__uint_as_float(v[jx]) + __uint_as_float(w2[jx]));
+                    }
+                    // SiLU(gate) * up (SwiGluKernel.cs:13-35), two tokens per step: the gate lanes take token j (up comes from
+                    // the partner lane), the up lanes token j + 1 (gate comes from the partner).  ex2 / rcp approximations:
+                    // the product is rounded to 16 bits right here.
+#pragma unroll
+                    for (int jx = 0; jx < 32; jx += 2) {
+                        const float x0 = __uint_as_float(v[jx]) + bvm, x1 = __uint_as_float(v[jx + 1]) + bvm;
+                        if (stage_gu) {
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(st_x + jx * 256), "f"(x0) : "memory");
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(st_x + (jx + 1) * 256), "f"(x1) : "memory");
+                        }
+                        const float other = __shfl_xor_sync(0xffffffffu, mm ? x0 : x1, 16);
+                        const float g = mm ? other : x0, u = mm ? x1 : other;
+                        float sig;
+                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + __expf(-g)));
+                        const T16 hv = T16(g * sig * u);
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(st_h + jx * 128), "h"(*reinterpret_cast<const unsigned short *>(&hv)) : "memory");
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + cgrp) : "memory");
+                    // this warp writes token rows quad * 8 .. + 7 of the chunk
+                    const int row0 = c * 32 + quad * 8;
+                    const int n_rows = tile_ok ? max(0, min(8, tok_lim - row0)) : 0;
+                    const int64_t t_first = (int64_t)tok0 + row0;
+                    if (h16 && n_rows > 0) {
+                        uint32_t r[8];
+#pragma unroll
+                        for (int jj = 0; jj < 8; jj++) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r[jj]) : "r"(ld_h + jj * 128));
+                        T16 *hp = h16 + t_first * p.ld_h16 + f0 + 2 * lane;
+#pragma unroll
+                        for (int jj = 0; jj < 8; jj++)
+                            if (jj < n_rows) *reinterpret_cast<uint32_t *>(hp + (int64_t)jj * p.ld_h16) = r[jj];
+                    }
+                    if (stage_gu && n_rows > 0) {
+#pragma unroll
+                        for (int half = 0; half < 2; half++) {
+                            float *const op = half ? out_u : out_g;
+                            if (!op) continue;
+                            float2 r[8];
+#pragma unroll
+                            for (int jj = 0; jj < 8; jj++)
+                                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(r[jj].x), "=f"(r[jj].y) : "r"(ld_g + half * 8192 + jj * 256));
+                            float *gp = op + t_first * ld_gu + f0 + 2 * lane;
+#pragma unroll
+                            for (int jj = 0; jj < 8; jj++)
+                                if (jj < n_rows) *reinterpret_cast<float2 *>(gp + (int64_t)jj * ld_gu) = r[jj];
+                        }
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + cgrp) : "memory");      // the staging tiles are rewritten next
+                }
+            }
             const int orow = ltile * kTileW + quad * 32 + lane;
-            const bool row_ok = orow < (BWD ? p.K : M.N);
+            const bool row_ok = orow < (BWD ? p.K : M.N) && !(!BWD && p.dual);
             const float bv = (!BWD && !p.atomic_out && M.bias && row_ok) ? M.bias[orow] : 0.f;
             float *const out_base = M.out;       // backward: member 0 holds the shared dX
             const int ld_out = M.ld_out;
-            const int nch = (tb + 31) >> 5;
+            const int nch = (!BWD && p.dual) ? 0 : (tb + 31) >> 5;      // (the dual forward has written its tile above)
             for (int c = cgrp; c < nch; c += 4) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
@@ -939,7 +1110,26 @@ int umma_group_splits(const UmmaLaunch *m, int n, int sm_count) {
 
 // Members share T, math mode, direction, in_features and quantization type (umma_group_ok).  Forward: the activation
 // operand and `splits` / `out_prefilled` come from member 0.  Backward: every member brings its own dY; `out` is shared.
-cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const char **err) {
+// gate | up with the SwiGLU product in the epilogue: members 0 and 1 of the same shape and type, no split-K; either
+// member's `out` may be null (nothing but the product is wanted), h16 receives SiLU(out0) * out1 as 16-bit values
+bool umma_dual_ok(const UmmaLaunch *m, int sm_count) {
+    if (!umma_group_ok(m, 2) || m[0].backward || few_group(m, 2)) return false;
+    const WeightDev *a = m[0].w, *b = m[1].w;
+    if (a->qtype == kTypeF16 || a->N != b->N || a->N % 64 != 0 || m[0].rows || m[1].rows) return false;
+    if (m[0].rank > 32 || m[1].rank > 32 || m[0].out_prefilled || m[1].out_prefilled) return false;
+    if (m[0].T <= 128) return false;      // the kernel's 256-row activation stages
+    // one CTA per 64 features and token chunk, no split-K: worth it where those alone fill the GPU
+    // (GT_FFN_DUAL_MIN_TILES, read at every call: a smaller bound, for tests on small tensors)
+    const char *env = getenv("GT_FFN_DUAL_MIN_TILES");
+    const int need = env ? atoi(env) : sm_count;
+    return (a->N / 64) * ((m[0].T + kMaxTok - 1) / kMaxTok) >= need;
+}
+
+cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const char **err, const UmmaDual *dual) {
+    if (dual && (n != 2 || !umma_dual_ok(m, 0))) {
+        if (err) *err = "the two projections do not qualify for the dual forward";
+        return cudaErrorInvalidValue;
+    }
     if (!umma_group_ok(m, n)) {
         if (err) *err = "projections cannot share one launch (type, in_features, token count or TMA layout differ)";
         return cudaErrorInvalidValue;
@@ -947,7 +1137,7 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     const UmmaLaunch &L0 = m[0];
     if (L0.T <= 0) return cudaSuccess;
     const bool bwd = L0.backward != 0;
-    if (few_group(m, n)) {
+    if (!dual && few_group(m, n)) {
         // up to 128 tokens: the kernel with the weights on the wide operand, one launch per member; the adapter terms
         // follow on the exact rank-r kernels
         for (int j = 0; j < n; j++) {
@@ -997,9 +1187,10 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
         const UmmaLaunch &L = m[j];
         const WeightDev *w = L.w;
         Member &M = p.m[j];
-        M.tm_hdr = L0.backward ? w->tm_hdr : w->tm_hdr_f;
-        M.tm_q0 = L0.backward ? w->tm_q0 : w->tm_q0_f;
-        M.tm_q1 = L0.backward ? w->tm_q1 : w->tm_q1_f;
+        // (64-row boxes: the backward's raw stages, and the dual forward's two half-tiles)
+        M.tm_hdr = (L0.backward || dual) ? w->tm_hdr : w->tm_hdr_f;
+        M.tm_q0 = (L0.backward || dual) ? w->tm_q0 : w->tm_q0_f;
+        M.tm_q1 = (L0.backward || dual) ? w->tm_q1 : w->tm_q1_f;
         const int rows = eff_rows(L);
         M.row_base = L.row_base;
         if (bwd || j == 0) {
@@ -1024,6 +1215,15 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
             M.lora_flag = L.lora_flag;
         }
         int count;
+        if (dual) {
+            // every tile holds 64 rows of both members: all tiles are listed under member 0
+            count = j == 0 ? rows / 64 : 0;
+            if (pair && j == 0) count = (count + 1) & ~1;
+            M.first = j == 0 ? 0 : 0x7fffffff;
+            M.count = count;
+            first += count;
+            continue;
+        }
         if (bwd) {
             count = (rows + 63) / 64;
         } else {
@@ -1040,6 +1240,12 @@ cudaError_t launch_umma_group(const UmmaLaunch *m, int n, cudaStream_t s, const 
     p.K = L0.w->K;
     p.units = bwd ? first : L0.w->K / 128;
     p.splits = L0.splits < 1 ? 1 : (L0.splits > p.units ? p.units : L0.splits);
+    if (dual) {
+        p.splits = 1;
+        p.dual = 1;
+        p.h16 = dual->h16;
+        p.ld_h16 = dual->ld_h16;
+    }
     // plain stores when one CTA owns each output tile and the output is to be written, not added to: a forward without
     // split-K, and a backward without split-K whose caller asked for "dX =" (out_assign)
     p.atomic_out = bwd ? ((p.splits > 1 || !L0.out_assign) ? 1 : 0) : (p.splits > 1 || L0.out_prefilled ? 1 : 0);

@@ -147,6 +147,38 @@ def test_forward_backward_matches_cpu_chain(G, oracle, mode, checkpoint, mix, T)
     eng.close()
 
 
+@pytest.mark.parametrize("checkpoint,mix,T", [(True, True, 300), (False, False, 200)])
+def test_dual_ffn_forward_matches_cpu_chain(G, oracle, checkpoint, mix, T, monkeypatch):
+    """gate | up in one launch with SiLU(gate) * up formed in its epilogue (the engine takes it where the 64-feature tiles
+    fill the GPU; GT_FFN_DUAL_MIN_TILES lets this small model take it too): same loss and gradients as the CPU chain, one
+    SwiGLU launch less per block forward."""
+    model = _make_model(oracle, mix=mix, bias=True, seed=13)
+    tokens, labels = _tokens(np.random.default_rng(T), model["cfg"]["vocab"], T)
+    grads = oracle.new_grads(model)
+    want_loss = oracle.model_forward_backward(model, tokens, labels, grads)
+    want = oracle.flat_grads(model, grads)
+    launches, res = [], []
+    for min_tiles in ("1", "1000000"):
+        monkeypatch.setenv("GT_FFN_DUAL_MIN_TILES", min_tiles)
+        eng = G.Engine(0, G.MATH_BF16)
+        m, handles, heads, n = _to_device(G, eng, model, max_tokens=T, checkpoint=checkpoint, graph=False)
+        eng.profile_read(reset=True)
+        loss = m.forward_backward(tokens, labels)
+        launches.append(eng.profile_read(reset=True)["kernel_launches"])
+        got = _device_grads(handles)
+        assert abs(loss - want_loss) < 5e-3 * abs(want_loss), (loss, want_loss)
+        assert _cos(got, want) > 0.99 and oracle.rel_fro(got, want) < 1.5e-1
+        res.append((loss, got))
+        _free(m, handles, heads)
+        eng.close()
+    # the two routes do the same arithmetic (fp32 accumulators, fp32 SiLU, one rounding to bf16): they differ by the
+    # run-to-run spread of the atomic sums only
+    assert abs(res[0][0] - res[1][0]) < 2e-5 * abs(res[1][0]) and oracle.rel_fro(res[0][1], res[1][1]) < 1e-2
+    n_layers = len(model["layers"])
+    # every block forward (and every recomputed one: all but the last block's) runs without its SwiGLU launch
+    assert launches[1] - launches[0] == n_layers + (n_layers - 1 if checkpoint else 0), launches
+
+
 def test_checkpointing_changes_nothing(G, oracle):
     eng = G.Engine(0, G.MATH_FP16)
     model = _make_model(oracle, seed=5)
