@@ -147,12 +147,13 @@ def test_forward_backward_matches_cpu_chain(G, oracle, mode, checkpoint, mix, T)
     eng.close()
 
 
-@pytest.mark.parametrize("checkpoint,mix,T", [(True, True, 300), (False, False, 200)])
-def test_dual_ffn_forward_matches_cpu_chain(G, oracle, checkpoint, mix, T, monkeypatch):
+@pytest.mark.parametrize("checkpoint,mix,T,zero_b,rank", [(True, True, 300, False, 16), (False, False, 200, True, 16), (True, False, 160, False, 24)])
+def test_dual_ffn_forward_matches_cpu_chain(G, oracle, checkpoint, mix, T, zero_b, rank, monkeypatch):
     """gate | up in one launch with SiLU(gate) * up formed in its epilogue (the engine takes it where the 64-feature tiles
     fill the GPU; GT_FFN_DUAL_MIN_TILES lets this small model take it too): same loss and gradients as the CPU chain, one
-    SwiGLU launch less per block forward."""
-    model = _make_model(oracle, mix=mix, bias=True, seed=13)
+    SwiGLU launch less per block forward.  Also with B == 0 (no rank-update stage at all) and with rank 24 (both adapters'
+    ranks, padded to 32 each, fill the one 64-deep stage)."""
+    model = _make_model(oracle, mix=mix, bias=True, seed=13, zero_b=zero_b, R=rank)
     tokens, labels = _tokens(np.random.default_rng(T), model["cfg"]["vocab"], T)
     grads = oracle.new_grads(model)
     want_loss = oracle.model_forward_backward(model, tokens, labels, grads)
