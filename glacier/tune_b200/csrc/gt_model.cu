@@ -505,6 +505,9 @@ int gt_model_forward_backward(gt_model *m, const int32_t *tokens, const int32_t 
     gt_engine *e = m->eng;
     std::lock_guard<std::mutex> lk(e->mu);
     GT_CUDA(cudaSetDevice(e->device));
+    // collectives of an earlier call that no optimizer step has waited for read the gradient buffer this call adds into
+    rc = join_comm(e);
+    if (rc != GT_OK) return rc;
     rc = stage_inputs(m, tokens, labels, T, flags);
     if (rc != GT_OK) return rc;
     bool queued = false;
