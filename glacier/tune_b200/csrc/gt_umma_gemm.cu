@@ -22,7 +22,9 @@
 //
 // One launch serves up to three member projections (forward: they share the activation tiles, each tile index belongs
 // to one member; backward: their contraction ranges are concatenated and all sum into one dX), each with its own
-// rank-update stage when it has an adapter.
+// rank-update stage when it has an adapter.  The dual forward (Params.dual) is the gate | up launch of a SwiGLU block:
+// every tile holds 64 rows of both members, interleaved so that one warp reads gate and up of a feature from its own
+// TMEM quadrant, and the epilogue writes SiLU(gate) * up as 16-bit values (gate and up themselves only where wanted).
 //
 // The dequantized tile image is the same for both directions: row = weight row n, 128 bytes = 64 consecutive
 // k, chunks XOR-swizzled by (row & 7).  Forward reads it as a K-major A operand (M = n, K = k); backward
@@ -60,7 +62,7 @@ constexpr int kOffX = 0;
 constexpr int kOffBar = kNumA * 32768 + kNumA * kAStageBytes + 32768;
 constexpr int kMaxRaw = 16;
 constexpr int kBarBytes = 512;
-constexpr int kDequantWarps = 16;   // two groups of 8
+constexpr int kDequantWarps = 16;   // four groups of 4
 constexpr int kThreads = 32 * (4 + kDequantWarps);   // + weight producer (0), two MMA issuers (1, 18), activation producer (19)
 constexpr int kIssuer2Warp = 18, kActProducerWarp = 19;
 constexpr int kSmemBytes = kOffBar + kBarBytes + 1024;   // + slack for 1024-byte alignment
