@@ -1,4 +1,4 @@
-// C++ host mirror of the reference's projection API over the C ABI of libglaciertune_b200.so.
+// C++ host mirror of the reference's projection and training-step API over the C ABI of libglaciertune_b200.so.
 //
 // The reference host is C# (src/Glacier.Tune/Gpu/GpuLoraEngine*.cs, src/Glacier.Tune/Model/LoraAdapter.cs); this header
 // keeps its member names, argument order and error behaviour (a failing call throws, as CuDriver.Check does) so a
@@ -167,5 +167,78 @@ inline void BackwardGroup(GpuLoraEngine &engine, LoraAdapter *const *projections
     Check(gt_proj_backward_group(engine.Handle(), n, w, a, g, x.DataPointer, dXInput.DataPointer, x.Shape[0], GT_FLAG_DX_ASSIGN),
           "BackwardGroup");
 }
+
+// Replaces the training-step half of GgufLoraModel (src/Glacier.Tune/Model/GgufLoraModel.cs:370-557) and the step tail of
+// LoraTrainer (src/Glacier.Tune/Trainer/LoraTrainer.cs:217-231) with the device-resident driver: the seven projections
+// of every block are LoraAdapter objects of this header (their weights set with SetGpuBaseWeights), in the reference's
+// order q, k, v, o, gate, up, down (TransformerBlock.cs:149-165).
+class GgufLoraModel {
+public:
+    GgufLoraModel(GpuLoraEngine &engine, int layers, int hidden, int heads, int kvHeads, int headDim, int ffn, int vocab, int maxTokens,
+                  float rmsEps = 1e-6f, float ropeTheta = 1e6f, bool checkpointActivations = true)
+        : engine_(engine) {
+        gt_model_config cfg{};
+        cfg.n_layers = layers;
+        cfg.hidden = hidden;
+        cfg.n_heads = heads;
+        cfg.n_kv_heads = kvHeads;
+        cfg.head_dim = headDim;
+        cfg.ffn = ffn;
+        cfg.vocab = vocab;
+        cfg.rms_eps = rmsEps;
+        cfg.rope_theta = ropeTheta;
+        cfg.max_tokens = maxTokens;
+        cfg.checkpoint = checkpointActivations ? 1 : 0;
+        Check(gt_model_create(engine.Handle(), &cfg, &model_), "gt_model_create");
+    }
+    ~GgufLoraModel() {
+        if (model_) gt_model_destroy(model_);
+    }
+    GgufLoraModel(const GgufLoraModel &) = delete;
+    GgufLoraModel &operator=(const GgufLoraModel &) = delete;
+
+    // projections[7]: q, k, v, o, gate, up, down; attnNorm / ffnNorm: host arrays [hidden]
+    void SetBlock(int layer, LoraAdapter *const *projections, const float *attnNorm, const float *ffnNorm) {
+        const gt_weight *w[7];
+        gt_adapter *a[7];
+        for (int j = 0; j < 7; j++) {
+            w[j] = projections[j]->Weight();
+            a[j] = projections[j]->Handle();
+        }
+        Check(gt_model_set_block(model_, layer, w, a, attnNorm, ffnNorm), "gt_model_set_block");
+    }
+    void SetHead(gt_weight *embedding, const float *outNorm, gt_weight *lmHead) {
+        Check(gt_model_set_head(model_, embedding, outNorm, lmHead), "gt_model_set_head");
+    }
+    // one flat gradient buffer in the reference's parameter order; returns its length
+    int64_t BindGradients() {
+        int64_t n = 0;
+        Check(gt_model_bind_grads(model_, nullptr, &n), "gt_model_bind_grads");
+        return n;
+    }
+    // GgufLoraModel.ComputeLoss (GgufLoraModel.cs:370-426)
+    float ComputeLoss(const int32_t *inputTokens, const int32_t *targetTokens, int seqLen) {
+        float loss = 0.f;
+        Check(gt_model_loss(model_, inputTokens, targetTokens, seqLen, &loss, nullptr, 0), "gt_model_loss");
+        return loss;
+    }
+    // GgufLoraModel.ForwardLossAndBackward (GgufLoraModel.cs:428-557): the adapters' gradients accumulate
+    float ForwardLossAndBackward(const int32_t *inputTokens, const int32_t *targetTokens, int seqLen) {
+        float loss = 0.f;
+        Check(gt_model_forward_backward(model_, inputTokens, targetTokens, seqLen, &loss, 0), "gt_model_forward_backward");
+        return loss;
+    }
+    // ScaleAccumulatedGradients -> ClipGradients -> AdamW -> ZeroGrad (LoraTrainer.cs:217-231); returns the pre-clip norm
+    double OptimizerStep(float lr, float beta1, float beta2, float eps, float weightDecay, float gradScale, double maxNorm, int step) {
+        double norm = 0.0;
+        Check(gt_model_optimizer_step(model_, lr, beta1, beta2, eps, weightDecay, gradScale, maxNorm, step, &norm), "gt_model_optimizer_step");
+        return norm;
+    }
+    gt_model *Handle() const { return model_; }
+
+private:
+    GpuLoraEngine &engine_;
+    gt_model *model_ = nullptr;
+};
 
 }  // namespace Glacier::Tune
