@@ -99,3 +99,31 @@ def test_new_entry_points_reject_null_arguments():
     assert lib.gt_model_destroy(None) == 0
     assert lib.gt_supports_attention(512, 128) == 1 and lib.gt_supports_attention(512, 96) == 0
     assert capi.supports(capi.TYPE_F16, capi.DIR_FORWARD)
+
+
+def test_ctypes_structs_match_the_header(tmp_path):
+    """The ctypes mirrors of gt_config / gt_model_config have the header's size and field offsets (a C compiler is the
+    judge): a field added on one side only would shift everything behind it silently."""
+    import ctypes as C
+    import shutil
+    import subprocess
+    from glacier.tune_b200 import capi as G
+    HEADER = os.path.join(ROOT, "include", "glaciertune_b200.h")
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    fields_cfg = ["device", "math_mode", "stream", "max_tokens", "max_features"]
+    fields_model = ["n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "rms_eps", "rope_theta", "max_tokens",
+                    "checkpoint", "no_graph", "reserved"]
+    src = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {",
+           'printf("%zu\\n", sizeof(gt_config));']
+    src += [f'printf("%zu\\n", offsetof(gt_config, {f}));' for f in fields_cfg]
+    src += ['printf("%zu\\n", sizeof(gt_model_config));']
+    src += [f'printf("%zu\\n", offsetof(gt_model_config, {f}));' for f in fields_model]
+    src += ["return 0; }"]
+    c_file, exe = tmp_path / "layout.c", tmp_path / "layout"
+    c_file.write_text("\n".join(src))
+    subprocess.check_call(["gcc", "-std=c11", "-o", str(exe), str(c_file)])
+    got = [int(x) for x in subprocess.check_output([str(exe)]).split()]
+    want = [C.sizeof(G.GtConfig)] + [getattr(G.GtConfig, f).offset for f in fields_cfg]
+    want += [C.sizeof(G.GtModelConfig)] + [getattr(G.GtModelConfig, f).offset for f in fields_model]
+    assert got == want
