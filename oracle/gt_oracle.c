@@ -29,8 +29,11 @@
  *           (tests/Glacier.Tune.Tests/GradientAndGpuParityTests.cs:174-260).
  *   Layer glue — SwiGLU and RoPE restate in-repo sources (src/Glacier.Tune/Kernels/SwiGluKernel.cs,
  *           RoPEKernel.cs); the reference holds no known answers for them, the tests pin them by
- *           closed forms, finite differences and the rotation's inverse.  RMSNorm lives in
- *           Glacier.Tensor 1.1.0 (not vendored): textbook definition, PARITY UNPINNED.
+ *           closed forms, finite differences and the rotation's inverse, and by the Qwen2 operators
+ *           of the `transformers` package (rotate-half RoPE, SiLU * up; tests/test_oracle_pins_qwen2.py).
+ *           RMSNorm lives in Glacier.Tensor 1.1.0 (not vendored): textbook definition, PARITY UNPINNED
+ *           against the reference; pinned, forward and backward, to `Qwen2RMSNorm` of transformers
+ *           5.5.0 - the definition of the architecture the workload names (same test file).
  */
 #include <math.h>
 #include <stddef.h>
@@ -713,8 +716,9 @@ void gt_oracle_rope(float *q, float *k, int T, int heads_q, int heads_kv, int he
 
 /* RMSNorm forward: y[t, :] = x[t, :] * rsqrt(mean(x[t, :]^2) + eps) * w.  The implementation the reference calls
  * (ElementwiseKernels.RMSNorm, Glacier.Tensor 1.1.0, call sites src/Glacier.Tune/Model/TransformerBlock.cs:318,524) is not
- * in the repository: this is the textbook definition, PARITY UNPINNED.  The mean is accumulated in fp64 here so that
- * the oracle is the more accurate side. */
+ * in the repository: this is the textbook definition, PARITY UNPINNED against the reference and pinned to Qwen2RMSNorm of
+ * the transformers package (tests/test_oracle_pins_qwen2.py).  The mean is accumulated in fp64 here so that the oracle
+ * is the more accurate side. */
 void gt_oracle_rmsnorm_forward(const float *x, const float *w, float *y, int T, int H, float eps) {
 #pragma omp parallel for schedule(static)
     for (int t = 0; t < T; t++) {
@@ -727,7 +731,8 @@ void gt_oracle_rmsnorm_forward(const float *x, const float *w, float *y, int T, 
 }
 
 /* RMSNorm backward with frozen weight (the reference passes dW = null, TransformerBlock.cs:672,827):
- *   g = dy * w;  dx = r * g - x * r^3 * mean(g * x),  r = rsqrt(mean(x^2) + eps).  PARITY UNPINNED (as above). */
+ *   g = dy * w;  dx = r * g - x * r^3 * mean(g * x),  r = rsqrt(mean(x^2) + eps).  Pinning as above (autograd through
+ *   Qwen2RMSNorm). */
 void gt_oracle_rmsnorm_backward(const float *dy, const float *x, const float *w, float *dx, int T, int H, float eps) {
 #pragma omp parallel for schedule(static)
     for (int t = 0; t < T; t++) {
