@@ -1,5 +1,5 @@
-"""CPU tests: the oracle's layer operators against the Qwen2 definitions that ship with `transformers` and against torch
-autograd - independent implementations of the architecture the workload names (Qwen2.5-7B: RMSNorm with eps 1e-6,
+"""CPU tests: the oracle's layer operators, and its whole training-step chain, against the Qwen2 definitions that ship
+with `transformers` and against torch autograd - independent implementations of the architecture the workload names (Qwen2.5-7B: RMSNorm with eps 1e-6,
 rotate-half RoPE with theta 1e6, SwiGLU, causal grouped-query attention with 1/sqrt(head_dim) scaling).
 
 The reference's RMSNorm lives in a package that is not in its repository, so the oracle restates the textbook form;
@@ -91,3 +91,72 @@ def test_attention_matches_torch_causal_gqa(oracle, T, hq, hk, d):
     assert np.allclose(dq, qt.grad.numpy(), rtol=1e-4, atol=5e-6)
     assert np.allclose(dk, kt.grad.numpy(), rtol=1e-4, atol=5e-6)
     assert np.allclose(dv, vt.grad.numpy(), rtol=1e-4, atol=5e-6)
+
+
+def _qwen2_params(oracle, model, adapters):
+    """State dict of a Qwen2ForCausalLM built from the oracle's model dict: every projection weight is the exactly
+    dequantized base plus the adapter's delta s * (A B)^T, with A and B the torch leaves in `adapters`."""
+    cfg = model["cfg"]
+    H = cfg["hidden"]
+    names = {"q": "self_attn.q_proj", "k": "self_attn.k_proj", "v": "self_attn.v_proj", "o": "self_attn.o_proj", "gate": "mlp.gate_proj",
+             "up": "mlp.up_proj", "down": "mlp.down_proj"}
+    sd = {}
+    et, ew = model["embed"]
+    lt, lw = model["lm_head"]
+    sd["model.embed_tokens.weight"] = torch.from_numpy(oracle.dequant_rows(et, ew, H, 0, cfg["vocab"]).reshape(cfg["vocab"], H)).double()
+    sd["lm_head.weight"] = torch.from_numpy(oracle.dequant_rows(lt, lw, H, 0, cfg["vocab"]).reshape(cfg["vocab"], H)).double()
+    sd["model.norm.weight"] = torch.from_numpy(model["out_norm"]).double()
+    for l, layer in enumerate(model["layers"]):
+        pre = f"model.layers.{l}."
+        sd[pre + "input_layernorm.weight"] = torch.from_numpy(layer["norm1"]).double()
+        sd[pre + "post_attention_layernorm.weight"] = torch.from_numpy(layer["norm2"]).double()
+        for name, mod in names.items():
+            p = layer["proj"][name]
+            W = torch.from_numpy(oracle.dequant_rows(p["qtype"], p["w"], p["K"], 0, p["N"]).reshape(p["N"], p["K"])).double()
+            A, B = adapters[l][name]
+            sd[pre + mod + ".weight"] = W + p["scaling"] * (A @ B).T
+            if name in ("q", "k", "v"):
+                bias = p["bias"] if p["bias"] is not None else np.zeros(p["N"], np.float32)
+                sd[pre + mod + ".bias"] = torch.from_numpy(bias).double()
+    return sd
+
+
+@pytest.mark.parametrize("mix", [False, True])
+def test_model_chain_matches_qwen2_for_causal_lm(oracle, mix):
+    """The CPU chain of the training step (oracle.model_forward_backward: the order of TransformerBlock.Forward / Backward and
+    GgufLoraModel.ForwardLossAndBackward) against `Qwen2ForCausalLM` of the transformers package in fp64, built from the same
+    dequantized weights with the adapters merged as differentiable terms: the loss, and the gradient of every A and B."""
+    transformers = pytest.importorskip("transformers")
+    from test_gpu_model import _make_model, _tokens
+    model = _make_model(oracle, n_layers=2, H=256, HQ=2, HK=1, F=512, V=300, mix=mix, bias=True, seed=31)
+    cfg = model["cfg"]
+    T = 24
+    tokens, labels = _tokens(np.random.default_rng(7), cfg["vocab"], T)
+    grads = oracle.new_grads(model)
+    loss = oracle.model_forward_backward(model, tokens, labels, grads)
+    got = oracle.flat_grads(model, grads)
+
+    hf_cfg = transformers.Qwen2Config(vocab_size=cfg["vocab"], hidden_size=cfg["hidden"], intermediate_size=cfg["ffn"],
+                                      num_hidden_layers=len(model["layers"]), num_attention_heads=cfg["n_heads"],
+                                      num_key_value_heads=cfg["n_kv_heads"], rms_norm_eps=cfg["rms_eps"], max_position_embeddings=64,
+                                      rope_parameters={"rope_type": "default", "rope_theta": cfg["rope_theta"]},
+                                      tie_word_embeddings=False, use_sliding_window=False, attention_dropout=0.0)
+    hf_cfg._attn_implementation = "eager"
+    assert hf_cfg.hidden_size // hf_cfg.num_attention_heads == cfg["head_dim"]
+    hf = transformers.Qwen2ForCausalLM(hf_cfg).double().eval()
+    adapters = []
+    for layer in model["layers"]:
+        adapters.append({name: (torch.from_numpy(layer["proj"][name]["a"]).double().requires_grad_(True),
+                                torch.from_numpy(layer["proj"][name]["b"]).double().requires_grad_(True)) for name in oracle.PROJ_NAMES})
+    sd = _qwen2_params(oracle, model, adapters)
+    ids = torch.from_numpy(tokens.astype(np.int64))[None]
+    out = torch.func.functional_call(hf, sd, (ids,), {"use_cache": False})
+    logits = out.logits[0]                                                    # [T, vocab]
+    want_loss = torch.nn.functional.cross_entropy(logits, torch.from_numpy(labels.astype(np.int64)), ignore_index=-100)
+    want_loss.backward()
+    want = np.concatenate([t.grad.numpy().reshape(-1) for ad in adapters for name in oracle.PROJ_NAMES for t in ad[name]])
+    ref_loss = float(want_loss.detach())
+    assert abs(loss - ref_loss) < 2e-6 * abs(ref_loss), (loss, ref_loss)
+    assert want.size == got.size
+    cos = float(got.astype(np.float64) @ want / (np.linalg.norm(got) * np.linalg.norm(want)))
+    assert cos > 0.999999 and oracle.rel_fro(got, want) < 2e-4, (cos, oracle.rel_fro(got, want))
