@@ -160,3 +160,53 @@ def test_model_chain_matches_qwen2_for_causal_lm(oracle, mix):
     assert want.size == got.size
     cos = float(got.astype(np.float64) @ want / (np.linalg.norm(got) * np.linalg.norm(want)))
     assert cos > 0.999999 and oracle.rel_fro(got, want) < 2e-4, (cos, oracle.rel_fro(got, want))
+
+
+@pytest.mark.parametrize("qname", ["Q4_K", "Q6_K"])
+def test_lora_projection_matches_torch_autograd(oracle, qname):
+    """LoraAdapter.Forward / Backward on the CPU path (Y = X W^T + b + s (X A) B; dX, dA, dB) against torch autograd in fp64
+    over the exactly dequantized weight."""
+    from glacier.tune_b200 import synth as S
+    qt = S.TYPE_Q4_K if qname == "Q4_K" else S.TYPE_Q6_K
+    c = S.make_projection_case(qt, 96, 512, 11, seed=77)
+    N, K, T, R, s = c["N"], c["K"], 11, 16, c["scaling"]
+    bias = (0.1 * np.random.default_rng(5).standard_normal(N)).astype(np.float32)
+    W = torch.from_numpy(oracle.dequant_rows(qt, c["w"], K, 0, N).reshape(N, K)).double()
+    X, A, B = _t(c["x"]), _t(c["a"]), _t(c["b"])
+    Y = X @ W.T + torch.from_numpy(bias).double() + s * (X @ A) @ B
+    Y.backward(torch.from_numpy(c["dy"]).double())
+    y = oracle.proj_forward(qt, c["w"], bias, c["x"], K, N, T, c["a"], c["b"], R, s)
+    dx, da, db = oracle.proj_backward(qt, c["w"], c["dy"], c["x"], K, N, T, c["a"], c["b"], R, s)
+    assert oracle.rel_fro(y, Y.detach().numpy()) < 1e-6
+    assert oracle.rel_fro(dx, X.grad.numpy()) < 1e-6
+    assert oracle.rel_fro(da, A.grad.numpy()) < 1e-6 and oracle.rel_fro(db, B.grad.numpy()) < 1e-6
+
+
+def test_cross_entropy_matches_torch(oracle):
+    """The streaming cross-entropy (vocabulary tiles, ignored labels) against torch.nn.functional.cross_entropy in fp64."""
+    rng = np.random.default_rng(8)
+    T, H, V = 9, 48, 1000
+    hidden = rng.standard_normal((T, H)).astype(np.float32)
+    W = (0.2 * rng.standard_normal((V, H))).astype(np.float32)
+    labels = rng.integers(0, V, T).astype(np.int32)
+    labels[3] = -100
+    ht = _t(hidden)
+    want = torch.nn.functional.cross_entropy(ht @ torch.from_numpy(W).double().T, torch.from_numpy(labels.astype(np.int64)), ignore_index=-100)
+    want.backward()
+    loss, valid, dh = oracle.cross_entropy(oracle.TYPE_F32, W, hidden, labels, V, tile=256)
+    assert valid == T - 1 and abs(loss - float(want.detach())) < 1e-6 * float(want.detach())
+    assert oracle.rel_fro(dh, ht.grad.numpy()) < 1e-5 and np.all(dh[3] == 0.0)
+
+
+def test_clip_matches_torch_clip_grad_norm(oracle):
+    """ClipGradients (global L2 norm over every gradient, scale by max / (norm + 1e-6) when above) against
+    torch.nn.utils.clip_grad_norm_, which uses the same epsilon."""
+    rng = np.random.default_rng(9)
+    g = (3 * rng.standard_normal(5000)).astype(np.float32)
+    p = torch.nn.Parameter(torch.zeros(5000, dtype=torch.float64))
+    p.grad = torch.from_numpy(g).double()
+    want_norm = float(torch.nn.utils.clip_grad_norm_([p], max_norm=1.0))
+    got = g.copy()
+    norm = oracle.clip_gradients(got, 1.0)
+    assert abs(norm - want_norm) < 1e-6 * want_norm
+    assert oracle.rel_fro(got, p.grad.numpy()) < 1e-6
